@@ -1,0 +1,348 @@
+#!/usr/bin/env python
+"""Benchmark of the frame-parallel render path: batched harmonic+noise synthesis forward +
+multi-scale spectral loss (B=16 voices per GPU, 64000 frames, 100 harmonics, 65 noise bands as
+257-tap FIR, FFT sizes 2048..64, 75 % overlap), on synthetic seeded inputs.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+A step is one pass of the path over one batch.  `value` is synthesized samples per second
+(voices x frames, all GPUs) with inputs resident in HBM; `e2e` is the same metric through the
+host-buffer C-ABI call (host->device copies of every input and the device->host loss read inside
+the timed region).  Multi-GPU: one process per GPU (torchrun), voices sharded, no data-path
+collective (forward-only render): weak scaling.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for p in (ROOT, os.path.join(ROOT, "dgen-audio_b200")):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+import numpy as np  # noqa: E402
+
+METRIC = "synthesized samples/sec (batch x frames) fwd+loss"
+UNIT = "samples/s"
+CFG = dict(B=16, T=64000, K=100, F=1000, sr=16000.0, nbands=65, taps=257)
+SIZES = (2048, 1024, 512, 256, 128, 64)
+SEED = 20260001
+
+
+def config_json(n_gpus):
+    return {"workload": "harmonic+noise synthesis fwd + multi-scale spectral loss (BASELINE.json configs[1])",
+            "voices_per_gpu": CFG["B"], "frames": CFG["T"], "harmonics": CFG["K"], "control_frames": CFG["F"],
+            "sample_rate": CFG["sr"], "noise_bands": CFG["nbands"], "fir_taps": CFG["taps"],
+            "fft_sizes": list(SIZES), "overlap": 0.75, "global_voices": CFG["B"] * n_gpus,
+            "phase_mode": "scan", "sharding": "voices across GPUs, no collective",
+            "l2": "L2 flushed (512 MiB write) between timed steps"}
+
+
+# --------------------------------------------------------------------------------------------------
+# clocks
+# --------------------------------------------------------------------------------------------------
+class ClockSampler:
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.th = threading.Thread(target=self._read, daemon=True)
+            self.th.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[1]))
+                mx.append(float(r[2]))
+            except Exception:
+                continue
+            for name, col in (("hw_slowdown", 5), ("hw_thermal_slowdown", 6), ("sw_thermal_slowdown", 7),
+                              ("sw_power_cap", 8)):
+                if len(r) > col and r[col].lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------------------------------
+# CPU arm (oracle restatement of the reference C backend), used for cpu_baseline and --impl reference
+# --------------------------------------------------------------------------------------------------
+def cpu_arm(voices, threads, seed=SEED):
+    """Times render + loss of `voices` voices of the workload on the host with `threads` threads.
+    Returns (samples_per_s, seconds)."""
+    import tempfile
+    from concurrent.futures import ThreadPoolExecutor
+    from dgen_b200 import workloads as wl
+    from oracle import oracle as orc
+    out_dir = os.path.join(tempfile.gettempdir(), "dgen_oracle_native")
+    so = os.path.join(out_dir, "libdgen_oracle_fast.so")
+    try:
+        orc.build(out_dir=out_dir, march="-march=native")  # built on the machine that runs it
+        L = orc.lib(path=so)
+    except Exception:
+        L = orc.lib(fast=True)
+    d = wl.harmonic_noise_inputs(seed, B=voices, **{k: CFG[k] for k in ("T", "K", "F", "sr", "nbands", "taps")})
+    t = wl.harmonic_noise_inputs(seed + 1, B=voices, **{k: CFG[k] for k in ("T", "K", "F", "sr", "nbands", "taps")})
+    taps = wl.taps_from_bands(d)
+    rng = np.random.default_rng(0)
+    target = rng.standard_normal((voices, CFG["T"])).astype(np.float32) * 0.1
+    del t
+
+    def one(b):
+        sl = slice(b, b + 1)
+        a = orc.harmonic_noise_render(d["f0"][:, sl], d["uv"][:, sl], d["amps"][:, sl], d["gain"][:, sl],
+                                      d["noise_gain"][:, sl], taps[:, sl], d["noise"][sl], CFG["T"], CFG["sr"], L=L)
+        return orc.mss_loss(a, target[sl], sizes=SIZES, L=L)
+
+    one(0)  # warm-up (page in, build twiddles)
+    t0 = time.perf_counter()
+    with ThreadPoolExecutor(max_workers=threads) as ex:
+        list(ex.map(one, range(voices)))
+    dt = time.perf_counter() - t0
+    return voices * CFG["T"] / dt, dt
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    cores = os.cpu_count() or 1
+    threads = max(1, min(cores, 64))
+    voices = threads * 2 if threads > 1 else 4
+    vals, secs = [], []
+    for _ in range(max(1, args.warmup > 0)):
+        cpu_arm(min(voices, threads), threads)
+    for _ in range(args.steps):
+        v, s = cpu_arm(voices, threads)
+        vals.append(v)
+        secs.append(s)
+    value = float(np.mean(vals))
+    ms = float(np.mean(secs)) * 1e3
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": config_json(args.gpus),
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port",
+                             "sample": "%d voices x %d frames per step, render + 6-scale loss, one voice per thread; "
+                                       "CPU restatement of the reference C backend (the Swift compiler that emits "
+                                       "the reference's C is not available)" % (voices, CFG["T"])},
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+# --------------------------------------------------------------------------------------------------
+# GPU arm
+# --------------------------------------------------------------------------------------------------
+def run_ours(args, rank, world, local_rank):
+    import torch
+    import torch.distributed as dist
+    import dgen_b200
+    from dgen_b200 import workloads as wl
+
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    ctx = dgen_b200.Context(local_rank)
+    B, T, K, F, sr = CFG["B"], CFG["T"], CFG["K"], CFG["F"], CFG["sr"]
+    d = wl.harmonic_noise_inputs(SEED + 100 * rank, **CFG)
+    tg = wl.harmonic_noise_inputs(SEED + 100 * rank + 1, **CFG)
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    D = {k: dev(v) for k, v in d.items() if isinstance(v, np.ndarray)}
+    G = {k: dev(v) for k, v in tg.items() if isinstance(v, np.ndarray)}
+    audio = torch.empty(B, T, device="cuda")
+    loss = torch.zeros(1, dtype=torch.float64, device="cuda")
+    mss = dgen_b200.mss_params(B, T, SIZES)
+    import ctypes as C
+    hp = dgen_b200.HarmonicParams(B, T, K, F, sr, 1.0, dgen_b200.PHASE_SCAN, 0)
+    fp = dgen_b200.FirParams(B, T, F, CFG["taps"], 0.12, 1)
+    lib, h = ctx.lib, ctx.h
+    taps_buf = torch.empty(F, B, CFG["taps"], device="cuda")
+
+    def stage_taps(X):
+        ctx.check(lib.dgc_bands_to_taps(h, X["bands"].data_ptr(), X["W"].data_ptr(), F * B, CFG["nbands"], CFG["taps"],
+                                        taps_buf.data_ptr()))
+
+    def stage_harm(X, out):
+        ctx.check(lib.dgc_harmonic_render(h, C.byref(hp), X["f0"].data_ptr(), X["uv"].data_ptr(),
+                                          X["amps"].data_ptr(), X["gain"].data_ptr(), None, out.data_ptr()))
+
+    def stage_fir(X, out):
+        ctx.check(lib.dgc_fir_noise(h, C.byref(fp), X["noise"].data_ptr(), taps_buf.data_ptr(),
+                                    X["noise_gain"].data_ptr(), out.data_ptr()))
+
+    def stage_loss(pred, target):
+        ctx.check(lib.dgc_mss_loss_fwd(h, C.byref(mss), pred.data_ptr(), target.data_ptr(), None, loss.data_ptr()))
+
+    # target audio: rendered once from seed+1 (setup, untimed)
+    target = torch.empty(B, T, device="cuda")
+    stage_taps(G); stage_harm(G, target); stage_fir(G, target)
+    torch.cuda.synchronize()
+
+    def step():
+        stage_taps(D); stage_harm(D, audio); stage_fir(D, audio); stage_loss(audio, target)
+
+    flush = torch.empty(512 * 1024 * 1024 // 4, device="cuda")
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    launches0 = ctx.launch_count()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    barrier()
+    for s in range(args.steps):
+        flush.fill_(float(s))
+        evs[s][0].record()
+        step()
+        evs[s][1].record()
+    barrier()
+    launches = ctx.launch_count() - launches0
+    total_ms = sum(a.elapsed_time(b) for a, b in evs)
+    loss_val = float(loss.cpu()[0])
+
+    # per-stage times (device events, same L2-flush discipline) for the roofline of the dominant kernel
+    stages = {"bands_to_taps": lambda: stage_taps(D), "harmonic_render": lambda: stage_harm(D, audio),
+              "fir_noise": lambda: stage_fir(D, audio), "mss_loss_fwd": lambda: stage_loss(audio, target)}
+    stage_ms = {}
+    reps = max(3, min(args.steps, 10))
+    for name, fn in stages.items():
+        acc = 0.0
+        for r in range(reps):
+            flush.fill_(float(r))
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(); fn(); b.record()
+            torch.cuda.synchronize()
+            acc += a.elapsed_time(b)
+        stage_ms[name] = acc / reps
+
+    # end to end through the host-buffer entry point: pinned host inputs, H2D + D2H inside the timed region
+    pin = lambda a: torch.from_numpy(np.ascontiguousarray(a)).pin_memory()
+    P = {k: pin(v) for k, v in d.items() if isinstance(v, np.ndarray)}
+    target_host = pin(target.cpu().numpy())
+    st = dgen_b200.HnStep()
+    st.harm, st.fir, st.mss, st.nbands = hp, dgen_b200.FirParams(B, T, F, CFG["taps"], 0.12, 1), mss, CFG["nbands"]
+
+    def e2e_step():
+        return ctx.hn_forward_loss_host(st, P["f0"], P["uv"], P["amps"], P["gain"], P["noise_gain"], P["bands"],
+                                        P["W"], P["noise"], target_host)
+
+    for _ in range(max(3, args.warmup)):
+        e2e_loss = e2e_step()
+    barrier()
+    e2e_ms = 0.0
+    for s in range(args.steps):
+        flush.fill_(float(s))
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        e2e_loss = e2e_step()
+        b.record()
+        torch.cuda.synchronize()
+        e2e_ms += a.elapsed_time(b)
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    h2d = 4 * sum(int(P[k].numel()) for k in ("f0", "uv", "amps", "gain", "noise_gain", "bands", "W", "noise")) \
+        + 4 * int(target_host.numel())
+
+    t = torch.tensor([total_ms, e2e_ms], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms, e2e_ms = float(t[0]), float(t[1])
+    if rank == 0:
+        samples_per_step = B * T * world
+        value = samples_per_step * args.steps / (total_ms * 1e-3)
+        e2e_value = samples_per_step * args.steps / (e2e_ms * 1e-3)
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        except Exception:
+            pass
+        peak = float(peaks.get("hbm_gbs", 6650.0))
+        # algorithmic bytes per launch of each stage (fp32 = 4 bytes)
+        alg = {"harmonic_render": 4 * (B * F * (K + 2) + B * T),
+               "fir_noise": 4 * (B * T + B * F * CFG["taps"] + 2 * B * T),
+               "bands_to_taps": 4 * (B * F * CFG["nbands"] + B * F * CFG["taps"]),
+               "mss_loss_fwd": 2 * 4 * B * T * len(SIZES)}
+        dom = max(stage_ms, key=stage_ms.get)
+        achieved = alg[dom] / (stage_ms[dom] * 1e-3) / 1e9
+        step_bytes = sum(alg.values())
+        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": config_json(world), "clocks": clocks,
+                "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 8,
+                        "ms_per_step": e2e_ms / args.steps},
+                "gpu_launches": int(launches),
+                "roofline": {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "GB/s",
+                             "frac": achieved / peak, "traffic": None,
+                             "peak_source": "measured" if peaks else "fallback",
+                             "note": "the stage is FP32/SFU-issue bound, not HBM bound; see DESIGN.md"},
+                "stage_ms": stage_ms,
+                "whole_step": {"algorithmic_bytes": step_bytes,
+                               "achieved_gbs": step_bytes / (total_ms / args.steps * 1e-3) / 1e9},
+                "loss": loss_val, "e2e_loss": e2e_loss}
+        if not args.no_cpu and world == 1:
+            v, secs = cpu_arm(4, 1)
+            line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": 1, "kind": "port",
+                                    "sample": "4 voices x %d frames, render + 6-scale loss, single thread (%.1f s); "
+                                              "CPU restatement of the reference's single-threaded C backend"
+                                              % (T, secs)}
+        print(json.dumps(line))
+    ctx.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    if args.warmup < 3:
+        args.warmup = 3
+    run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

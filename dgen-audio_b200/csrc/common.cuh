@@ -1,0 +1,68 @@
+// Shared declarations of libdgen_cuda: context object, error plumbing, launch helpers.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <map>
+#include <string>
+#include <utility>
+
+#include "../../include/dgen_cuda.h"
+
+#define DGC_EXPORT extern "C" __attribute__((visibility("default")))
+
+struct dgc_ctx {
+  int device = 0;
+  cudaStream_t own_stream = nullptr;
+  cudaStream_t stream = nullptr;
+  cudaEvent_t ev_begin = nullptr, ev_end = nullptr, ev_sync = nullptr;
+  int32_t *status_dev = nullptr;  // device status word: kernels report bounded-wait failures here
+  int64_t launches = 0;
+  char err[512] = {0};
+  int sm_count = 148;
+  // context-owned scratch (grown on demand, never shrunk)
+  float *scratch = nullptr;
+  uint64_t scratch_floats = 0;
+  // cached data-independent tables
+  std::map<std::pair<int, int>, float *> playheads;  // (F, T) -> device clock
+  std::map<int, float *> hann_sym;                   // N -> symmetric Hann (spectral loss)
+  std::map<int, float *> hann_per;                   // N -> periodic Hann (hann())
+  std::map<int, float2 *> twiddles;                  // N -> exp(-2 pi i m / N), m < N
+  double *loss_accum = nullptr;                      // small device buffer for reductions
+  // staging for the host-buffer composite entry points
+  float *stage_dev = nullptr;
+  uint64_t stage_floats = 0;
+};
+
+int32_t dgc_fail(dgc_ctx *ctx, int32_t code, const char *fmt, ...);
+int32_t dgc_check_launch(dgc_ctx *ctx, const char *what);
+// returns device pointer to at least n floats of context scratch (nullptr + error set on failure)
+float *dgc_ctx_scratch(dgc_ctx *ctx, uint64_t nfloats);
+const float *dgc_ctx_hann_sym(dgc_ctx *ctx, int N);
+const float *dgc_ctx_hann_per(dgc_ctx *ctx, int N);
+const float2 *dgc_ctx_twiddles(dgc_ctx *ctx, int N);
+
+#define DGC_CUDA(ctx, call)                                                                  \
+  do {                                                                                       \
+    cudaError_t e__ = (call);                                                                \
+    if (e__ != cudaSuccess)                                                                  \
+      return dgc_fail(ctx, e__ == cudaErrorMemoryAllocation ? DGC_ERR_OOM : DGC_ERR_CUDA,    \
+                      "%s: %s", #call, cudaGetErrorString(e__));                             \
+  } while (0)
+
+#define DGC_REQUIRE(ctx, cond, msg)                            \
+  do {                                                         \
+    if (!(cond)) return dgc_fail(ctx, DGC_ERR_INVALID, "%s: %s", __func__, msg); \
+  } while (0)
+
+#define DGC_LAUNCHED(ctx, name)                     \
+  do {                                              \
+    (ctx)->launches++;                              \
+    int32_t rc__ = dgc_check_launch(ctx, name);     \
+    if (rc__ != DGC_OK) return rc__;                \
+  } while (0)
+
+static inline int dgc_div_up(int64_t a, int64_t b) { return (int)((a + b - 1) / b); }
+static inline bool dgc_is_pow2(int n) { return n > 0 && (n & (n - 1)) == 0; }

@@ -1,0 +1,246 @@
+// Context, arena, tables, timing: the plumbing every entry point of libdgen_cuda shares.
+#include <math.h>
+#include <stdarg.h>
+
+#include <chrono>
+#include <thread>
+#include <vector>
+
+#include "common.cuh"
+
+struct dgc_arena {
+  dgc_ctx *ctx;
+  float *ptr;
+  uint64_t n;
+};
+
+int32_t dgc_fail(dgc_ctx *ctx, int32_t code, const char *fmt, ...) {
+  if (ctx) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(ctx->err, sizeof(ctx->err), fmt, ap);
+    va_end(ap);
+  }
+  return code;
+}
+
+int32_t dgc_check_launch(dgc_ctx *ctx, const char *what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return dgc_fail(ctx, DGC_ERR_CUDA, "launch %s: %s", what, cudaGetErrorString(e));
+  return DGC_OK;
+}
+
+float *dgc_ctx_scratch(dgc_ctx *ctx, uint64_t nfloats) {
+  if (nfloats <= ctx->scratch_floats) return ctx->scratch;
+  // the old buffer may still be in use by enqueued work: free it only after the stream drains
+  if (ctx->scratch) {
+    cudaStreamSynchronize(ctx->stream);
+    cudaFree(ctx->scratch);
+    ctx->scratch = nullptr;
+    ctx->scratch_floats = 0;
+  }
+  float *p = nullptr;
+  cudaError_t e = cudaMalloc(&p, nfloats * sizeof(float));
+  if (e != cudaSuccess) {
+    dgc_fail(ctx, DGC_ERR_OOM, "scratch of %llu floats: %s", (unsigned long long)nfloats, cudaGetErrorString(e));
+    return nullptr;
+  }
+  ctx->scratch = p;
+  ctx->scratch_floats = nfloats;
+  return p;
+}
+
+template <typename T>
+static T *upload_table(dgc_ctx *ctx, const std::vector<T> &h) {
+  T *d = nullptr;
+  if (cudaMalloc(&d, h.size() * sizeof(T)) != cudaSuccess) {
+    dgc_fail(ctx, DGC_ERR_OOM, "table allocation failed");
+    return nullptr;
+  }
+  // tables are tiny and built once: a synchronous copy keeps their lifetime simple
+  if (cudaMemcpy(d, h.data(), h.size() * sizeof(T), cudaMemcpyHostToDevice) != cudaSuccess) {
+    dgc_fail(ctx, DGC_ERR_CUDA, "table upload failed");
+    cudaFree(d);
+    return nullptr;
+  }
+  return d;
+}
+
+// Symmetric Hann evaluated in double and rounded to float, as the reference builds its static
+// window tensor for the spectral loss (Sources/DGen/HigherOps.swift:72-76).
+const float *dgc_ctx_hann_sym(dgc_ctx *ctx, int N) {
+  auto it = ctx->hann_sym.find(N);
+  if (it != ctx->hann_sym.end()) return it->second;
+  std::vector<float> h(N);
+  for (int i = 0; i < N; ++i) h[i] = (float)(0.5 * (1.0 - cos(2.0 * M_PI * (double)i / (double)(N - 1))));
+  float *d = upload_table(ctx, h);
+  if (d) ctx->hann_sym[N] = d;
+  return d;
+}
+
+// hann(n) of the public API: periodic, evaluated in single precision with Swift's Float.pi
+// (pi rounded toward zero), Sources/DGenLazy/SpectralTensorOps.swift:42-49.
+const float *dgc_ctx_hann_per(dgc_ctx *ctx, int N) {
+  auto it = ctx->hann_per.find(N);
+  if (it != ctx->hann_per.end()) return it->second;
+  std::vector<float> h(N);
+  const float swift_pi = 3.1415925025939941f;
+  float scale = 2.0f * swift_pi / (float)N;
+  for (int i = 0; i < N; ++i) h[i] = 0.5f - 0.5f * cosf(scale * (float)i);
+  float *d = upload_table(ctx, h);
+  if (d) ctx->hann_per[N] = d;
+  return d;
+}
+
+const float2 *dgc_ctx_twiddles(dgc_ctx *ctx, int N) {
+  auto it = ctx->twiddles.find(N);
+  if (it != ctx->twiddles.end()) return it->second;
+  std::vector<float2> h(N);
+  for (int m = 0; m < N; ++m) {
+    double a = -2.0 * M_PI * (double)m / (double)N;
+    h[m] = make_float2((float)cos(a), (float)sin(a));
+  }
+  float2 *d = upload_table(ctx, h);
+  if (d) ctx->twiddles[N] = d;
+  return d;
+}
+
+DGC_EXPORT int32_t dgc_abi_version(void) { return DGC_ABI_VERSION; }
+
+DGC_EXPORT int32_t dgc_ctx_create(int32_t device, dgc_ctx **out) {
+  if (!out) return DGC_ERR_INVALID;
+  *out = nullptr;
+  int count = 0;
+  if (cudaGetDeviceCount(&count) != cudaSuccess || device < 0 || device >= count) return DGC_ERR_CUDA;
+  if (cudaSetDevice(device) != cudaSuccess) return DGC_ERR_CUDA;
+  dgc_ctx *c = new dgc_ctx();
+  c->device = device;
+  cudaDeviceProp prop;
+  if (cudaGetDeviceProperties(&prop, device) == cudaSuccess) c->sm_count = prop.multiProcessorCount;
+  bool ok = cudaStreamCreateWithFlags(&c->own_stream, cudaStreamNonBlocking) == cudaSuccess &&
+            cudaEventCreate(&c->ev_begin) == cudaSuccess && cudaEventCreate(&c->ev_end) == cudaSuccess &&
+            cudaEventCreateWithFlags(&c->ev_sync, cudaEventDisableTiming) == cudaSuccess &&
+            cudaMalloc(&c->status_dev, sizeof(int32_t)) == cudaSuccess &&
+            cudaMalloc(&c->loss_accum, 64 * sizeof(double)) == cudaSuccess &&
+            cudaMemset(c->status_dev, 0, sizeof(int32_t)) == cudaSuccess;
+  if (!ok) {
+    dgc_ctx_destroy(c);
+    return DGC_ERR_CUDA;
+  }
+  c->stream = c->own_stream;
+  *out = c;
+  return DGC_OK;
+}
+
+DGC_EXPORT int32_t dgc_ctx_destroy(dgc_ctx *c) {
+  if (!c) return DGC_ERR_INVALID;
+  cudaSetDevice(c->device);
+  if (c->stream) cudaStreamSynchronize(c->stream);
+  for (auto &kv : c->playheads) cudaFree(kv.second);
+  for (auto &kv : c->hann_sym) cudaFree(kv.second);
+  for (auto &kv : c->hann_per) cudaFree(kv.second);
+  for (auto &kv : c->twiddles) cudaFree(kv.second);
+  if (c->scratch) cudaFree(c->scratch);
+  if (c->stage_dev) cudaFree(c->stage_dev);
+  if (c->status_dev) cudaFree(c->status_dev);
+  if (c->loss_accum) cudaFree(c->loss_accum);
+  if (c->ev_begin) cudaEventDestroy(c->ev_begin);
+  if (c->ev_end) cudaEventDestroy(c->ev_end);
+  if (c->ev_sync) cudaEventDestroy(c->ev_sync);
+  if (c->own_stream) cudaStreamDestroy(c->own_stream);
+  delete c;
+  return DGC_OK;
+}
+
+DGC_EXPORT const char *dgc_last_error(dgc_ctx *ctx) { return ctx ? ctx->err : "null context"; }
+
+DGC_EXPORT int32_t dgc_ctx_set_stream(dgc_ctx *ctx, void *s) {
+  if (!ctx) return DGC_ERR_INVALID;
+  ctx->stream = s ? (cudaStream_t)s : ctx->own_stream;
+  return DGC_OK;
+}
+
+DGC_EXPORT int32_t dgc_sync(dgc_ctx *ctx, uint32_t timeout_ms) {
+  if (!ctx) return DGC_ERR_INVALID;
+  if (timeout_ms == 0) {
+    DGC_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  } else {
+    DGC_CUDA(ctx, cudaEventRecord(ctx->ev_sync, ctx->stream));
+    auto t0 = std::chrono::steady_clock::now();
+    for (;;) {
+      cudaError_t e = cudaEventQuery(ctx->ev_sync);
+      if (e == cudaSuccess) break;
+      if (e != cudaErrorNotReady) return dgc_fail(ctx, DGC_ERR_CUDA, "sync: %s", cudaGetErrorString(e));
+      auto ms = std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t0).count();
+      if (ms > (long long)timeout_ms) return dgc_fail(ctx, DGC_ERR_TIMEOUT, "sync: stream still busy after %u ms", timeout_ms);
+      std::this_thread::sleep_for(std::chrono::microseconds(50));
+    }
+  }
+  int32_t st = 0;
+  DGC_CUDA(ctx, cudaMemcpy(&st, ctx->status_dev, sizeof(st), cudaMemcpyDeviceToHost));
+  if (st != 0) {
+    cudaMemset(ctx->status_dev, 0, sizeof(int32_t));
+    return dgc_fail(ctx, DGC_ERR_DEVICE, "device status word = %d", st);
+  }
+  return DGC_OK;
+}
+
+DGC_EXPORT int32_t dgc_profile_begin(dgc_ctx *ctx) {
+  if (!ctx) return DGC_ERR_INVALID;
+  DGC_CUDA(ctx, cudaEventRecord(ctx->ev_begin, ctx->stream));
+  return DGC_OK;
+}
+
+DGC_EXPORT int32_t dgc_profile_end(dgc_ctx *ctx, float *ms) {
+  if (!ctx || !ms) return DGC_ERR_INVALID;
+  DGC_CUDA(ctx, cudaEventRecord(ctx->ev_end, ctx->stream));
+  DGC_CUDA(ctx, cudaEventSynchronize(ctx->ev_end));
+  DGC_CUDA(ctx, cudaEventElapsedTime(ms, ctx->ev_begin, ctx->ev_end));
+  return DGC_OK;
+}
+
+DGC_EXPORT int64_t dgc_launch_count(dgc_ctx *ctx) { return ctx ? ctx->launches : -1; }
+
+DGC_EXPORT int32_t dgc_arena_create(dgc_ctx *ctx, uint64_t nfloats, dgc_arena **out) {
+  if (!ctx || !out) return DGC_ERR_INVALID;
+  *out = nullptr;
+  // the reference arena is at least 1024 floats (Sources/DGen/Runtime.swift:732-744)
+  if (nfloats < 1024) nfloats = 1024;
+  float *p = nullptr;
+  DGC_CUDA(ctx, cudaMalloc(&p, nfloats * sizeof(float)));
+  dgc_arena *a = new dgc_arena{ctx, p, nfloats};
+  *out = a;
+  return dgc_arena_zero(a);
+}
+
+DGC_EXPORT int32_t dgc_arena_destroy(dgc_arena *a) {
+  if (!a) return DGC_ERR_INVALID;
+  cudaStreamSynchronize(a->ctx->stream);
+  cudaFree(a->ptr);
+  delete a;
+  return DGC_OK;
+}
+
+DGC_EXPORT float *dgc_arena_ptr(dgc_arena *a) { return a ? a->ptr : nullptr; }
+DGC_EXPORT uint64_t dgc_arena_size(dgc_arena *a) { return a ? a->n : 0; }
+
+DGC_EXPORT int32_t dgc_arena_zero(dgc_arena *a) {
+  if (!a) return DGC_ERR_INVALID;
+  DGC_CUDA(a->ctx, cudaMemsetAsync(a->ptr, 0, a->n * sizeof(float), a->ctx->stream));
+  return DGC_OK;
+}
+
+DGC_EXPORT int32_t dgc_arena_upload(dgc_arena *a, uint64_t off, const float *src, uint64_t n) {
+  if (!a || (!src && n)) return DGC_ERR_INVALID;
+  if (off > a->n || n > a->n - off) return dgc_fail(a->ctx, DGC_ERR_INVALID, "arena_upload: range outside the arena");
+  DGC_CUDA(a->ctx, cudaMemcpyAsync(a->ptr + off, src, n * sizeof(float), cudaMemcpyHostToDevice, a->ctx->stream));
+  return DGC_OK;
+}
+
+DGC_EXPORT int32_t dgc_arena_download(dgc_arena *a, uint64_t off, float *dst, uint64_t n) {
+  if (!a || (!dst && n)) return DGC_ERR_INVALID;
+  if (off > a->n || n > a->n - off) return dgc_fail(a->ctx, DGC_ERR_INVALID, "arena_download: range outside the arena");
+  DGC_CUDA(a->ctx, cudaMemcpyAsync(dst, a->ptr + off, n * sizeof(float), cudaMemcpyDeviceToHost, a->ctx->stream));
+  DGC_CUDA(a->ctx, cudaStreamSynchronize(a->ctx->stream));
+  return DGC_OK;
+}

@@ -1,0 +1,123 @@
+// Shared-memory Stockham FFT building blocks (radix 8 / 4 / 2), used by the spectral loss, the
+// STFT and the partitioned convolution.  A transform of N points is carried by N/8 threads; each
+// stage reads N points from one shared buffer, applies twiddles and a radix-R butterfly in
+// registers, and writes to the other buffer in the self-sorting (Stockham) order, so no bit
+// reversal pass exists.  Convention: forward X[k] = sum x[n] exp(-2 pi i k n / N), unnormalised in
+// both directions (the host FFT service of the reference, Sources/DGenHostSupport/DGenHostSupport.c:10-30).
+#pragma once
+#include <cuda_runtime.h>
+
+namespace dgfft {
+
+__device__ __forceinline__ float2 cmul(float2 a, float2 b) {
+  return make_float2(fmaf(a.x, b.x, -a.y * b.y), fmaf(a.x, b.y, a.y * b.x));
+}
+__device__ __forceinline__ float2 cadd(float2 a, float2 b) { return make_float2(a.x + b.x, a.y + b.y); }
+__device__ __forceinline__ float2 csub(float2 a, float2 b) { return make_float2(a.x - b.x, a.y - b.y); }
+// multiply by -i (forward) or +i (inverse)
+template <bool INV>
+__device__ __forceinline__ float2 rot90(float2 a) {
+  return INV ? make_float2(-a.y, a.x) : make_float2(a.y, -a.x);
+}
+
+template <bool INV>
+__device__ __forceinline__ void dft2(float2 &a, float2 &b) {
+  float2 t = a;
+  a = cadd(t, b);
+  b = csub(t, b);
+}
+
+template <bool INV>
+__device__ __forceinline__ void dft4(float2 &a, float2 &b, float2 &c, float2 &d) {
+  float2 s0 = cadd(a, c), s1 = csub(a, c), s2 = cadd(b, d), s3 = rot90<INV>(csub(b, d));
+  a = cadd(s0, s2);
+  b = cadd(s1, s3);
+  c = csub(s0, s2);
+  d = csub(s1, s3);
+}
+
+template <bool INV>
+__device__ __forceinline__ void dft8(float2 *v) {
+  // even / odd radix-4, then combine with W8^k
+  dft4<INV>(v[0], v[2], v[4], v[6]);
+  dft4<INV>(v[1], v[3], v[5], v[7]);
+  const float h = 0.70710678118654752f;
+  float2 o1 = v[3], o2 = v[5], o3 = v[7];
+  // W8^1 = h(1 -+ i), W8^2 = -+ i, W8^3 = h(-1 -+ i)
+  float2 w1 = INV ? make_float2(h * (o1.x - o1.y), h * (o1.x + o1.y)) : make_float2(h * (o1.x + o1.y), h * (o1.y - o1.x));
+  float2 w2 = rot90<INV>(o2);
+  float2 w3 = INV ? make_float2(-h * (o3.x + o3.y), h * (o3.x - o3.y)) : make_float2(h * (o3.y - o3.x), -h * (o3.x + o3.y));
+  float2 e0 = v[0], e1 = v[2], e2 = v[4], e3 = v[6], o0 = v[1];
+  v[0] = cadd(e0, o0); v[4] = csub(e0, o0);
+  v[1] = cadd(e1, w1); v[5] = csub(e1, w1);
+  v[2] = cadd(e2, w2); v[6] = csub(e2, w2);
+  v[3] = cadd(e3, w3); v[7] = csub(e3, w3);
+}
+
+template <int R, bool INV>
+__device__ __forceinline__ void dftR(float2 *v) {
+  if (R == 8) dft8<INV>(v);
+  else if (R == 4) dft4<INV>(v[0], v[1], v[2], v[3]);
+  else dft2<INV>(v[0], v[1]);
+}
+
+// One Stockham stage of radix R with input stride Ns (product of the radices already applied).
+// tid in [0, N/8); tw is the table exp(-2 pi i m / N), m < N.
+template <int N, int R, bool INV>
+__device__ __forceinline__ void stage(const float2 *__restrict__ in, float2 *__restrict__ out, int Ns, int tid,
+                                      const float2 *__restrict__ tw) {
+  constexpr int PER = 8 / R;
+#pragma unroll
+  for (int q = 0; q < PER; ++q) {
+    const int j = tid + q * (N / 8);
+    const int k = j & (Ns - 1);
+    float2 v[R];
+#pragma unroll
+    for (int t = 0; t < R; ++t) v[t] = in[j + t * (N / R)];
+    if (Ns > 1) {
+      const int step = N / (Ns * R);
+#pragma unroll
+      for (int t = 1; t < R; ++t) {
+        float2 w = __ldg(&tw[k * t * step]);
+        if (INV) w.y = -w.y;
+        v[t] = cmul(v[t], w);
+      }
+    }
+    dftR<R, INV>(v);
+    const int j0 = (j - k) * R + k;
+#pragma unroll
+    for (int t = 0; t < R; ++t) out[j0 + t * Ns] = v[t];
+  }
+}
+
+// Full transform of N points held in shared buffer `a` (scratch buffer `b`); N/8 threads take part
+// and every one of them must call this (it synchronises the whole block between stages).  Returns
+// the buffer that holds the result in natural order.
+template <int N, bool INV>
+__device__ __forceinline__ float2 *fft_block(float2 *a, float2 *b, int tid, const float2 *__restrict__ tw) {
+  static_assert(N >= 16 && N <= 4096 && (N & (N - 1)) == 0, "N must be a power of two in 16..4096");
+  int Ns = 1;
+  float2 *src = a, *dst = b, *t;
+  constexpr int LOG = N == 16 ? 4 : N == 32 ? 5 : N == 64 ? 6 : N == 128 ? 7 : N == 256 ? 8 : N == 512 ? 9
+                      : N == 1024 ? 10 : N == 2048 ? 11 : 12;
+  constexpr int N8 = LOG / 3, REM = LOG % 3;
+#pragma unroll
+  for (int s = 0; s < N8; ++s) {
+    stage<N, 8, INV>(src, dst, Ns, tid, tw);
+    Ns *= 8;
+    t = src; src = dst; dst = t;
+    __syncthreads();
+  }
+  if (REM == 2) {
+    stage<N, 4, INV>(src, dst, Ns, tid, tw);
+    t = src; src = dst; dst = t;
+    __syncthreads();
+  } else if (REM == 1) {
+    stage<N, 2, INV>(src, dst, Ns, tid, tw);
+    t = src; src = dst; dst = t;
+    __syncthreads();
+  }
+  return src;
+}
+
+}  // namespace dgfft

@@ -1,0 +1,210 @@
+// Noise branch of the batched harmonic synth: a time-varying FIR whose taps are linearly
+// interpolated between control rows at every sample (Examples/HarmonicE2E/Synth.swift:97-101),
+// and the band-magnitude -> tap matrix product that feeds it in the synthetic workload.
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ void row_pos(float idx, int rows, int &lo, float &fr) {
+  float fr_rows = (float)rows;
+  float w = fmodf(idx, fr_rows);
+  if (w < 0.0f) w += fr_rows;
+  float fl = floorf(w);
+  lo = (int)fl;
+  fr = w - fl;
+}
+
+// Block = 256 threads, thread = SPT consecutive frames of one voice, tile = 256*SPT frames.
+// Shared memory: the control rows the tile touches (R rows of `taps` floats) and the noise tile with
+// its taps-1 frames of history, de-interleaved by (index mod SPT) so that the sliding window of a
+// thread and of its neighbours falls in distinct banks.
+// A thread's SPT frames see at most two (lo, hi) row pairs (the host guarantees step*SPT < 1), so it
+// accumulates dot products against rows r0, r0+1 for every frame, and against r0+2 only when its
+// frames straddle a control-row boundary.
+template <int SPT>
+__global__ void __launch_bounds__(256)
+fir_noise_kernel(dgc_fir_params prm, const float *__restrict__ play, const float *__restrict__ noise,
+                 const float *__restrict__ taps_tab, const float *__restrict__ ngain, float *__restrict__ audio,
+                 int max_rows, int32_t *status) {
+  extern __shared__ float sh[];
+  const int B = prm.B, T = prm.T, F = prm.F, NT = prm.taps;
+  constexpr int TILE = 256 * SPT;
+  const int b = blockIdx.y, t0 = blockIdx.x * TILE;
+  const int t_last = min(T - 1, t0 + TILE - 1);
+  int rmin, rmax;
+  float dummy;
+  row_pos(play[t0], F, rmin, dummy);
+  row_pos(play[t_last], F, rmax, dummy);
+  const int R = rmax - rmin + 3;  // rows rmin .. rmax+2 (hi of the last frame, and the straddle row)
+  if (rmax < rmin || R > max_rows) {
+    if (threadIdx.x == 0) atomicExch(status, 101);  // playhead not monotone or step too large for the tile
+    return;
+  }
+  float *rows = sh;                          // [R][NT]
+  float *xs = sh + (size_t)max_rows * NT;    // [SPT][Q], Q = (TILE + NT - 1 + SPT - 1) / SPT + 1
+  const int XN = TILE + NT - 1;
+  const int Q = (XN + SPT - 1) / SPT + 1;
+  for (int i = threadIdx.x; i < R * NT; i += 256) {
+    int r = rmin + i / NT, col = i - (i / NT) * NT;
+    if (r >= F) r -= F;  // the ceil row wraps to row 0
+    if (r >= F) r = F - 1;
+    rows[i] = taps_tab[((size_t)r * B + b) * NT + col];
+  }
+  // xs position m <-> frame t0 - (NT-1) + m
+  const float *xn = noise + (size_t)b * T;
+  for (int m = threadIdx.x; m < XN; m += 256) {
+    int t = t0 - (NT - 1) + m;
+    float v = (t >= 0 && t < T) ? xn[t] : 0.0f;
+    xs[(m % SPT) * Q + m / SPT] = v;
+  }
+  __syncthreads();
+
+  const int nl = threadIdx.x * SPT;  // first local frame of this thread
+  if (t0 + nl >= T) return;
+  int lo[SPT];
+  float fr[SPT];
+#pragma unroll
+  for (int u = 0; u < SPT; ++u) {
+    int n = min(t0 + nl + u, T - 1);
+    row_pos(play[n], F, lo[u], fr[u]);
+  }
+  const int r0 = lo[0] - rmin;
+  const bool straddle = lo[SPT - 1] != lo[0];
+  const float *ra = rows + (size_t)r0 * NT, *rb = ra + NT, *rc = rb + NT;
+  float d0[SPT], d1[SPT], d2[SPT];
+#pragma unroll
+  for (int u = 0; u < SPT; ++u) d0[u] = d1[u] = d2[u] = 0.0f;
+
+  // frame (nl+u), tap i reads xs position m = nl + u + i
+  float win[SPT];
+#pragma unroll
+  for (int u = 0; u < SPT - 1; ++u) win[u + 1] = xs[((nl + u) % SPT) * Q + (nl + u) / SPT];
+  for (int i = 0; i < NT; ++i) {
+#pragma unroll
+    for (int u = 0; u < SPT - 1; ++u) win[u] = win[u + 1];
+    {
+      int m = nl + SPT - 1 + i;
+      win[SPT - 1] = xs[(m % SPT) * Q + m / SPT];
+    }
+    float ta = ra[i], tb = rb[i];
+#pragma unroll
+    for (int u = 0; u < SPT; ++u) {
+      d0[u] = fmaf(win[u], ta, d0[u]);
+      d1[u] = fmaf(win[u], tb, d1[u]);
+    }
+  }
+  if (straddle) {
+#pragma unroll
+    for (int u = 0; u < SPT - 1; ++u) win[u + 1] = xs[((nl + u) % SPT) * Q + (nl + u) / SPT];
+    for (int i = 0; i < NT; ++i) {
+#pragma unroll
+      for (int u = 0; u < SPT - 1; ++u) win[u] = win[u + 1];
+      int m = nl + SPT - 1 + i;
+      win[SPT - 1] = xs[(m % SPT) * Q + m / SPT];
+      float tc = rc[i];
+#pragma unroll
+      for (int u = 0; u < SPT; ++u) d2[u] = fmaf(win[u], tc, d2[u]);
+    }
+  }
+  float *dst = audio + (size_t)b * T;
+#pragma unroll
+  for (int u = 0; u < SPT; ++u) {
+    int n = t0 + nl + u;
+    if (n >= T) break;
+    bool second = lo[u] != lo[0];
+    float a = second ? d1[u] : d0[u], c = second ? d2[u] : d1[u];
+    float omf = 1.0f - fr[u];
+    int l = lo[u], h = l + 1 >= F ? 0 : l + 1;
+    float ng = fmaf(fr[u], ngain[(size_t)h * B + b], omf * ngain[(size_t)l * B + b]);
+    float y = fmaf(fr[u], c, omf * a) * ng * prm.scale;
+    dst[n] = prm.accumulate ? dst[n] + y : y;
+  }
+}
+
+// taps[r][i] = sum_j W[i][j] * bands[r][j]; block = 16 rows, thread = taps i, i+256, ...
+__global__ void __launch_bounds__(256)
+bands_to_taps_kernel(const float *__restrict__ bands, const float *__restrict__ w, int rows, int nb, int nt,
+                     float *__restrict__ out) {
+  extern __shared__ float sh[];
+  const int ws = nb | 1;                 // odd row stride: conflict-free column walks
+  float *wsh = sh;                       // [nt][ws]
+  float *bsh = sh + (((size_t)nt * ws + 3) & ~(size_t)3);  // [nb][16], row index fastest, 16-byte aligned
+  for (int i = threadIdx.x; i < nt * nb; i += 256) wsh[(i / nb) * ws + (i % nb)] = w[i];
+  const int r0 = blockIdx.x * 16;
+  for (int i = threadIdx.x; i < 16 * nb; i += 256) {
+    int r = i / nb, j = i - r * nb;
+    bsh[j * 16 + r] = (r0 + r < rows) ? bands[(size_t)(r0 + r) * nb + j] : 0.0f;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < nt; i += 256) {
+    float acc[16];
+#pragma unroll
+    for (int r = 0; r < 16; ++r) acc[r] = 0.0f;
+    const float *wr = wsh + (size_t)i * ws;
+    for (int j = 0; j < nb; ++j) {
+      float wv = wr[j];
+      const float4 *bp = reinterpret_cast<const float4 *>(bsh + j * 16);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        float4 v = bp[q];
+        acc[4 * q + 0] = fmaf(wv, v.x, acc[4 * q + 0]);
+        acc[4 * q + 1] = fmaf(wv, v.y, acc[4 * q + 1]);
+        acc[4 * q + 2] = fmaf(wv, v.z, acc[4 * q + 2]);
+        acc[4 * q + 3] = fmaf(wv, v.w, acc[4 * q + 3]);
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 16; ++r)
+      if (r0 + r < rows) out[(size_t)(r0 + r) * nt + i] = acc[r];
+  }
+}
+
+}  // namespace
+
+DGC_EXPORT int32_t dgc_fir_noise(dgc_ctx *ctx, const dgc_fir_params *p, const float *noise_dev,
+                                 const float *taps_dev, const float *noise_gain_dev, float *audio_dev) {
+  if (!ctx) return DGC_ERR_INVALID;
+  DGC_REQUIRE(ctx, p && noise_dev && taps_dev && noise_gain_dev && audio_dev, "null pointer");
+  DGC_REQUIRE(ctx, p->B > 0 && p->T > 0 && p->F > 0, "size out of range");
+  DGC_REQUIRE(ctx, p->taps >= 1 && p->taps <= 1024, "taps must be in 1..1024");
+  const float *play = nullptr;
+  int32_t rc = dgc_playhead(ctx, p->F, p->T, &play);
+  if (rc != DGC_OK) return rc;
+  // playhead advance per frame; the sequential single-precision clock runs up to ~0.5% fast
+  double step = p->T > 1 ? (double)(p->F - 1) / (double)(p->T - 1) : 0.0;
+  step *= 1.01;
+  const int NT = p->taps;
+  auto launch = [&](auto kern, int spt) -> int32_t {
+    int tile = 256 * spt;
+    int max_rows = (int)(step * tile) + 5;
+    size_t smem = ((size_t)max_rows * NT + (size_t)spt * ((tile + NT - 1 + spt - 1) / spt + 1)) * sizeof(float);
+    if (smem > 200 * 1024) return DGC_ERR_UNSUPPORTED;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return dgc_fail(ctx, DGC_ERR_CUDA, "fir smem opt-in: %s", cudaGetErrorString(e));
+    kern<<<dim3(dgc_div_up(p->T, tile), p->B), 256, smem, ctx->stream>>>(*p, play, noise_dev, taps_dev,
+                                                                          noise_gain_dev, audio_dev, max_rows,
+                                                                          ctx->status_dev);
+    ctx->launches++;
+    return dgc_check_launch(ctx, "fir_noise");
+  };
+  rc = DGC_ERR_UNSUPPORTED;
+  if (step * 8 < 0.98) rc = launch(fir_noise_kernel<8>, 8);
+  if (rc == DGC_ERR_UNSUPPORTED) rc = launch(fir_noise_kernel<1>, 1);
+  if (rc == DGC_ERR_UNSUPPORTED)
+    return dgc_fail(ctx, DGC_ERR_UNSUPPORTED, "fir_noise: control rate too high for the shared-memory tile");
+  return rc;
+}
+
+DGC_EXPORT int32_t dgc_bands_to_taps(dgc_ctx *ctx, const float *bands_dev, const float *w_dev, int32_t rows,
+                                     int32_t nbands, int32_t taps, float *taps_dev) {
+  if (!ctx) return DGC_ERR_INVALID;
+  DGC_REQUIRE(ctx, bands_dev && w_dev && taps_dev, "null pointer");
+  DGC_REQUIRE(ctx, rows > 0 && nbands > 0 && taps > 0, "size out of range");
+  size_t smem = ((((size_t)taps * (nbands | 1) + 3) & ~(size_t)3) + (size_t)nbands * 16) * sizeof(float);
+  DGC_REQUIRE(ctx, smem <= 200 * 1024, "taps*nbands too large for shared memory");
+  DGC_CUDA(ctx, cudaFuncSetAttribute(bands_to_taps_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  bands_to_taps_kernel<<<dgc_div_up(rows, 16), 256, smem, ctx->stream>>>(bands_dev, w_dev, rows, nbands, taps,
+                                                                          taps_dev);
+  DGC_LAUNCHED(ctx, "bands_to_taps");
+  return DGC_OK;
+}

@@ -1,0 +1,211 @@
+// Multi-scale spectral loss (forward and backward) fused with windowing and magnitude.
+//
+// Reference semantics (Sources/DGen/Emit+SpectralLoss.swift:719-938): at every hop frame f the
+// window s[n] = x[f-(N-1)+n] * hann[n] (zero outside [0,T)) of both signals is transformed, the
+// magnitudes of bins 0..N/2 are compared (L1 on |X| and L1 on log(|X|+eps)), summed over bins per
+// (hop frame, voice), averaged over voices.  The reference runs one thread per (hop frame, voice)
+// and one kernel per term; here one block transforms several windows cooperatively in shared
+// memory, prediction and target ride the real and imaginary lane of ONE complex FFT, and the
+// linear and log terms come from the same spectrum.
+#include "common.cuh"
+#include "fft.cuh"
+
+namespace {
+
+using namespace dgfft;
+
+constexpr int LOSS_THREADS = 256;
+constexpr float LOG_EPS = 1e-8f;  // DGenSpectralConfig.logMagnitudeEpsilon, Sources/DGen/GradientConfig.swift:38
+
+// Sum `v` over the G = N/8 threads that carry one transform (G is a power of two).  `red` is a
+// shared array of one float per warp of the block.  Result valid in the group's first thread.
+template <int G>
+__device__ __forceinline__ float group_sum(float v, float *red, int tid) {
+  constexpr int W = G < 32 ? G : 32;
+#pragma unroll
+  for (int off = W / 2; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+  if (G > 32) {
+    __syncthreads();
+    if ((tid & 31) == 0) red[tid >> 5] = v;
+    __syncthreads();
+    if ((tid & (G - 1)) == 0) {
+      float s = 0.0f;
+#pragma unroll
+      for (int w = 0; w < G / 32; ++w) s += red[(tid >> 5) + w];
+      v = s;
+    }
+  }
+  return v;
+}
+
+// Unpack the spectra of two real signals from the transform of z = x1 + i x2.
+__device__ __forceinline__ void unpack(float2 zk, float2 znk, float2 &x1, float2 &x2) {
+  x1 = make_float2(0.5f * (zk.x + znk.x), 0.5f * (zk.y - znk.y));
+  x2 = make_float2(0.5f * (zk.y + znk.y), 0.5f * (znk.x - zk.x));
+}
+
+template <int N>
+__global__ void __launch_bounds__(LOSS_THREADS)
+mss_fwd_kernel(const float *__restrict__ pred, const float *__restrict__ target, int B, int T, int hop, int H,
+               const float *__restrict__ window, const float2 *__restrict__ tw, float *__restrict__ part_lin,
+               float *__restrict__ part_log) {
+  constexpr int G = N / 8;                    // threads per transform
+  constexpr int NF = LOSS_THREADS / G;        // transforms per block
+  __shared__ float2 bufa[NF * N];
+  __shared__ float2 bufb[NF * N];
+  __shared__ float red[LOSS_THREADS / 32];
+  const int tid = threadIdx.x, f = tid / G, lt = tid % G;
+  const int b = blockIdx.y;
+  const int h = blockIdx.x * NF + f;
+  const bool valid = h < H;
+  const int t_base = h * hop - (N - 1);
+  const float *x1 = pred + (size_t)b * T, *x2 = target + (size_t)b * T;
+  float2 *a = bufa + f * N, *bb = bufb + f * N;
+#pragma unroll
+  for (int q = 0; q < 8; ++q) {
+    int i = lt + q * G, t = t_base + i;
+    float2 v = make_float2(0.0f, 0.0f);
+    if (valid && t >= 0 && t < T) {
+      float w = __ldg(&window[i]);
+      v = make_float2(x1[t] * w, x2[t] * w);
+    }
+    a[i] = v;
+  }
+  __syncthreads();
+  float2 *z = fft_block<N, false>(a, bb, lt, tw);
+  float lin = 0.0f, lg = 0.0f;
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    int k = lt + q * G;  // 0 .. N/2-1
+    float2 X1, X2;
+    unpack(z[k], z[(N - k) & (N - 1)], X1, X2);
+    float m1 = sqrtf(X1.x * X1.x + X1.y * X1.y), m2 = sqrtf(X2.x * X2.x + X2.y * X2.y);
+    lin += fabsf(m1 - m2);
+    lg += fabsf(__logf(m1 + LOG_EPS) - __logf(m2 + LOG_EPS));
+  }
+  if (lt == 0) {  // Nyquist bin
+    float2 zn = z[N / 2];
+    float m1 = fabsf(zn.x), m2 = fabsf(zn.y);
+    lin += fabsf(m1 - m2);
+    lg += fabsf(__logf(m1 + LOG_EPS) - __logf(m2 + LOG_EPS));
+  }
+  lin = group_sum<G>(lin, red, tid);
+  lg = group_sum<G>(lg, red, tid);
+  if (valid && lt == 0) {
+    part_lin[(size_t)h * B + b] = lin;
+    part_log[(size_t)h * B + b] = lg;
+  }
+}
+
+// total = sum_s (w_lin * sum(lin_s) + w_log * sum(log_s)) / B / nscales / T ; one block, fixed order
+struct ReduceDesc {
+  int nscales;
+  long long off[DGC_MSS_MAX_SCALES];  // offset of the lin block of scale s; log block follows
+  long long cnt[DGC_MSS_MAX_SCALES];  // H_s * B
+};
+
+__global__ void mss_reduce_kernel(const float *__restrict__ part, ReduceDesc d, double scale_lin, double scale_log,
+                                  double *__restrict__ out) {
+  __shared__ double sh[1024];
+  double acc = 0.0;
+  for (int s = 0; s < d.nscales; ++s) {
+    const float *lin = part + d.off[s], *lg = lin + d.cnt[s];
+    double a = 0.0, c = 0.0;
+    for (long long i = threadIdx.x; i < d.cnt[s]; i += blockDim.x) {
+      a += (double)lin[i];
+      c += (double)lg[i];
+    }
+    acc += a * scale_lin + c * scale_log;
+  }
+  sh[threadIdx.x] = acc;
+  __syncthreads();
+  for (int off = blockDim.x / 2; off > 0; off >>= 1) {
+    if (threadIdx.x < off) sh[threadIdx.x] += sh[threadIdx.x + off];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) out[0] = sh[0];
+}
+
+template <int N>
+int32_t launch_fwd(dgc_ctx *ctx, const dgc_mss_params *p, const float *pred, const float *target, int hop, int H,
+                   float *lin, float *lg) {
+  const float *win = dgc_ctx_hann_sym(ctx, N);
+  const float2 *tw = dgc_ctx_twiddles(ctx, N);
+  if (!win || !tw) return DGC_ERR_OOM;
+  constexpr int NF = LOSS_THREADS / (N / 8);
+  mss_fwd_kernel<N><<<dim3(dgc_div_up(H, NF), p->B), LOSS_THREADS, 0, ctx->stream>>>(pred, target, p->B, p->T, hop, H,
+                                                                                    win, tw, lin, lg);
+  ctx->launches++;
+  return dgc_check_launch(ctx, "mss_fwd");
+}
+
+int32_t validate(dgc_ctx *ctx, const dgc_mss_params *p) {
+  DGC_REQUIRE(ctx, p->B > 0 && p->T > 0, "B and T must be positive");
+  DGC_REQUIRE(ctx, p->nscales > 0 && p->nscales <= DGC_MSS_MAX_SCALES, "nscales out of range");
+  DGC_REQUIRE(ctx, p->hop_div >= 1, "hop_div must be >= 1");
+  for (int s = 0; s < p->nscales; ++s)
+    DGC_REQUIRE(ctx, dgc_is_pow2(p->sizes[s]) && p->sizes[s] >= 16 && p->sizes[s] <= 2048,
+                "window sizes must be powers of two in 16..2048");
+  return DGC_OK;
+}
+
+inline int hop_of(const dgc_mss_params *p, int s) {
+  int hop = p->sizes[s] / p->hop_div;
+  return hop < 1 ? 1 : hop;
+}
+
+}  // namespace
+
+DGC_EXPORT uint64_t dgc_mss_partial_floats(const dgc_mss_params *p) {
+  if (!p || p->B <= 0 || p->T <= 0 || p->nscales <= 0 || p->nscales > DGC_MSS_MAX_SCALES || p->hop_div < 1) return 0;
+  uint64_t n = 0;
+  for (int s = 0; s < p->nscales; ++s) {
+    if (p->sizes[s] > p->T) continue;  // the reference skips windows longer than the render
+    int hop = hop_of(p, s);
+    n += 2ull * (uint64_t)dgc_div_up(p->T, hop) * p->B;
+  }
+  return n;
+}
+
+DGC_EXPORT int32_t dgc_mss_loss_fwd(dgc_ctx *ctx, const dgc_mss_params *p, const float *pred_dev,
+                                    const float *target_dev, float *partial_dev, double *loss_dev) {
+  if (!ctx) return DGC_ERR_INVALID;
+  DGC_REQUIRE(ctx, p && pred_dev && target_dev && loss_dev, "null pointer");
+  int32_t rc = validate(ctx, p);
+  if (rc != DGC_OK) return rc;
+  float *part = partial_dev ? partial_dev : dgc_ctx_scratch(ctx, dgc_mss_partial_floats(p) + 4);
+  if (!part) return DGC_ERR_OOM;
+  ReduceDesc d;
+  d.nscales = 0;
+  long long off = 0;
+  int used = 0;
+  for (int s = 0; s < p->nscales; ++s) {
+    const int N = p->sizes[s];
+    if (N > p->T) continue;
+    ++used;
+  }
+  for (int s = 0; s < p->nscales; ++s) {
+    const int N = p->sizes[s];
+    if (N > p->T) continue;
+    const int hop = hop_of(p, s), H = dgc_div_up(p->T, hop);
+    float *lin = part + off, *lg = lin + (long long)H * p->B;
+    switch (N) {
+#define CASE(NN) case NN: rc = launch_fwd<NN>(ctx, p, pred_dev, target_dev, hop, H, lin, lg); break;
+      CASE(16) CASE(32) CASE(64) CASE(128) CASE(256) CASE(512) CASE(1024) CASE(2048)
+#undef CASE
+      default: return dgc_fail(ctx, DGC_ERR_UNSUPPORTED, "window size %d", N);
+    }
+    if (rc != DGC_OK) return rc;
+    d.off[d.nscales] = off;
+    d.cnt[d.nscales] = (long long)H * p->B;
+    d.nscales++;
+    off += 2ll * H * p->B;
+  }
+  // weights: (w / nscales) with nscales = number of usable windows, normalize:true divides by T
+  // (Examples/HarmonicE2E/Trainer.swift:553-586, Sources/DGenLazy/Functions.swift:951-954);
+  // the batched loss is the mean over voices (Emit+SpectralLoss.swift:937-938)
+  const double den = (double)p->B * (double)(used > 0 ? used : 1) * (double)p->T;
+  mss_reduce_kernel<<<1, 1024, 0, ctx->stream>>>(part, d, (double)p->w_lin / den, (double)p->w_log / den, loss_dev);
+  DGC_LAUNCHED(ctx, "mss_reduce");
+  return DGC_OK;
+}

@@ -1,0 +1,440 @@
+// Oscillator bank: scalar clocks, phase anchors (serial or prefix-scan) and the fused
+// phase -> sin -> amplitude -> sum-over-partials render.
+//
+// Time axis decomposition.  The reference's stateful phasor adds f/sr and wraps once per sample in
+// single precision (Sources/DGen/Emit+State.swift:322-369); every add rounds, and those roundings
+// are part of the result.  The render kernel therefore follows that recurrence literally, but only
+// inside chunks of CH = 64 frames: one thread-group per (voice, chunk) starts from a phase anchor
+// and steps 64 times.  Anchors come from one of two kernels:
+//   SEQUENTIAL  one thread per (voice, partial) runs the recurrence over all T frames and records
+//               the state every 64 frames: bit-identical to the reference, latency bound;
+//   SCAN        every (voice, partial, chunk) sums its 64 increments exactly in 64-bit fixed point,
+//               a second kernel prefix-sums the chunk totals: frame-parallel.
+#include "common.cuh"
+
+namespace {
+
+constexpr int CH = 64;            // frames per phase chunk
+constexpr float TWO_PI_F = 6.2831850051879883f;  // Float(2*Float.pi) of the reference graphs
+
+// a / b for a fixed b with r = RN(1/b): q + fma(-q, b, a) * r is the correctly rounded quotient
+// (checked exhaustively on the host for the common sample rates, a in [1e-3, 2e6]).
+__device__ __forceinline__ float div_by_const(float a, float b, float r) {
+  float q = __fmul_rn(a, r);
+  float rem = __fmaf_rn(-q, b, a);
+  return __fmaf_rn(rem, r, q);
+}
+
+// One step of the reference recurrence: next = p + inc ; w = next - floor(next) ; if (w >= 1) w -= 1.
+__device__ __forceinline__ float phasor_step(float p, float inc) {
+  float next = __fadd_rn(p, inc);
+  if (inc >= 0.0f && inc < 1.0f) {
+    // p in [0,1) and inc in [0,1): next in [0,2), floor is 0 or 1 and next-1 is exact
+    float t = __fadd_rn(next, -1.0f);
+    return next >= 1.0f ? t : next;
+  }
+  float w = __fsub_rn(next, floorf(next));
+  return w >= 1.0f ? __fadd_rn(w, -1.0f) : w;
+}
+
+// sampleRow position (Sources/DGen/Emit+RowSelection.swift:166-184)
+__device__ __forceinline__ void row_pos(float idx, int rows, int &lo, int &hi, float &fr) {
+  float fr_rows = (float)rows;
+  float w = fmodf(idx, fr_rows);
+  if (w < 0.0f) w = __fadd_rn(w, fr_rows);
+  float fl = floorf(w);
+  float ce = fl + 1.0f;
+  if (ce >= fr_rows) ce = 0.0f;
+  lo = (int)fl;
+  hi = (int)ce;
+  fr = __fsub_rn(w, fl);
+}
+
+__device__ __forceinline__ float lerp_strict(float omf, float a, float fr, float b) {
+  return __fadd_rn(__fmul_rn(omf, a), __fmul_rn(fr, b));
+}
+
+// sin(2*pi*p) for p in [0,1): centre to [-pi, pi) where the fast sine's absolute error is 2^-21.4
+__device__ __forceinline__ float sin_turns(float p) {
+  float c = p >= 0.5f ? p - 1.0f : p;
+  return __sinf(c * TWO_PI_F);
+}
+
+// ---------------------------------------------------------------------------------------------
+// scalar accum clock, one thread (Sources/DGen/Definitions.swift:215-246)
+// ---------------------------------------------------------------------------------------------
+__global__ void clock_accum_kernel(float incr, float mn, float mx, float state0, int T, float *out, int clip,
+                                   float clip_lo, float clip_hi) {
+  if (blockIdx.x != 0 || threadIdx.x != 0) return;
+  float acc = state0;
+  const float span = __fsub_rn(mx, mn);
+  for (int n = 0; n < T; ++n) {
+    float v = acc;
+    if (clip) v = fminf(fmaxf(v, clip_lo), clip_hi);
+    out[n] = v;
+    float next = __fadd_rn(acc, incr);
+    float rel = __fsub_rn(next, mn);
+    float k = floorf(__fdiv_rn(rel, span));
+    float w = __fsub_rn(next, __fmul_rn(k, span));
+    acc = w >= mx ? __fsub_rn(w, span) : w;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// constant-frequency bank summed to mono
+// ---------------------------------------------------------------------------------------------
+// deterministic phasor: frame-parallel, one thread per frame looping over partials
+__global__ void osc_const_det_kernel(const float *__restrict__ freq, const float *__restrict__ amp, int K, int T,
+                                     float sr, float *__restrict__ audio) {
+  extern __shared__ float sh[];  // inc[K], amp[K]
+  for (int k = threadIdx.x; k < K; k += blockDim.x) {
+    sh[k] = __fdiv_rn(freq[k], sr);
+    sh[K + k] = amp[k];
+  }
+  __syncthreads();
+  int n = blockIdx.x * blockDim.x + threadIdx.x;
+  if (n >= T) return;
+  float fn = (float)n, acc = 0.0f;
+  for (int k = 0; k < K; ++k) {
+    float raw = __fmul_rn(sh[k], fn);
+    float p = __fsub_rn(raw, floorf(raw));
+    acc += sin_turns(p) * sh[K + k];
+  }
+  audio[n] = acc;
+}
+
+// stateful phasor, constant frequency: anchors by the serial recurrence (one thread per partial)
+__global__ void osc_const_anchor_seq_kernel(const float *__restrict__ freq, int K, int T, float sr,
+                                            float *__restrict__ anchors /* [C][K] */) {
+  int k = blockIdx.x * blockDim.x + threadIdx.x;
+  if (k >= K) return;
+  float inc = __fdiv_rn(freq[k], sr);
+  float p = 0.0f;
+  for (int n = 0; n < T; ++n) {
+    if ((n & (CH - 1)) == 0) anchors[(size_t)(n / CH) * K + k] = p;
+    p = phasor_step(p, inc);
+  }
+}
+
+__global__ void osc_const_render_kernel(const float *__restrict__ freq, const float *__restrict__ amp,
+                                        const float *__restrict__ anchors, int K, int T, float sr,
+                                        float *__restrict__ audio) {
+  // one warp per chunk; lanes stride over partials and keep 64 per-frame sums in registers; the
+  // cross-lane sum is a fixed shuffle tree, so the result does not depend on scheduling
+  int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  int C = (T + CH - 1) / CH;
+  if (warp >= C) return;
+  int n0 = warp * CH;
+  float acc[CH];
+#pragma unroll
+  for (int s = 0; s < CH; ++s) acc[s] = 0.0f;
+  for (int k = lane; k < K; k += 32) {
+    float inc = __fdiv_rn(freq[k], sr), a = amp[k];
+    float p = anchors[(size_t)warp * K + k];
+#pragma unroll
+    for (int s = 0; s < CH; ++s) {
+      acc[s] = fmaf(sin_turns(p), a, acc[s]);
+      p = phasor_step(p, inc);
+    }
+  }
+#pragma unroll
+  for (int s = 0; s < CH; ++s) {
+    float v = acc[s];
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+    if (lane == (s & 31) && n0 + s < T) audio[n0 + s] = v;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// batched harmonic bank
+// ---------------------------------------------------------------------------------------------
+// f0t[b][n] = sampleRow(f0)[n][b], strict single-precision lerp
+__global__ void f0_track_kernel(const float *__restrict__ play, const float *__restrict__ f0, int B, int T, int F,
+                                float *__restrict__ f0t) {
+  int n = blockIdx.x * blockDim.x + threadIdx.x, b = blockIdx.y;
+  if (n >= T) return;
+  int lo, hi;
+  float fr;
+  row_pos(play[n], F, lo, hi, fr);
+  float omf = __fsub_rn(1.0f, fr);
+  f0t[(size_t)b * T + n] = lerp_strict(omf, f0[(size_t)lo * B + b], fr, f0[(size_t)hi * B + b]);
+}
+
+// SEQUENTIAL anchors: thread = (voice, partial), partial fastest; anchors[b][c][k]
+__global__ void anchor_seq_kernel(const float *__restrict__ f0t, int B, int T, int K, float sr, float rsr,
+                                  float *__restrict__ anchors) {
+  int lane_id = blockIdx.x * blockDim.x + threadIdx.x;
+  if (lane_id >= B * K) return;
+  int b = lane_id / K, k = lane_id - b * K;
+  const float kf = (float)(k + 1);
+  const float *f = f0t + (size_t)b * T;
+  const int C = (T + CH - 1) / CH;
+  float *out = anchors + (size_t)b * C * K + k;
+  float p = 0.0f;
+  for (int c = 0; c < C; ++c) {
+    out[(size_t)c * K] = p;
+    int n0 = c * CH, n1 = min(T, n0 + CH);
+#pragma unroll 8
+    for (int n = n0; n < n1; ++n) {
+      float inc = div_by_const(__fmul_rn(kf, f[n]), sr, rsr);
+      p = phasor_step(p, inc);
+    }
+  }
+}
+
+// SCAN anchors, stage 1: exact sum of the 64 increments of a chunk in Q0.64 (mod 1)
+__global__ void anchor_sum_kernel(const float *__restrict__ f0t, int B, int T, int K, float sr, float rsr,
+                                  unsigned long long *__restrict__ sums /* [B][C][K] */) {
+  int k = threadIdx.x, c = blockIdx.x, b = blockIdx.y;
+  if (k >= K) return;
+  const int C = gridDim.x;
+  const float kf = (float)(k + 1);
+  const float *f = f0t + (size_t)b * T;
+  int n0 = c * CH, n1 = min(T, n0 + CH);
+  unsigned long long acc = 0ull;
+  for (int n = n0; n < n1; ++n) {
+    float inc = div_by_const(__fmul_rn(kf, f[n]), sr, rsr);
+    if (!(inc >= 0.0f && inc < 1.0f)) inc = inc - floorf(inc);
+    if (!(inc >= 0.0f && inc < 1.0f)) inc = 0.0f;  // non-finite or rounded up to 1
+    acc += __float2ull_rz(inc * 18446744073709551616.0f);
+  }
+  sums[((size_t)b * C + c) * K + k] = acc;
+}
+
+// SCAN anchors, stage 2: exclusive prefix over chunks; the fixed-point phase is rounded to float
+__global__ void anchor_scan_kernel(const unsigned long long *__restrict__ sums, int B, int C, int K,
+                                   float *__restrict__ anchors) {
+  int lane_id = blockIdx.x * blockDim.x + threadIdx.x;
+  if (lane_id >= B * K) return;
+  int b = lane_id / K, k = lane_id - b * K;
+  const unsigned long long *s = sums + (size_t)b * C * K + k;
+  float *out = anchors + (size_t)b * C * K + k;
+  unsigned long long acc = 0ull;
+  for (int c = 0; c < C; ++c) {
+    float p = __ull2float_rn(acc) * 5.421010862427522e-20f;  // 2^-64
+    out[(size_t)c * K] = p >= 1.0f ? 0.0f : p;
+    acc += s[(size_t)c * K];
+  }
+}
+
+// Render: a group of LPC lanes owns one (voice, chunk); lane j carries partials j, j+LPC, ...
+// (P per lane) through the 64 frames; per frame the group reduces sum(sin*masked) and sum(masked)
+// with shuffles; lane 0 stores four frames at a time.
+template <int LPC, int P>
+__global__ void __launch_bounds__(128)
+harmonic_render_kernel(dgc_harmonic_params prm, float rsr, const float *__restrict__ play,
+                       const float *__restrict__ f0, const float *__restrict__ uv,
+                       const float *__restrict__ amps, const float *__restrict__ gain,
+                       const float *__restrict__ anchors, float *__restrict__ audio) {
+  constexpr int G = 128 / LPC;
+  const int B = prm.B, T = prm.T, K = prm.K, F = prm.F;
+  const int C = (T + CH - 1) / CH;
+  const int g = threadIdx.x / LPC, j = threadIdx.x % LPC;
+  int c = blockIdx.x * G + g;
+  const int b = blockIdx.y;
+  const bool active = c < C;
+  if (!active) c = C - 1;
+  const int n0 = c * CH;
+  const float sr = prm.sample_rate, nyq = sr * 0.5f;
+
+  float ph[P], kf[P], alo[P], ahi[P];
+  const float *anc = anchors + ((size_t)b * C + c) * K;
+#pragma unroll
+  for (int i = 0; i < P; ++i) {
+    int k = j + LPC * i;
+    kf[i] = (float)(k + 1);
+    ph[i] = k < K ? anc[k] : 0.0f;
+    alo[i] = 0.0f;
+    ahi[i] = 0.0f;
+  }
+  int cur_lo = -1;
+  float f0lo = 0, f0hi = 0, uvlo = 0, uvhi = 0, glo = 0, ghi = 0;
+  float *dst = audio + (size_t)b * T;
+
+  for (int s = 0; s < CH; s += 4) {
+    float val[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      int n = min(n0 + s + u, T - 1);
+      int lo, hi;
+      float fr;
+      row_pos(play[n], F, lo, hi, fr);
+      if (lo != cur_lo) {
+        cur_lo = lo;
+        const float *rl = amps + ((size_t)lo * B + b) * K, *rh = amps + ((size_t)hi * B + b) * K;
+#pragma unroll
+        for (int i = 0; i < P; ++i) {
+          int k = j + LPC * i;
+          alo[i] = k < K ? rl[k] : 0.0f;
+          ahi[i] = k < K ? rh[k] : 0.0f;
+        }
+        f0lo = f0[(size_t)lo * B + b]; f0hi = f0[(size_t)hi * B + b];
+        uvlo = uv[(size_t)lo * B + b]; uvhi = uv[(size_t)hi * B + b];
+        glo = gain[(size_t)lo * B + b]; ghi = gain[(size_t)hi * B + b];
+      }
+      float omf = __fsub_rn(1.0f, fr);
+      float f0t = lerp_strict(omf, f0lo, fr, f0hi);
+      float s1 = 0.0f, s2 = 0.0f;
+#pragma unroll
+      for (int i = 0; i < P; ++i) {
+        float freq = __fmul_rn(kf[i], f0t);
+        float a = fmaf(fr, ahi[i], omf * alo[i]);
+        float m = freq < nyq ? a : 0.0f;
+        s2 += m;
+        s1 = fmaf(sin_turns(ph[i]), m, s1);
+        ph[i] = phasor_step(ph[i], div_by_const(freq, sr, rsr));
+      }
+#pragma unroll
+      for (int off = LPC / 2; off > 0; off >>= 1) {
+        s1 += __shfl_xor_sync(0xffffffffu, s1, off);
+        s2 += __shfl_xor_sync(0xffffffffu, s2, off);
+      }
+      float gt = fmaf(fr, ghi, omf * glo), uvt = fmaf(fr, uvhi, omf * uvlo);
+      val[u] = s1 / (s2 + 1e-8f) * gt * uvt * prm.harmonic_scale;
+    }
+    if (active && j == 0) {
+      int n = n0 + s;
+      if (n + 3 < T && ((((size_t)b * T + n) & 3) == 0) && !prm.accumulate) {
+        *reinterpret_cast<float4 *>(dst + n) = make_float4(val[0], val[1], val[2], val[3]);
+      } else {
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (n + u < T) dst[n + u] = prm.accumulate ? dst[n + u] + val[u] : val[u];
+      }
+    }
+  }
+}
+
+template <int LPC, int P>
+void launch_render(dgc_ctx *ctx, const dgc_harmonic_params &p, const float *play, const float *f0, const float *uv,
+                   const float *amps, const float *gain, const float *anchors, float *audio) {
+  int C = (p.T + CH - 1) / CH;
+  constexpr int G = 128 / LPC;
+  dim3 grid(dgc_div_up(C, G), p.B);
+  harmonic_render_kernel<LPC, P><<<grid, 128, 0, ctx->stream>>>(p, 1.0f / p.sample_rate, play, f0, uv, amps, gain,
+                                                                 anchors, audio);
+}
+
+}  // namespace
+
+DGC_EXPORT int32_t dgc_clock_accum(dgc_ctx *ctx, float incr, float mn, float mx, float state0, int32_t T,
+                                   float *out_dev) {
+  if (!ctx) return DGC_ERR_INVALID;
+  DGC_REQUIRE(ctx, out_dev && T > 0, "null output or T <= 0");
+  DGC_REQUIRE(ctx, mx > mn, "max must exceed min");
+  clock_accum_kernel<<<1, 32, 0, ctx->stream>>>(incr, mn, mx, state0, T, out_dev, 0, 0.f, 0.f);
+  DGC_LAUNCHED(ctx, "clock_accum");
+  return DGC_OK;
+}
+
+DGC_EXPORT int32_t dgc_playhead(dgc_ctx *ctx, int32_t F, int32_t T, const float **out_dev) {
+  if (!ctx) return DGC_ERR_INVALID;
+  DGC_REQUIRE(ctx, out_dev && F > 0 && T > 0, "bad arguments");
+  auto key = std::make_pair((int)F, (int)T);
+  auto it = ctx->playheads.find(key);
+  if (it != ctx->playheads.end()) {
+    *out_dev = it->second;
+    return DGC_OK;
+  }
+  float *d = nullptr;
+  DGC_CUDA(ctx, cudaMalloc(&d, (size_t)T * sizeof(float)));
+  // Examples/HarmonicE2E/Synth.swift:57-70, all in Float
+  float fmax = (float)(F > 1 ? F - 1 : 0);
+  float denom = (float)(T > 1 ? T - 1 : 1);
+  float step = fmax / denom;
+  float hi = fmax - 1e-4f;
+  if (hi < 0.f) hi = 0.f;
+  if (fmax <= 0.f) {
+    DGC_CUDA(ctx, cudaMemsetAsync(d, 0, (size_t)T * sizeof(float), ctx->stream));
+  } else {
+    clock_accum_kernel<<<1, 32, 0, ctx->stream>>>(step, 0.f, fmax, 0.f, T, d, 1, 0.f, hi);
+    ctx->launches++;
+    int32_t rc = dgc_check_launch(ctx, "playhead");
+    if (rc != DGC_OK) {
+      cudaFree(d);
+      return rc;
+    }
+  }
+  ctx->playheads[key] = d;
+  *out_dev = d;
+  return DGC_OK;
+}
+
+DGC_EXPORT int32_t dgc_osc_bank_const(dgc_ctx *ctx, const float *freq_dev, const float *amp_dev, int32_t K,
+                                      int32_t T, float sr, int32_t phase_mode, float *audio_dev) {
+  if (!ctx) return DGC_ERR_INVALID;
+  DGC_REQUIRE(ctx, freq_dev && amp_dev && audio_dev, "null pointer");
+  DGC_REQUIRE(ctx, K > 0 && K <= 4096 && T > 0 && sr > 0, "size out of range");
+  if (phase_mode == DGC_PHASE_DETERMINISTIC) {
+    osc_const_det_kernel<<<dgc_div_up(T, 256), 256, 2 * K * sizeof(float), ctx->stream>>>(freq_dev, amp_dev, K, T, sr,
+                                                                                          audio_dev);
+    DGC_LAUNCHED(ctx, "osc_const_det");
+    return DGC_OK;
+  }
+  if (phase_mode != DGC_PHASE_SEQUENTIAL)
+    return dgc_fail(ctx, DGC_ERR_UNSUPPORTED, "osc_bank_const: phase mode %d", phase_mode);
+  int C = dgc_div_up(T, CH);
+  float *anchors = dgc_ctx_scratch(ctx, (uint64_t)C * K);
+  if (!anchors) return DGC_ERR_OOM;
+  osc_const_anchor_seq_kernel<<<dgc_div_up(K, 32), 32, 0, ctx->stream>>>(freq_dev, K, T, sr, anchors);
+  DGC_LAUNCHED(ctx, "osc_const_anchor_seq");
+  osc_const_render_kernel<<<dgc_div_up(C, 4), 128, 0, ctx->stream>>>(freq_dev, amp_dev, anchors, K, T, sr, audio_dev);
+  DGC_LAUNCHED(ctx, "osc_const_render");
+  return DGC_OK;
+}
+
+DGC_EXPORT uint64_t dgc_harmonic_scratch_floats(const dgc_harmonic_params *p) {
+  if (!p || p->B <= 0 || p->T <= 0 || p->K <= 0) return 0;
+  uint64_t C = (uint64_t)(p->T + CH - 1) / CH;
+  uint64_t lanes = (uint64_t)p->B * C * p->K;
+  // f0 track [B][T] (rounded up to 4), anchors [B][C][K], chunk sums as 64-bit words
+  return (((uint64_t)p->B * p->T + 3) & ~3ull) + lanes + 2 * lanes + 8;
+}
+
+DGC_EXPORT int32_t dgc_harmonic_render(dgc_ctx *ctx, const dgc_harmonic_params *p, const float *f0_dev,
+                                       const float *uv_dev, const float *amps_dev, const float *gain_dev,
+                                       float *scratch_dev, float *audio_dev) {
+  if (!ctx) return DGC_ERR_INVALID;
+  DGC_REQUIRE(ctx, p && f0_dev && uv_dev && amps_dev && gain_dev && audio_dev, "null pointer");
+  DGC_REQUIRE(ctx, p->B > 0 && p->T > 0 && p->F > 0 && p->K > 0 && p->K <= 512, "size out of range (K <= 512)");
+  DGC_REQUIRE(ctx, p->sample_rate > 0, "sample rate must be positive");
+  DGC_REQUIRE(ctx, p->phase_mode == DGC_PHASE_SEQUENTIAL || p->phase_mode == DGC_PHASE_SCAN, "phase mode");
+  const int B = p->B, T = p->T, K = p->K, F = p->F;
+  const int C = dgc_div_up(T, CH);
+  const float *play = nullptr;
+  int32_t rc = dgc_playhead(ctx, F, T, &play);
+  if (rc != DGC_OK) return rc;
+  float *scratch = scratch_dev ? scratch_dev : dgc_ctx_scratch(ctx, dgc_harmonic_scratch_floats(p));
+  if (!scratch) return DGC_ERR_OOM;
+  DGC_REQUIRE(ctx, (((uintptr_t)scratch) & 15) == 0, "scratch must be 16-byte aligned");
+  float *f0t = scratch;
+  float *anchors = scratch + (((uint64_t)B * T + 3) & ~3ull);
+  uint64_t lanes = (uint64_t)B * C * K;
+  unsigned long long *sums = reinterpret_cast<unsigned long long *>(anchors + ((lanes + 1) & ~1ull));
+  const float sr = p->sample_rate, rsr = 1.0f / sr;
+
+  f0_track_kernel<<<dim3(dgc_div_up(T, 256), B), 256, 0, ctx->stream>>>(play, f0_dev, B, T, F, f0t);
+  DGC_LAUNCHED(ctx, "f0_track");
+  if (p->phase_mode == DGC_PHASE_SEQUENTIAL) {
+    anchor_seq_kernel<<<dgc_div_up(B * K, 32), 32, 0, ctx->stream>>>(f0t, B, T, K, sr, rsr, anchors);
+    DGC_LAUNCHED(ctx, "anchor_seq");
+  } else {
+    anchor_sum_kernel<<<dim3(C, B), ((K + 31) / 32) * 32, 0, ctx->stream>>>(f0t, B, T, K, sr, rsr, sums);
+    DGC_LAUNCHED(ctx, "anchor_sum");
+    anchor_scan_kernel<<<dgc_div_up(B * K, 64), 64, 0, ctx->stream>>>(sums, B, C, K, anchors);
+    DGC_LAUNCHED(ctx, "anchor_scan");
+  }
+#define RENDER(LPC, P) launch_render<LPC, P>(ctx, *p, play, f0_dev, uv_dev, amps_dev, gain_dev, anchors, audio_dev)
+  if (K <= 8) RENDER(8, 1);
+  else if (K <= 16) RENDER(8, 2);
+  else if (K <= 32) RENDER(8, 4);
+  else if (K <= 64) RENDER(8, 8);
+  else if (K <= 104) RENDER(8, 13);
+  else if (K <= 128) RENDER(8, 16);
+  else if (K <= 256) RENDER(16, 16);
+  else RENDER(32, 16);
+#undef RENDER
+  DGC_LAUNCHED(ctx, "harmonic_render");
+  return DGC_OK;
+}

@@ -1,0 +1,261 @@
+"""Host-side binding of libdgen_cuda.so (ctypes) for tests, the benchmark and Python callers.
+
+The product is the shared library behind include/dgen_cuda.h; this module only loads it, declares
+the C signatures and offers thin helpers that pass `torch` CUDA tensors as raw device pointers.
+There is no CPU fallback: importing works anywhere, but every compute entry point needs the
+library and a CUDA device, and raises `DgenCudaError` otherwise.
+"""
+import ctypes as C
+import os
+
+PKG_DIR = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+LIB_PATH = os.path.join(PKG_DIR, "libdgen_cuda.so")
+
+DGC_OK = 0
+PHASE_DETERMINISTIC, PHASE_SEQUENTIAL, PHASE_SCAN = 0, 1, 2
+MSS_MAX_SCALES = 8
+
+
+class DgenCudaError(RuntimeError):
+    pass
+
+
+class HarmonicParams(C.Structure):
+    _fields_ = [("B", C.c_int32), ("T", C.c_int32), ("K", C.c_int32), ("F", C.c_int32),
+                ("sample_rate", C.c_float), ("harmonic_scale", C.c_float),
+                ("phase_mode", C.c_int32), ("accumulate", C.c_int32)]
+
+
+class FirParams(C.Structure):
+    _fields_ = [("B", C.c_int32), ("T", C.c_int32), ("F", C.c_int32), ("taps", C.c_int32),
+                ("scale", C.c_float), ("accumulate", C.c_int32)]
+
+
+class MssParams(C.Structure):
+    _fields_ = [("B", C.c_int32), ("T", C.c_int32), ("nscales", C.c_int32),
+                ("sizes", C.c_int32 * MSS_MAX_SCALES), ("hop_div", C.c_int32),
+                ("w_lin", C.c_float), ("w_log", C.c_float)]
+
+
+class BiquadParams(C.Structure):
+    _fields_ = [("B", C.c_int32), ("T", C.c_int32), ("L", C.c_int32), ("gain", C.c_float), ("mode", C.c_float)]
+
+
+class HnStep(C.Structure):
+    _fields_ = [("harm", HarmonicParams), ("fir", FirParams), ("mss", MssParams), ("nbands", C.c_int32)]
+
+
+_vp, _i32, _i64, _u64, _u32, _f = C.c_void_p, C.c_int32, C.c_int64, C.c_uint64, C.c_uint32, C.c_float
+
+# name -> (restype, argtypes); one line per declaration of include/dgen_cuda.h
+SIGNATURES = {
+    "dgc_abi_version": (_i32, []),
+    "dgc_ctx_create": (_i32, [_i32, C.POINTER(_vp)]),
+    "dgc_ctx_destroy": (_i32, [_vp]),
+    "dgc_last_error": (C.c_char_p, [_vp]),
+    "dgc_ctx_set_stream": (_i32, [_vp, _vp]),
+    "dgc_sync": (_i32, [_vp, _u32]),
+    "dgc_profile_begin": (_i32, [_vp]),
+    "dgc_profile_end": (_i32, [_vp, C.POINTER(_f)]),
+    "dgc_launch_count": (_i64, [_vp]),
+    "dgc_arena_create": (_i32, [_vp, _u64, C.POINTER(_vp)]),
+    "dgc_arena_destroy": (_i32, [_vp]),
+    "dgc_arena_ptr": (_vp, [_vp]),
+    "dgc_arena_size": (_u64, [_vp]),
+    "dgc_arena_zero": (_i32, [_vp]),
+    "dgc_arena_upload": (_i32, [_vp, _u64, _vp, _u64]),
+    "dgc_arena_download": (_i32, [_vp, _u64, _vp, _u64]),
+    "dgc_clock_accum": (_i32, [_vp, _f, _f, _f, _f, _i32, _vp]),
+    "dgc_playhead": (_i32, [_vp, _i32, _i32, C.POINTER(_vp)]),
+    "dgc_osc_bank_const": (_i32, [_vp, _vp, _vp, _i32, _i32, _f, _i32, _vp]),
+    "dgc_harmonic_scratch_floats": (_u64, [C.POINTER(HarmonicParams)]),
+    "dgc_harmonic_render": (_i32, [_vp, C.POINTER(HarmonicParams), _vp, _vp, _vp, _vp, _vp, _vp]),
+    "dgc_fir_noise": (_i32, [_vp, C.POINTER(FirParams), _vp, _vp, _vp, _vp]),
+    "dgc_bands_to_taps": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _vp]),
+    "dgc_mss_partial_floats": (_u64, [C.POINTER(MssParams)]),
+    "dgc_mss_loss_fwd": (_i32, [_vp, C.POINTER(MssParams), _vp, _vp, _vp, _vp]),
+    "dgc_hn_forward_loss_host": (_i32, [_vp, C.POINTER(HnStep)] + [_vp] * 9 + [C.POINTER(C.c_double), _vp]),
+}
+
+_lib = None
+
+
+def load():
+    """Load libdgen_cuda.so (built in-tree by dgen-audio_b200/build.py).  Raises if it is missing."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise DgenCudaError("libdgen_cuda.so not found at %s: run `python dgen-audio_b200/build.py` "
+                            "(there is no CPU fallback)" % LIB_PATH)
+    lib = C.CDLL(LIB_PATH)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError if the library does not export a declared symbol
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib
+
+
+def mss_params(B, T, sizes=(2048, 1024, 512, 256, 128, 64), hop_div=4, w_lin=1.0, w_log=1.0):
+    p = MssParams()
+    p.B, p.T, p.nscales, p.hop_div, p.w_lin, p.w_log = B, T, len(sizes), hop_div, w_lin, w_log
+    for i, s in enumerate(sizes):
+        p.sizes[i] = s
+    return p
+
+
+def _ptr(t):
+    """Device pointer of a contiguous float32 CUDA tensor (or None)."""
+    if t is None:
+        return None
+    assert t.is_cuda and t.is_contiguous(), "expected a contiguous CUDA tensor"
+    return t.data_ptr()
+
+
+class Context:
+    """One dgc_ctx on one GPU.  Methods take torch CUDA tensors and enqueue on torch's current stream."""
+
+    def __init__(self, device=0, use_torch_stream=True):
+        import torch
+        if not torch.cuda.is_available():
+            raise DgenCudaError("no CUDA device: libdgen_cuda has no CPU path")
+        self.lib = load()
+        self.torch = torch
+        self.device = device
+        torch.cuda.set_device(device)
+        h = _vp()
+        rc = self.lib.dgc_ctx_create(device, C.byref(h))
+        if rc != DGC_OK:
+            raise DgenCudaError("dgc_ctx_create failed: %d" % rc)
+        self.h = h
+        if use_torch_stream:
+            self.check(self.lib.dgc_ctx_set_stream(self.h, torch.cuda.current_stream(device).cuda_stream))
+
+    def close(self):
+        if getattr(self, "h", None):
+            self.lib.dgc_ctx_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def check(self, rc):
+        if rc != DGC_OK:
+            raise DgenCudaError("libdgen_cuda error %d: %s" % (rc, self.lib.dgc_last_error(self.h).decode()))
+
+    def sync(self, timeout_ms=0):
+        self.check(self.lib.dgc_sync(self.h, timeout_ms))
+
+    def launch_count(self):
+        return self.lib.dgc_launch_count(self.h)
+
+    def _empty(self, *shape, dtype=None):
+        return self.torch.empty(*shape, dtype=dtype or self.torch.float32, device="cuda:%d" % self.device)
+
+    # ---- clocks -----------------------------------------------------------------------------
+    def clock_accum(self, incr, mn, mx, T, state0=0.0):
+        out = self._empty(T)
+        self.check(self.lib.dgc_clock_accum(self.h, incr, mn, mx, state0, T, _ptr(out)))
+        return out
+
+    def playhead(self, F, T):
+        """Copy of the context's cached control clock for (F, T) in a tensor the caller owns."""
+        p = _vp()
+        self.check(self.lib.dgc_playhead(self.h, F, T, C.byref(p)))
+        out = self._empty(T)
+        self.torch.cuda.synchronize()
+        rc = _cudart().cudaMemcpy(C.c_void_p(out.data_ptr()), p, C.c_size_t(4 * T), 3)  # device to device
+        if rc != 0:
+            raise DgenCudaError("cudaMemcpy of the playhead failed: %d" % rc)
+        return out
+
+    # ---- oscillator bank ----------------------------------------------------------------------
+    def osc_bank_const(self, freq, amp, T, sr, phase_mode=PHASE_DETERMINISTIC):
+        out = self._empty(T)
+        self.check(self.lib.dgc_osc_bank_const(self.h, _ptr(freq), _ptr(amp), freq.numel(), T, sr, phase_mode,
+                                               _ptr(out)))
+        return out
+
+    def harmonic_render(self, f0, uv, amps, gain, T, sr, phase_mode=PHASE_SCAN, scale=1.0, out=None,
+                        accumulate=False, scratch=None):
+        F, B = f0.shape
+        K = amps.shape[2]
+        p = HarmonicParams(B, T, K, F, sr, scale, phase_mode, int(accumulate))
+        if out is None:
+            out = self._empty(B, T)
+        self.check(self.lib.dgc_harmonic_render(self.h, C.byref(p), _ptr(f0), _ptr(uv), _ptr(amps), _ptr(gain),
+                                                _ptr(scratch), _ptr(out)))
+        return out
+
+    def harmonic_scratch_floats(self, B, T, K, F):
+        p = HarmonicParams(B, T, K, F, 1.0, 1.0, PHASE_SCAN, 0)
+        return self.lib.dgc_harmonic_scratch_floats(C.byref(p))
+
+    def fir_noise(self, noise, taps, noise_gain, scale=0.12, out=None, accumulate=False):
+        F, B, NT = taps.shape
+        T = noise.shape[1]
+        p = FirParams(B, T, F, NT, scale, int(accumulate))
+        if out is None:
+            out = self._empty(B, T)
+        self.check(self.lib.dgc_fir_noise(self.h, C.byref(p), _ptr(noise), _ptr(taps), _ptr(noise_gain), _ptr(out)))
+        return out
+
+    def bands_to_taps(self, bands, w):
+        F, B, NB = bands.shape
+        NT = w.shape[0]
+        out = self._empty(F, B, NT)
+        self.check(self.lib.dgc_bands_to_taps(self.h, _ptr(bands), _ptr(w), F * B, NB, NT, _ptr(out)))
+        return out
+
+    # ---- spectral loss ------------------------------------------------------------------------
+    def mss_loss_fwd(self, pred, target, sizes=(2048, 1024, 512, 256, 128, 64), hop_div=4, w_lin=1.0, w_log=1.0,
+                     want_partial=False):
+        B, T = pred.shape
+        p = mss_params(B, T, sizes, hop_div, w_lin, w_log)
+        loss = self._empty(1, dtype=self.torch.float64)
+        part = None
+        if want_partial:
+            part = self._empty(int(self.lib.dgc_mss_partial_floats(C.byref(p))))
+        self.check(self.lib.dgc_mss_loss_fwd(self.h, C.byref(p), _ptr(pred), _ptr(target), _ptr(part), _ptr(loss)))
+        return (loss, part) if want_partial else loss
+
+    # ---- composite, host buffers --------------------------------------------------------------
+    def hn_forward_loss_host(self, step, f0, uv, amps, gain, noise_gain, taps_or_bands, w, noise, target,
+                             audio_out=None):
+        """All array arguments are host numpy float32 arrays or pinned CPU torch tensors."""
+        def hp(a):
+            if a is None:
+                return None
+            if hasattr(a, "data_ptr"):
+                return a.data_ptr()
+            return a.ctypes.data
+        loss = C.c_double(0.0)
+        self.check(self.lib.dgc_hn_forward_loss_host(self.h, C.byref(step), hp(f0), hp(uv), hp(amps), hp(gain),
+                                                     hp(noise_gain), hp(taps_or_bands), hp(w), hp(noise),
+                                                     hp(target), C.byref(loss), hp(audio_out)))
+        return loss.value
+
+
+_cudart_lib = None
+
+
+def _cudart():
+    """The CUDA runtime torch already loaded (for plain cudaMemcpy of library-owned device tables)."""
+    global _cudart_lib
+    if _cudart_lib is None:
+        import torch  # noqa: F401
+        import glob
+        cands = glob.glob(os.path.join(os.path.dirname(torch.__file__), "lib", "libcudart*.so*"))
+        cands += glob.glob("/usr/local/cuda/lib64/libcudart.so*")
+        site = os.path.dirname(os.path.dirname(torch.__file__))
+        cands = glob.glob(os.path.join(site, "nvidia", "cuda_runtime", "lib", "libcudart.so*")) + cands
+        if not cands:
+            raise DgenCudaError("libcudart not found")
+        _cudart_lib = C.CDLL(cands[0])
+        _cudart_lib.cudaMemcpy.restype = C.c_int
+        _cudart_lib.cudaMemcpy.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int]
+    return _cudart_lib

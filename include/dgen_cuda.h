@@ -1,0 +1,183 @@
+/*
+ * dgen_cuda.h -- C ABI of libdgen_cuda.so: the sm_100a implementation of DGen's frame-parallel
+ * render path (oscillator bank, linear recurrences, hop-gated FFT / overlap-add / partitioned
+ * convolution, multi-scale spectral loss, controller matmul, Adam).
+ *
+ * This is the boundary a host (DGen's Swift `CUDALazyRuntime`, or any C caller) binds.  Plain
+ * pointers and sizes only.  Every function returns a status (DGC_OK = 0, negative = error) and
+ * never throws or aborts; dgc_last_error() gives the text for the last failure on a context.
+ * All work is enqueued on the context's CUDA stream; dgc_sync() is the only blocking call.
+ * One context per GPU; calls on one context must be serialised by the caller (the reference's
+ * runtimes have the same rule: one global graph, not thread-safe, Sources/DGenLazy/LazyGraph.swift:241-264).
+ *
+ * Pointers named *_dev are CUDA device pointers (for example dgc_arena_ptr() + an offset, which
+ * replaces the reference's host-visible `float *memory` arena, Sources/DGen/Runtime.swift:732-744);
+ * pointers named *_host are ordinary host memory.
+ *
+ * Layouts.  Batched audio is voice-major `[B][T]` floats.  Control tables are `[F][B]` and
+ * `[F][B][K]` exactly as Examples/HarmonicE2E/Synth.swift:72-75 builds them.  Lane signals of the
+ * biquad bank are `[B][T][L]` (lanes fastest, the reference's frame-major tensor layout,
+ * Sources/DGenLazy/Realize.swift:418-436).
+ *
+ * In the comments below "replaces" names the reference code whose work the entry point does.
+ */
+#ifndef DGEN_CUDA_H
+#define DGEN_CUDA_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DGC_ABI_VERSION 1
+
+enum {
+  DGC_OK = 0,
+  DGC_ERR_INVALID = -1,   /* bad argument (null pointer, size out of range, unsupported shape) */
+  DGC_ERR_CUDA = -2,      /* a CUDA runtime call or launch failed; text in dgc_last_error */
+  DGC_ERR_OOM = -3,       /* device allocation failed */
+  DGC_ERR_TIMEOUT = -4,   /* dgc_sync: the stream did not drain in time */
+  DGC_ERR_DEVICE = -5,    /* a kernel reported a device-side error through the status word */
+  DGC_ERR_UNSUPPORTED = -6
+};
+
+typedef struct dgc_ctx dgc_ctx;
+typedef struct dgc_arena dgc_arena;
+
+/* ---- context ------------------------------------------------------------------------------------
+ * replaces: MetalCompiledKernel.init / CCompiledKernel.compileAndLoad as the owner of device,
+ * queue and scratch (Sources/DGen/MetalRuntime.swift:40, Sources/DGen/Runtime.swift:240-340). */
+int32_t dgc_abi_version(void);
+int32_t dgc_ctx_create(int32_t device, dgc_ctx **out);
+int32_t dgc_ctx_destroy(dgc_ctx *ctx);
+const char *dgc_last_error(dgc_ctx *ctx);
+/* Use an existing CUDA stream (a cudaStream_t) instead of the context's own; NULL restores it. */
+int32_t dgc_ctx_set_stream(dgc_ctx *ctx, void *cuda_stream);
+/* Waits for the stream, at most timeout_ms (0 = no limit), then checks the device status word. */
+int32_t dgc_sync(dgc_ctx *ctx, uint32_t timeout_ms);
+/* Event timing on the context's stream (replaces profileKernels, Sources/DGen/MetalRuntime.swift:397-425). */
+int32_t dgc_profile_begin(dgc_ctx *ctx);
+int32_t dgc_profile_end(dgc_ctx *ctx, float *elapsed_ms);
+/* Number of kernels this library has launched on the context since creation. */
+int64_t dgc_launch_count(dgc_ctx *ctx);
+
+/* ---- arena --------------------------------------------------------------------------------------
+ * replaces: the caller-owned flat float arena `state` of dgen_process_v1
+ * (toolchain/include/dgen_runtime.h:282-288) and LazyRuntime.memoryPointer()
+ * (Sources/DGenLazy/Realize.swift:12-19): device memory plus explicit upload / download. */
+int32_t dgc_arena_create(dgc_ctx *ctx, uint64_t nfloats, dgc_arena **out);
+int32_t dgc_arena_destroy(dgc_arena *a);
+float *dgc_arena_ptr(dgc_arena *a);
+uint64_t dgc_arena_size(dgc_arena *a);
+int32_t dgc_arena_zero(dgc_arena *a);                                          /* zeroAllBuffers */
+int32_t dgc_arena_upload(dgc_arena *a, uint64_t offset, const float *src_host, uint64_t n);   /* injectTensorData */
+int32_t dgc_arena_download(dgc_arena *a, uint64_t offset, float *dst_host, uint64_t n);       /* readOutputs / readGradients */
+
+/* ---- scalar clocks ------------------------------------------------------------------------------
+ * replaces: scalar `accum` (Sources/DGen/Definitions.swift:215-246): out[n] = state before the
+ * n-th update, sequential single-precision semantics (the rounding of every step is part of the
+ * result).  One thread; meant for data-independent clocks that are computed once and kept. */
+int32_t dgc_clock_accum(dgc_ctx *ctx, float incr, float min, float max, float state0, int32_t T, float *out_dev);
+/* The control playhead of the batched harmonic synth (Examples/HarmonicE2E/Synth.swift:57-70):
+ * clip(accum((F-1)/(T-1), 0, F-1), 0, F-1-1e-4).  Cached per (F, T) inside the context. */
+int32_t dgc_playhead(dgc_ctx *ctx, int32_t F, int32_t T, const float **out_dev);
+
+/* ---- oscillator bank ----------------------------------------------------------------------------
+ * How the phase of a stateful phasor is carried across the time axis. */
+enum {
+  /* frac((f/sr) * n): deterministicPhasor (Sources/DGen/Emit+State.swift:370-387); constant f only */
+  DGC_PHASE_DETERMINISTIC = 0,
+  /* the reference's recurrence, one single-precision add + wrap per sample, carried serially by
+   * one thread per (voice, partial): bit-identical phases (Emit+State.swift:322-369) */
+  DGC_PHASE_SEQUENTIAL = 1,
+  /* frame-parallel: increments are summed exactly (64-bit fixed point) by a prefix scan across
+   * chunks of 64 frames; inside a chunk the single-precision recurrence is followed.  Differs from
+   * SEQUENTIAL only by the rounding drift the serial recurrence accumulates across chunks. */
+  DGC_PHASE_SCAN = 2
+};
+
+/* Constant-frequency bank summed to mono: audio[n] = sum_k sin(phase_k[n]*2pi) * amp[k].
+ * replaces: phasor/deterministicPhasor + sin + mul + sum (Emit+State.swift:322-387,
+ * Sources/DGen/Renderer/CRenderer.swift:825-827). */
+int32_t dgc_osc_bank_const(dgc_ctx *ctx, const float *freq_dev, const float *amp_dev, int32_t K, int32_t T,
+                           float sample_rate, int32_t phase_mode, float *audio_dev);
+
+typedef struct dgc_harmonic_params {
+  int32_t B;            /* voices */
+  int32_t T;            /* frames */
+  int32_t K;            /* partials per voice (1..512) */
+  int32_t F;            /* control frames */
+  float sample_rate;
+  float harmonic_scale; /* harmonicPathScale */
+  int32_t phase_mode;   /* DGC_PHASE_SEQUENTIAL or DGC_PHASE_SCAN */
+  int32_t accumulate;   /* 0: audio = harmonics ; 1: audio += harmonics */
+} dgc_harmonic_params;
+
+/* Harmonic branch of HarmonicSynth.renderBatchedSignal (Examples/HarmonicE2E/Synth.swift:47-95):
+ * sampleRow of f0/uv/gain [F][B] and amps [F][B][K] at the playhead (Emit+RowSelection.swift:145-213),
+ * Nyquist mask + renormalise (Synth.swift:161-170), stateful phasor of k*f0, sin, weighted sum over
+ * partials, times gain*uv*scale.  audio is [B][T].
+ * scratch: needs dgc_harmonic_scratch_floats(p) floats of device memory (phase anchors and the
+ * per-sample fundamental); pass NULL to let the context keep a buffer of its own. */
+uint64_t dgc_harmonic_scratch_floats(const dgc_harmonic_params *p);
+int32_t dgc_harmonic_render(dgc_ctx *ctx, const dgc_harmonic_params *p, const float *f0_dev, const float *uv_dev,
+                            const float *amps_dev, const float *gain_dev, float *scratch_dev, float *audio_dev);
+
+typedef struct dgc_fir_params {
+  int32_t B, T, F;
+  int32_t taps;        /* FIR length (1..1024); tap taps-1 multiplies the current sample */
+  float scale;         /* 0.12 * noisePathScale in the reference */
+  int32_t accumulate;  /* 0: audio = branch ; 1: audio += branch */
+} dgc_fir_params;
+
+/* Noise branch (Synth.swift:97-101): per-sample interpolated FIR over buffer(size: taps) of the
+ * noise input: y[n] = (sum_i x[n-taps+1+i] * lerp(taps_tab)[i]) * lerp(noise_gain) * scale.
+ * noise [B][T], taps_tab [F][B][taps], noise_gain [F][B]. */
+int32_t dgc_fir_noise(dgc_ctx *ctx, const dgc_fir_params *p, const float *noise_dev, const float *taps_dev,
+                      const float *noise_gain_dev, float *audio_dev);
+
+/* taps[r][i] = sum_j W[i][j] * bands[r][j]  (rows r = F*B, W is [taps][nbands]): the linear map
+ * from band magnitudes to zero-phase FIR taps used by the synthetic harmonic+noise workload. */
+int32_t dgc_bands_to_taps(dgc_ctx *ctx, const float *bands_dev, const float *w_dev, int32_t rows, int32_t nbands,
+                          int32_t taps, float *taps_dev);
+
+/* ---- multi-scale spectral loss ------------------------------------------------------------------ */
+#define DGC_MSS_MAX_SCALES 8
+typedef struct dgc_mss_params {
+  int32_t B, T;
+  int32_t nscales;
+  int32_t sizes[DGC_MSS_MAX_SCALES]; /* powers of two, 16..4096 */
+  int32_t hop_div;                   /* hop = size / hop_div */
+  float w_lin, w_log;                /* weights of the L1 linear / L1 log-magnitude terms */
+} dgc_mss_params;
+
+/* spectralLossFFTBatched forward for every scale, linear and log-magnitude terms from one FFT
+ * (HigherOps.swift:165-263, Emit+SpectralLoss.swift:719-938, Examples/HarmonicE2E/Trainer.swift:538-588):
+ * loss = sum_scales (w_lin*lin_s + w_log*log_s) / nscales / T, each term the sum over hop frames of
+ * the batch mean.  pred/target [B][T].  loss_dev receives one double.
+ * partial_dev (optional) receives per (scale, hop frame, voice) sums: lin then log, see
+ * dgc_mss_partial_floats(). */
+uint64_t dgc_mss_partial_floats(const dgc_mss_params *p);
+int32_t dgc_mss_loss_fwd(dgc_ctx *ctx, const dgc_mss_params *p, const float *pred_dev, const float *target_dev,
+                         float *partial_dev, double *loss_dev);
+/* ---- composite steps with host buffers (the call a host makes per batch) ------------------------ */
+typedef struct dgc_hn_step {
+  dgc_harmonic_params harm;
+  dgc_fir_params fir;      /* fir.taps == 0 disables the noise branch */
+  dgc_mss_params mss;
+  int32_t nbands;          /* > 0: taps are synthesised from bands_host [F][B][nbands] with w_host [taps][nbands] */
+} dgc_hn_step;
+
+/* Harmonic+noise synthesis forward + multi-scale spectral loss, inputs and result in host memory:
+ * uploads the control tables, noise and target, renders, evaluates the loss and returns it.
+ * audio_host may be NULL.  replaces: one realize() of the HarmonicE2E forward graph. */
+int32_t dgc_hn_forward_loss_host(dgc_ctx *ctx, const dgc_hn_step *s, const float *f0_host, const float *uv_host,
+                                 const float *amps_host, const float *gain_host, const float *noise_gain_host,
+                                 const float *taps_or_bands_host, const float *w_host, const float *noise_host,
+                                 const float *target_host, double *loss_host, float *audio_host);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

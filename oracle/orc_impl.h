@@ -470,6 +470,9 @@ double FN(orc_spectral_loss)(const R *x1, const R *x2, int B, int T, int N, int 
 double FN(orc_mss_loss)(const R *x1, const R *x2, int B, int T, const int *sizes, int nscales, int hop_div,
                         R w_lin, R w_log) {
   double total = 0;
+  int usable = 0;
+  for (int s = 0; s < nscales; ++s)
+    if (sizes[s] > 1 && sizes[s] <= T) ++usable;
   for (int s = 0; s < nscales; ++s) {
     int N = sizes[s];
     if (N <= 1 || N > T) continue;
@@ -477,7 +480,7 @@ double FN(orc_mss_loss)(const R *x1, const R *x2, int B, int T, const int *sizes
     if (hop < 1) hop = 1;
     double lin = w_lin != 0 ? FN(orc_spectral_loss)(x1, x2, B, T, N, hop, 0, 0, 0) : 0;
     double lg = w_log != 0 ? FN(orc_spectral_loss)(x1, x2, B, T, N, hop, 1, 0, 0) : 0;
-    total += (lin * (double)w_lin + lg * (double)w_log) / (double)nscales / (double)T;
+    total += (lin * (double)w_lin + lg * (double)w_log) / (double)usable / (double)T;
   }
   return total;
 }

@@ -1,0 +1,119 @@
+"""GPU parity of the oscillator bank, noise FIR and clocks against the CPU oracle (through the C ABI)."""
+import numpy as np
+import pytest
+
+import dgen_b200
+from dgen_b200 import workloads as wl
+from oracle import oracle as orc
+
+pytestmark = pytest.mark.gpu
+f32 = np.float32
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    c = dgen_b200.Context(0)
+    yield c
+    c.close()
+
+
+def dev(a):
+    import torch
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def test_clock_accum_bit_exact(ctx):
+    for incr, mn, mx, T in ((0.1, 0.0, 1.0, 4096), (1.0, 0.0, 79.0, 1000), (0.37, -2.0, 3.0, 5000)):
+        got = ctx.clock_accum(incr, mn, mx, T).cpu().numpy()
+        assert np.array_equal(got, orc.accum(incr, mn, mx, T))
+
+
+def test_playhead_bit_exact(ctx):
+    for F, T in ((1000, 64000), (250, 16000), (1, 512), (7, 1001)):
+        assert np.array_equal(ctx.playhead(F, T).cpu().numpy(), orc.playhead(F, T))
+
+
+def test_osc_bank_const_deterministic_matches_oracle(ctx):
+    # the oscillator-bank -> filter -> FFT configuration: 64 partials, 110*k Hz, 1/k, sr 44100, 65536 frames
+    c = wl.osc_filter_fft_inputs()
+    want = orc.osc_bank_const(c["freq"], c["amp"], c["T"], c["sr"], stateful=False)
+    got = ctx.osc_bank_const(dev(c["freq"]), dev(c["amp"]), c["T"], c["sr"], dgen_b200.PHASE_DETERMINISTIC)
+    assert np.abs(got.cpu().numpy() - want).max() < 1e-4  # forward audio tolerance of the path: 1e-4
+
+
+def test_osc_bank_const_sequential_matches_oracle(ctx):
+    c = wl.osc_filter_fft_inputs(T=16384)
+    want = orc.osc_bank_const(c["freq"], c["amp"], c["T"], c["sr"], stateful=True)
+    got = ctx.osc_bank_const(dev(c["freq"]), dev(c["amp"]), c["T"], c["sr"], dgen_b200.PHASE_SEQUENTIAL)
+    assert np.abs(got.cpu().numpy() - want).max() < 2e-5
+
+
+def test_known_answers_through_the_abi(ctx):
+    # Tests/DGenLazyTests/CBackendTests.swift:63-76: 1 Hz at sr 4 -> 0, 1, 0, -1
+    for mode in (dgen_b200.PHASE_DETERMINISTIC, dgen_b200.PHASE_SEQUENTIAL):
+        got = ctx.osc_bank_const(dev(np.array([1.0], f32)), dev(np.array([1.0], f32)), 4, 4.0, mode).cpu().numpy()
+        assert np.allclose(got, [0, 1, 0, -1], atol=1e-4)
+
+
+def _render_both(ctx, d, mode, noise=True):
+    T, sr = d["T"], d["sr"]
+    taps = wl.taps_from_bands(d) if noise else None
+    want = orc.harmonic_noise_render(d["f0"], d["uv"], d["amps"], d["gain"], d["noise_gain"], taps,
+                                     d["noise"] if noise else None, T, sr)
+    audio = ctx.harmonic_render(dev(d["f0"]), dev(d["uv"]), dev(d["amps"]), dev(d["gain"]), T, sr, phase_mode=mode)
+    if noise:
+        taps_dev = ctx.bands_to_taps(dev(d["bands"]), dev(d["W"]))
+        assert np.abs(taps_dev.cpu().numpy() - taps).max() < 1e-5
+        ctx.fir_noise(dev(d["noise"]), taps_dev, dev(d["noise_gain"]), out=audio, accumulate=True)
+    ctx.sync()
+    return audio.cpu().numpy(), want
+
+
+@pytest.mark.parametrize("shape", [dict(B=2, T=4096, K=100, F=64), dict(B=3, T=5000, K=7, F=33),
+                                   dict(B=1, T=1000, K=1, F=2), dict(B=2, T=2048, K=130, F=40),
+                                   dict(B=1, T=640, K=300, F=11)])
+def test_harmonic_render_sequential_matches_oracle(ctx, shape):
+    d = wl.harmonic_noise_inputs(11, sr=16000.0, **shape)
+    got, want = _render_both(ctx, d, dgen_b200.PHASE_SEQUENTIAL, noise=False)
+    assert np.abs(got - want).max() < 2e-5
+
+
+def test_harmonic_noise_render_full_config_both_phase_modes(ctx):
+    """The batched harmonic+noise configuration at full size (B=16, T=64000, K=100, 65 bands, 257 taps)."""
+    d = wl.harmonic_noise_inputs(20260001)
+    got, want = _render_both(ctx, d, dgen_b200.PHASE_SEQUENTIAL)
+    err_seq = np.abs(got - want).max()
+    got2, _ = _render_both(ctx, d, dgen_b200.PHASE_SCAN)
+    err_scan = np.abs(got2 - want).max()
+    print("max abs err: sequential %.3g, scan %.3g" % (err_seq, err_scan))
+    assert err_seq < 2e-5
+    assert err_scan < 1e-4  # the stated forward tolerance
+
+
+def test_fir_noise_ragged_and_short(ctx):
+    for B, T, F, NT in ((2, 3000, 50, 257), (1, 100, 5, 17), (2, 2049, 9, 64), (1, 5000, 1, 33)):
+        rng = np.random.default_rng(T)
+        taps = rng.standard_normal((F, B, NT)).astype(f32)
+        noise = rng.standard_normal((B, T)).astype(f32)
+        ng = rng.uniform(0, 1, (F, B)).astype(f32)
+        K = 1
+        z = np.zeros((F, B), f32)
+        want = orc.harmonic_noise_render(z + 100, z, np.ones((F, B, K), f32), z, ng, taps, noise, T, 16000.0)
+        got = ctx.fir_noise(dev(noise), dev(taps), dev(ng)).cpu().numpy()
+        scale = max(1.0, np.abs(want).max())
+        assert np.abs(got - want).max() < 2e-5 * scale
+
+
+def test_render_is_deterministic(ctx):
+    d = wl.harmonic_noise_inputs(5, B=2, T=8192, K=100, F=128)
+    a = ctx.harmonic_render(dev(d["f0"]), dev(d["uv"]), dev(d["amps"]), dev(d["gain"]), d["T"], d["sr"]).cpu().numpy()
+    b = ctx.harmonic_render(dev(d["f0"]), dev(d["uv"]), dev(d["amps"]), dev(d["gain"]), d["T"], d["sr"]).cpu().numpy()
+    assert np.array_equal(a, b)
+
+
+def test_bad_arguments_return_errors(ctx):
+    import torch
+    with pytest.raises(dgen_b200.DgenCudaError):
+        ctx.osc_bank_const(torch.zeros(1, device="cuda"), torch.zeros(1, device="cuda"), 0, 44100.0)
+    with pytest.raises(dgen_b200.DgenCudaError):
+        ctx.clock_accum(1.0, 1.0, 1.0, 16)
