@@ -154,9 +154,9 @@ DGC_EXPORT int32_t dgc_ctx_destroy(dgc_ctx *c) {
 
 DGC_EXPORT const char *dgc_last_error(dgc_ctx *ctx) { return ctx ? ctx->err : "null context"; }
 
-DGC_EXPORT int32_t dgc_ctx_set_stream(dgc_ctx *ctx, void *s) {
+DGC_EXPORT int32_t dgc_ctx_set_stream(dgc_ctx *ctx, void *s, int32_t external) {
   if (!ctx) return DGC_ERR_INVALID;
-  ctx->stream = s ? (cudaStream_t)s : ctx->own_stream;
+  ctx->stream = external ? (cudaStream_t)s : ctx->own_stream;
   return DGC_OK;
 }
 

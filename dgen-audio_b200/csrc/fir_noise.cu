@@ -31,13 +31,28 @@ fir_noise_kernel(dgc_fir_params prm, const float *__restrict__ play, const float
   constexpr int TILE = 256 * SPT;
   const int b = blockIdx.y, t0 = blockIdx.x * TILE;
   const int t_last = min(T - 1, t0 + TILE - 1);
+  // The control clock wraps to 0 when it reaches its maximum (the sequential single-precision
+  // clock runs slightly fast, so this happens a few frames before the end of the render).  Find
+  // the wrap frame of this tile, if any; row numbers after it are unwrapped (+F) so that the rows a
+  // tile touches stay one contiguous run.
+  __shared__ int wrap_sh;
+  if (threadIdx.x == 0) wrap_sh = 0x7fffffff;
+  __syncthreads();
+#pragma unroll
+  for (int u = 0; u < SPT; ++u) {
+    int n = t0 + threadIdx.x * SPT + u;
+    if (n > t0 && n <= t_last && play[n] < play[n - 1]) atomicMin(&wrap_sh, n);
+  }
+  __syncthreads();
+  const int wrap = wrap_sh;
   int rmin, rmax;
   float dummy;
   row_pos(play[t0], F, rmin, dummy);
   row_pos(play[t_last], F, rmax, dummy);
+  if (t_last >= wrap) rmax += F;
   const int R = rmax - rmin + 3;  // rows rmin .. rmax+2 (hi of the last frame, and the straddle row)
-  if (rmax < rmin || R > max_rows) {
-    if (threadIdx.x == 0) atomicExch(status, 101);  // playhead not monotone or step too large for the tile
+  if (R > max_rows) {
+    if (threadIdx.x == 0) atomicExch(status, 101);  // control rate too high for the staged tile
     return;
   }
   float *rows = sh;                          // [R][NT]
@@ -67,9 +82,11 @@ fir_noise_kernel(dgc_fir_params prm, const float *__restrict__ play, const float
   for (int u = 0; u < SPT; ++u) {
     int n = min(t0 + nl + u, T - 1);
     row_pos(play[n], F, lo[u], fr[u]);
+    if (n >= wrap) lo[u] += F;
   }
   const int r0 = lo[0] - rmin;
-  const bool straddle = lo[SPT - 1] != lo[0];
+  const int spread = lo[SPT - 1] - lo[0];
+  const bool straddle = spread == 1;
   const float *ra = rows + (size_t)r0 * NT, *rb = ra + NT, *rc = rb + NT;
   float d0[SPT], d1[SPT], d2[SPT];
 #pragma unroll
@@ -106,15 +123,31 @@ fir_noise_kernel(dgc_fir_params prm, const float *__restrict__ play, const float
       for (int u = 0; u < SPT; ++u) d2[u] = fmaf(win[u], tc, d2[u]);
     }
   }
+  if (spread > 1 || spread < 0) {
+    // the frames of this thread sit across the clock wrap: evaluate each frame against its own rows
+#pragma unroll
+    for (int u = 0; u < SPT; ++u) {
+      const float *pa = rows + (size_t)(lo[u] - rmin) * NT, *pb = pa + NT;
+      float sa = 0.0f, sb = 0.0f;
+      for (int i = 0; i < NT; ++i) {
+        int m = nl + u + i;
+        float xv = xs[(m % SPT) * Q + m / SPT];
+        sa = fmaf(xv, pa[i], sa);
+        sb = fmaf(xv, pb[i], sb);
+      }
+      d0[u] = sa;
+      d1[u] = sb;
+    }
+  }
   float *dst = audio + (size_t)b * T;
 #pragma unroll
   for (int u = 0; u < SPT; ++u) {
     int n = t0 + nl + u;
     if (n >= T) break;
-    bool second = lo[u] != lo[0];
+    bool second = straddle && lo[u] != lo[0];
     float a = second ? d1[u] : d0[u], c = second ? d2[u] : d1[u];
     float omf = 1.0f - fr[u];
-    int l = lo[u], h = l + 1 >= F ? 0 : l + 1;
+    int l = lo[u] >= F ? lo[u] - F : lo[u], h = l + 1 >= F ? 0 : l + 1;
     float ng = fmaf(fr[u], ngain[(size_t)h * B + b], omf * ngain[(size_t)l * B + b]);
     float y = fmaf(fr[u], c, omf * a) * ng * prm.scale;
     dst[n] = prm.accumulate ? dst[n] + y : y;

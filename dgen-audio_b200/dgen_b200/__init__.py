@@ -53,7 +53,7 @@ SIGNATURES = {
     "dgc_ctx_create": (_i32, [_i32, C.POINTER(_vp)]),
     "dgc_ctx_destroy": (_i32, [_vp]),
     "dgc_last_error": (C.c_char_p, [_vp]),
-    "dgc_ctx_set_stream": (_i32, [_vp, _vp]),
+    "dgc_ctx_set_stream": (_i32, [_vp, _vp, _i32]),
     "dgc_sync": (_i32, [_vp, _u32]),
     "dgc_profile_begin": (_i32, [_vp]),
     "dgc_profile_end": (_i32, [_vp, C.POINTER(_f)]),
@@ -130,7 +130,7 @@ class Context:
             raise DgenCudaError("dgc_ctx_create failed: %d" % rc)
         self.h = h
         if use_torch_stream:
-            self.check(self.lib.dgc_ctx_set_stream(self.h, torch.cuda.current_stream(device).cuda_stream))
+            self.check(self.lib.dgc_ctx_set_stream(self.h, torch.cuda.current_stream(device).cuda_stream, 1))
 
     def close(self):
         if getattr(self, "h", None):

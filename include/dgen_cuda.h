@@ -52,8 +52,9 @@ int32_t dgc_abi_version(void);
 int32_t dgc_ctx_create(int32_t device, dgc_ctx **out);
 int32_t dgc_ctx_destroy(dgc_ctx *ctx);
 const char *dgc_last_error(dgc_ctx *ctx);
-/* Use an existing CUDA stream (a cudaStream_t) instead of the context's own; NULL restores it. */
-int32_t dgc_ctx_set_stream(dgc_ctx *ctx, void *cuda_stream);
+/* external != 0: enqueue on the caller's CUDA stream (a cudaStream_t; NULL is CUDA's default stream).
+ * external == 0: go back to the context's own stream. */
+int32_t dgc_ctx_set_stream(dgc_ctx *ctx, void *cuda_stream, int32_t external);
 /* Waits for the stream, at most timeout_ms (0 = no limit), then checks the device status word. */
 int32_t dgc_sync(dgc_ctx *ctx, uint32_t timeout_ms);
 /* Event timing on the context's stream (replaces profileKernels, Sources/DGen/MetalRuntime.swift:397-425). */

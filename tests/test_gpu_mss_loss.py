@@ -53,7 +53,9 @@ def test_multi_scale_total_matches_oracle_fp32_and_fp64(ctx):
 def test_identical_signals_give_zero_and_short_render_skips_long_windows(ctx):
     rng = np.random.default_rng(1)
     x = rng.standard_normal((2, 1000)).astype(f32)
-    assert float(ctx.mss_loss_fwd(dev(x), dev(x)).cpu()[0]) == 0.0
+    # prediction and target share one complex FFT, so identical inputs cancel to rounding, not to 0.0
+    # (the reference's own test accepts 0.01: Tests/DGenLazyTests/BatchedSpectralLossTests.swift:174-191)
+    assert abs(float(ctx.mss_loss_fwd(dev(x), dev(x)).cpu()[0])) < 1e-5
     y = rng.standard_normal((2, 1000)).astype(f32)
     got = float(ctx.mss_loss_fwd(dev(x), dev(y)).cpu()[0])   # 2048 and 1024 are longer than T: skipped
     want = orc.mss_loss(x, y)
