@@ -18,7 +18,8 @@ struct dgc_ctx {
   cudaStream_t own_stream = nullptr;
   cudaStream_t stream = nullptr;
   cudaEvent_t ev_begin = nullptr, ev_end = nullptr, ev_sync = nullptr;
-  int32_t *status_dev = nullptr;  // device status word: kernels report bounded-wait failures here
+  int32_t *status_dev = nullptr;  // device status word: kernels report failures here
+  unsigned int *ticket_dev = nullptr;  // last-block-done counter of the multi-block reductions (kept at 0)
   int64_t launches = 0;
   char err[512] = {0};
   int sm_count = 148;
@@ -30,7 +31,7 @@ struct dgc_ctx {
   std::map<int, float *> hann_sym;                   // N -> symmetric Hann (spectral loss)
   std::map<int, float *> hann_per;                   // N -> periodic Hann (hann())
   std::map<int, float2 *> twiddles;                  // N -> exp(-2 pi i m / N), m < N
-  double *loss_accum = nullptr;                      // small device buffer for reductions
+  double *loss_accum = nullptr;                      // 256 doubles: [0..64) results, [64..) per-block sums
   // staging for the host-buffer composite entry points
   float *stage_dev = nullptr;
   uint64_t stage_floats = 0;

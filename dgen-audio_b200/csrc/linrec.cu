@@ -1,0 +1,521 @@
+// Linear recurrences over time as chunked parallel scans: one-pole history feedback, the tensor
+// biquad bank forward, and the reverse-time (BPTT) pass that yields coefficient gradients.
+//
+// The reference runs these per sample through history cells (Sources/DGen/Emit+State.swift:150-224,
+// Sources/DGen/HigherOps.swift:401-570): one thread per lane, a serial loop over frames, and for
+// BPTT a stored forward tape plus a reverse loop (Sources/DGen/Blocks/Emission/BPTTEmission.swift:471-518).
+// Here time is cut into chunks; every (lane, chunk) runs the recurrence from a zero state, the
+// chunk-to-chunk carry is an affine map (a power of the 2x2 transition matrix) resolved by a short
+// scan, and a second sweep produces the output (forward) or the gradient sums (backward; by
+// linearity the sums are corrected for the carried adjoint state without re-reading the signals).
+#include "common.cuh"
+
+namespace {
+
+// ---------------------------------------------------------------------------------------------
+// one-pole  y[n] = x[n] + a*y[n-1]
+// ---------------------------------------------------------------------------------------------
+constexpr int OP_THREADS = 256, OP_PER = 8, OP_CHUNK = OP_THREADS * OP_PER;
+
+// inclusive scan over the block of v_t = sum_{s<=t} r^(t-s) * e_s   (r = a^OP_PER), via shuffles
+__device__ __forceinline__ float block_decay_scan(float e, const float *rpow /* r^(2^i), i<8 */, float *warp_tot,
+                                                  int tid) {
+  float v = e;
+#pragma unroll
+  for (int i = 0; i < 5; ++i) {
+    float o = __shfl_up_sync(0xffffffffu, v, 1 << i);
+    if ((tid & 31) >= (1 << i)) v = fmaf(rpow[i], o, v);
+  }
+  if ((tid & 31) == 31) warp_tot[tid >> 5] = v;
+  __syncthreads();
+  if (tid < 32) {
+    float w = tid < OP_THREADS / 32 ? warp_tot[tid] : 0.0f;
+    // scan over warps with multiplier r^32 = rpow[5], r^64, r^128
+#pragma unroll
+    for (int i = 0; i < 3; ++i) {
+      float o = __shfl_up_sync(0xffffffffu, w, 1 << i);
+      if (tid >= (1 << i)) w = fmaf(rpow[5 + i], o, w);
+    }
+    if (tid < OP_THREADS / 32) warp_tot[tid] = w;
+  }
+  __syncthreads();
+  if (tid >= 32) {
+    // add the carry of all previous warps, decayed by r^(lane+1)
+    float carry = warp_tot[(tid >> 5) - 1];
+    float d = rpow[8 + (tid & 31)];
+    v = fmaf(d, carry, v);
+  }
+  return v;
+}
+
+// phase 0: chunk end values with zero carry-in; phase 1: final output using carry[chunk]
+template <int PHASE>
+__global__ void __launch_bounds__(OP_THREADS)
+onepole_kernel(const float *__restrict__ x, int T, int NC, float a, const float *__restrict__ carry_in,
+               float *__restrict__ chunk_end, float *__restrict__ y) {
+  __shared__ float rpow[8 + 32];
+  __shared__ float warp_tot[OP_THREADS / 32];
+  const int tid = threadIdx.x, c = blockIdx.x, b = blockIdx.y;
+  if (tid == 0) {
+    float r = 1.0f;
+    for (int i = 0; i < OP_PER; ++i) r *= a;  // a^OP_PER
+    float p = r;
+    for (int i = 0; i < 8; ++i) { rpow[i] = p; p *= p; }
+    float q = r;
+    for (int i = 0; i < 32; ++i) { rpow[8 + i] = q; q *= r; }  // r^(i+1)
+  }
+  __syncthreads();
+  const float *xb = x + (size_t)b * T;
+  const int n0 = c * OP_CHUNK + tid * OP_PER;
+  float loc[OP_PER];
+  float prev = 0.0f;
+#pragma unroll
+  for (int j = 0; j < OP_PER; ++j) {
+    float xv = (n0 + j < T) ? xb[n0 + j] : 0.0f;
+    prev = fmaf(a, prev, xv);
+    loc[j] = prev;
+  }
+  float incl = block_decay_scan(prev, rpow, warp_tot, tid);  // state at the end of this thread's run
+  if (PHASE == 0) {
+    if (tid == OP_THREADS - 1) chunk_end[(size_t)b * NC + c] = incl;
+    return;
+  }
+  // state entering this thread's run = (incl - prev)/... simpler: exclusive value via shuffle
+  float excl = __shfl_up_sync(0xffffffffu, incl, 1);
+  __shared__ float last_of_warp[OP_THREADS / 32];
+  if ((tid & 31) == 31) last_of_warp[tid >> 5] = incl;
+  __syncthreads();
+  if ((tid & 31) == 0) excl = tid == 0 ? 0.0f : last_of_warp[(tid >> 5) - 1];
+  // carry from previous chunks decays by a^(tid*OP_PER) before reaching this thread
+  float cin = carry_in[(size_t)b * NC + c];
+  float dec = 1.0f;
+  {
+    // a^(tid*OP_PER) = r^tid from the binary powers
+    int e = tid;
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (e & (1 << i)) dec *= rpow[i];
+  }
+  float state = fmaf(dec, cin, excl);
+  float *yb = y + (size_t)b * T;
+  float ap = a;
+#pragma unroll
+  for (int j = 0; j < OP_PER; ++j) {
+    if (n0 + j < T) yb[n0 + j] = fmaf(ap, state, loc[j]);
+    ap *= a;
+  }
+}
+
+// carry[c] = state entering chunk c; serial over chunks (few), one thread per voice
+__global__ void onepole_carry_kernel(const float *__restrict__ chunk_end, int B, int NC, float a, float y0,
+                                     float *__restrict__ carry) {
+  int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= B) return;
+  float ac = 1.0f;
+  for (int i = 0; i < OP_CHUNK; ++i) ac *= a;
+  float s = y0;
+  for (int c = 0; c < NC; ++c) {
+    carry[(size_t)b * NC + c] = s;
+    s = fmaf(ac, s, chunk_end[(size_t)b * NC + c]);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// biquad bank
+// ---------------------------------------------------------------------------------------------
+constexpr int BQ_CHUNK = 512;     // frames per (lane, chunk) thread
+constexpr int BQ_THREADS = 128;   // lanes per block
+
+// value with derivatives w.r.t. cutoff and q
+struct Dual {
+  float v, dc, dq;
+};
+__device__ __forceinline__ Dual dmul(Dual a, Dual b) { return {a.v * b.v, a.dc * b.v + a.v * b.dc, a.dq * b.v + a.v * b.dq}; }
+__device__ __forceinline__ Dual dadd(Dual a, Dual b) { return {a.v + b.v, a.dc + b.dc, a.dq + b.dq}; }
+__device__ __forceinline__ Dual dsub(Dual a, Dual b) { return {a.v - b.v, a.dc - b.dc, a.dq - b.dq}; }
+__device__ __forceinline__ Dual ddiv(Dual a, Dual b) {
+  float q = a.v / b.v;
+  return {q, (a.dc - q * b.dc) / b.v, (a.dq - q * b.dq) / b.v};
+}
+__device__ __forceinline__ Dual dconst(float c) { return {c, 0.f, 0.f}; }
+__device__ __forceinline__ Dual dabs(Dual a) { return a.v < 0.f ? Dual{-a.v, -a.dc, -a.dq} : a; }
+
+__device__ __forceinline__ Dual dselect(float mode1, const Dual *opt, int n) {
+  if (mode1 <= 0.f) return dconst(0.f);
+  for (int i = 0; i < n; ++i)
+    if (mode1 <= (float)(i + 1)) return opt[i];
+  return dconst(0.f);
+}
+
+// Graph.biquad coefficient DAG (Sources/DGen/HigherOps.swift:444-555), modes 0..5, node by node.
+// coef layout per lane: b0 b1 b2 a1 a2, then d/dcutoff of the five, then d/dq of the five.
+__global__ void biquad_coef_kernel(const float *__restrict__ cutoff, const float *__restrict__ q, int L, float gain,
+                                   float mode, float *__restrict__ coef) {
+  int l = blockIdx.x * blockDim.x + threadIdx.x;
+  if (l >= L) return;
+  Dual cut = {cutoff[l], 1.f, 0.f}, res = {q[l], 0.f, 1.f};
+  float add4 = mode + 1.0f;
+  Dual mult7 = dmul(dabs(cut), dconst(0.00014247585730565955f));
+  Dual cos8 = {cosf(mult7.v), -sinf(mult7.v) * mult7.dc, -sinf(mult7.v) * mult7.dq};
+  Dual mult9 = dmul(cos8, dconst(-1.f));
+  Dual add10 = dadd(mult9, dconst(1.f));
+  Dual div11 = ddiv(add10, dconst(2.f));
+  Dual sub12 = dsub(mult9, dconst(1.f));
+  Dual div13 = ddiv(sub12, dconst(-2.f));
+  Dual sin14 = {sinf(mult7.v), cosf(mult7.v) * mult7.dc, cosf(mult7.v) * mult7.dq};
+  Dual mult15 = dmul(sin14, dconst(0.5f));
+  Dual abs17 = dabs(res);
+  Dual div18 = ddiv(mult15, abs17);
+  Dual mult19 = dmul(div18, dconst(-1.f));
+  Dual mult20 = dmul(div18, abs17);
+  Dual mult21 = dmul(mult20, dconst(-1.f));
+  Dual add22 = dadd(div18, dconst(1.f));
+  Dual recip24 = ddiv(dconst(1.f), add22);
+  Dual mult26 = dmul(recip24, dconst(gain));
+  Dual mult31 = dmul(mult9, dconst(2.f));
+  Dual not_sub35 = dsub(dconst(1.f), div18);
+  Dual o23[6] = {div11, div13, mult19, mult21, dconst(1.f), add22};
+  Dual o32[6] = {add10, sub12, dconst(0.f), dconst(0.f), mult31, mult31};
+  Dual o36[6] = {div11, div13, div18, mult20, dconst(1.f), not_sub35};
+  Dual b2 = dmul(dselect(add4, o23, 6), mult26);
+  Dual b1 = dmul(dselect(add4, o32, 6), mult26);
+  Dual b0 = dmul(dselect(add4, o36, 6), mult26);
+  Dual a2 = dmul(not_sub35, recip24);
+  Dual a1 = dmul(mult31, recip24);
+  float *c = coef + (size_t)l * 15;
+  c[0] = b0.v; c[1] = b1.v; c[2] = b2.v; c[3] = a1.v; c[4] = a2.v;
+  c[5] = b0.dc; c[6] = b1.dc; c[7] = b2.dc; c[8] = a1.dc; c[9] = a2.dc;
+  c[10] = b0.dq; c[11] = b1.dq; c[12] = b2.dq; c[13] = a1.dq; c[14] = a2.dq;
+}
+
+struct Coef {
+  float b0, b1, b2, a1, a2;
+};
+__device__ __forceinline__ Coef load_coef(const float *coef, int l) {
+  const float *c = coef + (size_t)l * 15;
+  return {c[0], c[1], c[2], c[3], c[4]};
+}
+
+// y = ((b2*x2 + b1*x1) + b0*x0) - (a2*y2 + a1*y1), each operation rounded as in the reference graph
+__device__ __forceinline__ float biquad_step(const Coef &c, float x0, float x1, float x2, float y1, float y2) {
+  float add39 = __fadd_rn(__fadd_rn(__fmul_rn(x2, c.b2), __fmul_rn(x1, c.b1)), __fmul_rn(x0, c.b0));
+  float add45 = __fadd_rn(__fmul_rn(y2, c.a2), __fmul_rn(y1, c.a1));
+  return __fsub_rn(add39, add45);
+}
+
+// Per lane: the homogeneous transition over one chunk, M = [[m11 m12],[m21 m22]] with
+// (y1,y2)_end = M (y1,y2)_start for zero input.  Poles close to the unit circle make the entries of
+// M large with cancelling signs, so M and the chunk-to-chunk carry are kept in double precision.
+__global__ void biquad_trans_kernel(const float *__restrict__ coef, int L, int len, double *__restrict__ trans) {
+  int l = blockIdx.x * blockDim.x + threadIdx.x;
+  if (l >= L) return;
+  Coef c = load_coef(coef, l);
+  const double a1 = c.a1, a2 = c.a2;
+  double m[4];
+  for (int col = 0; col < 2; ++col) {
+    double y1 = col == 0 ? 1.0 : 0.0, y2 = col == 0 ? 0.0 : 1.0;
+    for (int n = 0; n < len; ++n) {
+      double v = -(a2 * y2 + a1 * y1);
+      y2 = y1;
+      y1 = v;
+    }
+    m[col] = y1;      // m11, m12
+    m[2 + col] = y2;  // m21, m22
+  }
+  for (int i = 0; i < 4; ++i) trans[(size_t)l * 4 + i] = m[i];
+}
+
+// Forward sweep.  PHASE 0: end state of every (voice, lane, chunk) from a zero y-state.
+//                 PHASE 1: rerun from the carried state and write y[b][n][l] (lanes fastest).
+template <int PHASE>
+__global__ void __launch_bounds__(BQ_THREADS)
+biquad_fwd_kernel(const float *__restrict__ x, const float *__restrict__ coef, int B, int T, int L, int NC,
+                  float *__restrict__ state /* [B][NC][L][2] */, float *__restrict__ y) {
+  const int l = blockIdx.x * BQ_THREADS + threadIdx.x, c = blockIdx.y, b = blockIdx.z;
+  __shared__ float xs[BQ_CHUNK + 2];
+  const float *xb = x + (size_t)b * T;
+  const int n0 = c * BQ_CHUNK, len = min(BQ_CHUNK, T - n0);
+  for (int i = threadIdx.x; i < len + 2; i += BQ_THREADS) {
+    int t = n0 - 2 + i;
+    xs[i] = t >= 0 ? xb[t] : 0.0f;
+  }
+  __syncthreads();
+  if (l >= L) return;
+  const Coef cf = load_coef(coef, l);
+  float *st = state + (((size_t)b * NC + c) * L + l) * 2;
+  float y1 = 0.f, y2 = 0.f;
+  if (PHASE == 1) {
+    y1 = st[0];
+    y2 = st[1];
+  }
+  float x2 = xs[0], x1 = xs[1];
+  float *yo = y + ((size_t)b * T + n0) * L + l;
+#pragma unroll 4
+  for (int n = 0; n < len; ++n) {
+    float x0 = xs[n + 2];
+    float v = biquad_step(cf, x0, x1, x2, y1, y2);
+    if (PHASE == 1) yo[(size_t)n * L] = v;
+    x2 = x1; x1 = x0; y2 = y1; y1 = v;
+  }
+  if (PHASE == 0) {
+    st[0] = y1;
+    st[1] = y2;
+  }
+}
+
+// state[c] <- state entering chunk c (exclusive scan of the affine maps), thread per (voice, lane)
+__global__ void biquad_carry_kernel(const double *__restrict__ trans, int B, int L, int NC,
+                                    float *__restrict__ state) {
+  int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= B * L) return;
+  int b = idx / L, l = idx - b * L;
+  const double m11 = trans[(size_t)l * 4], m12 = trans[(size_t)l * 4 + 1], m21 = trans[(size_t)l * 4 + 2],
+               m22 = trans[(size_t)l * 4 + 3];
+  double s1 = 0.0, s2 = 0.0;
+  for (int c = 0; c < NC; ++c) {
+    float *st = state + (((size_t)b * NC + c) * L + l) * 2;
+    double e1 = st[0], e2 = st[1];
+    st[0] = (float)s1;
+    st[1] = (float)s2;
+    // every chunk but possibly the last has full length; the state after the last chunk is unused
+    double n1 = m11 * s1 + m12 * s2 + e1, n2 = m21 * s1 + m22 * s2 + e2;
+    s1 = n1;
+    s2 = n2;
+  }
+}
+
+// Backward sweep for loss = scale * sum (y - t)^2.  Adjoint recurrence (transposed filter, reverse time):
+//   lam[n] = g[n] - a1*lam[n+1] - a2*lam[n+2],  g = 2*scale*(y - t)
+//   dL/db0 = sum lam[n] x[n], dL/db1 = sum lam[n] x[n-1], dL/db2 = sum lam[n] x[n-2],
+//   dL/da1 = -sum lam[n] y[n-1], dL/da2 = -sum lam[n] y[n-2].
+// One sweep per (voice, lane, chunk) from a zero terminal adjoint accumulates the five sums for the
+// local adjoint AND for the two homogeneous adjoint responses h1, h2 (terminal state (1,0) and (0,1));
+// the carry kernel then supplies the true terminal state s of each chunk and the total is
+// S_loc + s1*S_h1 + s2*S_h2.  Record per (voice, chunk, lane): 15 sums + local start adjoint (2) + sq error.
+constexpr int BW_REC = 18;
+
+__global__ void __launch_bounds__(BQ_THREADS)
+biquad_bwd_kernel(const float *__restrict__ x, const float *__restrict__ coef, const float *__restrict__ y,
+                  const float *__restrict__ tgt, int B, int T, int L, int NC, float gscale,
+                  float *__restrict__ rec /* [B][NC][BW_REC][L] */) {
+  const int l = blockIdx.x * BQ_THREADS + threadIdx.x, c = blockIdx.y, b = blockIdx.z;
+  __shared__ float xs[BQ_CHUNK + 2];
+  const float *xb = x + (size_t)b * T;
+  const int n0 = c * BQ_CHUNK, len = min(BQ_CHUNK, T - n0);
+  for (int i = threadIdx.x; i < len + 2; i += BQ_THREADS) {
+    int t = n0 - 2 + i;
+    xs[i] = t >= 0 ? xb[t] : 0.0f;
+  }
+  __syncthreads();
+  if (l >= L) return;
+  const Coef cf = load_coef(coef, l);
+  const float *yb = y + (size_t)b * T * L + l, *tb = tgt + (size_t)b * T * L + l;
+  float la1 = 0.f, la2 = 0.f;            // lam[n+1], lam[n+2] (local)
+  float h1a = 1.f, h1b = 0.f;            // homogeneous response to terminal (lam[n_end+1], lam[n_end+2]) = (1,0)
+  float h2a = 0.f, h2b = 1.f;            // ... = (0,1)
+  float S[15];
+#pragma unroll
+  for (int i = 0; i < 15; ++i) S[i] = 0.f;
+  float sq = 0.f;
+  // y[n-1], y[n-2] sliding from the top: prefetch y at n, n-1, n-2
+  int nt = n0 + len - 1;
+  float yc = yb[(size_t)nt * L];
+  float ym1 = nt - 1 >= 0 ? yb[(size_t)(nt - 1) * L] : 0.f;
+  for (int n = len - 1; n >= 0; --n) {
+    int t = n0 + n;
+    float ym2 = t - 2 >= 0 ? yb[(size_t)(t - 2) * L] : 0.f;
+    float d = yc - tb[(size_t)t * L];
+    sq = fmaf(d, d, sq);
+    float g = gscale * d;
+    float lam = g - (cf.a1 * la1 + cf.a2 * la2);
+    float h1 = -(cf.a1 * h1a + cf.a2 * h1b);
+    float h2 = -(cf.a1 * h2a + cf.a2 * h2b);
+    float x0 = xs[n + 2], x1 = xs[n + 1], x2 = xs[n];
+    S[0] = fmaf(lam, x0, S[0]); S[1] = fmaf(lam, x1, S[1]); S[2] = fmaf(lam, x2, S[2]);
+    S[3] = fmaf(lam, ym1, S[3]); S[4] = fmaf(lam, ym2, S[4]);
+    S[5] = fmaf(h1, x0, S[5]); S[6] = fmaf(h1, x1, S[6]); S[7] = fmaf(h1, x2, S[7]);
+    S[8] = fmaf(h1, ym1, S[8]); S[9] = fmaf(h1, ym2, S[9]);
+    S[10] = fmaf(h2, x0, S[10]); S[11] = fmaf(h2, x1, S[11]); S[12] = fmaf(h2, x2, S[12]);
+    S[13] = fmaf(h2, ym1, S[13]); S[14] = fmaf(h2, ym2, S[14]);
+    la2 = la1; la1 = lam;
+    h1b = h1a; h1a = h1;
+    h2b = h2a; h2a = h2;
+    yc = ym1; ym1 = ym2;
+  }
+  float *r = rec + ((size_t)b * NC + c) * BW_REC * L + l;
+#pragma unroll
+  for (int i = 0; i < 15; ++i) r[(size_t)i * L] = S[i];
+  r[(size_t)15 * L] = la1;  // local adjoint at the first frame of the chunk: lam[n0]
+  r[(size_t)16 * L] = la2;  // lam[n0+1]
+  r[(size_t)17 * L] = sq;
+}
+
+// Reverse carry over chunks, thread per (voice, lane): resolves the terminal adjoint of every chunk,
+// combines the sums, and writes per (voice, lane) the five coefficient-gradient sums and the squared error.
+__global__ void biquad_bwd_carry_kernel(const float *__restrict__ rec, const float *__restrict__ coef, int B, int L,
+                                        int NC, int T, double *__restrict__ acc /* [B][L][6] */) {
+  int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= B * L) return;
+  int b = idx / L, l = idx - b * L;
+  const Coef cf = load_coef(coef, l);
+  // adjoint transition over a full chunk: (lam[n0], lam[n0+1]) = A (s1, s2) + local, with A from the
+  // homogeneous responses; recompute A by running the recurrence (cheap, per thread)
+  const double da1 = cf.a1, da2 = cf.a2;
+  auto homog = [&](int len, double &a11, double &a12, double &a21, double &a22) {
+    double p1 = 1.0, p2 = 0.0, q1 = 0.0, q2 = 1.0;
+    for (int n = 0; n < len; ++n) {
+      double v = -(da1 * p1 + da2 * p2);
+      p2 = p1; p1 = v;
+      double w = -(da1 * q1 + da2 * q2);
+      q2 = q1; q1 = w;
+    }
+    a11 = p1; a21 = p2; a12 = q1; a22 = q2;
+  };
+  double f11, f12, f21, f22;
+  homog(BQ_CHUNK, f11, f12, f21, f22);
+  double G[5] = {0, 0, 0, 0, 0}, sq = 0;
+  double s1 = 0.0, s2 = 0.0;  // terminal adjoint (lam[n_end+1], lam[n_end+2]) of the current chunk
+  for (int c = NC - 1; c >= 0; --c) {
+    const float *r = rec + ((size_t)b * NC + c) * BW_REC * L + l;
+    for (int i = 0; i < 5; ++i)
+      G[i] += (double)r[(size_t)i * L] + s1 * (double)r[(size_t)(5 + i) * L] + s2 * (double)r[(size_t)(10 + i) * L];
+    sq += (double)r[(size_t)17 * L];
+    int len = min(BQ_CHUNK, T - c * BQ_CHUNK);
+    double a11 = f11, a12 = f12, a21 = f21, a22 = f22;
+    if (len != BQ_CHUNK) homog(len, a11, a12, a21, a22);
+    double n1 = a11 * s1 + a12 * s2 + (double)r[(size_t)15 * L];
+    double n2 = a21 * s1 + a22 * s2 + (double)r[(size_t)16 * L];
+    s1 = n1;
+    s2 = n2;
+  }
+  double *o = acc + ((size_t)b * L + l) * 6;
+  o[0] = G[0]; o[1] = G[1]; o[2] = G[2]; o[3] = -G[3]; o[4] = -G[4]; o[5] = sq;
+}
+
+// Sum over voices (fixed order), chain rule to cutoff and q, total loss.
+__global__ void biquad_bwd_final_kernel(const double *__restrict__ acc, const float *__restrict__ coef, int B, int L,
+                                        float loss_scale, float *__restrict__ gcut, float *__restrict__ gq,
+                                        double *__restrict__ lane_loss) {
+  int l = blockIdx.x * blockDim.x + threadIdx.x;
+  if (l >= L) return;
+  double G[5] = {0, 0, 0, 0, 0}, sq = 0;
+  for (int b = 0; b < B; ++b) {
+    const double *a = acc + ((size_t)b * L + l) * 6;
+    for (int i = 0; i < 5; ++i) G[i] += a[i];
+    sq += a[5];
+  }
+  const float *c = coef + (size_t)l * 15;
+  double dc = 0, dq = 0;
+  for (int i = 0; i < 5; ++i) {
+    dc += G[i] * (double)c[5 + i];
+    dq += G[i] * (double)c[10 + i];
+  }
+  gcut[l] = (float)dc;
+  gq[l] = (float)dq;
+  lane_loss[l] = sq * (double)loss_scale;
+}
+
+__global__ void sum_doubles_kernel(const double *__restrict__ v, int n, double *__restrict__ out) {
+  if (blockIdx.x != 0 || threadIdx.x != 0) return;
+  double t = 0;
+  for (int i = 0; i < n; ++i) t += v[i];
+  out[0] = t;
+}
+
+}  // namespace
+
+DGC_EXPORT int32_t dgc_onepole_fwd(dgc_ctx *ctx, const float *x_dev, int32_t B, int32_t T, float a, float *y_dev) {
+  if (!ctx) return DGC_ERR_INVALID;
+  DGC_REQUIRE(ctx, x_dev && y_dev, "null pointer");
+  DGC_REQUIRE(ctx, B > 0 && T > 0, "size out of range");
+  const int NC = dgc_div_up(T, OP_CHUNK);
+  float *scr = dgc_ctx_scratch(ctx, 2ull * B * NC + 8);
+  if (!scr) return DGC_ERR_OOM;
+  float *chunk_end = scr, *carry = scr + (size_t)B * NC;
+  onepole_kernel<0><<<dim3(NC, B), OP_THREADS, 0, ctx->stream>>>(x_dev, T, NC, a, nullptr, chunk_end, nullptr);
+  DGC_LAUNCHED(ctx, "onepole_pass0");
+  onepole_carry_kernel<<<dgc_div_up(B, 64), 64, 0, ctx->stream>>>(chunk_end, B, NC, a, 0.0f, carry);
+  DGC_LAUNCHED(ctx, "onepole_carry");
+  onepole_kernel<1><<<dim3(NC, B), OP_THREADS, 0, ctx->stream>>>(x_dev, T, NC, a, carry, nullptr, y_dev);
+  DGC_LAUNCHED(ctx, "onepole_pass1");
+  return DGC_OK;
+}
+
+static int32_t biquad_validate(dgc_ctx *ctx, const dgc_biquad_params *p) {
+  DGC_REQUIRE(ctx, p->B > 0 && p->T > 0 && p->L > 0, "size out of range");
+  DGC_REQUIRE(ctx, p->B <= 65535, "B must be <= 65535");
+  DGC_REQUIRE(ctx, p->mode >= 0.0f && p->mode <= 5.0f, "mode must be in 0..5");
+  return DGC_OK;
+}
+
+DGC_EXPORT uint64_t dgc_biquad_scratch_floats(const dgc_biquad_params *p, int32_t backward) {
+  if (!p || p->B <= 0 || p->T <= 0 || p->L <= 0) return 0;
+  uint64_t NC = (uint64_t)(p->T + BQ_CHUNK - 1) / BQ_CHUNK;
+  uint64_t coef = (((uint64_t)p->L * 16 + (uint64_t)p->L * 8) + 3) & ~3ull;
+  if (!backward) return coef + (uint64_t)p->B * NC * p->L * 2 + 8;
+  uint64_t rec = (uint64_t)p->B * NC * BW_REC * p->L;
+  return coef + ((rec + 3) & ~3ull) + 2 * ((uint64_t)p->B * p->L * 6 + p->L) + 16;
+}
+
+DGC_EXPORT int32_t dgc_biquad_fwd(dgc_ctx *ctx, const dgc_biquad_params *p, const float *x_dev,
+                                  const float *cutoff_dev, const float *q_dev, float *scratch_dev, float *y_dev) {
+  if (!ctx) return DGC_ERR_INVALID;
+  DGC_REQUIRE(ctx, p && x_dev && cutoff_dev && q_dev && y_dev, "null pointer");
+  int32_t rc = biquad_validate(ctx, p);
+  if (rc != DGC_OK) return rc;
+  const int B = p->B, T = p->T, L = p->L, NC = dgc_div_up(T, BQ_CHUNK);
+  DGC_REQUIRE(ctx, NC <= 65535, "T too large");
+  float *scr = scratch_dev ? scratch_dev : dgc_ctx_scratch(ctx, dgc_biquad_scratch_floats(p, 0));
+  if (!scr) return DGC_ERR_OOM;
+  DGC_REQUIRE(ctx, (((uintptr_t)scr) & 15) == 0, "scratch must be 16-byte aligned");
+  float *coef = scr;
+  double *trans = reinterpret_cast<double *>(scr + (size_t)L * 16);
+  float *state = scr + ((((size_t)L * 24) + 3) & ~(size_t)3);
+  biquad_coef_kernel<<<dgc_div_up(L, 128), 128, 0, ctx->stream>>>(cutoff_dev, q_dev, L, p->gain, p->mode, coef);
+  DGC_LAUNCHED(ctx, "biquad_coef");
+  biquad_trans_kernel<<<dgc_div_up(L, 128), 128, 0, ctx->stream>>>(coef, L, BQ_CHUNK, trans);
+  DGC_LAUNCHED(ctx, "biquad_trans");
+  dim3 grid(dgc_div_up(L, BQ_THREADS), NC, B);
+  biquad_fwd_kernel<0><<<grid, BQ_THREADS, 0, ctx->stream>>>(x_dev, coef, B, T, L, NC, state, nullptr);
+  DGC_LAUNCHED(ctx, "biquad_fwd_state");
+  biquad_carry_kernel<<<dgc_div_up(B * L, 128), 128, 0, ctx->stream>>>(trans, B, L, NC, state);
+  DGC_LAUNCHED(ctx, "biquad_carry");
+  biquad_fwd_kernel<1><<<grid, BQ_THREADS, 0, ctx->stream>>>(x_dev, coef, B, T, L, NC, state, y_dev);
+  DGC_LAUNCHED(ctx, "biquad_fwd_out");
+  return DGC_OK;
+}
+
+DGC_EXPORT int32_t dgc_biquad_mse_bwd(dgc_ctx *ctx, const dgc_biquad_params *p, const float *x_dev,
+                                      const float *cutoff_dev, const float *q_dev, const float *y_dev,
+                                      const float *target_dev, float loss_scale, float *scratch_dev,
+                                      float *grad_cutoff_dev, float *grad_q_dev, double *loss_dev) {
+  if (!ctx) return DGC_ERR_INVALID;
+  DGC_REQUIRE(ctx, p && x_dev && cutoff_dev && q_dev && y_dev && target_dev && grad_cutoff_dev && grad_q_dev &&
+                       loss_dev, "null pointer");
+  int32_t rc = biquad_validate(ctx, p);
+  if (rc != DGC_OK) return rc;
+  const int B = p->B, T = p->T, L = p->L, NC = dgc_div_up(T, BQ_CHUNK);
+  DGC_REQUIRE(ctx, NC <= 65535, "T too large");
+  float *scr = scratch_dev ? scratch_dev : dgc_ctx_scratch(ctx, dgc_biquad_scratch_floats(p, 1));
+  if (!scr) return DGC_ERR_OOM;
+  DGC_REQUIRE(ctx, (((uintptr_t)scr) & 15) == 0, "scratch must be 16-byte aligned");
+  float *coef = scr;
+  float *rec = scr + ((((size_t)L * 24) + 3) & ~(size_t)3);
+  size_t rec_n = ((size_t)B * NC * BW_REC * L + 3) & ~(size_t)3;
+  double *acc = reinterpret_cast<double *>(rec + rec_n);
+  double *lane_loss = acc + (size_t)B * L * 6;
+  biquad_coef_kernel<<<dgc_div_up(L, 128), 128, 0, ctx->stream>>>(cutoff_dev, q_dev, L, p->gain, p->mode, coef);
+  DGC_LAUNCHED(ctx, "biquad_coef");
+  dim3 grid(dgc_div_up(L, BQ_THREADS), NC, B);
+  biquad_bwd_kernel<<<grid, BQ_THREADS, 0, ctx->stream>>>(x_dev, coef, y_dev, target_dev, B, T, L, NC,
+                                                          2.0f * loss_scale, rec);
+  DGC_LAUNCHED(ctx, "biquad_bwd");
+  biquad_bwd_carry_kernel<<<dgc_div_up(B * L, 128), 128, 0, ctx->stream>>>(rec, coef, B, L, NC, T, acc);
+  DGC_LAUNCHED(ctx, "biquad_bwd_carry");
+  biquad_bwd_final_kernel<<<dgc_div_up(L, 128), 128, 0, ctx->stream>>>(acc, coef, B, L, loss_scale, grad_cutoff_dev,
+                                                                        grad_q_dev, lane_loss);
+  DGC_LAUNCHED(ctx, "biquad_bwd_final");
+  sum_doubles_kernel<<<1, 32, 0, ctx->stream>>>(lane_loss, L, loss_dev);
+  DGC_LAUNCHED(ctx, "biquad_loss_sum");
+  return DGC_OK;
+}

@@ -97,21 +97,29 @@ mss_fwd_kernel(const float *__restrict__ pred, const float *__restrict__ target,
   }
 }
 
-// total = sum_s (w_lin * sum(lin_s) + w_log * sum(log_s)) / B / nscales / T ; one block, fixed order
+// total = sum_s (w_lin * sum(lin_s) + w_log * sum(log_s)) / B / nscales / T
 struct ReduceDesc {
   int nscales;
   long long off[DGC_MSS_MAX_SCALES];  // offset of the lin block of scale s; log block follows
   long long cnt[DGC_MSS_MAX_SCALES];  // H_s * B
 };
 
-__global__ void mss_reduce_kernel(const float *__restrict__ part, ReduceDesc d, double scale_lin, double scale_log,
-                                  double *__restrict__ out) {
-  __shared__ double sh[1024];
+constexpr int RED_BLOCKS = 64, RED_THREADS = 256;
+
+// Stage 1: every block sums a strided share of all partials (weighted) in double, in a fixed
+// order; the last block to finish (ticket counter) adds the RED_BLOCKS block sums in index order.
+// The result therefore does not depend on scheduling.
+__global__ void __launch_bounds__(RED_THREADS)
+mss_reduce_kernel(const float *__restrict__ part, ReduceDesc d, double scale_lin, double scale_log,
+                  double *__restrict__ block_sums, unsigned int *__restrict__ ticket, double *__restrict__ out) {
+  __shared__ double sh[RED_THREADS];
+  __shared__ bool last;
   double acc = 0.0;
+  const long long stride = (long long)RED_BLOCKS * RED_THREADS;
   for (int s = 0; s < d.nscales; ++s) {
     const float *lin = part + d.off[s], *lg = lin + d.cnt[s];
     double a = 0.0, c = 0.0;
-    for (long long i = threadIdx.x; i < d.cnt[s]; i += blockDim.x) {
+    for (long long i = (long long)blockIdx.x * RED_THREADS + threadIdx.x; i < d.cnt[s]; i += stride) {
       a += (double)lin[i];
       c += (double)lg[i];
     }
@@ -119,11 +127,23 @@ __global__ void mss_reduce_kernel(const float *__restrict__ part, ReduceDesc d, 
   }
   sh[threadIdx.x] = acc;
   __syncthreads();
-  for (int off = blockDim.x / 2; off > 0; off >>= 1) {
+  for (int off = RED_THREADS / 2; off > 0; off >>= 1) {
     if (threadIdx.x < off) sh[threadIdx.x] += sh[threadIdx.x + off];
     __syncthreads();
   }
-  if (threadIdx.x == 0) out[0] = sh[0];
+  if (threadIdx.x == 0) {
+    block_sums[blockIdx.x] = sh[0];
+    __threadfence();
+    last = atomicAdd(ticket, 1u) == RED_BLOCKS - 1;
+  }
+  __syncthreads();
+  if (last && threadIdx.x == 0) {
+    __threadfence();
+    double t = 0.0;
+    for (int i = 0; i < RED_BLOCKS; ++i) t += reinterpret_cast<volatile double *>(block_sums)[i];
+    out[0] = t;
+    *ticket = 0u;
+  }
 }
 
 template <int N>
@@ -137,6 +157,159 @@ int32_t launch_fwd(dgc_ctx *ctx, const dgc_mss_params *p, const float *pred, con
                                                                                     win, tw, lin, lg);
   ctx->launches++;
   return dgc_check_launch(ctx, "mss_fwd");
+}
+
+// ---------------------------------------------------------------------------------------------
+// Backward.  Reference: three kernels per term with device scratch for the spectra, the spectral
+// gradient and the time gradient (Sources/DGen/Emit+SpectralLoss.swift:940-1325):
+//   gradMag1 = sign(d) (* 1/(m1+eps) for the log term) * upstream / B ; gradX1 = gradMag1 * X1 / max(m1, 1e-8)
+//   for bins 0..N/2, zero above; time gradient = Re(sum_k gradX1[k] e^{+2 pi i k n / N}) * hann[n];
+//   d loss / d x[p] = sum of the time gradients of the hop windows that cover p.
+// Here nothing is stored: a block owns a run of output frames, recomputes the spectra of every window
+// that covers them (prediction and target in one transform), builds the Hermitian-symmetrised
+// spectral gradient of two windows in the real / imaginary lane of one inverse transform, and sums
+// the covering windows into a shared-memory tile in a fixed order (rounds ascending, windows
+// ascending), so the result is bit-reproducible and needs no atomics.
+// ---------------------------------------------------------------------------------------------
+template <int N>
+struct BwdGeom {
+  static constexpr int G = N / 8;
+  static constexpr int NF = LOSS_THREADS / G;                      // window pairs per round
+  static constexpr int WR = 2 * NF;                                // windows per round
+  static constexpr int ROUNDS = WR >= 16 ? 1 : 16 / WR;            // at least 16 windows per block
+  static constexpr int WB = WR * ROUNDS;                           // windows per block
+};
+
+__device__ __forceinline__ float sgn(float v) { return v > 0.f ? 1.f : (v < 0.f ? -1.f : 0.f); }
+
+template <int N>
+__global__ void __launch_bounds__(LOSS_THREADS)
+mss_bwd_kernel(const float *__restrict__ pred, const float *__restrict__ target, int B, int T, int hop, int H,
+               int S /* windows whose first-covered frames this block owns */, const float *__restrict__ window,
+               const float2 *__restrict__ tw, float c_lin, float c_log, int accumulate, float *__restrict__ grad) {
+  using Gm = BwdGeom<N>;
+  constexpr int G = Gm::G, NF = Gm::NF, WR = Gm::WR;
+  extern __shared__ float2 sm2[];
+  float2 *bufa = sm2, *bufb = sm2 + NF * N, *bufg = sm2 + 2 * NF * N;
+  float *tile = reinterpret_cast<float *>(sm2 + 3 * NF * N);
+  const int tid = threadIdx.x, f = tid / G, lt = tid % G;
+  const int b = blockIdx.y;
+  const int hA = blockIdx.x * S;
+  const int p0 = (hA - 1) * hop + 1;          // first owned frame (may be negative for the first block)
+  const int owned = S * hop;
+  const float *x1 = pred + (size_t)b * T, *x2 = target + (size_t)b * T;
+  float2 *a = bufa + f * N, *bb = bufb + f * N, *gi = bufg + f * N;
+  for (int o = tid; o < owned; o += LOSS_THREADS) tile[o] = 0.0f;
+  const int E = (N - 1) / hop;
+  const int nwin = min(S + E, H - hA);        // windows this block must visit
+  for (int r0 = 0; r0 < nwin; r0 += WR) {
+    const int hr0 = hA + r0;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) gi[lt + q * G] = make_float2(0.f, 0.f);
+    for (int w = 0; w < 2; ++w) {
+      const int h = hr0 + 2 * f + w;
+      const bool valid = h < H && (h - hA) < nwin;
+      const int t_base = h * hop - (N - 1);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        int i = lt + q * G, t = t_base + i;
+        float2 v = make_float2(0.f, 0.f);
+        if (valid && t >= 0 && t < T) {
+          float wv = __ldg(&window[i]);
+          v = make_float2(x1[t] * wv, x2[t] * wv);
+        }
+        a[i] = v;
+      }
+      __syncthreads();
+      float2 *z = fft_block<N, false>(a, bb, lt, tw);
+      if (valid) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          int k = lt + q * G;
+          float2 X1, X2;
+          unpack(z[k], z[(N - k) & (N - 1)], X1, X2);
+          float m1 = sqrtf(X1.x * X1.x + X1.y * X1.y), m2 = sqrtf(X2.x * X2.x + X2.y * X2.y);
+          float ld = __logf(m1 + LOG_EPS) - __logf(m2 + LOG_EPS);
+          float gm = c_lin * sgn(m1 - m2) + c_log * sgn(ld) / (m1 + LOG_EPS);
+          float sc = gm / fmaxf(m1, 1e-8f);
+          float2 gk = make_float2(sc * X1.x, sc * X1.y);
+          if (k == 0) {
+            // a real bin: only Re contributes to the real part of the synthesis
+            if (w == 0) gi[0].x += gk.x; else gi[0].y += gk.x;
+          } else {
+            float2 hk = make_float2(0.5f * gk.x, 0.5f * gk.y);
+            if (w == 0) {
+              gi[k].x += hk.x; gi[k].y += hk.y;
+              gi[N - k].x += hk.x; gi[N - k].y -= hk.y;
+            } else {  // times i: (x, y) -> (-y, x)
+              gi[k].x -= hk.y; gi[k].y += hk.x;
+              gi[N - k].x += hk.y; gi[N - k].y += hk.x;
+            }
+          }
+        }
+        if (lt == 0) {
+          float2 zn = z[N / 2];
+          float m1 = fabsf(zn.x), m2 = fabsf(zn.y);
+          float ld = __logf(m1 + LOG_EPS) - __logf(m2 + LOG_EPS);
+          float gm = c_lin * sgn(m1 - m2) + c_log * sgn(ld) / (m1 + LOG_EPS);
+          float gre = gm / fmaxf(m1, 1e-8f) * zn.x;
+          if (w == 0) gi[N / 2].x += gre; else gi[N / 2].y += gre;
+        }
+      }
+      __syncthreads();
+    }
+    float2 *zt = fft_block<N, true>(gi, a, lt, tw);
+    const bool in_g = (zt == gi);  // uniform: depends on the stage count of N only
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      int i = lt + q * G;
+      float wv = __ldg(&window[i]);
+      zt[i] = make_float2(zt[i].x * wv, zt[i].y * wv);
+    }
+    __syncthreads();
+    const float2 *res = in_g ? bufg : bufa;
+    for (int o = tid; o < owned; o += LOSS_THREADS) {
+      int p = p0 + o;
+      if (p < 0 || p >= T) continue;
+      int hlo = max(hr0, (p + hop - 1) / hop);
+      int hhi = min(min(hr0 + WR - 1, (p + N - 1) / hop), min(H - 1, hA + nwin - 1));
+      float acc = tile[o];
+      for (int h = hlo; h <= hhi; ++h) {
+        int slot = h - hr0;
+        float2 v = res[(slot >> 1) * N + (p - (h * hop - (N - 1)))];
+        acc += (slot & 1) ? v.y : v.x;
+      }
+      tile[o] = acc;
+    }
+    __syncthreads();
+  }
+  float *g = grad + (size_t)b * T;
+  for (int o = tid; o < owned; o += LOSS_THREADS) {
+    int p = p0 + o;
+    if (p >= 0 && p < T) g[p] = accumulate ? g[p] + tile[o] : tile[o];
+  }
+}
+
+template <int N>
+int32_t launch_bwd(dgc_ctx *ctx, const dgc_mss_params *p, const float *pred, const float *target, int hop, int H,
+                   float c_lin, float c_log, int accumulate, float *grad) {
+  using Gm = BwdGeom<N>;
+  const float *win = dgc_ctx_hann_sym(ctx, N);
+  const float2 *tw = dgc_ctx_twiddles(ctx, N);
+  if (!win || !tw) return DGC_ERR_OOM;
+  const int E = (N - 1) / hop;
+  int S = Gm::WB - E;
+  if (S < 1) return dgc_fail(ctx, DGC_ERR_UNSUPPORTED, "hop %d too small for window %d", hop, N);
+  size_t smem = (size_t)3 * Gm::NF * N * sizeof(float2) + (size_t)S * hop * sizeof(float);
+  if (smem > 200 * 1024) return dgc_fail(ctx, DGC_ERR_UNSUPPORTED, "backward tile does not fit shared memory");
+  cudaError_t e = cudaFuncSetAttribute(mss_bwd_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return dgc_fail(ctx, DGC_ERR_CUDA, "mss_bwd smem opt-in: %s", cudaGetErrorString(e));
+  // block j owns the frames whose first covering window is in [j*S, (j+1)*S); frames up to T-1 have
+  // first covering window <= H-1
+  mss_bwd_kernel<N><<<dim3(dgc_div_up(H, S), p->B), LOSS_THREADS, smem, ctx->stream>>>(
+      pred, target, p->B, p->T, hop, H, S, win, tw, c_lin, c_log, accumulate, grad);
+  ctx->launches++;
+  return dgc_check_launch(ctx, "mss_bwd");
 }
 
 int32_t validate(dgc_ctx *ctx, const dgc_mss_params *p) {
@@ -205,7 +378,41 @@ DGC_EXPORT int32_t dgc_mss_loss_fwd(dgc_ctx *ctx, const dgc_mss_params *p, const
   // (Examples/HarmonicE2E/Trainer.swift:553-586, Sources/DGenLazy/Functions.swift:951-954);
   // the batched loss is the mean over voices (Emit+SpectralLoss.swift:937-938)
   const double den = (double)p->B * (double)(used > 0 ? used : 1) * (double)p->T;
-  mss_reduce_kernel<<<1, 1024, 0, ctx->stream>>>(part, d, (double)p->w_lin / den, (double)p->w_log / den, loss_dev);
+  mss_reduce_kernel<<<RED_BLOCKS, RED_THREADS, 0, ctx->stream>>>(part, d, (double)p->w_lin / den, (double)p->w_log / den,
+                                                                  ctx->loss_accum + 64, ctx->ticket_dev, loss_dev);
   DGC_LAUNCHED(ctx, "mss_reduce");
+  return DGC_OK;
+}
+
+DGC_EXPORT int32_t dgc_mss_loss_bwd(dgc_ctx *ctx, const dgc_mss_params *p, const float *pred_dev,
+                                    const float *target_dev, float upstream, float *grad_pred_dev) {
+  if (!ctx) return DGC_ERR_INVALID;
+  DGC_REQUIRE(ctx, p && pred_dev && target_dev && grad_pred_dev, "null pointer");
+  int32_t rc = validate(ctx, p);
+  if (rc != DGC_OK) return rc;
+  int used = 0;
+  for (int s = 0; s < p->nscales; ++s)
+    if (p->sizes[s] <= p->T) ++used;
+  if (used == 0) {
+    DGC_CUDA(ctx, cudaMemsetAsync(grad_pred_dev, 0, (size_t)p->B * p->T * sizeof(float), ctx->stream));
+    return DGC_OK;
+  }
+  const double den = (double)p->B * (double)used * (double)p->T;
+  const float c_lin = (float)((double)upstream * (double)p->w_lin / den);
+  const float c_log = (float)((double)upstream * (double)p->w_log / den);
+  int accumulate = 0;
+  for (int s = 0; s < p->nscales; ++s) {
+    const int N = p->sizes[s];
+    if (N > p->T) continue;
+    const int hop = hop_of(p, s), H = dgc_div_up(p->T, hop);
+    switch (N) {
+#define CASE(NN) case NN: rc = launch_bwd<NN>(ctx, p, pred_dev, target_dev, hop, H, c_lin, c_log, accumulate, grad_pred_dev); break;
+      CASE(16) CASE(32) CASE(64) CASE(128) CASE(256) CASE(512) CASE(1024) CASE(2048)
+#undef CASE
+      default: return dgc_fail(ctx, DGC_ERR_UNSUPPORTED, "window size %d", N);
+    }
+    if (rc != DGC_OK) return rc;
+    accumulate = 1;
+  }
   return DGC_OK;
 }

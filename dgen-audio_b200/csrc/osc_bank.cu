@@ -202,16 +202,29 @@ __global__ void anchor_sum_kernel(const float *__restrict__ f0t, int B, int T, i
   sums[((size_t)b * C + c) * K + k] = acc;
 }
 
-// SCAN anchors, stage 2: exclusive prefix over chunks; the fixed-point phase is rounded to float
-__global__ void anchor_scan_kernel(const unsigned long long *__restrict__ sums, int B, int C, int K,
-                                   float *__restrict__ anchors) {
-  int lane_id = blockIdx.x * blockDim.x + threadIdx.x;
-  if (lane_id >= B * K) return;
-  int b = lane_id / K, k = lane_id - b * K;
+// SCAN anchors, stage 2: exclusive prefix over chunks; the fixed-point phase is rounded to float.
+// Block = 32 time segments (warps) x 32 partials (lanes, coalesced); each warp totals its segment,
+// the segment totals are prefixed through shared memory, then each warp walks its segment again.
+__global__ void __launch_bounds__(1024)
+anchor_scan_kernel(const unsigned long long *__restrict__ sums, int B, int C, int K,
+                   float *__restrict__ anchors) {
+  __shared__ unsigned long long seg_tot[32][33];
+  const int kk = threadIdx.x & 31, seg = threadIdx.x >> 5;
+  const int k = blockIdx.x * 32 + kk, b = blockIdx.y;
+  const bool ok = k < K;
+  const int per = (C + 31) / 32;
+  const int c0 = min(C, seg * per), c1 = min(C, c0 + per);
   const unsigned long long *s = sums + (size_t)b * C * K + k;
   float *out = anchors + (size_t)b * C * K + k;
+  unsigned long long tot = 0ull;
+  if (ok)
+    for (int c = c0; c < c1; ++c) tot += s[(size_t)c * K];
+  seg_tot[seg][kk] = tot;
+  __syncthreads();
   unsigned long long acc = 0ull;
-  for (int c = 0; c < C; ++c) {
+  for (int s2 = 0; s2 < seg; ++s2) acc += seg_tot[s2][kk];
+  if (!ok) return;
+  for (int c = c0; c < c1; ++c) {
     float p = __ull2float_rn(acc) * 5.421010862427522e-20f;  // 2^-64
     out[(size_t)c * K] = p >= 1.0f ? 0.0f : p;
     acc += s[(size_t)c * K];
@@ -422,7 +435,7 @@ DGC_EXPORT int32_t dgc_harmonic_render(dgc_ctx *ctx, const dgc_harmonic_params *
   } else {
     anchor_sum_kernel<<<dim3(C, B), ((K + 31) / 32) * 32, 0, ctx->stream>>>(f0t, B, T, K, sr, rsr, sums);
     DGC_LAUNCHED(ctx, "anchor_sum");
-    anchor_scan_kernel<<<dgc_div_up(B * K, 64), 64, 0, ctx->stream>>>(sums, B, C, K, anchors);
+    anchor_scan_kernel<<<dim3(dgc_div_up(K, 32), B), 1024, 0, ctx->stream>>>(sums, B, C, K, anchors);
     DGC_LAUNCHED(ctx, "anchor_scan");
   }
 #define RENDER(LPC, P) launch_render<LPC, P>(ctx, *p, play, f0_dev, uv_dev, amps_dev, gain_dev, anchors, audio_dev)

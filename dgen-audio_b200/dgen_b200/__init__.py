@@ -72,8 +72,16 @@ SIGNATURES = {
     "dgc_harmonic_render": (_i32, [_vp, C.POINTER(HarmonicParams), _vp, _vp, _vp, _vp, _vp, _vp]),
     "dgc_fir_noise": (_i32, [_vp, C.POINTER(FirParams), _vp, _vp, _vp, _vp]),
     "dgc_bands_to_taps": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _vp]),
+    "dgc_onepole_fwd": (_i32, [_vp, _vp, _i32, _i32, _f, _vp]),
+    "dgc_biquad_scratch_floats": (_u64, [C.POINTER(BiquadParams), _i32]),
+    "dgc_biquad_fwd": (_i32, [_vp, C.POINTER(BiquadParams), _vp, _vp, _vp, _vp, _vp]),
+    "dgc_biquad_mse_bwd": (_i32, [_vp, C.POINTER(BiquadParams), _vp, _vp, _vp, _vp, _vp, _f, _vp, _vp, _vp, _vp]),
+    "dgc_stft_mag": (_i32, [_vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp]),
+    "dgc_partconv_scratch_floats": (_u64, [_i32, _i32, _i32, _i32, _i32]),
+    "dgc_partconv": (_i32, [_vp, _vp, _i32, _i32, _vp, _i32, _i32, _i32, _f, _vp, _vp]),
     "dgc_mss_partial_floats": (_u64, [C.POINTER(MssParams)]),
     "dgc_mss_loss_fwd": (_i32, [_vp, C.POINTER(MssParams), _vp, _vp, _vp, _vp]),
+    "dgc_mss_loss_bwd": (_i32, [_vp, C.POINTER(MssParams), _vp, _vp, _f, _vp]),
     "dgc_hn_forward_loss_host": (_i32, [_vp, C.POINTER(HnStep)] + [_vp] * 9 + [C.POINTER(C.c_double), _vp]),
 }
 
@@ -211,6 +219,45 @@ class Context:
         self.check(self.lib.dgc_bands_to_taps(self.h, _ptr(bands), _ptr(w), F * B, NB, NT, _ptr(out)))
         return out
 
+    # ---- linear recurrences -------------------------------------------------------------------
+    def onepole_fwd(self, x, a):
+        B, T = x.shape
+        y = self._empty(B, T)
+        self.check(self.lib.dgc_onepole_fwd(self.h, _ptr(x), B, T, a, _ptr(y)))
+        return y
+
+    def biquad_fwd(self, x, cutoff, q, gain=1.0, mode=0.0):
+        B, T = x.shape
+        L = cutoff.numel()
+        p = BiquadParams(B, T, L, gain, mode)
+        y = self._empty(B, T, L)
+        self.check(self.lib.dgc_biquad_fwd(self.h, C.byref(p), _ptr(x), _ptr(cutoff), _ptr(q), None, _ptr(y)))
+        return y
+
+    def biquad_mse_bwd(self, x, cutoff, q, y, target, loss_scale=1.0, gain=1.0, mode=0.0):
+        B, T = x.shape
+        L = cutoff.numel()
+        p = BiquadParams(B, T, L, gain, mode)
+        gc, gq = self._empty(L), self._empty(L)
+        loss = self._empty(1, dtype=self.torch.float64)
+        self.check(self.lib.dgc_biquad_mse_bwd(self.h, C.byref(p), _ptr(x), _ptr(cutoff), _ptr(q), _ptr(y),
+                                               _ptr(target), loss_scale, None, _ptr(gc), _ptr(gq), _ptr(loss)))
+        return gc, gq, loss
+
+    # ---- hop-gated spectral blocks ------------------------------------------------------------
+    def stft_mag(self, x, N, hop, window=None):
+        V, T = x.shape
+        H = (T + hop - 1) // hop
+        out = self._empty(V, H, N // 2 + 1)
+        self.check(self.lib.dgc_stft_mag(self.h, _ptr(x), V, T, N, hop, _ptr(window), _ptr(out)))
+        return out
+
+    def partconv(self, x, ir, N, hop, gain=1.0):
+        V, T = x.shape
+        out = self._empty(V, T)
+        self.check(self.lib.dgc_partconv(self.h, _ptr(x), V, T, _ptr(ir), ir.numel(), N, hop, gain, None, _ptr(out)))
+        return out
+
     # ---- spectral loss ------------------------------------------------------------------------
     def mss_loss_fwd(self, pred, target, sizes=(2048, 1024, 512, 256, 128, 64), hop_div=4, w_lin=1.0, w_log=1.0,
                      want_partial=False):
@@ -222,6 +269,14 @@ class Context:
             part = self._empty(int(self.lib.dgc_mss_partial_floats(C.byref(p))))
         self.check(self.lib.dgc_mss_loss_fwd(self.h, C.byref(p), _ptr(pred), _ptr(target), _ptr(part), _ptr(loss)))
         return (loss, part) if want_partial else loss
+
+    def mss_loss_bwd(self, pred, target, sizes=(2048, 1024, 512, 256, 128, 64), hop_div=4, w_lin=1.0, w_log=1.0,
+                     upstream=1.0):
+        B, T = pred.shape
+        p = mss_params(B, T, sizes, hop_div, w_lin, w_log)
+        grad = self._empty(B, T)
+        self.check(self.lib.dgc_mss_loss_bwd(self.h, C.byref(p), _ptr(pred), _ptr(target), upstream, _ptr(grad)))
+        return grad
 
     # ---- composite, host buffers --------------------------------------------------------------
     def hn_forward_loss_host(self, step, f0, uv, amps, gain, noise_gain, taps_or_bands, w, noise, target,

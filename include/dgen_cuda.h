@@ -143,6 +143,47 @@ int32_t dgc_fir_noise(dgc_ctx *ctx, const dgc_fir_params *p, const float *noise_
 int32_t dgc_bands_to_taps(dgc_ctx *ctx, const float *bands_dev, const float *w_dev, int32_t rows, int32_t nbands,
                           int32_t taps, float *taps_dev);
 
+/* ---- linear recurrences -------------------------------------------------------------------------
+ * y[n] = x[n] + a*y[n-1] per voice, chunked parallel scan over time.
+ * replaces: historyRead/historyWrite feedback (Sources/DGen/Emit+State.swift:150-224). x,y [B][T]. */
+int32_t dgc_onepole_fwd(dgc_ctx *ctx, const float *x_dev, int32_t B, int32_t T, float a, float *y_dev);
+
+typedef struct dgc_biquad_params {
+  int32_t B, T, L;   /* voices, frames, lanes */
+  float gain;
+  float mode;        /* 0 low-pass .. 5, as Graph.biquad's selector */
+} dgc_biquad_params;
+
+/* Device scratch (floats) the biquad entry points need; backward != 0 for dgc_biquad_mse_bwd. */
+uint64_t dgc_biquad_scratch_floats(const dgc_biquad_params *p, int32_t backward);
+/* Tensor biquad bank (Sources/DGen/HigherOps.swift:401-570): x [B][T] shared by L lanes with
+ * per-lane cutoff/q; y [B][T][L].  scratch_dev NULL = context-owned buffer. */
+int32_t dgc_biquad_fwd(dgc_ctx *ctx, const dgc_biquad_params *p, const float *x_dev, const float *cutoff_dev,
+                       const float *q_dev, float *scratch_dev, float *y_dev);
+/* Reverse-time pass (BPTT, Sources/DGen/Gradients.swift:765-778,
+ * Sources/DGen/Blocks/Emission/BPTTEmission.swift:471-518) for loss = loss_scale * sum (y - target)^2:
+ * gradients w.r.t. the per-lane cutoff and q, summed over voices and frames; loss_dev gets the loss.
+ * y, target [B][T][L]. */
+int32_t dgc_biquad_mse_bwd(dgc_ctx *ctx, const dgc_biquad_params *p, const float *x_dev, const float *cutoff_dev,
+                           const float *q_dev, const float *y_dev, const float *target_dev, float loss_scale,
+                           float *scratch_dev, float *grad_cutoff_dev, float *grad_q_dev, double *loss_dev);
+
+/* ---- hop-gated spectral blocks ------------------------------------------------------------------
+ * buffer(size:N, hop:) -> FFT -> magnitude for V signals of T frames: mags [V][H][N/2+1],
+ * H = ceil(T/hop), window element i of hop frame f = x[f-N+1+i] * window[i] (window NULL = none).
+ * replaces: bufferView + acceleratedFFT/tensorFFT + sqrt(re^2+im^2)
+ * (HigherOps.swift:738-792, Emit+AcceleratedFFT.swift:16-112, DGenHostSupport.c:10-30). */
+int32_t dgc_stft_mag(dgc_ctx *ctx, const float *x_dev, int32_t V, int32_t T, int32_t N, int32_t hop,
+                     const float *window_dev, float *mags_dev);
+
+/* partitionedConvolve (Sources/DGenLazy/SpectralTensorOps.swift:204-254,
+ * Emit+PartitionedConvolution.swift:26-113, Emit+FFT.swift:6-62): V signals [V][T], one IR; periodic
+ * Hann analysis and synthesis windows, IFFT scaled by 1/N, overlap-add at `hop`.
+ * scratch_dev: dgc_partconv_scratch_floats() floats, or NULL for a context-owned buffer. */
+uint64_t dgc_partconv_scratch_floats(int32_t V, int32_t T, int32_t ir_len, int32_t N, int32_t hop);
+int32_t dgc_partconv(dgc_ctx *ctx, const float *x_dev, int32_t V, int32_t T, const float *ir_dev, int32_t ir_len,
+                     int32_t N, int32_t hop, float gain, float *scratch_dev, float *out_dev);
+
 /* ---- multi-scale spectral loss ------------------------------------------------------------------ */
 #define DGC_MSS_MAX_SCALES 8
 typedef struct dgc_mss_params {
@@ -162,6 +203,12 @@ typedef struct dgc_mss_params {
 uint64_t dgc_mss_partial_floats(const dgc_mss_params *p);
 int32_t dgc_mss_loss_fwd(dgc_ctx *ctx, const dgc_mss_params *p, const float *pred_dev, const float *target_dev,
                          float *partial_dev, double *loss_dev);
+/* Backward: d loss / d pred, [B][T] (Sources/DGen/Gradients.swift:1038-1142,
+ * Emit+SpectralLoss.swift:940-1325), recomputing the spectra instead of storing them; `upstream` is
+ * d objective / d loss.  grad is overwritten.  Bit-reproducible (no atomics). */
+int32_t dgc_mss_loss_bwd(dgc_ctx *ctx, const dgc_mss_params *p, const float *pred_dev, const float *target_dev,
+                         float upstream, float *grad_pred_dev);
+
 /* ---- composite steps with host buffers (the call a host makes per batch) ------------------------ */
 typedef struct dgc_hn_step {
   dgc_harmonic_params harm;

@@ -48,6 +48,7 @@ def _declare(L):
         fn("orc_biquad", None, [p, C.c_int, ct, ct, ct, ct, p])
         fn("orc_biquad_coef", None, [ct, ct, ct, ct, p])
         fn("orc_biquad_bank", None, [p, C.c_int, C.c_int, C.c_int, p, p, ct, ct, p])
+        fn("orc_biquad_bank_mse_grad", C.c_double, [p, C.c_int, C.c_int, C.c_int, p, p, ct, ct, p, ct, p, p])
         fn("orc_fft", None, [p, p, C.c_int, C.c_int])
         fn("orc_hann_periodic", None, [C.c_int, p])
         fn("orc_hann_symmetric", None, [C.c_int, p])
@@ -56,6 +57,7 @@ def _declare(L):
         fn("orc_partitioned_convolve", None, [p, C.c_int, p, C.c_int, C.c_int, C.c_int, ct, p])
         fn("orc_spectral_loss", C.c_double, [p, p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, vp])
         fn("orc_mss_loss", C.c_double, [p, p, C.c_int, C.c_int, i32p, C.c_int, C.c_int, ct, ct])
+        fn("orc_mss_loss_grad", None, [p, p, C.c_int, C.c_int, i32p, C.c_int, C.c_int, ct, ct, ct, p])
         fn("orc_harmonic_noise_render", None,
            [C.c_int] * 5 + [ct] + [p, p, p, p, p, vp, vp, ct, ct, p, vp])
         fn("orc_adam", None, [p, p, p, p, C.c_size_t, C.c_int, ct, ct, ct, ct])
@@ -173,6 +175,20 @@ def biquad_bank(x, cutoff, q, gain=1.0, mode=0.0, double=False, L=None):
     return y
 
 
+def biquad_bank_mse_grad(x, cutoff, q, target, scale=1.0, gain=1.0, mode=0.0, double=True, L=None):
+    """target [B][L][T]. Returns (loss, grad_cutoff[L], grad_q[L])."""
+    dt, s = _dt(double)
+    x = np.ascontiguousarray(x, dt)
+    B, T = x.shape
+    cutoff = np.ascontiguousarray(cutoff, dt)
+    q = np.ascontiguousarray(q, dt)
+    target = np.ascontiguousarray(target, dt)
+    gc, gq = np.empty(cutoff.size, dt), np.empty(cutoff.size, dt)
+    loss = getattr(L or lib(), "orc_biquad_bank_mse_grad" + s)(x, B, T, cutoff.size, cutoff, q, gain, mode, target,
+                                                               scale, gc, gq)
+    return loss, gc, gq
+
+
 def fft(re, im, inverse=False, double=False, L=None):
     dt, s = _dt(double)
     re = np.array(re, dt)
@@ -241,6 +257,18 @@ def mss_loss(x1, x2, sizes=(2048, 1024, 512, 256, 128, 64), hop_div=4, w_lin=1.0
     B, T = x1.shape
     sz = np.asarray(sizes, np.int32)
     return getattr(L or lib(), "orc_mss_loss" + s)(x1, x2, B, T, sz, sz.size, hop_div, w_lin, w_log)
+
+
+def mss_loss_grad(x1, x2, sizes=(2048, 1024, 512, 256, 128, 64), hop_div=4, w_lin=1.0, w_log=1.0, upstream=1.0,
+                  double=True, L=None):
+    dt, s = _dt(double)
+    x1 = np.ascontiguousarray(x1, dt)
+    x2 = np.ascontiguousarray(x2, dt)
+    B, T = x1.shape
+    sz = np.asarray(sizes, np.int32)
+    g = np.empty((B, T), dt)
+    getattr(L or lib(), "orc_mss_loss_grad" + s)(x1, x2, B, T, sz, sz.size, hop_div, w_lin, w_log, upstream, g)
+    return g
 
 
 def harmonic_noise_render(f0, uv, amps, gain, noise_gain, taps, noise, T, sr, hscale=1.0, nscale=1.0,

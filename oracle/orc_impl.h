@@ -234,6 +234,54 @@ void FN(orc_biquad_bank)(const R *x, int B, int T, int L, const R *cutoff, const
 }
 
 /* ---------------------------------------------------------------------------------------------
+ * Gradient reference for the biquad bank: loss = scale * sum_{b,l,n} (y - target)^2, gradients
+ * w.r.t. per-lane cutoff and q through the recurrence (what BPTT computes,
+ * Sources/DGen/Gradients.swift:765-778): adjoint lam[n] = g[n] - a1 lam[n+1] - a2 lam[n+2],
+ * dL/db_i = sum lam[n] x[n-i], dL/da_i = -sum lam[n] y[n-i]; the coefficient Jacobian is taken by
+ * central differences of orc_biquad_coef in this precision (meant for R = double).
+ * x [B][T], target [B][L][T] (oracle layout).  Returns the loss.
+ * ------------------------------------------------------------------------------------------- */
+double FN(orc_biquad_bank_mse_grad)(const R *x, int B, int T, int L, const R *cutoff, const R *q, R gain, R mode,
+                                    const R *target, R scale, R *gcut, R *gq) {
+  R *y = (R *)malloc(sizeof(R) * T), *lam = (R *)malloc(sizeof(R) * (T + 2));
+  double loss = 0;
+  for (int l = 0; l < L; ++l) {
+    FN(OrcBiquadCoef) c;
+    FN(orc_biquad_coef)(cutoff[l], q[l], gain, mode, &c);
+    double G[5] = {0, 0, 0, 0, 0};
+    for (int b = 0; b < B; ++b) {
+      const R *xb = x + (size_t)b * T, *tb = target + ((size_t)b * L + l) * T;
+      FN(orc_biquad)(xb, T, cutoff[l], q[l], gain, mode, y);
+      lam[T] = 0; lam[T + 1] = 0;
+      for (int n = T - 1; n >= 0; --n) {
+        R d = y[n] - tb[n];
+        loss += (double)scale * (double)d * (double)d;
+        lam[n] = (R)2 * scale * d - c.a1 * lam[n + 1] - c.a2 * lam[n + 2];
+        G[0] += (double)lam[n] * (double)xb[n];
+        if (n >= 1) { G[1] += (double)lam[n] * (double)xb[n - 1]; G[3] -= (double)lam[n] * (double)y[n - 1]; }
+        if (n >= 2) { G[2] += (double)lam[n] * (double)xb[n - 2]; G[4] -= (double)lam[n] * (double)y[n - 2]; }
+      }
+    }
+    R hc = FABS(cutoff[l]) * (R)1e-5 + (R)1e-7, hq = FABS(q[l]) * (R)1e-5 + (R)1e-7;
+    FN(OrcBiquadCoef) cp, cm, qp, qm;
+    FN(orc_biquad_coef)(cutoff[l] + hc, q[l], gain, mode, &cp);
+    FN(orc_biquad_coef)(cutoff[l] - hc, q[l], gain, mode, &cm);
+    FN(orc_biquad_coef)(cutoff[l], q[l] + hq, gain, mode, &qp);
+    FN(orc_biquad_coef)(cutoff[l], q[l] - hq, gain, mode, &qm);
+    const R *pp = (const R *)&cp, *pm = (const R *)&cm, *rp = (const R *)&qp, *rm = (const R *)&qm;
+    double dc = 0, dq = 0;
+    for (int i = 0; i < 5; ++i) {
+      dc += G[i] * ((double)pp[i] - (double)pm[i]) / (2.0 * (double)hc);
+      dq += G[i] * ((double)rp[i] - (double)rm[i]) / (2.0 * (double)hq);
+    }
+    gcut[l] = (R)dc;
+    gq[l] = (R)dq;
+  }
+  free(y); free(lam);
+  return loss;
+}
+
+/* ---------------------------------------------------------------------------------------------
  * Host FFT service: Sources/DGenHostSupport/DGenHostSupport.c:10-30 wraps vDSP_fft_zip (Apple
  * Accelerate, closed source, version = whatever the OS ships).  Its published definition is the
  * unnormalised complex DFT  X[k] = sum x[n] exp(-+2 pi i k n / N)  on split re/im arrays, in
@@ -483,6 +531,61 @@ double FN(orc_mss_loss)(const R *x1, const R *x2, int B, int T, const int *sizes
     total += (lin * (double)w_lin + lg * (double)w_log) / (double)usable / (double)T;
   }
   return total;
+}
+
+/* ---------------------------------------------------------------------------------------------
+ * Gradient of orc_mss_loss w.r.t. x1 (the prediction), following the reference's backward rules
+ * (Sources/DGen/Emit+SpectralLoss.swift:940-1325, Sources/DGen/Gradients.swift:1038-1142):
+ *   gradMag1 = sign(d)            (linear term)   or  sign(dlog) / (m1 + eps)   (log term), times c;
+ *   gradX1[k] = gradMag1 * X1[k] / max(m1, 1e-8), k = 0..N/2, zero above;
+ *   time gradient = Re(unnormalised inverse transform of gradX1) * hann; summed over covering windows.
+ * c = upstream * w / (B * usable * T).  grad [B][T] is overwritten.  Meant for R = double.
+ * ------------------------------------------------------------------------------------------- */
+void FN(orc_mss_loss_grad)(const R *x1, const R *x2, int B, int T, const int *sizes, int nscales, int hop_div,
+                           R w_lin, R w_log, R upstream, R *grad) {
+  int usable = 0;
+  for (int s = 0; s < nscales; ++s)
+    if (sizes[s] > 1 && sizes[s] <= T) ++usable;
+  for (size_t i = 0; i < (size_t)B * T; ++i) grad[i] = 0;
+  const R eps = (R)1e-8f;
+  for (int s = 0; s < nscales; ++s) {
+    int N = sizes[s];
+    if (N <= 1 || N > T) continue;
+    int hop = N / (hop_div > 0 ? hop_div : 1);
+    if (hop < 1) hop = 1;
+    R c_lin = upstream * w_lin / ((R)B * (R)usable * (R)T), c_log = upstream * w_log / ((R)B * (R)usable * (R)T);
+    R *win = (R *)malloc(sizeof(R) * N);
+    FN(orc_hann_symmetric)(N, win);
+    R *r1 = (R *)malloc(sizeof(R) * N), *i1 = (R *)malloc(sizeof(R) * N);
+    R *r2 = (R *)malloc(sizeof(R) * N), *i2 = (R *)malloc(sizeof(R) * N);
+    for (int b = 0; b < B; ++b)
+      for (int f = 0; f < T; f += hop) {
+        for (int n = 0; n < N; ++n) {
+          int t = f - (N - 1) + n;
+          int ok = t >= 0 && t < T;
+          r1[n] = ok ? x1[(size_t)b * T + t] * win[n] : 0; i1[n] = 0;
+          r2[n] = ok ? x2[(size_t)b * T + t] * win[n] : 0; i2[n] = 0;
+        }
+        FN(orc_fft)(r1, i1, N, 0);
+        FN(orc_fft)(r2, i2, N, 0);
+        for (int k = 0; k < N; ++k) {
+          if (k > N / 2) { r1[k] = 0; i1[k] = 0; continue; }
+          R m1 = SQRT(r1[k] * r1[k] + i1[k] * i1[k]), m2 = SQRT(r2[k] * r2[k] + i2[k] * i2[k]);
+          R d = m1 - m2, dl = LOG(m1 + eps) - LOG(m2 + eps);
+          R sd = d > 0 ? (R)1 : (d < 0 ? (R)-1 : 0), sl = dl > 0 ? (R)1 : (dl < 0 ? (R)-1 : 0);
+          R gm = c_lin * sd + c_log * sl / (m1 + eps);
+          R safe = m1 > (R)1e-8f ? m1 : (R)1e-8f;
+          r1[k] = gm * r1[k] / safe;
+          i1[k] = gm * i1[k] / safe;
+        }
+        FN(orc_fft)(r1, i1, N, 1);
+        for (int n = 0; n < N; ++n) {
+          int t = f - (N - 1) + n;
+          if (t >= 0 && t < T) grad[(size_t)b * T + t] += r1[n] * win[n];
+        }
+      }
+    free(win); free(r1); free(i1); free(r2); free(i2);
+  }
 }
 
 /* ---------------------------------------------------------------------------------------------

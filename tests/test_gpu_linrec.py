@@ -1,0 +1,117 @@
+"""GPU parity of the linear-recurrence scans (one-pole, biquad bank forward and BPTT) against the oracle."""
+import numpy as np
+import pytest
+
+import dgen_b200
+from dgen_b200 import workloads as wl
+from oracle import oracle as orc
+
+pytestmark = pytest.mark.gpu
+f32 = np.float32
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    c = dgen_b200.Context(0)
+    yield c
+    c.close()
+
+
+def dev(a):
+    import torch
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+@pytest.mark.parametrize("B,T,a", [(1, 65536, 0.9), (3, 5000, 0.5), (2, 1, 0.9), (2, 2049, -0.7), (1, 300000, 0.99)])
+def test_onepole_matches_oracle(ctx, B, T, a):
+    rng = np.random.default_rng(T)
+    x = rng.standard_normal((B, T)).astype(f32)
+    want = np.stack([orc.onepole(x[b], a) for b in range(B)])
+    got = ctx.onepole_fwd(dev(x), a).cpu().numpy()
+    assert np.abs(got - want).max() < 1e-5 * max(1.0, np.abs(want).max())
+
+
+def test_osc_filter_fft_configuration(ctx):
+    """Oscillator bank (64 partials, 110k Hz, 1/k) -> one-pole y = x + 0.9 y1 -> buffer(1024, hop 256) -> FFT
+    -> magnitude, 65536 frames at 44.1 kHz: audio and per-hop magnitude frames against the oracle."""
+    c = wl.osc_filter_fft_inputs()
+    audio_o = orc.onepole(orc.osc_bank_const(c["freq"], c["amp"], c["T"], c["sr"]), c["pole"])
+    mags_o = orc.buffer_fft_mag(audio_o, c["N"], c["hop"])
+    osc = ctx.osc_bank_const(dev(c["freq"]), dev(c["amp"]), c["T"], c["sr"], dgen_b200.PHASE_DETERMINISTIC)
+    audio = ctx.onepole_fwd(osc.view(1, -1), c["pole"])
+    mags = ctx.stft_mag(audio, c["N"], c["hop"])
+    ctx.sync()
+    assert np.abs(audio.cpu().numpy()[0] - audio_o).max() < 1e-4
+    assert mags.shape == (1, 256, 513)
+    assert np.abs(mags.cpu().numpy()[0] - mags_o).max() < 1e-4 * np.abs(mags_o).max()
+
+
+@pytest.mark.parametrize("B,T,L,mode", [(2, 3000, 5, 0.0), (1, 512, 130, 0.0), (2, 1025, 3, 1.0), (1, 700, 4, 2.0),
+                                        (1, 2048, 6, 5.0), (3, 1, 2, 0.0)])
+def test_biquad_forward_matches_oracle(ctx, B, T, L, mode):
+    d = wl.biquad_bank_inputs(17, B=B, L=L, T=T)
+    want = orc.biquad_bank(d["x"], d["cutoff"], d["q"], mode=mode)              # [B][L][T]
+    got = ctx.biquad_fwd(dev(d["x"]), dev(d["cutoff"]), dev(d["q"]), mode=mode)  # [B][T][L]
+    got = got.cpu().numpy().transpose(0, 2, 1)
+    # scalar-vs-lane tolerance of the reference's own tests is 1e-4..1e-6 (TensorBiquadTests.swift:72-221)
+    assert np.abs(got - want).max() < 1e-4 * max(1.0, np.abs(want).max())
+
+
+def test_biquad_lanes_are_independent(ctx):
+    """Lane independence is exact (Tests/DGenLazyTests/TensorBiquadGradientTests.swift)."""
+    d = wl.biquad_bank_inputs(3, B=2, L=8, T=2000)
+    full = ctx.biquad_fwd(dev(d["x"]), dev(d["cutoff"]), dev(d["q"])).cpu().numpy()
+    for l in (0, 5):
+        one = ctx.biquad_fwd(dev(d["x"]), dev(d["cutoff"][l:l + 1]), dev(d["q"][l:l + 1])).cpu().numpy()
+        assert np.array_equal(one[:, :, 0], full[:, :, l])
+
+
+@pytest.mark.parametrize("B,T,L", [(2, 4000, 6), (1, 513, 3), (3, 1500, 40)])
+def test_biquad_bptt_gradients_match_fp64_and_finite_differences(ctx, B, T, L):
+    """Cutoffs from 400 Hz up: below that the reference's single-precision coefficient formula
+    (1 - cos(w), Sources/DGen/HigherOps.swift:447-452) loses up to 3 digits by cancellation, so no
+    single-precision evaluation of the graph can sit within 1e-3 of a double-precision one."""
+    d = wl.biquad_bank_inputs(29, B=B, L=L, T=T)
+    x, q = d["x"], d["q"]
+    cut = np.exp(np.random.default_rng(L).uniform(np.log(400.0), np.log(8000.0), L)).astype(f32)
+    target = orc.biquad_bank(x, cut * f32(1.05), q)                             # [B][L][T]
+    scale = 1.0 / (B * T)
+    loss64, gc64, gq64 = orc.biquad_bank_mse_grad(x, cut, q, target, scale=scale)
+    y = ctx.biquad_fwd(dev(x), dev(cut), dev(q))
+    gc, gq, loss = ctx.biquad_mse_bwd(dev(x), dev(cut), dev(q), y, dev(target.transpose(0, 2, 1)), loss_scale=scale)
+    gc, gq, loss = gc.cpu().numpy(), gq.cpu().numpy(), float(loss.cpu()[0])
+    own = ((y.cpu().numpy().astype(np.float64) - target.transpose(0, 2, 1)) ** 2).sum() * scale
+    assert abs(loss - own) < 1e-5 * own                     # the reduction itself
+    assert abs(loss - loss64) < 1e-3 * abs(loss64)
+    # gradient tolerance of the path: 1e-3 relative to the fp64 evaluation
+    assert np.abs(gc - gc64).max() < 1e-3 * np.abs(gc64).max()
+    assert np.abs(gq - gq64).max() < 1e-3 * np.abs(gq64).max()
+    # finite-difference check of the fp64 loss on one lane
+    l = int(np.argmax(np.abs(gc64)))
+    h = float(cut[l]) * 1e-5
+    cp, cm = cut.astype(np.float64).copy(), cut.astype(np.float64).copy()
+    cp[l] += h
+    cm[l] -= h
+    lp = ((orc.biquad_bank(x, cp, q, double=True) - target) ** 2).sum() * scale
+    lm = ((orc.biquad_bank(x, cm, q, double=True) - target) ** 2).sum() * scale
+    fd = (lp - lm) / (2 * h)
+    assert abs(fd - gc[l]) < 2e-3 * abs(fd)
+
+
+def test_biquad_bptt_full_cutoff_range_is_finite_and_close(ctx):
+    """The biquad-bank configuration's own parameter range (50..8000 Hz, Q 0.5..8): gradients agree with
+    the fp64 evaluation to the accuracy the single-precision coefficient formula allows."""
+    d = wl.biquad_bank_inputs(20260002, B=2, L=64, T=8192)
+    x, cut, q = d["x"], d["cutoff"], d["q"]
+    target = orc.biquad_bank(x, cut * f32(1.05), q)
+    scale = 1.0 / (2 * 8192)
+    loss64, gc64, gq64 = orc.biquad_bank_mse_grad(x, cut, q, target, scale=scale)
+    y = ctx.biquad_fwd(dev(x), dev(cut), dev(q))
+    gc, gq, loss = ctx.biquad_mse_bwd(dev(x), dev(cut), dev(q), y, dev(target.transpose(0, 2, 1)), loss_scale=scale)
+    gc, gq = gc.cpu().numpy(), gq.cpu().numpy()
+    assert np.isfinite(gc).all() and np.isfinite(gq).all()
+    assert abs(float(loss.cpu()[0]) - loss64) < 2e-2 * loss64
+    ok = cut >= 400.0
+    assert np.abs(gc - gc64)[ok].max() < 2e-3 * np.abs(gc64)[ok].max()
+    assert np.abs(gq - gq64)[ok].max() < 2e-3 * np.abs(gq64)[ok].max()
+    assert np.abs(gc - gc64).max() < 0.1 * np.abs(gc64).max()

@@ -68,3 +68,46 @@ def test_loss_is_bit_deterministic(ctx):
     a = ctx.mss_loss_fwd(x, y).cpu().numpy()
     b = ctx.mss_loss_fwd(x, y).cpu().numpy()
     assert a.tobytes() == b.tobytes()
+
+
+@pytest.mark.parametrize("sizes,T", [((64,), 1000), ((2048,), 9000), ((16, 32), 300), ((512, 128), 4000),
+                                     ((2048, 1024, 512, 256, 128, 64), 16000)])
+def test_backward_matches_fp64_oracle(ctx, sizes, T):
+    rng = np.random.default_rng(T)
+    B = 3
+    x = rng.standard_normal((B, T)).astype(f32)
+    y = (0.7 * rng.standard_normal((B, T))).astype(f32)
+    want = orc.mss_loss_grad(x, y, sizes, upstream=2.0)
+    got = ctx.mss_loss_bwd(dev(x), dev(y), sizes=sizes, upstream=2.0).cpu().numpy()
+    # gradient tolerance of the path: 1e-3 relative to the fp64 evaluation.  The L1 terms carry sign(m1 - m2):
+    # a bin whose two magnitudes agree to single-precision rounding flips that sign in ANY fp32 evaluation
+    # (separate per-signal fp32 FFTs on the host produce the very same outliers, to 4 digits), and one
+    # flipped bin moves every frame of its window.  So: all but the worst 0.5 % of frames within 1e-3
+    # norm-wise, and no frame off by more than 5e-3 of the largest gradient.
+    err = np.abs(got - want)
+    keep = err <= np.quantile(err, 0.995)
+    assert np.linalg.norm(err[keep]) < 1e-3 * np.linalg.norm(want)
+    assert err.max() < 5e-3 * np.abs(want).max()
+
+
+def test_backward_passes_a_finite_difference_check(ctx):
+    rng = np.random.default_rng(5)
+    B, T, sizes = 2, 3000, (256, 64)
+    x = rng.standard_normal((B, T)).astype(f32)
+    y = rng.standard_normal((B, T)).astype(f32)
+    g = ctx.mss_loss_bwd(dev(x), dev(y), sizes=sizes).cpu().numpy()
+    for b, t in ((0, 10), (1, 1500), (0, 2900)):
+        h = 1e-4
+        xp, xm = x.astype(np.float64), x.astype(np.float64)
+        xp[b, t] += h
+        xm[b, t] -= h
+        fd = (orc.mss_loss(xp, y, sizes, double=True) - orc.mss_loss(xm, y, sizes, double=True)) / (2 * h)
+        assert abs(g[b, t] - fd) < 2e-3 * max(abs(fd), np.abs(g).max() * 0.05)
+
+
+def test_backward_is_bit_deterministic(ctx):
+    rng = np.random.default_rng(9)
+    x, y = dev(rng.standard_normal((2, 9000)).astype(f32)), dev(rng.standard_normal((2, 9000)).astype(f32))
+    a = ctx.mss_loss_bwd(x, y).cpu().numpy()
+    b = ctx.mss_loss_bwd(x, y).cpu().numpy()
+    assert a.tobytes() == b.tobytes()
