@@ -519,3 +519,86 @@ DGC_EXPORT int32_t dgc_biquad_mse_bwd(dgc_ctx *ctx, const dgc_biquad_params *p, 
   DGC_LAUNCHED(ctx, "biquad_loss_sum");
   return DGC_OK;
 }
+
+// ---------------------------------------------------------------------------------------------
+// One-pole filter for callers that must not allocate.
+//
+// A real-time audio thread (a plug-in's render callback, a driver I/O thread) may not call anything
+// that allocates or may block for an unbounded time; cudaMalloc does both, and a dgc_ctx allocates
+// when it is created and whenever its scratch grows.  This entry point therefore takes no context:
+// the chunk-carry scratch the scan needs lives in a fixed array in device memory that is part of the
+// library image (every GPU that loads the library holds these 256 KiB until the process exits), and
+// the caller supplies only the stream, the input and the output.
+// ---------------------------------------------------------------------------------------------
+#include <mutex>
+
+namespace {
+constexpr int STATIC_MAX_CHUNKS = DGC_ONEPOLE_STATIC_MAX_CHUNKS;
+// [0, MAX): end value of every chunk; [MAX, 2 MAX): carry entering every chunk
+static __device__ __align__(256) float g_onepole_static_scratch[2 * STATIC_MAX_CHUNKS];
+
+constexpr int STATIC_MAX_DEVICES = 64;
+std::mutex g_static_mutex;
+float *g_static_ptr[STATIC_MAX_DEVICES] = {nullptr};
+
+void static_msg(char *buf, uint32_t len, const char *fmt, long long a = 0, long long b = 0) {
+  if (buf && len) snprintf(buf, len, fmt, a, b);
+}
+}  // namespace
+
+DGC_EXPORT int32_t dgc_onepole_fwd_static(void *cuda_stream, const float *x_dev, int32_t B, int32_t T, float a,
+                                          float *y_dev, char *err_buf, uint32_t err_len) {
+  if (err_buf && err_len) err_buf[0] = 0;
+  if (!x_dev || !y_dev) {
+    static_msg(err_buf, err_len, "dgc_onepole_fwd_static: null input or output pointer");
+    return DGC_ERR_INVALID;
+  }
+  if (B <= 0 || T <= 0) {
+    static_msg(err_buf, err_len, "dgc_onepole_fwd_static: B and T must be positive");
+    return DGC_ERR_INVALID;
+  }
+  const long long NC = ((long long)T + OP_CHUNK - 1) / OP_CHUNK;
+  if ((long long)B * NC > STATIC_MAX_CHUNKS || B > 65535) {
+    static_msg(err_buf, err_len,
+               "dgc_onepole_fwd_static: B*ceil(T/2048) = %lld exceeds the built-in scratch of %lld chunk slots; "
+               "use dgc_onepole_fwd with a context for larger signals",
+               (long long)B * NC, (long long)STATIC_MAX_CHUNKS);
+    return DGC_ERR_INVALID;
+  }
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= STATIC_MAX_DEVICES) {
+    static_msg(err_buf, err_len, "dgc_onepole_fwd_static: no usable current device (cudaGetDevice = %lld)", (long long)e);
+    return DGC_ERR_CUDA;
+  }
+  float *scratch = nullptr;
+  {
+    // Set-up, once per device, with that device current: the array's name is only a host-side
+    // handle for the symbol; the address a kernel can use comes from cudaGetSymbolAddress.
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    if (!g_static_ptr[dev]) {
+      float *p = nullptr;
+      e = cudaGetSymbolAddress((void **)&p, g_onepole_static_scratch);
+      if (e != cudaSuccess || !p) {
+        static_msg(err_buf, err_len, "dgc_onepole_fwd_static: cudaGetSymbolAddress failed (%lld) on device %lld",
+                   (long long)e, (long long)dev);
+        return DGC_ERR_CUDA;
+      }
+      g_static_ptr[dev] = p;
+    }
+    scratch = g_static_ptr[dev];
+  }
+  cudaStream_t st = (cudaStream_t)cuda_stream;
+  float *chunk_end = scratch, *carry = scratch + STATIC_MAX_CHUNKS;
+  // Every slot that is read below is written first by this call (chunk ends by pass 0, carries by the
+  // carry kernel), so nothing has to be cleared although the array keeps the previous call's contents.
+  onepole_kernel<0><<<dim3((unsigned)NC, B), OP_THREADS, 0, st>>>(x_dev, T, (int)NC, a, nullptr, chunk_end, nullptr);
+  onepole_carry_kernel<<<dgc_div_up(B, 64), 64, 0, st>>>(chunk_end, B, (int)NC, a, 0.0f, carry);
+  onepole_kernel<1><<<dim3((unsigned)NC, B), OP_THREADS, 0, st>>>(x_dev, T, (int)NC, a, carry, nullptr, y_dev);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    static_msg(err_buf, err_len, "dgc_onepole_fwd_static: launch failed (%lld)", (long long)e);
+    return DGC_ERR_CUDA;
+  }
+  return DGC_OK;
+}

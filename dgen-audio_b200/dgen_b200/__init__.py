@@ -73,6 +73,7 @@ SIGNATURES = {
     "dgc_fir_noise": (_i32, [_vp, C.POINTER(FirParams), _vp, _vp, _vp, _vp]),
     "dgc_bands_to_taps": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _vp]),
     "dgc_onepole_fwd": (_i32, [_vp, _vp, _i32, _i32, _f, _vp]),
+    "dgc_onepole_fwd_static": (_i32, [_vp, _vp, _i32, _i32, _f, _vp, C.c_char_p, _u32]),
     "dgc_biquad_scratch_floats": (_u64, [C.POINTER(BiquadParams), _i32]),
     "dgc_biquad_fwd": (_i32, [_vp, C.POINTER(BiquadParams), _vp, _vp, _vp, _vp, _vp]),
     "dgc_biquad_mse_bwd": (_i32, [_vp, C.POINTER(BiquadParams), _vp, _vp, _vp, _vp, _vp, _f, _vp, _vp, _vp, _vp]),

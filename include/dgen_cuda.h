@@ -148,6 +148,25 @@ int32_t dgc_bands_to_taps(dgc_ctx *ctx, const float *bands_dev, const float *w_d
  * replaces: historyRead/historyWrite feedback (Sources/DGen/Emit+State.swift:150-224). x,y [B][T]. */
 int32_t dgc_onepole_fwd(dgc_ctx *ctx, const float *x_dev, int32_t B, int32_t T, float a, float *y_dev);
 
+/* The same filter for callers that must not allocate.  No counterpart in the reference: it exists
+ * because a real-time audio thread (a plug-in render callback, a driver I/O thread) cannot call
+ * cudaMalloc -- it may block without bound -- and creating or growing a dgc_ctx does.  This call takes
+ * no context and allocates nothing, on the host or on the device: its chunk-carry scratch is a fixed
+ * 256 KiB array inside the library's device image, present on every GPU that loads the library until
+ * the process exits.
+ *   limit     B * ceil(T / 2048) <= DGC_ONEPOLE_STATIC_MAX_CHUNKS (and B <= 65535); larger requests
+ *             return DGC_ERR_INVALID with the reason in err_buf (err_buf may be NULL).
+ *   set-up    the first call on each device looks up the array's device address
+ *             (cudaGetSymbolAddress) with that device current; make that first call before any
+ *             stream capture begins.  Later calls only launch kernels on `cuda_stream`
+ *             (a cudaStream_t; NULL = default stream) of the CURRENT device.
+ *   sharing   all calls on a device use the same array, which keeps the last call's contents; the
+ *             filter overwrites every slot before reading it, so nothing needs clearing, but two
+ *             calls that overlap on the GPU (different streams, no ordering) race: serialise them. */
+#define DGC_ONEPOLE_STATIC_MAX_CHUNKS 32768
+int32_t dgc_onepole_fwd_static(void *cuda_stream, const float *x_dev, int32_t B, int32_t T, float a, float *y_dev,
+                               char *err_buf, uint32_t err_len);
+
 typedef struct dgc_biquad_params {
   int32_t B, T, L;   /* voices, frames, lanes */
   float gain;
