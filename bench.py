@@ -31,6 +31,7 @@ UNIT = "samples/s"
 CFG = dict(B=16, T=64000, K=100, F=1000, sr=16000.0, nbands=65, taps=257)
 SIZES = (2048, 1024, 512, 256, 128, 64)
 SEED = 20260001
+PHASE = {"mode": "scan"}
 
 
 def config_json(n_gpus):
@@ -38,7 +39,7 @@ def config_json(n_gpus):
             "voices_per_gpu": CFG["B"], "frames": CFG["T"], "harmonics": CFG["K"], "control_frames": CFG["F"],
             "sample_rate": CFG["sr"], "noise_bands": CFG["nbands"], "fir_taps": CFG["taps"],
             "fft_sizes": list(SIZES), "overlap": 0.75, "global_voices": CFG["B"] * n_gpus,
-            "phase_mode": "scan", "sharding": "voices across GPUs, no collective",
+            "phase_mode": PHASE["mode"], "sharding": "voices across GPUs, no collective",
             "l2": "L2 flushed (512 MiB write) between timed steps"}
 
 
@@ -178,7 +179,8 @@ def run_ours(args, rank, world, local_rank):
     loss = torch.zeros(1, dtype=torch.float64, device="cuda")
     mss = dgen_b200.mss_params(B, T, SIZES)
     import ctypes as C
-    hp = dgen_b200.HarmonicParams(B, T, K, F, sr, 1.0, dgen_b200.PHASE_SCAN, 0)
+    hp = dgen_b200.HarmonicParams(B, T, K, F, sr, 1.0,
+                                  dgen_b200.PHASE_SCAN if PHASE["mode"] == "scan" else dgen_b200.PHASE_SEQUENTIAL, 0)
     fp = dgen_b200.FirParams(B, T, F, CFG["taps"], 0.12, 1)
     lib, h = ctx.lib, ctx.h
     taps_buf = torch.empty(F, B, CFG["taps"], device="cuda")
@@ -332,10 +334,18 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--voices", type=int, default=0,
+                    help="voices per GPU (default: the configuration's 16); other values are for profiling "
+                         "captures and scaling studies, not for the headline number")
+    ap.add_argument("--phase", default="scan", choices=["scan", "sequential"],
+                    help="phase-anchor mode of the oscillator bank")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.voices > 0:
+        CFG["B"] = args.voices
+    PHASE["mode"] = args.phase
     if args.impl == "reference":
         run_reference(args, rank, world)
         return

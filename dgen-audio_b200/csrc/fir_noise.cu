@@ -154,7 +154,10 @@ fir_noise_kernel(dgc_fir_params prm, const float *__restrict__ play, const float
   }
 }
 
-// taps[r][i] = sum_j W[i][j] * bands[r][j]; block = 16 rows, thread = taps i, i+256, ...
+// taps[r][i] = sum_j W[i][j] * bands[r][j]; W is staged once per block and reused for BT_PASSES
+// groups of 16 rows; thread = taps i, i+256, ...
+constexpr int BT_PASSES = 8;
+
 __global__ void __launch_bounds__(256)
 bands_to_taps_kernel(const float *__restrict__ bands, const float *__restrict__ w, int rows, int nb, int nt,
                      float *__restrict__ out) {
@@ -163,32 +166,36 @@ bands_to_taps_kernel(const float *__restrict__ bands, const float *__restrict__ 
   float *wsh = sh;                       // [nt][ws]
   float *bsh = sh + (((size_t)nt * ws + 3) & ~(size_t)3);  // [nb][16], row index fastest, 16-byte aligned
   for (int i = threadIdx.x; i < nt * nb; i += 256) wsh[(i / nb) * ws + (i % nb)] = w[i];
-  const int r0 = blockIdx.x * 16;
-  for (int i = threadIdx.x; i < 16 * nb; i += 256) {
-    int r = i / nb, j = i - r * nb;
-    bsh[j * 16 + r] = (r0 + r < rows) ? bands[(size_t)(r0 + r) * nb + j] : 0.0f;
-  }
-  __syncthreads();
-  for (int i = threadIdx.x; i < nt; i += 256) {
-    float acc[16];
-#pragma unroll
-    for (int r = 0; r < 16; ++r) acc[r] = 0.0f;
-    const float *wr = wsh + (size_t)i * ws;
-    for (int j = 0; j < nb; ++j) {
-      float wv = wr[j];
-      const float4 *bp = reinterpret_cast<const float4 *>(bsh + j * 16);
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        float4 v = bp[q];
-        acc[4 * q + 0] = fmaf(wv, v.x, acc[4 * q + 0]);
-        acc[4 * q + 1] = fmaf(wv, v.y, acc[4 * q + 1]);
-        acc[4 * q + 2] = fmaf(wv, v.z, acc[4 * q + 2]);
-        acc[4 * q + 3] = fmaf(wv, v.w, acc[4 * q + 3]);
-      }
+  for (int pass = 0; pass < BT_PASSES; ++pass) {
+    const int r0 = (blockIdx.x * BT_PASSES + pass) * 16;
+    if (r0 >= rows) break;
+    __syncthreads();
+    for (int i = threadIdx.x; i < 16 * nb; i += 256) {
+      int r = i / nb, j = i - r * nb;
+      bsh[j * 16 + r] = (r0 + r < rows) ? bands[(size_t)(r0 + r) * nb + j] : 0.0f;
     }
+    __syncthreads();
+    for (int i = threadIdx.x; i < nt; i += 256) {
+      float acc[16];
 #pragma unroll
-    for (int r = 0; r < 16; ++r)
-      if (r0 + r < rows) out[(size_t)(r0 + r) * nt + i] = acc[r];
+      for (int r = 0; r < 16; ++r) acc[r] = 0.0f;
+      const float *wr = wsh + (size_t)i * ws;
+      for (int j = 0; j < nb; ++j) {
+        float wv = wr[j];
+        const float4 *bp = reinterpret_cast<const float4 *>(bsh + j * 16);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          float4 v = bp[q];
+          acc[4 * q + 0] = fmaf(wv, v.x, acc[4 * q + 0]);
+          acc[4 * q + 1] = fmaf(wv, v.y, acc[4 * q + 1]);
+          acc[4 * q + 2] = fmaf(wv, v.z, acc[4 * q + 2]);
+          acc[4 * q + 3] = fmaf(wv, v.w, acc[4 * q + 3]);
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < 16; ++r)
+        if (r0 + r < rows) out[(size_t)(r0 + r) * nt + i] = acc[r];
+    }
   }
 }
 
@@ -236,7 +243,7 @@ DGC_EXPORT int32_t dgc_bands_to_taps(dgc_ctx *ctx, const float *bands_dev, const
   size_t smem = ((((size_t)taps * (nbands | 1) + 3) & ~(size_t)3) + (size_t)nbands * 16) * sizeof(float);
   DGC_REQUIRE(ctx, smem <= 200 * 1024, "taps*nbands too large for shared memory");
   DGC_CUDA(ctx, cudaFuncSetAttribute(bands_to_taps_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  bands_to_taps_kernel<<<dgc_div_up(rows, 16), 256, smem, ctx->stream>>>(bands_dev, w_dev, rows, nbands, taps,
+  bands_to_taps_kernel<<<dgc_div_up(rows, 16 * BT_PASSES), 256, smem, ctx->stream>>>(bands_dev, w_dev, rows, nbands, taps,
                                                                           taps_dev);
   DGC_LAUNCHED(ctx, "bands_to_taps");
   return DGC_OK;

@@ -40,8 +40,11 @@ __device__ __forceinline__ float phasor_step(float p, float inc) {
 // sampleRow position (Sources/DGen/Emit+RowSelection.swift:166-184)
 __device__ __forceinline__ void row_pos(float idx, int rows, int &lo, int &hi, float &fr) {
   float fr_rows = (float)rows;
-  float w = fmodf(idx, fr_rows);
-  if (w < 0.0f) w = __fadd_rn(w, fr_rows);
+  float w = idx;
+  if (!(idx >= 0.0f && idx < fr_rows)) {  // fmod is the identity inside [0, rows)
+    w = fmodf(idx, fr_rows);
+    if (w < 0.0f) w = __fadd_rn(w, fr_rows);
+  }
   float fl = floorf(w);
   float ce = fl + 1.0f;
   if (ce >= fr_rows) ce = 0.0f;
@@ -183,23 +186,70 @@ __global__ void anchor_seq_kernel(const float *__restrict__ f0t, int B, int T, i
   }
 }
 
-// SCAN anchors, stage 1: exact sum of the 64 increments of a chunk in Q0.64 (mod 1)
-__global__ void anchor_sum_kernel(const float *__restrict__ f0t, int B, int T, int K, float sr, float rsr,
-                                  unsigned long long *__restrict__ sums /* [B][C][K] */) {
-  int k = threadIdx.x, c = blockIdx.x, b = blockIdx.y;
-  if (k >= K) return;
-  const int C = gridDim.x;
-  const float kf = (float)(k + 1);
+// Exact conversion of a float in [0,1) to Q0.64 with integer operations (bits below 2^-64 dropped).
+__device__ __forceinline__ unsigned long long turns_to_q64(float v) {
+  unsigned u = __float_as_uint(v);
+  int e = (int)(u >> 23);                       // biased exponent (sign is 0)
+  if (e == 0) return 0ull;                      // zero / subnormal: below 2^-64 anyway
+  unsigned long long m = (unsigned long long)((u & 0x7fffffu) | 0x800000u);
+  int sh = e - 86;                              // value = m * 2^(e-150); Q0.64 = m * 2^(e-86)
+  return sh >= 0 ? (m << sh) : (sh > -24 ? (m >> (-sh)) : 0ull);
+}
+
+// SCAN anchors, stage 1: exact sum of the 64 increments of a chunk in Q0.64 (mod 1).
+// Same thread mapping as the render kernel: a group of LPC lanes owns one (voice, chunk), lane j
+// carries partials j, j+LPC, ... so the per-frame work (f0 load, loop) is shared by P partials.
+template <int LPC, int P>
+__global__ void __launch_bounds__(128)
+anchor_sum_kernel(const float *__restrict__ f0t, int B, int T, int K, float sr, float rsr,
+                  unsigned long long *__restrict__ sums /* [B][C][K] */) {
+  constexpr int G = 128 / LPC;
+  const int C = (T + CH - 1) / CH;
+  const int g = threadIdx.x / LPC, j = threadIdx.x % LPC;
+  const int c = blockIdx.x * G + g, b = blockIdx.y;
+  if (c >= C) return;
   const float *f = f0t + (size_t)b * T;
-  int n0 = c * CH, n1 = min(T, n0 + CH);
-  unsigned long long acc = 0ull;
+  const int n0 = c * CH, n1 = min(T, n0 + CH);
+  // Double-float accumulation (error-free two-sum per add): the 64 increments of a chunk are summed
+  // to ~2^-45 absolute, far below the 2^-25 spacing of the single-precision anchors, with plain
+  // FP32 adds; the chunk total is converted to Q0.64 once.
+  float hi[P], lo[P];
+#pragma unroll
+  for (int i = 0; i < P; ++i) hi[i] = lo[i] = 0.0f;
+  const float kmax = (float)K;
   for (int n = n0; n < n1; ++n) {
-    float inc = div_by_const(__fmul_rn(kf, f[n]), sr, rsr);
-    if (!(inc >= 0.0f && inc < 1.0f)) inc = inc - floorf(inc);
-    if (!(inc >= 0.0f && inc < 1.0f)) inc = 0.0f;  // non-finite or rounded up to 1
-    acc += __float2ull_rz(inc * 18446744073709551616.0f);
+    const float f0 = f[n];
+    const bool fast = f0 >= 0.0f && __fmul_rn(kmax, f0) < sr;
+#pragma unroll
+    for (int i = 0; i < P; ++i) {
+      float inc = div_by_const(__fmul_rn((float)(j + LPC * i + 1), f0), sr, rsr);
+      if (!fast) {
+        if (!(inc >= 0.0f && inc < 1.0f)) inc = inc - floorf(inc);
+        if (!(inc >= 0.0f && inc < 1.0f)) inc = 0.0f;  // non-finite or rounded up to 1
+      }
+      float s = __fadd_rn(hi[i], inc);
+      float bb = __fsub_rn(s, hi[i]);
+      float err = __fadd_rn(__fsub_rn(hi[i], __fsub_rn(s, bb)), __fsub_rn(inc, bb));
+      hi[i] = s;
+      lo[i] = __fadd_rn(lo[i], err);
+    }
   }
-  sums[((size_t)b * C + c) * K + k] = acc;
+  unsigned long long acc[P];
+#pragma unroll
+  for (int i = 0; i < P; ++i) {
+    // hi in [0, 64], |lo| tiny: total mod 1 in Q0.64 (two's-complement add handles a negative lo)
+    float ip = floorf(hi[i]);
+    unsigned long long q = turns_to_q64(__fsub_rn(hi[i], ip));
+    float al = fabsf(lo[i]);
+    unsigned long long ql = al < 1.0f ? turns_to_q64(al) : 0ull;
+    acc[i] = lo[i] < 0.0f ? q - ql : q + ql;
+  }
+  unsigned long long *o = sums + ((size_t)b * C + c) * K;
+#pragma unroll
+  for (int i = 0; i < P; ++i) {
+    int k = j + LPC * i;
+    if (k < K) o[k] = acc[i];
+  }
 }
 
 // SCAN anchors, stage 2: exclusive prefix over chunks; the fixed-point phase is rounded to float.
@@ -233,9 +283,9 @@ anchor_scan_kernel(const unsigned long long *__restrict__ sums, int B, int C, in
 
 // Render: a group of LPC lanes owns one (voice, chunk); lane j carries partials j, j+LPC, ...
 // (P per lane) through the 64 frames; per frame the group reduces sum(sin*masked) and sum(masked)
-// with shuffles; lane 0 stores four frames at a time.
+// with shuffles; results of four frames are collected in lanes 0..3 and stored as one float4.
 template <int LPC, int P>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, 4)
 harmonic_render_kernel(dgc_harmonic_params prm, float rsr, const float *__restrict__ play,
                        const float *__restrict__ f0, const float *__restrict__ uv,
                        const float *__restrict__ amps, const float *__restrict__ gain,
@@ -249,14 +299,13 @@ harmonic_render_kernel(dgc_harmonic_params prm, float rsr, const float *__restri
   const bool active = c < C;
   if (!active) c = C - 1;
   const int n0 = c * CH;
-  const float sr = prm.sample_rate, nyq = sr * 0.5f;
+  const float sr = prm.sample_rate, nyq = sr * 0.5f, kmax = (float)K;
 
-  float ph[P], kf[P], alo[P], ahi[P];
+  float ph[P], alo[P], ahi[P];
   const float *anc = anchors + ((size_t)b * C + c) * K;
 #pragma unroll
   for (int i = 0; i < P; ++i) {
     int k = j + LPC * i;
-    kf[i] = (float)(k + 1);
     ph[i] = k < K ? anc[k] : 0.0f;
     alo[i] = 0.0f;
     ahi[i] = 0.0f;
@@ -264,59 +313,109 @@ harmonic_render_kernel(dgc_harmonic_params prm, float rsr, const float *__restri
   int cur_lo = -1;
   float f0lo = 0, f0hi = 0, uvlo = 0, uvhi = 0, glo = 0, ghi = 0;
   float *dst = audio + (size_t)b * T;
+  float keep = 0.0f;
 
-  for (int s = 0; s < CH; s += 4) {
-    float val[4];
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      int n = min(n0 + s + u, T - 1);
-      int lo, hi;
-      float fr;
-      row_pos(play[n], F, lo, hi, fr);
-      if (lo != cur_lo) {
-        cur_lo = lo;
-        const float *rl = amps + ((size_t)lo * B + b) * K, *rh = amps + ((size_t)hi * B + b) * K;
-#pragma unroll
-        for (int i = 0; i < P; ++i) {
-          int k = j + LPC * i;
-          alo[i] = k < K ? rl[k] : 0.0f;
-          ahi[i] = k < K ? rh[k] : 0.0f;
-        }
-        f0lo = f0[(size_t)lo * B + b]; f0hi = f0[(size_t)hi * B + b];
-        uvlo = uv[(size_t)lo * B + b]; uvhi = uv[(size_t)hi * B + b];
-        glo = gain[(size_t)lo * B + b]; ghi = gain[(size_t)hi * B + b];
-      }
-      float omf = __fsub_rn(1.0f, fr);
-      float f0t = lerp_strict(omf, f0lo, fr, f0hi);
-      float s1 = 0.0f, s2 = 0.0f;
+#pragma unroll 1
+  for (int s = 0; s < CH; ++s) {
+    const int n = min(n0 + s, T - 1);
+    int lo, hi;
+    float fr;
+    row_pos(play[n], F, lo, hi, fr);
+    if (lo != cur_lo) {
+      cur_lo = lo;
+      const float *rl = amps + ((size_t)lo * B + b) * K, *rh = amps + ((size_t)hi * B + b) * K;
 #pragma unroll
       for (int i = 0; i < P; ++i) {
-        float freq = __fmul_rn(kf[i], f0t);
-        float a = fmaf(fr, ahi[i], omf * alo[i]);
+        int k = j + LPC * i;
+        alo[i] = k < K ? rl[k] : 0.0f;
+        ahi[i] = k < K ? rh[k] : 0.0f;
+      }
+      f0lo = f0[(size_t)lo * B + b]; f0hi = f0[(size_t)hi * B + b];
+      uvlo = uv[(size_t)lo * B + b]; uvhi = uv[(size_t)hi * B + b];
+      glo = gain[(size_t)lo * B + b]; ghi = gain[(size_t)hi * B + b];
+    }
+    const float omf = __fsub_rn(1.0f, fr);
+    const float f0t = lerp_strict(omf, f0lo, fr, f0hi);
+    const float oa = omf;
+    float s1 = 0.0f, s2 = 0.0f;
+    // one decision per frame instead of one per partial: all increments of this frame in [0,1)?
+    if (f0t >= 0.0f && __fmul_rn(kmax, f0t) < sr) {
+#pragma unroll
+      for (int i = 0; i < P; ++i) {
+        float freq = __fmul_rn((float)(j + LPC * i + 1), f0t);
+        float a = fmaf(fr, ahi[i], oa * alo[i]);
+        float m = freq < nyq ? a : 0.0f;
+        s2 += m;
+        s1 = fmaf(sin_turns(ph[i]), m, s1);
+        float next = __fadd_rn(ph[i], div_by_const(freq, sr, rsr));
+        ph[i] = next >= 1.0f ? __fadd_rn(next, -1.0f) : next;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < P; ++i) {
+        float freq = __fmul_rn((float)(j + LPC * i + 1), f0t);
+        float a = fmaf(fr, ahi[i], oa * alo[i]);
         float m = freq < nyq ? a : 0.0f;
         s2 += m;
         s1 = fmaf(sin_turns(ph[i]), m, s1);
         ph[i] = phasor_step(ph[i], div_by_const(freq, sr, rsr));
       }
-#pragma unroll
-      for (int off = LPC / 2; off > 0; off >>= 1) {
-        s1 += __shfl_xor_sync(0xffffffffu, s1, off);
-        s2 += __shfl_xor_sync(0xffffffffu, s2, off);
-      }
-      float gt = fmaf(fr, ghi, omf * glo), uvt = fmaf(fr, uvhi, omf * uvlo);
-      val[u] = s1 / (s2 + 1e-8f) * gt * uvt * prm.harmonic_scale;
     }
-    if (active && j == 0) {
-      int n = n0 + s;
-      if (n + 3 < T && ((((size_t)b * T + n) & 3) == 0) && !prm.accumulate) {
-        *reinterpret_cast<float4 *>(dst + n) = make_float4(val[0], val[1], val[2], val[3]);
-      } else {
 #pragma unroll
-        for (int u = 0; u < 4; ++u)
-          if (n + u < T) dst[n + u] = prm.accumulate ? dst[n + u] + val[u] : val[u];
+    for (int off = LPC / 2; off > 0; off >>= 1) {
+      s1 += __shfl_xor_sync(0xffffffffu, s1, off);
+      s2 += __shfl_xor_sync(0xffffffffu, s2, off);
+    }
+    const float gt = fmaf(fr, ghi, omf * glo), uvt = fmaf(fr, uvhi, omf * uvlo);
+    const float val = s1 / (s2 + 1e-8f) * gt * uvt * prm.harmonic_scale;
+    if (j == (s & 3)) keep = val;
+    if ((s & 3) == 3) {
+      // lanes 0..3 of the group hold frames s-3..s
+      const int base = threadIdx.x - j;  // first lane of this group within the warp is (base & 31)
+      float v1 = __shfl_sync(0xffffffffu, keep, (base & 31) + 1);
+      float v2 = __shfl_sync(0xffffffffu, keep, (base & 31) + 2);
+      float v3 = __shfl_sync(0xffffffffu, keep, (base & 31) + 3);
+      if (active && j == 0) {
+        int nn = n0 + s - 3;
+        if (nn + 3 < T && ((((size_t)b * T + nn) & 3) == 0) && !prm.accumulate) {
+          *reinterpret_cast<float4 *>(dst + nn) = make_float4(keep, v1, v2, v3);
+        } else {
+          float vv[4] = {keep, v1, v2, v3};
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            if (nn + u < T) dst[nn + u] = prm.accumulate ? dst[nn + u] + vv[u] : vv[u];
+        }
       }
     }
   }
+}
+
+template <int LPC, int P>
+void launch_anchor_sum_t(dgc_ctx *ctx, int B, int T, int K, int C, const float *f0t, float sr, float rsr,
+                         unsigned long long *sums) {
+  constexpr int G = 128 / LPC;
+  anchor_sum_kernel<LPC, P><<<dim3(dgc_div_up(C, G), B), 128, 0, ctx->stream>>>(f0t, B, T, K, sr, rsr, sums);
+}
+
+// lanes per (voice, chunk) group and partials per lane for K partials (K <= 512)
+#define DGC_PICK_GROUP(K, CALL)            \
+  do {                                     \
+    if ((K) <= 8) CALL(8, 1);              \
+    else if ((K) <= 16) CALL(8, 2);        \
+    else if ((K) <= 32) CALL(8, 4);        \
+    else if ((K) <= 64) CALL(8, 8);        \
+    else if ((K) <= 104) CALL(8, 13);      \
+    else if ((K) <= 112) CALL(16, 7);      \
+    else if ((K) <= 128) CALL(16, 8);      \
+    else if ((K) <= 256) CALL(32, 8);      \
+    else CALL(32, 16);                     \
+  } while (0)
+
+void launch_anchor_sum(dgc_ctx *ctx, int B, int T, int K, int C, const float *f0t, float sr, float rsr,
+                       unsigned long long *sums) {
+#define CALL_SUM(LPC, P) launch_anchor_sum_t<LPC, P>(ctx, B, T, K, C, f0t, sr, rsr, sums)
+  DGC_PICK_GROUP(K, CALL_SUM);
+#undef CALL_SUM
 }
 
 template <int LPC, int P>
@@ -433,20 +532,13 @@ DGC_EXPORT int32_t dgc_harmonic_render(dgc_ctx *ctx, const dgc_harmonic_params *
     anchor_seq_kernel<<<dgc_div_up(B * K, 32), 32, 0, ctx->stream>>>(f0t, B, T, K, sr, rsr, anchors);
     DGC_LAUNCHED(ctx, "anchor_seq");
   } else {
-    anchor_sum_kernel<<<dim3(C, B), ((K + 31) / 32) * 32, 0, ctx->stream>>>(f0t, B, T, K, sr, rsr, sums);
+    launch_anchor_sum(ctx, B, T, K, C, f0t, sr, rsr, sums);
     DGC_LAUNCHED(ctx, "anchor_sum");
     anchor_scan_kernel<<<dim3(dgc_div_up(K, 32), B), 1024, 0, ctx->stream>>>(sums, B, C, K, anchors);
     DGC_LAUNCHED(ctx, "anchor_scan");
   }
 #define RENDER(LPC, P) launch_render<LPC, P>(ctx, *p, play, f0_dev, uv_dev, amps_dev, gain_dev, anchors, audio_dev)
-  if (K <= 8) RENDER(8, 1);
-  else if (K <= 16) RENDER(8, 2);
-  else if (K <= 32) RENDER(8, 4);
-  else if (K <= 64) RENDER(8, 8);
-  else if (K <= 104) RENDER(8, 13);
-  else if (K <= 128) RENDER(8, 16);
-  else if (K <= 256) RENDER(16, 16);
-  else RENDER(32, 16);
+  DGC_PICK_GROUP(K, RENDER);
 #undef RENDER
   DGC_LAUNCHED(ctx, "harmonic_render");
   return DGC_OK;
