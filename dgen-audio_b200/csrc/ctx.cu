@@ -92,6 +92,47 @@ const float *dgc_ctx_hann_per(dgc_ctx *ctx, int N) {
   return d;
 }
 
+// Frame ranges per control row, derived once per (F, T) from the cached control clock: the clock is
+// data independent, so which frames interpolate from row r is a static table (like a window).
+const int *dgc_ctx_row_ranges(dgc_ctx *ctx, int F, int T) {
+  auto key = std::make_pair(F, T);
+  auto it = ctx->row_ranges.find(key);
+  if (it != ctx->row_ranges.end()) return it->second;
+  const float *play_dev = nullptr;
+  if (dgc_playhead(ctx, F, T, &play_dev) != DGC_OK) return nullptr;
+  std::vector<float> play(T);
+  if (cudaStreamSynchronize(ctx->stream) != cudaSuccess ||
+      cudaMemcpy(play.data(), play_dev, (size_t)T * sizeof(float), cudaMemcpyDeviceToHost) != cudaSuccess) {
+    dgc_fail(ctx, DGC_ERR_CUDA, "row_ranges: reading the control clock failed");
+    return nullptr;
+  }
+  std::vector<int> tab((size_t)F * 4, 0);
+  std::vector<int> runs(F, 0);
+  int n = 0;
+  while (n < T) {
+    float w = fmodf(play[n], (float)F);
+    if (w < 0) w += (float)F;
+    int lo = (int)floorf(w), e = n + 1;
+    while (e < T) {
+      float w2 = fmodf(play[e], (float)F);
+      if (w2 < 0) w2 += (float)F;
+      if ((int)floorf(w2) != lo) break;
+      ++e;
+    }
+    if (lo < 0 || lo >= F || runs[lo] >= 2) {
+      dgc_fail(ctx, DGC_ERR_UNSUPPORTED, "row_ranges: control row %d is visited in more than two runs", lo);
+      return nullptr;
+    }
+    tab[(size_t)lo * 4 + 2 * runs[lo]] = n;
+    tab[(size_t)lo * 4 + 2 * runs[lo] + 1] = e;
+    runs[lo]++;
+    n = e;
+  }
+  int *d = upload_table(ctx, tab);
+  if (d) ctx->row_ranges[key] = d;
+  return d;
+}
+
 const float2 *dgc_ctx_twiddles(dgc_ctx *ctx, int N) {
   auto it = ctx->twiddles.find(N);
   if (it != ctx->twiddles.end()) return it->second;
@@ -138,6 +179,7 @@ DGC_EXPORT int32_t dgc_ctx_destroy(dgc_ctx *c) {
   cudaSetDevice(c->device);
   if (c->stream) cudaStreamSynchronize(c->stream);
   for (auto &kv : c->playheads) cudaFree(kv.second);
+  for (auto &kv : c->row_ranges) cudaFree(kv.second);
   for (auto &kv : c->hann_sym) cudaFree(kv.second);
   for (auto &kv : c->hann_per) cudaFree(kv.second);
   for (auto &kv : c->twiddles) cudaFree(kv.second);

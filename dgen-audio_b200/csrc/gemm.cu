@@ -1,0 +1,200 @@
+// Controller layers and optimiser: dense fp32 matmul (+ bias, tanh), its backward, and Adam.
+//
+// The reference expresses a layer as mul + sumAxis over a broadcast [M,N,K] product on the C backend
+// and as 8x8 simdgroup tiles on Metal (Sources/DGen/Tensor.swift:1195-1230, Sources/DGen/Emit+GEMM.swift);
+// parameters live on the host and Adam is a per-element Swift loop (Sources/DGenLazy/Optimizers.swift:164-243).
+// Here activations, weights, gradients and optimiser state stay in HBM; the matmul is a register-tiled
+// SIMT kernel in full fp32 (the gradient tolerance of the path, 1e-3 relative against an fp64
+// evaluation, leaves no room for single-pass TF32).
+#include "common.cuh"
+
+namespace {
+
+// C[M][N] (+)= op(A) * op(B) with 128x128 block tiles, 8-deep k-slices, 8x8 register tiles per thread.
+// TA: A is stored [K][M] (use A^T);  TB: B is stored [N][K] (use B^T).
+constexpr int BM = 128, BN = 128, BK = 8, TM = 8, TN = 8;
+
+// EPI 0: C = acc ; 1: C = acc + bias[n] ; 2: C = tanh(acc + bias[n])
+template <bool TA, bool TB, int EPI>
+__global__ void __launch_bounds__(256)
+sgemm_kernel(const float *__restrict__ A, const float *__restrict__ B, const float *__restrict__ bias, int M, int N,
+             int K, float *__restrict__ C) {
+  __shared__ float As[BK][BM + 4];
+  __shared__ float Bs[BK][BN + 4];
+  const int tid = threadIdx.x;
+  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  const int tx = tid % 16, ty = tid / 16;  // 16 x 16 threads, each 8 x 8 outputs
+  float acc[TM][TN];
+#pragma unroll
+  for (int i = 0; i < TM; ++i)
+#pragma unroll
+    for (int j = 0; j < TN; ++j) acc[i][j] = 0.0f;
+
+  for (int k0 = 0; k0 < K; k0 += BK) {
+    // stage A tile [BM][BK] and B tile [BK][BN]: 1024 elements each, 4 per thread
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      int idx = tid + e * 256;
+      if (!TA) {  // A stored [M][K]: consecutive idx walk k fastest
+        int m = idx / BK, k = idx % BK;
+        int gm = m0 + m, gk = k0 + k;
+        As[k][m] = (gm < M && gk < K) ? A[(size_t)gm * K + gk] : 0.0f;
+      } else {    // A stored [K][M]: consecutive idx walk m fastest
+        int k = idx / BM, m = idx % BM;
+        int gm = m0 + m, gk = k0 + k;
+        As[k][m] = (gm < M && gk < K) ? A[(size_t)gk * M + gm] : 0.0f;
+      }
+      if (!TB) {  // B stored [K][N]
+        int k = idx / BN, n = idx % BN;
+        int gn = n0 + n, gk = k0 + k;
+        Bs[k][n] = (gn < N && gk < K) ? B[(size_t)gk * N + gn] : 0.0f;
+      } else {    // B stored [N][K]
+        int n = idx / BK, k = idx % BK;
+        int gn = n0 + n, gk = k0 + k;
+        Bs[k][n] = (gn < N && gk < K) ? B[(size_t)gn * K + gk] : 0.0f;
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < BK; ++k) {
+      float a[TM], b[TN];
+#pragma unroll
+      for (int i = 0; i < TM; i += 4) {
+        float4 v = *reinterpret_cast<const float4 *>(&As[k][ty * 4 + i * 16]);  // rows ty*4 + {0..3} + i*16... see below
+        a[i] = v.x; a[i + 1] = v.y; a[i + 2] = v.z; a[i + 3] = v.w;
+      }
+#pragma unroll
+      for (int j = 0; j < TN; j += 4) {
+        float4 v = *reinterpret_cast<const float4 *>(&Bs[k][tx * 4 + j * 16]);
+        b[j] = v.x; b[j + 1] = v.y; b[j + 2] = v.z; b[j + 3] = v.w;
+      }
+#pragma unroll
+      for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+  // thread (ty, tx) owns rows m0 + ty*4 + {0..3} and m0 + 64 + ty*4 + {0..3}; same pattern for columns
+#pragma unroll
+  for (int i = 0; i < TM; ++i) {
+    int gm = m0 + ty * 4 + (i & 3) + (i >> 2) * 64;
+    if (gm >= M) continue;
+#pragma unroll
+    for (int j = 0; j < TN; ++j) {
+      int gn = n0 + tx * 4 + (j & 3) + (j >> 2) * 64;
+      if (gn >= N) continue;
+      float v = acc[i][j];
+      if (EPI >= 1) v += bias[gn];
+      if (EPI == 2) v = tanhf(v);
+      C[(size_t)gm * N + gn] = v;
+    }
+  }
+}
+
+template <bool TA, bool TB, int EPI>
+void launch_sgemm(dgc_ctx *ctx, const float *A, const float *B, const float *bias, int M, int N, int K, float *C) {
+  dim3 grid(dgc_div_up(N, BN), dgc_div_up(M, BM));
+  sgemm_kernel<TA, TB, EPI><<<grid, 256, 0, ctx->stream>>>(A, B, bias, M, N, K, C);
+}
+
+// dZ = dC * (1 - C^2) in place-compatible form (tanh'), or copy when act == 0
+__global__ void act_bwd_kernel(const float *__restrict__ dC, const float *__restrict__ Cv, size_t n, int act,
+                               float *__restrict__ dZ) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float g = dC[i];
+  if (act == 1) {
+    float c = Cv[i];
+    g *= (1.0f - c * c);
+  }
+  dZ[i] = g;
+}
+
+// db[n] = sum_m dZ[m][n]: block per 32 columns, fixed-order tree -> bit-reproducible
+__global__ void __launch_bounds__(256)
+bias_grad_kernel(const float *__restrict__ dZ, int M, int N, float *__restrict__ db) {
+  __shared__ float sh[8][33];
+  const int col = blockIdx.x * 32 + (threadIdx.x & 31), rg = threadIdx.x >> 5;
+  float acc = 0.0f;
+  if (col < N)
+    for (int m = rg; m < M; m += 8) acc += dZ[(size_t)m * N + col];
+  sh[rg][threadIdx.x & 31] = acc;
+  __syncthreads();
+  if (rg == 0 && col < N) {
+    float t = 0.0f;
+#pragma unroll
+    for (int r = 0; r < 8; ++r) t += sh[r][threadIdx.x & 31];
+    db[col] = t;
+  }
+}
+
+__global__ void adam_kernel(float *__restrict__ theta, const float *__restrict__ g, float *__restrict__ m,
+                            float *__restrict__ v, size_t n, float lr, float b1, float b2, float eps, float c1,
+                            float c2) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  // operation order of Optimizers.swift:188-203
+  float gi = g[i];
+  float mi = __fadd_rn(__fmul_rn(b1, m[i]), __fmul_rn(1.0f - b1, gi));
+  float vi = __fadd_rn(__fmul_rn(b2, v[i]), __fmul_rn(__fmul_rn(1.0f - b2, gi), gi));
+  m[i] = mi;
+  v[i] = vi;
+  float mh = __fdiv_rn(mi, c1), vh = __fdiv_rn(vi, c2);
+  theta[i] = __fsub_rn(theta[i], __fdiv_rn(__fmul_rn(lr, mh), __fadd_rn(__fsqrt_rn(vh), eps)));
+}
+
+}  // namespace
+
+DGC_EXPORT int32_t dgc_linear_fwd(dgc_ctx *ctx, const float *a_dev, const float *w_dev, const float *bias_dev,
+                                  int32_t M, int32_t K, int32_t N, int32_t act, float *c_dev) {
+  if (!ctx) return DGC_ERR_INVALID;
+  DGC_REQUIRE(ctx, a_dev && w_dev && c_dev, "null pointer");
+  DGC_REQUIRE(ctx, M > 0 && K > 0 && N > 0, "size out of range");
+  DGC_REQUIRE(ctx, act == 0 || act == 1, "act must be 0 (none) or 1 (tanh)");
+  DGC_REQUIRE(ctx, act == 0 || bias_dev, "tanh layers need a bias");
+  if (act == 1) launch_sgemm<false, false, 2>(ctx, a_dev, w_dev, bias_dev, M, N, K, c_dev);
+  else if (bias_dev) launch_sgemm<false, false, 1>(ctx, a_dev, w_dev, bias_dev, M, N, K, c_dev);
+  else launch_sgemm<false, false, 0>(ctx, a_dev, w_dev, nullptr, M, N, K, c_dev);
+  DGC_LAUNCHED(ctx, "linear_fwd");
+  return DGC_OK;
+}
+
+DGC_EXPORT int32_t dgc_linear_bwd(dgc_ctx *ctx, const float *a_dev, const float *w_dev, const float *c_dev,
+                                  const float *dc_dev, int32_t M, int32_t K, int32_t N, int32_t act, float *dz_dev,
+                                  float *da_dev, float *dw_dev, float *dbias_dev) {
+  if (!ctx) return DGC_ERR_INVALID;
+  DGC_REQUIRE(ctx, a_dev && w_dev && dc_dev && dz_dev && dw_dev, "null pointer");
+  DGC_REQUIRE(ctx, M > 0 && K > 0 && N > 0, "size out of range");
+  DGC_REQUIRE(ctx, act == 0 || (act == 1 && c_dev), "tanh backward needs the layer output");
+  const size_t n = (size_t)M * N;
+  act_bwd_kernel<<<dgc_div_up((int64_t)n, 256), 256, 0, ctx->stream>>>(dc_dev, c_dev, n, act, dz_dev);
+  DGC_LAUNCHED(ctx, "act_bwd");
+  if (dbias_dev) {
+    bias_grad_kernel<<<dgc_div_up(N, 32), 256, 0, ctx->stream>>>(dz_dev, M, N, dbias_dev);
+    DGC_LAUNCHED(ctx, "bias_grad");
+  }
+  // dW[K][N] = A^T[K][M] * dZ[M][N]
+  launch_sgemm<true, false, 0>(ctx, a_dev, dz_dev, nullptr, K, N, M, dw_dev);
+  DGC_LAUNCHED(ctx, "linear_bwd_dw");
+  if (da_dev) {
+    // dA[M][K] = dZ[M][N] * W^T[N][K]
+    launch_sgemm<false, true, 0>(ctx, dz_dev, w_dev, nullptr, M, K, N, da_dev);
+    DGC_LAUNCHED(ctx, "linear_bwd_da");
+  }
+  return DGC_OK;
+}
+
+DGC_EXPORT int32_t dgc_adam_step(dgc_ctx *ctx, float *theta_dev, const float *grad_dev, float *m_dev, float *v_dev,
+                                 uint64_t n, int32_t t, float lr, float beta1, float beta2, float eps) {
+  if (!ctx) return DGC_ERR_INVALID;
+  DGC_REQUIRE(ctx, theta_dev && grad_dev && m_dev && v_dev, "null pointer");
+  DGC_REQUIRE(ctx, t >= 1, "t is the 1-based step index");
+  if (n == 0) return DGC_OK;
+  // bias corrections as the reference computes them: 1 - pow(beta, Float(t)) in single precision
+  float c1 = 1.0f - powf(beta1, (float)t), c2 = 1.0f - powf(beta2, (float)t);
+  adam_kernel<<<dgc_div_up((int64_t)n, 256), 256, 0, ctx->stream>>>(theta_dev, grad_dev, m_dev, v_dev, n, lr, beta1,
+                                                                    beta2, eps, c1, c2);
+  DGC_LAUNCHED(ctx, "adam");
+  return DGC_OK;
+}

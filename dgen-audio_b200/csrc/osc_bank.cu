@@ -10,58 +10,11 @@
 //               the state every 64 frames: bit-identical to the reference, latency bound;
 //   SCAN        every (voice, partial, chunk) sums its 64 increments exactly in 64-bit fixed point,
 //               a second kernel prefix-sums the chunk totals: frame-parallel.
-#include "common.cuh"
+#include "osc_common.cuh"
 
 namespace {
 
-constexpr int CH = 64;            // frames per phase chunk
-constexpr float TWO_PI_F = 6.2831850051879883f;  // Float(2*Float.pi) of the reference graphs
-
-// a / b for a fixed b with r = RN(1/b): q + fma(-q, b, a) * r is the correctly rounded quotient
-// (checked exhaustively on the host for the common sample rates, a in [1e-3, 2e6]).
-__device__ __forceinline__ float div_by_const(float a, float b, float r) {
-  float q = __fmul_rn(a, r);
-  float rem = __fmaf_rn(-q, b, a);
-  return __fmaf_rn(rem, r, q);
-}
-
-// One step of the reference recurrence: next = p + inc ; w = next - floor(next) ; if (w >= 1) w -= 1.
-__device__ __forceinline__ float phasor_step(float p, float inc) {
-  float next = __fadd_rn(p, inc);
-  if (inc >= 0.0f && inc < 1.0f) {
-    // p in [0,1) and inc in [0,1): next in [0,2), floor is 0 or 1 and next-1 is exact
-    float t = __fadd_rn(next, -1.0f);
-    return next >= 1.0f ? t : next;
-  }
-  float w = __fsub_rn(next, floorf(next));
-  return w >= 1.0f ? __fadd_rn(w, -1.0f) : w;
-}
-
-// sampleRow position (Sources/DGen/Emit+RowSelection.swift:166-184)
-__device__ __forceinline__ void row_pos(float idx, int rows, int &lo, int &hi, float &fr) {
-  float fr_rows = (float)rows;
-  float w = idx;
-  if (!(idx >= 0.0f && idx < fr_rows)) {  // fmod is the identity inside [0, rows)
-    w = fmodf(idx, fr_rows);
-    if (w < 0.0f) w = __fadd_rn(w, fr_rows);
-  }
-  float fl = floorf(w);
-  float ce = fl + 1.0f;
-  if (ce >= fr_rows) ce = 0.0f;
-  lo = (int)fl;
-  hi = (int)ce;
-  fr = __fsub_rn(w, fl);
-}
-
-__device__ __forceinline__ float lerp_strict(float omf, float a, float fr, float b) {
-  return __fadd_rn(__fmul_rn(omf, a), __fmul_rn(fr, b));
-}
-
-// sin(2*pi*p) for p in [0,1): centre to [-pi, pi) where the fast sine's absolute error is 2^-21.4
-__device__ __forceinline__ float sin_turns(float p) {
-  float c = p >= 0.5f ? p - 1.0f : p;
-  return __sinf(c * TWO_PI_F);
-}
+using namespace dgosc;
 
 // ---------------------------------------------------------------------------------------------
 // scalar accum clock, one thread (Sources/DGen/Definitions.swift:215-246)
@@ -504,28 +457,23 @@ DGC_EXPORT uint64_t dgc_harmonic_scratch_floats(const dgc_harmonic_params *p) {
   return (((uint64_t)p->B * p->T + 3) & ~3ull) + lanes + 2 * lanes + 8;
 }
 
-DGC_EXPORT int32_t dgc_harmonic_render(dgc_ctx *ctx, const dgc_harmonic_params *p, const float *f0_dev,
-                                       const float *uv_dev, const float *amps_dev, const float *gain_dev,
-                                       float *scratch_dev, float *audio_dev) {
-  if (!ctx) return DGC_ERR_INVALID;
-  DGC_REQUIRE(ctx, p && f0_dev && uv_dev && amps_dev && gain_dev && audio_dev, "null pointer");
+int32_t dgc_harmonic_prepare(dgc_ctx *ctx, const dgc_harmonic_params *p, const float *f0_dev, float *scratch,
+                             const float **play_out, const float **anchors_out) {
   DGC_REQUIRE(ctx, p->B > 0 && p->T > 0 && p->F > 0 && p->K > 0 && p->K <= 512, "size out of range (K <= 512)");
+  DGC_REQUIRE(ctx, p->B <= 65535, "B must be <= 65535");
   DGC_REQUIRE(ctx, p->sample_rate > 0, "sample rate must be positive");
   DGC_REQUIRE(ctx, p->phase_mode == DGC_PHASE_SEQUENTIAL || p->phase_mode == DGC_PHASE_SCAN, "phase mode");
+  DGC_REQUIRE(ctx, (((uintptr_t)scratch) & 15) == 0, "scratch must be 16-byte aligned");
   const int B = p->B, T = p->T, K = p->K, F = p->F;
   const int C = dgc_div_up(T, CH);
   const float *play = nullptr;
   int32_t rc = dgc_playhead(ctx, F, T, &play);
   if (rc != DGC_OK) return rc;
-  float *scratch = scratch_dev ? scratch_dev : dgc_ctx_scratch(ctx, dgc_harmonic_scratch_floats(p));
-  if (!scratch) return DGC_ERR_OOM;
-  DGC_REQUIRE(ctx, (((uintptr_t)scratch) & 15) == 0, "scratch must be 16-byte aligned");
   float *f0t = scratch;
   float *anchors = scratch + (((uint64_t)B * T + 3) & ~3ull);
   uint64_t lanes = (uint64_t)B * C * K;
   unsigned long long *sums = reinterpret_cast<unsigned long long *>(anchors + ((lanes + 1) & ~1ull));
   const float sr = p->sample_rate, rsr = 1.0f / sr;
-
   f0_track_kernel<<<dim3(dgc_div_up(T, 256), B), 256, 0, ctx->stream>>>(play, f0_dev, B, T, F, f0t);
   DGC_LAUNCHED(ctx, "f0_track");
   if (p->phase_mode == DGC_PHASE_SEQUENTIAL) {
@@ -537,6 +485,22 @@ DGC_EXPORT int32_t dgc_harmonic_render(dgc_ctx *ctx, const dgc_harmonic_params *
     anchor_scan_kernel<<<dim3(dgc_div_up(K, 32), B), 1024, 0, ctx->stream>>>(sums, B, C, K, anchors);
     DGC_LAUNCHED(ctx, "anchor_scan");
   }
+  *play_out = play;
+  *anchors_out = anchors;
+  return DGC_OK;
+}
+
+DGC_EXPORT int32_t dgc_harmonic_render(dgc_ctx *ctx, const dgc_harmonic_params *p, const float *f0_dev,
+                                       const float *uv_dev, const float *amps_dev, const float *gain_dev,
+                                       float *scratch_dev, float *audio_dev) {
+  if (!ctx) return DGC_ERR_INVALID;
+  DGC_REQUIRE(ctx, p && f0_dev && uv_dev && amps_dev && gain_dev && audio_dev, "null pointer");
+  float *scratch = scratch_dev ? scratch_dev : dgc_ctx_scratch(ctx, dgc_harmonic_scratch_floats(p));
+  if (!scratch) return DGC_ERR_OOM;
+  const float *play = nullptr, *anchors = nullptr;
+  int32_t rc = dgc_harmonic_prepare(ctx, p, f0_dev, scratch, &play, &anchors);
+  if (rc != DGC_OK) return rc;
+  const int K = p->K;
 #define RENDER(LPC, P) launch_render<LPC, P>(ctx, *p, play, f0_dev, uv_dev, amps_dev, gain_dev, anchors, audio_dev)
   DGC_PICK_GROUP(K, RENDER);
 #undef RENDER

@@ -1,0 +1,62 @@
+// Device helpers shared by the oscillator-bank forward and backward kernels: the reference's phasor
+// recurrence, exact division by the sample rate, sampleRow positions, the centred fast sine.
+#pragma once
+#include "common.cuh"
+
+namespace dgosc {
+
+constexpr int CH = 64;            // frames per phase chunk
+constexpr float TWO_PI_F = 6.2831850051879883f;  // Float(2*Float.pi) of the reference graphs
+
+// a / b for a fixed b with r = RN(1/b): q + fma(-q, b, a) * r is the correctly rounded quotient
+// (checked exhaustively on the host for the common sample rates, a in [1e-3, 2e6]).
+__device__ __forceinline__ float div_by_const(float a, float b, float r) {
+  float q = __fmul_rn(a, r);
+  float rem = __fmaf_rn(-q, b, a);
+  return __fmaf_rn(rem, r, q);
+}
+
+// One step of the reference recurrence: next = p + inc ; w = next - floor(next) ; if (w >= 1) w -= 1.
+__device__ __forceinline__ float phasor_step(float p, float inc) {
+  float next = __fadd_rn(p, inc);
+  if (inc >= 0.0f && inc < 1.0f) {
+    // p in [0,1) and inc in [0,1): next in [0,2), floor is 0 or 1 and next-1 is exact
+    float t = __fadd_rn(next, -1.0f);
+    return next >= 1.0f ? t : next;
+  }
+  float w = __fsub_rn(next, floorf(next));
+  return w >= 1.0f ? __fadd_rn(w, -1.0f) : w;
+}
+
+// sampleRow position (Sources/DGen/Emit+RowSelection.swift:166-184)
+__device__ __forceinline__ void row_pos(float idx, int rows, int &lo, int &hi, float &fr) {
+  float fr_rows = (float)rows;
+  float w = idx;
+  if (!(idx >= 0.0f && idx < fr_rows)) {  // fmod is the identity inside [0, rows)
+    w = fmodf(idx, fr_rows);
+    if (w < 0.0f) w = __fadd_rn(w, fr_rows);
+  }
+  float fl = floorf(w);
+  float ce = fl + 1.0f;
+  if (ce >= fr_rows) ce = 0.0f;
+  lo = (int)fl;
+  hi = (int)ce;
+  fr = __fsub_rn(w, fl);
+}
+
+__device__ __forceinline__ float lerp_strict(float omf, float a, float fr, float b) {
+  return __fadd_rn(__fmul_rn(omf, a), __fmul_rn(fr, b));
+}
+
+// sin(2*pi*p) for p in [0,1): centre to [-pi, pi) where the fast sine's absolute error is 2^-21.4
+__device__ __forceinline__ float sin_turns(float p) {
+  float c = p >= 0.5f ? p - 1.0f : p;
+  return __sinf(c * TWO_PI_F);
+}
+
+}  // namespace dgosc
+
+// Runs the per-sample fundamental track and the phase-anchor kernels for `p` into `scratch`
+// (dgc_harmonic_scratch_floats(p) floats); returns the control clock and the anchors [B][C][K].
+int32_t dgc_harmonic_prepare(dgc_ctx *ctx, const dgc_harmonic_params *p, const float *f0_dev, float *scratch,
+                             const float **play_out, const float **anchors_out);

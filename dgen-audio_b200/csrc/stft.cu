@@ -20,6 +20,8 @@ constexpr int ST_THREADS = 256;
 // Pair p of transform slot holds real sequences (2p, 2p+1) of one signal v as re / im.
 // SRC 0: bufferView windows of x[v]: element i of hop frame h = x[h*hop - (N-1) + i] * window[i]
 // SRC 1: zero-padded partitions of one IR: element i of partition h = ir[h*hop + i], i < hop
+// SRC 2: overlap-add aligned frames of x[v]: element i of hop frame h = x[h*hop + i] * window[i]
+//        (the adjoint of the overlap-add scatter, used by the backward pass)
 // OUT 0: magnitudes [V][H][N/2+1]     OUT 1: half spectra float2 [V][H][N/2+1]
 template <int N, int SRC, int OUT>
 __global__ void __launch_bounds__(ST_THREADS)
@@ -37,16 +39,20 @@ stft_kernel(const float *__restrict__ x, int T, int hop, int H, const float *__r
 #pragma unroll
   for (int q = 0; q < 8; ++q) {
     int i = lt + q * G;
-    float w = (SRC == 0 && window) ? __ldg(&window[i]) : 1.0f;
+    float w = (SRC != 1 && window) ? __ldg(&window[i]) : 1.0f;
     float2 val = make_float2(0.f, 0.f);
     if (SRC == 0) {
       int t0 = h0 * hop - (N - 1) + i, t1 = h1 * hop - (N - 1) + i;
       if (h0 < H && t0 >= 0 && t0 < T) val.x = xv[t0] * w;
       if (h1 < H && t1 >= 0 && t1 < T) val.y = xv[t1] * w;
-    } else {
+    } else if (SRC == 1) {
       int t0 = h0 * hop + i, t1 = h1 * hop + i;
       if (h0 < H && i < hop && t0 < T) val.x = xv[t0];
       if (h1 < H && i < hop && t1 < T) val.y = xv[t1];
+    } else {
+      int t0 = h0 * hop + i, t1 = h1 * hop + i;
+      if (h0 < H && t0 < T) val.x = xv[t0] * w;
+      if (h1 < H && t1 < T) val.y = xv[t1] * w;
     }
     a[i] = val;
   }
@@ -152,24 +158,107 @@ istft_kernel(const float2 *__restrict__ Y, int H, const float *__restrict__ wind
 #pragma unroll
   for (int q = 0; q < 8; ++q) {
     int i = lt + q * G;
-    float w = __ldg(&window[i]);
+    float w = window ? __ldg(&window[i]) : 1.0f;
     float2 val = z[i];
     if (h0 < H) frames[((size_t)v * H + h0) * N + i] = ((val.x * invn) * w) * gain;
     if (h1 < H) frames[((size_t)v * H + h1) * N + i] = ((val.y * invn) * w) * gain;
   }
 }
 
-// out[v][t] = sum over hops h with h*hop <= t < h*hop + N of frames[v][h][t - h*hop], oldest first
-__global__ void overlap_add_kernel(const float *__restrict__ frames, int T, int N, int hop, int H,
-                                   float *__restrict__ out) {
+// out[v][t] (+)= sum over hops h with 0 <= t - h*hop - offset < N of frames[v][h][t - h*hop - offset],
+// oldest first.  offset 0: the forward overlap-add; offset -(N-1): the adjoint of the bufferView gather.
+__global__ void overlap_add_kernel(const float *__restrict__ frames, int T, int N, int hop, int H, int offset,
+                                   int accumulate, float *__restrict__ out) {
   int t = blockIdx.x * blockDim.x + threadIdx.x, v = blockIdx.y;
   if (t >= T) return;
-  int hmax = min(H - 1, t / hop);
-  int hmin = max(0, (t - N) / hop + 1);
-  if (t - N < 0) hmin = 0;
+  int u = t - offset;            // frame h covers u in [h*hop, h*hop + N)
+  int hmax = min(H - 1, u / hop);
+  int hmin = u - N < 0 ? 0 : (u - N) / hop + 1;
   float acc = 0.0f;
-  for (int h = hmin; h <= hmax; ++h) acc += frames[((size_t)v * H + h) * N + (t - h * hop)];
-  out[(size_t)v * T + t] = acc;
+  for (int h = hmin; h <= hmax; ++h) acc += frames[((size_t)v * H + h) * N + (u - h * hop)];
+  size_t o = (size_t)v * T + t;
+  out[o] = accumulate ? out[o] + acc : acc;
+}
+
+// V[v][m][k] = sum_{j < K, m + j < H} conj(Hs[j][k]) * U[v][m+j][k]: adjoint of the partitioned MAC
+__global__ void __launch_bounds__(256)
+partconv_mac_adj_kernel(const float2 *__restrict__ U, const float2 *__restrict__ Hs, int H, int K, int NB,
+                        float2 *__restrict__ V) {
+  extern __shared__ float2 smem[];
+  float2 *hs = smem;                          // [K][MAC_BINS]
+  float2 *us = smem + (size_t)K * MAC_BINS;   // [MAC_HT + K - 1][MAC_BINS], row r <-> hop hb + r
+  const int kb = blockIdx.x * MAC_BINS, hb = blockIdx.y * MAC_HT, v = blockIdx.z;
+  const int bin = threadIdx.x & 31, hg = threadIdx.x >> 5;
+  for (int i = threadIdx.x; i < K * MAC_BINS; i += 256) {
+    int j = i / MAC_BINS, kk = i % MAC_BINS;
+    hs[i] = (kb + kk < NB) ? Hs[(size_t)j * NB + kb + kk] : make_float2(0.f, 0.f);
+  }
+  const int rows = MAC_HT + K - 1;
+  for (int i = threadIdx.x; i < rows * MAC_BINS; i += 256) {
+    int r = i / MAC_BINS, kk = i % MAC_BINS;
+    int h = hb + r;
+    us[i] = (h < H && kb + kk < NB) ? U[((size_t)v * H + h) * NB + kb + kk] : make_float2(0.f, 0.f);
+  }
+  __syncthreads();
+  float2 acc[MAC_HPT];
+#pragma unroll
+  for (int u = 0; u < MAC_HPT; ++u) acc[u] = make_float2(0.f, 0.f);
+  const int rbase = hg * MAC_HPT;  // hop m = hb + rbase + u reads row rbase + u + j
+  for (int j = 0; j < K; ++j) {
+    float2 hv = hs[(size_t)j * MAC_BINS + bin];
+#pragma unroll
+    for (int u = 0; u < MAC_HPT; ++u) {
+      float2 x = us[(size_t)(rbase + u + j) * MAC_BINS + bin];
+      acc[u].x += x.x * hv.x + x.y * hv.y;   // conj(h) * x
+      acc[u].y += x.y * hv.x - x.x * hv.y;
+    }
+  }
+  if (kb + bin < NB) {
+#pragma unroll
+    for (int u = 0; u < MAC_HPT; ++u) {
+      int m = hb + rbase + u;
+      if (m < H) V[((size_t)v * H + m) * NB + kb + bin] = acc[u];
+    }
+  }
+}
+
+// G[k][bin] = sum_v sum_h conj(X[v][h-k][bin]) * U[v][h][bin]: gradient of the IR partition spectra.
+// block = (32 bins, partition k); 8 thread groups split the (voice, hop) sum, combined in fixed order.
+__global__ void __launch_bounds__(256)
+partconv_ir_grad_kernel(const float2 *__restrict__ X, const float2 *__restrict__ U, int V, int H, int NB,
+                        float2 *__restrict__ G) {
+  __shared__ float2 red[8][33];
+  const int bin = blockIdx.x * 32 + (threadIdx.x & 31), k = blockIdx.y, grp = threadIdx.x >> 5;
+  float2 acc = make_float2(0.f, 0.f);
+  if (bin < NB) {
+    const int terms = V * (H - k);
+    for (int i = grp; i < terms; i += 8) {
+      int v = i / (H - k), h = k + (i - v * (H - k));
+      float2 x = X[((size_t)v * H + (h - k)) * NB + bin], u = U[((size_t)v * H + h) * NB + bin];
+      acc.x += x.x * u.x + x.y * u.y;
+      acc.y += x.x * u.y - x.y * u.x;
+    }
+  }
+  red[grp][threadIdx.x & 31] = acc;
+  __syncthreads();
+  if (grp == 0 && bin < NB) {
+    float2 t = make_float2(0.f, 0.f);
+#pragma unroll
+    for (int g2 = 0; g2 < 8; ++g2) {
+      t.x += red[g2][threadIdx.x & 31].x;
+      t.y += red[g2][threadIdx.x & 31].y;
+    }
+    G[(size_t)k * NB + bin] = t;
+  }
+}
+
+// g_ir[k*hop + i] = frames[k][i], i < hop (the zero-padded tail of each partition carries no parameter)
+__global__ void take_partitions_kernel(const float *__restrict__ frames, int ir_len, int N, int hop,
+                                       float *__restrict__ g_ir) {
+  int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= ir_len) return;
+  int k = t / hop, i = t - k * hop;
+  g_ir[t] = frames[(size_t)k * N + i];
 }
 
 template <int N, int SRC, int OUT>
@@ -263,7 +352,77 @@ DGC_EXPORT int32_t dgc_partconv(dgc_ctx *ctx, const float *x_dev, int32_t V, int
 #undef CASE
   }
   if (rc != DGC_OK) return rc;
-  overlap_add_kernel<<<dim3(dgc_div_up(T, 256), V), 256, 0, ctx->stream>>>(frames, T, N, hop, H, out_dev);
+  overlap_add_kernel<<<dim3(dgc_div_up(T, 256), V), 256, 0, ctx->stream>>>(frames, T, N, hop, H, 0, 0, out_dev);
   DGC_LAUNCHED(ctx, "overlap_add");
+  return DGC_OK;
+}
+
+DGC_EXPORT uint64_t dgc_partconv_bwd_scratch_floats(int32_t V, int32_t T, int32_t ir_len, int32_t N, int32_t hop) {
+  if (V <= 0 || T <= 0 || ir_len <= 0 || N <= 0 || hop <= 0) return 0;
+  uint64_t H = (uint64_t)(T + hop - 1) / hop, K = (uint64_t)(ir_len + hop - 1) / hop, NB = N / 2 + 1;
+  // IR spectra + IR-gradient spectra, X, U, V spectra, frames (max of V*H and K frames)
+  uint64_t fr = (uint64_t)V * H > K ? (uint64_t)V * H : K;
+  return 4 * K * NB + 3 * (2 * (uint64_t)V * H * NB + 4) + fr * N + 64;
+}
+
+// Backward of dgc_partconv (a linear map in x and in ir): g_x = A(ir)^T g_out and/or g_ir.  The reference
+// has no backward for partitionedSpectralConvolve (Sources/DGen/Gradients.swift:1156-1164); this is the
+// exact adjoint of the forward above, checked against an fp64 evaluation.
+DGC_EXPORT int32_t dgc_partconv_bwd(dgc_ctx *ctx, const float *x_dev, int32_t V, int32_t T, const float *ir_dev,
+                                    int32_t ir_len, int32_t N, int32_t hop, float gain, const float *g_out_dev,
+                                    float *scratch_dev, int32_t accumulate_gx, float *g_x_dev, float *g_ir_dev) {
+  if (!ctx) return DGC_ERR_INVALID;
+  DGC_REQUIRE(ctx, x_dev && ir_dev && g_out_dev && (g_x_dev || g_ir_dev), "null pointer");
+  DGC_REQUIRE(ctx, V > 0 && V <= 65535 && T > 0 && ir_len > 0, "size out of range");
+  DGC_REQUIRE(ctx, dgc_is_pow2(N) && N >= 16 && N <= 2048, "N must be a power of two in 16..2048");
+  DGC_REQUIRE(ctx, hop > 0 && hop <= N, "hop must be in 1..N");
+  const int H = dgc_div_up(T, hop), K = dgc_div_up(ir_len, hop), NB = N / 2 + 1;
+  size_t mac_smem = ((size_t)K * MAC_BINS + (size_t)(MAC_HT + K - 1) * MAC_BINS) * sizeof(float2);
+  DGC_REQUIRE(ctx, mac_smem <= 200 * 1024, "impulse response has too many partitions (K <= 380)");
+  float *scr = scratch_dev ? scratch_dev
+                           : dgc_ctx_scratch(ctx, dgc_partconv_bwd_scratch_floats(V, T, ir_len, N, hop));
+  if (!scr) return DGC_ERR_OOM;
+  DGC_REQUIRE(ctx, (((uintptr_t)scr) & 15) == 0, "scratch must be 16-byte aligned");
+  const size_t nh = ((size_t)2 * K * NB + 3) & ~(size_t)3, nx = ((size_t)2 * V * H * NB + 3) & ~(size_t)3;
+  float *hs = scr, *gs = hs + nh, *xs = gs + nh, *us = xs + nx, *vs = us + nx, *frames = vs + nx;
+  const float *win = dgc_ctx_hann_per(ctx, N);
+  if (!win) return DGC_ERR_OOM;
+  int32_t rc = dispatch_stft<2, 1>(ctx, N, g_out_dev, V, T, hop, H, win, us);   // U_h = FFT(w * g[h*hop ..])
+  if (rc != DGC_OK) return rc;
+  if (g_x_dev) {
+    rc = dispatch_stft<1, 1>(ctx, N, ir_dev, 1, ir_len, hop, K, nullptr, hs);
+    if (rc != DGC_OK) return rc;
+    DGC_CUDA(ctx, cudaFuncSetAttribute(partconv_mac_adj_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)mac_smem));
+    partconv_mac_adj_kernel<<<dim3(dgc_div_up(NB, MAC_BINS), dgc_div_up(H, MAC_HT), V), 256, mac_smem, ctx->stream>>>(
+        reinterpret_cast<const float2 *>(us), reinterpret_cast<const float2 *>(hs), H, K, NB,
+        reinterpret_cast<float2 *>(vs));
+    DGC_LAUNCHED(ctx, "partconv_mac_adj");
+    switch (N) {
+#define CASE(NN) case NN: rc = launch_istft<NN>(ctx, reinterpret_cast<const float2 *>(vs), V, H, win, gain, frames); break;
+      CASE(16) CASE(32) CASE(64) CASE(128) CASE(256) CASE(512) CASE(1024) CASE(2048)
+#undef CASE
+    }
+    if (rc != DGC_OK) return rc;
+    overlap_add_kernel<<<dim3(dgc_div_up(T, 256), V), 256, 0, ctx->stream>>>(frames, T, N, hop, H, -(N - 1),
+                                                                             accumulate_gx, g_x_dev);
+    DGC_LAUNCHED(ctx, "overlap_add_adj");
+  }
+  if (g_ir_dev) {
+    rc = dispatch_stft<0, 1>(ctx, N, x_dev, V, T, hop, H, win, xs);
+    if (rc != DGC_OK) return rc;
+    partconv_ir_grad_kernel<<<dim3(dgc_div_up(NB, 32), K), 256, 0, ctx->stream>>>(
+        reinterpret_cast<const float2 *>(xs), reinterpret_cast<const float2 *>(us), V, H, NB,
+        reinterpret_cast<float2 *>(gs));
+    DGC_LAUNCHED(ctx, "partconv_ir_grad");
+    switch (N) {
+#define CASE(NN) case NN: rc = launch_istft<NN>(ctx, reinterpret_cast<const float2 *>(gs), 1, K, nullptr, gain, frames); break;
+      CASE(16) CASE(32) CASE(64) CASE(128) CASE(256) CASE(512) CASE(1024) CASE(2048)
+#undef CASE
+    }
+    if (rc != DGC_OK) return rc;
+    take_partitions_kernel<<<dgc_div_up(ir_len, 256), 256, 0, ctx->stream>>>(frames, ir_len, N, hop, g_ir_dev);
+    DGC_LAUNCHED(ctx, "take_partitions");
+  }
   return DGC_OK;
 }

@@ -83,6 +83,16 @@ SIGNATURES = {
     "dgc_mss_partial_floats": (_u64, [C.POINTER(MssParams)]),
     "dgc_mss_loss_fwd": (_i32, [_vp, C.POINTER(MssParams), _vp, _vp, _vp, _vp]),
     "dgc_mss_loss_bwd": (_i32, [_vp, C.POINTER(MssParams), _vp, _vp, _f, _vp]),
+    "dgc_harmonic_bwd_scratch_floats": (_u64, [C.POINTER(HarmonicParams)]),
+    "dgc_harmonic_render_bwd": (_i32, [_vp, C.POINTER(HarmonicParams), _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "dgc_fir_noise_bwd": (_i32, [_vp, C.POINTER(FirParams), _vp, _vp, _vp, _vp]),
+    "dgc_hn_heads_fwd": (_i32, [_vp, _vp, _i32, _i32, _i32, _vp, _vp]),
+    "dgc_hn_heads_bwd": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _vp]),
+    "dgc_partconv_bwd_scratch_floats": (_u64, [_i32, _i32, _i32, _i32, _i32]),
+    "dgc_partconv_bwd": (_i32, [_vp, _vp, _i32, _i32, _vp, _i32, _i32, _i32, _f, _vp, _vp, _i32, _vp, _vp]),
+    "dgc_linear_fwd": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp]),
+    "dgc_linear_bwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp]),
+    "dgc_adam_step": (_i32, [_vp, _vp, _vp, _vp, _vp, _u64, _i32, _f, _f, _f, _f]),
     "dgc_hn_forward_loss_host": (_i32, [_vp, C.POINTER(HnStep)] + [_vp] * 9 + [C.POINTER(C.c_double), _vp]),
 }
 
@@ -278,6 +288,67 @@ class Context:
         grad = self._empty(B, T)
         self.check(self.lib.dgc_mss_loss_bwd(self.h, C.byref(p), _ptr(pred), _ptr(target), upstream, _ptr(grad)))
         return grad
+
+    # ---- backward of the synthesis ------------------------------------------------------------
+    def harmonic_render_bwd(self, f0, uv, amps, gain, g_audio, T, sr, phase_mode=PHASE_SCAN, scale=1.0):
+        F, B = f0.shape
+        K = amps.shape[2]
+        p = HarmonicParams(B, T, K, F, sr, scale, phase_mode, 0)
+        g = self._empty(F, B, K)
+        self.check(self.lib.dgc_harmonic_render_bwd(self.h, C.byref(p), _ptr(f0), _ptr(uv), _ptr(amps), _ptr(gain),
+                                                    _ptr(g_audio), None, _ptr(g)))
+        return g
+
+    def fir_noise_bwd(self, noise, noise_gain, g_audio, F, taps, scale=0.12):
+        B, T = noise.shape
+        p = FirParams(B, T, F, taps, scale, 0)
+        g = self._empty(F, B, taps)
+        self.check(self.lib.dgc_fir_noise_bwd(self.h, C.byref(p), _ptr(noise), _ptr(noise_gain), _ptr(g_audio),
+                                              _ptr(g)))
+        return g
+
+    def heads_fwd(self, z, K):
+        M, W = z.shape
+        amps, bands = self._empty(M, K), self._empty(M, W - K)
+        self.check(self.lib.dgc_hn_heads_fwd(self.h, _ptr(z), M, K, W - K, _ptr(amps), _ptr(bands)))
+        return amps, bands
+
+    def heads_bwd(self, z, g_amps, g_bands):
+        M, W = z.shape
+        K = g_amps.shape[1]
+        gz = self._empty(M, W)
+        self.check(self.lib.dgc_hn_heads_bwd(self.h, _ptr(z), _ptr(g_amps), _ptr(g_bands), M, K, W - K, _ptr(gz)))
+        return gz
+
+    def partconv_bwd(self, x, ir, N, hop, g_out, gain=1.0, need_gx=True, need_gir=True, gx_out=None):
+        V, T = x.shape
+        gx = (gx_out if gx_out is not None else self._empty(V, T)) if need_gx else None
+        gir = self._empty(ir.numel()) if need_gir else None
+        self.check(self.lib.dgc_partconv_bwd(self.h, _ptr(x), V, T, _ptr(ir), ir.numel(), N, hop, gain, _ptr(g_out),
+                                             None, 1 if gx_out is not None else 0, _ptr(gx), _ptr(gir)))
+        return gx, gir
+
+    # ---- controller ---------------------------------------------------------------------------
+    def linear_fwd(self, a, w, bias=None, act=0):
+        M, K = a.shape
+        N = w.shape[1]
+        c = self._empty(M, N)
+        self.check(self.lib.dgc_linear_fwd(self.h, _ptr(a), _ptr(w), _ptr(bias), M, K, N, act, _ptr(c)))
+        return c
+
+    def linear_bwd(self, a, w, c, dc, act=0, need_da=True, need_db=True):
+        M, K = a.shape
+        N = w.shape[1]
+        dz, dw = self._empty(M, N), self._empty(K, N)
+        da = self._empty(M, K) if need_da else None
+        db = self._empty(N) if need_db else None
+        self.check(self.lib.dgc_linear_bwd(self.h, _ptr(a), _ptr(w), _ptr(c), _ptr(dc), M, K, N, act, _ptr(dz),
+                                           _ptr(da), _ptr(dw), _ptr(db)))
+        return da, dw, db
+
+    def adam_step(self, theta, grad, m, v, t, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8):
+        self.check(self.lib.dgc_adam_step(self.h, _ptr(theta), _ptr(grad), _ptr(m), _ptr(v), theta.numel(), t, lr,
+                                          beta1, beta2, eps))
 
     # ---- composite, host buffers --------------------------------------------------------------
     def hn_forward_loss_host(self, step, f0, uv, amps, gain, noise_gain, taps_or_bands, w, noise, target,

@@ -143,6 +143,25 @@ int32_t dgc_fir_noise(dgc_ctx *ctx, const dgc_fir_params *p, const float *noise_
 int32_t dgc_bands_to_taps(dgc_ctx *ctx, const float *bands_dev, const float *w_dev, int32_t rows, int32_t nbands,
                           int32_t taps, float *taps_dev);
 
+/* ---- backward of the synthesis w.r.t. the controller outputs -------------------------------------
+ * Gradient of the harmonic branch w.r.t. the amplitude table: g_amps [F][B][K] from g_audio [B][T].
+ * replaces: the backward of sampleRow + mul + sumAxis + tensorAccumulate
+ * (Sources/DGen/Emit+RowSelection.swift:215-330, Sources/DGen/Emit+State.swift:50-115); the phasor
+ * input is data (no gradient), as in the HarmonicE2E trainer.  Fixed summation order, no atomics. */
+uint64_t dgc_harmonic_bwd_scratch_floats(const dgc_harmonic_params *p);
+int32_t dgc_harmonic_render_bwd(dgc_ctx *ctx, const dgc_harmonic_params *p, const float *f0_dev, const float *uv_dev,
+                                const float *amps_dev, const float *gain_dev, const float *g_audio_dev,
+                                float *scratch_dev, float *g_amps_dev);
+/* Gradient of the noise branch w.r.t. the tap table: g_taps [F][B][taps] from g_audio [B][T]. */
+int32_t dgc_fir_noise_bwd(dgc_ctx *ctx, const dgc_fir_params *p, const float *noise_dev, const float *noise_gain_dev,
+                          const float *g_audio_dev, float *g_taps_dev);
+/* Controller output heads (Examples/HarmonicE2E/Model.swift:102-106): z [M][K+NB] ->
+ * amps [M][K] = softplus(z[:, :K]) / (row sum + 1e-6), bands [M][NB] = sigmoid(z[:, K:]); and backward. */
+int32_t dgc_hn_heads_fwd(dgc_ctx *ctx, const float *z_dev, int32_t M, int32_t K, int32_t NB, float *amps_dev,
+                         float *bands_dev);
+int32_t dgc_hn_heads_bwd(dgc_ctx *ctx, const float *z_dev, const float *g_amps_dev, const float *g_bands_dev,
+                         int32_t M, int32_t K, int32_t NB, float *gz_dev);
+
 /* ---- linear recurrences -------------------------------------------------------------------------
  * y[n] = x[n] + a*y[n-1] per voice, chunked parallel scan over time.
  * replaces: historyRead/historyWrite feedback (Sources/DGen/Emit+State.swift:150-224). x,y [B][T]. */
@@ -203,6 +222,14 @@ uint64_t dgc_partconv_scratch_floats(int32_t V, int32_t T, int32_t ir_len, int32
 int32_t dgc_partconv(dgc_ctx *ctx, const float *x_dev, int32_t V, int32_t T, const float *ir_dev, int32_t ir_len,
                      int32_t N, int32_t hop, float gain, float *scratch_dev, float *out_dev);
 
+/* Backward of dgc_partconv (linear in x and in ir): g_x [V][T] (overwritten, or += when accumulate_gx)
+ * and/or g_ir [ir_len]; pass NULL for the one that is not needed.  The reference defines no backward
+ * for this op (Sources/DGen/Gradients.swift:1156-1164): this is the exact adjoint of the forward. */
+uint64_t dgc_partconv_bwd_scratch_floats(int32_t V, int32_t T, int32_t ir_len, int32_t N, int32_t hop);
+int32_t dgc_partconv_bwd(dgc_ctx *ctx, const float *x_dev, int32_t V, int32_t T, const float *ir_dev, int32_t ir_len,
+                         int32_t N, int32_t hop, float gain, const float *g_out_dev, float *scratch_dev,
+                         int32_t accumulate_gx, float *g_x_dev, float *g_ir_dev);
+
 /* ---- multi-scale spectral loss ------------------------------------------------------------------ */
 #define DGC_MSS_MAX_SCALES 8
 typedef struct dgc_mss_params {
@@ -227,6 +254,24 @@ int32_t dgc_mss_loss_fwd(dgc_ctx *ctx, const dgc_mss_params *p, const float *pre
  * d objective / d loss.  grad is overwritten.  Bit-reproducible (no atomics). */
 int32_t dgc_mss_loss_bwd(dgc_ctx *ctx, const dgc_mss_params *p, const float *pred_dev, const float *target_dev,
                          float upstream, float *grad_pred_dev);
+
+/* ---- controller -------------------------------------------------------------------------------
+ * C[M][N] = act(A[M][K] * W[K][N] + bias[N]); act: 0 none, 1 tanh; bias may be NULL when act == 0.
+ * Row-major, full fp32.  replaces: matmul -> mul + sumAxis / gemm
+ * (Sources/DGen/Tensor.swift:1195-1230, Sources/DGen/Emit+GEMM.swift). */
+int32_t dgc_linear_fwd(dgc_ctx *ctx, const float *a_dev, const float *w_dev, const float *bias_dev, int32_t M,
+                       int32_t K, int32_t N, int32_t act, float *c_dev);
+/* Backward of the layer above: dZ = dC * act'(C) (written to dz_dev [M][N]), dW[K][N] = A^T dZ,
+ * dbias[N] = column sums of dZ (optional), dA[M][K] = dZ W^T (optional).  Sums run in a fixed order
+ * (replaces tensorAccumulate, Sources/DGen/Emit+State.swift:50-115). */
+int32_t dgc_linear_bwd(dgc_ctx *ctx, const float *a_dev, const float *w_dev, const float *c_dev, const float *dc_dev,
+                       int32_t M, int32_t K, int32_t N, int32_t act, float *dz_dev, float *da_dev, float *dw_dev,
+                       float *dbias_dev);
+
+/* Adam step on device (Sources/DGenLazy/Optimizers.swift:164-243: bias-corrected, eps outside the
+ * square root, the reference's operation order); t is the 1-based step index. */
+int32_t dgc_adam_step(dgc_ctx *ctx, float *theta_dev, const float *grad_dev, float *m_dev, float *v_dev, uint64_t n,
+                      int32_t t, float lr, float beta1, float beta2, float eps);
 
 /* ---- composite steps with host buffers (the call a host makes per batch) ------------------------ */
 typedef struct dgc_hn_step {

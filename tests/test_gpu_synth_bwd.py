@@ -1,0 +1,93 @@
+"""GPU gradients of the synthesis (harmonic bank, noise FIR, partitioned convolution, heads) against the fp64
+autograd evaluation of the same graph (oracle/torch_oracle.py); tolerance 1e-3 relative."""
+import numpy as np
+import pytest
+import torch
+
+import dgen_b200
+from dgen_b200 import workloads as wl
+from oracle import torch_oracle as to
+
+pytestmark = pytest.mark.gpu
+f32 = np.float32
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    c = dgen_b200.Context(0)
+    yield c
+    c.close()
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def rel_err(got, want):
+    return np.abs(got - want).max() / max(np.abs(want).max(), 1e-30)
+
+
+@pytest.mark.parametrize("shape", [dict(B=2, T=4096, K=100, F=64), dict(B=3, T=3000, K=7, F=33),
+                                   dict(B=1, T=2000, K=130, F=9), dict(B=2, T=1500, K=20, F=1500)])
+def test_harmonic_render_backward(ctx, shape):
+    d = wl.harmonic_noise_inputs(21, sr=16000.0, **shape)
+    rng = np.random.default_rng(1)
+    g = rng.standard_normal((d["B"], d["T"])).astype(f32)
+    rows = to.rows_of(d["F"], d["T"])
+    amps = to.t64(d["amps"]).requires_grad_(True)
+    out = to.harmonic_render(to.t64(d["f0"]), to.t64(d["uv"]), amps, to.t64(d["gain"]), d["T"], d["sr"], rows)
+    (out * to.t64(g)).sum().backward()
+    got = ctx.harmonic_render_bwd(dev(d["f0"]), dev(d["uv"]), dev(d["amps"]), dev(d["gain"]), dev(g), d["T"], d["sr"])
+    assert rel_err(got.cpu().numpy(), amps.grad.numpy()) < 1e-3
+
+
+@pytest.mark.parametrize("B,T,F,NT", [(2, 3000, 50, 257), (1, 1000, 5, 17), (2, 2049, 300, 64)])
+def test_fir_noise_backward(ctx, B, T, F, NT):
+    rng = np.random.default_rng(T)
+    taps = rng.standard_normal((F, B, NT)).astype(f32)
+    noise = rng.standard_normal((B, T)).astype(f32)
+    ng = rng.uniform(0.2, 1, (F, B)).astype(f32)
+    g = rng.standard_normal((B, T)).astype(f32)
+    rows = to.rows_of(F, T)
+    tt = to.t64(taps).requires_grad_(True)
+    (to.fir_noise(to.t64(noise), tt, to.t64(ng), rows) * to.t64(g)).sum().backward()
+    got = ctx.fir_noise_bwd(dev(noise), dev(ng), dev(g), F, NT)
+    assert rel_err(got.cpu().numpy(), tt.grad.numpy()) < 1e-3
+
+
+@pytest.mark.parametrize("N,hop,T,V,irlen", [(64, 32, 3000, 2, 200), (2048, 1024, 20000, 2, 9000), (128, 64, 1000, 3, 1),
+                                             (256, 64, 2100, 1, 300)])
+def test_partconv_backward(ctx, N, hop, T, V, irlen):
+    rng = np.random.default_rng(N + T)
+    x = rng.standard_normal((V, T)).astype(f32)
+    ir = (rng.standard_normal(irlen) * np.exp(-np.arange(irlen) / max(1.0, irlen / 4))).astype(f32)
+    g = rng.standard_normal((V, T)).astype(f32)
+    xt, it = to.t64(x).requires_grad_(True), to.t64(ir).requires_grad_(True)
+    (to.partconv(xt, it, N, hop, gain=0.8) * to.t64(g)).sum().backward()
+    gx, gir = ctx.partconv_bwd(dev(x), dev(ir), N, hop, dev(g), gain=0.8)
+    assert rel_err(gx.cpu().numpy(), xt.grad.numpy()) < 1e-3
+    assert rel_err(gir.cpu().numpy(), it.grad.numpy()) < 1e-3
+
+
+def test_heads_forward_and_backward(ctx):
+    rng = np.random.default_rng(4)
+    M, K, NB = 777, 100, 65
+    z = (2 * rng.standard_normal((M, K + NB))).astype(f32)
+    ga, gb = rng.standard_normal((M, K)).astype(f32), rng.standard_normal((M, NB)).astype(f32)
+    zt = to.t64(z).requires_grad_(True)
+    a64, b64 = to.heads(zt, K)
+    ((a64 * to.t64(ga)).sum() + (b64 * to.t64(gb)).sum()).backward()
+    amps, bands = ctx.heads_fwd(dev(z), K)
+    assert rel_err(amps.cpu().numpy(), a64.detach().numpy()) < 1e-5
+    assert rel_err(bands.cpu().numpy(), b64.detach().numpy()) < 1e-5
+    gz = ctx.heads_bwd(dev(z), dev(ga), dev(gb))
+    assert rel_err(gz.cpu().numpy(), zt.grad.numpy()) < 1e-3
+
+
+def test_backward_kernels_are_deterministic(ctx):
+    d = wl.harmonic_noise_inputs(5, B=2, T=4096, K=100, F=64)
+    g = dev(np.random.default_rng(0).standard_normal((2, 4096)).astype(f32))
+    args = (dev(d["f0"]), dev(d["uv"]), dev(d["amps"]), dev(d["gain"]), g, d["T"], d["sr"])
+    a = ctx.harmonic_render_bwd(*args).cpu().numpy()
+    b = ctx.harmonic_render_bwd(*args).cpu().numpy()
+    assert np.array_equal(a, b)
