@@ -316,7 +316,7 @@ DGC_EXPORT uint64_t dgc_partconv_scratch_floats(int32_t V, int32_t T, int32_t ir
 
 DGC_EXPORT int32_t dgc_partconv(dgc_ctx *ctx, const float *x_dev, int32_t V, int32_t T, const float *ir_dev,
                                 int32_t ir_len, int32_t N, int32_t hop, float gain, float *scratch_dev,
-                                float *out_dev) {
+                                int32_t accumulate, float *out_dev) {
   if (!ctx) return DGC_ERR_INVALID;
   DGC_REQUIRE(ctx, x_dev && ir_dev && out_dev, "null pointer");
   DGC_REQUIRE(ctx, V > 0 && V <= 65535 && T > 0 && ir_len > 0, "size out of range");
@@ -352,7 +352,8 @@ DGC_EXPORT int32_t dgc_partconv(dgc_ctx *ctx, const float *x_dev, int32_t V, int
 #undef CASE
   }
   if (rc != DGC_OK) return rc;
-  overlap_add_kernel<<<dim3(dgc_div_up(T, 256), V), 256, 0, ctx->stream>>>(frames, T, N, hop, H, 0, 0, out_dev);
+  overlap_add_kernel<<<dim3(dgc_div_up(T, 256), V), 256, 0, ctx->stream>>>(frames, T, N, hop, H, 0, accumulate,
+                                                                           out_dev);
   DGC_LAUNCHED(ctx, "overlap_add");
   return DGC_OK;
 }

@@ -79,7 +79,7 @@ SIGNATURES = {
     "dgc_biquad_mse_bwd": (_i32, [_vp, C.POINTER(BiquadParams), _vp, _vp, _vp, _vp, _vp, _f, _vp, _vp, _vp, _vp]),
     "dgc_stft_mag": (_i32, [_vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp]),
     "dgc_partconv_scratch_floats": (_u64, [_i32, _i32, _i32, _i32, _i32]),
-    "dgc_partconv": (_i32, [_vp, _vp, _i32, _i32, _vp, _i32, _i32, _i32, _f, _vp, _vp]),
+    "dgc_partconv": (_i32, [_vp, _vp, _i32, _i32, _vp, _i32, _i32, _i32, _f, _vp, _i32, _vp]),
     "dgc_mss_partial_floats": (_u64, [C.POINTER(MssParams)]),
     "dgc_mss_loss_fwd": (_i32, [_vp, C.POINTER(MssParams), _vp, _vp, _vp, _vp]),
     "dgc_mss_loss_bwd": (_i32, [_vp, C.POINTER(MssParams), _vp, _vp, _f, _vp]),
@@ -263,10 +263,12 @@ class Context:
         self.check(self.lib.dgc_stft_mag(self.h, _ptr(x), V, T, N, hop, _ptr(window), _ptr(out)))
         return out
 
-    def partconv(self, x, ir, N, hop, gain=1.0):
+    def partconv(self, x, ir, N, hop, gain=1.0, out=None, accumulate=False):
         V, T = x.shape
-        out = self._empty(V, T)
-        self.check(self.lib.dgc_partconv(self.h, _ptr(x), V, T, _ptr(ir), ir.numel(), N, hop, gain, None, _ptr(out)))
+        if out is None:
+            out = self._empty(V, T)
+        self.check(self.lib.dgc_partconv(self.h, _ptr(x), V, T, _ptr(ir), ir.numel(), N, hop, gain, None,
+                                         int(accumulate), _ptr(out)))
         return out
 
     # ---- spectral loss ------------------------------------------------------------------------
@@ -320,12 +322,15 @@ class Context:
         self.check(self.lib.dgc_hn_heads_bwd(self.h, _ptr(z), _ptr(g_amps), _ptr(g_bands), M, K, W - K, _ptr(gz)))
         return gz
 
-    def partconv_bwd(self, x, ir, N, hop, g_out, gain=1.0, need_gx=True, need_gir=True, gx_out=None):
+    def partconv_bwd(self, x, ir, N, hop, g_out, gain=1.0, need_gx=True, need_gir=True, gx_accumulate_into=None,
+                     gir_out=None):
+        """gx_accumulate_into: a [V][T] tensor that receives += A^T g_out (it may be g_out itself)."""
         V, T = x.shape
-        gx = (gx_out if gx_out is not None else self._empty(V, T)) if need_gx else None
-        gir = self._empty(ir.numel()) if need_gir else None
+        acc = gx_accumulate_into is not None
+        gx = (gx_accumulate_into if acc else self._empty(V, T)) if need_gx else None
+        gir = (gir_out if gir_out is not None else self._empty(ir.numel())) if need_gir else None
         self.check(self.lib.dgc_partconv_bwd(self.h, _ptr(x), V, T, _ptr(ir), ir.numel(), N, hop, gain, _ptr(g_out),
-                                             None, 1 if gx_out is not None else 0, _ptr(gx), _ptr(gir)))
+                                             None, int(acc), _ptr(gx), _ptr(gir)))
         return gx, gir
 
     # ---- controller ---------------------------------------------------------------------------

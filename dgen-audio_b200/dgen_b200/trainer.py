@@ -1,0 +1,157 @@
+"""One training step of the batched harmonic+noise model, HarmonicE2E style
+(Examples/HarmonicE2E/Trainer.swift:247-487: forward -> multi-scale spectral loss -> backward ->
+optimizer.step), with every tensor resident in HBM and every operation a libdgen_cuda kernel.
+
+Graph (rows of all [F*B, *] matrices are ordered [control frame][voice], the layout of the control tables):
+    h = tanh(tanh(tanh(X W1 + b1) W2 + b2) W3 + b3);  z = h Wh + bh                     (Model.swift:96-101)
+    amps = softplus(z[:, :K]) / (sum + 1e-6);  bands = sigmoid(z[:, K:])                 (Model.swift:102-106)
+    taps = bands Wfs^T;  dry = harmonic(f0, amps, gain, uv) + fir(noise, taps, noise_gain)  (Synth.swift:47-102)
+    out  = dry + partitioned_convolve(dry, ir)                                           (learnable 1 s IR)
+    loss = multi-scale spectral L1 (lin + log) of out against the target                 (Trainer.swift:538-588)
+Parameters and Adam state live in ONE flat device buffer; with several ranks the flat gradient is
+summed over ranks (NCCL all-reduce over NVLink) before the Adam step, and each rank's loss gradient is
+pre-scaled by local_voices / global_voices so that the sum is the gradient of the global-batch mean.
+"""
+import ctypes as C
+
+import numpy as np
+
+from . import Context, FirParams, HarmonicParams, PHASE_SCAN, mss_params, sharding
+
+
+class HarmonicModel:
+    def __init__(self, ctx: Context, B, T, K=100, F=1000, sr=16000.0, nbands=65, taps=257, hidden=512, in_features=2,
+                 ir_len=16000, conv_n=2048, conv_hop=1024, sizes=(2048, 1024, 512, 256, 128, 64), seed=0,
+                 phase_mode=PHASE_SCAN, global_voices=None):
+        import torch
+        self.torch, self.ctx = torch, ctx
+        self.B, self.T, self.K, self.F, self.sr = B, T, K, F, sr
+        self.nbands, self.taps, self.hidden, self.in_features = nbands, taps, hidden, in_features
+        self.ir_len, self.conv_n, self.conv_hop, self.sizes = ir_len, conv_n, conv_hop, tuple(sizes)
+        self.phase_mode = phase_mode
+        self.global_voices = global_voices or B
+        self.M = F * B
+        dims = [(in_features, hidden), (hidden, hidden), (hidden, hidden), (hidden, K + nbands)]
+        self.layout, off = [], 0
+        for i, (a, b) in enumerate(dims):
+            self.layout.append(("W%d" % i, off, (a, b)))
+            off += a * b
+            self.layout.append(("b%d" % i, off, (b,)))
+            off += b
+        self.layout.append(("ir", off, (ir_len,)))
+        off += ir_len
+        self.n_params = off
+        rng = np.random.default_rng(seed)
+        flat = np.zeros(off, np.float32)
+        for name, o, shape in self.layout:
+            n = int(np.prod(shape))
+            if name.startswith("W"):
+                flat[o:o + n] = (rng.standard_normal(n) / np.sqrt(shape[0])).astype(np.float32)
+            elif name == "ir":
+                t = np.arange(ir_len) / sr
+                flat[o:o + n] = (0.05 * rng.standard_normal(n) * np.exp(-6.91 * t / 0.4)).astype(np.float32)
+        dev = "cuda:%d" % ctx.device
+        self.params = torch.from_numpy(flat).to(dev)
+        self.grads = torch.zeros_like(self.params)
+        self.m = torch.zeros_like(self.params)
+        self.v = torch.zeros_like(self.params)
+        self.step_index = 0
+        f = lambda *s: torch.empty(*s, dtype=torch.float32, device=dev)
+        M, H = self.M, hidden
+        self.act = [f(M, H), f(M, H), f(M, H), f(M, K + nbands)]
+        self.dact = [f(M, H), f(M, H), f(M, H)]          # gradient w.r.t. a layer's input
+        self.dz = [f(M, H), f(M, H), f(M, H), f(M, K + nbands)]
+        self.head_dz = f(M, K + nbands)
+        self.amps, self.bands = f(F, B, K), f(F, B, nbands)
+        self.taps_tab, self.g_taps = f(F, B, taps), f(F, B, taps)
+        self.g_amps, self.g_bands = f(F, B, K), f(F, B, nbands)
+        self.dry, self.out, self.g_out = f(B, T), f(B, T), f(B, T)
+        self.loss = torch.zeros(1, dtype=torch.float64, device=dev)
+        self.mss = mss_params(B, T, self.sizes)
+
+    def view(self, name, buf=None):
+        buf = self.params if buf is None else buf
+        for n, o, shape in self.layout:
+            if n == name:
+                return buf[o:o + int(np.prod(shape))].view(*shape)
+        raise KeyError(name)
+
+    # ------------------------------------------------------------------------------------------
+    def forward(self, X, f0, uv, gain, noise_gain, noise, w_fs, target):
+        c = self.ctx
+        lib, h = c.lib, c.h
+        a = X
+        for i in range(4):
+            W, b = self.view("W%d" % i), self.view("b%d" % i)
+            c.check(lib.dgc_linear_fwd(h, a.data_ptr(), W.data_ptr(), b.data_ptr(), self.M, W.shape[0], W.shape[1],
+                                       1 if i < 3 else 0, self.act[i].data_ptr()))
+            a = self.act[i]
+        c.check(lib.dgc_hn_heads_fwd(h, self.act[3].data_ptr(), self.M, self.K, self.nbands, self.amps.data_ptr(),
+                                     self.bands.data_ptr()))
+        c.check(lib.dgc_bands_to_taps(h, self.bands.data_ptr(), w_fs.data_ptr(), self.M, self.nbands, self.taps,
+                                      self.taps_tab.data_ptr()))
+        hp = HarmonicParams(self.B, self.T, self.K, self.F, self.sr, 1.0, self.phase_mode, 0)
+        c.check(lib.dgc_harmonic_render(h, C.byref(hp), f0.data_ptr(), uv.data_ptr(), self.amps.data_ptr(),
+                                        gain.data_ptr(), None, self.dry.data_ptr()))
+        fp = FirParams(self.B, self.T, self.F, self.taps, 0.12, 1)
+        c.check(lib.dgc_fir_noise(h, C.byref(fp), noise.data_ptr(), self.taps_tab.data_ptr(), noise_gain.data_ptr(),
+                                  self.dry.data_ptr()))
+        self.out.copy_(self.dry)
+        ir = self.view("ir")
+        c.check(lib.dgc_partconv(h, self.dry.data_ptr(), self.B, self.T, ir.data_ptr(), self.ir_len, self.conv_n,
+                                 self.conv_hop, 1.0, None, 1, self.out.data_ptr()))
+        c.check(lib.dgc_mss_loss_fwd(h, C.byref(self.mss), self.out.data_ptr(), target.data_ptr(), None,
+                                     self.loss.data_ptr()))
+        return self.loss
+
+    def backward(self, X, f0, uv, gain, noise_gain, noise, w_fs, target):
+        c = self.ctx
+        lib, h = c.lib, c.h
+        upstream = float(self.B) / float(self.global_voices)   # local share of the global-batch mean
+        c.check(lib.dgc_mss_loss_bwd(h, C.byref(self.mss), self.out.data_ptr(), target.data_ptr(), upstream,
+                                     self.g_out.data_ptr()))
+        ir, g_ir = self.view("ir"), self.view("ir", self.grads)
+        # g_dry = g_out + A(ir)^T g_out, accumulated in place; g_ir
+        c.check(lib.dgc_partconv_bwd(h, self.dry.data_ptr(), self.B, self.T, ir.data_ptr(), self.ir_len, self.conv_n,
+                                     self.conv_hop, 1.0, self.g_out.data_ptr(), None, 1, self.g_out.data_ptr(),
+                                     g_ir.data_ptr()))
+        hp = HarmonicParams(self.B, self.T, self.K, self.F, self.sr, 1.0, self.phase_mode, 0)
+        c.check(lib.dgc_harmonic_render_bwd(h, C.byref(hp), f0.data_ptr(), uv.data_ptr(), self.amps.data_ptr(),
+                                            gain.data_ptr(), self.g_out.data_ptr(), None, self.g_amps.data_ptr()))
+        fp = FirParams(self.B, self.T, self.F, self.taps, 0.12, 0)
+        c.check(lib.dgc_fir_noise_bwd(h, C.byref(fp), noise.data_ptr(), noise_gain.data_ptr(), self.g_out.data_ptr(),
+                                      self.g_taps.data_ptr()))
+        # g_bands = g_taps Wfs   ([M, taps] x [taps, nbands])
+        c.check(lib.dgc_linear_fwd(h, self.g_taps.data_ptr(), w_fs.data_ptr(), None, self.M, self.taps, self.nbands, 0,
+                                   self.g_bands.data_ptr()))
+        c.check(lib.dgc_hn_heads_bwd(h, self.act[3].data_ptr(), self.g_amps.data_ptr(), self.g_bands.data_ptr(),
+                                     self.M, self.K, self.nbands, self.dz[3].data_ptr()))
+        # head layer: dz[3] is the gradient w.r.t. z (no activation); trunk layers: dact[i] is the gradient
+        # w.r.t. act[i] and the kernel applies tanh' to it
+        for i in (3, 2, 1, 0):
+            W = self.view("W%d" % i)
+            inp = X if i == 0 else self.act[i - 1]
+            gW, gb = self.view("W%d" % i, self.grads), self.view("b%d" % i, self.grads)
+            dc = self.dz[3] if i == 3 else self.dact[i]
+            dz_out = self.head_dz if i == 3 else self.dz[i]
+            da = self.dact[i - 1].data_ptr() if i > 0 else None
+            c.check(lib.dgc_linear_bwd(h, inp.data_ptr(), W.data_ptr(), self.act[i].data_ptr(), dc.data_ptr(), self.M,
+                                       W.shape[0], W.shape[1], 1 if i < 3 else 0, dz_out.data_ptr(), da,
+                                       gW.data_ptr(), gb.data_ptr()))
+        return self.grads
+
+    def step(self, X, f0, uv, gain, noise_gain, noise, w_fs, target, lr=1e-3):
+        """forward + backward + gradient all-reduce + Adam; returns the device loss tensor (local mean)."""
+        self.forward(X, f0, uv, gain, noise_gain, noise, w_fs, target)
+        self.backward(X, f0, uv, gain, noise_gain, noise, w_fs, target)
+        sharding.allreduce_sum_(self.grads)
+        self.step_index += 1
+        self.ctx.adam_step(self.params, self.grads, self.m, self.v, self.step_index, lr=lr)
+        return self.loss
+
+
+def features_from_controls(f0, gain, f0_min=40.0, f0_max=2000.0):
+    """Per-control-frame conditioning [F*B, 2]: normalised log-f0 and loudness
+    (Examples/HarmonicE2E/Trainer.swift:590-625 builds the same kind of rows)."""
+    lf = (np.log(np.maximum(f0, 1.0)) - np.log(f0_min)) / (np.log(f0_max) - np.log(f0_min))
+    return np.stack([lf.reshape(-1), gain.reshape(-1)], axis=1).astype(np.float32)

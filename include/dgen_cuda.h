@@ -217,10 +217,11 @@ int32_t dgc_stft_mag(dgc_ctx *ctx, const float *x_dev, int32_t V, int32_t T, int
 /* partitionedConvolve (Sources/DGenLazy/SpectralTensorOps.swift:204-254,
  * Emit+PartitionedConvolution.swift:26-113, Emit+FFT.swift:6-62): V signals [V][T], one IR; periodic
  * Hann analysis and synthesis windows, IFFT scaled by 1/N, overlap-add at `hop`.
- * scratch_dev: dgc_partconv_scratch_floats() floats, or NULL for a context-owned buffer. */
+ * scratch_dev: dgc_partconv_scratch_floats() floats, or NULL for a context-owned buffer.
+ * accumulate != 0: out += result (dry + wet mix into a buffer that already holds the dry signal). */
 uint64_t dgc_partconv_scratch_floats(int32_t V, int32_t T, int32_t ir_len, int32_t N, int32_t hop);
 int32_t dgc_partconv(dgc_ctx *ctx, const float *x_dev, int32_t V, int32_t T, const float *ir_dev, int32_t ir_len,
-                     int32_t N, int32_t hop, float gain, float *scratch_dev, float *out_dev);
+                     int32_t N, int32_t hop, float gain, float *scratch_dev, int32_t accumulate, float *out_dev);
 
 /* Backward of dgc_partconv (linear in x and in ir): g_x [V][T] (overwritten, or += when accumulate_gx)
  * and/or g_ir [ir_len]; pass NULL for the one that is not needed.  The reference defines no backward
