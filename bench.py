@@ -325,6 +325,99 @@ def run_ours(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
+
+# --------------------------------------------------------------------------------------------------
+# training-step workload (BASELINE.json configs[4]): 32 voices per GPU, controller MLP 2-512-512-512-165,
+# harmonic+noise synthesis, 1 s learnable IR reverb, multi-scale spectral loss, backward, gradient
+# all-reduce (NCCL) and one Adam step
+# --------------------------------------------------------------------------------------------------
+def run_train(args, rank, world, local_rank):
+    import torch
+    import torch.distributed as dist
+    import dgen_b200
+    from dgen_b200 import sharding, trainer as tr, workloads as wl
+
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    ctx = dgen_b200.Context(local_rank)
+    B = args.voices if args.voices > 0 else 32
+    T, K, F, sr, NB, NT = CFG["T"], CFG["K"], CFG["F"], CFG["sr"], CFG["nbands"], CFG["taps"]
+    d = wl.harmonic_noise_inputs(SEED + 100 * rank, B=B, T=T, K=K, F=F, sr=sr, nbands=NB, taps=NT)
+    tg = wl.harmonic_noise_inputs(SEED + 100 * rank + 1, B=B, T=T, K=K, F=F, sr=sr, nbands=NB, taps=NT)
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    pin = lambda a: torch.from_numpy(np.ascontiguousarray(a)).pin_memory()
+    model = tr.HarmonicModel(ctx, B, T, K=K, F=F, sr=sr, nbands=NB, taps=NT, hidden=512, ir_len=16000, conv_n=2048,
+                             conv_hop=1024, sizes=SIZES, seed=7, global_voices=B * world)
+    # target: rendered from seed+1 controls (setup, untimed)
+    G = {k: dev(v) for k, v in tg.items() if isinstance(v, np.ndarray)}
+    target = ctx.harmonic_render(G["f0"], G["uv"], G["amps"], G["gain"], T, sr)
+    ctx.fir_noise(G["noise"], ctx.bands_to_taps(G["bands"], G["W"]), G["noise_gain"], out=target, accumulate=True)
+    host = dict(X=tr.features_from_controls(d["f0"], d["gain"]), f0=d["f0"], uv=d["uv"], gain=d["gain"],
+                noise_gain=d["noise_gain"], noise=d["noise"], W=d["W"], target=target.cpu().numpy())
+    order = ("X", "f0", "uv", "gain", "noise_gain", "noise", "W", "target")
+    P = {k: pin(host[k]) for k in order}
+    D = {k: dev(host[k]) for k in order}
+    dargs = [D[k] for k in order]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        model.step(*dargs)
+    barrier()
+    l0 = ctx.launch_count()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    barrier()
+    for s in range(args.steps):
+        evs[s][0].record()
+        loss = model.step(*dargs)
+        evs[s][1].record()
+    barrier()
+    launches = ctx.launch_count() - l0
+    total_ms = sum(a.elapsed_time(b) for a, b in evs)
+    # end to end: the step's inputs come from pinned host memory, the loss goes back to the host
+    e2e_ms = 0.0
+    for s in range(args.steps):
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for k in order:
+            D[k].copy_(P[k], non_blocking=True)
+        loss = model.step(*dargs)
+        loss_host = float(loss.cpu()[0])
+        b.record()
+        torch.cuda.synchronize()
+        e2e_ms += a.elapsed_time(b)
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    total_ms, e2e_ms = sharding.max_over_ranks([total_ms, e2e_ms], device="cuda")
+    glob_loss = sharding.global_mean_loss(loss_host, B, device="cuda")
+    if rank == 0:
+        ms = total_ms / args.steps
+        h2d = 4 * sum(int(P[k].numel()) for k in order)
+        line = {"metric": "ms/train step", "value": ms, "unit": "ms", "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": False, "scaling": "weak",
+                "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": {"workload": "full training step (BASELINE.json configs[4])", "voices_per_gpu": B,
+                           "global_voices": B * world, "frames": T, "harmonics": K, "control_frames": F,
+                           "controller": "MLP 2-512-512-512-165 fp32", "ir_taps": 16000, "fft_sizes": list(SIZES),
+                           "optimizer": "Adam lr 1e-3", "parallelism": "dp%d, NCCL all-reduce of %d gradients"
+                           % (world, model.n_params), "l2": "working set (>1 GB per step) exceeds L2"},
+                "samples_per_s": B * world * T / (ms * 1e-3), "clocks": clocks,
+                "e2e": {"value": e2e_ms / args.steps, "unit": "ms", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 8},
+                "gpu_launches": int(launches), "loss": glob_loss}
+        print(json.dumps(line))
+    ctx.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -332,6 +425,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--workload", default="fwd_loss", choices=["fwd_loss", "train"],
+                    help="fwd_loss: synthesis forward + loss (the headline metric); train: full training step")
     ap.add_argument("--voices", type=int, default=0,
                     help="voices per GPU (default: the configuration's 16); other values are for profiling "
                          "captures and scaling studies, not for the headline number")
@@ -349,7 +444,10 @@ def main():
         return
     if args.warmup < 3:
         args.warmup = 3
-    run_ours(args, rank, world, local_rank)
+    if args.workload == "train":
+        run_train(args, rank, world, local_rank)
+    else:
+        run_ours(args, rank, world, local_rank)
 
 
 if __name__ == "__main__":

@@ -18,7 +18,7 @@ constexpr int BM = 128, BN = 128, BK = 8, TM = 8, TN = 8;
 template <bool TA, bool TB, int EPI>
 __global__ void __launch_bounds__(256)
 sgemm_kernel(const float *__restrict__ A, const float *__restrict__ B, const float *__restrict__ bias, int M, int N,
-             int K, float *__restrict__ C) {
+             int K, int k_per_split, float *__restrict__ C) {
   __shared__ float As[BK][BM + 4];
   __shared__ float Bs[BK][BN + 4];
   const int tid = threadIdx.x;
@@ -30,7 +30,11 @@ sgemm_kernel(const float *__restrict__ A, const float *__restrict__ B, const flo
 #pragma unroll
     for (int j = 0; j < TN; ++j) acc[i][j] = 0.0f;
 
-  for (int k0 = 0; k0 < K; k0 += BK) {
+  // split-K: slice blockIdx.z of the reduction range goes to its own [M][N] slab of C
+  const int k_begin = blockIdx.z * k_per_split;
+  const int k_end = min(K, k_begin + k_per_split);
+  C += (size_t)blockIdx.z * M * N;
+  for (int k0 = k_begin; k0 < k_end; k0 += BK) {
     // stage A tile [BM][BK] and B tile [BK][BN]: 1024 elements each, 4 per thread
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
@@ -38,20 +42,20 @@ sgemm_kernel(const float *__restrict__ A, const float *__restrict__ B, const flo
       if (!TA) {  // A stored [M][K]: consecutive idx walk k fastest
         int m = idx / BK, k = idx % BK;
         int gm = m0 + m, gk = k0 + k;
-        As[k][m] = (gm < M && gk < K) ? A[(size_t)gm * K + gk] : 0.0f;
+        As[k][m] = (gm < M && gk < k_end) ? A[(size_t)gm * K + gk] : 0.0f;
       } else {    // A stored [K][M]: consecutive idx walk m fastest
         int k = idx / BM, m = idx % BM;
         int gm = m0 + m, gk = k0 + k;
-        As[k][m] = (gm < M && gk < K) ? A[(size_t)gk * M + gm] : 0.0f;
+        As[k][m] = (gm < M && gk < k_end) ? A[(size_t)gk * M + gm] : 0.0f;
       }
       if (!TB) {  // B stored [K][N]
         int k = idx / BN, n = idx % BN;
         int gn = n0 + n, gk = k0 + k;
-        Bs[k][n] = (gn < N && gk < K) ? B[(size_t)gk * N + gn] : 0.0f;
+        Bs[k][n] = (gn < N && gk < k_end) ? B[(size_t)gk * N + gn] : 0.0f;
       } else {    // B stored [N][K]
         int n = idx / BK, k = idx % BK;
         int gn = n0 + n, gk = k0 + k;
-        Bs[k][n] = (gn < N && gk < K) ? B[(size_t)gn * K + gk] : 0.0f;
+        Bs[k][n] = (gn < N && gk < k_end) ? B[(size_t)gn * K + gk] : 0.0f;
       }
     }
     __syncthreads();
@@ -92,10 +96,40 @@ sgemm_kernel(const float *__restrict__ A, const float *__restrict__ B, const flo
   }
 }
 
+// C[m][n] = sum_z part[z][m][n], z ascending: fixed order, bit-reproducible
+__global__ void splitk_reduce_kernel(const float *__restrict__ part, size_t mn, int splits, float *__restrict__ C) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= mn) return;
+  float acc = 0.0f;
+  for (int z = 0; z < splits; ++z) acc += part[(size_t)z * mn + i];
+  C[i] = acc;
+}
+
 template <bool TA, bool TB, int EPI>
-void launch_sgemm(dgc_ctx *ctx, const float *A, const float *B, const float *bias, int M, int N, int K, float *C) {
-  dim3 grid(dgc_div_up(N, BN), dgc_div_up(M, BM));
-  sgemm_kernel<TA, TB, EPI><<<grid, 256, 0, ctx->stream>>>(A, B, bias, M, N, K, C);
+int32_t launch_sgemm(dgc_ctx *ctx, const float *A, const float *B, const float *bias, int M, int N, int K, float *C) {
+  const int tiles = dgc_div_up(N, BN) * dgc_div_up(M, BM);
+  int splits = 1;
+  if (EPI == 0 && tiles < ctx->sm_count && K >= 2048) {
+    // few output tiles and a long reduction (weight gradients): split the reduction over blocks
+    splits = (2 * ctx->sm_count + tiles - 1) / tiles;
+    if (splits > K / 256) splits = K / 256;
+    if (splits < 1) splits = 1;
+  }
+  if (splits == 1) {
+    dim3 grid(dgc_div_up(N, BN), dgc_div_up(M, BM));
+    sgemm_kernel<TA, TB, EPI><<<grid, 256, 0, ctx->stream>>>(A, B, bias, M, N, K, K, C);
+    return DGC_OK;
+  }
+  int kps = dgc_div_up(dgc_div_up(K, splits), BK) * BK;
+  splits = dgc_div_up(K, kps);
+  float *part = dgc_ctx_scratch(ctx, (uint64_t)splits * M * N + 4);
+  if (!part) return DGC_ERR_OOM;
+  dim3 grid(dgc_div_up(N, BN), dgc_div_up(M, BM), splits);
+  sgemm_kernel<TA, TB, EPI><<<grid, 256, 0, ctx->stream>>>(A, B, bias, M, N, K, kps, part);
+  ctx->launches++;
+  size_t mn = (size_t)M * N;
+  splitk_reduce_kernel<<<dgc_div_up((int64_t)mn, 256), 256, 0, ctx->stream>>>(part, mn, splits, C);
+  return DGC_OK;
 }
 
 // dZ = dC * (1 - C^2) in place-compatible form (tanh'), or copy when act == 0
@@ -153,9 +187,11 @@ DGC_EXPORT int32_t dgc_linear_fwd(dgc_ctx *ctx, const float *a_dev, const float 
   DGC_REQUIRE(ctx, M > 0 && K > 0 && N > 0, "size out of range");
   DGC_REQUIRE(ctx, act == 0 || act == 1, "act must be 0 (none) or 1 (tanh)");
   DGC_REQUIRE(ctx, act == 0 || bias_dev, "tanh layers need a bias");
-  if (act == 1) launch_sgemm<false, false, 2>(ctx, a_dev, w_dev, bias_dev, M, N, K, c_dev);
-  else if (bias_dev) launch_sgemm<false, false, 1>(ctx, a_dev, w_dev, bias_dev, M, N, K, c_dev);
-  else launch_sgemm<false, false, 0>(ctx, a_dev, w_dev, nullptr, M, N, K, c_dev);
+  int32_t rc;
+  if (act == 1) rc = launch_sgemm<false, false, 2>(ctx, a_dev, w_dev, bias_dev, M, N, K, c_dev);
+  else if (bias_dev) rc = launch_sgemm<false, false, 1>(ctx, a_dev, w_dev, bias_dev, M, N, K, c_dev);
+  else rc = launch_sgemm<false, false, 0>(ctx, a_dev, w_dev, nullptr, M, N, K, c_dev);
+  if (rc != DGC_OK) return rc;
   DGC_LAUNCHED(ctx, "linear_fwd");
   return DGC_OK;
 }
@@ -175,11 +211,13 @@ DGC_EXPORT int32_t dgc_linear_bwd(dgc_ctx *ctx, const float *a_dev, const float 
     DGC_LAUNCHED(ctx, "bias_grad");
   }
   // dW[K][N] = A^T[K][M] * dZ[M][N]
-  launch_sgemm<true, false, 0>(ctx, a_dev, dz_dev, nullptr, K, N, M, dw_dev);
+  int32_t rc = launch_sgemm<true, false, 0>(ctx, a_dev, dz_dev, nullptr, K, N, M, dw_dev);
+  if (rc != DGC_OK) return rc;
   DGC_LAUNCHED(ctx, "linear_bwd_dw");
   if (da_dev) {
     // dA[M][K] = dZ[M][N] * W^T[N][K]
-    launch_sgemm<false, true, 0>(ctx, dz_dev, w_dev, nullptr, M, K, N, da_dev);
+    rc = launch_sgemm<false, true, 0>(ctx, dz_dev, w_dev, nullptr, M, K, N, da_dev);
+    if (rc != DGC_OK) return rc;
     DGC_LAUNCHED(ctx, "linear_bwd_da");
   }
   return DGC_OK;
