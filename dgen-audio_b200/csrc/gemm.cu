@@ -3,10 +3,14 @@
 // The reference expresses a layer as mul + sumAxis over a broadcast [M,N,K] product on the C backend
 // and as 8x8 simdgroup tiles on Metal (Sources/DGen/Tensor.swift:1195-1230, Sources/DGen/Emit+GEMM.swift);
 // parameters live on the host and Adam is a per-element Swift loop (Sources/DGenLazy/Optimizers.swift:164-243).
-// Here activations, weights, gradients and optimiser state stay in HBM; the matmul is a register-tiled
-// SIMT kernel in full fp32 (the gradient tolerance of the path, 1e-3 relative against an fp64
-// evaluation, leaves no room for single-pass TF32).
+// Here activations, weights, gradients and optimiser state stay in HBM.  The matmul runs on the
+// tcgen05 tensor cores in 3xTF32 (tc_gemm.cuh: fp32-grade accuracy, which the gradient tolerance of the
+// path -- 1e-3 relative against an fp64 evaluation -- needs; single-pass TF32 would not do), and a
+// register-tiled SIMT kernel covers small shapes.
+#include <stdlib.h>
+
 #include "common.cuh"
+#include "tc_gemm.cuh"
 
 namespace {
 
@@ -105,9 +109,21 @@ __global__ void splitk_reduce_kernel(const float *__restrict__ part, size_t mn, 
   C[i] = acc;
 }
 
+// true unless DGC_GEMM=simt is set in the environment (keeps the SIMT kernel reachable for comparison)
+bool use_tensor_cores() {
+  static int v = -1;
+  if (v < 0) {
+    const char *e = getenv("DGC_GEMM");
+    v = (e && strcmp(e, "simt") == 0) ? 0 : 1;
+  }
+  return v == 1;
+}
+
 template <bool TA, bool TB, int EPI>
 int32_t launch_sgemm(dgc_ctx *ctx, const float *A, const float *B, const float *bias, int M, int N, int K, float *C) {
-  const int tiles = dgc_div_up(N, BN) * dgc_div_up(M, BM);
+  const bool tc = use_tensor_cores() && (double)M * N * K >= (double)(1 << 21) && K >= 32;
+  const int bm = tc ? dgtc::TBM : BM, bn = tc ? dgtc::TBN : BN;
+  const int tiles = dgc_div_up(N, bn) * dgc_div_up(M, bm);
   int splits = 1;
   if (EPI == 0 && tiles < ctx->sm_count && K >= 2048) {
     // few output tiles and a long reduction (weight gradients): split the reduction over blocks
@@ -115,20 +131,30 @@ int32_t launch_sgemm(dgc_ctx *ctx, const float *A, const float *B, const float *
     if (splits > K / 256) splits = K / 256;
     if (splits < 1) splits = 1;
   }
-  if (splits == 1) {
-    dim3 grid(dgc_div_up(N, BN), dgc_div_up(M, BM));
-    sgemm_kernel<TA, TB, EPI><<<grid, 256, 0, ctx->stream>>>(A, B, bias, M, N, K, K, C);
-    return DGC_OK;
+  int kps = K;
+  float *dst = C;
+  if (splits > 1) {
+    kps = dgc_div_up(dgc_div_up(K, splits), 32) * 32;
+    splits = dgc_div_up(K, kps);
+    dst = dgc_ctx_scratch(ctx, (uint64_t)splits * M * N + 4);
+    if (!dst) return DGC_ERR_OOM;
   }
-  int kps = dgc_div_up(dgc_div_up(K, splits), BK) * BK;
-  splits = dgc_div_up(K, kps);
-  float *part = dgc_ctx_scratch(ctx, (uint64_t)splits * M * N + 4);
-  if (!part) return DGC_ERR_OOM;
-  dim3 grid(dgc_div_up(N, BN), dgc_div_up(M, BM), splits);
-  sgemm_kernel<TA, TB, EPI><<<grid, 256, 0, ctx->stream>>>(A, B, bias, M, N, K, kps, part);
-  ctx->launches++;
-  size_t mn = (size_t)M * N;
-  splitk_reduce_kernel<<<dgc_div_up((int64_t)mn, 256), 256, 0, ctx->stream>>>(part, mn, splits, C);
+  dim3 grid(dgc_div_up(N, bn), dgc_div_up(M, bm), splits);
+  if (tc) {
+    // tensor-core kernel: operand A is K-major in memory when it is NOT transposed ([M][K]);
+    // operand B is K-major in memory when it IS given transposed ([N][K])
+    auto kern = dgtc::tc_gemm_kernel<!TA, TB, EPI>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, dgtc::SMEM_BYTES);
+    if (e != cudaSuccess) return dgc_fail(ctx, DGC_ERR_CUDA, "tc_gemm smem opt-in: %s", cudaGetErrorString(e));
+    kern<<<grid, 128, dgtc::SMEM_BYTES, ctx->stream>>>(A, B, bias, M, N, K, kps, dst, ctx->status_dev);
+  } else {
+    sgemm_kernel<TA, TB, EPI><<<grid, 256, 0, ctx->stream>>>(A, B, bias, M, N, K, kps, dst);
+  }
+  if (splits > 1) {
+    ctx->launches++;
+    size_t mn = (size_t)M * N;
+    splitk_reduce_kernel<<<dgc_div_up((int64_t)mn, 256), 256, 0, ctx->stream>>>(dst, mn, splits, C);
+  }
   return DGC_OK;
 }
 
