@@ -146,7 +146,7 @@ int32_t launch_sgemm(dgc_ctx *ctx, const float *A, const float *B, const float *
     auto kern = dgtc::tc_gemm_kernel<!TA, TB, EPI>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, dgtc::SMEM_BYTES);
     if (e != cudaSuccess) return dgc_fail(ctx, DGC_ERR_CUDA, "tc_gemm smem opt-in: %s", cudaGetErrorString(e));
-    kern<<<grid, 128, dgtc::SMEM_BYTES, ctx->stream>>>(A, B, bias, M, N, K, kps, dst, ctx->status_dev);
+    kern<<<grid, dgtc::THREADS, dgtc::SMEM_BYTES, ctx->stream>>>(A, B, bias, M, N, K, kps, dst, ctx->status_dev);
   } else {
     sgemm_kernel<TA, TB, EPI><<<grid, 256, 0, ctx->stream>>>(A, B, bias, M, N, K, kps, dst);
   }
@@ -171,22 +171,32 @@ __global__ void act_bwd_kernel(const float *__restrict__ dC, const float *__rest
   dZ[i] = g;
 }
 
-// db[n] = sum_m dZ[m][n]: block per 32 columns, fixed-order tree -> bit-reproducible
+// db[n] = sum_m dZ[m][n].  Stage 1: block (32 columns x 1024 rows) sums its rows in a fixed order into
+// part[chunk][n]; stage 2 adds the chunks in index order: bit-reproducible.
 __global__ void __launch_bounds__(256)
-bias_grad_kernel(const float *__restrict__ dZ, int M, int N, float *__restrict__ db) {
+bias_grad_kernel(const float *__restrict__ dZ, int M, int N, float *__restrict__ part) {
   __shared__ float sh[8][33];
   const int col = blockIdx.x * 32 + (threadIdx.x & 31), rg = threadIdx.x >> 5;
+  const int m_begin = blockIdx.y * 1024, m_end = min(M, m_begin + 1024);
   float acc = 0.0f;
   if (col < N)
-    for (int m = rg; m < M; m += 8) acc += dZ[(size_t)m * N + col];
+    for (int m = m_begin + rg; m < m_end; m += 8) acc += dZ[(size_t)m * N + col];
   sh[rg][threadIdx.x & 31] = acc;
   __syncthreads();
   if (rg == 0 && col < N) {
     float t = 0.0f;
 #pragma unroll
     for (int r = 0; r < 8; ++r) t += sh[r][threadIdx.x & 31];
-    db[col] = t;
+    part[(size_t)blockIdx.y * N + col] = t;
   }
+}
+
+__global__ void bias_grad_reduce_kernel(const float *__restrict__ part, int chunks, int N, float *__restrict__ db) {
+  int col = blockIdx.x * blockDim.x + threadIdx.x;
+  if (col >= N) return;
+  float t = 0.0f;
+  for (int c = 0; c < chunks; ++c) t += part[(size_t)c * N + col];
+  db[col] = t;
 }
 
 __global__ void adam_kernel(float *__restrict__ theta, const float *__restrict__ g, float *__restrict__ m,
@@ -233,8 +243,13 @@ DGC_EXPORT int32_t dgc_linear_bwd(dgc_ctx *ctx, const float *a_dev, const float 
   act_bwd_kernel<<<dgc_div_up((int64_t)n, 256), 256, 0, ctx->stream>>>(dc_dev, c_dev, n, act, dz_dev);
   DGC_LAUNCHED(ctx, "act_bwd");
   if (dbias_dev) {
-    bias_grad_kernel<<<dgc_div_up(N, 32), 256, 0, ctx->stream>>>(dz_dev, M, N, dbias_dev);
+    const int chunks = dgc_div_up(M, 1024);
+    float *part = dgc_ctx_scratch(ctx, (uint64_t)chunks * N + 4);
+    if (!part) return DGC_ERR_OOM;
+    bias_grad_kernel<<<dim3(dgc_div_up(N, 32), chunks), 256, 0, ctx->stream>>>(dz_dev, M, N, part);
     DGC_LAUNCHED(ctx, "bias_grad");
+    bias_grad_reduce_kernel<<<dgc_div_up(N, 128), 128, 0, ctx->stream>>>(part, chunks, N, dbias_dev);
+    DGC_LAUNCHED(ctx, "bias_grad_reduce");
   }
   // dW[K][N] = A^T[K][M] * dZ[M][N]
   int32_t rc = launch_sgemm<true, false, 0>(ctx, a_dev, dz_dev, nullptr, K, N, M, dw_dev);

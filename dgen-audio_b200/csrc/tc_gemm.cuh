@@ -4,10 +4,11 @@
 // value the tensor core sees when it truncates x to TF32 and lo = x - hi (exact); the product is
 // accumulated as hi*hi + hi*lo + lo*hi in fp32 in TMEM (missing term lo*lo ~ 2^-22 relative).
 //
-// One CTA (128 threads) owns a 128 x 128 output tile.  Per k-tile of 32 the four warps load the fp32
+// One CTA (256 threads) owns a 128 x 128 output tile.  Per k-tile of 32 the eight warps load the fp32
 // operands from global memory, split them and store hi / lo parts to shared memory in the canonical
-// K-major no-swizzle layout of the UMMA shared-memory descriptor (8-row x 16-byte core matrices; rows
-// of a core matrix 16 bytes apart, 8-row groups SBO apart, 16-byte k-chunks LBO apart).  One elected
+// K-major no-swizzle layout of the UMMA shared-memory descriptor (8-row x 16-byte core matrices; rows of
+// a core matrix 16 bytes apart, 8-row groups SBO apart, 16-byte k-chunks LBO apart); operands that are
+// contiguous along m / n in memory are transposed on the way (vector loads, scalar stores).  One elected
 // thread issues 12 tcgen05.mma (4 k-steps of 8 x 3 products) and commits them to an mbarrier; two
 // shared-memory stages let the loads of tile t+1 overlap the MMAs of tile t.  The epilogue reads the
 // accumulators with tcgen05.ld (32 lanes x 32 columns per warp), applies bias / tanh and stores.
@@ -19,28 +20,42 @@
 
 namespace dgtc {
 
-constexpr int TBM = 128, TBN = 128, TBK = 32;
+constexpr int TBM = 128, TBN = 128, TBK = 32, THREADS = 256;
 constexpr int CHUNKS = TBK / 4;                 // 16-byte k-chunks per row
+// K-major canonical layout (operand contiguous along k in memory): 16-byte unit (row r, k-chunk kc) at
+// kc * LBO + r * 16; 8-row groups SBO = 128 bytes apart.
 constexpr int LBO_BYTES = TBM * 16 + 16;        // k-chunk stride (one 16-byte pad against bank conflicts)
 constexpr int SBO_BYTES = 8 * 16;               // 8-row group stride
-constexpr int OPER_BYTES = CHUNKS * LBO_BYTES;  // one operand part (hi or lo) of one stage
+// MN-major canonical layout (operand contiguous along m/n in memory): 16-byte unit = 4 consecutive m/n at one
+// k, at (mn/4) * SBO_MN + (k % 8) * 16 + (k / 8) * LBO_MN (core matrix = 8 k-rows of 16 bytes, contiguous).
+constexpr int SBO_MN_BYTES = 8 * 16;
+constexpr int LBO_MN_BYTES = (TBM / 4) * SBO_MN_BYTES + 16;
+// one operand part (hi or lo) of one stage: room for either layout
+constexpr int OPER_BYTES = (CHUNKS * LBO_BYTES > (TBK / 8) * LBO_MN_BYTES) ? CHUNKS * LBO_BYTES : (TBK / 8) * LBO_MN_BYTES;
 constexpr int STAGE_BYTES = 4 * OPER_BYTES;     // A_hi, A_lo, B_hi, B_lo
 constexpr int SMEM_BYTES = 2 * STAGE_BYTES + 64;
 constexpr uint32_t SPIN_LIMIT = 1u << 24;
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
+template <bool KMAJOR>
 __device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {
   // start address [0,14), leading byte offset [16,30), stride byte offset [32,46) (all >> 4),
   // descriptor version 1 at [46,48), layout type 0 (no swizzle) at [61,64)
-  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(LBO_BYTES >> 4) << 16) |
-         ((uint64_t)(SBO_BYTES >> 4) << 32) | (1ull << 46);
+  constexpr uint64_t lbo = KMAJOR ? LBO_BYTES : LBO_MN_BYTES, sbo = KMAJOR ? SBO_BYTES : SBO_MN_BYTES;
+  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((lbo >> 4) << 16) | ((sbo >> 4) << 32) | (1ull << 46);
 }
 
-// instruction descriptor: D = F32 (1 << 4), A = B = TF32 (2 << 7, 2 << 10), both K-major, N >> 3 at 17, M >> 4 at 24
-constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(TBN >> 3) << 17) | ((uint32_t)(TBM >> 4) << 24);
+// instruction descriptor: D = F32 (1 << 4), A = B = TF32 (2 << 7, 2 << 10), A / B major (0 = K, 1 = MN) at
+// bits 15 / 16, N >> 3 at 17, M >> 4 at 24
+template <bool A_KMAJOR, bool B_KMAJOR>
+struct IDesc {
+  static constexpr uint32_t value = (1u << 4) | (2u << 7) | (2u << 10) | (A_KMAJOR ? 0u : (1u << 15)) |
+                                    (B_KMAJOR ? 0u : (1u << 16)) | ((uint32_t)(TBN >> 3) << 17) |
+                                    ((uint32_t)(TBM >> 4) << 24);
+};
 
-__device__ __forceinline__ void mma_tf32(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t accumulate) {
+__device__ __forceinline__ void mma_tf32(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t IDESC, uint32_t accumulate) {
   asm volatile(
       "{\n\t"
       ".reg .pred p;\n\t"
@@ -81,21 +96,19 @@ __device__ __forceinline__ void split_tf32(float x, float &hi, float &lo) {
   lo = x - hi;
 }
 
-// element (row r, k index kk) of a K-major canonical operand part
-__device__ __forceinline__ int oper_off(int r, int kk) { return (kk >> 2) * LBO_BYTES + r * 16 + (kk & 3) * 4; }
-
-// Loads one 128 x 32 operand tile (rows r0.., k range k0..) and writes its hi / lo parts.
-// ROWMAJOR_K: element (r, k) at src[r * ld + k] (k contiguous); else at src[k * ld + r] (r contiguous).
+// Loads one 128 x 32 operand tile (rows r0.., k range k0..) and writes its hi / lo parts (256 threads).
+// ROWMAJOR_K: element (r, k) at src[r * ld + k] (k contiguous) -> K-major canonical layout;
+// else at src[k * ld + r] (r contiguous), transposed while it is stored.
 template <bool ROWMAJOR_K>
 __device__ __forceinline__ void load_operand(const float *__restrict__ src, int ld, int rows, int r0, int k0, int k_end,
                                              char *hi_part, char *lo_part, int tid) {
+  const bool vec_ok = ((ld & 3) == 0) && ((((uintptr_t)src) & 15) == 0);
   if (ROWMAJOR_K) {
-    // 8 lanes cover the 8 k-chunks of a row (128 contiguous bytes), 16 rows per pass, 8 passes
+    // 8 lanes cover the 8 k-chunks of a row (128 contiguous bytes), 32 rows per pass, 4 passes
     const int kc = tid & 7, rr = tid >> 3;
-    const bool vec_ok = ((ld & 3) == 0) && ((((uintptr_t)src) & 15) == 0);
 #pragma unroll
-    for (int p = 0; p < 8; ++p) {
-      const int r = rr + 16 * p, gr = r0 + r, gk = k0 + 4 * kc;
+    for (int p = 0; p < 4; ++p) {
+      const int r = rr + 32 * p, gr = r0 + r, gk = k0 + 4 * kc;
       float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
       if (gr < rows) {
         const float *q = src + (size_t)gr * ld + gk;
@@ -114,20 +127,35 @@ __device__ __forceinline__ void load_operand(const float *__restrict__ src, int 
       *reinterpret_cast<float4 *>(lo_part + off) = l;
     }
   } else {
-    // r contiguous in memory: a warp reads 32 consecutive rows of one k (128 bytes); 4 warps take k = w, w+4, ...
-    const int lane = tid & 31, w = tid >> 5;
+    // operand contiguous along m / n in memory: vector loads along m / n, transposed into the K-major
+    // layout with scalar stores.  A warp moves 8 k x 4 units (16 rows): per k 64 contiguous bytes of global
+    // memory; a store instruction (one of the four components) hits 8 k x 4 rows with 2-way bank conflicts.
+    // (An MN-major shared-memory descriptor with no swizzle was tried instead of this transposition and
+    // produced zeros on this part, so both operands always use the K-major descriptor.)
 #pragma unroll
-    for (int kq = 0; kq < TBK / 4; ++kq) {
-      const int kk = w + 4 * kq, gk = k0 + kk;
+    for (int p = 0; p < 4; ++p) {
+      const int idx = p * THREADS + tid;
+      const int kk = (idx & 7) + 8 * (idx >> 8), u = ((idx >> 3) & 3) + 4 * ((idx >> 5) & 7);
+      const int gk = k0 + kk, gr = r0 + 4 * u;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (gk < k_end) {
+        const float *q = src + (size_t)gk * ld + gr;
+        if (vec_ok && gr + 3 < rows) v = *reinterpret_cast<const float4 *>(q);
+        else {
+          if (gr < rows) v.x = q[0];
+          if (gr + 1 < rows) v.y = q[1];
+          if (gr + 2 < rows) v.z = q[2];
+          if (gr + 3 < rows) v.w = q[3];
+        }
+      }
+      const float vv[4] = {v.x, v.y, v.z, v.w};
+      const int base = (kk >> 2) * LBO_BYTES + (kk & 3) * 4 + (4 * u) * 16;
 #pragma unroll
-      for (int p = 0; p < 4; ++p) {
-        const int r = lane + 32 * p, gr = r0 + r;
-        float v = (gr < rows && gk < k_end) ? src[(size_t)gk * ld + gr] : 0.0f;
+      for (int j = 0; j < 4; ++j) {
         float h, l;
-        split_tf32(v, h, l);
-        const int off = oper_off(r, kk);
-        *reinterpret_cast<float *>(hi_part + off) = h;
-        *reinterpret_cast<float *>(lo_part + off) = l;
+        split_tf32(vv[j], h, l);
+        *reinterpret_cast<float *>(hi_part + base + j * 16) = h;
+        *reinterpret_cast<float *>(lo_part + base + j * 16) = l;
       }
     }
   }
@@ -136,7 +164,7 @@ __device__ __forceinline__ void load_operand(const float *__restrict__ src, int 
 // A_KMAJOR: A stored [M][K]; else stored [K][M].  B_KMAJOR: B stored [N][K]; else stored [K][N].
 // EPI 0: C = acc ; 1: + bias[n] ; 2: tanh(acc + bias[n]).  blockIdx.z selects a k-slice (split-K slab of C).
 template <bool A_KMAJOR, bool B_KMAJOR, int EPI>
-__global__ void __launch_bounds__(128, 1)
+__global__ void __launch_bounds__(THREADS, 1)
 tc_gemm_kernel(const float *__restrict__ A, const float *__restrict__ B, const float *__restrict__ bias, int M, int N,
                int K, int k_per_split, float *__restrict__ C, int32_t *status) {
   extern __shared__ __align__(128) char smem[];
@@ -182,14 +210,16 @@ tc_gemm_kernel(const float *__restrict__ A, const float *__restrict__ B, const f
     if (tid == 0 && ok) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t a_hi = smem_u32(st), a_lo = a_hi + OPER_BYTES, b_hi = a_hi + 2 * OPER_BYTES, b_lo = a_hi + 3 * OPER_BYTES;
+      constexpr uint32_t ID = IDesc<true, true>::value;
 #pragma unroll
       for (int ks = 0; ks < TBK / 8; ++ks) {
-        const uint32_t adv = ks * 2 * LBO_BYTES;  // 8 tf32 = two 16-byte k-chunks
-        const uint64_t dah = make_desc(a_hi + adv), dal = make_desc(a_lo + adv);
-        const uint64_t dbh = make_desc(b_hi + adv), dbl = make_desc(b_lo + adv);
-        mma_tf32(tmem_d, dal, dbh, (kt | ks) ? 1u : 0u);   // small terms first
-        mma_tf32(tmem_d, dah, dbl, 1u);
-        mma_tf32(tmem_d, dah, dbh, 1u);
+        // 8 tf32 along k = two 16-byte k-chunks
+        const uint32_t adv = ks * 2 * LBO_BYTES;
+        const uint64_t dah = make_desc<true>(a_hi + adv), dal = make_desc<true>(a_lo + adv);
+        const uint64_t dbh = make_desc<true>(b_hi + adv), dbl = make_desc<true>(b_lo + adv);
+        mma_tf32(tmem_d, dal, dbh, ID, (kt | ks) ? 1u : 0u);   // small terms first
+        mma_tf32(tmem_d, dah, dbl, ID, 1u);
+        mma_tf32(tmem_d, dah, dbh, ID, 1u);
       }
       commit_to(smem_u32(&bars[s]));
     }
@@ -200,11 +230,13 @@ tc_gemm_kernel(const float *__restrict__ A, const float *__restrict__ B, const f
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 
   if (ok && KT > 0) {
-    const int gm = m0 + warp * 32 + lane;
+    // warp w may touch tensor-memory lanes 32 * (w % 4) ..; warps 0-3 take columns 0..63, warps 4-7 the rest
+    const int lane_base = (warp & 3) * 32, col_base = (warp >> 2) * (TBN / 2);
+    const int gm = m0 + lane_base + lane;
 #pragma unroll 1
-    for (int c0 = 0; c0 < TBN; c0 += 32) {
+    for (int c0 = col_base; c0 < col_base + TBN / 2; c0 += 32) {
       uint32_t r[32];
-      const uint32_t taddr = tmem_d + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0;
+      const uint32_t taddr = tmem_d + ((uint32_t)lane_base << 16) + (uint32_t)c0;
       asm volatile(
           "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
           "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -239,8 +271,8 @@ tc_gemm_kernel(const float *__restrict__ A, const float *__restrict__ B, const f
     }
   } else if (KT == 0) {
     // empty reduction range: the slab is zero
-    const int gm = m0 + warp * 32 + lane;
-    if (gm < M)
+    const int gm = m0 + (warp & 3) * 32 + lane;
+    if (gm < M && warp < 4)
       for (int c = 0; c < TBN; ++c)
         if (n0 + c < N) C[(size_t)gm * N + n0 + c] = 0.0f;
   }
