@@ -46,6 +46,8 @@ float *dgc_ctx_scratch(dgc_ctx *ctx, uint64_t nfloats);
 const int *dgc_ctx_row_ranges(dgc_ctx *ctx, int F, int T);
 const float *dgc_ctx_hann_sym(dgc_ctx *ctx, int N);
 const float *dgc_ctx_hann_per(dgc_ctx *ctx, int N);
+// C[M][N] = A[M][K] * B[N][K]^T on the matmul path of gemm.cu
+int32_t dgc_gemm_nt(dgc_ctx *ctx, const float *a, const float *b, int M, int N, int K, float *c);
 const float2 *dgc_ctx_twiddles(dgc_ctx *ctx, int N);
 
 #define DGC_CUDA(ctx, call)                                                                  \

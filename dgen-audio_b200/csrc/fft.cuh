@@ -9,6 +9,12 @@
 
 namespace dgfft {
 
+// Shared-memory index padding: one extra float2 after every 16, so that the power-of-two strides of the
+// Stockham scatter (stride R after the first stage) spread over all banks.  Every access to a transform
+// buffer goes through pad(); a buffer of N points occupies padded(N) float2.
+__host__ __device__ constexpr int padded(int n) { return n + (n >> 4); }
+__device__ __forceinline__ int pad(int i) { return i + (i >> 4); }
+
 __device__ __forceinline__ float2 cmul(float2 a, float2 b) {
   return make_float2(fmaf(a.x, b.x, -a.y * b.y), fmaf(a.x, b.y, a.y * b.x));
 }
@@ -73,7 +79,7 @@ __device__ __forceinline__ void stage(const float2 *__restrict__ in, float2 *__r
     const int k = j & (Ns - 1);
     float2 v[R];
 #pragma unroll
-    for (int t = 0; t < R; ++t) v[t] = in[j + t * (N / R)];
+    for (int t = 0; t < R; ++t) v[t] = in[pad(j + t * (N / R))];
     if (Ns > 1) {
       const int step = N / (Ns * R);
 #pragma unroll
@@ -86,7 +92,7 @@ __device__ __forceinline__ void stage(const float2 *__restrict__ in, float2 *__r
     dftR<R, INV>(v);
     const int j0 = (j - k) * R + k;
 #pragma unroll
-    for (int t = 0; t < R; ++t) out[j0 + t * Ns] = v[t];
+    for (int t = 0; t < R; ++t) out[pad(j0 + t * Ns)] = v[t];
   }
 }
 

@@ -240,6 +240,8 @@ DGC_EXPORT int32_t dgc_bands_to_taps(dgc_ctx *ctx, const float *bands_dev, const
   if (!ctx) return DGC_ERR_INVALID;
   DGC_REQUIRE(ctx, bands_dev && w_dev && taps_dev, "null pointer");
   DGC_REQUIRE(ctx, rows > 0 && nbands > 0 && taps > 0, "size out of range");
+  // large row counts go to the tensor-core matmul (taps = bands * W^T); the shared-memory kernel keeps small ones
+  if ((double)rows * nbands * taps >= (double)(1 << 24)) return dgc_gemm_nt(ctx, bands_dev, w_dev, rows, taps, nbands, taps_dev);
   size_t smem = ((((size_t)taps * (nbands | 1) + 3) & ~(size_t)3) + (size_t)nbands * 16) * sizeof(float);
   DGC_REQUIRE(ctx, smem <= 200 * 1024, "taps*nbands too large for shared memory");
   DGC_CUDA(ctx, cudaFuncSetAttribute(bands_to_taps_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));

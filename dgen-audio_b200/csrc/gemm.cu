@@ -216,6 +216,14 @@ __global__ void adam_kernel(float *__restrict__ theta, const float *__restrict__
 
 }  // namespace
 
+// C[M][N] = A[M][K] * B[N][K]^T, no epilogue (used for the band -> tap map)
+int32_t dgc_gemm_nt(dgc_ctx *ctx, const float *a, const float *b, int M, int N, int K, float *c) {
+  int32_t rc = launch_sgemm<false, true, 0>(ctx, a, b, nullptr, M, N, K, c);
+  if (rc != DGC_OK) return rc;
+  ctx->launches++;
+  return dgc_check_launch(ctx, "gemm_nt");
+}
+
 DGC_EXPORT int32_t dgc_linear_fwd(dgc_ctx *ctx, const float *a_dev, const float *w_dev, const float *bias_dev,
                                   int32_t M, int32_t K, int32_t N, int32_t act, float *c_dev) {
   if (!ctx) return DGC_ERR_INVALID;

@@ -51,8 +51,9 @@ mss_fwd_kernel(const float *__restrict__ pred, const float *__restrict__ target,
                float *__restrict__ part_log) {
   constexpr int G = N / 8;                    // threads per transform
   constexpr int NF = LOSS_THREADS / G;        // transforms per block
-  __shared__ float2 bufa[NF * N];
-  __shared__ float2 bufb[NF * N];
+  constexpr int PN = padded(N);
+  __shared__ float2 bufa[NF * PN];
+  __shared__ float2 bufb[NF * PN];
   __shared__ float red[LOSS_THREADS / 32];
   const int tid = threadIdx.x, f = tid / G, lt = tid % G;
   const int b = blockIdx.y;
@@ -60,7 +61,7 @@ mss_fwd_kernel(const float *__restrict__ pred, const float *__restrict__ target,
   const bool valid = h < H;
   const int t_base = h * hop - (N - 1);
   const float *x1 = pred + (size_t)b * T, *x2 = target + (size_t)b * T;
-  float2 *a = bufa + f * N, *bb = bufb + f * N;
+  float2 *a = bufa + f * PN, *bb = bufb + f * PN;
 #pragma unroll
   for (int q = 0; q < 8; ++q) {
     int i = lt + q * G, t = t_base + i;
@@ -69,7 +70,7 @@ mss_fwd_kernel(const float *__restrict__ pred, const float *__restrict__ target,
       float w = __ldg(&window[i]);
       v = make_float2(x1[t] * w, x2[t] * w);
     }
-    a[i] = v;
+    a[pad(i)] = v;
   }
   __syncthreads();
   float2 *z = fft_block<N, false>(a, bb, lt, tw);
@@ -78,13 +79,13 @@ mss_fwd_kernel(const float *__restrict__ pred, const float *__restrict__ target,
   for (int q = 0; q < 4; ++q) {
     int k = lt + q * G;  // 0 .. N/2-1
     float2 X1, X2;
-    unpack(z[k], z[(N - k) & (N - 1)], X1, X2);
+    unpack(z[pad(k)], z[pad((N - k) & (N - 1))], X1, X2);
     float m1 = sqrtf(X1.x * X1.x + X1.y * X1.y), m2 = sqrtf(X2.x * X2.x + X2.y * X2.y);
     lin += fabsf(m1 - m2);
     lg += fabsf(__logf(m1 + LOG_EPS) - __logf(m2 + LOG_EPS));
   }
   if (lt == 0) {  // Nyquist bin
-    float2 zn = z[N / 2];
+    float2 zn = z[pad(N / 2)];
     float m1 = fabsf(zn.x), m2 = fabsf(zn.y);
     lin += fabsf(m1 - m2);
     lg += fabsf(__logf(m1 + LOG_EPS) - __logf(m2 + LOG_EPS));
@@ -190,22 +191,23 @@ mss_bwd_kernel(const float *__restrict__ pred, const float *__restrict__ target,
   using Gm = BwdGeom<N>;
   constexpr int G = Gm::G, NF = Gm::NF, WR = Gm::WR;
   extern __shared__ float2 sm2[];
-  float2 *bufa = sm2, *bufb = sm2 + NF * N, *bufg = sm2 + 2 * NF * N;
-  float *tile = reinterpret_cast<float *>(sm2 + 3 * NF * N);
+  constexpr int PN = padded(N);
+  float2 *bufa = sm2, *bufb = sm2 + NF * PN, *bufg = sm2 + 2 * NF * PN;
+  float *tile = reinterpret_cast<float *>(sm2 + 3 * NF * PN);
   const int tid = threadIdx.x, f = tid / G, lt = tid % G;
   const int b = blockIdx.y;
   const int hA = blockIdx.x * S;
   const int p0 = (hA - 1) * hop + 1;          // first owned frame (may be negative for the first block)
   const int owned = S * hop;
   const float *x1 = pred + (size_t)b * T, *x2 = target + (size_t)b * T;
-  float2 *a = bufa + f * N, *bb = bufb + f * N, *gi = bufg + f * N;
+  float2 *a = bufa + f * PN, *bb = bufb + f * PN, *gi = bufg + f * PN;
   for (int o = tid; o < owned; o += LOSS_THREADS) tile[o] = 0.0f;
   const int E = (N - 1) / hop;
   const int nwin = min(S + E, H - hA);        // windows this block must visit
   for (int r0 = 0; r0 < nwin; r0 += WR) {
     const int hr0 = hA + r0;
 #pragma unroll
-    for (int q = 0; q < 8; ++q) gi[lt + q * G] = make_float2(0.f, 0.f);
+    for (int q = 0; q < 8; ++q) gi[pad(lt + q * G)] = make_float2(0.f, 0.f);
     for (int w = 0; w < 2; ++w) {
       const int h = hr0 + 2 * f + w;
       const bool valid = h < H && (h - hA) < nwin;
@@ -218,7 +220,7 @@ mss_bwd_kernel(const float *__restrict__ pred, const float *__restrict__ target,
           float wv = __ldg(&window[i]);
           v = make_float2(x1[t] * wv, x2[t] * wv);
         }
-        a[i] = v;
+        a[pad(i)] = v;
       }
       __syncthreads();
       float2 *z = fft_block<N, false>(a, bb, lt, tw);
@@ -227,7 +229,7 @@ mss_bwd_kernel(const float *__restrict__ pred, const float *__restrict__ target,
         for (int q = 0; q < 4; ++q) {
           int k = lt + q * G;
           float2 X1, X2;
-          unpack(z[k], z[(N - k) & (N - 1)], X1, X2);
+          unpack(z[pad(k)], z[pad((N - k) & (N - 1))], X1, X2);
           float m1 = sqrtf(X1.x * X1.x + X1.y * X1.y), m2 = sqrtf(X2.x * X2.x + X2.y * X2.y);
           float ld = __logf(m1 + LOG_EPS) - __logf(m2 + LOG_EPS);
           float gm = c_lin * sgn(m1 - m2) + c_log * sgn(ld) / (m1 + LOG_EPS);
@@ -235,25 +237,25 @@ mss_bwd_kernel(const float *__restrict__ pred, const float *__restrict__ target,
           float2 gk = make_float2(sc * X1.x, sc * X1.y);
           if (k == 0) {
             // a real bin: only Re contributes to the real part of the synthesis
-            if (w == 0) gi[0].x += gk.x; else gi[0].y += gk.x;
+            if (w == 0) gi[0].x += gk.x; else gi[0].y += gk.x;  // pad(0) == 0
           } else {
             float2 hk = make_float2(0.5f * gk.x, 0.5f * gk.y);
             if (w == 0) {
-              gi[k].x += hk.x; gi[k].y += hk.y;
-              gi[N - k].x += hk.x; gi[N - k].y -= hk.y;
+              gi[pad(k)].x += hk.x; gi[pad(k)].y += hk.y;
+              gi[pad(N - k)].x += hk.x; gi[pad(N - k)].y -= hk.y;
             } else {  // times i: (x, y) -> (-y, x)
-              gi[k].x -= hk.y; gi[k].y += hk.x;
-              gi[N - k].x += hk.y; gi[N - k].y += hk.x;
+              gi[pad(k)].x -= hk.y; gi[pad(k)].y += hk.x;
+              gi[pad(N - k)].x += hk.y; gi[pad(N - k)].y += hk.x;
             }
           }
         }
         if (lt == 0) {
-          float2 zn = z[N / 2];
+          float2 zn = z[pad(N / 2)];
           float m1 = fabsf(zn.x), m2 = fabsf(zn.y);
           float ld = __logf(m1 + LOG_EPS) - __logf(m2 + LOG_EPS);
           float gm = c_lin * sgn(m1 - m2) + c_log * sgn(ld) / (m1 + LOG_EPS);
           float gre = gm / fmaxf(m1, 1e-8f) * zn.x;
-          if (w == 0) gi[N / 2].x += gre; else gi[N / 2].y += gre;
+          if (w == 0) gi[pad(N / 2)].x += gre; else gi[pad(N / 2)].y += gre;
         }
       }
       __syncthreads();
@@ -264,7 +266,7 @@ mss_bwd_kernel(const float *__restrict__ pred, const float *__restrict__ target,
     for (int q = 0; q < 8; ++q) {
       int i = lt + q * G;
       float wv = __ldg(&window[i]);
-      zt[i] = make_float2(zt[i].x * wv, zt[i].y * wv);
+      zt[pad(i)] = make_float2(zt[pad(i)].x * wv, zt[pad(i)].y * wv);
     }
     __syncthreads();
     const float2 *res = in_g ? bufg : bufa;
@@ -276,7 +278,7 @@ mss_bwd_kernel(const float *__restrict__ pred, const float *__restrict__ target,
       float acc = tile[o];
       for (int h = hlo; h <= hhi; ++h) {
         int slot = h - hr0;
-        float2 v = res[(slot >> 1) * N + (p - (h * hop - (N - 1)))];
+        float2 v = res[(slot >> 1) * PN + pad(p - (h * hop - (N - 1)))];
         acc += (slot & 1) ? v.y : v.x;
       }
       tile[o] = acc;
@@ -300,7 +302,7 @@ int32_t launch_bwd(dgc_ctx *ctx, const dgc_mss_params *p, const float *pred, con
   const int E = (N - 1) / hop;
   int S = Gm::WB - E;
   if (S < 1) return dgc_fail(ctx, DGC_ERR_UNSUPPORTED, "hop %d too small for window %d", hop, N);
-  size_t smem = (size_t)3 * Gm::NF * N * sizeof(float2) + (size_t)S * hop * sizeof(float);
+  size_t smem = (size_t)3 * Gm::NF * padded(N) * sizeof(float2) + (size_t)S * hop * sizeof(float);
   if (smem > 200 * 1024) return dgc_fail(ctx, DGC_ERR_UNSUPPORTED, "backward tile does not fit shared memory");
   cudaError_t e = cudaFuncSetAttribute(mss_bwd_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return dgc_fail(ctx, DGC_ERR_CUDA, "mss_bwd smem opt-in: %s", cudaGetErrorString(e));

@@ -27,15 +27,15 @@ template <int N, int SRC, int OUT>
 __global__ void __launch_bounds__(ST_THREADS)
 stft_kernel(const float *__restrict__ x, int T, int hop, int H, const float *__restrict__ window,
             const float2 *__restrict__ tw, float *__restrict__ out) {
-  constexpr int G = N / 8, NF = ST_THREADS / G, NB = N / 2 + 1;
-  __shared__ float2 bufa[NF * N];
-  __shared__ float2 bufb[NF * N];
+  constexpr int G = N / 8, NF = ST_THREADS / G, NB = N / 2 + 1, PN = padded(N);
+  __shared__ float2 bufa[NF * PN];
+  __shared__ float2 bufb[NF * PN];
   const int tid = threadIdx.x, f = tid / G, lt = tid % G;
   const int v = blockIdx.y;
   const int pair = blockIdx.x * NF + f;
   const int h0 = 2 * pair, h1 = h0 + 1;
   const float *xv = x + (size_t)v * T;
-  float2 *a = bufa + f * N, *bb = bufb + f * N;
+  float2 *a = bufa + f * PN, *bb = bufb + f * PN;
 #pragma unroll
   for (int q = 0; q < 8; ++q) {
     int i = lt + q * G;
@@ -54,13 +54,13 @@ stft_kernel(const float *__restrict__ x, int T, int hop, int H, const float *__r
       if (h0 < H && t0 < T) val.x = xv[t0] * w;
       if (h1 < H && t1 < T) val.y = xv[t1] * w;
     }
-    a[i] = val;
+    a[pad(i)] = val;
   }
   __syncthreads();
   float2 *z = fft_block<N, false>(a, bb, lt, tw);
   // bins 0..N/2 of both sequences
   for (int k = lt; k < NB; k += G) {
-    float2 zk = z[k], zn = z[(N - k) & (N - 1)];
+    float2 zk = z[pad(k)], zn = z[pad((N - k) & (N - 1))];
     float2 X0 = make_float2(0.5f * (zk.x + zn.x), 0.5f * (zk.y - zn.y));
     float2 X1 = make_float2(0.5f * (zk.y + zn.y), 0.5f * (zn.x - zk.x));
     if (OUT == 0) {
@@ -134,13 +134,13 @@ template <int N>
 __global__ void __launch_bounds__(ST_THREADS)
 istft_kernel(const float2 *__restrict__ Y, int H, const float *__restrict__ window, const float2 *__restrict__ tw,
              float gain, float *__restrict__ frames) {
-  constexpr int G = N / 8, NF = ST_THREADS / G, NB = N / 2 + 1;
-  __shared__ float2 bufa[NF * N];
-  __shared__ float2 bufb[NF * N];
+  constexpr int G = N / 8, NF = ST_THREADS / G, NB = N / 2 + 1, PN = padded(N);
+  __shared__ float2 bufa[NF * PN];
+  __shared__ float2 bufb[NF * PN];
   const int tid = threadIdx.x, f = tid / G, lt = tid % G;
   const int v = blockIdx.y, pair = blockIdx.x * NF + f;
   const int h0 = 2 * pair, h1 = h0 + 1;
-  float2 *a = bufa + f * N, *bb = bufb + f * N;
+  float2 *a = bufa + f * PN, *bb = bufb + f * PN;
   // z = Y0 + i*Y1 with Hermitian extension: Y[N-k] = conj(Y[k])
 #pragma unroll
   for (int q = 0; q < 8; ++q) {
@@ -150,7 +150,7 @@ istft_kernel(const float2 *__restrict__ Y, int H, const float *__restrict__ wind
     if (h0 < H) y0 = Y[((size_t)v * H + h0) * NB + ks];
     if (h1 < H) y1 = Y[((size_t)v * H + h1) * NB + ks];
     if (k > N / 2) { y0.y = -y0.y; y1.y = -y1.y; }
-    a[k] = make_float2(y0.x - y1.y, y0.y + y1.x);
+    a[pad(k)] = make_float2(y0.x - y1.y, y0.y + y1.x);
   }
   __syncthreads();
   float2 *z = fft_block<N, true>(a, bb, lt, tw);
@@ -159,7 +159,7 @@ istft_kernel(const float2 *__restrict__ Y, int H, const float *__restrict__ wind
   for (int q = 0; q < 8; ++q) {
     int i = lt + q * G;
     float w = window ? __ldg(&window[i]) : 1.0f;
-    float2 val = z[i];
+    float2 val = z[pad(i)];
     if (h0 < H) frames[((size_t)v * H + h0) * N + i] = ((val.x * invn) * w) * gain;
     if (h1 < H) frames[((size_t)v * H + h1) * N + i] = ((val.y * invn) * w) * gain;
   }
