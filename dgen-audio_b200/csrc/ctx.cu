@@ -185,6 +185,7 @@ DGC_EXPORT int32_t dgc_ctx_destroy(dgc_ctx *c) {
   for (auto &kv : c->twiddles) cudaFree(kv.second);
   if (c->scratch) cudaFree(c->scratch);
   if (c->stage_dev) cudaFree(c->stage_dev);
+  if (c->wt_buf) cudaFree(c->wt_buf);
   if (c->status_dev) cudaFree(c->status_dev);
   if (c->loss_accum) cudaFree(c->loss_accum);
   if (c->ev_begin) cudaEventDestroy(c->ev_begin);

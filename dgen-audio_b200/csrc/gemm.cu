@@ -158,6 +158,18 @@ int32_t launch_sgemm(dgc_ctx *ctx, const float *A, const float *B, const float *
   return DGC_OK;
 }
 
+// out[c][r] = in[r][c] (small weight matrices only), 32 x 32 tiles through shared memory
+__global__ void transpose_kernel(const float *__restrict__ in, int R, int Cc, float *__restrict__ out) {
+  __shared__ float t[32][33];
+  int c = blockIdx.x * 32 + threadIdx.x, r0 = blockIdx.y * 32;
+  for (int i = threadIdx.y; i < 32; i += 8)
+    if (r0 + i < R && c < Cc) t[i][threadIdx.x] = in[(size_t)(r0 + i) * Cc + c];
+  __syncthreads();
+  int r = r0 + threadIdx.x, c0 = blockIdx.x * 32;
+  for (int i = threadIdx.y; i < 32; i += 8)
+    if (c0 + i < Cc && r < R) out[(size_t)(c0 + i) * R + r] = t[threadIdx.x][i];
+}
+
 // dZ = dC * (1 - C^2) in place-compatible form (tanh'), or copy when act == 0
 __global__ void act_bwd_kernel(const float *__restrict__ dC, const float *__restrict__ Cv, size_t n, int act,
                                float *__restrict__ dZ) {
@@ -232,6 +244,24 @@ DGC_EXPORT int32_t dgc_linear_fwd(dgc_ctx *ctx, const float *a_dev, const float 
   DGC_REQUIRE(ctx, act == 0 || act == 1, "act must be 0 (none) or 1 (tanh)");
   DGC_REQUIRE(ctx, act == 0 || bias_dev, "tanh layers need a bias");
   int32_t rc;
+  if (use_tensor_cores() && (double)M * N * K >= (double)(1 << 24) && (size_t)K * N <= (4u << 20) && (K & 3) == 0) {
+    // The weight matrix is small next to the activations: transpose it once so that BOTH operands of the
+    // tensor-core kernel are contiguous along k (vector loads straight into the K-major layout).
+    if (!ctx->wt_buf || ctx->wt_floats < (uint64_t)K * N) {
+      if (ctx->wt_buf) {
+        cudaStreamSynchronize(ctx->stream);
+        cudaFree(ctx->wt_buf);
+        ctx->wt_buf = nullptr;
+      }
+      DGC_CUDA(ctx, cudaMalloc(&ctx->wt_buf, (size_t)K * N * sizeof(float)));
+      ctx->wt_floats = (uint64_t)K * N;
+    }
+    transpose_kernel<<<dim3(dgc_div_up(N, 32), dgc_div_up(K, 32)), dim3(32, 8), 0, ctx->stream>>>(w_dev, K, N, ctx->wt_buf);
+    DGC_LAUNCHED(ctx, "transpose_w");
+    if (act == 1) rc = launch_sgemm<false, true, 2>(ctx, a_dev, ctx->wt_buf, bias_dev, M, N, K, c_dev);
+    else if (bias_dev) rc = launch_sgemm<false, true, 1>(ctx, a_dev, ctx->wt_buf, bias_dev, M, N, K, c_dev);
+    else rc = launch_sgemm<false, true, 0>(ctx, a_dev, ctx->wt_buf, nullptr, M, N, K, c_dev);
+  } else
   if (act == 1) rc = launch_sgemm<false, false, 2>(ctx, a_dev, w_dev, bias_dev, M, N, K, c_dev);
   else if (bias_dev) rc = launch_sgemm<false, false, 1>(ctx, a_dev, w_dev, bias_dev, M, N, K, c_dev);
   else rc = launch_sgemm<false, false, 0>(ctx, a_dev, w_dev, nullptr, M, N, K, c_dev);

@@ -96,59 +96,67 @@ __device__ __forceinline__ void split_tf32(float x, float &hi, float &lo) {
   lo = x - hi;
 }
 
-// Loads one 128 x 32 operand tile (rows r0.., k range k0..) and writes its hi / lo parts (256 threads).
-// ROWMAJOR_K: element (r, k) at src[r * ld + k] (k contiguous) -> K-major canonical layout;
-// else at src[k * ld + r] (r contiguous), transposed while it is stored.
+// One 128 x 32 operand tile (rows r0.., k range k0..) moves in two steps so that the global loads of tile
+// t+1 can be in flight while tile t is stored and multiplied: fetch() global memory -> 4 float4 registers
+// per thread, stash() registers -> hi / lo parts in shared memory (256 threads).
+// ROWMAJOR_K: element (r, k) at src[r * ld + k] (k contiguous): 8 lanes cover the 8 k-chunks of a row,
+//   32 rows per pass, vector stores into the K-major layout.
+// else: element at src[k * ld + r] (r contiguous): vector loads along m / n, transposed into the K-major
+//   layout with scalar stores; a warp moves 8 k x 4 units (16 rows), a store instruction hits 8 k x 4 rows
+//   with 2-way bank conflicts.  (An MN-major shared-memory descriptor with no swizzle was tried instead of
+//   this transposition and produced zeros on this part, so both operands always use the K-major descriptor.)
 template <bool ROWMAJOR_K>
-__device__ __forceinline__ void load_operand(const float *__restrict__ src, int ld, int rows, int r0, int k0, int k_end,
-                                             char *hi_part, char *lo_part, int tid) {
+__device__ __forceinline__ void fetch(const float *__restrict__ src, int ld, int rows, int r0, int k0, int k_end,
+                                      int tid, float4 (&v)[4]) {
   const bool vec_ok = ((ld & 3) == 0) && ((((uintptr_t)src) & 15) == 0);
-  if (ROWMAJOR_K) {
-    // 8 lanes cover the 8 k-chunks of a row (128 contiguous bytes), 32 rows per pass, 4 passes
-    const int kc = tid & 7, rr = tid >> 3;
 #pragma unroll
-    for (int p = 0; p < 4; ++p) {
-      const int r = rr + 32 * p, gr = r0 + r, gk = k0 + 4 * kc;
-      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int p = 0; p < 4; ++p) {
+    v[p] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (ROWMAJOR_K) {
+      const int kc = tid & 7, r = (tid >> 3) + 32 * p, gr = r0 + r, gk = k0 + 4 * kc;
       if (gr < rows) {
         const float *q = src + (size_t)gr * ld + gk;
-        if (vec_ok && gk + 3 < k_end) v = *reinterpret_cast<const float4 *>(q);
+        if (vec_ok && gk + 3 < k_end) v[p] = *reinterpret_cast<const float4 *>(q);
         else {
-          if (gk < k_end) v.x = q[0];
-          if (gk + 1 < k_end) v.y = q[1];
-          if (gk + 2 < k_end) v.z = q[2];
-          if (gk + 3 < k_end) v.w = q[3];
+          if (gk < k_end) v[p].x = q[0];
+          if (gk + 1 < k_end) v[p].y = q[1];
+          if (gk + 2 < k_end) v[p].z = q[2];
+          if (gk + 3 < k_end) v[p].w = q[3];
         }
       }
-      float4 h, l;
-      split_tf32(v.x, h.x, l.x); split_tf32(v.y, h.y, l.y); split_tf32(v.z, h.z, l.z); split_tf32(v.w, h.w, l.w);
-      const int off = kc * LBO_BYTES + r * 16;
-      *reinterpret_cast<float4 *>(hi_part + off) = h;
-      *reinterpret_cast<float4 *>(lo_part + off) = l;
-    }
-  } else {
-    // operand contiguous along m / n in memory: vector loads along m / n, transposed into the K-major
-    // layout with scalar stores.  A warp moves 8 k x 4 units (16 rows): per k 64 contiguous bytes of global
-    // memory; a store instruction (one of the four components) hits 8 k x 4 rows with 2-way bank conflicts.
-    // (An MN-major shared-memory descriptor with no swizzle was tried instead of this transposition and
-    // produced zeros on this part, so both operands always use the K-major descriptor.)
-#pragma unroll
-    for (int p = 0; p < 4; ++p) {
+    } else {
       const int idx = p * THREADS + tid;
       const int kk = (idx & 7) + 8 * (idx >> 8), u = ((idx >> 3) & 3) + 4 * ((idx >> 5) & 7);
       const int gk = k0 + kk, gr = r0 + 4 * u;
-      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
       if (gk < k_end) {
         const float *q = src + (size_t)gk * ld + gr;
-        if (vec_ok && gr + 3 < rows) v = *reinterpret_cast<const float4 *>(q);
+        if (vec_ok && gr + 3 < rows) v[p] = *reinterpret_cast<const float4 *>(q);
         else {
-          if (gr < rows) v.x = q[0];
-          if (gr + 1 < rows) v.y = q[1];
-          if (gr + 2 < rows) v.z = q[2];
-          if (gr + 3 < rows) v.w = q[3];
+          if (gr < rows) v[p].x = q[0];
+          if (gr + 1 < rows) v[p].y = q[1];
+          if (gr + 2 < rows) v[p].z = q[2];
+          if (gr + 3 < rows) v[p].w = q[3];
         }
       }
-      const float vv[4] = {v.x, v.y, v.z, v.w};
+    }
+  }
+}
+
+template <bool ROWMAJOR_K>
+__device__ __forceinline__ void stash(const float4 (&v)[4], char *hi_part, char *lo_part, int tid) {
+#pragma unroll
+  for (int p = 0; p < 4; ++p) {
+    if (ROWMAJOR_K) {
+      const int kc = tid & 7, r = (tid >> 3) + 32 * p;
+      float4 h, l;
+      split_tf32(v[p].x, h.x, l.x); split_tf32(v[p].y, h.y, l.y); split_tf32(v[p].z, h.z, l.z); split_tf32(v[p].w, h.w, l.w);
+      const int off = kc * LBO_BYTES + r * 16;
+      *reinterpret_cast<float4 *>(hi_part + off) = h;
+      *reinterpret_cast<float4 *>(lo_part + off) = l;
+    } else {
+      const int idx = p * THREADS + tid;
+      const int kk = (idx & 7) + 8 * (idx >> 8), u = ((idx >> 3) & 3) + 4 * ((idx >> 5) & 7);
+      const float vv[4] = {v[p].x, v[p].y, v[p].z, v[p].w};
       const int base = (kk >> 2) * LBO_BYTES + (kk & 3) * 4 + (4 * u) * 16;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
@@ -193,17 +201,25 @@ tc_gemm_kernel(const float *__restrict__ A, const float *__restrict__ B, const f
   const uint32_t tmem_d = *tmem_slot;
   bool ok = true;
 
+  float4 va[4], vb[4], na[4], nb[4];
+  if (KT > 0) {
+    fetch<A_KMAJOR>(A, A_KMAJOR ? K : M, M, m0, k_begin, k_end, tid, va);
+    fetch<B_KMAJOR>(B, B_KMAJOR ? K : N, N, n0, k_begin, k_end, tid, vb);
+  }
   for (int kt = 0; kt < KT; ++kt) {
     const int s = kt & 1;
+    if (kt + 1 < KT) {  // next tile's global loads fly while this tile is stored and multiplied
+      fetch<A_KMAJOR>(A, A_KMAJOR ? K : M, M, m0, k_begin + (kt + 1) * TBK, k_end, tid, na);
+      fetch<B_KMAJOR>(B, B_KMAJOR ? K : N, N, n0, k_begin + (kt + 1) * TBK, k_end, tid, nb);
+    }
     if (kt >= 2) {
       ok = mbar_wait(smem_u32(&bars[s]), (uint32_t)(((kt >> 1) - 1) & 1));
       ok = __syncthreads_and(ok);   // same decision in every thread
       if (!ok) break;               // give up: no further MMAs are issued, TMEM is still released below
     }
     char *st = smem + s * STAGE_BYTES;
-    const int k0 = k_begin + kt * TBK;
-    load_operand<A_KMAJOR>(A, A_KMAJOR ? K : M, M, m0, k0, k_end, st, st + OPER_BYTES, tid);
-    load_operand<B_KMAJOR>(B, B_KMAJOR ? K : N, N, n0, k0, k_end, st + 2 * OPER_BYTES, st + 3 * OPER_BYTES, tid);
+    stash<A_KMAJOR>(va, st, st + OPER_BYTES, tid);
+    stash<B_KMAJOR>(vb, st + 2 * OPER_BYTES, st + 3 * OPER_BYTES, tid);
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> async proxy (tensor core)
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -222,6 +238,11 @@ tc_gemm_kernel(const float *__restrict__ A, const float *__restrict__ B, const f
         mma_tf32(tmem_d, dah, dbh, ID, 1u);
       }
       commit_to(smem_u32(&bars[s]));
+    }
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+      va[p] = na[p];
+      vb[p] = nb[p];
     }
   }
   // the last commit covers every MMA issued before it
