@@ -295,8 +295,15 @@ def run_ours(args, rank, world, local_rank):
                "fir_noise": 4 * (B * T + B * F * CFG["taps"] + 2 * B * T),
                "bands_to_taps": 4 * (B * F * CFG["nbands"] + B * F * CFG["taps"]),
                "mss_loss_fwd": 2 * 4 * B * T * len(SIZES)}
+        # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per voice of each stage's kernels, from the
+        # ncu --set full capture of this workload at 16 voices summarised in
+        # profiles/fwd_loss_c2_kernels_full_set.md; traffic grows in proportion to the voices per launch.
+        ncu_traffic_per_voice = {"harmonic_render": (13.27e6 + 4.12e6) / 16, "fir_noise": 25.02e6 / 16,
+                                 "mss_loss_fwd": 49.19e6 / 16}
         dom = max(stage_ms, key=stage_ms.get)
         achieved = alg[dom] / (stage_ms[dom] * 1e-3) / 1e9
+        traffic = ncu_traffic_per_voice.get(dom)
+        traffic = traffic * B if traffic is not None else None
         step_bytes = sum(alg.values())
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
@@ -306,7 +313,7 @@ def run_ours(args, rank, world, local_rank):
                         "ms_per_step": e2e_ms / args.steps},
                 "gpu_launches": int(launches),
                 "roofline": {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "GB/s",
-                             "frac": achieved / peak, "traffic": None,
+                             "frac": achieved / peak, "traffic": traffic,
                              "peak_source": "measured" if peaks else "fallback",
                              "note": "the stage is FP32/SFU-issue bound, not HBM bound; see DESIGN.md"},
                 "stage_ms": stage_ms,
