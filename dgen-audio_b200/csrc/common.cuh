@@ -35,7 +35,10 @@ struct dgc_ctx {
   double *loss_accum = nullptr;                      // 256 doubles: [0..64) results, [64..) per-block sums
   float *wt_buf = nullptr;  // transposed copy of the current layer's weights (matmul forward)
   uint64_t wt_floats = 0;
-  // staging for the host-buffer composite entry points
+  // staging for the host-buffer composite entry points; uploads run on their own stream so that the
+  // first kernels start while later inputs are still crossing PCIe
+  cudaStream_t copy_stream = nullptr;
+  cudaEvent_t copy_ev[3] = {nullptr, nullptr, nullptr};
   float *stage_dev = nullptr;
   uint64_t stage_floats = 0;
 };

@@ -185,6 +185,9 @@ DGC_EXPORT int32_t dgc_ctx_destroy(dgc_ctx *c) {
   for (auto &kv : c->twiddles) cudaFree(kv.second);
   if (c->scratch) cudaFree(c->scratch);
   if (c->stage_dev) cudaFree(c->stage_dev);
+  for (auto &e : c->copy_ev)
+    if (e) cudaEventDestroy(e);
+  if (c->copy_stream) cudaStreamDestroy(c->copy_stream);
   if (c->wt_buf) cudaFree(c->wt_buf);
   if (c->status_dev) cudaFree(c->status_dev);
   if (c->loss_accum) cudaFree(c->loss_accum);
@@ -286,5 +289,59 @@ DGC_EXPORT int32_t dgc_arena_download(dgc_arena *a, uint64_t off, float *dst, ui
   if (off > a->n || n > a->n - off) return dgc_fail(a->ctx, DGC_ERR_INVALID, "arena_download: range outside the arena");
   DGC_CUDA(a->ctx, cudaMemcpyAsync(dst, a->ptr + off, n * sizeof(float), cudaMemcpyDeviceToHost, a->ctx->stream));
   DGC_CUDA(a->ctx, cudaStreamSynchronize(a->ctx->stream));
+  return DGC_OK;
+}
+
+// ---- output sanitiser ---------------------------------------------------------------------------
+namespace {
+__device__ __forceinline__ float sanitize_bits(float v) {
+  return ((__float_as_uint(v) & 0x7f800000u) == 0x7f800000u) ? 0.0f : v;
+}
+// Pure streaming kernel (4 B in + 4 B out per element): 128-bit accesses over the aligned body, grid-stride,
+// scalar head / tail when the two pointers share a misalignment, all-scalar when they do not.
+__global__ void __launch_bounds__(256) sanitize_kernel(const float *__restrict__ in, float *__restrict__ out,
+                                                       uint64_t n, uint64_t head, int vec_ok) {
+  const uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x, nth = (uint64_t)gridDim.x * blockDim.x;
+  if (!vec_ok) {
+    for (uint64_t i = tid; i < n; i += nth) out[i] = sanitize_bits(in[i]);
+    return;
+  }
+  if (tid < head) out[tid] = sanitize_bits(in[tid]);
+  const uint64_t nv = (n - head) >> 2;
+  const float4 *iv = reinterpret_cast<const float4 *>(in + head);
+  float4 *ov = reinterpret_cast<float4 *>(out + head);
+  uint64_t i = tid;
+  for (; i + nth < nv; i += 2 * nth) {  // two independent 128-bit loads in flight per thread
+    float4 a = __ldcs(iv + i), b = __ldcs(iv + i + nth);
+    a.x = sanitize_bits(a.x); a.y = sanitize_bits(a.y); a.z = sanitize_bits(a.z); a.w = sanitize_bits(a.w);
+    b.x = sanitize_bits(b.x); b.y = sanitize_bits(b.y); b.z = sanitize_bits(b.z); b.w = sanitize_bits(b.w);
+    __stcs(ov + i, a);
+    __stcs(ov + i + nth, b);
+  }
+  if (i < nv) {
+    float4 a = __ldcs(iv + i);
+    a.x = sanitize_bits(a.x); a.y = sanitize_bits(a.y); a.z = sanitize_bits(a.z); a.w = sanitize_bits(a.w);
+    __stcs(ov + i, a);
+  }
+  const uint64_t tail0 = head + (nv << 2);
+  if (tail0 + tid < n) out[tail0 + tid] = sanitize_bits(in[tail0 + tid]);
+}
+}  // namespace
+
+DGC_EXPORT int32_t dgc_sanitize(dgc_ctx *ctx, const float *in_dev, uint64_t n, float *out_dev) {
+  if (!ctx) return DGC_ERR_INVALID;
+  if (n == 0) return DGC_OK;
+  DGC_REQUIRE(ctx, in_dev && out_dev, "null pointer");
+  DGC_REQUIRE(ctx, (((uintptr_t)in_dev | (uintptr_t)out_dev) & 3) == 0, "pointers must be 4-byte aligned");
+  const int vec_ok = (((uintptr_t)in_dev ^ (uintptr_t)out_dev) & 15) == 0;
+  uint64_t head = ((16 - ((uintptr_t)in_dev & 15)) & 15) >> 2;  // scalars before the first 16-byte boundary
+  if (head > n) head = n;
+  // 8 resident CTAs of 256 threads per SM; never more blocks than 128-bit items
+  int sms = 148;
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, ctx->device);
+  uint64_t want = dgc_div_up((int64_t)((n >> 2) + 1), 256);
+  int grid = (int)(want < (uint64_t)sms * 8 ? want : (uint64_t)sms * 8);
+  sanitize_kernel<<<grid, 256, 0, ctx->stream>>>(in_dev, out_dev, n, head, vec_ok);
+  DGC_LAUNCHED(ctx, "sanitize");
   return DGC_OK;
 }

@@ -163,26 +163,29 @@ anchor_sum_kernel(const float *__restrict__ f0t, int B, int T, int K, float sr, 
   if (c >= C) return;
   const float *f = f0t + (size_t)b * T;
   const int n0 = c * CH, n1 = min(T, n0 + CH);
-  // Double-float accumulation (error-free two-sum per add): the 64 increments of a chunk are summed
-  // to ~2^-45 absolute, far below the 2^-25 spacing of the single-precision anchors, with plain
-  // FP32 adds; the chunk total is converted to Q0.64 once.
+  // Double-float accumulation: the 64 increments of a chunk are summed to ~2^-36 absolute, far below the
+  // 2^-25 spacing of the single-precision anchors, with plain FP32 adds; the chunk total is converted to
+  // Q0.64 once.  hi starts at 1.0 (an integer number of turns, invisible mod 1) so that |hi| >= |inc|
+  // holds for every add and the three-operation Fast2Sum is error-free.
   float hi[P], lo[P];
 #pragma unroll
-  for (int i = 0; i < P; ++i) hi[i] = lo[i] = 0.0f;
-  const float kmax = (float)K;
+  for (int i = 0; i < P; ++i) {
+    hi[i] = 1.0f;
+    lo[i] = 0.0f;
+  }
+  const float kmax = (float)K, kf0 = (float)(j + 1);
   for (int n = n0; n < n1; ++n) {
     const float f0 = f[n];
     const bool fast = f0 >= 0.0f && __fmul_rn(kmax, f0) < sr;
 #pragma unroll
     for (int i = 0; i < P; ++i) {
-      float inc = div_by_const(__fmul_rn((float)(j + LPC * i + 1), f0), sr, rsr);
+      float inc = div_by_const(__fmul_rn(partial_number(kf0, LPC * i), f0), sr, rsr);
       if (!fast) {
         if (!(inc >= 0.0f && inc < 1.0f)) inc = inc - floorf(inc);
         if (!(inc >= 0.0f && inc < 1.0f)) inc = 0.0f;  // non-finite or rounded up to 1
       }
       float s = __fadd_rn(hi[i], inc);
-      float bb = __fsub_rn(s, hi[i]);
-      float err = __fadd_rn(__fsub_rn(hi[i], __fsub_rn(s, bb)), __fsub_rn(inc, bb));
+      float err = __fsub_rn(inc, __fsub_rn(s, hi[i]));
       hi[i] = s;
       lo[i] = __fadd_rn(lo[i], err);
     }
@@ -190,7 +193,7 @@ anchor_sum_kernel(const float *__restrict__ f0t, int B, int T, int K, float sr, 
   unsigned long long acc[P];
 #pragma unroll
   for (int i = 0; i < P; ++i) {
-    // hi in [0, 64], |lo| tiny: total mod 1 in Q0.64 (two's-complement add handles a negative lo)
+    // hi in [1, 65], |lo| tiny: total mod 1 in Q0.64 (two's-complement add handles a negative lo)
     float ip = floorf(hi[i]);
     unsigned long long q = turns_to_q64(__fsub_rn(hi[i], ip));
     float al = fabsf(lo[i]);
@@ -252,7 +255,7 @@ harmonic_render_kernel(dgc_harmonic_params prm, float rsr, const float *__restri
   const bool active = c < C;
   if (!active) c = C - 1;
   const int n0 = c * CH;
-  const float sr = prm.sample_rate, nyq = sr * 0.5f, kmax = (float)K;
+  const float sr = prm.sample_rate, nyq = sr * 0.5f, kmax = (float)K, kf0 = (float)(j + 1);
 
   float ph[P], alo[P], ahi[P];
   const float *anc = anchors + ((size_t)b * C + c) * K;
@@ -295,22 +298,22 @@ harmonic_render_kernel(dgc_harmonic_params prm, float rsr, const float *__restri
     if (f0t >= 0.0f && __fmul_rn(kmax, f0t) < sr) {
 #pragma unroll
       for (int i = 0; i < P; ++i) {
-        float freq = __fmul_rn((float)(j + LPC * i + 1), f0t);
+        float freq = __fmul_rn(partial_number(kf0, LPC * i), f0t);
         float a = fmaf(fr, ahi[i], oa * alo[i]);
         float m = freq < nyq ? a : 0.0f;
         s2 += m;
-        s1 = fmaf(sin_turns(ph[i]), m, s1);
+        s1 = fmaf(neg_sin_turns(ph[i]), -m, s1);
         float next = __fadd_rn(ph[i], div_by_const(freq, sr, rsr));
         ph[i] = next >= 1.0f ? __fadd_rn(next, -1.0f) : next;
       }
     } else {
 #pragma unroll
       for (int i = 0; i < P; ++i) {
-        float freq = __fmul_rn((float)(j + LPC * i + 1), f0t);
+        float freq = __fmul_rn(partial_number(kf0, LPC * i), f0t);
         float a = fmaf(fr, ahi[i], oa * alo[i]);
         float m = freq < nyq ? a : 0.0f;
         s2 += m;
-        s1 = fmaf(sin_turns(ph[i]), m, s1);
+        s1 = fmaf(neg_sin_turns(ph[i]), -m, s1);
         ph[i] = phasor_step(ph[i], div_by_const(freq, sr, rsr));
       }
     }

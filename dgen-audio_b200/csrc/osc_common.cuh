@@ -53,6 +53,11 @@ __device__ __forceinline__ float sin_turns(float p) {
   float c = p >= 0.5f ? p - 1.0f : p;
   return __sinf(c * TWO_PI_F);
 }
+// -sin(2*pi*p) for p in [0,1) with a single subtraction for the centring: sin(2 pi p) = -sin(2 pi (p - 1/2)).
+// p - 1/2 is exact for p >= 1/4 and within 2^-26 turns below, far inside the fast sine's own error.
+__device__ __forceinline__ float neg_sin_turns(float p) { return __sinf(__fadd_rn(p, -0.5f) * TWO_PI_F); }
+// (float)(j + 1 + step * i) for small integers without an integer-to-float conversion per use
+__device__ __forceinline__ float partial_number(float kf0, int step_times_i) { return kf0 + (float)step_times_i; }
 
 }  // namespace dgosc
 

@@ -1,8 +1,12 @@
 // Composite entry points that take HOST buffers: what a host calls once per batch.  They own a
 // device staging area inside the context, enqueue one asynchronous copy per input straight from the
-// caller's buffers (full PCIe rate when those are page-locked) and the kernels on the context
-// stream, and return the result to host memory.
+// caller's buffers (full PCIe rate when those are page-locked) on an upload stream, in the order the
+// kernels need them, and the kernels on the context stream behind per-group events: the render starts
+// as soon as its control tables have landed, while the noise inputs and the target are still in
+// flight.  The result returns to host memory.
 #include "common.cuh"
+#include <cstdlib>
+#include <cstring>
 
 namespace {
 
@@ -59,16 +63,33 @@ DGC_EXPORT int32_t dgc_hn_forward_loss_host(dgc_ctx *ctx, const dgc_hn_step *s, 
   int32_t rc = ensure_stage(ctx, in_floats + dev_extra + 64 * 16);
   if (rc != DGC_OK) return rc;
 
+  if (!ctx->copy_stream) {
+    DGC_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->copy_stream, cudaStreamNonBlocking));
+    for (auto &e : ctx->copy_ev) DGC_CUDA(ctx, cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+  }
+  // Every earlier call ended with a stream synchronisation, so no kernel still reads the staging area;
+  // work the caller queued on the context stream before this call does not touch it either.
   Carver dc(ctx->stage_dev);
   cudaError_t cp_err = cudaSuccess;
+  static const bool inline_upload = [] {
+    const char *e = getenv("DGC_UPLOAD");
+    return e && strcmp(e, "inline") == 0;
+  }();
+  cudaStream_t up = inline_upload ? ctx->stream : ctx->copy_stream;
   auto put = [&](const float *src, uint64_t n) -> float * {
     float *d = dc.take(n);
-    cudaError_t e = cudaMemcpyAsync(d, src, n * sizeof(float), cudaMemcpyHostToDevice, ctx->stream);
+    cudaError_t e = cudaMemcpyAsync(d, src, n * sizeof(float), cudaMemcpyHostToDevice, up);
     if (e != cudaSuccess && cp_err == cudaSuccess) cp_err = e;
     return d;
   };
+  auto mark = [&](int i) {
+    cudaError_t e = cudaEventRecord(ctx->copy_ev[i], up);
+    if (e != cudaSuccess && cp_err == cudaSuccess) cp_err = e;
+  };
+  // group 0: harmonic controls; group 1: noise branch; group 2: target
   float *d_f0 = put(f0_host, nFB), *d_uv = put(uv_host, nFB), *d_gain = put(gain_host, nFB);
   float *d_amps = put(amps_host, nFB * K);
+  mark(0);
   float *d_ng = nullptr, *d_tab = nullptr, *d_w = nullptr, *d_noise = nullptr;
   if (noise) {
     d_ng = put(noise_gain_host, nFB);
@@ -76,27 +97,41 @@ DGC_EXPORT int32_t dgc_hn_forward_loss_host(dgc_ctx *ctx, const dgc_hn_step *s, 
     if (NB > 0) d_w = put(w_host, n_w);
     d_noise = put(noise_host, nBT);
   }
+  mark(1);
   float *d_target = put(target_host, nBT);
-  if (cp_err != cudaSuccess) return dgc_fail(ctx, DGC_ERR_CUDA, "input upload: %s", cudaGetErrorString(cp_err));
+  mark(2);
+  if (cp_err != cudaSuccess) {
+    cudaStreamSynchronize(ctx->copy_stream);
+    return dgc_fail(ctx, DGC_ERR_CUDA, "input upload: %s", cudaGetErrorString(cp_err));
+  }
+  // from here on every exit path drains the upload stream before returning (the caller may reuse or free
+  // its buffers as soon as this function returns)
+  auto bail = [&](int32_t code) {
+    cudaStreamSynchronize(ctx->copy_stream);
+    return code;
+  };
   float *d_audio = dc.take(nBT);
   float *d_taps = d_tab;
+  dgc_harmonic_params hp = s->harm;
+  hp.accumulate = 0;
+  if (cudaStreamWaitEvent(ctx->stream, ctx->copy_ev[0], 0) != cudaSuccess) return bail(dgc_fail(ctx, DGC_ERR_CUDA, "event wait"));
+  rc = dgc_harmonic_render(ctx, &hp, d_f0, d_uv, d_amps, d_gain, nullptr, d_audio);
+  if (rc != DGC_OK) return bail(rc);
+  if (cudaStreamWaitEvent(ctx->stream, ctx->copy_ev[1], 0) != cudaSuccess) return bail(dgc_fail(ctx, DGC_ERR_CUDA, "event wait"));
   if (noise && NB > 0) {
     d_taps = dc.take(nFB * NT);
     rc = dgc_bands_to_taps(ctx, d_tab, d_w, (int32_t)nFB, NB, NT, d_taps);
-    if (rc != DGC_OK) return rc;
+    if (rc != DGC_OK) return bail(rc);
   }
-  dgc_harmonic_params hp = s->harm;
-  hp.accumulate = 0;
-  rc = dgc_harmonic_render(ctx, &hp, d_f0, d_uv, d_amps, d_gain, nullptr, d_audio);
-  if (rc != DGC_OK) return rc;
   if (noise) {
     dgc_fir_params fp = s->fir;
     fp.accumulate = 1;
     rc = dgc_fir_noise(ctx, &fp, d_noise, d_taps, d_ng, d_audio);
-    if (rc != DGC_OK) return rc;
+    if (rc != DGC_OK) return bail(rc);
   }
+  if (cudaStreamWaitEvent(ctx->stream, ctx->copy_ev[2], 0) != cudaSuccess) return bail(dgc_fail(ctx, DGC_ERR_CUDA, "event wait"));
   rc = dgc_mss_loss_fwd(ctx, &s->mss, d_audio, d_target, nullptr, ctx->loss_accum);
-  if (rc != DGC_OK) return rc;
+  if (rc != DGC_OK) return bail(rc);
   DGC_CUDA(ctx, cudaMemcpyAsync(loss_host, ctx->loss_accum, sizeof(double), cudaMemcpyDeviceToHost, ctx->stream));
   if (audio_host)
     DGC_CUDA(ctx, cudaMemcpyAsync(audio_host, d_audio, nBT * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));

@@ -165,7 +165,7 @@ harmonic_bwd_kernel(dgc_harmonic_params prm, float rsr, const float *__restrict_
   const bool active = r < F;
   if (!active) r = F - 1;
   const int hi_row = r + 1 >= F ? 0 : r + 1;
-  const float sr = prm.sample_rate, nyq = sr * 0.5f;
+  const float sr = prm.sample_rate, nyq = sr * 0.5f, kf0 = (float)(j + 1);
   float alo[P], ahi[P], pl[P], phh[P], ph[P];
   const float *rl = amps + ((size_t)r * B + b) * K, *rh = amps + ((size_t)hi_row * B + b) * K;
 #pragma unroll
@@ -206,7 +206,7 @@ harmonic_bwd_kernel(dgc_harmonic_params prm, float rsr, const float *__restrict_
         float f0t = lerp_strict(omf, f0[(size_t)lo * B + b], fr, f0[(size_t)hi * B + b]);
 #pragma unroll
         for (int i = 0; i < P; ++i)
-          ph[i] = phasor_step(ph[i], div_by_const(__fmul_rn((float)(j + LPC * i + 1), f0t), sr, rsr));
+          ph[i] = phasor_step(ph[i], div_by_const(__fmul_rn(partial_number(kf0, LPC * i), f0t), sr, rsr));
       }
     }
     for (int m = 0; m < maxlen; ++m) {
@@ -229,7 +229,7 @@ harmonic_bwd_kernel(dgc_harmonic_params prm, float rsr, const float *__restrict_
       float s1v = 0.0f, s2v = 0.0f;
 #pragma unroll
       for (int i = 0; i < P; ++i) {
-        float freq = __fmul_rn((float)(j + LPC * i + 1), f0t);
+        float freq = __fmul_rn(partial_number(kf0, LPC * i), f0t);
         float a = fmaf(fr, ahi[i], omf * alo[i]);
         mk[i] = freq < nyq ? 1.0f : 0.0f;
         float mm = mk[i] * a;

@@ -93,6 +93,7 @@ SIGNATURES = {
     "dgc_linear_fwd": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp]),
     "dgc_linear_bwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp]),
     "dgc_adam_step": (_i32, [_vp, _vp, _vp, _vp, _vp, _u64, _i32, _f, _f, _f, _f]),
+    "dgc_sanitize": (_i32, [_vp, _vp, _u64, _vp]),
     "dgc_hn_forward_loss_host": (_i32, [_vp, C.POINTER(HnStep)] + [_vp] * 9 + [C.POINTER(C.c_double), _vp]),
 }
 
@@ -354,6 +355,12 @@ class Context:
     def adam_step(self, theta, grad, m, v, t, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8):
         self.check(self.lib.dgc_adam_step(self.h, _ptr(theta), _ptr(grad), _ptr(m), _ptr(v), theta.numel(), t, lr,
                                           beta1, beta2, eps))
+
+    def sanitize(self, x, out=None):
+        """Non-finite -> 0 (toolchain/include/dgen_runtime.h:72-84); in place when out is None."""
+        out = x if out is None else out
+        self.check(self.lib.dgc_sanitize(self.h, _ptr(x), x.numel(), _ptr(out)))
+        return out
 
     # ---- composite, host buffers --------------------------------------------------------------
     def hn_forward_loss_host(self, step, f0, uv, amps, gain, noise_gain, taps_or_bands, w, noise, target,

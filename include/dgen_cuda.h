@@ -274,6 +274,12 @@ int32_t dgc_linear_bwd(dgc_ctx *ctx, const float *a_dev, const float *w_dev, con
 int32_t dgc_adam_step(dgc_ctx *ctx, float *theta_dev, const float *grad_dev, float *m_dev, float *v_dev, uint64_t n,
                       int32_t t, float lr, float beta1, float beta2, float eps);
 
+/* Output sanitiser: out[i] = in[i] when its IEEE-754 exponent field is not all ones, else +0.0f (NaN and
+ * +-Inf become 0; denormals, -0.0 and every finite value pass through bit for bit).  in_dev == out_dev is
+ * allowed.  Replaces dgen_sanitize_f32 / dgen_sanitize_f32x4 applied at every `output` store
+ * (toolchain/include/dgen_runtime.h:59-84, Sources/DGen/Renderer/CRenderer.swift:1021-1039). */
+int32_t dgc_sanitize(dgc_ctx *ctx, const float *in_dev, uint64_t n, float *out_dev);
+
 /* ---- composite steps with host buffers (the call a host makes per batch) ------------------------ */
 typedef struct dgc_hn_step {
   dgc_harmonic_params harm;

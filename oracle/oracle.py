@@ -313,6 +313,14 @@ def noise_xorshift(state, T, L=None):
 REF_DIR = os.path.join(HERE, "_ref")
 
 
+def sanitize(x, L=None):
+    """Non-finite -> 0 in a copy of x (toolchain/include/dgen_runtime.h:72-74)."""
+    L = L or lib()
+    y = np.ascontiguousarray(x, dtype=np.float32).copy()
+    L.orc_sanitize(y, y.size)
+    return y
+
+
 def ref_available():
     return os.path.exists(os.path.join(REF_DIR, "libref_harness.so"))
 
