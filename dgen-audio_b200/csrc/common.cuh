@@ -29,6 +29,7 @@ struct dgc_ctx {
   // cached data-independent tables
   std::map<std::pair<int, int>, float *> playheads;  // (F, T) -> device clock
   std::map<std::pair<int, int>, int *> row_ranges;   // (F, T) -> [F][4] frame ranges per control row
+  std::map<std::pair<int, int>, float2 *> row_tables;  // (F, T) -> per frame (floor row as int bits, fraction)
   std::map<int, float *> hann_sym;                   // N -> symmetric Hann (spectral loss)
   std::map<int, float *> hann_per;                   // N -> periodic Hann (hann())
   std::map<int, float2 *> twiddles;                  // N -> exp(-2 pi i m / N), m < N
@@ -49,6 +50,8 @@ int32_t dgc_check_launch(dgc_ctx *ctx, const char *what);
 float *dgc_ctx_scratch(dgc_ctx *ctx, uint64_t nfloats);
 // [F][4] ints: frames whose floor control row is r are [a,b) and [c,d) (second run: after the clock wrap)
 const int *dgc_ctx_row_ranges(dgc_ctx *ctx, int F, int T);
+// [T] float2: x = bits of the floor control row (int), y = lerp fraction of sampleRow at the cached clock
+const float2 *dgc_ctx_row_table(dgc_ctx *ctx, int F, int T);
 const float *dgc_ctx_hann_sym(dgc_ctx *ctx, int N);
 const float *dgc_ctx_hann_per(dgc_ctx *ctx, int N);
 // C[M][N] = A[M][K] * B[N][K]^T on the matmul path of gemm.cu

@@ -180,6 +180,7 @@ DGC_EXPORT int32_t dgc_ctx_destroy(dgc_ctx *c) {
   if (c->stream) cudaStreamSynchronize(c->stream);
   for (auto &kv : c->playheads) cudaFree(kv.second);
   for (auto &kv : c->row_ranges) cudaFree(kv.second);
+  for (auto &kv : c->row_tables) cudaFree(kv.second);
   for (auto &kv : c->hann_sym) cudaFree(kv.second);
   for (auto &kv : c->hann_per) cudaFree(kv.second);
   for (auto &kv : c->twiddles) cudaFree(kv.second);

