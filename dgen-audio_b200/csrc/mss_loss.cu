@@ -7,6 +7,8 @@
 // and one kernel per term; here one block transforms several windows cooperatively in shared
 // memory, prediction and target ride the real and imaginary lane of ONE complex FFT, and the
 // linear and log terms come from the same spectrum.
+#include <algorithm>
+
 #include "common.cuh"
 #include "fft.cuh"
 
@@ -44,20 +46,19 @@ __device__ __forceinline__ void unpack(float2 zk, float2 znk, float2 &x1, float2
   x2 = make_float2(0.5f * (zk.y + znk.y), 0.5f * (znk.x - zk.x));
 }
 
+// One block of one scale: LOSS_THREADS / (N/8) windows of one voice, prediction and target in the real
+// and imaginary lane of one transform; sm holds 2 * NF * padded(N) float2 (the same 34.8 KB for every N).
 template <int N>
-__global__ void __launch_bounds__(LOSS_THREADS)
-mss_fwd_kernel(const float *__restrict__ pred, const float *__restrict__ target, int B, int T, int hop, int H,
-               const float *__restrict__ window, const float2 *__restrict__ tw, float *__restrict__ part_lin,
-               float *__restrict__ part_log) {
+__device__ __forceinline__ void mss_fwd_body(float2 *sm, float *red, int bx, int b, const float *__restrict__ pred,
+                                             const float *__restrict__ target, int B, int T, int hop, int H,
+                                             const float *__restrict__ window, const float2 *__restrict__ tw,
+                                             float *__restrict__ part_lin, float *__restrict__ part_log) {
   constexpr int G = N / 8;                    // threads per transform
   constexpr int NF = LOSS_THREADS / G;        // transforms per block
   constexpr int PN = padded(N);
-  __shared__ float2 bufa[NF * PN];
-  __shared__ float2 bufb[NF * PN];
-  __shared__ float red[LOSS_THREADS / 32];
+  float2 *bufa = sm, *bufb = sm + NF * PN;
   const int tid = threadIdx.x, f = tid / G, lt = tid % G;
-  const int b = blockIdx.y;
-  const int h = blockIdx.x * NF + f;
+  const int h = bx * NF + f;
   const bool valid = h < H;
   const int t_base = h * hop - (N - 1);
   const float *x1 = pred + (size_t)b * T, *x2 = target + (size_t)b * T;
@@ -95,6 +96,36 @@ mss_fwd_kernel(const float *__restrict__ pred, const float *__restrict__ target,
   if (valid && lt == 0) {
     part_lin[(size_t)h * B + b] = lin;
     part_log[(size_t)h * B + b] = lg;
+  }
+}
+
+// All scales of the multi-scale loss in ONE launch: blockIdx.x runs through the blocks of scale 0, then
+// scale 1, ... (the host orders the scales by decreasing window so the long blocks start first and the
+// short ones fill the tail); no launch gap and no partial last wave per scale.
+struct FwdDesc {
+  int nscales;
+  int N[DGC_MSS_MAX_SCALES], hop[DGC_MSS_MAX_SCALES], H[DGC_MSS_MAX_SCALES];
+  int first_block[DGC_MSS_MAX_SCALES + 1];
+  const float *window[DGC_MSS_MAX_SCALES];
+  const float2 *tw[DGC_MSS_MAX_SCALES];
+  float *lin[DGC_MSS_MAX_SCALES], *lg[DGC_MSS_MAX_SCALES];
+};
+
+constexpr int FWD_SMEM_BYTES = 2 * (LOSS_THREADS / (2048 / 8)) * padded(2048) * (int)sizeof(float2);
+
+__global__ void __launch_bounds__(LOSS_THREADS)
+mss_fwd_kernel(const float *__restrict__ pred, const float *__restrict__ target, int B, int T, const FwdDesc d) {
+  extern __shared__ float2 fwd_sm[];
+  __shared__ float red[LOSS_THREADS / 32];
+  int s = 0;
+  while (s + 1 < d.nscales && (int)blockIdx.x >= d.first_block[s + 1]) ++s;
+  const int bx = blockIdx.x - d.first_block[s], b = blockIdx.y;
+  switch (d.N[s]) {
+#define CASE(NN) \
+  case NN: mss_fwd_body<NN>(fwd_sm, red, bx, b, pred, target, B, T, d.hop[s], d.H[s], d.window[s], d.tw[s], d.lin[s], d.lg[s]); break;
+    CASE(16) CASE(32) CASE(64) CASE(128) CASE(256) CASE(512) CASE(1024) CASE(2048)
+#undef CASE
+    default: break;
   }
 }
 
@@ -145,19 +176,6 @@ mss_reduce_kernel(const float *__restrict__ part, ReduceDesc d, double scale_lin
     out[0] = t;
     *ticket = 0u;
   }
-}
-
-template <int N>
-int32_t launch_fwd(dgc_ctx *ctx, const dgc_mss_params *p, const float *pred, const float *target, int hop, int H,
-                   float *lin, float *lg) {
-  const float *win = dgc_ctx_hann_sym(ctx, N);
-  const float2 *tw = dgc_ctx_twiddles(ctx, N);
-  if (!win || !tw) return DGC_ERR_OOM;
-  constexpr int NF = LOSS_THREADS / (N / 8);
-  mss_fwd_kernel<N><<<dim3(dgc_div_up(H, NF), p->B), LOSS_THREADS, 0, ctx->stream>>>(pred, target, p->B, p->T, hop, H,
-                                                                                    win, tw, lin, lg);
-  ctx->launches++;
-  return dgc_check_launch(ctx, "mss_fwd");
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -359,22 +377,44 @@ DGC_EXPORT int32_t dgc_mss_loss_fwd(dgc_ctx *ctx, const dgc_mss_params *p, const
     if (N > p->T) continue;
     ++used;
   }
+  // partial layout and summation order follow the caller's scale order; the launch runs the usable
+  // scales largest window first
+  int order[DGC_MSS_MAX_SCALES], no = 0;
+  long long off_of[DGC_MSS_MAX_SCALES];
   for (int s = 0; s < p->nscales; ++s) {
     const int N = p->sizes[s];
     if (N > p->T) continue;
-    const int hop = hop_of(p, s), H = dgc_div_up(p->T, hop);
-    float *lin = part + off, *lg = lin + (long long)H * p->B;
-    switch (N) {
-#define CASE(NN) case NN: rc = launch_fwd<NN>(ctx, p, pred_dev, target_dev, hop, H, lin, lg); break;
-      CASE(16) CASE(32) CASE(64) CASE(128) CASE(256) CASE(512) CASE(1024) CASE(2048)
-#undef CASE
-      default: return dgc_fail(ctx, DGC_ERR_UNSUPPORTED, "window size %d", N);
-    }
-    if (rc != DGC_OK) return rc;
+    if (N < 16 || N > 2048 || (N & (N - 1))) return dgc_fail(ctx, DGC_ERR_UNSUPPORTED, "window size %d", N);
+    const int H = dgc_div_up(p->T, hop_of(p, s));
+    order[no++] = s;
+    off_of[s] = off;
     d.off[d.nscales] = off;
     d.cnt[d.nscales] = (long long)H * p->B;
     d.nscales++;
     off += 2ll * H * p->B;
+  }
+  std::stable_sort(order, order + no, [&](int x, int y) { return p->sizes[x] > p->sizes[y]; });
+  FwdDesc fd;
+  fd.nscales = no;
+  int blocks = 0;
+  for (int i = 0; i < no; ++i) {
+    const int s = order[i], N = p->sizes[s];
+    const int hop = hop_of(p, s), H = dgc_div_up(p->T, hop);
+    fd.N[i] = N;
+    fd.hop[i] = hop;
+    fd.H[i] = H;
+    fd.window[i] = dgc_ctx_hann_sym(ctx, N);
+    fd.tw[i] = dgc_ctx_twiddles(ctx, N);
+    if (!fd.window[i] || !fd.tw[i]) return DGC_ERR_OOM;
+    fd.lin[i] = part + off_of[s];
+    fd.lg[i] = fd.lin[i] + (long long)H * p->B;
+    fd.first_block[i] = blocks;
+    blocks += dgc_div_up(H, LOSS_THREADS / (N / 8));
+  }
+  fd.first_block[no] = blocks;
+  if (no > 0) {
+    mss_fwd_kernel<<<dim3(blocks, p->B), LOSS_THREADS, FWD_SMEM_BYTES, ctx->stream>>>(pred_dev, target_dev, p->B, p->T, fd);
+    DGC_LAUNCHED(ctx, "mss_fwd");
   }
   // weights: (w / nscales) with nscales = number of usable windows, normalize:true divides by T
   // (Examples/HarmonicE2E/Trainer.swift:553-586, Sources/DGenLazy/Functions.swift:951-954);

@@ -193,18 +193,25 @@ anchor_sum_kernel(const float *__restrict__ f0t, int B, int T, int K, float sr, 
   const float kmax = (float)K, kf0 = (float)(j + 1);
   for (int n = n0; n < n1; ++n) {
     const float f0 = f[n];
-    const bool fast = f0 >= 0.0f && __fmul_rn(kmax, f0) < sr;
+    // one decision per frame, taken as a branch: all increments of this frame already in [0,1)?
+    if (f0 >= 0.0f && __fmul_rn(kmax, f0) < sr) {
 #pragma unroll
-    for (int i = 0; i < P; ++i) {
-      float inc = div_by_const(__fmul_rn(partial_number(kf0, LPC * i), f0), sr, rsr);
-      if (!fast) {
+      for (int i = 0; i < P; ++i) {
+        const float inc = div_by_const(__fmul_rn(partial_number(kf0, LPC * i), f0), sr, rsr);
+        const float s = __fadd_rn(hi[i], inc);
+        lo[i] = __fadd_rn(lo[i], __fsub_rn(inc, __fsub_rn(s, hi[i])));
+        hi[i] = s;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < P; ++i) {
+        float inc = div_by_const(__fmul_rn(partial_number(kf0, LPC * i), f0), sr, rsr);
         if (!(inc >= 0.0f && inc < 1.0f)) inc = inc - floorf(inc);
         if (!(inc >= 0.0f && inc < 1.0f)) inc = 0.0f;  // non-finite or rounded up to 1
+        const float s = __fadd_rn(hi[i], inc);
+        lo[i] = __fadd_rn(lo[i], __fsub_rn(inc, __fsub_rn(s, hi[i])));
+        hi[i] = s;
       }
-      float s = __fadd_rn(hi[i], inc);
-      float err = __fsub_rn(inc, __fsub_rn(s, hi[i]));
-      hi[i] = s;
-      lo[i] = __fadd_rn(lo[i], err);
     }
   }
   unsigned long long acc[P];
@@ -389,12 +396,16 @@ __device__ __forceinline__ uint32_t inc_q32(float f0v, float sr, float rsr) {
 // Same thread mapping as the float kernel; the sums of 8 frames are reduced over the group's lanes by a
 // transposing butterfly (7 shuffles per quantity instead of 24), after which lane j owns frame j of the
 // block, divides by the amplitude sum, applies the envelope and stores.
-template <int LPC, int P>
+//
+// MODE 0 renders audio.  MODE 1 writes, per frame, the phase gradient folded over the partials,
+// sum_k k * dL/dphi_k[m] with dL/dphi_k = g_audio * env * a_k / (sum a + eps) * 2 pi cos(2 pi phi_k): the
+// input of the temporal scan that gives dL/df0 (the same walk over the phases, cosine instead of sine).
+template <int LPC, int P, int MODE>
 __global__ void __launch_bounds__(128, 5)
 harmonic_render_q_kernel(dgc_harmonic_params prm, float rsr, const float2 *__restrict__ rowtab,
                          const float *__restrict__ f0t, const float *__restrict__ env,
                          const float *__restrict__ amps, const uint32_t *__restrict__ anchors_q,
-                         float *__restrict__ audio) {
+                         const float *__restrict__ g_audio, float *__restrict__ audio) {
   constexpr int G = 128 / LPC, FB = 8;
   constexpr float THREE_PI = 9.42477796076938f;
   const int B = prm.B, T = prm.T, K = prm.K, F = prm.F;
@@ -448,13 +459,15 @@ harmonic_render_q_kernel(dgc_harmonic_params prm, float rsr, const float2 *__res
       float s1 = 0.0f, s2 = 0.0f;
 #pragma unroll
       for (int i = 0; i < P; ++i) {
-        const float freq = __fmul_rn(partial_number(kf0, LPC * i), f0v);
+        const float kf = partial_number(kf0, LPC * i);
+        const float freq = __fmul_rn(kf, f0v);
         const float a = fmaf(fr, dl[i], alo[i]);
         const float ph1 = __uint_as_float(__funnelshift_r(q[i], 0x7Fu, 9));  // 1 + phase
-        const float sn = __sinf(fmaf(ph1, TWO_PI_F, -THREE_PI));
+        const float xr = fmaf(ph1, TWO_PI_F, -THREE_PI);
         if (freq < nyq) {  // Nyquist mask on the reference's single-precision product
           s2 += a;
-          s1 = fmaf(sn, a, s1);
+          if (MODE == 0) s1 = fmaf(__sinf(xr), a, s1);
+          else s1 = fmaf(__cosf(xr), kf * a, s1);
         }
         q[i] += incv;
         incv += step;
@@ -493,8 +506,10 @@ harmonic_render_q_kernel(dgc_harmonic_params prm, float rsr, const float2 *__res
     const float r2 = (h0 ? B2[1] : B2[0]) + __shfl_xor_sync(0xffffffffu, h0 ? B2[0] : B2[1], 1);
     const int n = n0 + blk * FB + (j & 7);
     if (active && j < 8 && n < T) {
-      const float val = -r1 / (r2 + 1e-8f) * envp[n];
-      dst[n] = prm.accumulate ? dst[n] + val : val;
+      // sin(2 pi p) = -sin(xr), cos(2 pi p) = -cos(xr)
+      float val = -r1 / (r2 + 1e-8f) * envp[n];
+      if (MODE == 1) val *= TWO_PI_F * g_audio[(size_t)b * T + n];
+      dst[n] = (MODE == 0 && prm.accumulate) ? dst[n] + val : val;
     }
   }
 }
@@ -537,14 +552,64 @@ void launch_render(dgc_ctx *ctx, const dgc_harmonic_params &p, const float *play
                                                                  anchors, audio);
 }
 
-template <int LPC, int P>
+template <int LPC, int P, int MODE>
 void launch_render_q(dgc_ctx *ctx, const dgc_harmonic_params &p, const float2 *rowtab, const dgc_harmonic_extra &x,
-                     const float *amps, float *audio) {
+                     const float *amps, const float *g_audio, float *out) {
   int C = (p.T + CH - 1) / CH;
   constexpr int G = 128 / LPC;
   dim3 grid(dgc_div_up(C, G), p.B);
-  harmonic_render_q_kernel<LPC, P><<<grid, 128, 0, ctx->stream>>>(p, 1.0f / p.sample_rate, rowtab, x.f0t, x.env, amps,
-                                                                   x.anchors_q, audio);
+  harmonic_render_q_kernel<LPC, P, MODE><<<grid, 128, 0, ctx->stream>>>(p, 1.0f / p.sample_rate, rowtab, x.f0t, x.env,
+                                                                         amps, x.anchors_q, g_audio, out);
+}
+
+// out[e][n] = scale * sum_{m > n} g[e][m]: the reverse exclusive scan of the reference's temporalGradScan
+// (Sources/DGen/Emit+TemporalGradient.swift:60-88, no resets).  One block per element row; every thread
+// owns a contiguous run of frames, run totals are scanned in double through shared memory.
+constexpr int TSCAN_THREADS = 1024;
+__global__ void __launch_bounds__(TSCAN_THREADS)
+temporal_suffix_scan_kernel(const float *__restrict__ g, int T, float scale, float *__restrict__ out) {
+  __shared__ double tot[TSCAN_THREADS];
+  const float *row = g + (size_t)blockIdx.x * T;
+  float *orow = out + (size_t)blockIdx.x * T;
+  const int per = (T + TSCAN_THREADS - 1) / TSCAN_THREADS;
+  const int n0 = min(T, (int)threadIdx.x * per), n1 = min(T, n0 + per);
+  double s = 0.0;
+  for (int n = n0; n < n1; ++n) s += (double)row[n];
+  tot[threadIdx.x] = s;
+  __syncthreads();
+  // inclusive suffix scan over the run totals (Hillis-Steele, 10 steps)
+  for (int off = 1; off < TSCAN_THREADS; off <<= 1) {
+    double add = threadIdx.x + off < TSCAN_THREADS ? tot[threadIdx.x + off] : 0.0;
+    __syncthreads();
+    tot[threadIdx.x] += add;
+    __syncthreads();
+  }
+  double carry = threadIdx.x + 1 < TSCAN_THREADS ? tot[threadIdx.x + 1] : 0.0;  // everything after this run
+  for (int n = n1 - 1; n >= n0; --n) {
+    orow[n] = (float)(carry * (double)scale);
+    carry += (double)row[n];
+  }
+}
+
+// g_f0[r][b] = sum over the frames whose lerp touches control row r of weight * G[b][n]: (1 - fr) where r is
+// the floor row, fr where r is the next row (Sources/DGen/Emit+RowSelection.swift:166-199 backward).
+__global__ void f0_rows_grad_kernel(const float2 *__restrict__ rowtab, const int *__restrict__ ranges,
+                                    const float *__restrict__ G, int F, int B, int T, float *__restrict__ g_f0) {
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= F * B) return;
+  const int r = idx / B, b = idx - r * B;
+  const float *Gb = G + (size_t)b * T;
+  double acc = 0.0;
+  for (int run = 0; run < 2; ++run) {
+    const int s0 = ranges[r * 4 + 2 * run], s1 = ranges[r * 4 + 2 * run + 1];
+    for (int n = s0; n < s1; ++n) acc += (double)__fsub_rn(1.0f, rowtab[n].y) * (double)Gb[n];
+  }
+  const int prev = (r + F - 1) % F;
+  for (int run = 0; run < 2; ++run) {
+    const int s0 = ranges[prev * 4 + 2 * run], s1 = ranges[prev * 4 + 2 * run + 1];
+    for (int n = s0; n < s1; ++n) acc += (double)rowtab[n].y * (double)Gb[n];
+  }
+  g_f0[(size_t)r * B + b] = (float)acc;
 }
 
 }  // namespace
@@ -706,7 +771,7 @@ DGC_EXPORT int32_t dgc_harmonic_render(dgc_ctx *ctx, const dgc_harmonic_params *
   if (p->phase_mode == DGC_PHASE_SCAN) {
     const float2 *rowtab = dgc_ctx_row_table(ctx, p->F, p->T);
     if (!rowtab) return DGC_ERR_CUDA;
-#define RENDERQ(LPC, P) launch_render_q<LPC, P>(ctx, *p, rowtab, extra, amps_dev, audio_dev)
+#define RENDERQ(LPC, P) launch_render_q<LPC, P, 0>(ctx, *p, rowtab, extra, amps_dev, nullptr, audio_dev)
     DGC_PICK_GROUP(K, RENDERQ);
 #undef RENDERQ
   } else {
@@ -715,5 +780,55 @@ DGC_EXPORT int32_t dgc_harmonic_render(dgc_ctx *ctx, const dgc_harmonic_params *
 #undef RENDER
   }
   DGC_LAUNCHED(ctx, "harmonic_render");
+  return DGC_OK;
+}
+
+DGC_EXPORT int32_t dgc_temporal_grad_scan(dgc_ctx *ctx, const float *g_dev, int32_t E, int32_t T, float scale,
+                                          float *out_dev) {
+  if (!ctx) return DGC_ERR_INVALID;
+  DGC_REQUIRE(ctx, g_dev && out_dev, "null pointer");
+  DGC_REQUIRE(ctx, E > 0 && T > 0, "E and T must be positive");
+  DGC_REQUIRE(ctx, g_dev != out_dev, "the scan is not in place");
+  temporal_suffix_scan_kernel<<<E, TSCAN_THREADS, 0, ctx->stream>>>(g_dev, T, scale, out_dev);
+  DGC_LAUNCHED(ctx, "temporal_grad_scan");
+  return DGC_OK;
+}
+
+DGC_EXPORT uint64_t dgc_harmonic_f0_bwd_scratch_floats(const dgc_harmonic_params *p) {
+  if (!p || p->B <= 0 || p->T <= 0 || p->K <= 0) return 0;
+  return dgc_harmonic_scratch_floats(p) + 2 * (((uint64_t)p->B * p->T + 3) & ~3ull) + 16;
+}
+
+DGC_EXPORT int32_t dgc_harmonic_f0_bwd(dgc_ctx *ctx, const dgc_harmonic_params *p, const float *f0_dev,
+                                       const float *uv_dev, const float *amps_dev, const float *gain_dev,
+                                       const float *g_audio_dev, float *scratch_dev, float *g_f0_dev) {
+  if (!ctx) return DGC_ERR_INVALID;
+  DGC_REQUIRE(ctx, p && f0_dev && uv_dev && amps_dev && gain_dev && g_audio_dev && g_f0_dev, "null pointer");
+  float *scratch = scratch_dev ? scratch_dev : dgc_ctx_scratch(ctx, dgc_harmonic_f0_bwd_scratch_floats(p));
+  if (!scratch) return DGC_ERR_OOM;
+  // the gradient walks the phases of the scan mode whatever mode rendered the audio: the two differ by
+  // < 3e-5 turns, far inside the gradient tolerance
+  dgc_harmonic_params q = *p;
+  q.phase_mode = DGC_PHASE_SCAN;
+  q.accumulate = 0;
+  const float *play = nullptr, *anchors = nullptr;
+  dgc_harmonic_extra extra;
+  int32_t rc = dgc_harmonic_prepare(ctx, &q, f0_dev, scratch, &play, &anchors, uv_dev, gain_dev, &extra);
+  if (rc != DGC_OK) return rc;
+  const float2 *rowtab = dgc_ctx_row_table(ctx, q.F, q.T);
+  const int *ranges = dgc_ctx_row_ranges(ctx, q.F, q.T);
+  if (!rowtab || !ranges) return DGC_ERR_UNSUPPORTED;
+  const uint64_t bt = ((uint64_t)q.B * q.T + 3) & ~3ull;
+  float *gphi = scratch + ((dgc_harmonic_scratch_floats(&q) + 3) & ~3ull), *gsum = gphi + bt;
+  const int K = q.K;
+#define PHGRAD(LPC, P) launch_render_q<LPC, P, 1>(ctx, q, rowtab, extra, amps_dev, g_audio_dev, gphi)
+  DGC_PICK_GROUP(K, PHGRAD);
+#undef PHGRAD
+  DGC_LAUNCHED(ctx, "harmonic_phase_grad");
+  temporal_suffix_scan_kernel<<<q.B, TSCAN_THREADS, 0, ctx->stream>>>(gphi, q.T, 1.0f / q.sample_rate, gsum);
+  DGC_LAUNCHED(ctx, "temporal_grad_scan");
+  f0_rows_grad_kernel<<<dgc_div_up((int64_t)q.F * q.B, 128), 128, 0, ctx->stream>>>(rowtab, ranges, gsum, q.F, q.B, q.T,
+                                                                                g_f0_dev);
+  DGC_LAUNCHED(ctx, "f0_rows_grad");
   return DGC_OK;
 }

@@ -94,6 +94,9 @@ SIGNATURES = {
     "dgc_linear_bwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp]),
     "dgc_adam_step": (_i32, [_vp, _vp, _vp, _vp, _vp, _u64, _i32, _f, _f, _f, _f]),
     "dgc_sanitize": (_i32, [_vp, _vp, _u64, _vp]),
+    "dgc_harmonic_f0_bwd_scratch_floats": (_u64, [_vp]),
+    "dgc_harmonic_f0_bwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "dgc_temporal_grad_scan": (_i32, [_vp, _vp, _i32, _i32, _f, _vp]),
     "dgc_hn_forward_loss_host": (_i32, [_vp, C.POINTER(HnStep)] + [_vp] * 9 + [C.POINTER(C.c_double), _vp]),
 }
 
@@ -301,6 +304,23 @@ class Context:
         self.check(self.lib.dgc_harmonic_render_bwd(self.h, C.byref(p), _ptr(f0), _ptr(uv), _ptr(amps), _ptr(gain),
                                                     _ptr(g_audio), None, _ptr(g)))
         return g
+
+    def harmonic_f0_bwd(self, f0, uv, amps, gain, g_audio, T, sr, scale=1.0):
+        """d loss / d f0 [F][B] through the phases (temporal gradient of the phasor)."""
+        F, B = f0.shape
+        K = amps.shape[2]
+        p = HarmonicParams(B, T, K, F, sr, scale, PHASE_SCAN, 0)
+        g = self._empty(F, B)
+        self.check(self.lib.dgc_harmonic_f0_bwd(self.h, C.byref(p), _ptr(f0), _ptr(uv), _ptr(amps), _ptr(gain),
+                                                _ptr(g_audio), None, _ptr(g)))
+        return g
+
+    def temporal_grad_scan(self, g, scale=1.0):
+        """out[e][n] = scale * sum_{m>n} g[e][m]."""
+        E, T = g.shape
+        out = self._empty(E, T)
+        self.check(self.lib.dgc_temporal_grad_scan(self.h, _ptr(g), E, T, scale, _ptr(out)))
+        return out
 
     def fir_noise_bwd(self, noise, noise_gain, g_audio, F, taps, scale=0.12):
         B, T = noise.shape

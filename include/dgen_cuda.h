@@ -152,6 +152,20 @@ uint64_t dgc_harmonic_bwd_scratch_floats(const dgc_harmonic_params *p);
 int32_t dgc_harmonic_render_bwd(dgc_ctx *ctx, const dgc_harmonic_params *p, const float *f0_dev, const float *uv_dev,
                                 const float *amps_dev, const float *gain_dev, const float *g_audio_dev,
                                 float *scratch_dev, float *g_amps_dev);
+/* Gradient of the harmonic branch w.r.t. the fundamental table: g_f0 [F][B] from g_audio [B][T], through the
+ * phases: dL/dfreq_k[n] = (1/sr) * sum_{m>n} dL/dphi_k[m] (exclusive reverse scan; the wrap is the identity,
+ * the Nyquist comparison has no gradient), freq_k = k * sampleRow(f0).
+ * replaces: temporalGradStore / temporalGradScan / temporalGradRead of the phasor
+ * (Sources/DGen/Gradients.swift:216-261, Sources/DGen/Emit+TemporalGradient.swift:15-110) chained with the
+ * backward of sin, mul, sum and sampleRow. */
+uint64_t dgc_harmonic_f0_bwd_scratch_floats(const dgc_harmonic_params *p);
+int32_t dgc_harmonic_f0_bwd(dgc_ctx *ctx, const dgc_harmonic_params *p, const float *f0_dev, const float *uv_dev,
+                            const float *amps_dev, const float *gain_dev, const float *g_audio_dev,
+                            float *scratch_dev, float *g_f0_dev);
+/* The scan alone: out[e][n] = scale * sum_{m>n} g[e][m] for E rows of T frames (not in place).
+ * replaces: temporalGradScan + temporalGradRead (Emit+TemporalGradient.swift:60-110) for a graph without
+ * resets; scale = 1/sampleRate for a phasor, 1 for an accum. */
+int32_t dgc_temporal_grad_scan(dgc_ctx *ctx, const float *g_dev, int32_t E, int32_t T, float scale, float *out_dev);
 /* Gradient of the noise branch w.r.t. the tap table: g_taps [F][B][taps] from g_audio [B][T]. */
 int32_t dgc_fir_noise_bwd(dgc_ctx *ctx, const dgc_fir_params *p, const float *noise_dev, const float *noise_gain_dev,
                           const float *g_audio_dev, float *g_taps_dev);

@@ -37,8 +37,12 @@ def lerp_rows(table, rows):
     return (1 - fr).reshape(shape) * table[lo] + fr.reshape(shape) * table[hi]
 
 
-def harmonic_render(f0, uv, amps, gain, T, sr, rows, scale=1.0):
-    """Examples/HarmonicE2E/Synth.swift:47-95. f0/uv/gain [F,B], amps [F,B,K] -> audio [B,T]."""
+def harmonic_render(f0, uv, amps, gain, T, sr, rows, scale=1.0, reference_increments=True):
+    """Examples/HarmonicE2E/Synth.swift:47-95. f0/uv/gain [F,B], amps [F,B,K] -> audio [B,T].
+    The gradient w.r.t. f0 flows through the phases as the reference's temporal gradient defines it
+    (Sources/DGen/Gradients.swift:216-261: exclusive reverse sum of the phase gradients / sr; floor and the
+    Nyquist comparison have no gradient).  reference_increments=False evaluates the increments in double
+    as well (a smooth function of f0, used for the finite-difference check)."""
     F, B, K = amps.shape
     # The phasor's input is single-precision data in the reference graph (f0 is not a parameter): the
     # per-frame increment is RN(RN(k * f0t) / sr) with f0t the strict single-precision lerp, exactly the
@@ -52,7 +56,12 @@ def harmonic_render(f0, uv, amps, gain, T, sr, rows, scale=1.0):
     f0t32 = ((f32(1.0) - fr32) * f0n[lo.numpy()]).astype(f32) + (fr32 * f0n[hi.numpy()]).astype(f32)
     k32 = np.arange(1, K + 1, dtype=f32)
     freq32 = (f0t32[:, :, None] * k32).astype(f32)          # [T,B,K]
-    inc = t64((freq32 / f32(sr)).astype(f32))
+    k = torch.arange(1, K + 1, dtype=DT)
+    inc_exact = lerp_rows(f0, rows)[:, :, None] * k / sr    # differentiable, double
+    if reference_increments:                                # reference values, exact derivative
+        inc = t64((freq32 / f32(sr)).astype(f32)) + (inc_exact - inc_exact.detach())
+    else:
+        inc = inc_exact
     freq = t64(freq32)
     phase = torch.cumsum(inc, 0) - inc                      # phase before the update (first frame 0)
     phase = phase - torch.floor(phase)

@@ -91,3 +91,30 @@ def test_backward_kernels_are_deterministic(ctx):
     a = ctx.harmonic_render_bwd(*args).cpu().numpy()
     b = ctx.harmonic_render_bwd(*args).cpu().numpy()
     assert np.array_equal(a, b)
+
+
+def test_temporal_grad_scan_is_the_exclusive_reverse_sum(ctx):
+    """temporalGradScan without resets (Sources/DGen/Emit+TemporalGradient.swift:60-88): out[n] = sum_{m>n} g[m]."""
+    rng = np.random.default_rng(3)
+    for E, T in [(1, 1), (3, 7), (2, 1025), (5, 64000)]:
+        g = rng.standard_normal((E, T)).astype(f32)
+        want = (np.cumsum(g[:, ::-1].astype(np.float64), axis=1)[:, ::-1] - g) / 48000.0
+        got = ctx.temporal_grad_scan(dev(g), 1.0 / 48000.0).cpu().numpy()
+        assert np.abs(got - want).max() <= 1e-6 * max(np.abs(want).max(), 1e-30), (E, T)
+
+
+@pytest.mark.parametrize("B,T,K,F", [(2, 4096, 12, 32), (3, 5000, 40, 17), (1, 64000, 100, 1000)])
+def test_harmonic_f0_gradient_against_fp64_autograd(ctx, B, T, K, F):
+    """d loss / d f0 through the phases (phasor temporal gradient + sin + sum + sampleRow backward) against the
+    fp64 autograd evaluation of the same graph: 1e-3 relative to the largest entry."""
+    d = wl.harmonic_noise_inputs(50 + K, B=B, T=T, K=K, F=F)
+    rng = np.random.default_rng(K)
+    g = rng.standard_normal((B, T)).astype(f32)
+    f0 = to.t64(d["f0"]).requires_grad_(True)
+    audio = to.harmonic_render(f0, to.t64(d["uv"]), to.t64(d["amps"]), to.t64(d["gain"]), T, d["sr"], to.rows_of(F, T))
+    (audio * to.t64(g)).sum().backward()
+    want = f0.grad.numpy()
+    got = ctx.harmonic_f0_bwd(dev(d["f0"]), dev(d["uv"]), dev(d["amps"]), dev(d["gain"]), dev(g), T, d["sr"]).cpu().numpy()
+    err = np.abs(got - want).max() / np.abs(want).max()
+    print("f0 grad rel err %.2e" % err)
+    assert err < 1e-3

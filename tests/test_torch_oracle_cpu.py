@@ -40,3 +40,29 @@ def test_autograd_loss_gradient_agrees_with_the_c_gradient_oracle():
     to.mss_loss(xt, to.t64(y), sizes=(256, 64)).backward()
     want = orc.mss_loss_grad(x, y, sizes=(256, 64))
     assert np.abs(xt.grad.numpy() - want).max() < 1e-5 * np.abs(want).max()
+
+
+def test_f0_gradient_of_the_autograd_graph_agrees_with_finite_differences():
+    """The temporal gradient through the phases (d loss / d f0) of the fp64 graph against central differences
+    of the same graph with double-precision increments (a smooth function of f0)."""
+    import torch
+    F, B, K, T, sr = 6, 2, 5, 512, 16000.0
+    rng = np.random.default_rng(9)
+    f0 = to.t64(rng.uniform(100.0, 400.0, (F, B)).astype(np.float32)).requires_grad_(True)
+    uv, gain = to.t64(rng.uniform(0.5, 1.0, (F, B))), to.t64(rng.uniform(0.5, 1.0, (F, B)))
+    amps = to.t64(rng.uniform(0.1, 1.0, (F, B, K)))
+    g = to.t64(rng.standard_normal((B, T)))
+    rows = to.rows_of(F, T)
+
+    def loss(f):
+        return (to.harmonic_render(f, uv, amps, gain, T, sr, rows, reference_increments=False) * g).sum()
+    loss(f0).backward()
+    got = f0.grad.numpy()
+    fd = np.zeros_like(got)
+    with torch.no_grad():
+        for r in range(F):
+            for b in range(B):
+                e = torch.zeros_like(f0)
+                e[r, b] = 1e-4
+                fd[r, b] = float(loss(f0 + e) - loss(f0 - e)) / 2e-4
+    assert np.abs(got - fd).max() < 1e-5 * np.abs(fd).max()
