@@ -356,6 +356,9 @@ def run_train(args, rank, world, local_rank):
     pin = lambda a: torch.from_numpy(np.ascontiguousarray(a)).pin_memory()
     model = tr.HarmonicModel(ctx, B, T, K=K, F=F, sr=sr, nbands=NB, taps=NT, hidden=512, ir_len=16000, conv_n=2048,
                              conv_hop=1024, sizes=SIZES, seed=7, global_voices=B * world)
+    # gradient exchange: the context's own NCCL communicator (dgc_allreduce_sum through the C ABI) unless
+    # --allreduce torch asks for the torch.distributed call
+    model.use_ctx_comm = args.allreduce == "dgc" and sharding.init_ctx_comm(ctx)
     # target: rendered from seed+1 controls (setup, untimed)
     G = {k: dev(v) for k, v in tg.items() if isinstance(v, np.ndarray)}
     target = ctx.harmonic_render(G["f0"], G["uv"], G["amps"], G["gain"], T, sr)
@@ -414,8 +417,9 @@ def run_train(args, rank, world, local_rank):
                 "config": {"workload": "full training step (BASELINE.json configs[4])", "voices_per_gpu": B,
                            "global_voices": B * world, "frames": T, "harmonics": K, "control_frames": F,
                            "controller": "MLP 2-512-512-512-165 fp32", "ir_taps": 16000, "fft_sizes": list(SIZES),
-                           "optimizer": "Adam lr 1e-3", "parallelism": "dp%d, NCCL all-reduce of %d gradients"
-                           % (world, model.n_params), "l2": "working set (>1 GB per step) exceeds L2"},
+                           "optimizer": "Adam lr 1e-3", "parallelism": "dp%d, NCCL all-reduce of %d gradients (%s)"
+                           % (world, model.n_params,
+                              "dgc_allreduce_sum" if model.use_ctx_comm else "torch.distributed"), "l2": "working set (>1 GB per step) exceeds L2"},
                 "samples_per_s": B * world * T / (ms * 1e-3), "clocks": clocks,
                 "e2e": {"value": e2e_ms / args.steps, "unit": "ms", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 8},
                 "gpu_launches": int(launches), "loss": glob_loss}
@@ -434,6 +438,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--workload", default="fwd_loss", choices=["fwd_loss", "train"],
                     help="fwd_loss: synthesis forward + loss (the headline metric); train: full training step")
+    ap.add_argument("--allreduce", default="dgc", choices=["dgc", "torch"],
+                    help="training workload: gradient all-reduce through the library's communicator or torch's")
     ap.add_argument("--voices", type=int, default=0,
                     help="voices per GPU (default: the configuration's 16); other values are for profiling "
                          "captures and scaling studies, not for the headline number")

@@ -42,6 +42,9 @@ struct dgc_ctx {
   cudaEvent_t copy_ev[3] = {nullptr, nullptr, nullptr};
   float *stage_dev = nullptr;
   uint64_t stage_floats = 0;
+  // NCCL communicator of the gradient exchange (comm.cu); nullptr = a world of one
+  void *comm = nullptr;
+  int comm_world = 1;
 };
 
 int32_t dgc_fail(dgc_ctx *ctx, int32_t code, const char *fmt, ...);

@@ -185,6 +185,7 @@ DGC_EXPORT int32_t dgc_ctx_destroy(dgc_ctx *c) {
   for (auto &kv : c->hann_per) cudaFree(kv.second);
   for (auto &kv : c->twiddles) cudaFree(kv.second);
   if (c->scratch) cudaFree(c->scratch);
+  if (c->comm) dgc_comm_destroy(c);
   if (c->stage_dev) cudaFree(c->stage_dev);
   for (auto &e : c->copy_ev)
     if (e) cudaEventDestroy(e);

@@ -94,6 +94,14 @@ SIGNATURES = {
     "dgc_linear_bwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp]),
     "dgc_adam_step": (_i32, [_vp, _vp, _vp, _vp, _vp, _u64, _i32, _f, _f, _f, _f]),
     "dgc_sanitize": (_i32, [_vp, _vp, _u64, _vp]),
+    "dgc_module_load": (_i32, [_vp, _vp, _u64, C.POINTER(_vp)]),
+    "dgc_module_compile": (_i32, [_vp, C.c_char_p, C.c_char_p, C.POINTER(_vp)]),
+    "dgc_module_unload": (_i32, [_vp]),
+    "dgc_launch": (_i32, [_vp, C.c_char_p, C.POINTER(_u32), C.POINTER(_u32), _u32, C.POINTER(_vp)]),
+    "dgc_comm_unique_id": (_i32, [C.c_char_p]),
+    "dgc_comm_init": (_i32, [_vp, _i32, _i32, C.c_char_p]),
+    "dgc_allreduce_sum": (_i32, [_vp, _vp, _u64]),
+    "dgc_comm_destroy": (_i32, [_vp]),
     "dgc_harmonic_f0_bwd_scratch_floats": (_u64, [_vp]),
     "dgc_harmonic_f0_bwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "dgc_temporal_grad_scan": (_i32, [_vp, _vp, _i32, _i32, _f, _vp]),
@@ -101,6 +109,36 @@ SIGNATURES = {
 }
 
 _lib = None
+
+
+def comm_unique_id():
+    """128 bytes that rank 0 creates and every rank passes to Context.comm_init."""
+    buf = C.create_string_buffer(128)
+    rc = load().dgc_comm_unique_id(buf)
+    if rc != DGC_OK:
+        raise DgenCudaError("dgc_comm_unique_id failed: %d (NCCL not found?)" % rc)
+    return buf.raw
+
+
+class Module:
+    """A loaded set of generated kernels (dgc_module)."""
+
+    def __init__(self, ctx, handle):
+        self.ctx, self.h = ctx, handle
+
+    def launch(self, name, grid, block, args, smem=0):
+        """args: ctypes scalars (c_int, c_float, ...) or torch CUDA tensors (passed as device pointers)."""
+        def dim3(v):
+            v = tuple(v) if isinstance(v, (tuple, list)) else (v,)
+            return (_u32 * 3)(*(v + (1, 1, 1))[:3])
+        keep = [a if isinstance(a, C._SimpleCData) else _vp(a.data_ptr()) for a in args]
+        argv = (_vp * max(1, len(keep)))(*[C.cast(C.byref(k), _vp) for k in keep])
+        self.ctx.check(self.ctx.lib.dgc_launch(self.h, name.encode(), dim3(grid), dim3(block), smem, argv))
+
+    def close(self):
+        if self.h:
+            self.ctx.lib.dgc_module_unload(self.h)
+            self.h = None
 
 
 def load():
@@ -381,6 +419,29 @@ class Context:
         out = x if out is None else out
         self.check(self.lib.dgc_sanitize(self.h, _ptr(x), x.numel(), _ptr(out)))
         return out
+
+    # ---- generated blocks ----------------------------------------------------------------------
+    def compile_module(self, cuda_source, name="dgen_block.cu"):
+        """CUDA C source of generated blocks -> Module (NVRTC, sm_100a)."""
+        m = _vp()
+        self.check(self.lib.dgc_module_compile(self.h, cuda_source.encode(), name.encode(), C.byref(m)))
+        return Module(self, m)
+
+    def load_module(self, image):
+        """cubin bytes or PTX text -> Module."""
+        if isinstance(image, str):
+            image = image.encode() + b"\0"
+        m = _vp()
+        self.check(self.lib.dgc_module_load(self.h, image, len(image), C.byref(m)))
+        return Module(self, m)
+
+    # ---- gradient exchange ---------------------------------------------------------------------
+    def comm_init(self, world, rank, uid):
+        self.check(self.lib.dgc_comm_init(self.h, world, rank, uid))
+
+    def allreduce_sum_(self, buf):
+        self.check(self.lib.dgc_allreduce_sum(self.h, _ptr(buf), buf.numel()))
+        return buf
 
     # ---- composite, host buffers --------------------------------------------------------------
     def hn_forward_loss_host(self, step, f0, uv, amps, gain, noise_gain, taps_or_bands, w, noise, target,

@@ -37,3 +37,15 @@ def allreduce_sum_(flat_grad):
     if dist.is_initialized() and dist.get_world_size() > 1:
         dist.all_reduce(flat_grad, op=dist.ReduceOp.SUM)
     return flat_grad
+
+
+def init_ctx_comm(ctx):
+    """Gives `ctx` its own NCCL communicator over the ranks of the initialised torch.distributed group:
+    rank 0 creates the id, the group's object broadcast carries it (the one use of the process group)."""
+    import dgen_b200
+    if not (dist.is_initialized() and dist.get_world_size() > 1):
+        return False
+    box = [dgen_b200.comm_unique_id() if dist.get_rank() == 0 else None]
+    dist.broadcast_object_list(box, src=0)
+    ctx.comm_init(dist.get_world_size(), dist.get_rank(), box[0])
+    return True

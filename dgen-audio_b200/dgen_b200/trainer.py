@@ -144,7 +144,10 @@ class HarmonicModel:
         """forward + backward + gradient all-reduce + Adam; returns the device loss tensor (local mean)."""
         self.forward(X, f0, uv, gain, noise_gain, noise, w_fs, target)
         self.backward(X, f0, uv, gain, noise_gain, noise, w_fs, target)
-        sharding.allreduce_sum_(self.grads)
+        if getattr(self, "use_ctx_comm", False):
+            self.ctx.allreduce_sum_(self.grads)   # NCCL communicator owned by the context (C ABI)
+        else:
+            sharding.allreduce_sum_(self.grads)   # torch.distributed process group
         self.step_index += 1
         self.ctx.adam_step(self.params, self.grads, self.m, self.v, self.step_index, lr=lr)
         return self.loss

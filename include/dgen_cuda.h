@@ -294,6 +294,34 @@ int32_t dgc_adam_step(dgc_ctx *ctx, float *theta_dev, const float *grad_dev, flo
  * (toolchain/include/dgen_runtime.h:59-84, Sources/DGen/Renderer/CRenderer.swift:1021-1039). */
 int32_t dgc_sanitize(dgc_ctx *ctx, const float *in_dev, uint64_t n, float *out_dev);
 
+/* ---- generated blocks -------------------------------------------------------------------------------
+ * Device code the host's renderer emits for elementwise blocks that no primitive above covers.
+ * replaces: compiling the C renderer's source and loading it (Sources/DGen/Runtime.swift:291-311) and
+ * the call of the generated `process` symbol (toolchain/include/dgen_runtime.h:282-290).
+ * dgc_module_load takes a cubin for sm_100a or NUL-terminated PTX; dgc_module_compile takes CUDA C and
+ * compiles it in process with NVRTC (found at run time; DGC_NVRTC_PATH overrides the search).  Kernels are
+ * extern "C" __global__ functions, launched on the context stream with the argument-pointer array of
+ * cudaLaunchKernel. */
+typedef struct dgc_module dgc_module;
+int32_t dgc_module_load(dgc_ctx *ctx, const void *image, uint64_t size, dgc_module **out);
+int32_t dgc_module_compile(dgc_ctx *ctx, const char *cuda_source, const char *name, dgc_module **out);
+int32_t dgc_module_unload(dgc_module *m);
+int32_t dgc_launch(dgc_module *m, const char *kernel_name, const uint32_t grid[3], const uint32_t block[3],
+                   uint32_t smem_bytes, void **args);
+
+/* ---- gradient exchange between GPUs ------------------------------------------------------------------
+ * One process per GPU, one communicator per context (NCCL, found at run time; DGC_NCCL_PATH overrides).
+ * Rank 0 creates the id, the host hands its DGC_COMM_ID_BYTES bytes to every rank, every rank calls
+ * dgc_comm_init, then dgc_allreduce_sum(buf) leaves the sum over ranks in buf on every rank (in place, on
+ * the context stream).  Without a communicator dgc_allreduce_sum is the identity (a world of one).
+ * replaces: nothing in the reference (it trains on one device); the buffer is what readGradients collects
+ * (Sources/DGenLazy/Backward.swift:132-165). */
+#define DGC_COMM_ID_BYTES 128
+int32_t dgc_comm_unique_id(uint8_t *id_out);
+int32_t dgc_comm_init(dgc_ctx *ctx, int32_t world, int32_t rank, const uint8_t *id);
+int32_t dgc_allreduce_sum(dgc_ctx *ctx, float *buf_dev, uint64_t n_floats);
+int32_t dgc_comm_destroy(dgc_ctx *ctx);
+
 /* ---- composite steps with host buffers (the call a host makes per batch) ------------------------ */
 typedef struct dgc_hn_step {
   dgc_harmonic_params harm;
