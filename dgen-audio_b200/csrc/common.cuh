@@ -36,6 +36,8 @@ struct dgc_ctx {
   double *loss_accum = nullptr;                      // 256 doubles: [0..64) results, [64..) per-block sums
   float *wt_buf = nullptr;  // transposed copy of the current layer's weights (matmul forward)
   uint64_t wt_floats = 0;
+  float *dzt_buf = nullptr;  // transposed copy of the current layer's output gradient (matmul backward)
+  uint64_t dzt_floats = 0;
   // staging for the host-buffer composite entry points; uploads run on their own stream so that the
   // first kernels start while later inputs are still crossing PCIe
   cudaStream_t copy_stream = nullptr;

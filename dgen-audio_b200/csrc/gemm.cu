@@ -120,7 +120,9 @@ bool use_tensor_cores() {
 }
 
 template <bool TA, bool TB, int EPI>
-int32_t launch_sgemm(dgc_ctx *ctx, const float *A, const float *B, const float *bias, int M, int N, int K, float *C) {
+int32_t launch_sgemm(dgc_ctx *ctx, const float *A, const float *B, const float *bias, int M, int N, int K, float *C,
+                     float *Ct = nullptr, bool *ct_written = nullptr) {
+  if (ct_written) *ct_written = false;
   const bool tc = use_tensor_cores() && (double)M * N * K >= (double)(1 << 21) && K >= 32;
   const int bm = tc ? dgtc::TBM : BM, bn = tc ? dgtc::TBN : BN;
   const int tiles = dgc_div_up(N, bn) * dgc_div_up(M, bm);
@@ -140,7 +142,28 @@ int32_t launch_sgemm(dgc_ctx *ctx, const float *A, const float *B, const float *
     if (!dst) return DGC_ERR_OOM;
   }
   dim3 grid(dgc_div_up(N, bn), dgc_div_up(M, bm), splits);
-  if (tc) {
+  static const int kk_bk = [] {   // DGC_GEMM_KK: 0 off; 32 (default) swizzled 32-wide k tiles; 33 / 16 no swizzle, 32 / 16 wide
+    const char *e = getenv("DGC_GEMM_KK");
+    return e ? atoi(e) : 32;
+  }();
+  if (tc && !TA && TB && kk_bk && (K & 3) == 0 && ((((uintptr_t)A) | ((uintptr_t)B)) & 15) == 0 &&
+      (splits == 1 || kps % 32 == 0)) {
+    // both operands contiguous along k: the cp.async pipeline
+#define DGC_KK_LAUNCH(BKV, SWV)                                                                                      \
+  do {                                                                                                              \
+    auto kern = dgtc::tc_gemm_kk_kernel<EPI, BKV, SWV>;                                                             \
+    constexpr int SM = dgtc::KK<BKV, SWV>::SMEM;                                                                    \
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM);                    \
+    if (e != cudaSuccess) return dgc_fail(ctx, DGC_ERR_CUDA, "tc_gemm smem opt-in: %s", cudaGetErrorString(e));     \
+    kern<<<grid, dgtc::THREADS, SM, ctx->stream>>>(A, B, bias, M, N, K, kps, dst, splits == 1 ? Ct : nullptr,       \
+                                                   ctx->status_dev);                                                \
+  } while (0)
+    if (kk_bk == 16) DGC_KK_LAUNCH(16, false);
+    else if (kk_bk == 33) DGC_KK_LAUNCH(32, false);
+    else DGC_KK_LAUNCH(32, true);
+#undef DGC_KK_LAUNCH
+    if (ct_written) *ct_written = Ct && splits == 1;
+  } else if (tc) {
     // tensor-core kernel: operand A is K-major in memory when it is NOT transposed ([M][K]);
     // operand B is K-major in memory when it IS given transposed ([N][K])
     auto kern = dgtc::tc_gemm_kernel<!TA, TB, EPI>;
@@ -168,6 +191,32 @@ __global__ void transpose_kernel(const float *__restrict__ in, int R, int Cc, fl
   int r = r0 + threadIdx.x, c0 = blockIdx.x * 32;
   for (int i = threadIdx.y; i < 32; i += 8)
     if (c0 + i < Cc && r < R) out[(size_t)(c0 + i) * R + r] = t[threadIdx.x][i];
+}
+
+// dZ = dC * act'(C) written twice: dZ[m][n] and the transposed copy dZt[n][m] (32 x 32 tiles through shared
+// memory), so that the weight-gradient product can read both of its operands along the reduction index
+__global__ void act_bwd_t_kernel(const float *__restrict__ dC, const float *__restrict__ Cv, int M, int N, int act,
+                                 float *__restrict__ dZ, float *__restrict__ dZt) {
+  __shared__ float t[32][33];
+  const int n = blockIdx.x * 32 + threadIdx.x, m0 = blockIdx.y * 32;
+  for (int i = threadIdx.y; i < 32; i += 8) {
+    const int m = m0 + i;
+    float g = 0.0f;
+    if (m < M && n < N) {
+      const size_t idx = (size_t)m * N + n;
+      g = dC[idx];
+      if (act == 1) {
+        const float c = Cv[idx];
+        g *= (1.0f - c * c);
+      }
+      dZ[idx] = g;
+    }
+    t[i][threadIdx.x] = g;
+  }
+  __syncthreads();
+  const int m = m0 + threadIdx.x, nb = blockIdx.x * 32;
+  for (int i = threadIdx.y; i < 32; i += 8)
+    if (nb + i < N && m < M) dZt[(size_t)(nb + i) * M + m] = t[threadIdx.x][i];
 }
 
 // dZ = dC * (1 - C^2) in place-compatible form (tanh'), or copy when act == 0
@@ -237,13 +286,14 @@ int32_t dgc_gemm_nt(dgc_ctx *ctx, const float *a, const float *b, int M, int N, 
 }
 
 DGC_EXPORT int32_t dgc_linear_fwd(dgc_ctx *ctx, const float *a_dev, const float *w_dev, const float *bias_dev,
-                                  int32_t M, int32_t K, int32_t N, int32_t act, float *c_dev) {
+                                  int32_t M, int32_t K, int32_t N, int32_t act, float *c_dev, float *ct_dev) {
   if (!ctx) return DGC_ERR_INVALID;
   DGC_REQUIRE(ctx, a_dev && w_dev && c_dev, "null pointer");
   DGC_REQUIRE(ctx, M > 0 && K > 0 && N > 0, "size out of range");
   DGC_REQUIRE(ctx, act == 0 || act == 1, "act must be 0 (none) or 1 (tanh)");
   DGC_REQUIRE(ctx, act == 0 || bias_dev, "tanh layers need a bias");
   int32_t rc;
+  bool ct_done = false;
   if (use_tensor_cores() && (double)M * N * K >= (double)(1 << 24) && (size_t)K * N <= (4u << 20) && (K & 3) == 0) {
     // The weight matrix is small next to the activations: transpose it once so that BOTH operands of the
     // tensor-core kernel are contiguous along k (vector loads straight into the K-major layout).
@@ -258,27 +308,49 @@ DGC_EXPORT int32_t dgc_linear_fwd(dgc_ctx *ctx, const float *a_dev, const float 
     }
     transpose_kernel<<<dim3(dgc_div_up(N, 32), dgc_div_up(K, 32)), dim3(32, 8), 0, ctx->stream>>>(w_dev, K, N, ctx->wt_buf);
     DGC_LAUNCHED(ctx, "transpose_w");
-    if (act == 1) rc = launch_sgemm<false, true, 2>(ctx, a_dev, ctx->wt_buf, bias_dev, M, N, K, c_dev);
-    else if (bias_dev) rc = launch_sgemm<false, true, 1>(ctx, a_dev, ctx->wt_buf, bias_dev, M, N, K, c_dev);
-    else rc = launch_sgemm<false, true, 0>(ctx, a_dev, ctx->wt_buf, nullptr, M, N, K, c_dev);
+    if (act == 1) rc = launch_sgemm<false, true, 2>(ctx, a_dev, ctx->wt_buf, bias_dev, M, N, K, c_dev, ct_dev, &ct_done);
+    else if (bias_dev) rc = launch_sgemm<false, true, 1>(ctx, a_dev, ctx->wt_buf, bias_dev, M, N, K, c_dev, ct_dev, &ct_done);
+    else rc = launch_sgemm<false, true, 0>(ctx, a_dev, ctx->wt_buf, nullptr, M, N, K, c_dev, ct_dev, &ct_done);
   } else
   if (act == 1) rc = launch_sgemm<false, false, 2>(ctx, a_dev, w_dev, bias_dev, M, N, K, c_dev);
   else if (bias_dev) rc = launch_sgemm<false, false, 1>(ctx, a_dev, w_dev, bias_dev, M, N, K, c_dev);
   else rc = launch_sgemm<false, false, 0>(ctx, a_dev, w_dev, nullptr, M, N, K, c_dev);
   if (rc != DGC_OK) return rc;
   DGC_LAUNCHED(ctx, "linear_fwd");
+  if (ct_dev && !ct_done) {  // the matmul kernel that ran has no transposed store: one extra pass
+    transpose_kernel<<<dim3(dgc_div_up(N, 32), dgc_div_up(M, 32)), dim3(32, 8), 0, ctx->stream>>>(c_dev, M, N, ct_dev);
+    DGC_LAUNCHED(ctx, "transpose_c");
+  }
   return DGC_OK;
 }
 
 DGC_EXPORT int32_t dgc_linear_bwd(dgc_ctx *ctx, const float *a_dev, const float *w_dev, const float *c_dev,
                                   const float *dc_dev, int32_t M, int32_t K, int32_t N, int32_t act, float *dz_dev,
-                                  float *da_dev, float *dw_dev, float *dbias_dev) {
+                                  float *da_dev, float *dw_dev, float *dbias_dev, const float *at_dev) {
   if (!ctx) return DGC_ERR_INVALID;
   DGC_REQUIRE(ctx, a_dev && w_dev && dc_dev && dz_dev && dw_dev, "null pointer");
   DGC_REQUIRE(ctx, M > 0 && K > 0 && N > 0, "size out of range");
   DGC_REQUIRE(ctx, act == 0 || (act == 1 && c_dev), "tanh backward needs the layer output");
   const size_t n = (size_t)M * N;
-  act_bwd_kernel<<<dgc_div_up((int64_t)n, 256), 256, 0, ctx->stream>>>(dc_dev, c_dev, n, act, dz_dev);
+  // With a transposed copy of the layer input at hand, the weight gradient reads both operands along the
+  // reduction index m (the asynchronous K-major pipeline): dZ is then written in both orientations.
+  const bool dw_kmajor = at_dev && use_tensor_cores() && (M & 3) == 0 && (double)M * N * K >= (double)(1 << 24) &&
+                         (((uintptr_t)at_dev) & 15) == 0;
+  if (dw_kmajor) {
+    if (!ctx->dzt_buf || ctx->dzt_floats < n) {
+      if (ctx->dzt_buf) {
+        cudaStreamSynchronize(ctx->stream);
+        cudaFree(ctx->dzt_buf);
+        ctx->dzt_buf = nullptr;
+      }
+      DGC_CUDA(ctx, cudaMalloc(&ctx->dzt_buf, n * sizeof(float)));
+      ctx->dzt_floats = n;
+    }
+    act_bwd_t_kernel<<<dim3(dgc_div_up(N, 32), dgc_div_up(M, 32)), dim3(32, 8), 0, ctx->stream>>>(dc_dev, c_dev, M, N, act,
+                                                                                                dz_dev, ctx->dzt_buf);
+  } else {
+    act_bwd_kernel<<<dgc_div_up((int64_t)n, 256), 256, 0, ctx->stream>>>(dc_dev, c_dev, n, act, dz_dev);
+  }
   DGC_LAUNCHED(ctx, "act_bwd");
   if (dbias_dev) {
     const int chunks = dgc_div_up(M, 1024);
@@ -290,7 +362,8 @@ DGC_EXPORT int32_t dgc_linear_bwd(dgc_ctx *ctx, const float *a_dev, const float 
     DGC_LAUNCHED(ctx, "bias_grad_reduce");
   }
   // dW[K][N] = A^T[K][M] * dZ[M][N]
-  int32_t rc = launch_sgemm<true, false, 0>(ctx, a_dev, dz_dev, nullptr, K, N, M, dw_dev);
+  int32_t rc = dw_kmajor ? launch_sgemm<false, true, 0>(ctx, at_dev, ctx->dzt_buf, nullptr, K, N, M, dw_dev)
+                         : launch_sgemm<true, false, 0>(ctx, a_dev, dz_dev, nullptr, K, N, M, dw_dev);
   if (rc != DGC_OK) return rc;
   DGC_LAUNCHED(ctx, "linear_bwd_dw");
   if (da_dev) {

@@ -169,6 +169,57 @@ __device__ __forceinline__ void stash(const float4 (&v)[4], char *hi_part, char 
   }
 }
 
+// Accumulators -> global memory.  Warp w may touch tensor-memory lanes 32 * (w % 4) ..; warps 0-3 take columns
+// 0..63, warps 4-7 the rest; lane = output row.  EPI 0: C = acc ; 1: + bias[n] ; 2: tanh(acc + bias[n]).
+// Ct (optional): a second, transposed copy Ct[n][m] of the result (lanes = consecutive m: 128-byte stores).
+template <int EPI>
+__device__ __forceinline__ void epilogue(uint32_t tmem_d, const float *__restrict__ bias, int M, int N, int m0, int n0,
+                                         float *__restrict__ C, int warp, int lane, float *__restrict__ Ct = nullptr) {
+    const int lane_base = (warp & 3) * 32, col_base = (warp >> 2) * (TBN / 2);
+    const int gm = m0 + lane_base + lane;
+#pragma unroll 1
+    for (int c0 = col_base; c0 < col_base + TBN / 2; c0 += 32) {
+      uint32_t r[32];
+      const uint32_t taddr = tmem_d + ((uint32_t)lane_base << 16) + (uint32_t)c0;
+      asm volatile(
+          "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+          "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+          "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+          : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+            "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+            "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+            "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+          : "r"(taddr));
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      if (gm < M) {
+        float *crow = C + (size_t)gm * N + n0 + c0;
+        const bool vec_ok = ((N & 3) == 0) && (n0 + c0 + 31 < N) && ((((uintptr_t)C) & 15) == 0);
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+          float v[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            float x = __uint_as_float(r[j + u]);
+            int gn = n0 + c0 + j + u;
+            if (EPI >= 1 && gn < N) x += bias[gn];
+            if (EPI == 2) x = tanhf(x);
+            v[u] = x;
+          }
+          if (Ct) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+              if (n0 + c0 + j + u < N) Ct[(size_t)(n0 + c0 + j + u) * M + gm] = v[u];
+          }
+          if (vec_ok) *reinterpret_cast<float4 *>(crow + j) = make_float4(v[0], v[1], v[2], v[3]);
+          else
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+              if (n0 + c0 + j + u < N) crow[j + u] = v[u];
+        }
+      }
+    }
+}
+
 // A_KMAJOR: A stored [M][K]; else stored [K][M].  B_KMAJOR: B stored [N][K]; else stored [K][N].
 // EPI 0: C = acc ; 1: + bias[n] ; 2: tanh(acc + bias[n]).  blockIdx.z selects a k-slice (split-K slab of C).
 template <bool A_KMAJOR, bool B_KMAJOR, int EPI>
@@ -251,45 +302,7 @@ tc_gemm_kernel(const float *__restrict__ A, const float *__restrict__ B, const f
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 
   if (ok && KT > 0) {
-    // warp w may touch tensor-memory lanes 32 * (w % 4) ..; warps 0-3 take columns 0..63, warps 4-7 the rest
-    const int lane_base = (warp & 3) * 32, col_base = (warp >> 2) * (TBN / 2);
-    const int gm = m0 + lane_base + lane;
-#pragma unroll 1
-    for (int c0 = col_base; c0 < col_base + TBN / 2; c0 += 32) {
-      uint32_t r[32];
-      const uint32_t taddr = tmem_d + ((uint32_t)lane_base << 16) + (uint32_t)c0;
-      asm volatile(
-          "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-          "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-          "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
-          : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-            "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-            "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-            "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-          : "r"(taddr));
-      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-      if (gm < M) {
-        float *crow = C + (size_t)gm * N + n0 + c0;
-        const bool vec_ok = ((N & 3) == 0) && (n0 + c0 + 31 < N) && ((((uintptr_t)C) & 15) == 0);
-#pragma unroll
-        for (int j = 0; j < 32; j += 4) {
-          float v[4];
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            float x = __uint_as_float(r[j + u]);
-            int gn = n0 + c0 + j + u;
-            if (EPI >= 1 && gn < N) x += bias[gn];
-            if (EPI == 2) x = tanhf(x);
-            v[u] = x;
-          }
-          if (vec_ok) *reinterpret_cast<float4 *>(crow + j) = make_float4(v[0], v[1], v[2], v[3]);
-          else
-#pragma unroll
-            for (int u = 0; u < 4; ++u)
-              if (n0 + c0 + j + u < N) crow[j + u] = v[u];
-        }
-      }
-    }
+    epilogue<EPI>(tmem_d, bias, M, N, m0, n0, C, warp, lane);
   } else if (KT == 0) {
     // empty reduction range: the slab is zero
     const int gm = m0 + (warp & 3) * 32 + lane;
@@ -298,6 +311,166 @@ tc_gemm_kernel(const float *__restrict__ A, const float *__restrict__ B, const f
         if (n0 + c < N) C[(size_t)gm * N + n0 + c] = 0.0f;
   }
   if (!ok && tid == 0) atomicExch(status, 201);  // an MMA completion never arrived within the spin limit
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 0) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"((uint32_t)TBN) : "memory");
+  }
+}
+
+
+// ---------------------------------------------------------------------------------------------------------
+// Both operands contiguous along k in memory (A [M][K], B [N][K]), K a multiple of 4, 16-byte aligned rows:
+// the asynchronous pipeline.  cp.async copies 16-byte chunks straight into the canonical K-major layout,
+// RAW raw stages deep, PF tiles ahead of the tensor core; the raw fp32 tile IS the "hi" operand (the tensor
+// core reads the top 19 bits of every 32-bit word and ignores the 13 low mantissa bits, i.e. it truncates
+// to TF32 itself), so the threads only compute lo = x - trunc(x), shared memory to shared memory, into one
+// of two lo buffers.  Tile t's MMAs commit to an mbarrier of their own raw stage; the only wait of
+// iteration t is on tile t-2 (it frees both the raw stage about to be refilled and the lo buffer about to
+// be rewritten), two iterations after its MMAs were issued.
+// ---------------------------------------------------------------------------------------------------------
+// SW: the 128-byte-swizzle K-major layout (BK = 32: one row of a tile is exactly one 128-byte swizzle row;
+// 8-row groups of 1024 bytes, 16-byte chunk c of row r stored at chunk c ^ (r % 8)) instead of the
+// no-swizzle layout of 8 x 16-byte core matrices.
+template <int BK, bool SW = false>
+struct KK {
+  static_assert(!SW || BK == 32, "the swizzled layout is built for 128-byte rows");
+  static constexpr int CHUNKS_K = BK / 4;
+  static constexpr int OPER = SW ? TBM * 128 : CHUNKS_K * LBO_BYTES;       // one operand of one tile
+  static constexpr int RAW = 4, PF = 2;
+  static constexpr int RAW_STAGE = 2 * OPER;              // A, B
+  static constexpr int SMEM = (RAW + 2) * RAW_STAGE + 128 + (SW ? 1024 : 0);   // + room to align to 1024
+  // byte offset of 16-byte chunk kc of row r inside one operand
+  __device__ static __forceinline__ int unit_offset(int r, int kc) {
+    return SW ? (r >> 3) * 1024 + (r & 7) * 128 + ((kc ^ (r & 7)) << 4) : kc * LBO_BYTES + r * 16;
+  }
+  static constexpr int UNITS = 2 * TBM * CHUNKS_K;        // 16-byte units per tile (A and B)
+};
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, int src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+
+// K-major, 128-byte swizzle: LBO unused (1), SBO = 1024 bytes between 8-row groups, layout type 2 at [61,64)
+__device__ __forceinline__ uint64_t make_desc_sw128(uint32_t saddr) {
+  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+
+template <int EPI, int BK, bool SW>
+__global__ void __launch_bounds__(THREADS, BK == 16 ? 2 : 1)
+tc_gemm_kk_kernel(const float *__restrict__ A, const float *__restrict__ B, const float *__restrict__ bias, int M, int N,
+                  int K, int k_per_split, float *__restrict__ C, float *__restrict__ Ct, int32_t *status) {
+  using G = KK<BK, SW>;
+  extern __shared__ __align__(128) char smem_base[];
+  // the swizzle pattern is a function of the address: tiles start on 1024-byte boundaries
+  char *smem = SW ? smem_base + ((1024u - (smem_u32(smem_base) & 1023u)) & 1023u) : smem_base;
+  char *raw = smem, *lob = smem + G::RAW * G::RAW_STAGE;
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + (G::RAW + 2) * G::RAW_STAGE);  // RAW mbarriers
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + (G::RAW + 2) * G::RAW_STAGE + 64);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int m0 = blockIdx.y * TBM, n0 = blockIdx.x * TBN;
+  const int k_begin = blockIdx.z * k_per_split, k_end = min(K, k_begin + k_per_split);
+  C += (size_t)blockIdx.z * M * N;
+  const int KT = (k_end - k_begin + BK - 1) / BK;
+
+  if (tid == 0) {
+#pragma unroll
+    for (int i = 0; i < G::RAW; ++i) mbar_init(smem_u32(&bars[i]), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"((uint32_t)TBN)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_d = *tmem_slot;
+  bool ok = true;
+
+  // this thread's share of a tile: units u = tid + 256 * i; unit -> (operand, row, k-chunk), chunk fastest
+  auto issue_tile = [&](int kt) {
+    if (kt < KT) {
+      const int k0 = k_begin + kt * BK;
+      char *st = raw + (kt % G::RAW) * G::RAW_STAGE;
+#pragma unroll
+      for (int i = 0; i < G::UNITS / THREADS; ++i) {
+        const int u = tid + THREADS * i;
+        const int op = u / (TBM * G::CHUNKS_K), rem = u % (TBM * G::CHUNKS_K);
+        const int r = rem / G::CHUNKS_K, kc = rem % G::CHUNKS_K;
+        const int gk = k0 + 4 * kc;
+        const int rows = op ? N : M, gr = (op ? n0 : m0) + r;
+        const float *base = op ? B : A;
+        int bytes = (k_end - gk) * 4;
+        bytes = gr < rows ? (bytes > 16 ? 16 : (bytes < 0 ? 0 : bytes)) : 0;
+        const float *src = bytes > 0 ? base + (size_t)gr * K + gk : base;   // zero-fill: any valid address
+        cp_async16(smem_u32(st + op * G::OPER + G::unit_offset(r, kc)), src, bytes);
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");   // one group per call keeps the counting uniform
+  };
+
+#pragma unroll
+  for (int p = 0; p < G::PF; ++p) issue_tile(p);
+  for (int kt = 0; kt < KT; ++kt) {
+    if (kt >= 2) {  // tile kt-2 done: frees raw stage (kt + PF) % RAW and lo buffer kt % 2
+      ok = mbar_wait(smem_u32(&bars[(kt - 2) % G::RAW]), (uint32_t)(((kt - 2) / G::RAW) & 1));
+      ok = __syncthreads_and(ok);
+      if (!ok) break;
+    }
+    issue_tile(kt + G::PF);
+    asm volatile("cp.async.wait_group %0;" ::"n"(G::PF) : "memory");   // this thread's chunks of tile kt landed
+    __syncthreads();                                                    // ... and everybody else's
+    char *st = raw + (kt % G::RAW) * G::RAW_STAGE, *lo = lob + (kt & 1) * G::RAW_STAGE;
+#pragma unroll
+    for (int i = 0; i < G::UNITS / THREADS; ++i) {
+      const int u = tid + THREADS * i;
+      const int op = u / (TBM * G::CHUNKS_K), rem = u % (TBM * G::CHUNKS_K);
+      // the split is elementwise: walk the operand in address order (no-swizzle: skip the pad after each chunk)
+      const int off = op * G::OPER + (SW ? rem * 16 : (rem / TBM) * LBO_BYTES + (rem % TBM) * 16);
+      const float4 v = *reinterpret_cast<const float4 *>(st + off);
+      float4 h, l;
+      split_tf32(v.x, h.x, l.x); split_tf32(v.y, h.y, l.y); split_tf32(v.z, h.z, l.z); split_tf32(v.w, h.w, l.w);
+      *reinterpret_cast<float4 *>(lo + off) = l;
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (tid == 0) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t a_hi = smem_u32(st), b_hi = a_hi + G::OPER, a_lo = smem_u32(lo), b_lo = a_lo + G::OPER;
+      constexpr uint32_t ID = IDesc<true, true>::value;
+#pragma unroll
+      for (int ks = 0; ks < BK / 8; ++ks) {
+        // 8 tf32 along k: two 16-byte chunks (no swizzle), or 32 bytes further inside the swizzled row
+        const uint32_t adv = SW ? ks * 32 : ks * 2 * LBO_BYTES;
+        const uint64_t dah = SW ? make_desc_sw128(a_hi + adv) : make_desc<true>(a_hi + adv);
+        const uint64_t dal = SW ? make_desc_sw128(a_lo + adv) : make_desc<true>(a_lo + adv);
+        const uint64_t dbh = SW ? make_desc_sw128(b_hi + adv) : make_desc<true>(b_hi + adv);
+        const uint64_t dbl = SW ? make_desc_sw128(b_lo + adv) : make_desc<true>(b_lo + adv);
+        mma_tf32(tmem_d, dal, dbh, ID, (kt | ks) ? 1u : 0u);
+        mma_tf32(tmem_d, dah, dbl, ID, 1u);
+        mma_tf32(tmem_d, dah, dbh, ID, 1u);
+      }
+      commit_to(smem_u32(&bars[kt % G::RAW]));
+    }
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  if (KT > 0 && ok) ok = mbar_wait(smem_u32(&bars[(KT - 1) % G::RAW]), (uint32_t)(((KT - 1) / G::RAW) & 1));
+  ok = __syncthreads_and(ok);
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+
+  if (ok && KT > 0) {
+    epilogue<EPI>(tmem_d, bias, M, N, m0, n0, C, warp, lane, Ct);
+  } else if (KT == 0) {
+    const int gm = m0 + (warp & 3) * 32 + lane;
+    if (gm < M && warp < 4)
+      for (int c = 0; c < TBN; ++c)
+        if (n0 + c < N) C[(size_t)gm * N + n0 + c] = 0.0f;
+  }
+  if (!ok && tid == 0) atomicExch(status, 201);
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (warp == 0) {

@@ -90,8 +90,8 @@ SIGNATURES = {
     "dgc_hn_heads_bwd": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _vp]),
     "dgc_partconv_bwd_scratch_floats": (_u64, [_i32, _i32, _i32, _i32, _i32]),
     "dgc_partconv_bwd": (_i32, [_vp, _vp, _i32, _i32, _vp, _i32, _i32, _i32, _f, _vp, _vp, _i32, _vp, _vp]),
-    "dgc_linear_fwd": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp]),
-    "dgc_linear_bwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp]),
+    "dgc_linear_fwd": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp]),
+    "dgc_linear_bwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp]),
     "dgc_adam_step": (_i32, [_vp, _vp, _vp, _vp, _vp, _u64, _i32, _f, _f, _f, _f]),
     "dgc_sanitize": (_i32, [_vp, _vp, _u64, _vp]),
     "dgc_module_load": (_i32, [_vp, _vp, _u64, C.POINTER(_vp)]),
@@ -393,21 +393,22 @@ class Context:
         return gx, gir
 
     # ---- controller ---------------------------------------------------------------------------
-    def linear_fwd(self, a, w, bias=None, act=0):
+    def linear_fwd(self, a, w, bias=None, act=0, want_transposed=False):
         M, K = a.shape
         N = w.shape[1]
         c = self._empty(M, N)
-        self.check(self.lib.dgc_linear_fwd(self.h, _ptr(a), _ptr(w), _ptr(bias), M, K, N, act, _ptr(c)))
-        return c
+        ct = self._empty(N, M) if want_transposed else None
+        self.check(self.lib.dgc_linear_fwd(self.h, _ptr(a), _ptr(w), _ptr(bias), M, K, N, act, _ptr(c), _ptr(ct)))
+        return (c, ct) if want_transposed else c
 
-    def linear_bwd(self, a, w, c, dc, act=0, need_da=True, need_db=True):
+    def linear_bwd(self, a, w, c, dc, act=0, need_da=True, need_db=True, a_t=None):
         M, K = a.shape
         N = w.shape[1]
         dz, dw = self._empty(M, N), self._empty(K, N)
         da = self._empty(M, K) if need_da else None
         db = self._empty(N) if need_db else None
         self.check(self.lib.dgc_linear_bwd(self.h, _ptr(a), _ptr(w), _ptr(c), _ptr(dc), M, K, N, act, _ptr(dz),
-                                           _ptr(da), _ptr(dw), _ptr(db)))
+                                           _ptr(da), _ptr(dw), _ptr(db), _ptr(a_t)))
         return da, dw, db
 
     def adam_step(self, theta, grad, m, v, t, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8):

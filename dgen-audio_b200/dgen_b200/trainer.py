@@ -59,6 +59,7 @@ class HarmonicModel:
         f = lambda *s: torch.empty(*s, dtype=torch.float32, device=dev)
         M, H = self.M, hidden
         self.act = [f(M, H), f(M, H), f(M, H), f(M, K + nbands)]
+        self.act_t = [f(H, M), f(H, M), f(H, M)]         # transposed copies of the trunk activations
         self.dact = [f(M, H), f(M, H), f(M, H)]          # gradient w.r.t. a layer's input
         self.dz = [f(M, H), f(M, H), f(M, H), f(M, K + nbands)]
         self.head_dz = f(M, K + nbands)
@@ -83,8 +84,10 @@ class HarmonicModel:
         a = X
         for i in range(4):
             W, b = self.view("W%d" % i), self.view("b%d" % i)
+            # trunk activations are also kept transposed: the next layer's weight gradient reads them along m
             c.check(lib.dgc_linear_fwd(h, a.data_ptr(), W.data_ptr(), b.data_ptr(), self.M, W.shape[0], W.shape[1],
-                                       1 if i < 3 else 0, self.act[i].data_ptr()))
+                                       1 if i < 3 else 0, self.act[i].data_ptr(),
+                                       self.act_t[i].data_ptr() if i < 3 else None))
             a = self.act[i]
         c.check(lib.dgc_hn_heads_fwd(h, self.act[3].data_ptr(), self.M, self.K, self.nbands, self.amps.data_ptr(),
                                      self.bands.data_ptr()))
@@ -123,7 +126,7 @@ class HarmonicModel:
                                       self.g_taps.data_ptr()))
         # g_bands = g_taps Wfs   ([M, taps] x [taps, nbands])
         c.check(lib.dgc_linear_fwd(h, self.g_taps.data_ptr(), w_fs.data_ptr(), None, self.M, self.taps, self.nbands, 0,
-                                   self.g_bands.data_ptr()))
+                                   self.g_bands.data_ptr(), None))
         c.check(lib.dgc_hn_heads_bwd(h, self.act[3].data_ptr(), self.g_amps.data_ptr(), self.g_bands.data_ptr(),
                                      self.M, self.K, self.nbands, self.dz[3].data_ptr()))
         # head layer: dz[3] is the gradient w.r.t. z (no activation); trunk layers: dact[i] is the gradient
@@ -137,7 +140,7 @@ class HarmonicModel:
             da = self.dact[i - 1].data_ptr() if i > 0 else None
             c.check(lib.dgc_linear_bwd(h, inp.data_ptr(), W.data_ptr(), self.act[i].data_ptr(), dc.data_ptr(), self.M,
                                        W.shape[0], W.shape[1], 1 if i < 3 else 0, dz_out.data_ptr(), da,
-                                       gW.data_ptr(), gb.data_ptr()))
+                                       gW.data_ptr(), gb.data_ptr(), self.act_t[i - 1].data_ptr() if i > 0 else None))
         return self.grads
 
     def step(self, X, f0, uv, gain, noise_gain, noise, w_fs, target, lr=1e-3):

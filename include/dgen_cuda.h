@@ -272,16 +272,20 @@ int32_t dgc_mss_loss_bwd(dgc_ctx *ctx, const dgc_mss_params *p, const float *pre
 
 /* ---- controller -------------------------------------------------------------------------------
  * C[M][N] = act(A[M][K] * W[K][N] + bias[N]); act: 0 none, 1 tanh; bias may be NULL when act == 0.
- * Row-major, full fp32.  replaces: matmul -> mul + sumAxis / gemm
+ * Row-major, full fp32.  ct_dev (optional, may be NULL) receives a second, transposed copy C^T [N][M] of the
+ * output: handing it to dgc_linear_bwd of the NEXT layer as at_dev lets that layer's weight gradient run on
+ * the faster both-operands-contiguous matmul path.  replaces: matmul -> mul + sumAxis / gemm
  * (Sources/DGen/Tensor.swift:1195-1230, Sources/DGen/Emit+GEMM.swift). */
 int32_t dgc_linear_fwd(dgc_ctx *ctx, const float *a_dev, const float *w_dev, const float *bias_dev, int32_t M,
-                       int32_t K, int32_t N, int32_t act, float *c_dev);
+                       int32_t K, int32_t N, int32_t act, float *c_dev, float *ct_dev);
 /* Backward of the layer above: dZ = dC * act'(C) (written to dz_dev [M][N]), dW[K][N] = A^T dZ,
- * dbias[N] = column sums of dZ (optional), dA[M][K] = dZ W^T (optional).  Sums run in a fixed order
+ * dbias[N] = column sums of dZ (optional), dA[M][K] = dZ W^T (optional).  at_dev (optional, may be NULL) is
+ * A^T [K][M], see dgc_linear_fwd; the result does not depend on whether it is given beyond the rounding of a
+ * different summation order.  Sums run in a fixed order
  * (replaces tensorAccumulate, Sources/DGen/Emit+State.swift:50-115). */
 int32_t dgc_linear_bwd(dgc_ctx *ctx, const float *a_dev, const float *w_dev, const float *c_dev, const float *dc_dev,
                        int32_t M, int32_t K, int32_t N, int32_t act, float *dz_dev, float *da_dev, float *dw_dev,
-                       float *dbias_dev);
+                       float *dbias_dev, const float *at_dev);
 
 /* Adam step on device (Sources/DGenLazy/Optimizers.swift:164-243: bias-corrected, eps outside the
  * square root, the reference's operation order); t is the 1-based step index. */

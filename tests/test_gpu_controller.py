@@ -22,7 +22,7 @@ def dev(a):
 
 
 @pytest.mark.parametrize("M,K,N,act", [(1000, 2, 512, 1), (777, 512, 512, 1), (300, 512, 165, 0), (1, 1, 1, 0),
-                                       (129, 130, 131, 1)])
+                                       (129, 130, 131, 1), (4096, 512, 512, 1), (2052, 256, 165, 0)])
 def test_linear_forward_and_backward_match_fp64(ctx, M, K, N, act):
     rng = np.random.default_rng(M + K + N)
     a = rng.standard_normal((M, K)).astype(f32)
@@ -40,6 +40,17 @@ def test_linear_forward_and_backward_match_fp64(ctx, M, K, N, act):
     for got, want in ((da, dz @ w.astype(np.float64).T), (dw, a.astype(np.float64).T @ dz), (db, dz.sum(0))):
         want = np.asarray(want)
         assert np.abs(got.cpu().numpy() - want).max() < 1e-3 * max(1e-6, np.abs(want).max())  # gradient tolerance
+    # the transposed copy of the output, and the weight gradient computed from a transposed input
+    c2, ct = ctx.linear_fwd(dev(a), dev(w), dev(b), act, want_transposed=True)
+    assert torch_equal(c2, c) and torch_equal(ct, c2.t().contiguous())
+    _, dw2, _ = ctx.linear_bwd(dev(a), dev(w), c, dev(dc), act, a_t=dev(np.ascontiguousarray(a.T)))
+    want = a.astype(np.float64).T @ dz
+    assert np.abs(dw2.cpu().numpy() - want).max() < 1e-3 * max(1e-6, np.abs(want).max())
+
+
+def torch_equal(x, y):
+    import torch
+    return torch.equal(x, y)
 
 
 def test_linear_without_bias(ctx):
