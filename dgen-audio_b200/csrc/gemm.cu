@@ -142,7 +142,7 @@ int32_t launch_sgemm(dgc_ctx *ctx, const float *A, const float *B, const float *
     if (!dst) return DGC_ERR_OOM;
   }
   dim3 grid(dgc_div_up(N, bn), dgc_div_up(M, bm), splits);
-  static const int kk_bk = [] {   // DGC_GEMM_KK: 0 off; 32 (default) swizzled 32-wide k tiles; 33 / 16 no swizzle, 32 / 16 wide
+  static const int kk_bk = [] {   // DGC_GEMM_KK: 0 off; 32 (default) / 16: swizzled 32- / 16-wide k tiles; 33 / 17: the same without swizzle
     const char *e = getenv("DGC_GEMM_KK");
     return e ? atoi(e) : 32;
   }();
@@ -155,10 +155,11 @@ int32_t launch_sgemm(dgc_ctx *ctx, const float *A, const float *B, const float *
     constexpr int SM = dgtc::KK<BKV, SWV>::SMEM;                                                                    \
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM);                    \
     if (e != cudaSuccess) return dgc_fail(ctx, DGC_ERR_CUDA, "tc_gemm smem opt-in: %s", cudaGetErrorString(e));     \
-    kern<<<grid, dgtc::THREADS, SM, ctx->stream>>>(A, B, bias, M, N, K, kps, dst, splits == 1 ? Ct : nullptr,       \
+    kern<<<grid, dgtc::KK_THREADS, SM, ctx->stream>>>(A, B, bias, M, N, K, kps, dst, splits == 1 ? Ct : nullptr,    \
                                                    ctx->status_dev);                                                \
   } while (0)
-    if (kk_bk == 16) DGC_KK_LAUNCH(16, false);
+    if (kk_bk == 16) DGC_KK_LAUNCH(16, true);
+    else if (kk_bk == 17) DGC_KK_LAUNCH(16, false);
     else if (kk_bk == 33) DGC_KK_LAUNCH(32, false);
     else DGC_KK_LAUNCH(32, true);
 #undef DGC_KK_LAUNCH

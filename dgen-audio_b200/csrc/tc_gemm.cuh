@@ -332,17 +332,22 @@ tc_gemm_kernel(const float *__restrict__ A, const float *__restrict__ B, const f
 // SW: the 128-byte-swizzle K-major layout (BK = 32: one row of a tile is exactly one 128-byte swizzle row;
 // 8-row groups of 1024 bytes, 16-byte chunk c of row r stored at chunk c ^ (r % 8)) instead of the
 // no-swizzle layout of 8 x 16-byte core matrices.
+// With BK = 16 a row is 64 bytes and the 64-byte swizzle applies (8-row groups of 512 bytes, chunk c of row r at
+// c ^ ((r / 2) % 4)); that variant needs 97 KB per CTA, so two CTAs share an SM and one's epilogue runs under
+// the other's main loop.
 template <int BK, bool SW = false>
 struct KK {
-  static_assert(!SW || BK == 32, "the swizzled layout is built for 128-byte rows");
   static constexpr int CHUNKS_K = BK / 4;
-  static constexpr int OPER = SW ? TBM * 128 : CHUNKS_K * LBO_BYTES;       // one operand of one tile
+  static constexpr int ROW_BYTES = BK * 4;                                  // 128 or 64
+  static constexpr int OPER = SW ? TBM * ROW_BYTES : CHUNKS_K * LBO_BYTES;  // one operand of one tile
   static constexpr int RAW = 4, PF = 2;
   static constexpr int RAW_STAGE = 2 * OPER;              // A, B
   static constexpr int SMEM = (RAW + 2) * RAW_STAGE + 128 + (SW ? 1024 : 0);   // + room to align to 1024
   // byte offset of 16-byte chunk kc of row r inside one operand
   __device__ static __forceinline__ int unit_offset(int r, int kc) {
-    return SW ? (r >> 3) * 1024 + (r & 7) * 128 + ((kc ^ (r & 7)) << 4) : kc * LBO_BYTES + r * 16;
+    if (!SW) return kc * LBO_BYTES + r * 16;
+    return BK == 32 ? (r >> 3) * 1024 + (r & 7) * 128 + ((kc ^ (r & 7)) << 4)
+                    : (r >> 3) * 512 + (r & 7) * 64 + ((kc ^ ((r >> 1) & 3)) << 4);
   }
   static constexpr int UNITS = 2 * TBM * CHUNKS_K;        // 16-byte units per tile (A and B)
 };
@@ -352,12 +357,21 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, int sr
 }
 
 // K-major, 128-byte swizzle: LBO unused (1), SBO = 1024 bytes between 8-row groups, layout type 2 at [61,64)
+// (64-byte swizzle: SBO = 512 bytes, layout type 4)
+template <int ROW_BYTES = 128>
 __device__ __forceinline__ uint64_t make_desc_sw128(uint32_t saddr) {
-  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+  constexpr uint64_t sbo = ROW_BYTES * 8, type = ROW_BYTES == 128 ? 2 : 4;
+  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | (1ull << 16) | ((sbo >> 4) << 32) | (1ull << 46) | (type << 61);
+}
+
+constexpr int KK_THREADS = THREADS + 32;   // 8 worker warps + 1 warp whose lane 0 issues the MMAs
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
 template <int EPI, int BK, bool SW>
-__global__ void __launch_bounds__(THREADS, BK == 16 ? 2 : 1)
+__global__ void __launch_bounds__(KK_THREADS, BK == 16 ? 2 : 1)
 tc_gemm_kk_kernel(const float *__restrict__ A, const float *__restrict__ B, const float *__restrict__ bias, int M, int N,
                   int K, int k_per_split, float *__restrict__ C, float *__restrict__ Ct, int32_t *status) {
   using G = KK<BK, SW>;
@@ -365,7 +379,8 @@ tc_gemm_kk_kernel(const float *__restrict__ A, const float *__restrict__ B, cons
   // the swizzle pattern is a function of the address: tiles start on 1024-byte boundaries
   char *smem = SW ? smem_base + ((1024u - (smem_u32(smem_base) & 1023u)) & 1023u) : smem_base;
   char *raw = smem, *lob = smem + G::RAW * G::RAW_STAGE;
-  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + (G::RAW + 2) * G::RAW_STAGE);  // RAW mbarriers
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + (G::RAW + 2) * G::RAW_STAGE);  // RAW "tile consumed" mbarriers
+  uint64_t *ready = bars + G::RAW;                                                    // 2 "lo buffer written" mbarriers
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + (G::RAW + 2) * G::RAW_STAGE + 64);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int m0 = blockIdx.y * TBM, n0 = blockIdx.x * TBN;
@@ -376,6 +391,8 @@ tc_gemm_kk_kernel(const float *__restrict__ A, const float *__restrict__ B, cons
   if (tid == 0) {
 #pragma unroll
     for (int i = 0; i < G::RAW; ++i) mbar_init(smem_u32(&bars[i]), 1);
+    mbar_init(smem_u32(&ready[0]), THREADS / 32);   // one arrival per worker warp
+    mbar_init(smem_u32(&ready[1]), THREADS / 32);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 0) {
@@ -390,80 +407,101 @@ tc_gemm_kk_kernel(const float *__restrict__ A, const float *__restrict__ B, cons
   const uint32_t tmem_d = *tmem_slot;
   bool ok = true;
 
-  // this thread's share of a tile: units u = tid + 256 * i; unit -> (operand, row, k-chunk), chunk fastest
-  auto issue_tile = [&](int kt) {
-    if (kt < KT) {
-      const int k0 = k_begin + kt * BK;
-      char *st = raw + (kt % G::RAW) * G::RAW_STAGE;
-#pragma unroll
-      for (int i = 0; i < G::UNITS / THREADS; ++i) {
-        const int u = tid + THREADS * i;
-        const int op = u / (TBM * G::CHUNKS_K), rem = u % (TBM * G::CHUNKS_K);
-        const int r = rem / G::CHUNKS_K, kc = rem % G::CHUNKS_K;
-        const int gk = k0 + 4 * kc;
-        const int rows = op ? N : M, gr = (op ? n0 : m0) + r;
-        const float *base = op ? B : A;
-        int bytes = (k_end - gk) * 4;
-        bytes = gr < rows ? (bytes > 16 ? 16 : (bytes < 0 ? 0 : bytes)) : 0;
-        const float *src = bytes > 0 ? base + (size_t)gr * K + gk : base;   // zero-fill: any valid address
-        cp_async16(smem_u32(st + op * G::OPER + G::unit_offset(r, kc)), src, bytes);
-      }
-    }
-    asm volatile("cp.async.commit_group;" ::: "memory");   // one group per call keeps the counting uniform
-  };
+  volatile int *failed = reinterpret_cast<volatile int *>(tmem_slot + 1);
+  if (tid == 0) *failed = 0;
+  __syncthreads();
 
+  if (warp < THREADS / 32) {
+    // ---- worker warps: copy, split, publish -----------------------------------------------------------------
+    // This thread's share of every tile: units u = tid + 256 * i -> (operand, row, k-chunk), chunk fastest, so 8
+    // lanes fetch one 128-byte row.  Global pointers and shared offsets are fixed per thread, and the thread
+    // splits exactly the units it copied itself, so the only synchronisation of the loop is through mbarriers:
+    // "tile kt-2 consumed" before its raw stage and lo buffer are reused, "lo buffer written" towards the MMA warp.
+    constexpr int UPT = G::UNITS / THREADS;
+    const float *src0[UPT];
+    int soff[UPT], kc4[UPT];
+    bool rowok[UPT];
 #pragma unroll
-  for (int p = 0; p < G::PF; ++p) issue_tile(p);
-  for (int kt = 0; kt < KT; ++kt) {
-    if (kt >= 2) {  // tile kt-2 done: frees raw stage (kt + PF) % RAW and lo buffer kt % 2
-      ok = mbar_wait(smem_u32(&bars[(kt - 2) % G::RAW]), (uint32_t)(((kt - 2) / G::RAW) & 1));
-      ok = __syncthreads_and(ok);
-      if (!ok) break;
-    }
-    issue_tile(kt + G::PF);
-    asm volatile("cp.async.wait_group %0;" ::"n"(G::PF) : "memory");   // this thread's chunks of tile kt landed
-    __syncthreads();                                                    // ... and everybody else's
-    char *st = raw + (kt % G::RAW) * G::RAW_STAGE, *lo = lob + (kt & 1) * G::RAW_STAGE;
-#pragma unroll
-    for (int i = 0; i < G::UNITS / THREADS; ++i) {
+    for (int i = 0; i < UPT; ++i) {
       const int u = tid + THREADS * i;
       const int op = u / (TBM * G::CHUNKS_K), rem = u % (TBM * G::CHUNKS_K);
-      // the split is elementwise: walk the operand in address order (no-swizzle: skip the pad after each chunk)
-      const int off = op * G::OPER + (SW ? rem * 16 : (rem / TBM) * LBO_BYTES + (rem % TBM) * 16);
-      const float4 v = *reinterpret_cast<const float4 *>(st + off);
-      float4 h, l;
-      split_tf32(v.x, h.x, l.x); split_tf32(v.y, h.y, l.y); split_tf32(v.z, h.z, l.z); split_tf32(v.w, h.w, l.w);
-      *reinterpret_cast<float4 *>(lo + off) = l;
+      const int r = rem / G::CHUNKS_K, kc = rem % G::CHUNKS_K;
+      const int rows = op ? N : M, gr = (op ? n0 : m0) + r;
+      rowok[i] = gr < rows;
+      kc4[i] = 4 * kc;
+      src0[i] = (op ? B : A) + (rowok[i] ? (size_t)gr * K : 0) + k_begin + 4 * kc;
+      soff[i] = op * G::OPER + G::unit_offset(r, kc);
     }
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    if (tid == 0) {
+    auto issue_tile = [&](int kt) {
+      if (kt < KT) {
+        const int k0 = kt * BK;   // relative to k_begin
+        const uint32_t st = smem_u32(raw + (kt % G::RAW) * G::RAW_STAGE);
+#pragma unroll
+        for (int i = 0; i < UPT; ++i) {
+          int bytes = (k_end - k_begin - k0 - kc4[i]) * 4;
+          bytes = rowok[i] ? (bytes > 16 ? 16 : (bytes < 0 ? 0 : bytes)) : 0;
+          cp_async16(st + soff[i], bytes > 0 ? src0[i] + k0 : A, bytes);   // 0 bytes: zero fill, any valid address
+        }
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");   // one group per call keeps the counting uniform
+    };
+#pragma unroll
+    for (int p = 0; p < G::PF; ++p) issue_tile(p);
+    for (int kt = 0; kt < KT; ++kt) {
+      if (kt >= 2 && !*failed) {   // bounded; a thread that gives up raises the shared flag and everybody stops waiting
+        if (!mbar_wait(smem_u32(&bars[(kt - 2) % G::RAW]), (uint32_t)(((kt - 2) / G::RAW) & 1))) *failed = 1;
+      }
+      issue_tile(kt + G::PF);
+      asm volatile("cp.async.wait_group %0;" ::"n"(G::PF) : "memory");   // this thread's chunks of tile kt landed
+      char *st = raw + (kt % G::RAW) * G::RAW_STAGE, *lo = lob + (kt & 1) * G::RAW_STAGE;
+#pragma unroll
+      for (int i = 0; i < UPT; ++i) {
+        const float4 v = *reinterpret_cast<const float4 *>(st + soff[i]);
+        float4 h, l;
+        split_tf32(v.x, h.x, l.x); split_tf32(v.y, h.y, l.y); split_tf32(v.z, h.z, l.z); split_tf32(v.w, h.w, l.w);
+        *reinterpret_cast<float4 *>(lo + soff[i]) = l;
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // this thread's writes -> tensor-core proxy
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&ready[kt & 1]));
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+  } else if (lane == 0) {
+    // ---- MMA issue: one thread, nothing else to do ----------------------------------------------------------
+    constexpr uint32_t ID = IDesc<true, true>::value;
+    for (int kt = 0; kt < KT; ++kt) {
+      if (*failed || !mbar_wait(smem_u32(&ready[kt & 1]), (uint32_t)((kt >> 1) & 1))) {
+        *failed = 1;
+        break;
+      }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const uint32_t a_hi = smem_u32(st), b_hi = a_hi + G::OPER, a_lo = smem_u32(lo), b_lo = a_lo + G::OPER;
-      constexpr uint32_t ID = IDesc<true, true>::value;
+      const uint32_t a_hi = smem_u32(raw + (kt % G::RAW) * G::RAW_STAGE), b_hi = a_hi + G::OPER;
+      const uint32_t a_lo = smem_u32(lob + (kt & 1) * G::RAW_STAGE), b_lo = a_lo + G::OPER;
 #pragma unroll
       for (int ks = 0; ks < BK / 8; ++ks) {
         // 8 tf32 along k: two 16-byte chunks (no swizzle), or 32 bytes further inside the swizzled row
         const uint32_t adv = SW ? ks * 32 : ks * 2 * LBO_BYTES;
-        const uint64_t dah = SW ? make_desc_sw128(a_hi + adv) : make_desc<true>(a_hi + adv);
-        const uint64_t dal = SW ? make_desc_sw128(a_lo + adv) : make_desc<true>(a_lo + adv);
-        const uint64_t dbh = SW ? make_desc_sw128(b_hi + adv) : make_desc<true>(b_hi + adv);
-        const uint64_t dbl = SW ? make_desc_sw128(b_lo + adv) : make_desc<true>(b_lo + adv);
+        const uint64_t dah = SW ? make_desc_sw128<G::ROW_BYTES>(a_hi + adv) : make_desc<true>(a_hi + adv);
+        const uint64_t dal = SW ? make_desc_sw128<G::ROW_BYTES>(a_lo + adv) : make_desc<true>(a_lo + adv);
+        const uint64_t dbh = SW ? make_desc_sw128<G::ROW_BYTES>(b_hi + adv) : make_desc<true>(b_hi + adv);
+        const uint64_t dbl = SW ? make_desc_sw128<G::ROW_BYTES>(b_lo + adv) : make_desc<true>(b_lo + adv);
         mma_tf32(tmem_d, dal, dbh, ID, (kt | ks) ? 1u : 0u);
         mma_tf32(tmem_d, dah, dbl, ID, 1u);
         mma_tf32(tmem_d, dah, dbh, ID, 1u);
       }
       commit_to(smem_u32(&bars[kt % G::RAW]));
     }
+    // the last commit covers every MMA issued before it
+    if (KT > 0 && !*failed && !mbar_wait(smem_u32(&bars[(KT - 1) % G::RAW]), (uint32_t)(((KT - 1) / G::RAW) & 1)))
+      *failed = 1;
   }
-  asm volatile("cp.async.wait_group 0;" ::: "memory");
-  if (KT > 0 && ok) ok = mbar_wait(smem_u32(&bars[(KT - 1) % G::RAW]), (uint32_t)(((KT - 1) / G::RAW) & 1));
-  ok = __syncthreads_and(ok);
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  ok = !*failed;
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 
   if (ok && KT > 0) {
-    epilogue<EPI>(tmem_d, bias, M, N, m0, n0, C, warp, lane, Ct);
+    if (warp < THREADS / 32) epilogue<EPI>(tmem_d, bias, M, N, m0, n0, C, warp, lane, Ct);
   } else if (KT == 0) {
     const int gm = m0 + (warp & 3) * 32 + lane;
     if (gm < M && warp < 4)
