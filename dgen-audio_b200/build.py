@@ -11,7 +11,7 @@ SOURCES = ["ctx.cu", "osc_bank.cu", "fir_noise.cu", "mss_loss.cu", "linrec.cu", 
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--use_fast_math=false",
          "-Xcompiler", "-fPIC,-fvisibility=hidden,-O2", "-cudart", "static", "-Xptxas", "-v"]
-FLAGS = [f for f in FLAGS if f != "--use_fast_math=false"]
+FLAGS = [f for f in FLAGS if f != "--use_fast_math=false"] + os.environ.get("DGC_EXTRA_NVCC_FLAGS", "").split()
 
 
 def needs_build():

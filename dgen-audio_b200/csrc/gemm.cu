@@ -142,9 +142,9 @@ int32_t launch_sgemm(dgc_ctx *ctx, const float *A, const float *B, const float *
     if (!dst) return DGC_ERR_OOM;
   }
   dim3 grid(dgc_div_up(N, bn), dgc_div_up(M, bm), splits);
-  static const int kk_bk = [] {   // DGC_GEMM_KK: 0 off; 32 (default) / 16: swizzled 32- / 16-wide k tiles; 33 / 17: the same without swizzle
+  static const int kk_bk = [] {   // DGC_GEMM_KK: 0 off; 16 (default) / 32: swizzled 16- / 32-wide k tiles; 17 / 33: the same without swizzle
     const char *e = getenv("DGC_GEMM_KK");
-    return e ? atoi(e) : 32;
+    return e ? atoi(e) : 16;
   }();
   if (tc && !TA && TB && kk_bk && (K & 3) == 0 && ((((uintptr_t)A) | ((uintptr_t)B)) & 15) == 0 &&
       (splits == 1 || kps % 32 == 0)) {
@@ -389,3 +389,10 @@ DGC_EXPORT int32_t dgc_adam_step(dgc_ctx *ctx, float *theta_dev, const float *gr
   DGC_LAUNCHED(ctx, "adam");
   return DGC_OK;
 }
+
+#ifdef DGC_KK_TIMING
+DGC_EXPORT int32_t dgc_debug_kk_times(unsigned long long *out8) {
+  cudaDeviceSynchronize();
+  return cudaMemcpyFromSymbol(out8, dgtc::dgc_kk_times, 8 * sizeof(unsigned long long)) == cudaSuccess ? 0 : -1;
+}
+#endif

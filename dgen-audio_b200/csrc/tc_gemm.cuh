@@ -169,55 +169,78 @@ __device__ __forceinline__ void stash(const float4 (&v)[4], char *hi_part, char 
   }
 }
 
+// tanh to ~1e-7 absolute in ~15 instructions (the library routine costs ~50 and dominated the epilogue):
+// odd polynomial below 1/4 (next term 62/2835 x^9 < 1e-7 relative there), 1 - 2 / (e^{2|x|} + 1) above.
+__device__ __forceinline__ float tanh_fast(float x) {
+  const float ax = fabsf(x), x2 = x * x;
+  const float p = x * fmaf(x2, fmaf(x2, fmaf(x2, -17.0f / 315.0f, 2.0f / 15.0f), -1.0f / 3.0f), 1.0f);
+  const float e = __expf(2.0f * fminf(ax, 15.0f));
+  const float t = copysignf(1.0f - __fdividef(2.0f, e + 1.0f), x);
+  return ax < 0.25f ? p : t;
+}
+
+constexpr int EPI_STAGE_FLOATS = 32 * 33;   // per warp: a 32 x 32 block, rows padded to 33 floats
+
 // Accumulators -> global memory.  Warp w may touch tensor-memory lanes 32 * (w % 4) ..; warps 0-3 take columns
-// 0..63, warps 4-7 the rest; lane = output row.  EPI 0: C = acc ; 1: + bias[n] ; 2: tanh(acc + bias[n]).
-// Ct (optional): a second, transposed copy Ct[n][m] of the result (lanes = consecutive m: 128-byte stores).
+// 0..63, warps 4-7 the rest; after tcgen05.ld a lane holds 32 columns of ONE output row.  Storing from there
+// would make every store instruction touch 32 different rows, so each warp turns its 32 x 32 block through a
+// private shared-memory tile (`stage`, EPI_STAGE_FLOATS floats per warp, the pipeline's buffers are idle by
+// now) and writes full 128-byte row segments.  EPI 0: C = acc ; 1: + bias[n] ; 2: tanh(acc + bias[n]).
+// Ct (optional): a second, transposed copy Ct[n][m] of the result, written straight from the registers
+// (lanes = consecutive m: already 128-byte stores).
 template <int EPI>
 __device__ __forceinline__ void epilogue(uint32_t tmem_d, const float *__restrict__ bias, int M, int N, int m0, int n0,
-                                         float *__restrict__ C, int warp, int lane, float *__restrict__ Ct = nullptr) {
-    const int lane_base = (warp & 3) * 32, col_base = (warp >> 2) * (TBN / 2);
-    const int gm = m0 + lane_base + lane;
+                                         float *__restrict__ C, int warp, int lane, float *__restrict__ Ct,
+                                         float *__restrict__ stage_all) {
+  const int lane_base = (warp & 3) * 32, col_base = (warp >> 2) * (TBN / 2);
+  const int gm = m0 + lane_base + lane;
+  float *stage = stage_all + warp * EPI_STAGE_FLOATS;
+  const bool aligned = ((N & 3) == 0) && ((((uintptr_t)C) & 15) == 0);
 #pragma unroll 1
-    for (int c0 = col_base; c0 < col_base + TBN / 2; c0 += 32) {
-      uint32_t r[32];
-      const uint32_t taddr = tmem_d + ((uint32_t)lane_base << 16) + (uint32_t)c0;
-      asm volatile(
-          "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-          "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-          "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
-          : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-            "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-            "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-            "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-          : "r"(taddr));
-      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-      if (gm < M) {
-        float *crow = C + (size_t)gm * N + n0 + c0;
-        const bool vec_ok = ((N & 3) == 0) && (n0 + c0 + 31 < N) && ((((uintptr_t)C) & 15) == 0);
+  for (int c0 = col_base; c0 < col_base + TBN / 2; c0 += 32) {
+    uint32_t r[32];
+    const uint32_t taddr = tmem_d + ((uint32_t)lane_base << 16) + (uint32_t)c0;
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    const int gn0 = n0 + c0;
 #pragma unroll
-        for (int j = 0; j < 32; j += 4) {
-          float v[4];
+    for (int j = 0; j < 32; ++j) {
+      float x = __uint_as_float(r[j]);
+      if (EPI >= 1 && gn0 + j < N) x += __ldg(&bias[gn0 + j]);
+      if (EPI == 2) x = tanh_fast(x);
+      if (Ct && gm < M && gn0 + j < N) Ct[(size_t)(gn0 + j) * M + gm] = x;
+      stage[lane * 33 + j] = x;   // bank (lane + j) % 32: conflict-free
+    }
+    __syncwarp();
+    // 4 rows per instruction: lane -> (row it * 4 + lane / 8, columns 4 * (lane % 8) ..)
+    const int rsub = lane >> 3, c4 = (lane & 7) * 4;
+    const bool vec_ok = aligned && gn0 + 31 < N;
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            float x = __uint_as_float(r[j + u]);
-            int gn = n0 + c0 + j + u;
-            if (EPI >= 1 && gn < N) x += bias[gn];
-            if (EPI == 2) x = tanhf(x);
-            v[u] = x;
-          }
-          if (Ct) {
-#pragma unroll
-            for (int u = 0; u < 4; ++u)
-              if (n0 + c0 + j + u < N) Ct[(size_t)(n0 + c0 + j + u) * M + gm] = v[u];
-          }
-          if (vec_ok) *reinterpret_cast<float4 *>(crow + j) = make_float4(v[0], v[1], v[2], v[3]);
-          else
-#pragma unroll
-            for (int u = 0; u < 4; ++u)
-              if (n0 + c0 + j + u < N) crow[j + u] = v[u];
+    for (int it = 0; it < 8; ++it) {
+      const int rr = it * 4 + rsub, grow = m0 + lane_base + rr;
+      const float *sp = stage + rr * 33 + c4;
+      const float v0 = sp[0], v1 = sp[1], v2 = sp[2], v3 = sp[3];
+      if (grow < M) {
+        float *crow = C + (size_t)grow * N + gn0 + c4;
+        if (vec_ok) *reinterpret_cast<float4 *>(crow) = make_float4(v0, v1, v2, v3);
+        else {
+          if (gn0 + c4 < N) crow[0] = v0;
+          if (gn0 + c4 + 1 < N) crow[1] = v1;
+          if (gn0 + c4 + 2 < N) crow[2] = v2;
+          if (gn0 + c4 + 3 < N) crow[3] = v3;
         }
       }
     }
+    __syncwarp();
+  }
 }
 
 // A_KMAJOR: A stored [M][K]; else stored [K][M].  B_KMAJOR: B stored [N][K]; else stored [K][N].
@@ -302,7 +325,7 @@ tc_gemm_kernel(const float *__restrict__ A, const float *__restrict__ B, const f
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 
   if (ok && KT > 0) {
-    epilogue<EPI>(tmem_d, bias, M, N, m0, n0, C, warp, lane);
+    epilogue<EPI>(tmem_d, bias, M, N, m0, n0, C, warp, lane, nullptr, reinterpret_cast<float *>(smem));
   } else if (KT == 0) {
     // empty reduction range: the slab is zero
     const int gm = m0 + (warp & 3) * 32 + lane;
@@ -364,6 +387,19 @@ __device__ __forceinline__ uint64_t make_desc_sw128(uint32_t saddr) {
   return (uint64_t)((saddr & 0x3FFFFu) >> 4) | (1ull << 16) | ((sbo >> 4) << 32) | (1ull << 46) | (type << 61);
 }
 
+#ifdef DGC_KK_TIMING
+// development aid: per-phase timestamps (ns) of CTA (0,0,0), read back with cudaMemcpyFromSymbol
+__device__ unsigned long long dgc_kk_times[8];
+__device__ __forceinline__ unsigned long long gtime() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define KK_STAMP(i) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (threadIdx.x & 31) == 0 && (threadIdx.x == 0 || (i) == 3 || (i) == 4)) dgc_kk_times[i] = gtime(); } while (0)
+#else
+#define KK_STAMP(i) do {} while (0)
+#endif
+
 constexpr int KK_THREADS = THREADS + 32;   // 8 worker warps + 1 warp whose lane 0 issues the MMAs
 
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
@@ -375,6 +411,7 @@ __global__ void __launch_bounds__(KK_THREADS, BK == 16 ? 2 : 1)
 tc_gemm_kk_kernel(const float *__restrict__ A, const float *__restrict__ B, const float *__restrict__ bias, int M, int N,
                   int K, int k_per_split, float *__restrict__ C, float *__restrict__ Ct, int32_t *status) {
   using G = KK<BK, SW>;
+  KK_STAMP(0);
   extern __shared__ __align__(128) char smem_base[];
   // the swizzle pattern is a function of the address: tiles start on 1024-byte boundaries
   char *smem = SW ? smem_base + ((1024u - (smem_u32(smem_base) & 1023u)) & 1023u) : smem_base;
@@ -410,6 +447,7 @@ tc_gemm_kk_kernel(const float *__restrict__ A, const float *__restrict__ B, cons
   volatile int *failed = reinterpret_cast<volatile int *>(tmem_slot + 1);
   if (tid == 0) *failed = 0;
   __syncthreads();
+  KK_STAMP(1);
 
   if (warp < THREADS / 32) {
     // ---- worker warps: copy, split, publish -----------------------------------------------------------------
@@ -453,6 +491,7 @@ tc_gemm_kk_kernel(const float *__restrict__ A, const float *__restrict__ B, cons
       }
       issue_tile(kt + G::PF);
       asm volatile("cp.async.wait_group %0;" ::"n"(G::PF) : "memory");   // this thread's chunks of tile kt landed
+      if (kt == 0) KK_STAMP(2);
       char *st = raw + (kt % G::RAW) * G::RAW_STAGE, *lo = lob + (kt & 1) * G::RAW_STAGE;
 #pragma unroll
       for (int i = 0; i < UPT; ++i) {
@@ -475,6 +514,7 @@ tc_gemm_kk_kernel(const float *__restrict__ A, const float *__restrict__ B, cons
         break;
       }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if (kt == 0) KK_STAMP(3);
       const uint32_t a_hi = smem_u32(raw + (kt % G::RAW) * G::RAW_STAGE), b_hi = a_hi + G::OPER;
       const uint32_t a_lo = smem_u32(lob + (kt & 1) * G::RAW_STAGE), b_lo = a_lo + G::OPER;
 #pragma unroll
@@ -494,14 +534,17 @@ tc_gemm_kk_kernel(const float *__restrict__ A, const float *__restrict__ B, cons
     // the last commit covers every MMA issued before it
     if (KT > 0 && !*failed && !mbar_wait(smem_u32(&bars[(KT - 1) % G::RAW]), (uint32_t)(((KT - 1) / G::RAW) & 1)))
       *failed = 1;
+    KK_STAMP(4);
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   ok = !*failed;
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  KK_STAMP(5);
 
   if (ok && KT > 0) {
-    if (warp < THREADS / 32) epilogue<EPI>(tmem_d, bias, M, N, m0, n0, C, warp, lane, Ct);
+    if (warp < THREADS / 32) epilogue<EPI>(tmem_d, bias, M, N, m0, n0, C, warp, lane, Ct, reinterpret_cast<float *>(smem));
+    KK_STAMP(6);
   } else if (KT == 0) {
     const int gm = m0 + (warp & 3) * 32 + lane;
     if (gm < M && warp < 4)
