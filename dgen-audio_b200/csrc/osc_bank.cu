@@ -182,19 +182,21 @@ anchor_sum_kernel(const float *__restrict__ f0t, int B, int T, int K, float sr, 
   const int n0 = c * CH, n1 = min(T, n0 + CH);
   // Double-float accumulation: the 64 increments of a chunk are summed to ~2^-36 absolute, far below the
   // 2^-25 spacing of the single-precision anchors, with plain FP32 adds; the chunk total is converted to
-  // Q0.64 once.  hi starts at 1.0 (an integer number of turns, invisible mod 1) so that |hi| >= |inc|
-  // holds for every add and the three-operation Fast2Sum is error-free.
+  // Q0.64 once.  hi starts at 8.0 (an integer number of turns, invisible mod 1) so that |hi| >= |inc|
+  // holds for every add of an increment below 8 turns and the three-operation Fast2Sum is error-free.
+  // Increments of 1 turn and more (partials above the sample rate, far above Nyquist and masked, but their
+  // phase must stay defined for when f0 comes down again) are summed unwrapped: only the sum mod 1 matters.
   float hi[P], lo[P];
 #pragma unroll
   for (int i = 0; i < P; ++i) {
-    hi[i] = 1.0f;
+    hi[i] = 8.0f;
     lo[i] = 0.0f;
   }
   const float kmax = (float)K, kf0 = (float)(j + 1);
   for (int n = n0; n < n1; ++n) {
     const float f0 = f[n];
-    // one decision per frame, taken as a branch: all increments of this frame already in [0,1)?
-    if (f0 >= 0.0f && __fmul_rn(kmax, f0) < sr) {
+    // one decision per frame, taken as a branch: all increments of this frame in [0, 8)?
+    if (f0 >= 0.0f && __fmul_rn(kmax, f0) < 8.0f * sr) {
 #pragma unroll
       for (int i = 0; i < P; ++i) {
         const float inc = div_by_const(__fmul_rn(partial_number(kf0, LPC * i), f0), sr, rsr);
@@ -217,7 +219,7 @@ anchor_sum_kernel(const float *__restrict__ f0t, int B, int T, int K, float sr, 
   unsigned long long acc[P];
 #pragma unroll
   for (int i = 0; i < P; ++i) {
-    // hi in [1, 65], |lo| tiny: total mod 1 in Q0.64 (two's-complement add handles a negative lo)
+    // hi in [8, 520], |lo| < 1e-2: total mod 1 in Q0.64 (two's-complement add handles a negative lo)
     float ip = floorf(hi[i]);
     unsigned long long q = turns_to_q64(__fsub_rn(hi[i], ip));
     float al = fabsf(lo[i]);
