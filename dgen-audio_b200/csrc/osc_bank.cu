@@ -714,7 +714,7 @@ DGC_EXPORT uint64_t dgc_harmonic_scratch_floats(const dgc_harmonic_params *p) {
 
 int32_t dgc_harmonic_prepare(dgc_ctx *ctx, const dgc_harmonic_params *p, const float *f0_dev, float *scratch,
                              const float **play_out, const float **anchors_out, const float *uv_dev,
-                             const float *gain_dev, dgc_harmonic_extra *extra) {
+                             const float *gain_dev, dgc_harmonic_extra *extra, bool already_prepared) {
   DGC_REQUIRE(ctx, p->B > 0 && p->T > 0 && p->F > 0 && p->K > 0 && p->K <= 512, "size out of range (K <= 512)");
   DGC_REQUIRE(ctx, p->B <= 65535, "B must be <= 65535");
   DGC_REQUIRE(ctx, p->sample_rate > 0, "sample rate must be positive");
@@ -735,6 +735,9 @@ int32_t dgc_harmonic_prepare(dgc_ctx *ctx, const dgc_harmonic_params *p, const f
   const float2 *rowtab = dgc_ctx_row_table(ctx, F, T);
   if (!rowtab) return DGC_ERR_CUDA;
   const float sr = p->sample_rate, rsr = 1.0f / sr;
+  if (already_prepared) {
+    // nothing to launch
+  } else {
   f0_track_kernel<<<dim3(dgc_div_up(T, 256), B), 256, 0, ctx->stream>>>(rowtab, f0_dev, B, T, F, f0t, uv_dev, gain_dev,
                                                                          p->harmonic_scale, want_env ? env : nullptr);
   DGC_LAUNCHED(ctx, "f0_track");
@@ -747,6 +750,7 @@ int32_t dgc_harmonic_prepare(dgc_ctx *ctx, const dgc_harmonic_params *p, const f
     anchor_scan_kernel<<<dim3(dgc_div_up(K, 32), B), 1024, 0, ctx->stream>>>(sums, B, C, K, anchors,
                                                                              extra ? anchors_q : nullptr);
     DGC_LAUNCHED(ctx, "anchor_scan");
+  }
   }
   if (extra) {
     extra->f0t = f0t;

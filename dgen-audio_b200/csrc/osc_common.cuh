@@ -63,6 +63,8 @@ __device__ __forceinline__ float partial_number(float kf0, int step_times_i) { r
 
 // Runs the per-sample fundamental track and the phase-anchor kernels for `p` into `scratch`
 // (dgc_harmonic_scratch_floats(p) floats); returns the control clock and the anchors [B][C][K].
+// already_prepared: the scratch still holds the tracks and anchors of an earlier call with the same inputs;
+// nothing is launched, only the pointers are returned.
 // When uv_dev and gain_dev are given it also writes the per-sample output envelope
 // env[b][n] = lerp(gain) * lerp(uv) * harmonic_scale, and in SCAN mode the anchors as Q0.32 turns.
 struct dgc_harmonic_extra {
@@ -72,4 +74,5 @@ struct dgc_harmonic_extra {
 };
 int32_t dgc_harmonic_prepare(dgc_ctx *ctx, const dgc_harmonic_params *p, const float *f0_dev, float *scratch,
                              const float **play_out, const float **anchors_out, const float *uv_dev = nullptr,
-                             const float *gain_dev = nullptr, dgc_harmonic_extra *extra = nullptr);
+                             const float *gain_dev = nullptr, dgc_harmonic_extra *extra = nullptr,
+                             bool already_prepared = false);

@@ -271,6 +271,149 @@ harmonic_bwd_kernel(dgc_harmonic_params prm, float rsr, const float *__restrict_
   }
 }
 
+// The same gradient with the fixed-point phases of the scan-mode render (see harmonic_render_q_kernel in
+// osc_bank.cu): phases in Q0.32 from the Q0.32 chunk anchors, advanced by k * (f0 / sr) per frame with one
+// integer add; the per-sample fundamental, the output envelope gain * uv * scale and the control-row
+// position come from the precursor kernel's tracks instead of being re-derived per lane; the walk from a
+// chunk anchor to the first frame of a run adds up the fundamental's increments once (shared by all
+// partials, split over the group's lanes) instead of stepping every partial.
+__device__ __forceinline__ uint32_t inc_q32_bwd(float f0v, float sr, float rsr) {
+  if (!(f0v >= 0.0f && f0v < sr)) {
+    float r = f0v * rsr;
+    r = r - floorf(r);
+    if (!(r >= 0.0f && r < 1.0f)) r = 0.0f;
+    return __float2uint_rn(r * 4294967296.0f);
+  }
+  const float qh = div_by_const(f0v, sr, rsr);
+  const float ql = __fmaf_rn(-qh, sr, f0v) * rsr;
+  return __float2uint_rn(qh * 4294967296.0f) + (uint32_t)__float2int_rn(ql * 4294967296.0f);
+}
+
+template <int LPC, int P>
+__global__ void __launch_bounds__(128)
+harmonic_bwd_q_kernel(dgc_harmonic_params prm, float rsr, const float2 *__restrict__ rowtab,
+                      const int *__restrict__ ranges, const float *__restrict__ f0t, const float *__restrict__ env,
+                      const float *__restrict__ amps, const uint32_t *__restrict__ anchors_q,
+                      const float *__restrict__ g_audio, float *__restrict__ part_lo, float *__restrict__ part_hi) {
+  constexpr int G = 128 / LPC;
+  constexpr float THREE_PI = 9.42477796076938f;
+  const int B = prm.B, T = prm.T, K = prm.K, F = prm.F;
+  const int C = (T + CH - 1) / CH;
+  const int grp = threadIdx.x / LPC, j = threadIdx.x % LPC;
+  int r = blockIdx.x * G + grp;
+  const int b = blockIdx.y;
+  const bool active = r < F;
+  if (!active) r = F - 1;
+  const int hi_row = r + 1 >= F ? 0 : r + 1;
+  const float sr = prm.sample_rate, nyq = sr * 0.5f, kf0 = (float)(j + 1);
+  float alo[P], dl[P], pl[P], phh[P];
+  uint32_t q[P];
+  const float *rl = amps + ((size_t)r * B + b) * K, *rh = amps + ((size_t)hi_row * B + b) * K;
+#pragma unroll
+  for (int i = 0; i < P; ++i) {
+    int k = j + LPC * i;
+    alo[i] = k < K ? rl[k] : 0.0f;
+    dl[i] = k < K ? rh[k] - alo[i] : 0.0f;
+    pl[i] = phh[i] = 0.0f;
+    q[i] = 0u;
+  }
+  const float *g = g_audio + (size_t)b * T, *f0p = f0t + (size_t)b * T, *envp = env + (size_t)b * T;
+  for (int run = 0; run < 2; ++run) {
+    const int s0 = ranges[r * 4 + 2 * run], s1 = ranges[r * 4 + 2 * run + 1];
+    const int len = active ? s1 - s0 : 0;
+    int maxlen = len;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) maxlen = max(maxlen, __shfl_xor_sync(0xffffffffu, maxlen, off));
+    if (maxlen <= 0) continue;
+    // phases at s0: chunk anchor + k * (sum of the fundamental's increments from the chunk start to s0);
+    // the lanes of the group share the walk (every lane takes part in the shuffles, with 0 when it has no run)
+    {
+      const int c0 = len > 0 ? s0 / CH : 0;
+      uint32_t part = 0u;
+      if (len > 0)
+        for (int n = c0 * CH + j; n < s0; n += LPC) part += inc_q32_bwd(f0p[n], sr, rsr);
+#pragma unroll
+      for (int off = LPC / 2; off > 0; off >>= 1) part += __shfl_xor_sync(0xffffffffu, part, off);
+      if (len > 0) {
+        const uint32_t *anc = anchors_q + ((size_t)b * C + c0) * K;
+#pragma unroll
+        for (int i = 0; i < P; ++i) {
+          int k = j + LPC * i;
+          q[i] = (k < K ? anc[k] : 0u) + 0x100u + (uint32_t)(k + 1) * part;
+        }
+      }
+    }
+    for (int m = 0; m < maxlen; ++m) {
+      const bool live = m < len;
+      const int n = live ? s0 + m : 0;
+      if (live && (n % CH) == 0) {  // the forward re-anchors at every chunk boundary
+        const uint32_t *anc = anchors_q + ((size_t)b * C + n / CH) * K;
+#pragma unroll
+        for (int i = 0; i < P; ++i) {
+          int k = j + LPC * i;
+          q[i] = (k < K ? anc[k] : 0u) + 0x100u;
+        }
+      }
+      const float fr = rowtab[n].y, omf = __fsub_rn(1.0f, fr);
+      const float f0v = f0p[n];
+      const uint32_t dq = inc_q32_bwd(f0v, sr, rsr);
+      uint32_t incv = (uint32_t)(j + 1) * dq;
+      const uint32_t step = (uint32_t)LPC * dq;
+      float sn[P], mm[P];
+      float s1v = 0.0f, s2v = 0.0f;
+#pragma unroll
+      for (int i = 0; i < P; ++i) {
+        const float freq = __fmul_rn(partial_number(kf0, LPC * i), f0v);
+        const float a = fmaf(fr, dl[i], alo[i]);
+        const float ph1 = __uint_as_float(__funnelshift_r(q[i], 0x7Fu, 9));
+        sn[i] = -__sinf(fmaf(ph1, TWO_PI_F, -THREE_PI));   // sin(2 pi p)
+        mm[i] = freq < nyq ? 1.0f : 0.0f;
+        const float am = mm[i] * a;
+        s2v += am;
+        s1v = fmaf(sn[i], am, s1v);
+        if (live) q[i] += incv;
+        incv += step;
+      }
+#pragma unroll
+      for (int off = LPC / 2; off > 0; off >>= 1) {
+        s1v += __shfl_xor_sync(0xffffffffu, s1v, off);
+        s2v += __shfl_xor_sync(0xffffffffu, s2v, off);
+      }
+      if (live) {
+        const float inv = 1.0f / (s2v + 1e-8f);
+        const float ratio = s1v * inv;
+        const float c = g[n] * envp[n] * inv;
+        const float cl = c * omf, chh = c * fr;
+#pragma unroll
+        for (int i = 0; i < P; ++i) {
+          const float d = (sn[i] - ratio) * mm[i];
+          pl[i] = fmaf(cl, d, pl[i]);
+          phh[i] = fmaf(chh, d, phh[i]);
+        }
+      }
+    }
+  }
+  if (active) {
+    float *ol = part_lo + ((size_t)r * B + b) * K, *oh = part_hi + ((size_t)r * B + b) * K;
+#pragma unroll
+    for (int i = 0; i < P; ++i) {
+      int k = j + LPC * i;
+      if (k < K) {
+        ol[k] = pl[i];
+        oh[k] = phh[i];
+      }
+    }
+  }
+}
+
+template <int LPC, int P>
+void launch_hbwd_q(dgc_ctx *ctx, const dgc_harmonic_params &p, const float2 *rowtab, const int *ranges,
+                   const dgc_harmonic_extra &x, const float *amps, const float *g_audio, float *pl, float *ph) {
+  constexpr int G = 128 / LPC;
+  harmonic_bwd_q_kernel<LPC, P><<<dim3(dgc_div_up(p.F, G), p.B), 128, 0, ctx->stream>>>(
+      p, 1.0f / p.sample_rate, rowtab, ranges, x.f0t, x.env, amps, x.anchors_q, g_audio, pl, ph);
+}
+
 template <int LPC, int P>
 void launch_hbwd(dgc_ctx *ctx, const dgc_harmonic_params &p, const float *play, const int *ranges, const float *f0,
                  const float *uv, const float *amps, const float *gain, const float *anchors, const float *g_audio,
@@ -332,22 +475,32 @@ DGC_EXPORT uint64_t dgc_harmonic_bwd_scratch_floats(const dgc_harmonic_params *p
   return dgc_harmonic_scratch_floats(p) + 2ull * p->F * p->B * p->K + 16;
 }
 
-DGC_EXPORT int32_t dgc_harmonic_render_bwd(dgc_ctx *ctx, const dgc_harmonic_params *p, const float *f0_dev,
-                                           const float *uv_dev, const float *amps_dev, const float *gain_dev,
-                                           const float *g_audio_dev, float *scratch_dev, float *g_amps_dev) {
+static int32_t harmonic_render_bwd_impl(dgc_ctx *ctx, const dgc_harmonic_params *p, const float *f0_dev,
+                                        const float *uv_dev, const float *amps_dev, const float *gain_dev,
+                                        const float *g_audio_dev, float *scratch_dev, float *g_amps_dev,
+                                        bool prepared) {
   if (!ctx) return DGC_ERR_INVALID;
   DGC_REQUIRE(ctx, p && f0_dev && uv_dev && amps_dev && gain_dev && g_audio_dev && g_amps_dev, "null pointer");
+  DGC_REQUIRE(ctx, !prepared || scratch_dev, "the prepared variant needs the forward call's scratch");
   float *scratch = scratch_dev ? scratch_dev : dgc_ctx_scratch(ctx, dgc_harmonic_bwd_scratch_floats(p));
   if (!scratch) return DGC_ERR_OOM;
   const float *play = nullptr, *anchors = nullptr;
-  int32_t rc = dgc_harmonic_prepare(ctx, p, f0_dev, scratch, &play, &anchors);
+  dgc_harmonic_extra extra;
+  int32_t rc = dgc_harmonic_prepare(ctx, p, f0_dev, scratch, &play, &anchors, uv_dev, gain_dev, &extra, prepared);
   if (rc != DGC_OK) return rc;
   const int *ranges = dgc_ctx_row_ranges(ctx, p->F, p->T);
   if (!ranges) return DGC_ERR_UNSUPPORTED;
   const size_t n = (size_t)p->F * p->B * p->K;
   float *pl = scratch + ((dgc_harmonic_scratch_floats(p) + 3) & ~3ull), *ph = pl + n;
   const int K = p->K;
-#define HBWD(LPC, P) launch_hbwd<LPC, P>(ctx, *p, play, ranges, f0_dev, uv_dev, amps_dev, gain_dev, anchors, g_audio_dev, pl, ph)
+  const bool fixed_point = p->phase_mode == DGC_PHASE_SCAN && extra.anchors_q && extra.env;
+  const float2 *rowtab = fixed_point ? dgc_ctx_row_table(ctx, p->F, p->T) : nullptr;
+  if (fixed_point && !rowtab) return DGC_ERR_CUDA;
+#define HBWD(LPC, P)                                                                                                  \
+  do {                                                                                                                \
+    if (fixed_point) launch_hbwd_q<LPC, P>(ctx, *p, rowtab, ranges, extra, amps_dev, g_audio_dev, pl, ph);            \
+    else launch_hbwd<LPC, P>(ctx, *p, play, ranges, f0_dev, uv_dev, amps_dev, gain_dev, anchors, g_audio_dev, pl, ph); \
+  } while (0)
   if (K <= 8) HBWD(8, 1);
   else if (K <= 16) HBWD(8, 2);
   else if (K <= 32) HBWD(8, 4);
@@ -363,3 +516,17 @@ DGC_EXPORT int32_t dgc_harmonic_render_bwd(dgc_ctx *ctx, const dgc_harmonic_para
   DGC_LAUNCHED(ctx, "combine_rows");
   return DGC_OK;
 }
+
+DGC_EXPORT int32_t dgc_harmonic_render_bwd(dgc_ctx *ctx, const dgc_harmonic_params *p, const float *f0_dev,
+                                           const float *uv_dev, const float *amps_dev, const float *gain_dev,
+                                           const float *g_audio_dev, float *scratch_dev, float *g_amps_dev) {
+  return harmonic_render_bwd_impl(ctx, p, f0_dev, uv_dev, amps_dev, gain_dev, g_audio_dev, scratch_dev, g_amps_dev, false);
+}
+
+DGC_EXPORT int32_t dgc_harmonic_render_bwd_prepared(dgc_ctx *ctx, const dgc_harmonic_params *p, const float *f0_dev,
+                                                    const float *uv_dev, const float *amps_dev,
+                                                    const float *gain_dev, const float *g_audio_dev,
+                                                    float *scratch_dev, float *g_amps_dev) {
+  return harmonic_render_bwd_impl(ctx, p, f0_dev, uv_dev, amps_dev, gain_dev, g_audio_dev, scratch_dev, g_amps_dev, true);
+}
+

@@ -102,8 +102,9 @@ SIGNATURES = {
     "dgc_comm_init": (_i32, [_vp, _i32, _i32, C.c_char_p]),
     "dgc_allreduce_sum": (_i32, [_vp, _vp, _u64]),
     "dgc_comm_destroy": (_i32, [_vp]),
-    "dgc_harmonic_f0_bwd_scratch_floats": (_u64, [_vp]),
-    "dgc_harmonic_f0_bwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "dgc_harmonic_render_bwd_prepared": (_i32, [_vp, C.POINTER(HarmonicParams), _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "dgc_harmonic_f0_bwd_scratch_floats": (_u64, [C.POINTER(HarmonicParams)]),
+    "dgc_harmonic_f0_bwd": (_i32, [_vp, C.POINTER(HarmonicParams), _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "dgc_temporal_grad_scan": (_i32, [_vp, _vp, _i32, _i32, _f, _vp]),
     "dgc_hn_forward_loss_host": (_i32, [_vp, C.POINTER(HnStep)] + [_vp] * 9 + [C.POINTER(C.c_double), _vp]),
 }

@@ -60,6 +60,9 @@ class HarmonicModel:
         M, H = self.M, hidden
         self.act = [f(M, H), f(M, H), f(M, H), f(M, K + nbands)]
         self.act_t = [f(H, M), f(H, M), f(H, M)]         # transposed copies of the trunk activations
+        hp0 = HarmonicParams(B, T, K, F, sr, 1.0, phase_mode, 0)
+        self.h_scratch = f(int(ctx.lib.dgc_harmonic_bwd_scratch_floats(C.byref(hp0))) + 64)
+        self.h_prepared = None
         self.dact = [f(M, H), f(M, H), f(M, H)]          # gradient w.r.t. a layer's input
         self.dz = [f(M, H), f(M, H), f(M, H), f(M, K + nbands)]
         self.head_dz = f(M, K + nbands)
@@ -94,8 +97,10 @@ class HarmonicModel:
         c.check(lib.dgc_bands_to_taps(h, self.bands.data_ptr(), w_fs.data_ptr(), self.M, self.nbands, self.taps,
                                       self.taps_tab.data_ptr()))
         hp = HarmonicParams(self.B, self.T, self.K, self.F, self.sr, 1.0, self.phase_mode, 0)
+        # the render's per-sample tracks and phase anchors stay in this scratch for the backward pass
         c.check(lib.dgc_harmonic_render(h, C.byref(hp), f0.data_ptr(), uv.data_ptr(), self.amps.data_ptr(),
-                                        gain.data_ptr(), None, self.dry.data_ptr()))
+                                        gain.data_ptr(), self.h_scratch.data_ptr(), self.dry.data_ptr()))
+        self.h_prepared = (f0.data_ptr(), uv.data_ptr(), gain.data_ptr())
         fp = FirParams(self.B, self.T, self.F, self.taps, 0.12, 1)
         c.check(lib.dgc_fir_noise(h, C.byref(fp), noise.data_ptr(), self.taps_tab.data_ptr(), noise_gain.data_ptr(),
                                   self.dry.data_ptr()))
@@ -119,8 +124,12 @@ class HarmonicModel:
                                      self.conv_hop, 1.0, self.g_out.data_ptr(), None, 1, self.g_out.data_ptr(),
                                      g_ir.data_ptr()))
         hp = HarmonicParams(self.B, self.T, self.K, self.F, self.sr, 1.0, self.phase_mode, 0)
-        c.check(lib.dgc_harmonic_render_bwd(h, C.byref(hp), f0.data_ptr(), uv.data_ptr(), self.amps.data_ptr(),
-                                            gain.data_ptr(), self.g_out.data_ptr(), None, self.g_amps.data_ptr()))
+        bwd = lib.dgc_harmonic_render_bwd_prepared \
+            if getattr(self, "h_prepared", None) == (f0.data_ptr(), uv.data_ptr(), gain.data_ptr()) \
+            else lib.dgc_harmonic_render_bwd
+        c.check(bwd(h, C.byref(hp), f0.data_ptr(), uv.data_ptr(), self.amps.data_ptr(), gain.data_ptr(),
+                    self.g_out.data_ptr(), self.h_scratch.data_ptr(), self.g_amps.data_ptr()))
+        self.h_prepared = None
         fp = FirParams(self.B, self.T, self.F, self.taps, 0.12, 0)
         c.check(lib.dgc_fir_noise_bwd(h, C.byref(fp), noise.data_ptr(), noise_gain.data_ptr(), self.g_out.data_ptr(),
                                       self.g_taps.data_ptr()))

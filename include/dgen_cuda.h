@@ -152,6 +152,14 @@ uint64_t dgc_harmonic_bwd_scratch_floats(const dgc_harmonic_params *p);
 int32_t dgc_harmonic_render_bwd(dgc_ctx *ctx, const dgc_harmonic_params *p, const float *f0_dev, const float *uv_dev,
                                 const float *amps_dev, const float *gain_dev, const float *g_audio_dev,
                                 float *scratch_dev, float *g_amps_dev);
+/* The same, for a caller that has just rendered the forward with dgc_harmonic_render on the same p, f0, uv and
+ * gain and passed it scratch_dev (sized with dgc_harmonic_bwd_scratch_floats): the per-sample tracks and
+ * phase anchors the forward left in that scratch are used as they are instead of being computed again.
+ * The caller guarantees that the scratch was not written in between.  No reference counterpart (the
+ * reference recomputes the forward inside its backward kernels). */
+int32_t dgc_harmonic_render_bwd_prepared(dgc_ctx *ctx, const dgc_harmonic_params *p, const float *f0_dev,
+                                         const float *uv_dev, const float *amps_dev, const float *gain_dev,
+                                         const float *g_audio_dev, float *scratch_dev, float *g_amps_dev);
 /* Gradient of the harmonic branch w.r.t. the fundamental table: g_f0 [F][B] from g_audio [B][T], through the
  * phases: dL/dfreq_k[n] = (1/sr) * sum_{m>n} dL/dphi_k[m] (exclusive reverse scan; the wrap is the identity,
  * the Nyquist comparison has no gradient), freq_k = k * sampleRow(f0).
