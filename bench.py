@@ -298,13 +298,18 @@ def run_ours(args, rank, world, local_rank):
         # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per voice of each stage's kernels, from the
         # ncu --set full capture of this workload at 16 voices summarised in
         # profiles/fwd_loss_c2_kernels_full_set.md; traffic grows in proportion to the voices per launch.
-        ncu_traffic_per_voice = {"harmonic_render": (13.27e6 + 4.12e6) / 16, "fir_noise": 25.02e6 / 16,
-                                 "mss_loss_fwd": 49.19e6 / 16}
+        ncu_traffic_per_voice = {"harmonic_render": (21.55e6 + 4.12e6) / 16, "fir_noise": 25.02e6 / 16,
+                                 "mss_loss_fwd": 8.34e6 / 16, "bands_to_taps": 4.26e6 / 16}
         dom = max(stage_ms, key=stage_ms.get)
         achieved = alg[dom] / (stage_ms[dom] * 1e-3) / 1e9
         traffic = ncu_traffic_per_voice.get(dom)
         traffic = traffic * B if traffic is not None else None
         step_bytes = sum(alg.values())
+        sm_mhz = float((clocks or {}).get("sm_mhz") or 1965.0)
+        sfu_peak = 148 * 16 * sm_mhz / 1e3                                    # G sin/s
+        sfu_ach = B * T * K / (stage_ms["harmonic_render"] * 1e-3) / 1e9
+        sfu = {"unit": "G sin/s", "achieved": sfu_ach, "peak": sfu_peak, "frac": sfu_ach / sfu_peak,
+               "what": "render stage (4 kernels), one sine per voice x frame x harmonic"}
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
                 "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
@@ -315,7 +320,10 @@ def run_ours(args, rank, world, local_rank):
                 "roofline": {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "GB/s",
                              "frac": achieved / peak, "traffic": traffic,
                              "peak_source": "measured" if peaks else "fallback",
-                             "note": "the stage is FP32/SFU-issue bound, not HBM bound; see DESIGN.md"},
+                             "note": "the stage is FP32/SFU-issue bound, not HBM bound; see DESIGN.md",
+                             # the bound that does apply to the oscillator bank: one sine per (voice, frame,
+                             # harmonic) on the 16 SFU lanes of each SM at the sampled SM clock
+                             "sfu": sfu},
                 "stage_ms": stage_ms,
                 "whole_step": {"algorithmic_bytes": step_bytes,
                                "achieved_gbs": step_bytes / (total_ms / args.steps * 1e-3) / 1e9},
