@@ -1,34 +1,28 @@
 // Noise branch of the batched harmonic synth: a time-varying FIR whose taps are linearly
 // interpolated between control rows at every sample (Examples/HarmonicE2E/Synth.swift:97-101),
 // and the band-magnitude -> tap matrix product that feeds it in the synthetic workload.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace {
 
-__device__ __forceinline__ void row_pos(float idx, int rows, int &lo, float &fr) {
-  float fr_rows = (float)rows;
-  float w = fmodf(idx, fr_rows);
-  if (w < 0.0f) w += fr_rows;
-  float fl = floorf(w);
-  lo = (int)fl;
-  fr = w - fl;
-}
-
-// Block = 256 threads, thread = SPT consecutive frames of one voice, tile = 256*SPT frames.
+// Block = NTH threads, thread = SPT consecutive frames of one voice, tile = NTH*SPT frames.  NTH is picked by
+// the host so that all blocks of the launch are resident at once (no second, mostly empty wave).
 // Shared memory: the control rows the tile touches (R rows of `taps` floats) and the noise tile with
 // its taps-1 frames of history, de-interleaved by (index mod SPT) so that the sliding window of a
 // thread and of its neighbours falls in distinct banks.
 // A thread's SPT frames see at most two (lo, hi) row pairs (the host guarantees step*SPT < 1), so it
 // accumulates dot products against rows r0, r0+1 for every frame, and against r0+2 only when its
 // frames straddle a control-row boundary.
-template <int SPT>
-__global__ void __launch_bounds__(256)
-fir_noise_kernel(dgc_fir_params prm, const float *__restrict__ play, const float *__restrict__ noise,
+template <int SPT, int NTH>
+__global__ void __launch_bounds__(NTH)
+fir_noise_kernel(dgc_fir_params prm, const float2 *__restrict__ rowtab, const float *__restrict__ noise,
                  const float *__restrict__ taps_tab, const float *__restrict__ ngain, float *__restrict__ audio,
                  int max_rows, int32_t *status) {
   extern __shared__ float sh[];
   const int B = prm.B, T = prm.T, F = prm.F, NT = prm.taps;
-  constexpr int TILE = 256 * SPT;
+  constexpr int TILE = NTH * SPT;
   const int b = blockIdx.y, t0 = blockIdx.x * TILE;
   const int t_last = min(T - 1, t0 + TILE - 1);
   // The control clock wraps to 0 when it reaches its maximum (the sequential single-precision
@@ -41,14 +35,13 @@ fir_noise_kernel(dgc_fir_params prm, const float *__restrict__ play, const float
 #pragma unroll
   for (int u = 0; u < SPT; ++u) {
     int n = t0 + threadIdx.x * SPT + u;
-    if (n > t0 && n <= t_last && play[n] < play[n - 1]) atomicMin(&wrap_sh, n);
+    // (the cached row table holds the floor control row of every frame: a drop marks the wrap)
+    if (n > t0 && n <= t_last && __float_as_int(rowtab[n].x) < __float_as_int(rowtab[n - 1].x)) atomicMin(&wrap_sh, n);
   }
   __syncthreads();
   const int wrap = wrap_sh;
-  int rmin, rmax;
-  float dummy;
-  row_pos(play[t0], F, rmin, dummy);
-  row_pos(play[t_last], F, rmax, dummy);
+  const int rmin = __float_as_int(rowtab[t0].x);
+  int rmax = __float_as_int(rowtab[t_last].x);
   if (t_last >= wrap) rmax += F;
   const int R = rmax - rmin + 3;  // rows rmin .. rmax+2 (hi of the last frame, and the straddle row)
   if (R > max_rows) {
@@ -59,15 +52,22 @@ fir_noise_kernel(dgc_fir_params prm, const float *__restrict__ play, const float
   float *xs = sh + (size_t)max_rows * NT;    // [SPT][Q], Q = (TILE + NT - 1 + SPT - 1) / SPT + 1
   const int XN = TILE + NT - 1;
   const int Q = (XN + SPT - 1) / SPT + 1;
-  for (int i = threadIdx.x; i < R * NT; i += 256) {
-    int r = rmin + i / NT, col = i - (i / NT) * NT;
-    if (r >= F) r -= F;  // the ceil row wraps to row 0
-    if (r >= F) r = F - 1;
-    rows[i] = taps_tab[((size_t)r * B + b) * NT + col];
+  {
+    // flat copy of R * NT floats, independent iterations (the loads of several elements are in flight
+    // together); i / NT by multiplication with ceil(2^32 / NT), exact for i * NT < 2^32
+    const unsigned magic = (unsigned)((0x100000000ull + (unsigned)NT - 1) / (unsigned)NT);
+#pragma unroll 4
+    for (int i = threadIdx.x; i < R * NT; i += NTH) {
+      const int rr = (int)__umulhi((unsigned)i, magic), col = i - rr * NT;
+      int r = rmin + rr;
+      if (r >= F) r -= F;  // the ceil row wraps to row 0
+      if (r >= F) r = F - 1;
+      rows[i] = taps_tab[((size_t)r * B + b) * NT + col];
+    }
   }
   // xs position m <-> frame t0 - (NT-1) + m
   const float *xn = noise + (size_t)b * T;
-  for (int m = threadIdx.x; m < XN; m += 256) {
+  for (int m = threadIdx.x; m < XN; m += NTH) {
     int t = t0 - (NT - 1) + m;
     float v = (t >= 0 && t < T) ? xn[t] : 0.0f;
     xs[(m % SPT) * Q + m / SPT] = v;
@@ -81,7 +81,9 @@ fir_noise_kernel(dgc_fir_params prm, const float *__restrict__ play, const float
 #pragma unroll
   for (int u = 0; u < SPT; ++u) {
     int n = min(t0 + nl + u, T - 1);
-    row_pos(play[n], F, lo[u], fr[u]);
+    const float2 rt = rowtab[n];
+    lo[u] = __float_as_int(rt.x);
+    fr[u] = rt.y;
     if (n >= wrap) lo[u] += F;
   }
   const int r0 = lo[0] - rmin;
@@ -93,6 +95,56 @@ fir_noise_kernel(dgc_fir_params prm, const float *__restrict__ play, const float
   for (int u = 0; u < SPT; ++u) d0[u] = d1[u] = d2[u] = 0.0f;
 
   // frame (nl+u), tap i reads xs position m = nl + u + i
+  if (SPT == 8) {
+    // Taps in groups of 8: W[0..15] holds x at positions nl + i0 .. nl + i0 + 15 (two shared-memory rows of the
+    // de-interleaved tile per thread and group), so tap i0 + j of frame u multiplies W[u + j]: no per-tap
+    // window rotation and no index arithmetic inside the 128 (256 with the second row) multiply-adds of a group.
+    const float *xb = xs + threadIdx.x;   // W[t] = xb[(t % 8) * Q + i0 / 8 + t / 8]
+    auto dots = [&](const float *pa, const float *pb, float(&e0)[SPT], float(&e1)[SPT], bool two) {
+      float W[16];
+#pragma unroll
+      for (int t = 0; t < 8; ++t) W[t] = xb[t * Q];
+      const int NG = NT / 8;
+      for (int g8 = 0; g8 < NG; ++g8) {
+#pragma unroll
+        for (int t = 0; t < 8; ++t) W[8 + t] = xb[t * Q + g8 + 1];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float ta = pa[g8 * 8 + j];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) e0[u] = fmaf(W[u + j], ta, e0[u]);
+          if (two) {
+            const float tb = pb[g8 * 8 + j];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) e1[u] = fmaf(W[u + j], tb, e1[u]);
+          }
+        }
+#pragma unroll
+        for (int t = 0; t < 8; ++t) W[t] = W[8 + t];
+      }
+      // remaining taps (NT % 8), W[0..7] = positions nl + 8 * NG ..
+      const int rem = NT - NG * 8;
+      if (rem > 0) {
+#pragma unroll
+        for (int t = 0; t < 8; ++t) W[8 + t] = xb[t * Q + NG + 1];
+#pragma unroll
+        for (int j = 0; j < 7; ++j) {
+          if (j < rem) {
+            const float ta = pa[NG * 8 + j];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) e0[u] = fmaf(W[u + j], ta, e0[u]);
+            if (two) {
+              const float tb = pb[NG * 8 + j];
+#pragma unroll
+              for (int u = 0; u < 8; ++u) e1[u] = fmaf(W[u + j], tb, e1[u]);
+            }
+          }
+        }
+      }
+    };
+    dots(ra, rb, d0, d1, true);
+    if (straddle) dots(rc, rc, d2, d2, false);
+  } else {
   float win[SPT];
 #pragma unroll
   for (int u = 0; u < SPT - 1; ++u) win[u + 1] = xs[((nl + u) % SPT) * Q + (nl + u) / SPT];
@@ -122,6 +174,7 @@ fir_noise_kernel(dgc_fir_params prm, const float *__restrict__ play, const float
 #pragma unroll
       for (int u = 0; u < SPT; ++u) d2[u] = fmaf(win[u], tc, d2[u]);
     }
+  }
   }
   if (spread > 1 || spread < 0) {
     // the frames of this thread sit across the clock wrap: evaluate each frame against its own rows
@@ -207,29 +260,41 @@ DGC_EXPORT int32_t dgc_fir_noise(dgc_ctx *ctx, const dgc_fir_params *p, const fl
   DGC_REQUIRE(ctx, p && noise_dev && taps_dev && noise_gain_dev && audio_dev, "null pointer");
   DGC_REQUIRE(ctx, p->B > 0 && p->T > 0 && p->F > 0, "size out of range");
   DGC_REQUIRE(ctx, p->taps >= 1 && p->taps <= 1024, "taps must be in 1..1024");
-  const float *play = nullptr;
-  int32_t rc = dgc_playhead(ctx, p->F, p->T, &play);
-  if (rc != DGC_OK) return rc;
+  const float2 *play = dgc_ctx_row_table(ctx, p->F, p->T);   // (floor row, fraction) of every frame
+  if (!play) return DGC_ERR_CUDA;
+  int32_t rc = DGC_OK;
   // playhead advance per frame; the sequential single-precision clock runs up to ~0.5% fast
   double step = p->T > 1 ? (double)(p->F - 1) / (double)(p->T - 1) : 0.0;
   step *= 1.01;
   const int NT = p->taps;
-  auto launch = [&](auto kern, int spt) -> int32_t {
-    int tile = 256 * spt;
+  auto launch = [&](auto kern, int spt, int nth) -> int32_t {
+    int tile = nth * spt;
     int max_rows = (int)(step * tile) + 5;
     size_t smem = ((size_t)max_rows * NT + (size_t)spt * ((tile + NT - 1 + spt - 1) / spt + 1)) * sizeof(float);
     if (smem > 200 * 1024) return DGC_ERR_UNSUPPORTED;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return dgc_fail(ctx, DGC_ERR_CUDA, "fir smem opt-in: %s", cudaGetErrorString(e));
-    kern<<<dim3(dgc_div_up(p->T, tile), p->B), 256, smem, ctx->stream>>>(*p, play, noise_dev, taps_dev,
+    kern<<<dim3(dgc_div_up(p->T, tile), p->B), nth, smem, ctx->stream>>>(*p, play, noise_dev, taps_dev,
                                                                           noise_gain_dev, audio_dev, max_rows,
                                                                           ctx->status_dev);
     ctx->launches++;
     return dgc_check_launch(ctx, "fir_noise");
   };
   rc = DGC_ERR_UNSUPPORTED;
-  if (step * 8 < 0.98) rc = launch(fir_noise_kernel<8>, 8);
-  if (rc == DGC_ERR_UNSUPPORTED) rc = launch(fir_noise_kernel<1>, 1);
+  if (step * 8 < 0.98) {
+    // 256-thread tiles amortise the staged control rows best (measured against 128 and 64 at the headline
+    // configuration: 82.5 / 86.5 / 83 us); DGC_FIR_THREADS forces a tile size for experiments
+    static const int forced = [] {
+      const char *e = getenv("DGC_FIR_THREADS");
+      return e ? atoi(e) : 0;
+    }();
+    int nth = 256;
+    if (forced == 64 || forced == 128 || forced == 256) nth = forced;
+    if (nth == 256) rc = launch(fir_noise_kernel<8, 256>, 8, 256);
+    else if (nth == 128) rc = launch(fir_noise_kernel<8, 128>, 8, 128);
+    else rc = launch(fir_noise_kernel<8, 64>, 8, 64);
+  }
+  if (rc == DGC_ERR_UNSUPPORTED) rc = launch(fir_noise_kernel<1, 256>, 1, 256);
   if (rc == DGC_ERR_UNSUPPORTED)
     return dgc_fail(ctx, DGC_ERR_UNSUPPORTED, "fir_noise: control rate too high for the shared-memory tile");
   return rc;
