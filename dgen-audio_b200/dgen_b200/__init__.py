@@ -41,6 +41,43 @@ class BiquadParams(C.Structure):
     _fields_ = [("B", C.c_int32), ("T", C.c_int32), ("L", C.c_int32), ("gain", C.c_float), ("mode", C.c_float)]
 
 
+class Uop(C.Structure):
+    """One op of a generated block (dgc_uop)."""
+    _fields_ = [("op", C.c_int32), ("a", C.c_int32), ("b", C.c_int32), ("c", C.c_int32), ("imm", C.c_float)]
+
+
+# op codes of include/dgen_cuda.h
+OP = dict(CONST=0, LOAD=1, LOAD_SCALAR=2, FRAME_INDEX=3,
+          ADD=10, SUB=11, MUL=12, DIV=13, MOD=14, POW=15, MIN=16, MAX=17, ATAN2=18, AND=19, OR=20, XOR=21, GT=22,
+          GTE=23, LTE=24, LT=25, EQ=26,
+          ABS=40, SIGN=41, FLOOR=42, CEIL=43, ROUND=44, SIN=45, COS=46, TAN=47, ATAN=48, TANH=49, EXP=50, LOG=51,
+          LOG10=52, SQRT=53, GSWITCH=60, STORE=70, OUTPUT=71)
+
+
+def _uops(ops):
+    """ops: list of (name, a, b, c, imm) tuples (missing fields 0) -> ctypes array."""
+    arr = (Uop * len(ops))()
+    for k, o in enumerate(ops):
+        o = tuple(o) + (0,) * (5 - len(o))
+        arr[k] = Uop(OP[o[0]] if isinstance(o[0], str) else int(o[0]), int(o[1]), int(o[2]), int(o[3]), float(o[4]))
+    return arr
+
+
+def block_source(ops, name="dgen_block"):
+    """CUDA C source the library emits for an op list (no GPU needed)."""
+    arr = _uops(ops)
+    need = C.c_uint64(0)
+    lib = load()
+    rc = lib.dgc_block_emit(arr, len(ops), name.encode(), None, 0, C.byref(need))
+    if rc != DGC_OK:
+        raise DgenCudaError("dgc_block_emit failed: %d" % rc)
+    buf = C.create_string_buffer(need.value)
+    rc = lib.dgc_block_emit(arr, len(ops), name.encode(), buf, need.value, C.byref(need))
+    if rc != DGC_OK:
+        raise DgenCudaError("dgc_block_emit failed: %d" % rc)
+    return buf.value.decode()
+
+
 class HnStep(C.Structure):
     _fields_ = [("harm", HarmonicParams), ("fir", FirParams), ("mss", MssParams), ("nbands", C.c_int32)]
 
@@ -98,6 +135,8 @@ SIGNATURES = {
     "dgc_module_compile": (_i32, [_vp, C.c_char_p, C.c_char_p, C.POINTER(_vp)]),
     "dgc_module_unload": (_i32, [_vp]),
     "dgc_launch": (_i32, [_vp, C.c_char_p, C.POINTER(_u32), C.POINTER(_u32), _u32, C.POINTER(_vp)]),
+    "dgc_block_emit": (_i32, [C.POINTER(Uop), _i32, C.c_char_p, C.c_char_p, _u64, C.POINTER(_u64)]),
+    "dgc_block_compile": (_i32, [_vp, C.POINTER(Uop), _i32, C.c_char_p, C.POINTER(_vp)]),
     "dgc_comm_unique_id": (_i32, [C.c_char_p]),
     "dgc_comm_init": (_i32, [_vp, _i32, _i32, C.c_char_p]),
     "dgc_allreduce_sum": (_i32, [_vp, _vp, _u64]),
@@ -427,6 +466,13 @@ class Context:
         """CUDA C source of generated blocks -> Module (NVRTC, sm_100a)."""
         m = _vp()
         self.check(self.lib.dgc_module_compile(self.h, cuda_source.encode(), name.encode(), C.byref(m)))
+        return Module(self, m)
+
+    def compile_block(self, ops, name="dgen_block"):
+        """Op list (see block_source) -> Module with one kernel `name(float *memory, int count)`."""
+        arr = _uops(ops)
+        m = _vp()
+        self.check(self.lib.dgc_block_compile(self.h, arr, len(ops), name.encode(), C.byref(m)))
         return Module(self, m)
 
     def load_module(self, image):

@@ -321,6 +321,36 @@ int32_t dgc_module_unload(dgc_module *m);
 int32_t dgc_launch(dgc_module *m, const char *kernel_name, const uint32_t grid[3], const uint32_t block[3],
                    uint32_t smem_bytes, void **args);
 
+/* Blocks as op lists: the elementwise subset of the reference's UOps in SSA form (the value of op k is t_k;
+ * operands a, b, c are ids of earlier ops, or an arena cell offset for the memory ops), one thread per
+ * (frame, element) index i < count.  dgc_block_emit writes the CUDA C of `extern "C" __global__ void
+ * name(float *memory, int count)` using the scalar expressions of the reference's C renderer for every op
+ * (Sources/DGen/Renderer/CRenderer.swift:484-1040): division / modulo / power by a constant are specialised
+ * the same way, comparisons and logic yield 1.0f / 0.0f, gswitch tests `> 0`, OUTPUT sanitises.
+ * `needed` receives the size of the source including the terminator; call with out == NULL to size it.
+ * dgc_block_compile = emit + dgc_module_compile. */
+enum {
+  DGC_OP_CONST = 0,      /* imm */
+  DGC_OP_LOAD = 1,       /* memory[a + i] */
+  DGC_OP_LOAD_SCALAR = 2,/* memory[a] */
+  DGC_OP_FRAME_INDEX = 3,/* (float)i */
+  DGC_OP_ADD = 10, DGC_OP_SUB, DGC_OP_MUL, DGC_OP_DIV, DGC_OP_MOD, DGC_OP_POW, DGC_OP_MIN, DGC_OP_MAX, DGC_OP_ATAN2,
+  DGC_OP_AND, DGC_OP_OR, DGC_OP_XOR, DGC_OP_GT, DGC_OP_GTE, DGC_OP_LTE, DGC_OP_LT, DGC_OP_EQ,
+  DGC_OP_ABS = 40, DGC_OP_SIGN, DGC_OP_FLOOR, DGC_OP_CEIL, DGC_OP_ROUND, DGC_OP_SIN, DGC_OP_COS, DGC_OP_TAN,
+  DGC_OP_ATAN, DGC_OP_TANH, DGC_OP_EXP, DGC_OP_LOG, DGC_OP_LOG10, DGC_OP_SQRT,
+  DGC_OP_GSWITCH = 60,   /* t_a > 0 ? t_b : t_c */
+  DGC_OP_STORE = 70,     /* memory[a + i] = t_b */
+  DGC_OP_OUTPUT = 71     /* memory[a + i] = sanitize(t_b) */
+};
+typedef struct dgc_uop {
+  int32_t op;
+  int32_t a, b, c;
+  float imm;
+} dgc_uop;
+int32_t dgc_block_emit(const dgc_uop *ops, int32_t n_ops, const char *kernel_name, char *out, uint64_t out_cap,
+                       uint64_t *needed);
+int32_t dgc_block_compile(dgc_ctx *ctx, const dgc_uop *ops, int32_t n_ops, const char *kernel_name, dgc_module **out);
+
 /* ---- gradient exchange between GPUs ------------------------------------------------------------------
  * One process per GPU, one communicator per context (NCCL, found at run time; DGC_NCCL_PATH overrides).
  * Rank 0 creates the id, the host hands its DGC_COMM_ID_BYTES bytes to every rank, every rank calls
