@@ -152,6 +152,21 @@ class HarmonicModel:
                                        gW.data_ptr(), gb.data_ptr(), self.act_t[i - 1].data_ptr() if i > 0 else None))
         return self.grads
 
+    def snapshots(self):
+        """Named parameter tensors in the reference decoder's naming (Examples/HarmonicE2E/Model.swift:122-137), ready
+        for runfiles.write_model_state."""
+        from . import runfiles
+        return runfiles.snapshots_from_flat(self.layout, self.params.cpu().numpy(), self.K)
+
+    def load_snapshots(self, named):
+        """Inverse: `named` as runfiles.read_model_state returns it.  Adam moments and the step index are reset."""
+        from . import runfiles
+        flat = runfiles.flat_from_snapshots(self.layout, named, self.K)
+        self.params.copy_(self.torch.from_numpy(flat).to(self.params.device))
+        self.m.zero_()
+        self.v.zero_()
+        self.step_index = 0
+
     def step(self, X, f0, uv, gain, noise_gain, noise, w_fs, target, lr=1e-3):
         """forward + backward + gradient all-reduce + Adam; returns the device loss tensor (local mean)."""
         self.forward(X, f0, uv, gain, noise_gain, noise, w_fs, target)

@@ -1,5 +1,7 @@
 """One training step of the harmonic+noise model (controller MLP -> synthesis -> learnable-IR reverb ->
 multi-scale spectral loss -> backward -> Adam) against the fp64 autograd evaluation of the same graph."""
+import os
+
 import numpy as np
 import pytest
 import torch
@@ -86,4 +88,33 @@ def test_loss_decreases_over_a_few_steps():
             dev(d["noise_gain"]), dev(d["noise"]), dev(d["W"]), dev(target)]
     losses = [float(model.step(*args, lr=3e-3).cpu()[0]) for _ in range(30)]
     assert losses[-1] < 0.9 * losses[0]
+    ctx.close()
+
+
+def test_checkpoint_round_trip_through_the_reference_file_format(tmp_path):
+    """Parameters -> model_step_%08d.json (Examples/HarmonicE2E/Checkpoint.swift layout) -> a fresh model: the
+    loss of the restored model equals the loss of the saved one bit for bit."""
+    from dgen_b200 import runfiles as rf
+    B, T, K, F, NB, NT = 2, 4096, 16, 32, 9, 33
+    d = wl.harmonic_noise_inputs(51, B=B, T=T, K=K, F=F, nbands=NB, taps=NT)
+    target = orc.harmonic_noise_render(d["f0"], d["uv"], d["amps"], d["gain"], d["noise_gain"], wl.taps_from_bands(d),
+                                       d["noise"], T, d["sr"])
+    ctx = dgen_b200.Context(0)
+    kw = dict(K=K, F=F, nbands=NB, taps=NT, hidden=32, ir_len=512, conv_n=128, conv_hop=64, sizes=(256, 64))
+    args = [dev(tr.features_from_controls(d["f0"], d["gain"])), dev(d["f0"]), dev(d["uv"]), dev(d["gain"]),
+            dev(d["noise_gain"]), dev(d["noise"]), dev(d["W"]), dev(target)]
+    a = tr.HarmonicModel(ctx, B, T, seed=5, **kw)
+    for _ in range(2):
+        a.step(*args)
+    run = rf.RunDirectories(str(tmp_path / "run"))
+    path = rf.write_model_state(run.checkpoints, a.step_index, a.snapshots())
+    step, named = rf.read_model_state(path)
+    assert step == 2 and set(named) == {"W1", "b1", "W2", "b2", "W3", "b3", "W_harm", "b_harm", "W_noise", "b_noise", "ir"}
+    b = tr.HarmonicModel(ctx, B, T, seed=99, **kw)
+    b.load_snapshots(named)
+    la, lb = float(a.forward(*args).cpu()[0]), float(b.forward(*args).cpu()[0])
+    assert la == lb
+    rf.wav_save(os.path.join(run.renders, "pred.wav"), b.out[0].cpu().numpy(), d["sr"])
+    y, sr = rf.wav_load(os.path.join(run.renders, "pred.wav"))
+    assert sr == d["sr"] and np.array_equal(y, b.out[0].cpu().numpy())
     ctx.close()
