@@ -40,6 +40,8 @@ struct dgc_ctx {
   uint64_t dzt_floats = 0;
   // staging for the host-buffer composite entry points; uploads run on their own stream so that the
   // first kernels start while later inputs are still crossing PCIe
+  cudaStream_t aux_stream = nullptr;   // second stream of the composite steps (noise branch beside the harmonic one)
+  cudaEvent_t fork_ev = nullptr, join_ev = nullptr;
   cudaStream_t copy_stream = nullptr;
   cudaEvent_t copy_ev[3] = {nullptr, nullptr, nullptr};
   float *stage_dev = nullptr;
@@ -62,6 +64,9 @@ const float *dgc_ctx_hann_per(dgc_ctx *ctx, int N);
 // C[M][N] = A[M][K] * B[N][K]^T on the matmul path of gemm.cu
 int32_t dgc_gemm_nt(dgc_ctx *ctx, const float *a, const float *b, int M, int N, int K, float *c);
 const float2 *dgc_ctx_twiddles(dgc_ctx *ctx, int N);
+// dgc_mss_loss_fwd with the prediction given as the sum of two signals (pred_b may be null)
+int32_t dgc_mss_loss_fwd_sum(dgc_ctx *ctx, const dgc_mss_params *p, const float *pred_dev, const float *pred_b_dev,
+                             const float *target_dev, float *partial_dev, double *loss_dev);
 
 #define DGC_CUDA(ctx, call)                                                                  \
   do {                                                                                       \

@@ -190,6 +190,9 @@ DGC_EXPORT int32_t dgc_ctx_destroy(dgc_ctx *c) {
   for (auto &e : c->copy_ev)
     if (e) cudaEventDestroy(e);
   if (c->copy_stream) cudaStreamDestroy(c->copy_stream);
+  if (c->fork_ev) cudaEventDestroy(c->fork_ev);
+  if (c->join_ev) cudaEventDestroy(c->join_ev);
+  if (c->aux_stream) cudaStreamDestroy(c->aux_stream);
   if (c->wt_buf) cudaFree(c->wt_buf);
   if (c->dzt_buf) cudaFree(c->dzt_buf);
   if (c->status_dev) cudaFree(c->status_dev);

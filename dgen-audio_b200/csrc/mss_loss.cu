@@ -48,8 +48,9 @@ __device__ __forceinline__ void unpack(float2 zk, float2 znk, float2 &x1, float2
 
 // One block of one scale: LOSS_THREADS / (N/8) windows of one voice, prediction and target in the real
 // and imaginary lane of one transform; sm holds 2 * NF * padded(N) float2 (the same 34.8 KB for every N).
-template <int N>
+template <int N, bool SUM2>
 __device__ __forceinline__ void mss_fwd_body(float2 *sm, float *red, int bx, int b, const float *__restrict__ pred,
+                                             const float *__restrict__ pred_b,
                                              const float *__restrict__ target, int B, int T, int hop, int H,
                                              const float *__restrict__ window, const float2 *__restrict__ tw,
                                              float *__restrict__ part_lin, float *__restrict__ part_log) {
@@ -62,6 +63,7 @@ __device__ __forceinline__ void mss_fwd_body(float2 *sm, float *red, int bx, int
   const bool valid = h < H;
   const int t_base = h * hop - (N - 1);
   const float *x1 = pred + (size_t)b * T, *x2 = target + (size_t)b * T;
+  const float *x1b = SUM2 ? pred_b + (size_t)b * T : nullptr;   // prediction given as a sum of two signals
   float2 *a = bufa + f * PN, *bb = bufb + f * PN;
 #pragma unroll
   for (int q = 0; q < 8; ++q) {
@@ -69,7 +71,8 @@ __device__ __forceinline__ void mss_fwd_body(float2 *sm, float *red, int bx, int
     float2 v = make_float2(0.0f, 0.0f);
     if (valid && t >= 0 && t < T) {
       float w = __ldg(&window[i]);
-      v = make_float2(x1[t] * w, x2[t] * w);
+      const float xp = SUM2 ? __fadd_rn(x1[t], x1b[t]) : x1[t];
+      v = make_float2(xp * w, x2[t] * w);
     }
     a[pad(i)] = v;
   }
@@ -113,8 +116,10 @@ struct FwdDesc {
 
 constexpr int FWD_SMEM_BYTES = 2 * (LOSS_THREADS / (2048 / 8)) * padded(2048) * (int)sizeof(float2);
 
+template <bool SUM2>
 __global__ void __launch_bounds__(LOSS_THREADS)
-mss_fwd_kernel(const float *__restrict__ pred, const float *__restrict__ target, int B, int T, const FwdDesc d) {
+mss_fwd_kernel(const float *__restrict__ pred, const float *__restrict__ pred_b, const float *__restrict__ target,
+               int B, int T, const FwdDesc d) {
   extern __shared__ float2 fwd_sm[];
   __shared__ float red[LOSS_THREADS / 32];
   int s = 0;
@@ -122,7 +127,7 @@ mss_fwd_kernel(const float *__restrict__ pred, const float *__restrict__ target,
   const int bx = blockIdx.x - d.first_block[s], b = blockIdx.y;
   switch (d.N[s]) {
 #define CASE(NN) \
-  case NN: mss_fwd_body<NN>(fwd_sm, red, bx, b, pred, target, B, T, d.hop[s], d.H[s], d.window[s], d.tw[s], d.lin[s], d.lg[s]); break;
+  case NN: mss_fwd_body<NN, SUM2>(fwd_sm, red, bx, b, pred, pred_b, target, B, T, d.hop[s], d.H[s], d.window[s], d.tw[s], d.lin[s], d.lg[s]); break;
     CASE(16) CASE(32) CASE(64) CASE(128) CASE(256) CASE(512) CASE(1024) CASE(2048)
 #undef CASE
     default: break;
@@ -362,6 +367,13 @@ DGC_EXPORT uint64_t dgc_mss_partial_floats(const dgc_mss_params *p) {
 
 DGC_EXPORT int32_t dgc_mss_loss_fwd(dgc_ctx *ctx, const dgc_mss_params *p, const float *pred_dev,
                                     const float *target_dev, float *partial_dev, double *loss_dev) {
+  return dgc_mss_loss_fwd_sum(ctx, p, pred_dev, nullptr, target_dev, partial_dev, loss_dev);
+}
+
+// prediction = pred_dev + pred_b_dev (pred_b_dev may be null): lets two synthesis branches that ran
+// concurrently feed the loss without a pass that adds them
+int32_t dgc_mss_loss_fwd_sum(dgc_ctx *ctx, const dgc_mss_params *p, const float *pred_dev, const float *pred_b_dev,
+                             const float *target_dev, float *partial_dev, double *loss_dev) {
   if (!ctx) return DGC_ERR_INVALID;
   DGC_REQUIRE(ctx, p && pred_dev && target_dev && loss_dev, "null pointer");
   int32_t rc = validate(ctx, p);
@@ -413,7 +425,12 @@ DGC_EXPORT int32_t dgc_mss_loss_fwd(dgc_ctx *ctx, const dgc_mss_params *p, const
   }
   fd.first_block[no] = blocks;
   if (no > 0) {
-    mss_fwd_kernel<<<dim3(blocks, p->B), LOSS_THREADS, FWD_SMEM_BYTES, ctx->stream>>>(pred_dev, target_dev, p->B, p->T, fd);
+    if (pred_b_dev)
+      mss_fwd_kernel<true><<<dim3(blocks, p->B), LOSS_THREADS, FWD_SMEM_BYTES, ctx->stream>>>(pred_dev, pred_b_dev,
+                                                                                              target_dev, p->B, p->T, fd);
+    else
+      mss_fwd_kernel<false><<<dim3(blocks, p->B), LOSS_THREADS, FWD_SMEM_BYTES, ctx->stream>>>(pred_dev, nullptr,
+                                                                                               target_dev, p->B, p->T, fd);
     DGC_LAUNCHED(ctx, "mss_fwd");
   }
   // weights: (w / nscales) with nscales = number of usable windows, normalize:true divides by T

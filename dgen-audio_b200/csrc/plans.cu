@@ -35,7 +35,121 @@ int32_t ensure_stage(dgc_ctx *ctx, uint64_t nfloats) {
   return DGC_OK;
 }
 
+__global__ void add2_kernel(const float *__restrict__ a, const float *__restrict__ b, size_t n, float *__restrict__ out) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) out[i] = __fadd_rn(a[i], b[i]);
+}
+
 }  // namespace
+
+DGC_EXPORT uint64_t dgc_hn_forward_loss_work_floats(const dgc_hn_step *s) {
+  if (!s || s->harm.B <= 0 || s->harm.T <= 0 || s->harm.F <= 0) return 0;
+  const uint64_t nBT = ((uint64_t)s->harm.B * s->harm.T + 63) & ~63ull;
+  const uint64_t taps = (s->fir.taps > 0 && s->nbands > 0) ? (((uint64_t)s->harm.F * s->harm.B * s->fir.taps + 63) & ~63ull) : 0;
+  return 2 * nBT + taps + 64;
+}
+
+// Device-resident forward + loss.  The harmonic branch (track, chunk sums, scan, render) and the noise branch
+// (band -> tap map, FIR) share no data until the loss, so they run on two streams: the small or latency-bound
+// kernels of one chain (the 64-block phase scan, the band -> tap matmul) and the last waves of the big ones fill
+// under the other chain's work.  The loss reads the prediction as the sum of the two branch outputs.
+// ev_noise_inputs / ev_target (optional): events after which the noise-branch inputs / the target are in device
+// memory (the host-buffer variant uploads them on its own stream while the first kernels already run)
+static int32_t hn_forward_loss_impl(dgc_ctx *ctx, const dgc_hn_step *s, const float *f0_dev, const float *uv_dev,
+                                    const float *amps_dev, const float *gain_dev, const float *noise_gain_dev,
+                                    const float *taps_or_bands_dev, const float *w_dev, const float *noise_dev,
+                                    const float *target_dev, float *work_dev, double *loss_dev, float *audio_dev,
+                                    cudaEvent_t ev_noise_inputs, cudaEvent_t ev_target) {
+  if (!ctx) return DGC_ERR_INVALID;
+  DGC_REQUIRE(ctx, s && f0_dev && uv_dev && amps_dev && gain_dev && target_dev && loss_dev && work_dev, "null pointer");
+  const int B = s->harm.B, T = s->harm.T, K = s->harm.K, F = s->harm.F;
+  DGC_REQUIRE(ctx, B > 0 && T > 0 && K > 0 && F > 0, "size out of range");
+  const int NT = s->fir.taps, NB = s->nbands;
+  const bool noise = NT > 0;
+  if (noise) {
+    DGC_REQUIRE(ctx, noise_gain_dev && taps_or_bands_dev && noise_dev, "noise branch needs its inputs");
+    DGC_REQUIRE(ctx, s->fir.B == B && s->fir.T == T && s->fir.F == F, "fir shape differs from harmonic shape");
+    DGC_REQUIRE(ctx, NB == 0 || w_dev, "band synthesis needs the matrix W");
+  }
+  DGC_REQUIRE(ctx, s->mss.B == B && s->mss.T == T, "loss shape differs from harmonic shape");
+  DGC_REQUIRE(ctx, (((uintptr_t)work_dev) & 15) == 0, "work buffer must be 16-byte aligned");
+  const uint64_t nBT = (uint64_t)B * T, nFB = (uint64_t)F * B;
+  Carver wc(work_dev);
+  float *d_harm = wc.take(nBT), *d_noise = noise ? wc.take(nBT) : nullptr;
+  float *d_taps = (noise && NB > 0) ? wc.take(nFB * NT) : const_cast<float *>(taps_or_bands_dev);
+  // Size the context scratch for the largest user BEFORE the streams fork: growing it later would free a buffer
+  // the other stream may still be reading.
+  {
+    uint64_t need = dgc_harmonic_scratch_floats(&s->harm), m = dgc_mss_partial_floats(&s->mss) + 4;
+    if (m > need) need = m;
+    if (!dgc_ctx_scratch(ctx, need)) return DGC_ERR_OOM;
+  }
+  if (!ctx->aux_stream) {
+    DGC_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->aux_stream, cudaStreamNonBlocking));
+    DGC_CUDA(ctx, cudaEventCreateWithFlags(&ctx->fork_ev, cudaEventDisableTiming));
+    DGC_CUDA(ctx, cudaEventCreateWithFlags(&ctx->join_ev, cudaEventDisableTiming));
+  }
+  // tables cached per (F, T) are built on first use by a kernel on the current stream: make sure they exist
+  // before the streams fork, so that neither branch picks up a table the other one is still writing
+  if (!dgc_ctx_row_table(ctx, F, T)) return DGC_ERR_CUDA;
+  int32_t rc = DGC_OK;
+  cudaStream_t main_stream = ctx->stream;
+  bool forked = false;
+  if (noise) {
+    // fork: the noise branch starts where the caller's stream stands now
+    DGC_CUDA(ctx, cudaEventRecord(ctx->fork_ev, main_stream));
+    DGC_CUDA(ctx, cudaStreamWaitEvent(ctx->aux_stream, ctx->fork_ev, 0));
+    if (ev_noise_inputs) DGC_CUDA(ctx, cudaStreamWaitEvent(ctx->aux_stream, ev_noise_inputs, 0));
+    forked = true;
+    ctx->stream = ctx->aux_stream;
+    if (NB > 0) rc = dgc_bands_to_taps(ctx, taps_or_bands_dev, w_dev, (int32_t)nFB, NB, NT, d_taps);
+    if (rc == DGC_OK) {
+      dgc_fir_params fp = s->fir;
+      fp.accumulate = 0;
+      rc = dgc_fir_noise(ctx, &fp, noise_dev, d_taps, noise_gain_dev, d_noise);
+    }
+    cudaError_t e = cudaEventRecord(ctx->join_ev, ctx->aux_stream);
+    ctx->stream = main_stream;
+    if (rc == DGC_OK && e != cudaSuccess) rc = dgc_fail(ctx, DGC_ERR_CUDA, "event record: %s", cudaGetErrorString(e));
+  }
+  // the harmonic branch goes onto the caller's stream BEFORE that stream is told to wait for the noise branch
+  if (rc == DGC_OK) {
+    dgc_harmonic_params hp = s->harm;
+    hp.accumulate = 0;
+    rc = dgc_harmonic_render(ctx, &hp, f0_dev, uv_dev, amps_dev, gain_dev, nullptr, d_harm);
+  }
+  // join, whatever happened above: nothing of this call is left running beside the caller's stream
+  if (forked) cudaStreamWaitEvent(main_stream, ctx->join_ev, 0);
+  if (rc != DGC_OK) return rc;
+  if (ev_target) DGC_CUDA(ctx, cudaStreamWaitEvent(main_stream, ev_target, 0));
+  if (audio_dev) {
+    if (noise) {
+      add2_kernel<<<dgc_div_up((int64_t)nBT, 256), 256, 0, ctx->stream>>>(d_harm, d_noise, nBT, audio_dev);
+      DGC_LAUNCHED(ctx, "add_branches");
+    } else {
+      DGC_CUDA(ctx, cudaMemcpyAsync(audio_dev, d_harm, nBT * sizeof(float), cudaMemcpyDeviceToDevice, ctx->stream));
+    }
+    return dgc_mss_loss_fwd_sum(ctx, &s->mss, audio_dev, nullptr, target_dev, nullptr, loss_dev);
+  }
+  static const bool add_first = [] {
+    const char *e = getenv("DGC_HN_SUM");
+    return e && strcmp(e, "add") == 0;
+  }();
+  if (add_first && noise) {   // experiment switch: sum the branches in place first, then the plain loss kernel
+    add2_kernel<<<dgc_div_up((int64_t)nBT, 256), 256, 0, ctx->stream>>>(d_harm, d_noise, nBT, d_harm);
+    DGC_LAUNCHED(ctx, "add_branches");
+    return dgc_mss_loss_fwd_sum(ctx, &s->mss, d_harm, nullptr, target_dev, nullptr, loss_dev);
+  }
+  return dgc_mss_loss_fwd_sum(ctx, &s->mss, d_harm, d_noise, target_dev, nullptr, loss_dev);
+}
+
+DGC_EXPORT int32_t dgc_hn_forward_loss(dgc_ctx *ctx, const dgc_hn_step *s, const float *f0_dev, const float *uv_dev,
+                                       const float *amps_dev, const float *gain_dev, const float *noise_gain_dev,
+                                       const float *taps_or_bands_dev, const float *w_dev, const float *noise_dev,
+                                       const float *target_dev, float *work_dev, double *loss_dev, float *audio_dev) {
+  return hn_forward_loss_impl(ctx, s, f0_dev, uv_dev, amps_dev, gain_dev, noise_gain_dev, taps_or_bands_dev, w_dev,
+                              noise_dev, target_dev, work_dev, loss_dev, audio_dev, nullptr, nullptr);
+}
 
 DGC_EXPORT int32_t dgc_hn_forward_loss_host(dgc_ctx *ctx, const dgc_hn_step *s, const float *f0_host,
                                             const float *uv_host, const float *amps_host, const float *gain_host,
@@ -59,7 +173,7 @@ DGC_EXPORT int32_t dgc_hn_forward_loss_host(dgc_ctx *ctx, const dgc_hn_step *s, 
   const uint64_t n_w = (noise && NB > 0) ? (uint64_t)NT * NB : 0;
   // host -> device inputs, in one contiguous pinned block
   const uint64_t in_floats = 3 * nFB + nFB * K + (noise ? nFB + n_tab + n_w + nBT : 0) + nBT;
-  const uint64_t dev_extra = nBT /*audio*/ + (noise && NB > 0 ? nFB * NT : 0) + 64 * 16;
+  const uint64_t dev_extra = nBT /*audio*/ + dgc_hn_forward_loss_work_floats(s) + 64 * 16;
   int32_t rc = ensure_stage(ctx, in_floats + dev_extra + 64 * 16);
   if (rc != DGC_OK) return rc;
 
@@ -110,27 +224,15 @@ DGC_EXPORT int32_t dgc_hn_forward_loss_host(dgc_ctx *ctx, const dgc_hn_step *s, 
     cudaStreamSynchronize(ctx->copy_stream);
     return code;
   };
-  float *d_audio = dc.take(nBT);
-  float *d_taps = d_tab;
-  dgc_harmonic_params hp = s->harm;
-  hp.accumulate = 0;
+  // device work area of the two-branch step, and (only when the caller wants the audio back) the summed signal
+  dgc_hn_step st = *s;
+  float *d_work = dc.take(dgc_hn_forward_loss_work_floats(&st));
+  float *d_audio = audio_host ? dc.take(nBT) : nullptr;
+  // the harmonic branch only needs group 0; the noise branch and the loss wait for their own uploads inside
   if (cudaStreamWaitEvent(ctx->stream, ctx->copy_ev[0], 0) != cudaSuccess) return bail(dgc_fail(ctx, DGC_ERR_CUDA, "event wait"));
-  rc = dgc_harmonic_render(ctx, &hp, d_f0, d_uv, d_amps, d_gain, nullptr, d_audio);
-  if (rc != DGC_OK) return bail(rc);
-  if (cudaStreamWaitEvent(ctx->stream, ctx->copy_ev[1], 0) != cudaSuccess) return bail(dgc_fail(ctx, DGC_ERR_CUDA, "event wait"));
-  if (noise && NB > 0) {
-    d_taps = dc.take(nFB * NT);
-    rc = dgc_bands_to_taps(ctx, d_tab, d_w, (int32_t)nFB, NB, NT, d_taps);
-    if (rc != DGC_OK) return bail(rc);
-  }
-  if (noise) {
-    dgc_fir_params fp = s->fir;
-    fp.accumulate = 1;
-    rc = dgc_fir_noise(ctx, &fp, d_noise, d_taps, d_ng, d_audio);
-    if (rc != DGC_OK) return bail(rc);
-  }
-  if (cudaStreamWaitEvent(ctx->stream, ctx->copy_ev[2], 0) != cudaSuccess) return bail(dgc_fail(ctx, DGC_ERR_CUDA, "event wait"));
-  rc = dgc_mss_loss_fwd(ctx, &s->mss, d_audio, d_target, nullptr, ctx->loss_accum);
+  rc = hn_forward_loss_impl(ctx, &st, d_f0, d_uv, d_amps, d_gain, d_ng, d_tab, d_w, d_noise, d_target, d_work,
+                            ctx->loss_accum, d_audio, inline_upload ? nullptr : ctx->copy_ev[1],
+                            inline_upload ? nullptr : ctx->copy_ev[2]);
   if (rc != DGC_OK) return bail(rc);
   DGC_CUDA(ctx, cudaMemcpyAsync(loss_host, ctx->loss_accum, sizeof(double), cudaMemcpyDeviceToHost, ctx->stream));
   if (audio_host)

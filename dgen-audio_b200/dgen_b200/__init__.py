@@ -145,6 +145,8 @@ SIGNATURES = {
     "dgc_harmonic_f0_bwd_scratch_floats": (_u64, [C.POINTER(HarmonicParams)]),
     "dgc_harmonic_f0_bwd": (_i32, [_vp, C.POINTER(HarmonicParams), _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "dgc_temporal_grad_scan": (_i32, [_vp, _vp, _i32, _i32, _f, _vp]),
+    "dgc_hn_forward_loss_work_floats": (_u64, [C.POINTER(HnStep)]),
+    "dgc_hn_forward_loss": (_i32, [_vp, C.POINTER(HnStep)] + [_vp] * 9 + [_vp, _vp, _vp]),
     "dgc_hn_forward_loss_host": (_i32, [_vp, C.POINTER(HnStep)] + [_vp] * 9 + [C.POINTER(C.c_double), _vp]),
 }
 
@@ -492,6 +494,19 @@ class Context:
         return buf
 
     # ---- composite, host buffers --------------------------------------------------------------
+    def hn_forward_loss(self, step, f0, uv, amps, gain, noise_gain, taps_or_bands, w, noise, target, work=None,
+                        loss=None, audio=None):
+        """Device-resident forward + loss (dgc_hn_forward_loss); returns (loss tensor [1] float64, work buffer)."""
+        torch = self.torch
+        if work is None:
+            work = self._empty(int(self.lib.dgc_hn_forward_loss_work_floats(C.byref(step))))
+        if loss is None:
+            loss = torch.zeros(1, dtype=torch.float64, device=f0.device)
+        self.check(self.lib.dgc_hn_forward_loss(self.h, C.byref(step), _ptr(f0), _ptr(uv), _ptr(amps), _ptr(gain),
+                                                _ptr(noise_gain), _ptr(taps_or_bands), _ptr(w), _ptr(noise),
+                                                _ptr(target), _ptr(work), _ptr(loss), _ptr(audio)))
+        return loss, work
+
     def hn_forward_loss_host(self, step, f0, uv, amps, gain, noise_gain, taps_or_bands, w, noise, target,
                              audio_out=None):
         """All array arguments are host numpy float32 arrays or pinned CPU torch tensors."""

@@ -372,6 +372,18 @@ typedef struct dgc_hn_step {
   int32_t nbands;          /* > 0: taps are synthesised from bands_host [F][B][nbands] with w_host [taps][nbands] */
 } dgc_hn_step;
 
+/* Harmonic+noise synthesis forward + multi-scale spectral loss with every buffer in device memory: what a host
+ * that keeps its tensors resident calls once per batch.  The harmonic and the noise branch run concurrently on
+ * two streams and meet at the loss; the caller's stream (the context stream) is joined before the call returns,
+ * so the usual stream order holds for whatever the caller enqueues next.  work_dev: scratch of
+ * dgc_hn_forward_loss_work_floats(s) floats, 16-byte aligned.  audio_dev (optional) receives the summed signal.
+ * replaces: one realize() of the HarmonicE2E forward graph on resident tensors. */
+uint64_t dgc_hn_forward_loss_work_floats(const dgc_hn_step *s);
+int32_t dgc_hn_forward_loss(dgc_ctx *ctx, const dgc_hn_step *s, const float *f0_dev, const float *uv_dev,
+                            const float *amps_dev, const float *gain_dev, const float *noise_gain_dev,
+                            const float *taps_or_bands_dev, const float *w_dev, const float *noise_dev,
+                            const float *target_dev, float *work_dev, double *loss_dev, float *audio_dev);
+
 /* Harmonic+noise synthesis forward + multi-scale spectral loss, inputs and result in host memory:
  * uploads the control tables, noise and target, renders, evaluates the loss and returns it.
  * audio_host may be NULL.  replaces: one realize() of the HarmonicE2E forward graph. */

@@ -117,3 +117,31 @@ def test_bad_arguments_return_errors(ctx):
         ctx.osc_bank_const(torch.zeros(1, device="cuda"), torch.zeros(1, device="cuda"), 0, 44100.0)
     with pytest.raises(dgen_b200.DgenCudaError):
         ctx.clock_accum(1.0, 1.0, 1.0, 16)
+
+
+def test_device_resident_composite_equals_the_staged_calls(ctx):
+    """dgc_hn_forward_loss (two branches on two streams, joined at the loss) against the same step made of the
+    single entry points on one stream: identical loss, identical audio."""
+    import ctypes as C
+    import torch
+    B, T, K, F, NB, NT = 3, 9000, 40, 70, 9, 33
+    d = wl.harmonic_noise_inputs(61, B=B, T=T, K=K, F=F, nbands=NB, taps=NT)
+    D = {k: dev(v) for k, v in d.items() if isinstance(v, np.ndarray)}
+    target = dev(np.random.default_rng(2).standard_normal((B, T)).astype(f32) * f32(0.1))
+    audio = ctx.harmonic_render(D["f0"], D["uv"], D["amps"], D["gain"], T, d["sr"])
+    ctx.fir_noise(D["noise"], ctx.bands_to_taps(D["bands"], D["W"]), D["noise_gain"], out=audio, accumulate=True)
+    want = float(ctx.mss_loss_fwd(audio, target, sizes=(512, 128, 64)).cpu()[0])
+    st = dgen_b200.HnStep()
+    st.harm = dgen_b200.HarmonicParams(B, T, K, F, d["sr"], 1.0, dgen_b200.PHASE_SCAN, 0)
+    st.fir = dgen_b200.FirParams(B, T, F, NT, 0.12, 1)
+    st.mss = dgen_b200.mss_params(B, T, (512, 128, 64))
+    st.nbands = NB
+    for want_audio in (False, True):
+        out = torch.empty(B, T, device="cuda") if want_audio else None
+        for _ in range(3):          # repeated calls reuse the side stream and events
+            loss, _ = ctx.hn_forward_loss(st, D["f0"], D["uv"], D["amps"], D["gain"], D["noise_gain"], D["bands"], D["W"],
+                                          D["noise"], target, audio=out)
+        ctx.sync()
+        assert float(loss.cpu()[0]) == want
+        if want_audio:
+            assert torch.equal(out, audio)
