@@ -838,3 +838,13 @@ DGC_EXPORT int32_t dgc_harmonic_f0_bwd(dgc_ctx *ctx, const dgc_harmonic_params *
   DGC_LAUNCHED(ctx, "f0_rows_grad");
   return DGC_OK;
 }
+
+DGC_EXPORT int32_t dgc_ctx_prepare_tables(dgc_ctx *ctx, int32_t F, int32_t T) {
+  if (!ctx) return DGC_ERR_INVALID;
+  DGC_REQUIRE(ctx, F > 0 && T > 0, "F and T must be positive");
+  if (!dgc_ctx_row_table(ctx, F, T)) return DGC_ERR_CUDA;      // builds the playhead as well
+  dgc_ctx_row_ranges(ctx, F, T);   // only the backward kernels need the ranges: a clock they cannot handle is
+                                   // reported by them, not here
+  DGC_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return DGC_OK;
+}

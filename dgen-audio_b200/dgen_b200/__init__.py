@@ -131,6 +131,7 @@ SIGNATURES = {
     "dgc_linear_bwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp]),
     "dgc_adam_step": (_i32, [_vp, _vp, _vp, _vp, _vp, _u64, _i32, _f, _f, _f, _f]),
     "dgc_sanitize": (_i32, [_vp, _vp, _u64, _vp]),
+    "dgc_ctx_prepare_tables": (_i32, [_vp, _i32, _i32]),
     "dgc_module_load": (_i32, [_vp, _vp, _u64, C.POINTER(_vp)]),
     "dgc_module_compile": (_i32, [_vp, C.c_char_p, C.c_char_p, C.POINTER(_vp)]),
     "dgc_module_unload": (_i32, [_vp]),
@@ -234,6 +235,20 @@ class Context:
         self.h = h
         if use_torch_stream:
             self.check(self.lib.dgc_ctx_set_stream(self.h, torch.cuda.current_stream(device).cuda_stream, 1))
+
+    def on_stream(self, stream):
+        """Context manager: library calls inside run on `stream` (a torch.cuda.Stream); the binding to torch's
+        current stream is restored on exit."""
+        import contextlib
+
+        @contextlib.contextmanager
+        def scope():
+            self.check(self.lib.dgc_ctx_set_stream(self.h, stream.cuda_stream, 1))
+            try:
+                yield
+            finally:
+                self.check(self.lib.dgc_ctx_set_stream(self.h, self.torch.cuda.current_stream(self.device).cuda_stream, 1))
+        return scope()
 
     def close(self):
         if getattr(self, "h", None):

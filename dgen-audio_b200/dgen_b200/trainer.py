@@ -63,6 +63,11 @@ class HarmonicModel:
         hp0 = HarmonicParams(B, T, K, F, sr, 1.0, phase_mode, 0)
         self.h_scratch = f(int(ctx.lib.dgc_harmonic_bwd_scratch_floats(C.byref(hp0))) + 64)
         self.h_prepared = None
+        self.side = torch.cuda.Stream(device=dev)        # second stream for the noise branch
+        self.noise_out = f(B, T)
+        # the per-(F, T) clock tables are built on first use by a kernel on the then-current stream: build them
+        # now, so that the two concurrent branches of the first step both find them complete
+        ctx.check(ctx.lib.dgc_ctx_prepare_tables(ctx.h, F, T))
         self.dact = [f(M, H), f(M, H), f(M, H)]          # gradient w.r.t. a layer's input
         self.dz = [f(M, H), f(M, H), f(M, H), f(M, K + nbands)]
         self.head_dz = f(M, K + nbands)
@@ -94,16 +99,23 @@ class HarmonicModel:
             a = self.act[i]
         c.check(lib.dgc_hn_heads_fwd(h, self.act[3].data_ptr(), self.M, self.K, self.nbands, self.amps.data_ptr(),
                                      self.bands.data_ptr()))
-        c.check(lib.dgc_bands_to_taps(h, self.bands.data_ptr(), w_fs.data_ptr(), self.M, self.nbands, self.taps,
-                                      self.taps_tab.data_ptr()))
+        # the noise branch (band -> tap map, FIR) shares nothing with the harmonic branch until the two are
+        # summed: it runs on a side stream beside it
+        cur = self.torch.cuda.current_stream()
+        self.side.wait_stream(cur)
+        with c.on_stream(self.side):
+            c.check(lib.dgc_bands_to_taps(h, self.bands.data_ptr(), w_fs.data_ptr(), self.M, self.nbands, self.taps,
+                                          self.taps_tab.data_ptr()))
+            fp = FirParams(self.B, self.T, self.F, self.taps, 0.12, 0)
+            c.check(lib.dgc_fir_noise(h, C.byref(fp), noise.data_ptr(), self.taps_tab.data_ptr(),
+                                      noise_gain.data_ptr(), self.noise_out.data_ptr()))
         hp = HarmonicParams(self.B, self.T, self.K, self.F, self.sr, 1.0, self.phase_mode, 0)
         # the render's per-sample tracks and phase anchors stay in this scratch for the backward pass
         c.check(lib.dgc_harmonic_render(h, C.byref(hp), f0.data_ptr(), uv.data_ptr(), self.amps.data_ptr(),
                                         gain.data_ptr(), self.h_scratch.data_ptr(), self.dry.data_ptr()))
         self.h_prepared = (f0.data_ptr(), uv.data_ptr(), gain.data_ptr())
-        fp = FirParams(self.B, self.T, self.F, self.taps, 0.12, 1)
-        c.check(lib.dgc_fir_noise(h, C.byref(fp), noise.data_ptr(), self.taps_tab.data_ptr(), noise_gain.data_ptr(),
-                                  self.dry.data_ptr()))
+        cur.wait_stream(self.side)
+        self.torch.add(self.dry, self.noise_out, out=self.dry)
         self.out.copy_(self.dry)
         ir = self.view("ir")
         c.check(lib.dgc_partconv(h, self.dry.data_ptr(), self.B, self.T, ir.data_ptr(), self.ir_len, self.conv_n,
@@ -127,15 +139,21 @@ class HarmonicModel:
         bwd = lib.dgc_harmonic_render_bwd_prepared \
             if getattr(self, "h_prepared", None) == (f0.data_ptr(), uv.data_ptr(), gain.data_ptr()) \
             else lib.dgc_harmonic_render_bwd
+        # the two synthesis branches again side by side: noise-branch gradients on the side stream (the context
+        # scratch they use is not touched by the harmonic backward, which works in the model's own scratch)
+        cur = self.torch.cuda.current_stream()
+        self.side.wait_stream(cur)
+        with c.on_stream(self.side):
+            fp = FirParams(self.B, self.T, self.F, self.taps, 0.12, 0)
+            c.check(lib.dgc_fir_noise_bwd(h, C.byref(fp), noise.data_ptr(), noise_gain.data_ptr(),
+                                          self.g_out.data_ptr(), self.g_taps.data_ptr()))
+            # g_bands = g_taps Wfs   ([M, taps] x [taps, nbands])
+            c.check(lib.dgc_linear_fwd(h, self.g_taps.data_ptr(), w_fs.data_ptr(), None, self.M, self.taps,
+                                       self.nbands, 0, self.g_bands.data_ptr(), None))
         c.check(bwd(h, C.byref(hp), f0.data_ptr(), uv.data_ptr(), self.amps.data_ptr(), gain.data_ptr(),
                     self.g_out.data_ptr(), self.h_scratch.data_ptr(), self.g_amps.data_ptr()))
         self.h_prepared = None
-        fp = FirParams(self.B, self.T, self.F, self.taps, 0.12, 0)
-        c.check(lib.dgc_fir_noise_bwd(h, C.byref(fp), noise.data_ptr(), noise_gain.data_ptr(), self.g_out.data_ptr(),
-                                      self.g_taps.data_ptr()))
-        # g_bands = g_taps Wfs   ([M, taps] x [taps, nbands])
-        c.check(lib.dgc_linear_fwd(h, self.g_taps.data_ptr(), w_fs.data_ptr(), None, self.M, self.taps, self.nbands, 0,
-                                   self.g_bands.data_ptr(), None))
+        cur.wait_stream(self.side)
         c.check(lib.dgc_hn_heads_bwd(h, self.act[3].data_ptr(), self.g_amps.data_ptr(), self.g_bands.data_ptr(),
                                      self.M, self.K, self.nbands, self.dz[3].data_ptr()))
         # head layer: dz[3] is the gradient w.r.t. z (no activation); trunk layers: dact[i] is the gradient

@@ -75,6 +75,13 @@ int32_t dgc_arena_zero(dgc_arena *a);                                          /
 int32_t dgc_arena_upload(dgc_arena *a, uint64_t offset, const float *src_host, uint64_t n);   /* injectTensorData */
 int32_t dgc_arena_download(dgc_arena *a, uint64_t offset, float *dst_host, uint64_t n);       /* readOutputs / readGradients */
 
+/* Builds the tables the context caches per (control frames F, frames T) -- the control playhead, the per-frame
+ * control-row positions and the per-row frame ranges -- on the context stream and waits for them.  Every entry
+ * point builds what it needs on first use; a host calls this up front when the first use must not allocate
+ * or synchronise (real-time start-up), or before it drives one context from two streams.
+ * No reference counterpart (the reference recomputes the clock inside every kernel). */
+int32_t dgc_ctx_prepare_tables(dgc_ctx *ctx, int32_t F, int32_t T);
+
 /* ---- scalar clocks ------------------------------------------------------------------------------
  * replaces: scalar `accum` (Sources/DGen/Definitions.swift:215-246): out[n] = state before the
  * n-th update, sequential single-precision semantics (the rounding of every step is part of the
