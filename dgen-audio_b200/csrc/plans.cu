@@ -131,11 +131,13 @@ static int32_t hn_forward_loss_impl(dgc_ctx *ctx, const dgc_hn_step *s, const fl
     }
     return dgc_mss_loss_fwd_sum(ctx, &s->mss, audio_dev, nullptr, target_dev, nullptr, loss_dev);
   }
+  // Sum the branches in place first, then the plain loss kernel: measured 0.349 ms per step against 0.360 ms
+  // with the loss kernel adding the two signals as it loads them (DGC_HN_SUM=fused selects that variant).
   static const bool add_first = [] {
     const char *e = getenv("DGC_HN_SUM");
-    return e && strcmp(e, "add") == 0;
+    return !(e && strcmp(e, "fused") == 0);
   }();
-  if (add_first && noise) {   // experiment switch: sum the branches in place first, then the plain loss kernel
+  if (add_first && noise) {
     add2_kernel<<<dgc_div_up((int64_t)nBT, 256), 256, 0, ctx->stream>>>(d_harm, d_noise, nBT, d_harm);
     DGC_LAUNCHED(ctx, "add_branches");
     return dgc_mss_loss_fwd_sum(ctx, &s->mss, d_harm, nullptr, target_dev, nullptr, loss_dev);
