@@ -124,12 +124,26 @@ int32_t launch_sgemm(dgc_ctx *ctx, const float *A, const float *B, const float *
                      float *Ct = nullptr, bool *ct_written = nullptr) {
   if (ct_written) *ct_written = false;
   const bool tc = use_tensor_cores() && (double)M * N * K >= (double)(1 << 21) && K >= 32;
-  const int bm = tc ? dgtc::TBM : BM, bn = tc ? dgtc::TBN : BN;
+  static const int kk_bk = [] {   // DGC_GEMM_KK: 0 off; 16 (default) / 32: swizzled 16- / 32-wide k tiles; 17 / 33: the
+                                  // same without swizzle; 256: 16-wide k tiles with 128 x 256 output tiles where N >= 256
+    const char *e = getenv("DGC_GEMM_KK");
+    return e ? atoi(e) : 16;
+  }();
+  // the asynchronous pipeline needs both operands contiguous along k, K a multiple of 4 and aligned rows
+  const bool kk = tc && !TA && TB && kk_bk && (K & 3) == 0 && ((((uintptr_t)A) | ((uintptr_t)B)) & 15) == 0;
+  // 128 x 256 tiles, one CTA per SM: 25 % less shared-memory traffic per flop, but prologue and epilogue are no
+  // longer hidden by a second resident CTA, so they only pay where a CTA runs a long reduction -- the split-K
+  // weight gradients (measured: training step 3.84 -> 3.78 ms; the forward layers get 4 % slower with them).
+  // DGC_GEMM_KK=256 forces them wherever N >= 256.
+  const bool long_reduction = EPI == 0 && K >= 2048 && dgc_div_up(N, dgtc::TBN) * dgc_div_up(M, dgtc::TBM) < ctx->sm_count;
+  const bool wide = kk && N >= 256 && (kk_bk == 256 || (kk_bk == 16 && long_reduction));
+  const int bm = tc ? dgtc::TBM : BM, bn = wide ? 256 : (tc ? dgtc::TBN : BN);
   const int tiles = dgc_div_up(N, bn) * dgc_div_up(M, bm);
   int splits = 1;
   if (EPI == 0 && tiles < ctx->sm_count && K >= 2048) {
-    // few output tiles and a long reduction (weight gradients): split the reduction over blocks
-    splits = (2 * ctx->sm_count + tiles - 1) / tiles;
+    // few output tiles and a long reduction (weight gradients): split the reduction over blocks -- two resident
+    // CTAs per SM for the narrow tiles, one (and never a second, nearly empty wave) for the wide ones
+    splits = wide ? ctx->sm_count / tiles : (2 * ctx->sm_count + tiles - 1) / tiles;
     if (splits > K / 256) splits = K / 256;
     if (splits < 1) splits = 1;
   }
@@ -142,23 +156,25 @@ int32_t launch_sgemm(dgc_ctx *ctx, const float *A, const float *B, const float *
     if (!dst) return DGC_ERR_OOM;
   }
   dim3 grid(dgc_div_up(N, bn), dgc_div_up(M, bm), splits);
-  static const int kk_bk = [] {   // DGC_GEMM_KK: 0 off; 16 (default) / 32: swizzled 16- / 32-wide k tiles; 17 / 33: the same without swizzle
-    const char *e = getenv("DGC_GEMM_KK");
-    return e ? atoi(e) : 16;
-  }();
-  if (tc && !TA && TB && kk_bk && (K & 3) == 0 && ((((uintptr_t)A) | ((uintptr_t)B)) & 15) == 0 &&
-      (splits == 1 || kps % 32 == 0)) {
+  if (kk && (splits == 1 || kps % 32 == 0)) {
     // both operands contiguous along k: the cp.async pipeline
 #define DGC_KK_LAUNCH(BKV, SWV)                                                                                      \
   do {                                                                                                              \
-    auto kern = dgtc::tc_gemm_kk_kernel<EPI, BKV, SWV>;                                                             \
-    constexpr int SM = dgtc::KK<BKV, SWV>::SMEM;                                                                    \
+    auto kern = dgtc::tc_gemm_kk_kernel<EPI, BKV, SWV, dgtc::TBN>;                                                  \
+    constexpr int SM = dgtc::KK<BKV, SWV, dgtc::TBN>::SMEM;                                                         \
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM);                    \
     if (e != cudaSuccess) return dgc_fail(ctx, DGC_ERR_CUDA, "tc_gemm smem opt-in: %s", cudaGetErrorString(e));     \
     kern<<<grid, dgtc::KK_THREADS, SM, ctx->stream>>>(A, B, bias, M, N, K, kps, dst, splits == 1 ? Ct : nullptr,    \
                                                    ctx->status_dev);                                                \
   } while (0)
-    if (kk_bk == 16) DGC_KK_LAUNCH(16, true);
+    if (wide) {
+      auto kern = dgtc::tc_gemm_kk_kernel<EPI, 16, true, 256>;
+      constexpr int SM = dgtc::KK<16, true, 256>::SMEM;
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM);
+      if (e != cudaSuccess) return dgc_fail(ctx, DGC_ERR_CUDA, "tc_gemm smem opt-in: %s", cudaGetErrorString(e));
+      kern<<<grid, dgtc::KK_THREADS, SM, ctx->stream>>>(A, B, bias, M, N, K, kps, dst, splits == 1 ? Ct : nullptr,
+                                                         ctx->status_dev);
+    } else if (kk_bk == 16 || kk_bk == 256) DGC_KK_LAUNCH(16, true);
     else if (kk_bk == 17) DGC_KK_LAUNCH(16, false);
     else if (kk_bk == 33) DGC_KK_LAUNCH(32, false);
     else DGC_KK_LAUNCH(32, true);

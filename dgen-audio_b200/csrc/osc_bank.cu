@@ -235,16 +235,19 @@ anchor_sum_kernel(const float *__restrict__ f0t, int B, int T, int K, float sr, 
 }
 
 // SCAN anchors, stage 2: exclusive prefix over chunks; the fixed-point phase is rounded to float.
-// Block = 32 time segments (warps) x 32 partials (lanes, coalesced); each warp totals its segment,
-// the segment totals are prefixed through shared memory, then each warp walks its segment again.
-__global__ void __launch_bounds__(1024)
+// Block = SCAN_SEGS time segments x SCAN_KK partials (8 partials = one 64-byte run of the 64-bit sums per
+// segment); each thread totals its segment, the segment totals are prefixed through shared memory, then each
+// thread walks its segment again.  Many short segments keep every thread's serial walk to a few chunks and give
+// enough blocks (ceil(K / 8) x B) to occupy the whole GPU.
+constexpr int SCAN_KK = 8, SCAN_SEGS = 128;
+__global__ void __launch_bounds__(SCAN_KK * SCAN_SEGS)
 anchor_scan_kernel(const unsigned long long *__restrict__ sums, int B, int C, int K,
                    float *__restrict__ anchors, uint32_t *__restrict__ anchors_q) {
-  __shared__ unsigned long long seg_tot[32][33];
-  const int kk = threadIdx.x & 31, seg = threadIdx.x >> 5;
-  const int k = blockIdx.x * 32 + kk, b = blockIdx.y;
+  __shared__ unsigned long long seg_tot[SCAN_SEGS][SCAN_KK + 1];
+  const int kk = threadIdx.x % SCAN_KK, seg = threadIdx.x / SCAN_KK;
+  const int k = blockIdx.x * SCAN_KK + kk, b = blockIdx.y;
   const bool ok = k < K;
-  const int per = (C + 31) / 32;
+  const int per = (C + SCAN_SEGS - 1) / SCAN_SEGS;
   const int c0 = min(C, seg * per), c1 = min(C, c0 + per);
   const unsigned long long *s = sums + (size_t)b * C * K + k;
   float *out = anchors + (size_t)b * C * K + k;
@@ -747,7 +750,7 @@ int32_t dgc_harmonic_prepare(dgc_ctx *ctx, const dgc_harmonic_params *p, const f
   } else {
     launch_anchor_sum(ctx, B, T, K, C, f0t, sr, rsr, sums);
     DGC_LAUNCHED(ctx, "anchor_sum");
-    anchor_scan_kernel<<<dim3(dgc_div_up(K, 32), B), 1024, 0, ctx->stream>>>(sums, B, C, K, anchors,
+    anchor_scan_kernel<<<dim3(dgc_div_up(K, SCAN_KK), B), SCAN_KK * SCAN_SEGS, 0, ctx->stream>>>(sums, B, C, K, anchors,
                                                                              extra ? anchors_q : nullptr);
     DGC_LAUNCHED(ctx, "anchor_scan");
   }

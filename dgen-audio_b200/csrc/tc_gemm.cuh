@@ -48,10 +48,10 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {
 
 // instruction descriptor: D = F32 (1 << 4), A = B = TF32 (2 << 7, 2 << 10), A / B major (0 = K, 1 = MN) at
 // bits 15 / 16, N >> 3 at 17, M >> 4 at 24
-template <bool A_KMAJOR, bool B_KMAJOR>
+template <bool A_KMAJOR, bool B_KMAJOR, int BN = TBN>
 struct IDesc {
   static constexpr uint32_t value = (1u << 4) | (2u << 7) | (2u << 10) | (A_KMAJOR ? 0u : (1u << 15)) |
-                                    (B_KMAJOR ? 0u : (1u << 16)) | ((uint32_t)(TBN >> 3) << 17) |
+                                    (B_KMAJOR ? 0u : (1u << 16)) | ((uint32_t)(BN >> 3) << 17) |
                                     ((uint32_t)(TBM >> 4) << 24);
 };
 
@@ -188,16 +188,16 @@ constexpr int EPI_STAGE_FLOATS = 32 * 33;   // per warp: a 32 x 32 block, rows p
 // now) and writes full 128-byte row segments.  EPI 0: C = acc ; 1: + bias[n] ; 2: tanh(acc + bias[n]).
 // Ct (optional): a second, transposed copy Ct[n][m] of the result, written straight from the registers
 // (lanes = consecutive m: already 128-byte stores).
-template <int EPI>
+template <int EPI, int BN = TBN>
 __device__ __forceinline__ void epilogue(uint32_t tmem_d, const float *__restrict__ bias, int M, int N, int m0, int n0,
                                          float *__restrict__ C, int warp, int lane, float *__restrict__ Ct,
                                          float *__restrict__ stage_all) {
-  const int lane_base = (warp & 3) * 32, col_base = (warp >> 2) * (TBN / 2);
+  const int lane_base = (warp & 3) * 32, col_base = (warp >> 2) * (BN / 2);
   const int gm = m0 + lane_base + lane;
   float *stage = stage_all + warp * EPI_STAGE_FLOATS;
   const bool aligned = ((N & 3) == 0) && ((((uintptr_t)C) & 15) == 0);
 #pragma unroll 1
-  for (int c0 = col_base; c0 < col_base + TBN / 2; c0 += 32) {
+  for (int c0 = col_base; c0 < col_base + BN / 2; c0 += 32) {
     uint32_t r[32];
     const uint32_t taddr = tmem_d + ((uint32_t)lane_base << 16) + (uint32_t)c0;
     asm volatile(
@@ -358,13 +358,18 @@ tc_gemm_kernel(const float *__restrict__ A, const float *__restrict__ B, const f
 // With BK = 16 a row is 64 bytes and the 64-byte swizzle applies (8-row groups of 512 bytes, chunk c of row r at
 // c ^ ((r / 2) % 4)); that variant needs 97 KB per CTA, so two CTAs share an SM and one's epilogue runs under
 // the other's main loop.
-template <int BK, bool SW = false>
+// BN = 256 (swizzled layouts only): a 128 x 256 output tile per CTA.  Per flop the three MMAs of a k step then
+// fetch 25 % fewer operand bytes (A is shared by twice as many columns) and the copy / split traffic drops by
+// the same factor, which is what the kernel is bound by; 145 KB of shared memory, one CTA per SM.
+template <int BK, bool SW = false, int BN = TBN>
 struct KK {
+  static_assert(BN == TBN || SW, "the wide tile uses the swizzled layouts");
   static constexpr int CHUNKS_K = BK / 4;
   static constexpr int ROW_BYTES = BK * 4;                                  // 128 or 64
-  static constexpr int OPER = SW ? TBM * ROW_BYTES : CHUNKS_K * LBO_BYTES;  // one operand of one tile
+  static constexpr int OPER = SW ? TBM * ROW_BYTES : CHUNKS_K * LBO_BYTES;  // operand A of one tile
+  static constexpr int OPER_B = SW ? BN * ROW_BYTES : CHUNKS_K * LBO_BYTES; // operand B of one tile
   static constexpr int RAW = 4, PF = 2;
-  static constexpr int RAW_STAGE = 2 * OPER;              // A, B
+  static constexpr int RAW_STAGE = OPER + OPER_B;         // A, B
   static constexpr int SMEM = (RAW + 2) * RAW_STAGE + 128 + (SW ? 1024 : 0);   // + room to align to 1024
   // byte offset of 16-byte chunk kc of row r inside one operand
   __device__ static __forceinline__ int unit_offset(int r, int kc) {
@@ -372,7 +377,7 @@ struct KK {
     return BK == 32 ? (r >> 3) * 1024 + (r & 7) * 128 + ((kc ^ (r & 7)) << 4)
                     : (r >> 3) * 512 + (r & 7) * 64 + ((kc ^ ((r >> 1) & 3)) << 4);
   }
-  static constexpr int UNITS = 2 * TBM * CHUNKS_K;        // 16-byte units per tile (A and B)
+  static constexpr int UNITS = (TBM + BN) * CHUNKS_K;     // 16-byte units per tile (A and B)
 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, int src_bytes) {
@@ -406,11 +411,11 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
-template <int EPI, int BK, bool SW>
-__global__ void __launch_bounds__(KK_THREADS, BK == 16 ? 2 : 1)
+template <int EPI, int BK, bool SW, int BN = TBN>
+__global__ void __launch_bounds__(KK_THREADS, (BK == 16 && BN == TBN) ? 2 : 1)
 tc_gemm_kk_kernel(const float *__restrict__ A, const float *__restrict__ B, const float *__restrict__ bias, int M, int N,
                   int K, int k_per_split, float *__restrict__ C, float *__restrict__ Ct, int32_t *status) {
-  using G = KK<BK, SW>;
+  using G = KK<BK, SW, BN>;
   KK_STAMP(0);
   extern __shared__ __align__(128) char smem_base[];
   // the swizzle pattern is a function of the address: tiles start on 1024-byte boundaries
@@ -420,7 +425,7 @@ tc_gemm_kk_kernel(const float *__restrict__ A, const float *__restrict__ B, cons
   uint64_t *ready = bars + G::RAW;                                                    // 2 "lo buffer written" mbarriers
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + (G::RAW + 2) * G::RAW_STAGE + 64);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int m0 = blockIdx.y * TBM, n0 = blockIdx.x * TBN;
+  const int m0 = blockIdx.y * TBM, n0 = blockIdx.x * BN;
   const int k_begin = blockIdx.z * k_per_split, k_end = min(K, k_begin + k_per_split);
   C += (size_t)blockIdx.z * M * N;
   const int KT = (k_end - k_begin + BK - 1) / BK;
@@ -434,7 +439,7 @@ tc_gemm_kk_kernel(const float *__restrict__ A, const float *__restrict__ B, cons
   }
   if (warp == 0) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
-                 "r"((uint32_t)TBN)
+                 "r"((uint32_t)BN)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -462,7 +467,7 @@ tc_gemm_kk_kernel(const float *__restrict__ A, const float *__restrict__ B, cons
 #pragma unroll
     for (int i = 0; i < UPT; ++i) {
       const int u = tid + THREADS * i;
-      const int op = u / (TBM * G::CHUNKS_K), rem = u % (TBM * G::CHUNKS_K);
+      const int op = u >= TBM * G::CHUNKS_K, rem = u - op * (TBM * G::CHUNKS_K);   // A units first, then B
       const int r = rem / G::CHUNKS_K, kc = rem % G::CHUNKS_K;
       const int rows = op ? N : M, gr = (op ? n0 : m0) + r;
       rowok[i] = gr < rows;
@@ -507,7 +512,7 @@ tc_gemm_kk_kernel(const float *__restrict__ A, const float *__restrict__ B, cons
     asm volatile("cp.async.wait_group 0;" ::: "memory");
   } else if (lane == 0) {
     // ---- MMA issue: one thread, nothing else to do ----------------------------------------------------------
-    constexpr uint32_t ID = IDesc<true, true>::value;
+    constexpr uint32_t ID = IDesc<true, true, BN>::value;
     for (int kt = 0; kt < KT; ++kt) {
       if (*failed || !mbar_wait(smem_u32(&ready[kt & 1]), (uint32_t)((kt >> 1) & 1))) {
         *failed = 1;
@@ -543,19 +548,19 @@ tc_gemm_kk_kernel(const float *__restrict__ A, const float *__restrict__ B, cons
   KK_STAMP(5);
 
   if (ok && KT > 0) {
-    if (warp < THREADS / 32) epilogue<EPI>(tmem_d, bias, M, N, m0, n0, C, warp, lane, Ct, reinterpret_cast<float *>(smem));
+    if (warp < THREADS / 32) epilogue<EPI, BN>(tmem_d, bias, M, N, m0, n0, C, warp, lane, Ct, reinterpret_cast<float *>(smem));
     KK_STAMP(6);
   } else if (KT == 0) {
     const int gm = m0 + (warp & 3) * 32 + lane;
     if (gm < M && warp < 4)
-      for (int c = 0; c < TBN; ++c)
+      for (int c = 0; c < BN; ++c)
         if (n0 + c < N) C[(size_t)gm * N + n0 + c] = 0.0f;
   }
   if (!ok && tid == 0) atomicExch(status, 201);
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (warp == 0) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"((uint32_t)TBN) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"((uint32_t)BN) : "memory");
   }
 }
 
