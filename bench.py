@@ -339,7 +339,7 @@ def run_ours(args, rank, world, local_rank):
                 "roofline": {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "GB/s",
                              "frac": achieved / peak, "traffic": traffic,
                              "peak_source": "measured" if peaks else "fallback",
-                             "note": "the stage is FP32/SFU-issue bound, not HBM bound; see DESIGN.md",
+                             "note": "the stage is FP32/SFU-issue bound, not HBM bound; see roofline.sfu",
                              # the bound that does apply to the oscillator bank: one sine per (voice, frame,
                              # harmonic) on the 16 SFU lanes of each SM at the sampled SM clock
                              "sfu": sfu},

@@ -1,7 +1,7 @@
 #!/bin/sh
 # Compiles the reference's own generated C artefacts from where they lie in the reference tree
 # into oracle/_ref/ (git-ignored outputs only; no reference source is copied into this repo).
-#   usage: oracle/build_ref.sh [REFERENCE_ROOT]        (default /root/reference)
+#   usage: oracle/build_ref.sh [REFERENCE_ROOT]        (default: the location set in REF below)
 # The reference runtime header is written for AArch64; the single ARM-only inline-asm register
 # constraint ("+w", a NEON register) is rewritten to the x86 vector-register constraint ("+x")
 # in a generated copy under _ref/include, and <arm_neon.h> resolves to oracle/neon_shim.

@@ -1,7 +1,7 @@
 """Regenerates tests/golden/ref_artefacts.npz from the reference's own generated C artefacts.
 
 Run in a container that has the reference tree:
-    sh oracle/build_ref.sh /root/reference && python tests/golden/make_golden.py
+    sh oracle/build_ref.sh <reference checkout> && python tests/golden/make_golden.py
 It executes oracle/_ref/*.so (the reference's toolchain/generated/hermetic/*.c, compiled as they
 lie) with the memory initialisation, process context (48 kHz) and input signal of the reference's
 harness (toolchain/harness/toolchain_harness.c:153-181, 270-278) and stores the outputs, so the
