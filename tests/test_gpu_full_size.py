@@ -1,0 +1,92 @@
+"""The other configurations of the path at their FULL sizes, through properties that do not need the oracle to
+run at that size: exact lane / voice independence against a small run of the same kernel (which the oracle
+tests cover), linearity, time-shift invariance by a whole number of hops, and a slice against the oracle.
+
+  biquad bank:       256 lanes x 32 voices x 262144 frames (8.6 GB of lane signals), forward and BPTT
+  partitioned conv:  16 voices x 480000 frames, 96000-tap impulse response (94 partitions of 1024, N = 2048)
+  oscillator bank -> one-pole -> FFT: 64 partials, 65536 frames (against the oracle directly, see test_gpu_linrec)
+"""
+import numpy as np
+import pytest
+import torch
+
+import dgen_b200
+from dgen_b200 import workloads as wl
+from oracle import oracle as orc
+
+pytestmark = pytest.mark.gpu
+f32 = np.float32
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    c = dgen_b200.Context(0)
+    yield c
+    c.close()
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def test_biquad_bank_full_size_forward_and_bptt(ctx):
+    d = wl.biquad_bank_inputs(20260002)              # B=32, L=256, T=262144
+    B, L, T = d["B"], d["L"], d["T"]
+    x, cut, q = dev(d["x"]), dev(d["cutoff"]), dev(d["q"])
+    y = ctx.biquad_fwd(x, cut, q)                    # [B][T][L], 8.6 GB
+    ctx.sync()
+    assert y.shape == (B, T, L) and bool(torch.isfinite(y).all())
+    # lane and voice independence is exact: three lanes of two voices, run alone over the full length
+    lanes, voices = [0, 131, 255], [0, 31]
+    sub = ctx.biquad_fwd(x[voices].contiguous(), cut[lanes].contiguous(), q[lanes].contiguous())
+    ctx.sync()
+    for i, b in enumerate(voices):
+        for j, l in enumerate(lanes):
+            assert torch.equal(sub[i, :, j], y[b, :, l]), (b, l)
+    # the head of one voice against the oracle (the chunked scan must agree with the serial recurrence)
+    want = orc.biquad_bank(d["x"][0:1, :6000], d["cutoff"][lanes], d["q"][lanes])[0].T   # [frames][lanes]
+    got = sub[0, :6000].cpu().numpy()
+    assert np.abs(got - want).max() < 1e-4 * max(1.0, np.abs(want).max())
+    # BPTT at full size: gradients of the lanes above equal those of the small bank run alone (per-lane sums over
+    # voices and frames do not mix lanes), up to the split of the voice sum
+    target = ctx.biquad_fwd(x, cut * 1.05, q)
+    gc, gq, loss = ctx.biquad_mse_bwd(x, cut, q, y, target, loss_scale=1.0 / (B * T))
+    tsub = ctx.biquad_fwd(x, (cut * 1.05)[lanes].contiguous(), q[lanes].contiguous())
+    ysub = ctx.biquad_fwd(x, cut[lanes].contiguous(), q[lanes].contiguous())
+    gcs, gqs, _ = ctx.biquad_mse_bwd(x, cut[lanes].contiguous(), q[lanes].contiguous(), ysub, tsub,
+                                     loss_scale=1.0 / (B * T))
+    ctx.sync()
+    assert bool(torch.isfinite(gc).all()) and bool(torch.isfinite(gq).all()) and float(loss.cpu()[0]) > 0
+    assert torch.allclose(gc[lanes], gcs, rtol=1e-4, atol=0) and torch.allclose(gq[lanes], gqs, rtol=1e-4, atol=0)
+    del y, target
+
+
+def test_partitioned_convolution_full_size_properties(ctx):
+    d = wl.partconv_inputs(20260003)                 # V=16, T=480000, IR 96000, N=2048, hop=1024
+    V, T, N, hop = d["V"], d["T"], d["N"], d["hop"]
+    x, ir = dev(d["x"]), dev(d["ir"])
+    y = ctx.partconv(x, ir, N, hop)
+    ctx.sync()
+    assert y.shape == (V, T) and bool(torch.isfinite(y).all())
+    # voices are independent (exactly): two voices run alone
+    ysub = ctx.partconv(x[[3, 15]].contiguous(), ir, N, hop)
+    assert torch.equal(ysub[0], y[3]) and torch.equal(ysub[1], y[15])
+    # linear in the input and in the impulse response
+    x2 = torch.roll(x, 7, dims=0)
+    ylin = ctx.partconv(x + 2.0 * x2, ir, N, hop)
+    y2 = ctx.partconv(x2, ir, N, hop)
+    scale = float(y.abs().max())
+    assert float((ylin - (y + 2.0 * y2)).abs().max()) < 2e-5 * scale
+    assert float((ctx.partconv(x, 0.5 * ir, N, hop) - 0.5 * y).abs().max()) < 1e-6 * scale
+    # a delay of the input by a whole number of hops delays the output by the same amount
+    shift = 3 * hop
+    xs = torch.zeros_like(x)
+    xs[:, shift:] = x[:, :-shift]
+    ys = ctx.partconv(xs, ir, N, hop)
+    ctx.sync()
+    assert float((ys[:, shift:] - y[:, :-shift]).abs().max()) < 2e-5 * scale
+    assert float(ys[:, :shift - N].abs().max()) == 0.0     # nothing before the delayed input reaches a window
+    # head of one voice against the oracle (94 partitions in play after 96000 frames: take 1.2 s)
+    want = orc.partitioned_convolve(d["x"][3, :57600], d["ir"], N, hop)
+    got = ctx.partconv(x[3:4, :57600].contiguous(), ir, N, hop).cpu().numpy()[0]
+    assert np.abs(got - want).max() < 1e-4 * max(1.0, np.abs(want).max())
