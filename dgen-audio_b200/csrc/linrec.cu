@@ -263,6 +263,58 @@ biquad_fwd_kernel(const float *__restrict__ x, const float *__restrict__ coef, i
   }
 }
 
+// The same sweep with FOUR lanes per thread (L a multiple of 4): four independent recurrences hide the
+// latency of the dependent multiply-adds of one, and the output goes out as one 128-bit store per frame and
+// thread (a warp writes 512 contiguous bytes).  Block = (L/4 lane quads, up to 4 chunks).
+constexpr int BQ4_CHUNKS = 4;
+template <int PHASE>
+__global__ void __launch_bounds__(256)
+biquad_fwd4_kernel(const float *__restrict__ x, const float *__restrict__ coef, int B, int T, int L, int NC,
+                   float *__restrict__ state /* [B][NC][L][2] */, float *__restrict__ y) {
+  __shared__ float xs[BQ4_CHUNKS][BQ_CHUNK + 2];
+  const int lq = blockIdx.x * blockDim.x + threadIdx.x, cy = threadIdx.y;
+  const int c = blockIdx.y * BQ4_CHUNKS + cy, b = blockIdx.z;
+  const bool chunk_ok = c < NC;
+  const float *xb = x + (size_t)b * T;
+  const int n0 = c * BQ_CHUNK, len = chunk_ok ? min(BQ_CHUNK, T - n0) : 0;
+  for (int i = threadIdx.x; i < len + 2; i += blockDim.x) {
+    int t = n0 - 2 + i;
+    xs[cy][i] = t >= 0 ? xb[t] : 0.0f;
+  }
+  __syncthreads();
+  if (!chunk_ok || 4 * lq >= L) return;
+  Coef cf[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) cf[k] = load_coef(coef, 4 * lq + k);
+  float *st = state + (((size_t)b * NC + c) * L + 4 * lq) * 2;
+  float y1[4] = {0.f, 0.f, 0.f, 0.f}, y2[4] = {0.f, 0.f, 0.f, 0.f};
+  if (PHASE == 1) {
+    const float4 s0 = *reinterpret_cast<const float4 *>(st), s1 = *reinterpret_cast<const float4 *>(st + 4);
+    y1[0] = s0.x; y2[0] = s0.y; y1[1] = s0.z; y2[1] = s0.w;
+    y1[2] = s1.x; y2[2] = s1.y; y1[3] = s1.z; y2[3] = s1.w;
+  }
+  float x2 = xs[cy][0], x1 = xs[cy][1];
+  float *yo = y + ((size_t)b * T + n0) * L + 4 * lq;
+#pragma unroll 2
+  for (int n = 0; n < len; ++n) {
+    const float x0 = xs[cy][n + 2];
+    float v[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      v[k] = biquad_step(cf[k], x0, x1, x2, y1[k], y2[k]);
+      y2[k] = y1[k];
+      y1[k] = v[k];
+    }
+    if (PHASE == 1) __stcs(reinterpret_cast<float4 *>(yo + (size_t)n * L), make_float4(v[0], v[1], v[2], v[3]));
+    x2 = x1;
+    x1 = x0;
+  }
+  if (PHASE == 0) {
+    *reinterpret_cast<float4 *>(st) = make_float4(y1[0], y2[0], y1[1], y2[1]);
+    *reinterpret_cast<float4 *>(st + 4) = make_float4(y1[2], y2[2], y1[3], y2[3]);
+  }
+}
+
 // state[c] <- state entering chunk c (exclusive scan of the affine maps), thread per (voice, lane)
 __global__ void biquad_carry_kernel(const double *__restrict__ trans, int B, int L, int NC,
                                     float *__restrict__ state) {
@@ -475,12 +527,18 @@ DGC_EXPORT int32_t dgc_biquad_fwd(dgc_ctx *ctx, const dgc_biquad_params *p, cons
   DGC_LAUNCHED(ctx, "biquad_coef");
   biquad_trans_kernel<<<dgc_div_up(L, 128), 128, 0, ctx->stream>>>(coef, L, BQ_CHUNK, trans);
   DGC_LAUNCHED(ctx, "biquad_trans");
+  // four lanes per thread when the lane count and the output alignment allow 128-bit accesses
+  const bool quad = (L & 3) == 0 && L >= 16 && ((((uintptr_t)y_dev) | ((uintptr_t)state)) & 15) == 0;
+  const int qx = quad ? (L / 4 >= 64 ? 64 : L / 4) : 0;
   dim3 grid(dgc_div_up(L, BQ_THREADS), NC, B);
-  biquad_fwd_kernel<0><<<grid, BQ_THREADS, 0, ctx->stream>>>(x_dev, coef, B, T, L, NC, state, nullptr);
+  dim3 grid4(quad ? dgc_div_up(L / 4, qx) : 1, dgc_div_up(NC, BQ4_CHUNKS), B), block4(quad ? qx : 1, BQ4_CHUNKS);
+  if (quad) biquad_fwd4_kernel<0><<<grid4, block4, 0, ctx->stream>>>(x_dev, coef, B, T, L, NC, state, nullptr);
+  else biquad_fwd_kernel<0><<<grid, BQ_THREADS, 0, ctx->stream>>>(x_dev, coef, B, T, L, NC, state, nullptr);
   DGC_LAUNCHED(ctx, "biquad_fwd_state");
   biquad_carry_kernel<<<dgc_div_up(B * L, 128), 128, 0, ctx->stream>>>(trans, B, L, NC, state);
   DGC_LAUNCHED(ctx, "biquad_carry");
-  biquad_fwd_kernel<1><<<grid, BQ_THREADS, 0, ctx->stream>>>(x_dev, coef, B, T, L, NC, state, y_dev);
+  if (quad) biquad_fwd4_kernel<1><<<grid4, block4, 0, ctx->stream>>>(x_dev, coef, B, T, L, NC, state, y_dev);
+  else biquad_fwd_kernel<1><<<grid, BQ_THREADS, 0, ctx->stream>>>(x_dev, coef, B, T, L, NC, state, y_dev);
   DGC_LAUNCHED(ctx, "biquad_fwd_out");
   return DGC_OK;
 }
