@@ -263,6 +263,64 @@ biquad_fwd_kernel(const float *__restrict__ x, const float *__restrict__ coef, i
   }
 }
 
+// End state of a chunk as a LINEAR functional of its input.  Run from a zero y-state, the state (y[end], y[end-1])
+// of lane l after a chunk is sum_m G[2l+s][m] * x[n0+m] plus two terms for the x-history x[n0-1], x[n0-2]:
+//   hy[0] = 1, hy[k] = -a1 hy[k-1] - a2 hy[k-2]                  (response of the recursion to a unit drive)
+//   h[k]  = b0 hy[k] + b1 hy[k-1] + b2 hy[k-2]                   (impulse response of the filter)
+//   G[2l+0][m] = h[C-1-m], G[2l+1][m] = h[C-2-m]
+//   history:  x[n0-1] -> (b1 hy[C-1] + b2 hy[C-2], b1 hy[C-2] + b2 hy[C-3]),  x[n0-2] -> (b2 hy[C-1], b2 hy[C-2])
+// With that table the first pass of the forward -- the end state of EVERY (voice, chunk, lane) -- is one matrix
+// product X[B*NC][C] * G^T[C][2L] on the tensor cores (its result lands directly in the [B][NC][L][2] state
+// layout) instead of a second run of the serial recurrence.  The table is evaluated in double per call (the
+// coefficients are inputs) and rounded once.
+__global__ void biquad_endstate_table_kernel(const float *__restrict__ coef, int L, float *__restrict__ G,
+                                             float *__restrict__ hist /* [L][4] */) {
+  const int l = blockIdx.x * blockDim.x + threadIdx.x;
+  if (l >= L) return;
+  const Coef c = load_coef(coef, l);
+  const double a1 = c.a1, a2 = c.a2, b0 = c.b0, b1 = c.b1, b2 = c.b2;
+  float *g1 = G + (size_t)(2 * l) * BQ_CHUNK, *g2 = g1 + BQ_CHUNK;
+  double hm1 = 0.0, hm2 = 0.0;   // hy[k-1], hy[k-2]
+  double hprev = 0.0;            // h[k-1]
+  double hyC1 = 0, hyC2 = 0, hyC3 = 0;
+  for (int k = 0; k < BQ_CHUNK; ++k) {
+    const double hy = k == 0 ? 1.0 : -(a2 * hm2 + a1 * hm1);
+    const double h = b0 * hy + b1 * hm1 + b2 * hm2;
+    // h[k] multiplies x[n0 + C-1-k] in y[end] and x[n0 + C-2-k] in y[end-1]
+    g1[BQ_CHUNK - 1 - k] = (float)h;
+    if (k >= 1) g2[BQ_CHUNK - 1 - k] = (float)hprev;   // h[k-1] at m = C-1-k  <=>  h[C-2-m]
+    if (k == BQ_CHUNK - 1) {
+      g2[BQ_CHUNK - 1] = 0.0f;                         // m = C-1: h[-1] = 0
+      hyC1 = hy; hyC2 = hm1; hyC3 = hm2;
+    }
+    hprev = h;
+    hm2 = hm1;
+    hm1 = hy;
+  }
+  hist[l * 4 + 0] = (float)(b1 * hyC1 + b2 * hyC2);
+  hist[l * 4 + 1] = (float)(b1 * hyC2 + b2 * hyC3);
+  hist[l * 4 + 2] = (float)(b2 * hyC1);
+  hist[l * 4 + 3] = (float)(b2 * hyC2);
+}
+
+// adds the x-history terms to the matrix-product states
+__global__ void biquad_state_hist_kernel(const float *__restrict__ x, const float *__restrict__ hist, int B, int T, int L,
+                                         int NC, float *__restrict__ state) {
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (size_t)B * NC * L) return;
+  const int l = (int)(idx % L);
+  const size_t bc = idx / L;
+  const int c = (int)(bc % NC), b = (int)(bc / NC);
+  if (c == 0) return;   // no history before the first chunk
+  const float *xb = x + (size_t)b * T + (size_t)c * BQ_CHUNK;
+  const float x1 = xb[-1], x2 = xb[-2];
+  float2 *st = reinterpret_cast<float2 *>(state) + idx;
+  float2 v = *st;
+  v.x += hist[l * 4 + 0] * x1 + hist[l * 4 + 2] * x2;
+  v.y += hist[l * 4 + 1] * x1 + hist[l * 4 + 3] * x2;
+  *st = v;
+}
+
 // The same sweep with FOUR lanes per thread (L a multiple of 4): four independent recurrences hide the
 // latency of the dependent multiply-adds of one, and the output goes out as one 128-bit store per frame and
 // thread (a warp writes 512 contiguous bytes).  Block = (L/4 lane quads, up to 4 chunks).
@@ -504,7 +562,8 @@ DGC_EXPORT uint64_t dgc_biquad_scratch_floats(const dgc_biquad_params *p, int32_
   if (!p || p->B <= 0 || p->T <= 0 || p->L <= 0) return 0;
   uint64_t NC = (uint64_t)(p->T + BQ_CHUNK - 1) / BQ_CHUNK;
   uint64_t coef = (((uint64_t)p->L * 16 + (uint64_t)p->L * 8) + 3) & ~3ull;
-  if (!backward) return coef + (uint64_t)p->B * NC * p->L * 2 + 8;
+  // forward: chunk states, then the end-state response table [2L][BQ_CHUNK] and its 4L history terms
+  if (!backward) return coef + (((uint64_t)p->B * NC * p->L * 2 + 3) & ~3ull) + (uint64_t)p->L * (2 * BQ_CHUNK + 4) + 16;
   uint64_t rec = (uint64_t)p->B * NC * BW_REC * p->L;
   return coef + ((rec + 3) & ~3ull) + 2 * ((uint64_t)p->B * p->L * 6 + p->L) + 16;
 }
@@ -532,7 +591,17 @@ DGC_EXPORT int32_t dgc_biquad_fwd(dgc_ctx *ctx, const dgc_biquad_params *p, cons
   const int qx = quad ? (L / 4 >= 64 ? 64 : L / 4) : 0;
   dim3 grid(dgc_div_up(L, BQ_THREADS), NC, B);
   dim3 grid4(quad ? dgc_div_up(L / 4, qx) : 1, dgc_div_up(NC, BQ4_CHUNKS), B), block4(quad ? qx : 1, BQ4_CHUNKS);
-  if (quad) biquad_fwd4_kernel<0><<<grid4, block4, 0, ctx->stream>>>(x_dev, coef, B, T, L, NC, state, nullptr);
+  // first pass: chunk end states from a zero y-state -- as one tensor-core product when the chunks tile T exactly
+  // and the problem is large enough for that path, else by running the recurrence
+  const bool by_matmul = (T % BQ_CHUNK) == 0 && (double)B * NC * L >= (double)(1 << 16) && (((uintptr_t)x_dev) & 15) == 0;
+  if (by_matmul) {
+    float *G = state + ((((size_t)B * NC * L * 2) + 3) & ~(size_t)3), *hist = G + (size_t)L * 2 * BQ_CHUNK;
+    biquad_endstate_table_kernel<<<dgc_div_up(L, 64), 64, 0, ctx->stream>>>(coef, L, G, hist);
+    DGC_LAUNCHED(ctx, "biquad_endstate_table");
+    rc = dgc_gemm_nt(ctx, x_dev, G, B * NC, 2 * L, BQ_CHUNK, state);
+    if (rc != DGC_OK) return rc;
+    biquad_state_hist_kernel<<<dgc_div_up((int64_t)B * NC * L, 256), 256, 0, ctx->stream>>>(x_dev, hist, B, T, L, NC, state);
+  } else if (quad) biquad_fwd4_kernel<0><<<grid4, block4, 0, ctx->stream>>>(x_dev, coef, B, T, L, NC, state, nullptr);
   else biquad_fwd_kernel<0><<<grid, BQ_THREADS, 0, ctx->stream>>>(x_dev, coef, B, T, L, NC, state, nullptr);
   DGC_LAUNCHED(ctx, "biquad_fwd_state");
   biquad_carry_kernel<<<dgc_div_up(B * L, 128), 128, 0, ctx->stream>>>(trans, B, L, NC, state);
