@@ -431,10 +431,8 @@ biquad_bwd_kernel(const float *__restrict__ x, const float *__restrict__ coef, c
   int nt = n0 + len - 1;
   float yc = yb[(size_t)nt * L];
   float ym1 = nt - 1 >= 0 ? yb[(size_t)(nt - 1) * L] : 0.f;
-  for (int n = len - 1; n >= 0; --n) {
-    int t = n0 + n;
-    float ym2 = t - 2 >= 0 ? yb[(size_t)(t - 2) * L] : 0.f;
-    float d = yc - tb[(size_t)t * L];
+  auto body = [&](int n, float ym2, float tv) {
+    float d = yc - tv;
     sq = fmaf(d, d, sq);
     float g = gscale * d;
     float lam = g - (cf.a1 * la1 + cf.a2 * la2);
@@ -451,6 +449,28 @@ biquad_bwd_kernel(const float *__restrict__ x, const float *__restrict__ coef, c
     h1b = h1a; h1a = h1;
     h2b = h2a; h2a = h2;
     yc = ym1; ym1 = ym2;
+  };
+  if (len == BQ_CHUNK && n0 >= 2) {
+    // interior chunk: every load is in range, so a group of sixteen frames issues its 32 loads before the
+    // dependent recurrence steps (the sweep is bound by loads in flight, not by arithmetic)
+    constexpr int G = 16;
+    for (int nb = BQ_CHUNK - G; nb >= 0; nb -= G) {
+      float yv[G], tv[G];
+#pragma unroll
+      for (int j = 0; j < G; ++j) {
+        const int t = n0 + nb + j;
+        yv[j] = __ldcs(yb + (size_t)(t - 2) * L);
+        tv[j] = __ldcs(tb + (size_t)t * L);
+      }
+#pragma unroll
+      for (int j = G - 1; j >= 0; --j) body(nb + j, yv[j], tv[j]);
+    }
+  } else {
+    for (int n = len - 1; n >= 0; --n) {
+      int t = n0 + n;
+      float ym2 = t - 2 >= 0 ? yb[(size_t)(t - 2) * L] : 0.f;
+      body(n, ym2, tb[(size_t)t * L]);
+    }
   }
   float *r = rec + ((size_t)b * NC + c) * BW_REC * L + l;
 #pragma unroll
