@@ -69,10 +69,20 @@ onepole_kernel(const float *__restrict__ x, int T, int NC, float a, const float 
   const int n0 = c * OP_CHUNK + tid * OP_PER;
   float loc[OP_PER];
   float prev = 0.0f;
+  static_assert(OP_PER == 8, "the vector path moves a thread's run as two 128-bit words");
+  // a thread's run of eight frames is 32 contiguous bytes: two 128-bit accesses when the voice row is aligned
+  const bool vec = n0 + OP_PER <= T && ((((uintptr_t)(xb + n0)) | (PHASE == 1 ? (uintptr_t)(y + (size_t)b * T + n0) : 0)) & 15) == 0;
+  if (vec) {
+    const float4 u = __ldg(reinterpret_cast<const float4 *>(xb + n0)), w = __ldg(reinterpret_cast<const float4 *>(xb + n0) + 1);
+    loc[0] = u.x; loc[1] = u.y; loc[2] = u.z; loc[3] = u.w;
+    loc[4] = w.x; loc[5] = w.y; loc[6] = w.z; loc[7] = w.w;
+  } else {
+#pragma unroll
+    for (int j = 0; j < OP_PER; ++j) loc[j] = (n0 + j < T) ? xb[n0 + j] : 0.0f;
+  }
 #pragma unroll
   for (int j = 0; j < OP_PER; ++j) {
-    float xv = (n0 + j < T) ? xb[n0 + j] : 0.0f;
-    prev = fmaf(a, prev, xv);
+    prev = fmaf(a, prev, loc[j]);
     loc[j] = prev;
   }
   float incl = block_decay_scan(prev, rpow, warp_tot, tid);  // state at the end of this thread's run
@@ -101,8 +111,16 @@ onepole_kernel(const float *__restrict__ x, int T, int NC, float a, const float 
   float ap = a;
 #pragma unroll
   for (int j = 0; j < OP_PER; ++j) {
-    if (n0 + j < T) yb[n0 + j] = fmaf(ap, state, loc[j]);
+    loc[j] = fmaf(ap, state, loc[j]);
     ap *= a;
+  }
+  if (vec) {
+    __stcs(reinterpret_cast<float4 *>(yb + n0), make_float4(loc[0], loc[1], loc[2], loc[3]));
+    __stcs(reinterpret_cast<float4 *>(yb + n0) + 1, make_float4(loc[4], loc[5], loc[6], loc[7]));
+  } else {
+#pragma unroll
+    for (int j = 0; j < OP_PER; ++j)
+      if (n0 + j < T) yb[n0 + j] = loc[j];
   }
 }
 
