@@ -41,6 +41,11 @@ class BiquadParams(C.Structure):
     _fields_ = [("B", C.c_int32), ("T", C.c_int32), ("L", C.c_int32), ("gain", C.c_float), ("mode", C.c_float)]
 
 
+class CompressorParams(C.Structure):
+    _fields_ = [("B", C.c_int32), ("T", C.c_int64), ("ratio", C.c_float), ("threshold", C.c_float),
+                ("knee", C.c_float), ("attack", C.c_float), ("release", C.c_float), ("sample_rate", C.c_float)]
+
+
 class Uop(C.Structure):
     """One op of a generated block (dgc_uop)."""
     _fields_ = [("op", C.c_int32), ("a", C.c_int32), ("b", C.c_int32), ("c", C.c_int32), ("imm", C.c_float)]
@@ -131,6 +136,11 @@ SIGNATURES = {
     "dgc_linear_bwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp]),
     "dgc_adam_step": (_i32, [_vp, _vp, _vp, _vp, _vp, _u64, _i32, _f, _f, _f, _f]),
     "dgc_sanitize": (_i32, [_vp, _vp, _u64, _vp]),
+    "dgc_delay_line": (_i32, [_vp, _vp, _vp, _i32, _i64, _i32, _i32, _vp, _vp, _vp]),
+    "dgc_spectrum_delay": (_i32, [_vp, _vp, _vp, _i64, _i32, _i32, _vp, _vp, _vp]),
+    "dgc_latch_scratch_floats": (_u64, [_i64, _i32]),
+    "dgc_latch": (_i32, [_vp, _vp, _vp, _i32, _i64, _i32, _vp, _vp, _vp]),
+    "dgc_compressor": (_i32, [_vp, C.POINTER(CompressorParams), _vp, _vp, _vp, _vp]),
     "dgc_ctx_prepare_tables": (_i32, [_vp, _i32, _i32]),
     "dgc_module_load": (_i32, [_vp, _vp, _u64, C.POINTER(_vp)]),
     "dgc_module_compile": (_i32, [_vp, C.c_char_p, C.c_char_p, C.POINTER(_vp)]),
@@ -477,6 +487,58 @@ class Context:
         out = x if out is None else out
         self.check(self.lib.dgc_sanitize(self.h, _ptr(x), x.numel(), _ptr(out)))
         return out
+
+    # ---- ring and hold ops ---------------------------------------------------------------------
+    def delay_line(self, x, delay, max_delay, ring=None, head=None, per_lane=False):
+        """x [T][lanes]; delay: float, or a tensor of shape [1], [T], [T][lanes] or [lanes] (Sources/DGen/Emit.swift:331-403);
+        per_lane=True reads a 1-D delay as [lanes] when T == lanes makes it ambiguous.
+        ring [lanes][max_delay] and head [1] are updated in place when given."""
+        torch = self.torch
+        T, lanes = x.shape
+        if not torch.is_tensor(delay):
+            delay = torch.full((1,), float(delay), dtype=torch.float32, device=x.device)
+        if delay.numel() == 1:
+            mode = 0
+        elif delay.dim() == 2 and tuple(delay.shape) == (T, lanes):
+            mode = 2
+        elif delay.dim() == 1 and delay.numel() == T and not (T == lanes and per_lane):
+            mode = 1
+        elif delay.dim() == 1 and delay.numel() == lanes:
+            mode = 3
+        else:
+            raise ValueError("delay must have 1, T, lanes or T*lanes elements")
+        y = torch.empty_like(x)
+        self.check(self.lib.dgc_delay_line(self.h, _ptr(x), _ptr(delay), mode, T, lanes, max_delay,
+                                           _ptr(ring) if ring is not None else None,
+                                           _ptr(head) if head is not None else None, _ptr(y)))
+        return y
+
+    def spectrum_delay(self, spec, hops, delay=None, ring=None, row=None):
+        """spec [H][N]; delay None (exactly `hops` boundaries) or [H] in hops (Sources/DGen/Emit.swift:405-512)."""
+        H, N = spec.shape
+        out = self.torch.empty_like(spec)
+        self.check(self.lib.dgc_spectrum_delay(self.h, _ptr(spec), _ptr(delay) if delay is not None else None, H, N,
+                                               hops, _ptr(ring) if ring is not None else None,
+                                               _ptr(row) if row is not None else None, _ptr(out)))
+        return out
+
+    def latch(self, value, cond, state=None):
+        """value [T][lanes]; cond [T] or [T][lanes]; state [lanes] updated in place (Sources/DGen/Emit+State.swift:225-262)."""
+        T, lanes = value.shape
+        mode = 1 if cond.dim() == 1 else 2
+        y = self.torch.empty_like(value)
+        self.check(self.lib.dgc_latch(self.h, _ptr(value), _ptr(cond), mode, T, lanes,
+                                      _ptr(state) if state is not None else None, None, _ptr(y)))
+        return y
+
+    def compressor(self, x, ratio, threshold, knee, attack, release, sample_rate, sidechain=None, state=None):
+        """x [B][T] (Sources/DGen/HigherOps.swift:566-651); state [B] updated in place."""
+        B, T = x.shape
+        p = CompressorParams(B, T, ratio, threshold, knee, attack, release, sample_rate)
+        y = self.torch.empty_like(x)
+        self.check(self.lib.dgc_compressor(self.h, C.byref(p), _ptr(x), _ptr(sidechain) if sidechain is not None else None,
+                                           _ptr(state) if state is not None else None, _ptr(y)))
+        return y
 
     # ---- generated blocks ----------------------------------------------------------------------
     def compile_module(self, cuda_source, name="dgen_block.cu"):

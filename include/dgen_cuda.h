@@ -313,6 +313,51 @@ int32_t dgc_adam_step(dgc_ctx *ctx, float *theta_dev, const float *grad_dev, flo
  * (toolchain/include/dgen_runtime.h:59-84, Sources/DGen/Renderer/CRenderer.swift:1021-1039). */
 int32_t dgc_sanitize(dgc_ctx *ctx, const float *in_dev, uint64_t n, float *out_dev);
 
+/* ---- ring and hold ops ------------------------------------------------------------------------------
+ * The reference runs these frame by frame in sequential blocks because they read and write a memory cell;
+ * here every (frame, lane) element is computed independently from the input and from the cell contents at
+ * the start of the call, and the cells are rewritten at the end so consecutive calls continue seamlessly.
+ * State pointers may be NULL: the cells then start at zero and are not kept.  x and y must not alias. */
+
+/* Per-lane interpolated delay lines with one shared write head: tensorDelay
+ * (Sources/DGen/HigherOps+DelayLine.swift:33-65; emission Sources/DGen/Emit.swift:331-403).
+ * x_dev, y_dev [T][lanes]; delay in samples, clamped to [0, max_delay - 1], linear interpolation between the
+ * two bracketing past samples (a delay of 0 returns the current sample).
+ * delay_mode: 0 = delay_dev[0] for the whole call, 1 = [T], 2 = [T][lanes], 3 = [lanes].
+ * ring_dev [lanes][max_delay] (lane-major, as the reference's buffer cell), head_dev 1 float (write position). */
+int32_t dgc_delay_line(dgc_ctx *ctx, const float *x_dev, const float *delay_dev, int32_t delay_mode, int64_t T,
+                       int32_t lanes, int32_t max_delay, float *ring_dev, float *head_dev, float *y_dev);
+
+/* Delay of an [N] spectrum by whole or fractional hop boundaries: spectrumDelay / spectrumDelayMod
+ * (Sources/DGen/HigherOps+SpectrumDelay.swift:20-135; emission Sources/DGen/Emit.swift:405-512).
+ * spec_dev, out_dev [H][N]: one row per hop boundary.  delay_dev NULL: the row of exactly `hops` boundaries ago.
+ * delay_dev [H]: delay in hops, clamped to [0, hops], linear interpolation between floor and floor + 1 ago.
+ * ring_dev [hops + 1][N], row_dev 1 float (next write row). */
+int32_t dgc_spectrum_delay(dgc_ctx *ctx, const float *spec_dev, const float *delay_dev, int64_t H, int32_t N,
+                           int32_t hops, float *ring_dev, float *row_dev, float *out_dev);
+
+/* Sample and hold: y[n][e] = value[n][e] where cond > 0, else the value held from the most recent such frame
+ * (state_dev [lanes] before the first; updated to the last output).  latch
+ * (Sources/DGen/Definitions.swift:104-113 scalar, Sources/DGen/Emit+State.swift:225-262 tensor,
+ * Sources/DGen/HigherOps+Latch.swift:31-57).  cond_mode: 1 = cond_dev [T] shared by the lanes, 2 = [T][lanes].
+ * scratch_dev: dgc_latch_scratch_floats floats, or NULL to use context scratch. */
+uint64_t dgc_latch_scratch_floats(int64_t T, int32_t lanes);
+int32_t dgc_latch(dgc_ctx *ctx, const float *value_dev, const float *cond_dev, int32_t cond_mode, int64_t T,
+                  int32_t lanes, float *state_dev, float *scratch_dev, float *y_dev);
+
+/* Feed-forward compressor with soft knee and attack / release smoothing of the gain reduction in dB:
+ * Graph.compressor (Sources/DGen/HigherOps.swift:566-651).  x_dev, y_dev [B][T]; sidechain_dev [B][T] or NULL
+ * (detector = the input); state_dev [B] = previous smoothed gain reduction (the history cell), or NULL. */
+typedef struct dgc_compressor_params {
+  int32_t B;
+  int64_t T;
+  float ratio, threshold, knee; /* threshold and knee in dB */
+  float attack, release;        /* seconds */
+  float sample_rate;
+} dgc_compressor_params;
+int32_t dgc_compressor(dgc_ctx *ctx, const dgc_compressor_params *p, const float *x_dev, const float *sidechain_dev,
+                       float *state_dev, float *y_dev);
+
 /* ---- generated blocks -------------------------------------------------------------------------------
  * Device code the host's renderer emits for elementwise blocks that no primitive above covers.
  * replaces: compiling the C renderer's source and loading it (Sources/DGen/Runtime.swift:291-311) and
