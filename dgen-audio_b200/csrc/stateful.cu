@@ -5,6 +5,7 @@
 //                          Sources/DGen/HigherOps+SpectrumDelay.swift:20-135, emission Sources/DGen/Emit.swift:405-512
 //   latch (sample and hold) Sources/DGen/Definitions.swift:104-113, Sources/DGen/Emit+State.swift:225-262
 //   compressor             Sources/DGen/HigherOps.swift:566-651
+//   phase vocoder          Sources/DGen/HigherOps+PhaseVocoder.swift:15-88, emission Sources/DGen/Emit+PhaseVocoder.swift:6-118
 //
 // The reference runs each of them in a sequential block, one frame after the other, because they read and write
 // a memory cell.  None of the first three is a true recurrence: a delay line's output at frame n is a gather
@@ -13,7 +14,9 @@
 // is one thread; the ring / held-value cells are read for the frames that reach back before the call and
 // rewritten at the end of the call so that consecutive calls continue as the reference's persistent cells do.
 // The compressor's attack / release smoother IS a recurrence with a data-dependent coefficient (no associative
-// form): its gain computer and make-up run sample-parallel, the smoother runs one warp per voice.
+// form): its gain computer and make-up run sample-parallel, the smoother runs one warp per voice.  The phase
+// vocoder carries one value per bin from hop to hop (the synthesis phase): its analysis runs parallel over
+// (hop, bin), its resynthesis one thread per bin.
 #include "common.cuh"
 
 namespace {
@@ -239,6 +242,89 @@ compressor_kernel(const float *__restrict__ x, const float *__restrict__ side, i
   if (state && lane == 0) state[b] = s;
 }
 
+// ---- phase vocoder ----------------------------------------------------------------------------------------------
+// Emit+PhaseVocoder.swift:46-53
+__device__ __forceinline__ float principal_arg(float v) {
+  const float tau = 6.28318530717958647692f, half = 3.14159265358979323846f;
+  const float w = v - tau * roundf(v / tau);
+  const float wh = w > half ? w - tau : w;
+  return w < -half ? wh + tau : wh;
+}
+
+__device__ __forceinline__ float mixf(float a, float b, float t) { return fmaf(b, t, a * (1.0f - t)); }
+
+// Analysis (Emit+PhaseVocoder.swift:57-71), parallel over (voice, hop, bin): the "previous analysis phase" of hop h
+// is the phase of hop h - 1 of the INPUT (the state cell only for the first hop of the call), so nothing here is
+// a recurrence.
+__global__ void __launch_bounds__(256)
+pv_analysis_kernel(const float *__restrict__ re, const float *__restrict__ im, int V, int64_t H, int N, float omega_scale,
+                   const float *__restrict__ state, float *__restrict__ mag, float *__restrict__ omega) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (int64_t)V * H * N) return;
+  const int i = (int)(idx % N);
+  const int64_t vh = idx / N, h = vh % H;
+  const int v = (int)(vh / H);
+  const float r = re[idx], q = im[idx];
+  const float phase = atan2f(q, r);
+  const float prev = h > 0 ? atan2f(im[idx - N], re[idx - N]) : (state ? state[(size_t)v * (2 * N + 1) + i] : 0.0f);
+  const float target = (float)i * omega_scale;
+  mag[idx] = sqrtf(r * r + q * q);
+  omega[idx] = target + principal_arg(phase - prev - target);
+}
+
+// Resynthesis (Emit+PhaseVocoder.swift:73-108): thread per (voice, output bin), hops in order: the synthesis phase
+// is the one value carried from hop to hop.  ratio_mode 0: one value, 1: [H], 2: [V][H].
+__global__ void __launch_bounds__(128)
+pv_synthesis_kernel(const float *__restrict__ re, const float *__restrict__ im, const float *__restrict__ mag,
+                    const float *__restrict__ omega, const float *__restrict__ ratio, int ratio_mode, int V, int64_t H,
+                    int N, float *__restrict__ state, float *__restrict__ out_re, float *__restrict__ out_im) {
+  const int k = blockIdx.x * blockDim.x + threadIdx.x, v = blockIdx.y;
+  if (k >= N) return;
+  float *st = state ? state + (size_t)v * (2 * N + 1) : nullptr;
+  float synth = st ? st[N + k] : 0.0f;
+  bool started = st ? st[2 * N] != 0.0f : false;
+  const float nm1 = (float)(N - 1);
+  const size_t base = (size_t)v * H * N;
+  for (int64_t h = 0; h < H; ++h) {
+    const float rin = ratio_mode == 0 ? ratio[0] : ratio_mode == 1 ? ratio[h] : ratio[(size_t)v * H + h];
+    const float r = fmaxf(rin, 1e-4f);
+    const float src = (float)k / r;
+    const bool in_range = src <= nm1;
+    const float srcc = in_range ? src : nm1;
+    const float fl = floorf(srcc), frac = srcc - fl;
+    const int i0 = (int)fl, i1 = i0 < N - 1 ? i0 + 1 : i0;
+    const size_t row = base + (size_t)h * N;
+    const float m = mixf(mag[row + i0], mag[row + i1], frac);
+    const float om = mixf(omega[row + i0], omega[row + i1], frac) * r;
+    if (started) {
+      synth = principal_arg(synth + om);
+    } else {
+      // first hop of the stream: start from the interpolated analysis phase of this hop
+      const float p0 = atan2f(im[row + i0], re[row + i0]), p1 = atan2f(im[row + i1], re[row + i1]);
+      synth = principal_arg(mixf(p0, p1, frac));
+      started = true;
+    }
+    const float outm = in_range ? m : 0.0f;
+    float sn, cs;
+    sincosf(synth, &sn, &cs);
+    out_re[row + k] = outm * cs;
+    out_im[row + k] = outm * sn;
+  }
+  if (st) {
+    const size_t last = base + (size_t)(H - 1) * N + k;
+    const float ph = atan2f(im[last], re[last]);
+    // the "started" flag is shared by all bins of a voice and other blocks may still have to read it: a launch of
+    // its own sets it afterwards
+    st[N + k] = synth;
+    st[k] = ph;
+  }
+}
+
+__global__ void pv_mark_started_kernel(float *state, int V, int N) {
+  const int v = blockIdx.x * blockDim.x + threadIdx.x;
+  if (v < V) state[(size_t)v * (2 * N + 1) + 2 * N] = 1.0f;
+}
+
 }  // namespace
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -344,5 +430,38 @@ DGC_EXPORT int32_t dgc_compressor(dgc_ctx *ctx, const dgc_compressor_params *p, 
   compressor_kernel<<<dgc_div_up(p->B, COMP_WARPS), COMP_WARPS * 32, 0, ctx->stream>>>(x_dev, sidechain_dev, p->B, p->T, c,
                                                                                     state_dev, y_dev);
   DGC_LAUNCHED(ctx, "compressor");
+  return DGC_OK;
+}
+
+DGC_EXPORT uint64_t dgc_phase_vocoder_scratch_floats(int32_t V, int64_t H, int32_t N) {
+  if (V <= 0 || H <= 0 || N <= 0) return 0;
+  return 2ull * (uint64_t)V * (uint64_t)H * (uint64_t)N;
+}
+
+DGC_EXPORT int32_t dgc_phase_vocoder(dgc_ctx *ctx, const float *re_dev, const float *im_dev, const float *ratio_dev,
+                                     int32_t ratio_mode, int32_t V, int64_t H, int32_t N, int32_t hop, float *state_dev,
+                                     float *scratch_dev, float *out_re_dev, float *out_im_dev) {
+  if (!ctx) return DGC_ERR_INVALID;
+  DGC_REQUIRE(ctx, re_dev && im_dev && ratio_dev && out_re_dev && out_im_dev, "null pointer");
+  DGC_REQUIRE(ctx, V > 0 && V <= 65535 && H > 0 && N > 0 && hop > 0, "size out of range");
+  DGC_REQUIRE(ctx, ratio_mode >= 0 && ratio_mode <= 2, "ratio_mode must be 0 (one value), 1 ([H]) or 2 ([V][H])");
+  DGC_REQUIRE(ctx, re_dev != out_re_dev && im_dev != out_im_dev, "in-place operation is not supported");
+  const int64_t total = (int64_t)V * H * N;
+  DGC_REQUIRE(ctx, total / 256 < 0x7fffffffLL, "V * H * N too large");
+  float *scr = scratch_dev ? scratch_dev : dgc_ctx_scratch(ctx, dgc_phase_vocoder_scratch_floats(V, H, N));
+  if (!scr) return DGC_ERR_OOM;
+  float *mag = scr, *omega = scr + total;
+  const float omega_scale = 2.0f * 3.14159265358979323846f * (float)hop / (float)N;
+  pv_analysis_kernel<<<dgc_div_up(total, 256), 256, 0, ctx->stream>>>(re_dev, im_dev, V, H, N, omega_scale, state_dev, mag,
+                                                                     omega);
+  DGC_LAUNCHED(ctx, "phase_vocoder_analysis");
+  pv_synthesis_kernel<<<dim3(dgc_div_up(N, 128), V), 128, 0, ctx->stream>>>(re_dev, im_dev, mag, omega, ratio_dev,
+                                                                           ratio_mode, V, H, N, state_dev, out_re_dev,
+                                                                           out_im_dev);
+  DGC_LAUNCHED(ctx, "phase_vocoder_synthesis");
+  if (state_dev) {
+    pv_mark_started_kernel<<<dgc_div_up(V, 128), 128, 0, ctx->stream>>>(state_dev, V, N);
+    DGC_LAUNCHED(ctx, "phase_vocoder_state");
+  }
   return DGC_OK;
 }

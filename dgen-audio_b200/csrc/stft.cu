@@ -261,6 +261,32 @@ __global__ void take_partitions_kernel(const float *__restrict__ frames, int ir_
   g_ir[t] = frames[(size_t)k * N + i];
 }
 
+// half spectra float2 [rows][N/2+1] -> all N bins as split re / im [rows][N] (bins above N/2: the conjugate mirror,
+// which is what a complex transform of a real window holds there)
+__global__ void half_to_full_kernel(const float2 *__restrict__ half, int64_t rows, int N, float *__restrict__ re,
+                                    float *__restrict__ im) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= rows * N) return;
+  const int64_t r = idx / N;
+  const int k = (int)(idx - r * N), NB = N / 2 + 1;
+  const float2 z = half[r * NB + (k <= N / 2 ? k : N - k)];
+  re[idx] = z.x;
+  im[idx] = k <= N / 2 ? z.y : -z.y;
+}
+
+// split re / im [rows][N] of ANY complex spectrum -> the half spectrum of its Hermitian part, whose inverse
+// transform is the real part of the inverse transform of the whole (the reference keeps only that real part)
+__global__ void full_to_half_kernel(const float *__restrict__ re, const float *__restrict__ im, int64_t rows, int N,
+                                    float2 *__restrict__ half) {
+  const int NB = N / 2 + 1;
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= rows * NB) return;
+  const int64_t r = idx / NB;
+  const int k = (int)(idx - r * NB), kn = (N - k) & (N - 1);
+  const float *rr = re + r * N, *ii = im + r * N;
+  half[idx] = make_float2(0.5f * (rr[k] + rr[kn]), 0.5f * (ii[k] - ii[kn]));
+}
+
 template <int N, int SRC, int OUT>
 int32_t launch_stft(dgc_ctx *ctx, const float *x, int V, int T, int hop, int H, const float *window, float *out) {
   const float2 *tw = dgc_ctx_twiddles(ctx, N);
@@ -305,6 +331,61 @@ DGC_EXPORT int32_t dgc_stft_mag(dgc_ctx *ctx, const float *x_dev, int32_t V, int
   DGC_REQUIRE(ctx, dgc_is_pow2(N) && N >= 16 && N <= 2048, "N must be a power of two in 16..2048");
   const int H = dgc_div_up(T, hop);
   return dispatch_stft<0, 0>(ctx, N, x_dev, V, T, hop, H, window_dev, mags_dev);
+}
+
+DGC_EXPORT uint64_t dgc_stft_scratch_floats(int32_t V, int32_t T, int32_t N, int32_t hop, int32_t inverse) {
+  if (V <= 0 || T <= 0 || N <= 0 || hop <= 0) return 0;
+  const uint64_t H = (uint64_t)(T + hop - 1) / hop, NB = N / 2 + 1;
+  return ((2 * (uint64_t)V * H * NB + 3) & ~3ull) + (inverse ? (uint64_t)V * H * N : 0) + 16;
+}
+
+DGC_EXPORT int32_t dgc_stft_fwd(dgc_ctx *ctx, const float *x_dev, int32_t V, int32_t T, int32_t N, int32_t hop,
+                                const float *window_dev, float *scratch_dev, float *re_dev, float *im_dev) {
+  if (!ctx) return DGC_ERR_INVALID;
+  DGC_REQUIRE(ctx, x_dev && re_dev && im_dev, "null pointer");
+  DGC_REQUIRE(ctx, V > 0 && V <= 65535 && T > 0 && hop > 0, "size out of range");
+  DGC_REQUIRE(ctx, dgc_is_pow2(N) && N >= 16 && N <= 2048, "N must be a power of two in 16..2048");
+  const int H = dgc_div_up(T, hop);
+  float *scr = scratch_dev ? scratch_dev : dgc_ctx_scratch(ctx, dgc_stft_scratch_floats(V, T, N, hop, 0));
+  if (!scr) return DGC_ERR_OOM;
+  DGC_REQUIRE(ctx, (((uintptr_t)scr) & 7) == 0, "scratch must be 8-byte aligned");
+  int32_t rc = dispatch_stft<0, 1>(ctx, N, x_dev, V, T, hop, H, window_dev, scr);
+  if (rc != DGC_OK) return rc;
+  const int64_t rows = (int64_t)V * H;
+  half_to_full_kernel<<<dgc_div_up(rows * N, 256), 256, 0, ctx->stream>>>(reinterpret_cast<const float2 *>(scr), rows, N,
+                                                                         re_dev, im_dev);
+  DGC_LAUNCHED(ctx, "stft_full_bins");
+  return DGC_OK;
+}
+
+DGC_EXPORT int32_t dgc_istft_ola(dgc_ctx *ctx, const float *re_dev, const float *im_dev, int32_t V, int32_t T, int32_t N,
+                                 int32_t hop, const float *window_dev, float gain, float *scratch_dev,
+                                 int32_t accumulate, float *out_dev) {
+  if (!ctx) return DGC_ERR_INVALID;
+  DGC_REQUIRE(ctx, re_dev && im_dev && out_dev, "null pointer");
+  DGC_REQUIRE(ctx, V > 0 && V <= 65535 && T > 0, "size out of range");
+  DGC_REQUIRE(ctx, dgc_is_pow2(N) && N >= 16 && N <= 2048, "N must be a power of two in 16..2048");
+  DGC_REQUIRE(ctx, hop > 0 && hop <= N, "hop must be in 1..N");
+  const int H = dgc_div_up(T, hop), NB = N / 2 + 1;
+  float *scr = scratch_dev ? scratch_dev : dgc_ctx_scratch(ctx, dgc_stft_scratch_floats(V, T, N, hop, 1));
+  if (!scr) return DGC_ERR_OOM;
+  DGC_REQUIRE(ctx, (((uintptr_t)scr) & 7) == 0, "scratch must be 8-byte aligned");
+  float *frames = scr + (((size_t)2 * V * H * NB + 3) & ~(size_t)3);
+  const int64_t rows = (int64_t)V * H;
+  full_to_half_kernel<<<dgc_div_up(rows * NB, 256), 256, 0, ctx->stream>>>(re_dev, im_dev, rows, N,
+                                                                          reinterpret_cast<float2 *>(scr));
+  DGC_LAUNCHED(ctx, "istft_hermitian_part");
+  int32_t rc = DGC_OK;
+  switch (N) {
+#define CASE(NN) case NN: rc = launch_istft<NN>(ctx, reinterpret_cast<const float2 *>(scr), V, H, window_dev, gain, frames); break;
+    CASE(16) CASE(32) CASE(64) CASE(128) CASE(256) CASE(512) CASE(1024) CASE(2048)
+#undef CASE
+  }
+  if (rc != DGC_OK) return rc;
+  overlap_add_kernel<<<dim3(dgc_div_up(T, 256), V), 256, 0, ctx->stream>>>(frames, T, N, hop, H, 0, accumulate,
+                                                                           out_dev);
+  DGC_LAUNCHED(ctx, "overlap_add");
+  return DGC_OK;
 }
 
 DGC_EXPORT uint64_t dgc_partconv_scratch_floats(int32_t V, int32_t T, int32_t ir_len, int32_t N, int32_t hop) {

@@ -136,6 +136,11 @@ SIGNATURES = {
     "dgc_linear_bwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp]),
     "dgc_adam_step": (_i32, [_vp, _vp, _vp, _vp, _vp, _u64, _i32, _f, _f, _f, _f]),
     "dgc_sanitize": (_i32, [_vp, _vp, _u64, _vp]),
+    "dgc_stft_scratch_floats": (_u64, [_i32, _i32, _i32, _i32, _i32]),
+    "dgc_stft_fwd": (_i32, [_vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp]),
+    "dgc_istft_ola": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _f, _vp, _i32, _vp]),
+    "dgc_phase_vocoder_scratch_floats": (_u64, [_i32, _i64, _i32]),
+    "dgc_phase_vocoder": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i64, _i32, _i32, _vp, _vp, _vp, _vp]),
     "dgc_delay_line": (_i32, [_vp, _vp, _vp, _i32, _i64, _i32, _i32, _vp, _vp, _vp]),
     "dgc_spectrum_delay": (_i32, [_vp, _vp, _vp, _i64, _i32, _i32, _vp, _vp, _vp]),
     "dgc_latch_scratch_floats": (_u64, [_i64, _i32]),
@@ -539,6 +544,44 @@ class Context:
         self.check(self.lib.dgc_compressor(self.h, C.byref(p), _ptr(x), _ptr(sidechain) if sidechain is not None else None,
                                            _ptr(state) if state is not None else None, _ptr(y)))
         return y
+
+    def stft(self, x, N, hop, window=None):
+        """x [V][T] -> (re, im) [V][H][N], all bins of every hop's buffer window (Sources/DGen/HigherOps.swift:738-792,
+        Sources/DGen/Emit+AcceleratedFFT.swift:16-112)."""
+        V, T = x.shape
+        H = (T + hop - 1) // hop
+        re = self.torch.empty(V, H, N, dtype=self.torch.float32, device=x.device)
+        im = self.torch.empty_like(re)
+        self.check(self.lib.dgc_stft_fwd(self.h, _ptr(x), V, T, N, hop, _ptr(window) if window is not None else None,
+                                         None, _ptr(re), _ptr(im)))
+        return re, im
+
+    def istft_ola(self, re, im, T, hop, window=None, gain=1.0, out=None, accumulate=False):
+        """(re, im) [V][H][N] -> [V][T]: inverse FFT, window, overlap-add (Sources/DGen/Emit+FFT.swift:6-62)."""
+        V, H, N = re.shape
+        if H != (T + hop - 1) // hop:
+            raise ValueError("spectra hold %d hops, T / hop needs %d" % (H, (T + hop - 1) // hop))
+        out = self.torch.empty(V, T, dtype=self.torch.float32, device=re.device) if out is None else out
+        self.check(self.lib.dgc_istft_ola(self.h, _ptr(re), _ptr(im), V, T, N, hop,
+                                          _ptr(window) if window is not None else None, gain, None,
+                                          1 if accumulate else 0, _ptr(out)))
+        return out
+
+    def phase_vocoder(self, re, im, ratio, hop, state=None):
+        """(re, im) [V][H][N]; ratio: float, [H] or [V][H]; state [V][2N+1] updated in place
+        (Sources/DGen/Emit+PhaseVocoder.swift:6-118)."""
+        torch = self.torch
+        V, H, N = re.shape
+        if not torch.is_tensor(ratio):
+            ratio = torch.full((1,), float(ratio), dtype=torch.float32, device=re.device)
+        mode = 0 if ratio.numel() == 1 else (2 if ratio.dim() == 2 else 1)
+        if mode == 1 and ratio.numel() != H or mode == 2 and tuple(ratio.shape) != (V, H):
+            raise ValueError("ratio must have 1, H or V*H elements")
+        out_re, out_im = torch.empty_like(re), torch.empty_like(im)
+        self.check(self.lib.dgc_phase_vocoder(self.h, _ptr(re), _ptr(im), _ptr(ratio), mode, V, H, N, hop,
+                                              _ptr(state) if state is not None else None, None, _ptr(out_re),
+                                              _ptr(out_im)))
+        return out_re, out_im
 
     # ---- generated blocks ----------------------------------------------------------------------
     def compile_module(self, cuda_source, name="dgen_block.cu"):

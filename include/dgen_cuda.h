@@ -243,6 +243,22 @@ int32_t dgc_biquad_mse_bwd(dgc_ctx *ctx, const dgc_biquad_params *p, const float
 int32_t dgc_stft_mag(dgc_ctx *ctx, const float *x_dev, int32_t V, int32_t T, int32_t N, int32_t hop,
                      const float *window_dev, float *mags_dev);
 
+/* buffer(size:N, hop:) -> FFT with ALL N bins kept, split real / imaginary as the reference's spectrum tensors:
+ * re_dev, im_dev [V][H][N], H = ceil(T/hop); window as for dgc_stft_mag.
+ * replaces: bufferView + acceleratedFFT / tensorFFT (HigherOps.swift:738-792, Emit+AcceleratedFFT.swift:16-112,
+ * HigherOps+FFT.swift:16-123).  scratch_dev: dgc_stft_scratch_floats(.., 0) floats or NULL (context scratch). */
+uint64_t dgc_stft_scratch_floats(int32_t V, int32_t T, int32_t N, int32_t hop, int32_t inverse);
+int32_t dgc_stft_fwd(dgc_ctx *ctx, const float *x_dev, int32_t V, int32_t T, int32_t N, int32_t hop,
+                     const float *window_dev, float *scratch_dev, float *re_dev, float *im_dev);
+
+/* IFFT (scaled by 1/N, real part kept) -> * window * gain -> overlapAdd at `hop` into [V][T]; the spectra need not be
+ * Hermitian (a phase vocoder's are not): the real part of the inverse transform is what the reference keeps.
+ * replaces: acceleratedIFFT / tensorIFFT + overlapAdd (Emit+AcceleratedFFT.swift:16-112, Emit+FFT.swift:6-62).
+ * scratch_dev: dgc_stft_scratch_floats(.., 1) floats or NULL.  accumulate != 0: out += result. */
+int32_t dgc_istft_ola(dgc_ctx *ctx, const float *re_dev, const float *im_dev, int32_t V, int32_t T, int32_t N,
+                      int32_t hop, const float *window_dev, float gain, float *scratch_dev, int32_t accumulate,
+                      float *out_dev);
+
 /* partitionedConvolve (Sources/DGenLazy/SpectralTensorOps.swift:204-254,
  * Emit+PartitionedConvolution.swift:26-113, Emit+FFT.swift:6-62): V signals [V][T], one IR; periodic
  * Hann analysis and synthesis windows, IFFT scaled by 1/N, overlap-add at `hop`.
@@ -357,6 +373,17 @@ typedef struct dgc_compressor_params {
 } dgc_compressor_params;
 int32_t dgc_compressor(dgc_ctx *ctx, const dgc_compressor_params *p, const float *x_dev, const float *sidechain_dev,
                        float *state_dev, float *y_dev);
+
+/* Phase-vocoder pitch shift of a stream of N-bin spectra: phaseVocoder
+ * (Sources/DGen/HigherOps+PhaseVocoder.swift:15-88; emission Sources/DGen/Emit+PhaseVocoder.swift:6-118).
+ * re_dev, im_dev, out_re_dev, out_im_dev [V][H][N] (one row per hop boundary, all N bins).
+ * ratio_mode: 0 = ratio_dev[0], 1 = ratio_dev [H] shared by the voices, 2 = [V][H]; ratios below 1e-4 are raised to it.
+ * state_dev [V][2N+1] = previous analysis phase [N], synthesis phase [N], started flag; NULL = a fresh stream.
+ * scratch_dev: dgc_phase_vocoder_scratch_floats floats or NULL. */
+uint64_t dgc_phase_vocoder_scratch_floats(int32_t V, int64_t H, int32_t N);
+int32_t dgc_phase_vocoder(dgc_ctx *ctx, const float *re_dev, const float *im_dev, const float *ratio_dev,
+                          int32_t ratio_mode, int32_t V, int64_t H, int32_t N, int32_t hop, float *state_dev,
+                          float *scratch_dev, float *out_re_dev, float *out_im_dev);
 
 /* ---- generated blocks -------------------------------------------------------------------------------
  * Device code the host's renderer emits for elementwise blocks that no primitive above covers.

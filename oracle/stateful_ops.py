@@ -144,3 +144,59 @@ def compressor(x, ratio, threshold, knee, attack, release, sample_rate, sidechai
     att_db = (in_db - sm).astype(f32)
     amp = np.power(f32(10.0), (att_db / f32(20.0)).astype(f32)).astype(f32)
     return (np.sign(x).astype(f32) * amp).astype(f32), s
+
+
+def _principal_arg(v):
+    """Emit+PhaseVocoder.swift:46-53: v - 2 pi round(v / 2 pi), then folded into [-pi, pi]; round is roundf (half away
+    from zero)."""
+    tau, half = f32(2.0 * np.float32(np.pi)), f32(np.pi)
+    q = (v / tau).astype(f32)
+    r = (np.sign(q) * np.floor(np.abs(q) + f32(0.5))).astype(f32)
+    w = (v - (tau * r).astype(f32)).astype(f32)
+    wh = np.where(w > half, (w - tau).astype(f32), w)
+    return np.where(w < -half, (wh + tau).astype(f32), wh).astype(f32)
+
+
+def phase_vocoder(re, im, ratio, hop, state=None):
+    """re, im [H][N] (all N bins of each hop's spectrum); ratio [H] -> (out_re, out_im [H][N], state).
+    state = (previous analysis phase [N], synthesis phase [N], init flag).  Follows
+    Sources/DGen/Emit+PhaseVocoder.swift:32-114 hop by hop."""
+    re, im = np.ascontiguousarray(re, f32), np.ascontiguousarray(im, f32)
+    H, N = re.shape
+    ratio = np.broadcast_to(np.asarray(ratio, f32), (H,))
+    if state is None:
+        prev, synth, init = np.zeros(N, f32), np.zeros(N, f32), 0.0
+    else:
+        prev, synth, init = np.array(state[0], f32), np.array(state[1], f32), float(state[2])
+    omega_scale = f32(2.0 * np.float32(np.pi) * np.float32(hop) / np.float32(N))
+    bins = np.arange(N, dtype=f32)
+    out_re, out_im = np.zeros((H, N), f32), np.zeros((H, N), f32)
+
+    def mix(a, b, t):
+        return ((a * (f32(1) - t).astype(f32)).astype(f32) + (b * t).astype(f32)).astype(f32)
+
+    for h in range(H):
+        mag = np.sqrt((re[h] * re[h]).astype(f32) + (im[h] * im[h]).astype(f32)).astype(f32)
+        phase = np.arctan2(im[h], re[h]).astype(f32)
+        target = (bins * omega_scale).astype(f32)
+        delta = _principal_arg(((phase - prev).astype(f32) - target).astype(f32))
+        omega = (target + delta).astype(f32)
+        prev = phase
+        r = max(f32(ratio[h]), f32(1e-4))
+        src = (bins / r).astype(f32)
+        in_range = src <= f32(N - 1)
+        srcc = np.where(in_range, src, f32(N - 1)).astype(f32)
+        fl = np.floor(srcc).astype(f32)
+        i0 = fl.astype(np.int64)
+        i1 = np.where(i0 < N - 1, i0 + 1, i0)
+        frac = (srcc - fl).astype(f32)
+        imag_ = mix(mag[i0], mag[i1], frac)
+        iom = (mix(omega[i0], omega[i1], frac) * r).astype(f32)
+        iph = _principal_arg(mix(prev[i0], prev[i1], frac))
+        adv = _principal_arg((synth + iom).astype(f32))
+        synth = iph if init == 0.0 else adv
+        om = np.where(in_range, imag_, f32(0)).astype(f32)
+        out_re[h] = (om * np.cos(synth).astype(f32)).astype(f32)
+        out_im[h] = (om * np.sin(synth).astype(f32)).astype(f32)
+        init = 1.0
+    return out_re, out_im, (prev, synth, init)

@@ -178,3 +178,115 @@ def test_argument_errors(ctx):
     with pytest.raises(dgen_b200.DgenCudaError):
         ctx.check(ctx.lib.dgc_delay_line(ctx.h, x.data_ptr(), x.data_ptr(), 0, 8, 2, 16, x.data_ptr(), None,
                                          torch.empty_like(x).data_ptr()))     # ring without head
+
+
+# ---- standalone spectral blocks and the phase vocoder ----------------------------------------------------------
+from oracle import oracle as orc
+
+
+def oracle_stft(x, N, hop, window):
+    T = x.size
+    H = (T + hop - 1) // hop
+    re, im = np.zeros((H, N), f32), np.zeros((H, N), f32)
+    xp = np.concatenate([np.zeros(N - 1, f32), x])
+    for h in range(H):
+        w = xp[h * hop:h * hop + N]          # bufferView: element i of hop frame f = x[f - N + 1 + i]
+        if window is not None:
+            w = (w * window).astype(f32)
+        re[h], im[h] = orc.fft(w, np.zeros(N, f32))
+    return re, im
+
+
+def oracle_istft_ola(re, im, T, hop, window, gain=1.0):
+    H, N = re.shape
+    frames = np.zeros((H, N), f32)
+    for h in range(H):
+        r, _ = orc.fft(re[h], im[h], inverse=True)
+        r = (r * f32(1.0 / N)).astype(f32)          # the reference scales the inverse transform by 1/N
+        if window is not None:
+            r = (r * window).astype(f32)
+        frames[h] = (r * f32(gain)).astype(f32)
+    return orc.overlap_add(frames, T, hop)
+
+
+def test_oracle_fft_inverse_is_unnormalised():
+    re, im = orc.fft(np.asarray([1, 0, 0, 0, 0, 0, 0, 0] * 2, f32), np.zeros(16, f32))
+    r, _ = orc.fft(re, im, inverse=True)
+    assert abs(r[0] - 16.0) < 1e-4      # so oracle_istft_ola applies the 1/N itself
+
+
+@pytest.mark.parametrize("N,hop,T,V", [(16, 8, 200, 1), (256, 64, 5000, 3), (1024, 256, 16000, 2), (2048, 1024, 9000, 1)])
+def test_stft_fwd_and_istft_ola(ctx, N, hop, T, V):
+    rng = np.random.default_rng(N + T)
+    x = rng.standard_normal((V, T)).astype(f32)
+    win = orc.hann_periodic(N)
+    re, im = ctx.stft(dev(x), N, hop, window=dev(win))
+    for v in range(V):
+        wr, wi = oracle_stft(x[v], N, hop, win)
+        scale = max(np.abs(wr).max(), np.abs(wi).max())
+        assert np.abs(re[v].cpu().numpy() - wr).max() <= 2e-6 * scale * np.log2(N)
+        assert np.abs(im[v].cpu().numpy() - wi).max() <= 2e-6 * scale * np.log2(N)
+    # inverse of ARBITRARY (non-Hermitian) spectra: the real part of the inverse transform is kept
+    sr = rng.standard_normal(tuple(re.shape)).astype(f32)
+    si = rng.standard_normal(tuple(re.shape)).astype(f32)
+    y = ctx.istft_ola(dev(sr), dev(si), T, hop, window=dev(win), gain=0.5)
+    for v in range(V):
+        want = oracle_istft_ola(sr[v], si[v], T, hop, win, 0.5)
+        assert np.abs(y[v].cpu().numpy() - want).max() <= 2e-6 * max(1.0, np.abs(want).max()) * np.log2(N)
+    # Tests/DGenLazyTests/AcceleratedFFTTests.swift:11-140: FFT -> IFFT -> overlap-add of unwindowed frames scales the
+    # signal by N / hop once every frame is covered by N / hop windows
+    re, im = ctx.stft(dev(x), N, hop)
+    back = ctx.istft_ola(re, im, T, hop).cpu().numpy()
+    # window h = x[h*hop-N+1 .. h*hop], laid back at h*hop .. h*hop+N-1: a delay of N - 1 frames
+    d = N - 1
+    lo, hi = d + N, T - N
+    if hi > lo:
+        assert np.abs(back[:, lo:hi] - (N / hop) * x[:, lo - d:hi - d]).max() <= 1e-4 * (N / hop) * np.abs(x).max()
+
+
+def test_phase_vocoder_against_restatement(ctx):
+    rng = np.random.default_rng(77)
+    V, H, N, hop = 3, 40, 64, 16
+    re = rng.standard_normal((V, H, N)).astype(f32)
+    im = rng.standard_normal((V, H, N)).astype(f32)
+    ratio = np.stack([np.full(H, 1.0, f32), np.full(H, 1.5, f32), (0.5 + rng.random(H)).astype(f32)])
+    ratio[2, 5] = -3.0                                # raised to 1e-4: nothing in range but bin 0
+    state = torch.zeros(V, 2 * N + 1, device="cuda")
+    a_re, a_im = ctx.phase_vocoder(dev(re[:, :17]), dev(im[:, :17]), dev(ratio[:, :17]), hop, state=state)
+    b_re, b_im = ctx.phase_vocoder(dev(re[:, 17:]), dev(im[:, 17:]), dev(ratio[:, 17:]), hop, state=state)
+    got_re, got_im = torch.cat([a_re, b_re], 1).cpu().numpy(), torch.cat([a_im, b_im], 1).cpu().numpy()
+    for v in range(V):
+        w_re, w_im, st = so.phase_vocoder(re[v], im[v], ratio[v], hop)
+        err = np.maximum(np.abs(got_re[v] - w_re), np.abs(got_im[v] - w_im))
+        # the synthesis phase accumulates over the hops; a phase difference within rounding of +-pi flips a wrap in
+        # one implementation and not in the other, a 2 pi (ratio - 1) jump for that bin: bound the bulk tightly
+        assert np.quantile(err, 0.995) <= 2e-4 * np.abs(w_re).max(), v
+        assert float(state[v, 2 * N].cpu()) == 1.0
+    # ratio 1 returns the input (the synthesis phase tracks the analysis phase)
+    assert np.abs(got_re[0] - re[0]).max() <= 1e-4 * np.abs(re[0]).max()
+    assert np.abs(got_im[0] - im[0]).max() <= 1e-4 * np.abs(im[0]).max()
+    # one ratio for all voices and hops
+    o_re, _ = ctx.phase_vocoder(dev(re), dev(im), 1.5, hop)
+    w_re, _, _ = so.phase_vocoder(re[1], im[1], np.full(H, 1.5, f32), hop)
+    assert np.quantile(np.abs(o_re[1].cpu().numpy() - w_re), 0.995) <= 2e-4 * np.abs(w_re).max()
+
+
+def test_pitch_shift_chain_moves_a_sinusoid(ctx):
+    """Tests/DGenTests/PhaseVocoderTests.swift:99-150: buffer -> FFT -> phase vocoder -> IFFT -> overlap-add; an octave
+    up roughly doubles the zero-crossing rate of a sinusoid, ratio 1 keeps it."""
+    sr, T, N, hop = 44100.0, 32768, 1024, 256
+    t = np.arange(T, dtype=f32) / f32(sr)
+    x = np.sin(2 * np.pi * 440.0 * t).astype(f32)[None, :]
+    win = dev(orc.hann_periodic(N))
+    re, im = ctx.stft(dev(x), N, hop, window=win)
+
+    def crossings(ratio):
+        o_re, o_im = ctx.phase_vocoder(re, im, ratio, hop)
+        y = ctx.istft_ola(o_re, o_im, T, hop, window=win).cpu().numpy()[0, 4096:-4096]
+        assert np.isfinite(y).all() and np.abs(y).max() > 0.01
+        return int(np.sum(np.signbit(y[1:]) != np.signbit(y[:-1])))
+
+    same, up = crossings(1.0), crossings(2.0)
+    base = int(np.sum(np.signbit(x[0, 4097:-4096]) != np.signbit(x[0, 4096:-4097])))
+    assert abs(same - base) <= 0.02 * base
+    assert 1.8 * base <= up <= 2.2 * base
