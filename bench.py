@@ -382,7 +382,7 @@ def run_train(args, rank, world, local_rank):
     dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
     pin = lambda a: torch.from_numpy(np.ascontiguousarray(a)).pin_memory()
     model = tr.HarmonicModel(ctx, B, T, K=K, F=F, sr=sr, nbands=NB, taps=NT, hidden=512, ir_len=16000, conv_n=2048,
-                             conv_hop=1024, sizes=SIZES, seed=7, global_voices=B * world)
+                             conv_hop=1024, sizes=SIZES, seed=7, global_voices=B * world, counted_adam=True)
     # gradient exchange: the context's own NCCL communicator (dgc_allreduce_sum through the C ABI) unless
     # --allreduce torch asks for the torch.distributed call
     model.use_ctx_comm = args.allreduce == "dgc" and sharding.init_ctx_comm(ctx)
@@ -404,6 +404,16 @@ def run_train(args, rank, world, local_rank):
 
     for _ in range(args.warmup):
         model.step(*dargs)
+    # step mode: "replay" records the whole step once (both streams, gradient exchange, Adam) and launches the
+    # recording per step; "eager" enqueues it call by call.  Default: replay on one GPU, eager on several.
+    mode = args.step_mode if args.step_mode != "auto" else ("replay" if world == 1 else "eager")
+    if mode == "replay":
+        model.capture(*dargs)
+        step_fn = model.replay
+        for _ in range(2):
+            step_fn()
+    else:
+        step_fn = lambda: model.step(*dargs)
     barrier()
     l0 = ctx.launch_count()
     sampler = ClockSampler(local_rank)
@@ -413,7 +423,7 @@ def run_train(args, rank, world, local_rank):
     barrier()
     for s in range(args.steps):
         evs[s][0].record()
-        loss = model.step(*dargs)
+        loss = step_fn()
         evs[s][1].record()
     barrier()
     launches = ctx.launch_count() - l0
@@ -426,7 +436,7 @@ def run_train(args, rank, world, local_rank):
         a.record()
         for k in order:
             D[k].copy_(P[k], non_blocking=True)
-        loss = model.step(*dargs)
+        loss = step_fn()
         loss_host = float(loss.cpu()[0])
         b.record()
         torch.cuda.synchronize()
@@ -444,7 +454,7 @@ def run_train(args, rank, world, local_rank):
                 "config": {"workload": "full training step (BASELINE.json configs[4])", "voices_per_gpu": B,
                            "global_voices": B * world, "frames": T, "harmonics": K, "control_frames": F,
                            "controller": "MLP 2-512-512-512-165 fp32", "ir_taps": 16000, "fft_sizes": list(SIZES),
-                           "optimizer": "Adam lr 1e-3", "parallelism": "dp%d, NCCL all-reduce of %d gradients (%s)"
+                           "optimizer": "Adam lr 1e-3", "step_mode": mode, "parallelism": "dp%d, NCCL all-reduce of %d gradients (%s)"
                            % (world, model.n_params,
                               "dgc_allreduce_sum" if model.use_ctx_comm else "torch.distributed"), "l2": "working set (>1 GB per step) exceeds L2"},
                 "samples_per_s": B * world * T / (ms * 1e-3), "clocks": clocks,
@@ -463,6 +473,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--step-mode", default="auto", choices=["auto", "eager", "replay"],
+                    help="training workload: enqueue the step call by call, or replay one recording of it")
     ap.add_argument("--workload", default="fwd_loss", choices=["fwd_loss", "train"],
                     help="fwd_loss: synthesis forward + loss (the headline metric); train: full training step")
     ap.add_argument("--allreduce", default="dgc", choices=["dgc", "torch"],

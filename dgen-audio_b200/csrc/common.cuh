@@ -49,6 +49,10 @@ struct dgc_ctx {
   // NCCL communicator of the gradient exchange (comm.cu); nullptr = a world of one
   void *comm = nullptr;
   int comm_world = 1;
+  // step recording (graph.cu)
+  bool capturing = false;
+  cudaStream_t capture_stream = nullptr;   // the stream the recording started on (calls inside may rebind the context)
+  int64_t capture_launches0 = 0;
 };
 
 int32_t dgc_fail(dgc_ctx *ctx, int32_t code, const char *fmt, ...);

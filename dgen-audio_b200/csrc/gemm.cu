@@ -406,6 +406,47 @@ DGC_EXPORT int32_t dgc_adam_step(dgc_ctx *ctx, float *theta_dev, const float *gr
   return DGC_OK;
 }
 
+// The same step with the 1-based step index kept in device memory, so that a recorded step (graph.cu) advances it
+// on every replay: a one-thread kernel increments *t_dev and evaluates the two bias corrections (in double, then
+// rounded: the correctly rounded single-precision power), the update kernel reads them.
+namespace {
+__global__ void adam_tick_kernel(int32_t *t_dev, float beta1, float beta2, float *corr) {
+  const int32_t t = *t_dev + 1;
+  *t_dev = t;
+  corr[0] = 1.0f - (float)pow((double)beta1, (double)t);
+  corr[1] = 1.0f - (float)pow((double)beta2, (double)t);
+}
+
+__global__ void adam_counted_kernel(float *__restrict__ theta, const float *__restrict__ g, float *__restrict__ m,
+                                    float *__restrict__ v, uint64_t n, float lr, float b1, float b2, float eps,
+                                    const float *__restrict__ corr) {
+  uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const float c1 = corr[0], c2 = corr[1];
+  float gi = g[i];
+  float mi = __fadd_rn(__fmul_rn(b1, m[i]), __fmul_rn(1.0f - b1, gi));
+  float vi = __fadd_rn(__fmul_rn(b2, v[i]), __fmul_rn(__fmul_rn(1.0f - b2, gi), gi));
+  m[i] = mi;
+  v[i] = vi;
+  float mh = __fdiv_rn(mi, c1), vh = __fdiv_rn(vi, c2);
+  theta[i] = __fsub_rn(theta[i], __fdiv_rn(__fmul_rn(lr, mh), __fadd_rn(__fsqrt_rn(vh), eps)));
+}
+}  // namespace
+
+DGC_EXPORT int32_t dgc_adam_step_counted(dgc_ctx *ctx, float *theta_dev, const float *grad_dev, float *m_dev,
+                                         float *v_dev, uint64_t n, int32_t *t_dev, float *corr_dev, float lr,
+                                         float beta1, float beta2, float eps) {
+  if (!ctx) return DGC_ERR_INVALID;
+  DGC_REQUIRE(ctx, theta_dev && grad_dev && m_dev && v_dev && t_dev && corr_dev, "null pointer");
+  adam_tick_kernel<<<1, 1, 0, ctx->stream>>>(t_dev, beta1, beta2, corr_dev);
+  DGC_LAUNCHED(ctx, "adam_tick");
+  if (n == 0) return DGC_OK;
+  adam_counted_kernel<<<dgc_div_up((int64_t)n, 256), 256, 0, ctx->stream>>>(theta_dev, grad_dev, m_dev, v_dev, n, lr,
+                                                                            beta1, beta2, eps, corr_dev);
+  DGC_LAUNCHED(ctx, "adam");
+  return DGC_OK;
+}
+
 #ifdef DGC_KK_TIMING
 DGC_EXPORT int32_t dgc_debug_kk_times(unsigned long long *out8) {
   cudaDeviceSynchronize();

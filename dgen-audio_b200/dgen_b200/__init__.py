@@ -136,6 +136,12 @@ SIGNATURES = {
     "dgc_linear_bwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp]),
     "dgc_adam_step": (_i32, [_vp, _vp, _vp, _vp, _vp, _u64, _i32, _f, _f, _f, _f]),
     "dgc_sanitize": (_i32, [_vp, _vp, _u64, _vp]),
+    "dgc_adam_step_counted": (_i32, [_vp, _vp, _vp, _vp, _vp, _u64, _vp, _vp, _f, _f, _f, _f]),
+    "dgc_graph_begin": (_i32, [_vp]),
+    "dgc_graph_end": (_i32, [_vp, C.POINTER(_vp)]),
+    "dgc_graph_nodes": (_u64, [_vp]),
+    "dgc_graph_launch": (_i32, [_vp, _vp]),
+    "dgc_graph_destroy": (_i32, [_vp]),
     "dgc_stft_scratch_floats": (_u64, [_i32, _i32, _i32, _i32, _i32]),
     "dgc_stft_fwd": (_i32, [_vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp]),
     "dgc_istft_ola": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _f, _vp, _i32, _vp]),
@@ -230,6 +236,44 @@ def _ptr(t):
         return None
     assert t.is_cuda and t.is_contiguous(), "expected a contiguous CUDA tensor"
     return t.data_ptr()
+
+
+class StepGraph:
+    """A recorded step (dgc_graph): launch() replays it on the context's stream."""
+
+    def __init__(self, ctx, handle):
+        self.ctx, self.h = ctx, handle
+
+    @property
+    def nodes(self):
+        return int(self.ctx.lib.dgc_graph_nodes(self.h))
+
+    def launch(self):
+        self.ctx.check(self.ctx.lib.dgc_graph_launch(self.ctx.h, self.h))
+
+    def close(self):
+        if self.h:
+            self.ctx.lib.dgc_graph_destroy(self.h)
+            self.h = None
+
+
+class _Recording:
+    def __init__(self, ctx):
+        self.ctx, self.graph = ctx, None
+
+    def __enter__(self):
+        self.ctx.check(self.ctx.lib.dgc_graph_begin(self.ctx.h))
+        return self
+
+    def __exit__(self, et, ev, tb):
+        out = _vp()
+        rc = self.ctx.lib.dgc_graph_end(self.ctx.h, C.byref(out))
+        if et is None:
+            self.ctx.check(rc)
+            self.graph = StepGraph(self.ctx, out)
+        elif rc == 0 and out:
+            self.ctx.lib.dgc_graph_destroy(out)
+        return False
 
 
 class Context:
@@ -486,6 +530,16 @@ class Context:
     def adam_step(self, theta, grad, m, v, t, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8):
         self.check(self.lib.dgc_adam_step(self.h, _ptr(theta), _ptr(grad), _ptr(m), _ptr(v), theta.numel(), t, lr,
                                           beta1, beta2, eps))
+
+    def adam_step_counted(self, theta, grad, m, v, t_dev, corr, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8):
+        """Adam with the step index in device memory (t_dev: int32 [1], corr: float32 [2] work cell)."""
+        self.check(self.lib.dgc_adam_step_counted(self.h, _ptr(theta), _ptr(grad), _ptr(m), _ptr(v), theta.numel(),
+                                                  _ptr(t_dev), _ptr(corr), lr, beta1, beta2, eps))
+
+    def record(self):
+        """Context manager: library calls (and torch work on the same stream) inside are recorded, not run;
+        `.graph` afterwards holds the StepGraph to replay.  The context must be on a non-default stream."""
+        return _Recording(self)
 
     def sanitize(self, x, out=None):
         """Non-finite -> 0 (toolchain/include/dgen_runtime.h:72-84); in place when out is None."""

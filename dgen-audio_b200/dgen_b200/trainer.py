@@ -22,7 +22,7 @@ from . import Context, FirParams, HarmonicParams, PHASE_SCAN, mss_params, shardi
 class HarmonicModel:
     def __init__(self, ctx: Context, B, T, K=100, F=1000, sr=16000.0, nbands=65, taps=257, hidden=512, in_features=2,
                  ir_len=16000, conv_n=2048, conv_hop=1024, sizes=(2048, 1024, 512, 256, 128, 64), seed=0,
-                 phase_mode=PHASE_SCAN, global_voices=None):
+                 phase_mode=PHASE_SCAN, global_voices=None, counted_adam=False):
         import torch
         self.torch, self.ctx = torch, ctx
         self.B, self.T, self.K, self.F, self.sr = B, T, K, F, sr
@@ -56,6 +56,11 @@ class HarmonicModel:
         self.m = torch.zeros_like(self.params)
         self.v = torch.zeros_like(self.params)
         self.step_index = 0
+        # step index in device memory: a recorded step advances it on every replay
+        self.counted_adam = counted_adam
+        self.t_dev = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.corr = torch.zeros(2, dtype=torch.float32, device=dev)
+        self.graph, self.graph_stream = None, None
         f = lambda *s: torch.empty(*s, dtype=torch.float32, device=dev)
         M, H = self.M, hidden
         self.act = [f(M, H), f(M, H), f(M, H), f(M, K + nbands)]
@@ -184,6 +189,7 @@ class HarmonicModel:
         self.m.zero_()
         self.v.zero_()
         self.step_index = 0
+        self.t_dev.zero_()
 
     def step(self, X, f0, uv, gain, noise_gain, noise, w_fs, target, lr=1e-3):
         """forward + backward + gradient all-reduce + Adam; returns the device loss tensor (local mean)."""
@@ -194,7 +200,44 @@ class HarmonicModel:
         else:
             sharding.allreduce_sum_(self.grads)   # torch.distributed process group
         self.step_index += 1
-        self.ctx.adam_step(self.params, self.grads, self.m, self.v, self.step_index, lr=lr)
+        if self.counted_adam:
+            self.ctx.adam_step_counted(self.params, self.grads, self.m, self.v, self.t_dev, self.corr, lr=lr)
+        else:
+            self.ctx.adam_step(self.params, self.grads, self.m, self.v, self.step_index, lr=lr)
+        return self.loss
+
+    def capture(self, X, f0, uv, gain, noise_gain, noise, w_fs, target, lr=1e-3):
+        """Record one whole training step (both streams, the gradient exchange, Adam) on the given tensors, which
+        become the step's static input buffers: refill them in place and call replay().  Where the reference
+        rebuilds and recompiles its graph every step (Sources/DGenLazy/Backward.swift:225), this keeps one recording
+        per model.  Needs counted_adam=True and one eager step() before it (so that nothing allocates inside)."""
+        torch = self.torch
+        if not self.counted_adam:
+            raise ValueError("capture() needs a model built with counted_adam=True")
+        if self.step_index == 0:
+            raise ValueError("run one eager step() before capture(): first-use allocations cannot be recorded")
+        if self.graph_stream is None:
+            self.graph_stream = torch.cuda.Stream(device="cuda:%d" % self.ctx.device)
+        s = self.graph_stream
+        s.wait_stream(torch.cuda.current_stream())
+        with self.ctx.on_stream(s), torch.cuda.stream(s):
+            with self.ctx.record() as rec:
+                self.step(X, f0, uv, gain, noise_gain, noise, w_fs, target, lr=lr)
+        self.step_index -= 1          # recording runs nothing
+        if self.graph is not None:
+            self.graph.close()
+        self.graph = rec.graph
+        return self.graph
+
+    def replay(self):
+        """One recorded step; returns the device loss tensor."""
+        torch = self.torch
+        cur, s = torch.cuda.current_stream(), self.graph_stream
+        s.wait_stream(cur)            # the caller refilled the inputs on its own stream
+        with self.ctx.on_stream(s):
+            self.graph.launch()
+        cur.wait_stream(s)
+        self.step_index += 1
         return self.loss
 
 

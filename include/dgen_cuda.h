@@ -323,6 +323,13 @@ int32_t dgc_linear_bwd(dgc_ctx *ctx, const float *a_dev, const float *w_dev, con
 int32_t dgc_adam_step(dgc_ctx *ctx, float *theta_dev, const float *grad_dev, float *m_dev, float *v_dev, uint64_t n,
                       int32_t t, float lr, float beta1, float beta2, float eps);
 
+/* The same step with the step index kept on the device: *t_dev (int32, 0 before the first step) is incremented by
+ * the call and the bias corrections are evaluated on the device into corr_dev[2], so a recorded step (dgc_graph_*)
+ * advances the index on every replay. */
+int32_t dgc_adam_step_counted(dgc_ctx *ctx, float *theta_dev, const float *grad_dev, float *m_dev, float *v_dev,
+                              uint64_t n, int32_t *t_dev, float *corr_dev, float lr, float beta1, float beta2,
+                              float eps);
+
 /* Output sanitiser: out[i] = in[i] when its IEEE-754 exponent field is not all ones, else +0.0f (NaN and
  * +-Inf become 0; denormals, -0.0 and every finite value pass through bit for bit).  in_dev == out_dev is
  * allowed.  Replaces dgen_sanitize_f32 / dgen_sanitize_f32x4 applied at every `output` store
@@ -384,6 +391,22 @@ uint64_t dgc_phase_vocoder_scratch_floats(int32_t V, int64_t H, int32_t N);
 int32_t dgc_phase_vocoder(dgc_ctx *ctx, const float *re_dev, const float *im_dev, const float *ratio_dev,
                           int32_t ratio_mode, int32_t V, int64_t H, int32_t N, int32_t hop, float *state_dev,
                           float *scratch_dev, float *out_re_dev, float *out_im_dev);
+
+/* ---- step replay ---------------------------------------------------------------------------------------
+ * Record everything enqueued through this context between dgc_graph_begin and dgc_graph_end (work the host puts on
+ * other streams that fork from and join back into the context's stream is recorded with it), then replay it with
+ * one dgc_graph_launch per step.
+ * replaces: the per-step graph rebuild, recompilation and tensor re-upload of the reference's training loop
+ * (Sources/DGenLazy/Backward.swift:225, Sources/DGenLazy/Realize.swift:285-290, Sources/DGenLazy/LazyGraph.swift:171-234).
+ * The context must be bound to a non-default stream; run the step once before recording it, so that nothing inside
+ * the recording allocates; values passed by value are frozen into the recording -- refill input buffers in place and
+ * use dgc_adam_step_counted.  dgc_graph_end reports an invalidated recording as DGC_ERR_CUDA with the reason. */
+typedef struct dgc_graph dgc_graph;
+int32_t dgc_graph_begin(dgc_ctx *ctx);
+int32_t dgc_graph_end(dgc_ctx *ctx, dgc_graph **out);
+uint64_t dgc_graph_nodes(const dgc_graph *g);
+int32_t dgc_graph_launch(dgc_ctx *ctx, dgc_graph *g);
+int32_t dgc_graph_destroy(dgc_graph *g);
 
 /* ---- generated blocks -------------------------------------------------------------------------------
  * Device code the host's renderer emits for elementwise blocks that no primitive above covers.

@@ -118,3 +118,64 @@ def test_checkpoint_round_trip_through_the_reference_file_format(tmp_path):
     y, sr = rf.wav_load(os.path.join(run.renders, "pred.wav"))
     assert sr == d["sr"] and np.array_equal(y, b.out[0].cpu().numpy())
     ctx.close()
+
+
+def test_recorded_step_replays_like_eager_steps():
+    """One recording of the whole training step (both streams, Adam with the step index on the device), replayed
+    with refilled inputs, against the same steps enqueued call by call."""
+    B, T, K, F, NB, NT = 2, 4096, 16, 32, 9, 33
+    ds = [wl.harmonic_noise_inputs(61 + i, B=B, T=T, K=K, F=F, nbands=NB, taps=NT) for i in range(3)]
+    targets = [orc.harmonic_noise_render(d["f0"], d["uv"], d["amps"], d["gain"], d["noise_gain"], wl.taps_from_bands(d),
+                                         d["noise"], T, d["sr"]) for d in ds]
+
+    def host_args(i):
+        d = ds[i]
+        return [tr.features_from_controls(d["f0"], d["gain"]), d["f0"], d["uv"], d["gain"], d["noise_gain"], d["noise"],
+                d["W"], targets[i]]
+
+    ctx = dgen_b200.Context(0)
+    kw = dict(K=K, F=F, nbands=NB, taps=NT, hidden=32, ir_len=512, conv_n=128, conv_hop=64, sizes=(256, 64), seed=3,
+              counted_adam=True)
+    eager = tr.HarmonicModel(ctx, B, T, **kw)
+    order = [0, 1, 2, 1, 0]
+    eager_losses = [float(eager.step(*[dev(a) for a in host_args(i)], lr=2e-3).cpu()[0]) for i in order]
+
+    rec = tr.HarmonicModel(ctx, B, T, **kw)
+    static = [dev(a) for a in host_args(order[0])]
+    losses = [float(rec.step(*static, lr=2e-3).cpu()[0])]            # eager warm-up step = step 1
+    g = rec.capture(*static, lr=2e-3)
+    assert g.nodes > 20 and rec.step_index == 1
+    launches0 = ctx.launch_count()
+    for i in order[1:]:
+        for buf, a in zip(static, host_args(i)):
+            buf.copy_(torch.from_numpy(np.ascontiguousarray(a)))      # refill the static inputs in place
+        losses.append(float(rec.replay().cpu()[0]))
+    assert ctx.launch_count() - launches0 >= 4 * 20                   # replays count the launches they stand for
+    assert rec.step_index == 5 and int(rec.t_dev.cpu()[0]) == 5
+    assert np.allclose(losses, eager_losses, rtol=1e-6, atol=0)
+    assert torch.allclose(rec.params, eager.params, rtol=1e-6, atol=1e-9)
+    assert torch.allclose(rec.m, eager.m, rtol=1e-6, atol=1e-12)
+    # a model without the device-side step index cannot be recorded, nor one that has not run yet
+    plain = tr.HarmonicModel(ctx, B, T, **dict(kw, counted_adam=False))
+    with pytest.raises(ValueError):
+        plain.capture(*static)
+    with pytest.raises(ValueError):
+        tr.HarmonicModel(ctx, B, T, **kw).capture(*static)
+    ctx.close()
+
+
+def test_counted_adam_matches_host_indexed_adam():
+    ctx = dgen_b200.Context(0)
+    rng = np.random.default_rng(9)
+    n = 5000
+    th0, g = rng.standard_normal(n).astype(np.float32), rng.standard_normal((4, n)).astype(np.float32)
+    a = [dev(th0), dev(np.zeros(n, np.float32)), dev(np.zeros(n, np.float32))]
+    b = [dev(th0), dev(np.zeros(n, np.float32)), dev(np.zeros(n, np.float32))]
+    t_dev, corr = torch.zeros(1, dtype=torch.int32, device="cuda"), torch.zeros(2, device="cuda")
+    for t in range(1, 5):
+        ctx.adam_step(a[0], dev(g[t - 1]), a[1], a[2], t, lr=1e-2)
+        ctx.adam_step_counted(b[0], dev(g[t - 1]), b[1], b[2], t_dev, corr, lr=1e-2)
+    assert int(t_dev.cpu()[0]) == 4
+    # the two differ at most by the rounding of the bias corrections (host powf against the device's rounded pow)
+    assert torch.allclose(a[0], b[0], rtol=2e-6, atol=1e-8)
+    ctx.close()
