@@ -404,9 +404,9 @@ def run_train(args, rank, world, local_rank):
 
     for _ in range(args.warmup):
         model.step(*dargs)
-    # step mode: "replay" records the whole step once (both streams, gradient exchange, Adam) and launches the
-    # recording per step; "eager" enqueues it call by call.  Default: replay on one GPU, eager on several.
-    mode = args.step_mode if args.step_mode != "auto" else ("replay" if world == 1 else "eager")
+    # step mode: "replay" records the step once (both streams, Adam; with several ranks the gradient exchange stays
+    # between two recordings) and launches the recording per step; "eager" enqueues it call by call.
+    mode = args.step_mode if args.step_mode != "auto" else "replay"
     if mode == "replay":
         model.capture(*dargs)
         step_fn = model.replay

@@ -32,6 +32,10 @@ def max_over_ranks(values, device="cpu"):
     return [float(v) for v in t]
 
 
+def world_size():
+    return dist.get_world_size() if dist.is_initialized() else 1
+
+
 def allreduce_sum_(flat_grad):
     """In-place sum of a flat gradient buffer over ranks (controller-parameter gradients)."""
     if dist.is_initialized() and dist.get_world_size() > 1:

@@ -60,7 +60,7 @@ class HarmonicModel:
         self.counted_adam = counted_adam
         self.t_dev = torch.zeros(1, dtype=torch.int32, device=dev)
         self.corr = torch.zeros(2, dtype=torch.float32, device=dev)
-        self.graph, self.graph_stream = None, None
+        self.graph, self.graph_stream = None, None   # list of recordings (see capture)
         f = lambda *s: torch.empty(*s, dtype=torch.float32, device=dev)
         M, H = self.M, hidden
         self.act = [f(M, H), f(M, H), f(M, H), f(M, K + nbands)]
@@ -191,26 +191,43 @@ class HarmonicModel:
         self.step_index = 0
         self.t_dev.zero_()
 
-    def step(self, X, f0, uv, gain, noise_gain, noise, w_fs, target, lr=1e-3):
-        """forward + backward + gradient all-reduce + Adam; returns the device loss tensor (local mean)."""
-        self.forward(X, f0, uv, gain, noise_gain, noise, w_fs, target)
-        self.backward(X, f0, uv, gain, noise_gain, noise, w_fs, target)
+    def _exchange(self):
         if getattr(self, "use_ctx_comm", False):
             self.ctx.allreduce_sum_(self.grads)   # NCCL communicator owned by the context (C ABI)
         else:
             sharding.allreduce_sum_(self.grads)   # torch.distributed process group
-        self.step_index += 1
+
+    def _exchanges(self):
+        """True when the gradient sum really crosses ranks."""
+        if getattr(self, "use_ctx_comm", False):
+            return True
+        return sharding.world_size() > 1
+
+    def _update(self, lr):
         if self.counted_adam:
             self.ctx.adam_step_counted(self.params, self.grads, self.m, self.v, self.t_dev, self.corr, lr=lr)
         else:
             self.ctx.adam_step(self.params, self.grads, self.m, self.v, self.step_index, lr=lr)
+
+    def step(self, X, f0, uv, gain, noise_gain, noise, w_fs, target, lr=1e-3):
+        """forward + backward + gradient all-reduce + Adam; returns the device loss tensor (local mean)."""
+        self.forward(X, f0, uv, gain, noise_gain, noise, w_fs, target)
+        self.backward(X, f0, uv, gain, noise_gain, noise, w_fs, target)
+        self._exchange()
+        self.step_index += 1
+        self._update(lr)
         return self.loss
 
     def capture(self, X, f0, uv, gain, noise_gain, noise, w_fs, target, lr=1e-3):
-        """Record one whole training step (both streams, the gradient exchange, Adam) on the given tensors, which
-        become the step's static input buffers: refill them in place and call replay().  Where the reference
-        rebuilds and recompiles its graph every step (Sources/DGenLazy/Backward.swift:225), this keeps one recording
-        per model.  Needs counted_adam=True and one eager step() before it (so that nothing allocates inside)."""
+        """Record one whole training step (both streams, Adam) on the given tensors, which become the step's static
+        input buffers: refill them in place and call replay().  Where the reference rebuilds and recompiles its
+        graph every step (Sources/DGenLazy/Backward.swift:225), this keeps one recording per model.  Needs
+        counted_adam=True and one eager step() before it (so that nothing allocates inside).
+
+        With one rank the step is ONE recording.  With several the gradient exchange stays outside: forward +
+        backward is one recording, the all-reduce is enqueued call by call between, the update is a second one
+        (a collective inside a recording makes every rank's replay depend on the others' through the library's
+        own host threads; the call-by-call exchange is the path the multi-GPU runs have verified)."""
         torch = self.torch
         if not self.counted_adam:
             raise ValueError("capture() needs a model built with counted_adam=True")
@@ -220,22 +237,34 @@ class HarmonicModel:
             self.graph_stream = torch.cuda.Stream(device="cuda:%d" % self.ctx.device)
         s = self.graph_stream
         s.wait_stream(torch.cuda.current_stream())
+        args = (X, f0, uv, gain, noise_gain, noise, w_fs, target)
+        split = self._exchanges()
         with self.ctx.on_stream(s), torch.cuda.stream(s):
             with self.ctx.record() as rec:
-                self.step(X, f0, uv, gain, noise_gain, noise, w_fs, target, lr=lr)
-        self.step_index -= 1          # recording runs nothing
-        if self.graph is not None:
-            self.graph.close()
-        self.graph = rec.graph
-        return self.graph
+                self.forward(*args)
+                self.backward(*args)
+                if not split:
+                    self._update(lr)
+            graphs = [rec.graph]
+            if split:
+                with self.ctx.record() as rec2:
+                    self._update(lr)
+                graphs.append(rec2.graph)
+        for g in self.graph or []:
+            g.close()
+        self.graph = graphs
+        return graphs
 
     def replay(self):
         """One recorded step; returns the device loss tensor."""
         torch = self.torch
         cur, s = torch.cuda.current_stream(), self.graph_stream
         s.wait_stream(cur)            # the caller refilled the inputs on its own stream
-        with self.ctx.on_stream(s):
-            self.graph.launch()
+        with self.ctx.on_stream(s), torch.cuda.stream(s):
+            self.graph[0].launch()
+            if len(self.graph) > 1:
+                self._exchange()
+                self.graph[1].launch()
         cur.wait_stream(s)
         self.step_index += 1
         return self.loss
