@@ -5,8 +5,16 @@
 // index), then compiled for sm_100a through dgc_module_compile.  The Swift-side renderer that walks the
 // reference's UOps would produce exactly this op list; it is host code of the reference and not part of
 // this library.
+//
+// Blocks that read and write state cells (history feedback, phasor, latch: the reference's SEQUENTIAL blocks,
+// Sources/DGen/Blocks/FeedbackAnalysis.swift:357-365) are emitted in a second form: one thread per tensor lane,
+// the frame loop inside the thread in frame order, every state cell of the lane held in a register across the
+// loop (loaded before, stored after).  Lanes are independent in the reference too (tensor history cells are
+// per element, Sources/DGen/HigherOps.swift:408-420), so this is the same computation with the lane loop
+// turned into the grid.
 #include <cstdio>
 #include <string>
+#include <vector>
 
 #include "common.cuh"
 
@@ -34,14 +42,38 @@ std::string t(int id) { return "t" + std::to_string(id); }
 
 }  // namespace
 
-DGC_EXPORT int32_t dgc_block_emit(const dgc_uop *ops, int32_t n_ops, const char *kernel_name, char *out,
-                                  uint64_t out_cap, uint64_t *needed) {
+static int32_t emit_block(const dgc_uop *ops, int32_t n_ops, const char *kernel_name, bool seq, char *out,
+                          uint64_t out_cap, uint64_t *needed) {
   if (!ops || n_ops <= 0 || !kernel_name || !needed) return DGC_ERR_INVALID;
   Emit e;
-  e.s += "// generated block: one thread per (frame, element) index i of `count`\n";
-  e.s += "extern \"C\" __global__ void " + std::string(kernel_name) + "(float *memory, int count) {\n";
-  e.line("int i = blockIdx.x * blockDim.x + threadIdx.x;");
-  e.line("if (i >= count) return;");
+  // state cells of the sequential form, in order of first use
+  std::vector<int> cells;
+  auto cell_var = [&](int cell) {
+    for (int c : cells)
+      if (c == cell) return "s" + std::to_string(cell);
+    cells.push_back(cell);
+    return "s" + std::to_string(cell);
+  };
+  if (!seq) {
+    e.s += "// generated block: one thread per (frame, element) index i of `count`\n";
+    e.s += "extern \"C\" __global__ void " + std::string(kernel_name) + "(float *memory, int count) {\n";
+    e.line("int i = blockIdx.x * blockDim.x + threadIdx.x;");
+    e.line("if (i >= count) return;");
+  } else {
+    for (int k = 0; k < n_ops; ++k) {
+      const int op = ops[k].op;
+      if (op == DGC_OP_HISTORY_READ || op == DGC_OP_HISTORY_WRITE || op == DGC_OP_PHASOR || op == DGC_OP_LATCH) {
+        if (ops[k].a < 0) return DGC_ERR_INVALID;
+        cell_var(ops[k].a);
+      }
+    }
+    e.s += "// generated sequential block: one thread per lane e of `lanes`, frames i in order, state cells in registers\n";
+    e.s += "extern \"C\" __global__ void " + std::string(kernel_name) + "(float *memory, int frames, int lanes) {\n";
+    e.line("int e = blockIdx.x * blockDim.x + threadIdx.x;");
+    e.line("if (e >= lanes) return;");
+    for (int c : cells) e.line("float s" + std::to_string(c) + " = memory[" + std::to_string(c) + " + e];");
+    e.line("for (int i = 0; i < frames; ++i) {");
+  }
   for (int k = 0; k < n_ops; ++k) {
     const dgc_uop &u = ops[k];
     auto ok = [&](int id) { return id >= 0 && id < k; };
@@ -115,6 +147,48 @@ DGC_EXPORT int32_t dgc_block_emit(const dgc_uop *ops, int32_t n_ops, const char 
         if (!need(3)) return DGC_ERR_INVALID;
         e.line(R + A + " > 0.0f ? " + B + " : " + Cc + ";");
         break;
+      // ---- lane-indexed memory and state ops: sequential form only ----
+      case DGC_OP_LOAD_LANE:
+        if (!seq) return DGC_ERR_UNSUPPORTED;
+        e.line(R + "memory[" + std::to_string(u.a) + " + e];");
+        break;
+      case DGC_OP_LOAD_FRAME_LANE:
+        if (!seq) return DGC_ERR_UNSUPPORTED;
+        e.line(R + "memory[" + std::to_string(u.a) + " + (size_t)i * lanes + e];");
+        break;
+      case DGC_OP_STORE_FRAME_LANE:
+        if (!seq) return DGC_ERR_UNSUPPORTED;
+        if (!ok(u.b)) return DGC_ERR_INVALID;
+        e.line("memory[" + std::to_string(u.a) + " + (size_t)i * lanes + e] = " + B + ";");
+        e.line(R + B + ";");
+        break;
+      case DGC_OP_HISTORY_READ:   // Sources/DGen/Emit+State.swift:150-224: the cell's current content
+        if (!seq) return DGC_ERR_UNSUPPORTED;
+        e.line(R + cell_var(u.a) + ";");
+        break;
+      case DGC_OP_HISTORY_WRITE:  // pass-through store: later reads (this frame or the next) see the new value
+        if (!seq) return DGC_ERR_UNSUPPORTED;
+        if (!ok(u.b)) return DGC_ERR_INVALID;
+        e.line(cell_var(u.a) + " = " + B + ";");
+        e.line(R + B + ";");
+        break;
+      case DGC_OP_PHASOR: {       // Sources/DGen/Definitions.swift:96-102, Emit+State.swift:322-369; imm = sample rate
+        if (!seq) return DGC_ERR_UNSUPPORTED;
+        if (!ok(u.b) || !ok(u.c)) return DGC_ERR_INVALID;
+        const std::string S = cell_var(u.a), N = "n" + std::to_string(k);
+        e.line(R + S + ";");                                       // the output is the phase BEFORE the update
+        e.line("float " + N + " = " + S + " + " + B + " / " + fl(u.imm) + ";");
+        e.line(N + " = " + N + " - floorf(" + N + ");");
+        e.line("if (" + N + " >= 1.0f) " + N + " -= 1.0f;");
+        e.line(S + " = " + Cc + " > 0.0f ? 0.0f : " + N + ";");
+        break;
+      }
+      case DGC_OP_LATCH:          // Sources/DGen/Definitions.swift:104-113: cell a, value t_b, cond t_c
+        if (!seq) return DGC_ERR_UNSUPPORTED;
+        if (!ok(u.b) || !ok(u.c)) return DGC_ERR_INVALID;
+        e.line("if (" + Cc + " > 0.0f) " + cell_var(u.a) + " = " + B + ";");
+        e.line(R + cell_var(u.a) + ";");
+        break;
       case DGC_OP_STORE:   // memory[a + i] = t_b ; the op's own value is the stored value
         if (!ok(u.b)) return DGC_ERR_INVALID;
         e.line("memory[" + std::to_string(u.a) + " + i] = " + B + ";");
@@ -130,6 +204,10 @@ DGC_EXPORT int32_t dgc_block_emit(const dgc_uop *ops, int32_t n_ops, const char 
       default: return DGC_ERR_UNSUPPORTED;
     }
   }
+  if (seq) {
+    e.line("}");
+    for (int c : cells) e.line("memory[" + std::to_string(c) + " + e] = s" + std::to_string(c) + ";");
+  }
   e.s += "}\n";
   *needed = e.s.size() + 1;
   if (out && out_cap >= *needed) memcpy(out, e.s.c_str(), *needed);
@@ -137,15 +215,37 @@ DGC_EXPORT int32_t dgc_block_emit(const dgc_uop *ops, int32_t n_ops, const char 
   return DGC_OK;
 }
 
-DGC_EXPORT int32_t dgc_block_compile(dgc_ctx *ctx, const dgc_uop *ops, int32_t n_ops, const char *kernel_name,
-                                     dgc_module **out) {
+DGC_EXPORT int32_t dgc_block_emit(const dgc_uop *ops, int32_t n_ops, const char *kernel_name, char *out,
+                                  uint64_t out_cap, uint64_t *needed) {
+  return emit_block(ops, n_ops, kernel_name, false, out, out_cap, needed);
+}
+
+DGC_EXPORT int32_t dgc_block_emit_sequential(const dgc_uop *ops, int32_t n_ops, const char *kernel_name, char *out,
+                                             uint64_t out_cap, uint64_t *needed) {
+  return emit_block(ops, n_ops, kernel_name, true, out, out_cap, needed);
+}
+
+static int32_t compile_block(dgc_ctx *ctx, const dgc_uop *ops, int32_t n_ops, const char *kernel_name, bool seq,
+                             dgc_module **out) {
   if (!ctx) return DGC_ERR_INVALID;
   DGC_REQUIRE(ctx, ops && n_ops > 0 && kernel_name && out, "null argument");
   uint64_t need = 0;
-  int32_t rc = dgc_block_emit(ops, n_ops, kernel_name, nullptr, 0, &need);
-  if (rc != DGC_OK) return dgc_fail(ctx, rc, "dgc_block_compile: malformed op list (operand ids must precede their use)");
+  int32_t rc = emit_block(ops, n_ops, kernel_name, seq, nullptr, 0, &need);
+  if (rc == DGC_ERR_UNSUPPORTED)
+    return dgc_fail(ctx, rc, "block compile: an op of the list is not available in this block form");
+  if (rc != DGC_OK) return dgc_fail(ctx, rc, "block compile: malformed op list (operand ids must precede their use)");
   std::string src(need, '\0');
-  rc = dgc_block_emit(ops, n_ops, kernel_name, &src[0], need, &need);
-  if (rc != DGC_OK) return dgc_fail(ctx, rc, "dgc_block_compile: emit failed");
+  rc = emit_block(ops, n_ops, kernel_name, seq, &src[0], need, &need);
+  if (rc != DGC_OK) return dgc_fail(ctx, rc, "block compile: emit failed");
   return dgc_module_compile(ctx, src.c_str(), kernel_name, out);
+}
+
+DGC_EXPORT int32_t dgc_block_compile(dgc_ctx *ctx, const dgc_uop *ops, int32_t n_ops, const char *kernel_name,
+                                     dgc_module **out) {
+  return compile_block(ctx, ops, n_ops, kernel_name, false, out);
+}
+
+DGC_EXPORT int32_t dgc_block_compile_sequential(dgc_ctx *ctx, const dgc_uop *ops, int32_t n_ops,
+                                                const char *kernel_name, dgc_module **out) {
+  return compile_block(ctx, ops, n_ops, kernel_name, true, out);
 }

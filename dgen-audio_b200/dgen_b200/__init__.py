@@ -56,7 +56,9 @@ OP = dict(CONST=0, LOAD=1, LOAD_SCALAR=2, FRAME_INDEX=3,
           ADD=10, SUB=11, MUL=12, DIV=13, MOD=14, POW=15, MIN=16, MAX=17, ATAN2=18, AND=19, OR=20, XOR=21, GT=22,
           GTE=23, LTE=24, LT=25, EQ=26,
           ABS=40, SIGN=41, FLOOR=42, CEIL=43, ROUND=44, SIN=45, COS=46, TAN=47, ATAN=48, TANH=49, EXP=50, LOG=51,
-          LOG10=52, SQRT=53, GSWITCH=60, STORE=70, OUTPUT=71)
+          LOG10=52, SQRT=53, GSWITCH=60, STORE=70, OUTPUT=71,
+          LOAD_LANE=80, LOAD_FRAME_LANE=81, STORE_FRAME_LANE=82, HISTORY_READ=83, HISTORY_WRITE=84, PHASOR=85,
+          LATCH=86)
 
 
 def _uops(ops):
@@ -68,16 +70,18 @@ def _uops(ops):
     return arr
 
 
-def block_source(ops, name="dgen_block"):
-    """CUDA C source the library emits for an op list (no GPU needed)."""
+def block_source(ops, name="dgen_block", sequential=False):
+    """CUDA C source the library emits for an op list (no GPU needed).  sequential=True: the form for blocks
+    with state cells, one thread per lane with the frame loop inside."""
     arr = _uops(ops)
     need = C.c_uint64(0)
     lib = load()
-    rc = lib.dgc_block_emit(arr, len(ops), name.encode(), None, 0, C.byref(need))
+    emit = lib.dgc_block_emit_sequential if sequential else lib.dgc_block_emit
+    rc = emit(arr, len(ops), name.encode(), None, 0, C.byref(need))
     if rc != DGC_OK:
         raise DgenCudaError("dgc_block_emit failed: %d" % rc)
     buf = C.create_string_buffer(need.value)
-    rc = lib.dgc_block_emit(arr, len(ops), name.encode(), buf, need.value, C.byref(need))
+    rc = emit(arr, len(ops), name.encode(), buf, need.value, C.byref(need))
     if rc != DGC_OK:
         raise DgenCudaError("dgc_block_emit failed: %d" % rc)
     return buf.value.decode()
@@ -159,6 +163,8 @@ SIGNATURES = {
     "dgc_launch": (_i32, [_vp, C.c_char_p, C.POINTER(_u32), C.POINTER(_u32), _u32, C.POINTER(_vp)]),
     "dgc_block_emit": (_i32, [C.POINTER(Uop), _i32, C.c_char_p, C.c_char_p, _u64, C.POINTER(_u64)]),
     "dgc_block_compile": (_i32, [_vp, C.POINTER(Uop), _i32, C.c_char_p, C.POINTER(_vp)]),
+    "dgc_block_emit_sequential": (_i32, [C.POINTER(Uop), _i32, C.c_char_p, C.c_char_p, _u64, C.POINTER(_u64)]),
+    "dgc_block_compile_sequential": (_i32, [_vp, C.POINTER(Uop), _i32, C.c_char_p, C.POINTER(_vp)]),
     "dgc_comm_unique_id": (_i32, [C.c_char_p]),
     "dgc_comm_init": (_i32, [_vp, _i32, _i32, C.c_char_p]),
     "dgc_allreduce_sum": (_i32, [_vp, _vp, _u64]),
@@ -644,11 +650,13 @@ class Context:
         self.check(self.lib.dgc_module_compile(self.h, cuda_source.encode(), name.encode(), C.byref(m)))
         return Module(self, m)
 
-    def compile_block(self, ops, name="dgen_block"):
-        """Op list (see block_source) -> Module with one kernel `name(float *memory, int count)`."""
+    def compile_block(self, ops, name="dgen_block", sequential=False):
+        """Op list (see block_source) -> Module with one kernel `name(float *memory, int count)`, or
+        `name(float *memory, int frames, int lanes)` for the sequential form."""
         arr = _uops(ops)
         m = _vp()
-        self.check(self.lib.dgc_block_compile(self.h, arr, len(ops), name.encode(), C.byref(m)))
+        fn = self.lib.dgc_block_compile_sequential if sequential else self.lib.dgc_block_compile
+        self.check(fn(self.h, arr, len(ops), name.encode(), C.byref(m)))
         return Module(self, m)
 
     def load_module(self, image):

@@ -442,7 +442,15 @@ enum {
   DGC_OP_ATAN, DGC_OP_TANH, DGC_OP_EXP, DGC_OP_LOG, DGC_OP_LOG10, DGC_OP_SQRT,
   DGC_OP_GSWITCH = 60,   /* t_a > 0 ? t_b : t_c */
   DGC_OP_STORE = 70,     /* memory[a + i] = t_b */
-  DGC_OP_OUTPUT = 71     /* memory[a + i] = sanitize(t_b) */
+  DGC_OP_OUTPUT = 71,    /* memory[a + i] = sanitize(t_b) */
+  /* sequential form only (one thread per lane e, frames i in order; a = arena cell offset) */
+  DGC_OP_LOAD_LANE = 80,        /* memory[a + e]: per-lane, frame-invariant */
+  DGC_OP_LOAD_FRAME_LANE = 81,  /* memory[a + i * lanes + e]: frame-aware tensor */
+  DGC_OP_STORE_FRAME_LANE = 82, /* memory[a + i * lanes + e] = t_b */
+  DGC_OP_HISTORY_READ = 83,     /* content of state cell a (per lane: memory[a + e]) */
+  DGC_OP_HISTORY_WRITE = 84,    /* state cell a = t_b (pass-through) */
+  DGC_OP_PHASOR = 85,           /* state cell a; frequency t_b, reset t_c, imm = sample rate; value = phase before the update */
+  DGC_OP_LATCH = 86             /* state cell a = t_b where t_c > 0; value = the cell */
 };
 typedef struct dgc_uop {
   int32_t op;
@@ -452,6 +460,18 @@ typedef struct dgc_uop {
 int32_t dgc_block_emit(const dgc_uop *ops, int32_t n_ops, const char *kernel_name, char *out, uint64_t out_cap,
                        uint64_t *needed);
 int32_t dgc_block_compile(dgc_ctx *ctx, const dgc_uop *ops, int32_t n_ops, const char *kernel_name, dgc_module **out);
+
+/* Blocks with state cells (history feedback, phasor, latch: the reference's sequential blocks,
+ * Sources/DGen/Blocks/FeedbackAnalysis.swift:357-365, Sources/DGen/Emit+State.swift:150-369): the same op lists,
+ * emitted as `extern "C" __global__ void name(float *memory, int frames, int lanes)` with one thread per tensor
+ * lane and the frame loop inside it, in frame order.  In this form i is the FRAME (DGC_OP_LOAD reads a per-frame
+ * scalar signal memory[a + i]), the lane-indexed ops above address tensors, and every state cell of a lane lives
+ * in a register across the loop (read from memory[a + e] before, written back after), so consecutive calls
+ * continue where the last one stopped, as the reference's persistent cells do. */
+int32_t dgc_block_emit_sequential(const dgc_uop *ops, int32_t n_ops, const char *kernel_name, char *out,
+                                  uint64_t out_cap, uint64_t *needed);
+int32_t dgc_block_compile_sequential(dgc_ctx *ctx, const dgc_uop *ops, int32_t n_ops, const char *kernel_name,
+                                     dgc_module **out);
 
 /* ---- gradient exchange between GPUs ------------------------------------------------------------------
  * One process per GPU, one communicator per context (NCCL, found at run time; DGC_NCCL_PATH overrides).

@@ -39,3 +39,33 @@ def test_operands_must_precede_their_use():
         dgen_b200.block_source([("CONST", 0, 0, 0, 1.0), ("SIN", 1)])
     with pytest.raises(dgen_b200.DgenCudaError):
         dgen_b200.block_source([(999, 0, 0, 0, 0.0)])
+
+
+def test_sequential_form_keeps_state_cells_in_registers_across_the_frame_loop():
+    """History feedback (Sources/DGen/Emit+State.swift:150-224): y = x * gain[lane] + 0.9 * y1 per lane."""
+    ops = [("LOAD", 0), ("LOAD_LANE", 1000), ("MUL", 0, 1), ("HISTORY_READ", 2000), ("CONST", 0, 0, 0, 0.9),
+           ("MUL", 3, 4), ("ADD", 2, 5), ("HISTORY_WRITE", 2000, 6), ("STORE_FRAME_LANE", 3000, 7)]
+    src = dgen_b200.block_source(ops, "k", sequential=True)
+    lines = [l.strip() for l in src.splitlines()]
+    assert 'extern "C" __global__ void k(float *memory, int frames, int lanes) {' in lines
+    assert lines.index("float s2000 = memory[2000 + e];") < lines.index("for (int i = 0; i < frames; ++i) {")
+    assert "float t3 = s2000;" in lines and "s2000 = t6;" in lines
+    assert "memory[3000 + (size_t)i * lanes + e] = t7;" in lines
+    assert lines.index("memory[2000 + e] = s2000;") > lines.index("memory[3000 + (size_t)i * lanes + e] = t7;")
+
+
+def test_phasor_and_latch_render_the_reference_state_updates():
+    ops = [("LOAD_LANE", 10), ("CONST", 0, 0, 0, 0.0), ("PHASOR", 500, 0, 1, 44100.0), ("LATCH", 600, 2, 0)]
+    lines = [l.strip() for l in dgen_b200.block_source(ops, "k", sequential=True).splitlines()]
+    assert "float t2 = s500;" in lines                                  # output = phase before the update
+    assert "float n2 = s500 + t0 / 44100.0f;" in lines
+    assert "n2 = n2 - floorf(n2);" in lines and "if (n2 >= 1.0f) n2 -= 1.0f;" in lines
+    assert "s500 = t1 > 0.0f ? 0.0f : n2;" in lines
+    assert "if (t0 > 0.0f) s600 = t2;" in lines and "float t3 = s600;" in lines
+
+
+def test_state_ops_need_the_sequential_form():
+    with pytest.raises(dgen_b200.DgenCudaError):
+        dgen_b200.block_source([("HISTORY_READ", 5)])
+    with pytest.raises(dgen_b200.DgenCudaError):
+        dgen_b200.block_source([("LOAD_LANE", 5)])

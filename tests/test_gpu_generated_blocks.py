@@ -154,3 +154,127 @@ def test_emitted_block_matches_a_float32_interpreter(ctx):
     assert np.isfinite(got[3 * n:4 * n]).all()          # x / floor(x) hits 0 / 0 and x / 0: sanitised at the output
     assert err.max() < 5e-6, (err.max(), np.argmax(err))
     m.close()
+
+
+# ---- blocks with state cells: one thread per lane, the frame loop inside ------------------------------------------
+def test_sequential_block_history_feedback_against_the_one_pole_restatement(ctx):
+    """y = x + 0.9 * y1 (Sources/DGenLazy/Signal.swift:265-278 one-pole through historyRead / historyWrite), a lane
+    per voice; the state cell continues across two launches."""
+    from oracle import oracle as orc
+    frames, lanes = 3000, 37
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal((frames, lanes)).astype(f32)
+    X, S, Y = 0, frames * lanes, frames * lanes + lanes
+    ops = [("LOAD_FRAME_LANE", X), ("HISTORY_READ", S), ("CONST", 0, 0, 0, 0.9), ("MUL", 1, 2), ("ADD", 0, 3),
+           ("HISTORY_WRITE", S, 4), ("STORE_FRAME_LANE", Y, 5)]
+    m = ctx.compile_block(ops, "onepole_block", sequential=True)
+    mem = torch.zeros(2 * frames * lanes + lanes, device="cuda")
+    mem[:frames * lanes] = torch.from_numpy(x.reshape(-1)).cuda()
+    half = frames // 2
+    # first half, then the second half continuing from the stored state (the frame-lane cells are offset by hand)
+    m.launch("onepole_block", (lanes + 63) // 64, 64, [mem, C.c_int(half), C.c_int(lanes)])
+    ops2 = [("LOAD_FRAME_LANE", X + half * lanes)] + ops[1:6] + [("STORE_FRAME_LANE", Y + half * lanes, 5)]
+    m2 = ctx.compile_block(ops2, "onepole_block_b", sequential=True)
+    m2.launch("onepole_block_b", (lanes + 63) // 64, 64, [mem, C.c_int(frames - half), C.c_int(lanes)])
+    ctx.sync()
+    got = mem[Y:Y + frames * lanes].cpu().numpy().reshape(frames, lanes)
+    for l in (0, 17, 36):
+        want = orc.onepole(x[:, l], 0.9)
+        assert np.abs(got[:, l] - want).max() <= 2e-6 * np.abs(want).max()
+    assert np.array_equal(mem[S:S + lanes].cpu().numpy(), got[-1])      # the cell holds the last output
+    m.close()
+    m2.close()
+
+
+def test_sequential_block_nonlinear_feedback_phasor_and_latch(ctx):
+    """A graph no primitive covers: per-lane phasor -> sine, fed through a saturating feedback loop, sampled and held
+    on a shared trigger.  Against a frame-by-frame float32 evaluation of the same ops."""
+    frames, lanes, sr = 2000, 50, 44100.0
+    rng = np.random.default_rng(4)
+    freq = rng.uniform(50.0, 5000.0, lanes).astype(f32)
+    drive = rng.uniform(0.5, 3.0, lanes).astype(f32)
+    trig = (rng.random(frames) < 0.01).astype(f32)
+    reset = np.zeros(frames, f32)
+    reset[700] = 1.0
+    TRIG, RESET, FREQ, DRIVE = 0, frames, 2 * frames, 2 * frames + lanes
+    PH, FB, HOLD = DRIVE + lanes, DRIVE + 2 * lanes, DRIVE + 3 * lanes
+    OUT_A = HOLD + lanes
+    OUT_B = OUT_A + frames * lanes
+    total = OUT_B + frames * lanes
+    ops = [("LOAD", TRIG), ("LOAD", RESET), ("LOAD_LANE", FREQ), ("LOAD_LANE", DRIVE),
+           ("PHASOR", PH, 2, 1, sr),                      # t4
+           ("CONST", 0, 0, 0, 6.28318530717958647692), ("MUL", 4, 5), ("SIN", 6),          # t7 = sin(2 pi phase)
+           ("HISTORY_READ", FB), ("CONST", 0, 0, 0, 0.5), ("MUL", 8, 9), ("ADD", 7, 10), ("MUL", 11, 3), ("TANH", 12),
+           ("HISTORY_WRITE", FB, 13),                     # t14 = tanh(drive * (s + 0.5 * y1))
+           ("LATCH", HOLD, 14, 0),                        # t15
+           ("STORE_FRAME_LANE", OUT_A, 14), ("STORE_FRAME_LANE", OUT_B, 15)]
+    mem = np.zeros(total, f32)
+    mem[TRIG:TRIG + frames], mem[RESET:RESET + frames] = trig, reset
+    mem[FREQ:FREQ + lanes], mem[DRIVE:DRIVE + lanes] = freq, drive
+    mem[HOLD:HOLD + lanes] = -2.0                         # initial latch content: visible until the first trigger
+    d = torch.from_numpy(mem).cuda()
+    m = ctx.compile_block(ops, "fb_block", sequential=True)
+    m.launch("fb_block", (lanes + 63) // 64, 64, [d, C.c_int(frames), C.c_int(lanes)])
+    ctx.sync()
+    got = d.cpu().numpy()
+    # frame-by-frame evaluation, all lanes at once, single precision
+    ph, fb, hold = np.zeros(lanes, f32), np.zeros(lanes, f32), np.full(lanes, -2.0, f32)
+    want_a, want_b = np.zeros((frames, lanes), f32), np.zeros((frames, lanes), f32)
+    for i in range(frames):
+        out_ph = ph
+        nxt = (ph + (freq / f32(sr)).astype(f32)).astype(f32)
+        nxt = (nxt - np.floor(nxt)).astype(f32)
+        nxt = np.where(nxt >= 1, nxt - 1, nxt).astype(f32)
+        ph = np.zeros(lanes, f32) if reset[i] > 0 else nxt
+        s = np.sin((out_ph * f32(6.28318530717958647692)).astype(f32)).astype(f32)
+        y = np.tanh(((s + (fb * f32(0.5)).astype(f32)).astype(f32) * drive).astype(f32)).astype(f32)
+        fb = y
+        if trig[i] > 0:
+            hold = y
+        want_a[i], want_b[i] = y, hold
+    ga = got[OUT_A:OUT_A + frames * lanes].reshape(frames, lanes)
+    gb = got[OUT_B:OUT_B + frames * lanes].reshape(frames, lanes)
+    # the phase accumulates in single precision in both; sinf / tanhf of the two math libraries differ by ulps and
+    # the loop feeds them back: 1e-4 absolute on outputs in [-1, 1]
+    assert np.abs(ga - want_a).max() <= 1e-4
+    assert np.abs(gb - want_b).max() <= 1e-4
+    assert np.all(gb[0] == -2.0) or trig[0] > 0
+    assert np.abs(got[PH:PH + lanes] - ph).max() <= 1e-4 and np.abs(got[FB:FB + lanes] - fb).max() <= 1e-4
+    m.close()
+
+
+def test_sequential_block_biquad_from_ops_against_the_biquad_restatement(ctx):
+    """Direct-form-I biquad written as history ops (Sources/DGen/HigherOps.swift:401-570, coefficients given), a lane
+    per filter, against the oracle's bank."""
+    from oracle import oracle as orc
+    frames, lanes = 4000, 24
+    rng = np.random.default_rng(6)
+    x = rng.standard_normal(frames).astype(f32)
+    cutoff = np.exp(rng.uniform(np.log(400.0), np.log(8000.0), lanes)).astype(f32)
+    q = np.exp(rng.uniform(np.log(0.5), np.log(8.0), lanes)).astype(f32)
+    coef = np.stack([orc.biquad_coef(float(c_), float(q_)) for c_, q_ in zip(cutoff, q)]).astype(f32)   # b0 b1 b2 a1 a2
+    X = 0
+    CO = frames                                           # 5 planes of per-lane coefficients
+    ST = CO + 5 * lanes                                   # x1 x2 y1 y2
+    Y = ST + 4 * lanes
+    c = lambda j: ("LOAD_LANE", CO + j * lanes)
+    ops = [("LOAD", X), c(0), c(1), c(2), c(3), c(4),
+           ("HISTORY_READ", ST), ("HISTORY_READ", ST + lanes), ("HISTORY_READ", ST + 2 * lanes),
+           ("HISTORY_READ", ST + 3 * lanes),               # t6 x1, t7 x2, t8 y1, t9 y2
+           ("MUL", 7, 3), ("MUL", 6, 2), ("ADD", 10, 11), ("MUL", 0, 1), ("ADD", 12, 13),   # t14 = x2 b2 + x1 b1 + x0 b0
+           ("MUL", 9, 5), ("MUL", 8, 4), ("ADD", 15, 16), ("SUB", 14, 17),                  # t18 = ... - (y2 a2 + y1 a1)
+           ("HISTORY_WRITE", ST + lanes, 6), ("HISTORY_WRITE", ST, 0),
+           ("HISTORY_WRITE", ST + 3 * lanes, 8), ("HISTORY_WRITE", ST + 2 * lanes, 18),
+           ("STORE_FRAME_LANE", Y, 18)]
+    mem = np.zeros(Y + frames * lanes, f32)
+    mem[:frames] = x
+    for j in range(5):
+        mem[CO + j * lanes:CO + (j + 1) * lanes] = coef[:, j]
+    d = torch.from_numpy(mem).cuda()
+    m = ctx.compile_block(ops, "biquad_block", sequential=True)
+    m.launch("biquad_block", 1, 32, [d, C.c_int(frames), C.c_int(lanes)])
+    ctx.sync()
+    got = d.cpu().numpy()[Y:].reshape(frames, lanes)
+    want = orc.biquad_bank(x[None, :], cutoff, q)[0].T    # [frames][lanes]
+    assert np.abs(got - want).max() <= 1e-4 * max(1.0, np.abs(want).max())
+    m.close()
