@@ -466,6 +466,97 @@ def run_train(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
+# --------------------------------------------------------------------------------------------------
+# the other configurations of the path (BASELINE.json configs[2], configs[3]) and the streaming kernels: one JSON
+# line per kernel family with its own roofline (algorithmic bytes / CUDA-event time against the measured copy
+# bandwidth).  Single GPU; these are replicas-only workloads (no exchange between voices).
+# --------------------------------------------------------------------------------------------------
+def measured_hbm_peak():
+    """(GB/s, "measured" | "fallback"): the driver-written copy bandwidth of this pool's B200s, else 6650."""
+    try:
+        return float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+def run_filters(args, local_rank):
+    import ctypes as C
+    import torch
+    import dgen_b200
+    from dgen_b200 import workloads as wl
+
+    torch.cuda.set_device(local_rank)
+    ctx = dgen_b200.Context(local_rank)
+    peak, peak_kind = measured_hbm_peak()
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+    def timed(fn):
+        for _ in range(max(3, args.warmup)):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(args.steps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / args.steps
+
+    def emit(metric, workload, ms, bytes_, extra=None):
+        gbs = bytes_ / ms / 1e6
+        line = {"metric": metric, "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+                "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True, "dtype": "f32",
+                "data": "synthetic", "config": {"workload": workload, "l2": "inputs + outputs larger than L2"},
+                "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak,
+                             "peak_kind": peak_kind, "algorithmic_bytes": bytes_}}
+        if extra:
+            line.update(extra)
+        print(json.dumps(line))
+
+    scale = args.voices if args.voices > 0 else 0
+    # biquad bank: 256 lanes x 32 voices x 262144 frames (8.6 GB of lane signals)
+    d = wl.biquad_bank_inputs(20260002)
+    B, L, T = (scale or d["B"]), d["L"], d["T"]
+    x, cut, q = dev(d["x"][:B]), dev(d["cutoff"]), dev(d["q"])
+    y = ctx.biquad_fwd(x, cut, q)
+    p = dgen_b200.BiquadParams(B, T, L, 1.0, 0.0)
+    ms = timed(lambda: ctx.check(ctx.lib.dgc_biquad_fwd(ctx.h, C.byref(p), x.data_ptr(), cut.data_ptr(), q.data_ptr(),
+                                                        None, y.data_ptr())))
+    emit("biquad bank forward", "biquad bank %d lanes x %d voices x %d frames (BASELINE.json configs[2])" % (L, B, T),
+         ms, 4.0 * T * (B + B * L), {"lane_samples_per_s": B * L * T / (ms * 1e-3)})
+    target = ctx.biquad_fwd(x, cut * 1.05, q)
+    gc, gq = torch.empty(L, device="cuda"), torch.empty(L, device="cuda")
+    loss = torch.zeros(1, dtype=torch.float64, device="cuda")
+    ms = timed(lambda: ctx.check(ctx.lib.dgc_biquad_mse_bwd(ctx.h, C.byref(p), x.data_ptr(), cut.data_ptr(), q.data_ptr(),
+                                                            y.data_ptr(), target.data_ptr(), 1.0 / (B * T), None,
+                                                            gc.data_ptr(), gq.data_ptr(), loss.data_ptr())))
+    emit("biquad bank BPTT", "biquad bank %d lanes x %d voices x %d frames, MSE loss, gradients of cutoff and Q" % (L, B, T),
+         ms, 4.0 * T * (2 * B * L + B), {"lane_samples_per_s": B * L * T / (ms * 1e-3)})
+    del y, target
+    # one-pole and the output sanitiser on long streams
+    n = 1 << 28 if not scale else 1 << 26
+    xx = torch.randn(64, n // 64, device="cuda")
+    yy = torch.empty_like(xx)
+    ms = timed(lambda: ctx.check(ctx.lib.dgc_onepole_fwd(ctx.h, xx.data_ptr(), 64, n // 64, C.c_float(0.9), yy.data_ptr())))
+    emit("one-pole scan", "one-pole y = x + 0.9 y1, 64 voices x %d frames" % (n // 64), ms, 8.0 * n,
+         {"traffic_note": "x is read in both passes: 12 bytes per sample of traffic"})
+    ms = timed(lambda: ctx.sanitize(xx, yy))
+    emit("output sanitiser", "non-finite -> 0 over %d samples" % n, ms, 8.0 * n)
+    del xx, yy
+    # partitioned convolution: 16 voices x 480000 frames, 96000-tap IR
+    dd = wl.partconv_inputs(20260003)
+    V = min(scale, dd["V"]) if scale else dd["V"]
+    px, ir = dev(dd["x"][:V]), dev(dd["ir"])
+    po = torch.empty_like(px)
+    ms = timed(lambda: ctx.partconv(px, ir, dd["N"], dd["hop"], out=po))
+    K, H, N = (dd["ir"].size + dd["hop"] - 1) // dd["hop"], (px.shape[1] + dd["hop"] - 1) // dd["hop"], dd["N"]
+    emit("partitioned convolution", "partitioned convolution %d voices x %d frames, %d-tap IR (BASELINE.json configs[3])"
+         % (V, px.shape[1], dd["ir"].size), ms, 4.0 * 2 * px.numel() + 8.0 * K * N,
+         {"mac_gflops": 8.0 * K * N * H * V / (ms * 1e6),
+          "roofline_note": "compute bound: the partitioned multiply-accumulate does 8 K N flops per hop and voice"})
+    ctx.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -475,8 +566,10 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--step-mode", default="auto", choices=["auto", "eager", "replay"],
                     help="training workload: enqueue the step call by call, or replay one recording of it")
-    ap.add_argument("--workload", default="fwd_loss", choices=["fwd_loss", "train"],
-                    help="fwd_loss: synthesis forward + loss (the headline metric); train: full training step")
+    ap.add_argument("--workload", default="fwd_loss", choices=["fwd_loss", "train", "filters"],
+                    help="fwd_loss: synthesis forward + loss (the headline metric); train: full training step; "
+                         "filters: biquad bank forward / BPTT, one-pole, sanitiser, partitioned convolution at "
+                         "their full sizes, one JSON line each")
     ap.add_argument("--allreduce", default="dgc", choices=["dgc", "torch"],
                     help="training workload: gradient all-reduce through the library's communicator or torch's")
     ap.add_argument("--voices", type=int, default=0,
@@ -498,6 +591,9 @@ def main():
         args.warmup = 3
     if args.workload == "train":
         run_train(args, rank, world, local_rank)
+    elif args.workload == "filters":
+        if rank == 0:
+            run_filters(args, local_rank)
     else:
         run_ours(args, rank, world, local_rank)
 
