@@ -49,7 +49,9 @@ __device__ __forceinline__ float block_decay_scan(float e, const float *rpow /* 
 }
 
 // phase 0: chunk end values with zero carry-in; phase 1: final output using carry[chunk]
-template <int PHASE>
+// REV: the same scan run backwards in time (frame n of the scan is memory index T-1-n): the adjoint recursion
+// lam[n] = g[n] + a lam[n+1] of the filter's backward pass.
+template <int PHASE, bool REV = false>
 __global__ void __launch_bounds__(OP_THREADS)
 onepole_kernel(const float *__restrict__ x, int T, int NC, float a, const float *__restrict__ carry_in,
                float *__restrict__ chunk_end, float *__restrict__ y) {
@@ -71,14 +73,21 @@ onepole_kernel(const float *__restrict__ x, int T, int NC, float a, const float 
   float prev = 0.0f;
   static_assert(OP_PER == 8, "the vector path moves a thread's run as two 128-bit words");
   // a thread's run of eight frames is 32 contiguous bytes: two 128-bit accesses when the voice row is aligned
-  const bool vec = n0 + OP_PER <= T && ((((uintptr_t)(xb + n0)) | (PHASE == 1 ? (uintptr_t)(y + (size_t)b * T + n0) : 0)) & 15) == 0;
+  // memory index of the run's lowest address: n0 forwards, T - n0 - 8 backwards (the run is then read high to low)
+  const int m0 = REV ? T - n0 - OP_PER : n0;
+  const bool vec = n0 + OP_PER <= T && ((((uintptr_t)(xb + m0)) | (PHASE == 1 ? (uintptr_t)(y + (size_t)b * T + m0) : 0)) & 15) == 0;
   if (vec) {
-    const float4 u = __ldg(reinterpret_cast<const float4 *>(xb + n0)), w = __ldg(reinterpret_cast<const float4 *>(xb + n0) + 1);
-    loc[0] = u.x; loc[1] = u.y; loc[2] = u.z; loc[3] = u.w;
-    loc[4] = w.x; loc[5] = w.y; loc[6] = w.z; loc[7] = w.w;
+    const float4 u = __ldg(reinterpret_cast<const float4 *>(xb + m0)), w = __ldg(reinterpret_cast<const float4 *>(xb + m0) + 1);
+    if (REV) {
+      loc[7] = u.x; loc[6] = u.y; loc[5] = u.z; loc[4] = u.w;
+      loc[3] = w.x; loc[2] = w.y; loc[1] = w.z; loc[0] = w.w;
+    } else {
+      loc[0] = u.x; loc[1] = u.y; loc[2] = u.z; loc[3] = u.w;
+      loc[4] = w.x; loc[5] = w.y; loc[6] = w.z; loc[7] = w.w;
+    }
   } else {
 #pragma unroll
-    for (int j = 0; j < OP_PER; ++j) loc[j] = (n0 + j < T) ? xb[n0 + j] : 0.0f;
+    for (int j = 0; j < OP_PER; ++j) loc[j] = (n0 + j < T) ? xb[REV ? T - 1 - (n0 + j) : n0 + j] : 0.0f;
   }
 #pragma unroll
   for (int j = 0; j < OP_PER; ++j) {
@@ -114,13 +123,16 @@ onepole_kernel(const float *__restrict__ x, int T, int NC, float a, const float 
     loc[j] = fmaf(ap, state, loc[j]);
     ap *= a;
   }
-  if (vec) {
+  if (vec && REV) {
+    __stcs(reinterpret_cast<float4 *>(yb + m0), make_float4(loc[7], loc[6], loc[5], loc[4]));
+    __stcs(reinterpret_cast<float4 *>(yb + m0) + 1, make_float4(loc[3], loc[2], loc[1], loc[0]));
+  } else if (vec) {
     __stcs(reinterpret_cast<float4 *>(yb + n0), make_float4(loc[0], loc[1], loc[2], loc[3]));
     __stcs(reinterpret_cast<float4 *>(yb + n0) + 1, make_float4(loc[4], loc[5], loc[6], loc[7]));
   } else {
 #pragma unroll
     for (int j = 0; j < OP_PER; ++j)
-      if (n0 + j < T) yb[n0 + j] = loc[j];
+      if (n0 + j < T) yb[REV ? T - 1 - (n0 + j) : n0 + j] = loc[j];
   }
 }
 
@@ -422,6 +434,9 @@ __global__ void biquad_carry_kernel(const double *__restrict__ trans, int B, int
 // S_loc + s1*S_h1 + s2*S_h2.  Record per (voice, chunk, lane): 15 sums + local start adjoint (2) + sq error.
 constexpr int BW_REC = 18;
 
+// UP = false: g = gscale * (y - tgt) (the MSE loss, squared error summed on the way);  UP = true: `tgt` IS the
+// upstream gradient dL/dy [B][T][L] of an arbitrary loss.
+template <bool UP>
 __global__ void __launch_bounds__(BQ_THREADS)
 biquad_bwd_kernel(const float *__restrict__ x, const float *__restrict__ coef, const float *__restrict__ y,
                   const float *__restrict__ tgt, int B, int T, int L, int NC, float gscale,
@@ -450,9 +465,14 @@ biquad_bwd_kernel(const float *__restrict__ x, const float *__restrict__ coef, c
   float yc = yb[(size_t)nt * L];
   float ym1 = nt - 1 >= 0 ? yb[(size_t)(nt - 1) * L] : 0.f;
   auto body = [&](int n, float ym2, float tv) {
-    float d = yc - tv;
-    sq = fmaf(d, d, sq);
-    float g = gscale * d;
+    float g;
+    if (UP) {
+      g = tv;
+    } else {
+      float d = yc - tv;
+      sq = fmaf(d, d, sq);
+      g = gscale * d;
+    }
     float lam = g - (cf.a1 * la1 + cf.a2 * la2);
     float h1 = -(cf.a1 * h1a + cf.a2 * h1b);
     float h2 = -(cf.a1 * h2a + cf.a2 * h2b);
@@ -501,7 +521,8 @@ biquad_bwd_kernel(const float *__restrict__ x, const float *__restrict__ coef, c
 // Reverse carry over chunks, thread per (voice, lane): resolves the terminal adjoint of every chunk,
 // combines the sums, and writes per (voice, lane) the five coefficient-gradient sums and the squared error.
 __global__ void biquad_bwd_carry_kernel(const float *__restrict__ rec, const float *__restrict__ coef, int B, int L,
-                                        int NC, int T, double *__restrict__ acc /* [B][L][6] */) {
+                                        int NC, int T, double *__restrict__ acc /* [B][L][6] */,
+                                        float2 *__restrict__ term /* [B][NC][L] or null */) {
   int idx = blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= B * L) return;
   int b = idx / L, l = idx - b * L;
@@ -525,6 +546,7 @@ __global__ void biquad_bwd_carry_kernel(const float *__restrict__ rec, const flo
   double s1 = 0.0, s2 = 0.0;  // terminal adjoint (lam[n_end+1], lam[n_end+2]) of the current chunk
   for (int c = NC - 1; c >= 0; --c) {
     const float *r = rec + ((size_t)b * NC + c) * BW_REC * L + l;
+    if (term) term[((size_t)b * NC + c) * L + l] = make_float2((float)s1, (float)s2);
     for (int i = 0; i < 5; ++i)
       G[i] += (double)r[(size_t)i * L] + s1 * (double)r[(size_t)(5 + i) * L] + s2 * (double)r[(size_t)(10 + i) * L];
     sq += (double)r[(size_t)17 * L];
@@ -538,6 +560,78 @@ __global__ void biquad_bwd_carry_kernel(const float *__restrict__ rec, const flo
   }
   double *o = acc + ((size_t)b * L + l) * 6;
   o[0] = G[0]; o[1] = G[1]; o[2] = G[2]; o[3] = -G[3]; o[4] = -G[4]; o[5] = sq;
+}
+
+// Gradient with respect to the INPUT x[b][n] (shared by the lanes): sum over lanes of
+//   b0 lam[n] + b1 lam[n+1] + b2 lam[n+2]
+// A second reverse sweep per (voice, lane, chunk), now from the chunk's TRUE terminal adjoint (resolved by the carry
+// kernel), recomputes lam; the sum over the block's 128 lanes goes through a shared-memory tile of 32 frames, the
+// sum over lane blocks through per-block partial rows that a last kernel adds in a fixed order.
+constexpr int GX_FRAMES = 32;
+
+template <bool UP>
+__global__ void __launch_bounds__(BQ_THREADS)
+biquad_gx_kernel(const float *__restrict__ coef, const float *__restrict__ y, const float *__restrict__ tgt,
+                 const float2 *__restrict__ term, int B, int T, int L, int NC, float gscale,
+                 float *__restrict__ part /* [gridDim.x][B][T] */) {
+  __shared__ float red[GX_FRAMES][BQ_THREADS + 1];
+  const int tid = threadIdx.x, l = blockIdx.x * BQ_THREADS + tid, c = blockIdx.y, b = blockIdx.z;
+  const int n0 = c * BQ_CHUNK, len = min(BQ_CHUNK, T - n0);
+  const bool live = l < L;
+  Coef cf = {};
+  float la1 = 0.f, la2 = 0.f;
+  if (live) {
+    cf = load_coef(coef, l);
+    const float2 s = term[((size_t)b * NC + c) * L + l];
+    la1 = s.x;
+    la2 = s.y;
+  }
+  const float *yb = y + (size_t)b * T * L + l, *tb = tgt + (size_t)b * T * L + l;
+  float *pb = part + ((size_t)blockIdx.x * B + b) * T;
+  // groups of 32 frames from the end of the chunk; the last group (lowest frames) may be shorter
+  for (int hi = len; hi > 0; hi -= GX_FRAMES) {
+    const int lo = max(hi - GX_FRAMES, 0), cnt = hi - lo;
+    float gv[GX_FRAMES];
+    if (live) {
+#pragma unroll
+      for (int j = 0; j < GX_FRAMES; ++j) {
+        const int t = n0 + lo + j;
+        if (j < cnt) gv[j] = UP ? __ldcs(tb + (size_t)t * L) : gscale * (__ldcs(yb + (size_t)t * L) - __ldcs(tb + (size_t)t * L));
+        else gv[j] = 0.f;
+      }
+    }
+#pragma unroll
+    for (int j = GX_FRAMES - 1; j >= 0; --j) {
+      float contrib = 0.f;
+      if (live && j < cnt) {
+        const float lam = gv[j] - (cf.a1 * la1 + cf.a2 * la2);
+        contrib = fmaf(cf.b0, lam, fmaf(cf.b1, la1, cf.b2 * la2));
+        la2 = la1;
+        la1 = lam;
+      }
+      red[j][tid] = contrib;
+    }
+    __syncthreads();
+    // thread -> (frame j = tid / 4, quarter of the lanes): 32 adds, then the four quarters by shuffles
+    {
+      const int j = tid >> 2, seg = tid & 3;
+      float sum = 0.f;
+#pragma unroll 8
+      for (int k = 0; k < BQ_THREADS / 4; ++k) sum += red[j][seg * (BQ_THREADS / 4) + ((k + tid) & (BQ_THREADS / 4 - 1))];
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+      if (seg == 0 && j < cnt) pb[n0 + lo + j] = sum;
+    }
+    __syncthreads();
+  }
+}
+
+__global__ void sum_partial_rows_kernel(const float *__restrict__ part, int nparts, size_t n, float *__restrict__ out) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float s = 0.f;
+  for (int p = 0; p < nparts; ++p) s += part[(size_t)p * n + i];
+  out[i] = s;
 }
 
 // Sum over voices (fixed order), chain rule to cutoff and q, total loss.
@@ -603,7 +697,11 @@ DGC_EXPORT uint64_t dgc_biquad_scratch_floats(const dgc_biquad_params *p, int32_
   // forward: chunk states, then the end-state response table [2L][BQ_CHUNK] and its 4L history terms
   if (!backward) return coef + (((uint64_t)p->B * NC * p->L * 2 + 3) & ~3ull) + (uint64_t)p->L * (2 * BQ_CHUNK + 4) + 16;
   uint64_t rec = (uint64_t)p->B * NC * BW_REC * p->L;
-  return coef + ((rec + 3) & ~3ull) + 2 * ((uint64_t)p->B * p->L * 6 + p->L) + 16;
+  uint64_t base = coef + ((rec + 3) & ~3ull) + 2 * ((uint64_t)p->B * p->L * 6 + p->L) + 16;
+  if (backward == 1) return base;
+  // backward == 2 (dgc_biquad_bwd with the input gradient): terminal adjoints [B][NC][L] float2, partial rows
+  uint64_t blocks = ((uint64_t)p->L + BQ_THREADS - 1) / BQ_THREADS;
+  return base + 2 * (uint64_t)p->B * NC * p->L + blocks * (uint64_t)p->B * p->T + 16;
 }
 
 DGC_EXPORT int32_t dgc_biquad_fwd(dgc_ctx *ctx, const dgc_biquad_params *p, const float *x_dev,
@@ -672,16 +770,118 @@ DGC_EXPORT int32_t dgc_biquad_mse_bwd(dgc_ctx *ctx, const dgc_biquad_params *p, 
   biquad_coef_kernel<<<dgc_div_up(L, 128), 128, 0, ctx->stream>>>(cutoff_dev, q_dev, L, p->gain, p->mode, coef);
   DGC_LAUNCHED(ctx, "biquad_coef");
   dim3 grid(dgc_div_up(L, BQ_THREADS), NC, B);
-  biquad_bwd_kernel<<<grid, BQ_THREADS, 0, ctx->stream>>>(x_dev, coef, y_dev, target_dev, B, T, L, NC,
-                                                          2.0f * loss_scale, rec);
+  biquad_bwd_kernel<false><<<grid, BQ_THREADS, 0, ctx->stream>>>(x_dev, coef, y_dev, target_dev, B, T, L, NC,
+                                                                 2.0f * loss_scale, rec);
   DGC_LAUNCHED(ctx, "biquad_bwd");
-  biquad_bwd_carry_kernel<<<dgc_div_up(B * L, 128), 128, 0, ctx->stream>>>(rec, coef, B, L, NC, T, acc);
+  biquad_bwd_carry_kernel<<<dgc_div_up(B * L, 128), 128, 0, ctx->stream>>>(rec, coef, B, L, NC, T, acc, nullptr);
   DGC_LAUNCHED(ctx, "biquad_bwd_carry");
   biquad_bwd_final_kernel<<<dgc_div_up(L, 128), 128, 0, ctx->stream>>>(acc, coef, B, L, loss_scale, grad_cutoff_dev,
                                                                         grad_q_dev, lane_loss);
   DGC_LAUNCHED(ctx, "biquad_bwd_final");
   sum_doubles_kernel<<<1, 32, 0, ctx->stream>>>(lane_loss, L, loss_dev);
   DGC_LAUNCHED(ctx, "biquad_loss_sum");
+  return DGC_OK;
+}
+
+namespace {
+// part[b][s] = sum over segment s of lam[n] * y[n-1] (n >= 1), in double
+constexpr int OPG_SEGS = 32;
+__global__ void __launch_bounds__(256)
+onepole_ga_kernel(const float *__restrict__ lam, const float *__restrict__ y, int T, double *__restrict__ part) {
+  const int b = blockIdx.y, sgm = blockIdx.x;
+  const int64_t per = ((int64_t)T + OPG_SEGS - 1) / OPG_SEGS, lo = max((int64_t)1, sgm * per),
+                hi = min((int64_t)T, (sgm + 1) * per);
+  const float *lb = lam + (size_t)b * T, *yb = y + (size_t)b * T;
+  double acc = 0.0;
+  for (int64_t n = lo + threadIdx.x; n < hi; n += 256) acc += (double)lb[n] * (double)yb[n - 1];
+  __shared__ double sh[256];
+  sh[threadIdx.x] = acc;
+  __syncthreads();
+  for (int s = 128; s > 0; s >>= 1) {
+    if (threadIdx.x < s) sh[threadIdx.x] += sh[threadIdx.x + s];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) part[(size_t)b * OPG_SEGS + sgm] = sh[0];
+}
+
+__global__ void onepole_ga_sum_kernel(const double *__restrict__ part, int B, float *__restrict__ ga) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= B) return;
+  double s = 0.0;
+  for (int i = 0; i < OPG_SEGS; ++i) s += part[(size_t)b * OPG_SEGS + i];
+  ga[b] = (float)s;
+}
+}  // namespace
+
+// Backward of y[n] = x[n] + a y[n-1]: lam[n] = gy[n] + a lam[n+1] (the same scan, reversed in time),
+// dL/dx = lam, dL/da[b] = sum_n lam[n] y[n-1].
+DGC_EXPORT int32_t dgc_onepole_bwd(dgc_ctx *ctx, const float *y_dev, const float *gy_dev, int32_t B, int32_t T, float a,
+                                   float *grad_x_dev, float *grad_a_dev) {
+  if (!ctx) return DGC_ERR_INVALID;
+  DGC_REQUIRE(ctx, gy_dev && grad_x_dev, "null pointer");
+  DGC_REQUIRE(ctx, grad_a_dev == nullptr || y_dev != nullptr, "the coefficient gradient needs the forward output");
+  DGC_REQUIRE(ctx, B > 0 && T > 0, "size out of range");
+  DGC_REQUIRE(ctx, gy_dev != grad_x_dev, "in-place operation is not supported");
+  const int NC = dgc_div_up(T, OP_CHUNK);
+  DGC_REQUIRE(ctx, NC <= 65535 * 32 && B <= 65535, "size out of range");
+  const uint64_t need = 2ull * B * NC + 2ull * B * OPG_SEGS + 8;
+  float *scr = dgc_ctx_scratch(ctx, need);
+  if (!scr) return DGC_ERR_OOM;
+  float *chunk_end = scr, *carry = scr + (size_t)B * NC;
+  double *part = reinterpret_cast<double *>(scr + (((size_t)2 * B * NC + 1) & ~(size_t)1));
+  onepole_kernel<0, true><<<dim3(NC, B), OP_THREADS, 0, ctx->stream>>>(gy_dev, T, NC, a, nullptr, chunk_end, nullptr);
+  DGC_LAUNCHED(ctx, "onepole_bwd_pass0");
+  onepole_carry_kernel<<<dgc_div_up(B, 64), 64, 0, ctx->stream>>>(chunk_end, B, NC, a, 0.0f, carry);
+  DGC_LAUNCHED(ctx, "onepole_bwd_carry");
+  onepole_kernel<1, true><<<dim3(NC, B), OP_THREADS, 0, ctx->stream>>>(gy_dev, T, NC, a, carry, nullptr, grad_x_dev);
+  DGC_LAUNCHED(ctx, "onepole_bwd_pass1");
+  if (grad_a_dev) {
+    onepole_ga_kernel<<<dim3(OPG_SEGS, B), 256, 0, ctx->stream>>>(grad_x_dev, y_dev, T, part);
+    DGC_LAUNCHED(ctx, "onepole_grad_a");
+    onepole_ga_sum_kernel<<<dgc_div_up(B, 128), 128, 0, ctx->stream>>>(part, B, grad_a_dev);
+    DGC_LAUNCHED(ctx, "onepole_grad_a_sum");
+  }
+  return DGC_OK;
+}
+
+DGC_EXPORT int32_t dgc_biquad_bwd(dgc_ctx *ctx, const dgc_biquad_params *p, const float *x_dev, const float *cutoff_dev,
+                                  const float *q_dev, const float *y_dev, const float *gy_dev, float *scratch_dev,
+                                  float *grad_cutoff_dev, float *grad_q_dev, float *grad_x_dev) {
+  if (!ctx) return DGC_ERR_INVALID;
+  DGC_REQUIRE(ctx, p && x_dev && cutoff_dev && q_dev && y_dev && gy_dev && grad_cutoff_dev && grad_q_dev,
+              "null pointer");
+  int32_t rc = biquad_validate(ctx, p);
+  if (rc != DGC_OK) return rc;
+  const int B = p->B, T = p->T, L = p->L, NC = dgc_div_up(T, BQ_CHUNK);
+  DGC_REQUIRE(ctx, NC <= 65535, "T too large");
+  float *scr = scratch_dev ? scratch_dev : dgc_ctx_scratch(ctx, dgc_biquad_scratch_floats(p, grad_x_dev ? 2 : 1));
+  if (!scr) return DGC_ERR_OOM;
+  DGC_REQUIRE(ctx, (((uintptr_t)scr) & 15) == 0, "scratch must be 16-byte aligned");
+  float *coef = scr;
+  float *rec = scr + ((((size_t)L * 24) + 3) & ~(size_t)3);
+  size_t rec_n = ((size_t)B * NC * BW_REC * L + 3) & ~(size_t)3;
+  double *acc = reinterpret_cast<double *>(rec + rec_n);
+  double *lane_loss = acc + (size_t)B * L * 6;
+  float *after = scr + dgc_biquad_scratch_floats(p, 1);
+  float2 *term = grad_x_dev ? reinterpret_cast<float2 *>(after) : nullptr;
+  float *part = after + (size_t)2 * B * NC * L;
+  biquad_coef_kernel<<<dgc_div_up(L, 128), 128, 0, ctx->stream>>>(cutoff_dev, q_dev, L, p->gain, p->mode, coef);
+  DGC_LAUNCHED(ctx, "biquad_coef");
+  dim3 grid(dgc_div_up(L, BQ_THREADS), NC, B);
+  biquad_bwd_kernel<true><<<grid, BQ_THREADS, 0, ctx->stream>>>(x_dev, coef, y_dev, gy_dev, B, T, L, NC, 1.0f, rec);
+  DGC_LAUNCHED(ctx, "biquad_bwd");
+  biquad_bwd_carry_kernel<<<dgc_div_up(B * L, 128), 128, 0, ctx->stream>>>(rec, coef, B, L, NC, T, acc, term);
+  DGC_LAUNCHED(ctx, "biquad_bwd_carry");
+  biquad_bwd_final_kernel<<<dgc_div_up(L, 128), 128, 0, ctx->stream>>>(acc, coef, B, L, 0.0f, grad_cutoff_dev, grad_q_dev,
+                                                                        lane_loss);
+  DGC_LAUNCHED(ctx, "biquad_bwd_final");
+  if (grad_x_dev) {
+    biquad_gx_kernel<true><<<grid, BQ_THREADS, 0, ctx->stream>>>(coef, y_dev, gy_dev, term, B, T, L, NC, 1.0f, part);
+    DGC_LAUNCHED(ctx, "biquad_grad_x");
+    const size_t n = (size_t)B * T;
+    sum_partial_rows_kernel<<<dgc_div_up((int64_t)n, 256), 256, 0, ctx->stream>>>(part, (int)grid.x, n, grad_x_dev);
+    DGC_LAUNCHED(ctx, "biquad_grad_x_sum");
+  }
   return DGC_OK;
 }
 

@@ -140,6 +140,8 @@ SIGNATURES = {
     "dgc_linear_bwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp]),
     "dgc_adam_step": (_i32, [_vp, _vp, _vp, _vp, _vp, _u64, _i32, _f, _f, _f, _f]),
     "dgc_sanitize": (_i32, [_vp, _vp, _u64, _vp]),
+    "dgc_onepole_bwd": (_i32, [_vp, _vp, _vp, _i32, _i32, _f, _vp, _vp]),
+    "dgc_biquad_bwd": (_i32, [_vp, C.POINTER(BiquadParams)] + [_vp] * 9),
     "dgc_adam_step_counted": (_i32, [_vp, _vp, _vp, _vp, _vp, _u64, _vp, _vp, _f, _f, _f, _f]),
     "dgc_graph_begin": (_i32, [_vp]),
     "dgc_graph_end": (_i32, [_vp, C.POINTER(_vp)]),
@@ -418,6 +420,26 @@ class Context:
         self.check(self.lib.dgc_biquad_mse_bwd(self.h, C.byref(p), _ptr(x), _ptr(cutoff), _ptr(q), _ptr(y),
                                                _ptr(target), loss_scale, None, _ptr(gc), _ptr(gq), _ptr(loss)))
         return gc, gq, loss
+
+    def biquad_bwd(self, x, cutoff, q, y, gy, want_grad_x=True, gain=1.0, mode=0.0):
+        """Backward for an arbitrary upstream gradient gy [B][T][L] -> (grad_cutoff [L], grad_q [L], grad_x [B][T] | None)."""
+        B, T = x.shape
+        L = cutoff.numel()
+        p = BiquadParams(B, T, L, gain, mode)
+        gc, gq = self._empty(L), self._empty(L)
+        gx = self._empty(B, T) if want_grad_x else None
+        self.check(self.lib.dgc_biquad_bwd(self.h, C.byref(p), _ptr(x), _ptr(cutoff), _ptr(q), _ptr(y), _ptr(gy), None,
+                                           _ptr(gc), _ptr(gq), _ptr(gx) if want_grad_x else None))
+        return gc, gq, gx
+
+    def onepole_bwd(self, gy, a, y=None):
+        """-> (grad_x [B][T], grad_a [B] | None): grad_a only when the forward output y is given."""
+        B, T = gy.shape
+        gx = self._empty(B, T)
+        ga = self._empty(B) if y is not None else None
+        self.check(self.lib.dgc_onepole_bwd(self.h, _ptr(y) if y is not None else None, _ptr(gy), B, T, a, _ptr(gx),
+                                            _ptr(ga) if y is not None else None))
+        return gx, ga
 
     # ---- hop-gated spectral blocks ------------------------------------------------------------
     def stft_mag(self, x, N, hop, window=None):

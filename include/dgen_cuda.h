@@ -215,13 +215,20 @@ int32_t dgc_onepole_fwd(dgc_ctx *ctx, const float *x_dev, int32_t B, int32_t T, 
 int32_t dgc_onepole_fwd_static(void *cuda_stream, const float *x_dev, int32_t B, int32_t T, float a, float *y_dev,
                                char *err_buf, uint32_t err_len);
 
+/* Backward of the one-pole filter (the adjoint of historyRead / historyWrite feedback, Sources/DGen/Gradients.swift:765-778):
+ * lam[n] = gy[n] + a lam[n+1], the same scan reversed in time; grad_x = lam [B][T]; grad_a_dev [B] (optional, needs
+ * the forward output y_dev) = sum_n lam[n] y[n-1], the derivative with respect to the feedback coefficient. */
+int32_t dgc_onepole_bwd(dgc_ctx *ctx, const float *y_dev, const float *gy_dev, int32_t B, int32_t T, float a,
+                        float *grad_x_dev, float *grad_a_dev);
+
 typedef struct dgc_biquad_params {
   int32_t B, T, L;   /* voices, frames, lanes */
   float gain;
   float mode;        /* 0 low-pass .. 5, as Graph.biquad's selector */
 } dgc_biquad_params;
 
-/* Device scratch (floats) the biquad entry points need; backward != 0 for dgc_biquad_mse_bwd. */
+/* Device scratch (floats) the biquad entry points need: backward 0 = dgc_biquad_fwd, 1 = dgc_biquad_mse_bwd and
+ * dgc_biquad_bwd without the input gradient, 2 = dgc_biquad_bwd with it. */
 uint64_t dgc_biquad_scratch_floats(const dgc_biquad_params *p, int32_t backward);
 /* Tensor biquad bank (Sources/DGen/HigherOps.swift:401-570): x [B][T] shared by L lanes with
  * per-lane cutoff/q; y [B][T][L].  scratch_dev NULL = context-owned buffer. */
@@ -234,6 +241,13 @@ int32_t dgc_biquad_fwd(dgc_ctx *ctx, const dgc_biquad_params *p, const float *x_
 int32_t dgc_biquad_mse_bwd(dgc_ctx *ctx, const dgc_biquad_params *p, const float *x_dev, const float *cutoff_dev,
                            const float *q_dev, const float *y_dev, const float *target_dev, float loss_scale,
                            float *scratch_dev, float *grad_cutoff_dev, float *grad_q_dev, double *loss_dev);
+/* The same reverse-time pass for an ARBITRARY loss: gy_dev [B][T][L] is dL/dy.  Gradients w.r.t. cutoff and q as
+ * above; grad_x_dev [B][T] (optional) receives dL/dx, the sum over lanes of the transposed filters applied to gy
+ * (a second reverse sweep from each chunk's resolved terminal adjoint). */
+int32_t dgc_biquad_bwd(dgc_ctx *ctx, const dgc_biquad_params *p, const float *x_dev, const float *cutoff_dev,
+                       const float *q_dev, const float *y_dev, const float *gy_dev, float *scratch_dev,
+                       float *grad_cutoff_dev, float *grad_q_dev, float *grad_x_dev);
+
 
 /* ---- hop-gated spectral blocks ------------------------------------------------------------------
  * buffer(size:N, hop:) -> FFT -> magnitude for V signals of T frames: mags [V][H][N/2+1],
