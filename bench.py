@@ -543,6 +543,30 @@ def run_filters(args, local_rank):
     ms = timed(lambda: ctx.sanitize(xx, yy))
     emit("output sanitiser", "non-finite -> 0 over %d samples" % n, ms, 8.0 * n)
     del xx, yy
+    # ring / hold ops on long tensor streams: [frames][lanes] in, the same out
+    fr, ln = (1 << 20, 256) if not scale else (1 << 18, 256)
+    sig = torch.randn(fr, ln, device="cuda")
+    dly = (torch.rand(fr, device="cuda") * 3000.0)
+    out = torch.empty_like(sig)
+    ms = timed(lambda: ctx.check(ctx.lib.dgc_delay_line(ctx.h, sig.data_ptr(), dly.data_ptr(), 1, fr, ln, 4096, None, None,
+                                                        out.data_ptr())))
+    emit("tensor delay line", "interpolated delay lines, %d frames x %d lanes, per-frame delay time up to 3000 samples"
+         % (fr, ln), ms, 8.0 * fr * ln + 4.0 * fr,
+         {"traffic_note": "both taps of a lane are neighbouring rows: the second read hits L2"})
+    trig = (torch.rand(fr, device="cuda") < 0.004).float()
+    ms = timed(lambda: ctx.check(ctx.lib.dgc_latch(ctx.h, sig.data_ptr(), trig.data_ptr(), 1, fr, ln, None, None,
+                                                   out.data_ptr())))
+    emit("latch", "sample and hold, %d frames x %d lanes, shared trigger" % (fr, ln), ms, 8.0 * fr * ln + 4.0 * fr)
+    del sig, dly, out, trig
+    cb, ct = (64, 1 << 20) if not scale else (64, 1 << 18)
+    cx = torch.randn(cb, ct, device="cuda") * 0.3
+    cy = torch.empty_like(cx)
+    cp = dgen_b200.CompressorParams(cb, ct, 4.0, -20.0, 6.0, 0.005, 0.05, 44100.0)
+    ms = timed(lambda: ctx.check(ctx.lib.dgc_compressor(ctx.h, C.byref(cp), cx.data_ptr(), None, None, cy.data_ptr())))
+    emit("compressor", "compressor, %d voices x %d frames" % (cb, ct), ms, 8.0 * cb * ct,
+         {"samples_per_s": cb * ct / (ms * 1e-3),
+          "roofline_note": "latency bound: the attack / release smoother is a data-dependent recurrence, one warp per voice"})
+    del cx, cy
     # partitioned convolution: 16 voices x 480000 frames, 96000-tap IR
     dd = wl.partconv_inputs(20260003)
     V = min(scale, dd["V"]) if scale else dd["V"]

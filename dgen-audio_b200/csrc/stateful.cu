@@ -14,7 +14,8 @@
 // is one thread; the ring / held-value cells are read for the frames that reach back before the call and
 // rewritten at the end of the call so that consecutive calls continue as the reference's persistent cells do.
 // The compressor's attack / release smoother IS a recurrence with a data-dependent coefficient (no associative
-// form): its gain computer and make-up run sample-parallel, the smoother runs one warp per voice.  The phase
+// form): its gain computer and make-up run sample-parallel in kernels of their own, the smoother runs one warp
+// per voice between them.  The phase
 // vocoder carries one value per bin from hop to hop (the synthesis phase): its analysis runs parallel over
 // (hop, bin), its resynthesis one thread per bin.
 #include "common.cuh"
@@ -64,6 +65,77 @@ frac_delay_kernel(const float *__restrict__ x, const float *__restrict__ delay, 
   y[idx] = fmaf(s1, frac, s0 * (1.0f - frac));
 }
 
+// The same gather with FOUR lanes per thread (W a multiple of 4, 16-byte aligned rows): the two taps of a frame are
+// 128-bit loads and the result one 128-bit streaming store; only frames that reach back into the ring cell, and
+// per-lane delay times, fall back to one access per lane.
+template <bool ROW_MAJOR>
+__device__ __forceinline__ float4 delayed_sample4(const float *__restrict__ x, const float *__restrict__ ring, int w0,
+                                                  int64_t n, int k, int e, int W, int R) {
+  const int64_t m = n - k;
+  if (m >= 0) return __ldg(reinterpret_cast<const float4 *>(x + m * W + e));
+  return make_float4(delayed_sample<ROW_MAJOR>(x, ring, w0, n, k, e, W, R),
+                     delayed_sample<ROW_MAJOR>(x, ring, w0, n, k, e + 1, W, R),
+                     delayed_sample<ROW_MAJOR>(x, ring, w0, n, k, e + 2, W, R),
+                     delayed_sample<ROW_MAJOR>(x, ring, w0, n, k, e + 3, W, R));
+}
+
+template <bool ROW_MAJOR>
+__global__ void __launch_bounds__(256)
+frac_delay4_kernel(const float *__restrict__ x, const float *__restrict__ delay, int delay_mode, int fixed_k, int64_t T,
+                   int W, int R, float dmax, const float *__restrict__ ring, const float *__restrict__ head,
+                   float *__restrict__ y) {
+  const int W4 = W >> 2;
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, total = T * W4;
+  if (idx >= total) return;
+  const int64_t n = total <= 0xffffffffLL ? (int64_t)((uint32_t)idx / (uint32_t)W4) : idx / W4;
+  const int e = (int)(idx - n * W4) * 4;
+  const int w0 = head ? (int)head[0] : 0;
+  float4 out;
+  if (delay_mode < 0) {
+    out = delayed_sample4<ROW_MAJOR>(x, ring, w0, n, fixed_k, e, W, R);
+  } else if (delay_mode <= 1) {
+    const float d = delay_mode == 0 ? delay[0] : delay[n];
+    const float dc = d > dmax ? dmax : (d < 0.0f ? 0.0f : d);
+    const float kf = floorf(dc), frac = dc - kf, omf = 1.0f - frac;
+    const int k = (int)kf;
+    int k1 = k + 1;
+    if (k1 >= R) k1 -= R;
+    const float4 s0 = delayed_sample4<ROW_MAJOR>(x, ring, w0, n, k, e, W, R);
+    const float4 s1 = delayed_sample4<ROW_MAJOR>(x, ring, w0, n, k1, e, W, R);
+    out = make_float4(fmaf(s1.x, frac, s0.x * omf), fmaf(s1.y, frac, s0.y * omf), fmaf(s1.z, frac, s0.z * omf),
+                      fmaf(s1.w, frac, s0.w * omf));
+  } else {
+    const float4 d4 = __ldg(reinterpret_cast<const float4 *>(delay_mode == 2 ? delay + n * W + e : delay + e));
+    const float dv[4] = {d4.x, d4.y, d4.z, d4.w};
+    float o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float dc = dv[j] > dmax ? dmax : (dv[j] < 0.0f ? 0.0f : dv[j]);
+      const float kf = floorf(dc), frac = dc - kf;
+      const int k = (int)kf;
+      int k1 = k + 1;
+      if (k1 >= R) k1 -= R;
+      const float s0 = delayed_sample<ROW_MAJOR>(x, ring, w0, n, k, e + j, W, R);
+      const float s1 = delayed_sample<ROW_MAJOR>(x, ring, w0, n, k1, e + j, W, R);
+      o[j] = fmaf(s1, frac, s0 * (1.0f - frac));
+    }
+    out = make_float4(o[0], o[1], o[2], o[3]);
+  }
+  __stcs(reinterpret_cast<float4 *>(y + n * W + e), out);
+}
+
+template <bool ROW_MAJOR>
+static void launch_frac_delay(cudaStream_t st, const float *x, const float *delay, int delay_mode, int fixed_k, int64_t T,
+                              int W, int R, float dmax, const float *ring, const float *head, float *y) {
+  const bool vec = (W & 3) == 0 && ((((uintptr_t)x) | ((uintptr_t)y) | ((uintptr_t)delay)) & 15) == 0;
+  if (vec)
+    frac_delay4_kernel<ROW_MAJOR><<<dgc_div_up(T * (W >> 2), 256), 256, 0, st>>>(x, delay, delay_mode, fixed_k, T, W, R, dmax,
+                                                                                ring, head, y);
+  else
+    frac_delay_kernel<ROW_MAJOR><<<dgc_div_up(T * W, 256), 256, 0, st>>>(x, delay, delay_mode, fixed_k, T, W, R, dmax, ring,
+                                                                        head, y);
+}
+
 // ring slot p holds, after the call, the last row written to it: frames n = off, off + R, ... < T with
 // off = (p - head) mod R; untouched when off >= T
 template <bool ROW_MAJOR>
@@ -109,30 +181,53 @@ __global__ void latch_last_kernel(const float *__restrict__ cond, int cond_mode,
   last[(size_t)c * W + e] = found;
 }
 
-// Exclusive "most recent trigger" over chunks, one warp per lane: last[c][e] becomes the chunk index * CHUNK +
-// offset of the most recent trigger BEFORE chunk c, as a 64-bit frame index split over two int planes
-// (plane 0: chunk of the trigger or -1, plane 1: offset within it).
-__global__ void latch_carry_kernel(int *last, int *src_chunk, int W, int NC) {
-  const int e = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+// Exclusive "most recent trigger" over chunks in three coalesced steps (threads run along the lanes):
+//   segments of LATCH_SEG chunks: (chunk, offset) of the last trigger inside each segment;
+//   one thread per lane walks the segment summaries (NC / LATCH_SEG of them) into "most recent before the segment";
+//   each (segment, lane) thread then walks its chunks: last[c][e] becomes the offset and src_chunk[c][e] the chunk of
+//   the most recent trigger BEFORE chunk c (chunk -1: none yet, the state cell holds the value).
+constexpr int LATCH_SEG = 32;
+
+__global__ void latch_seg_kernel(const int *__restrict__ last, int W, int NC, int NS, int *__restrict__ seg_chunk,
+                                 int *__restrict__ seg_off) {
+  const int e = blockIdx.x * blockDim.x + threadIdx.x, sgm = blockIdx.y;
   if (e >= W) return;
-  const int seg = (NC + 31) / 32, c0 = lane * seg, c1 = min(c0 + seg, NC);
-  // most recent trigger chunk within this thread's segment
-  int mine = -1;
-  for (int c = c0; c < c1; ++c)
-    if (last[(size_t)c * W + e] >= 0) mine = c;
-  // exclusive prefix maximum across the warp (chunk indices grow with the segment)
-  int incl = mine;
-#pragma unroll
-  for (int s = 1; s < 32; s <<= 1) {
-    int o = __shfl_up_sync(0xffffffffu, incl, s);
-    if (lane >= s) incl = max(incl, o);
+  const int c0 = sgm * LATCH_SEG, c1 = min(c0 + LATCH_SEG, NC);
+  int ch = -1, off = 0;
+#pragma unroll 8
+  for (int c = c0; c < c1; ++c) {
+    const int v = last[(size_t)c * W + e];
+    if (v >= 0) {
+      ch = c;
+      off = v;
+    }
   }
-  int run = __shfl_up_sync(0xffffffffu, incl, 1);
-  if (lane == 0) run = -1;
-  int run_off = run >= 0 ? last[(size_t)run * W + e] : 0;   // read before any thread overwrites: see the sync below
-  __syncwarp();
-  // every thread has read the offsets it needs from other segments; within its own segment it reads ahead of
-  // what it writes
+  seg_chunk[(size_t)sgm * W + e] = ch;
+  seg_off[(size_t)sgm * W + e] = off;
+}
+
+__global__ void latch_seg_carry_kernel(int *seg_chunk, int *seg_off, int W, int NS) {
+  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= W) return;
+  int run = -1, run_off = 0;
+  for (int sgm = 0; sgm < NS; ++sgm) {
+    const int ch = seg_chunk[(size_t)sgm * W + e], off = seg_off[(size_t)sgm * W + e];
+    seg_chunk[(size_t)sgm * W + e] = run;
+    seg_off[(size_t)sgm * W + e] = run_off;
+    if (ch >= 0) {
+      run = ch;
+      run_off = off;
+    }
+  }
+}
+
+__global__ void latch_carry_kernel(int *last, int *src_chunk, const int *__restrict__ seg_chunk,
+                                   const int *__restrict__ seg_off, int W, int NC) {
+  const int e = blockIdx.x * blockDim.x + threadIdx.x, sgm = blockIdx.y;
+  if (e >= W) return;
+  const int c0 = sgm * LATCH_SEG, c1 = min(c0 + LATCH_SEG, NC);
+  int run = seg_chunk[(size_t)sgm * W + e], run_off = seg_off[(size_t)sgm * W + e];
+#pragma unroll 8
   for (int c = c0; c < c1; ++c) {
     const int here = last[(size_t)c * W + e];
     src_chunk[(size_t)c * W + e] = run;
@@ -154,11 +249,64 @@ __global__ void latch_out_kernel(const float *__restrict__ value, const float *_
   float held = sc >= 0 ? value[((int64_t)sc * LATCH_CHUNK + src_off[(size_t)c * W + e]) * W + e]
                        : (state ? state[e] : 0.0f);
   const int64_t n0 = (int64_t)c * LATCH_CHUNK, n1 = min(n0 + (int64_t)LATCH_CHUNK, T);
-#pragma unroll 4
-  for (int64_t n = n0; n < n1; ++n) {
-    const float v = value[n * W + e];
-    if (cond_at(cond, cond_mode, n, e, W) > 0.0f) held = v;
-    y[n * W + e] = held;
+  // groups of sixteen frames: all loads of a group are issued before the dependent selects and stores
+  constexpr int G = 16;
+  for (int64_t n = n0; n < n1; n += G) {
+    float v[G], c[G];
+#pragma unroll
+    for (int j = 0; j < G; ++j) {
+      const int64_t m = min(n + j, n1 - 1);
+      v[j] = __ldcs(value + m * W + e);
+      c[j] = cond_at(cond, cond_mode, m, e, W);
+    }
+#pragma unroll
+    for (int j = 0; j < G; ++j)
+      if (n + j < n1) {
+        if (c[j] > 0.0f) held = v[j];
+        __stcs(y + (n + j) * W + e, held);
+      }
+  }
+}
+
+// The output pass with FOUR lanes per thread (W a multiple of 4): a warp reads 512 contiguous bytes of a frame, the
+// block = (W / 4 lane groups) x (chunks) covers whole rows, results leave as 128-bit streaming stores.
+__global__ void __launch_bounds__(256)
+latch_out4_kernel(const float *__restrict__ value, const float *__restrict__ cond, int cond_mode, int64_t T, int W,
+                  int NC, const int *__restrict__ src_off, const int *__restrict__ src_chunk,
+                  const float *__restrict__ state, float *__restrict__ y) {
+  const int e = (blockIdx.x * blockDim.x + threadIdx.x) * 4, c = blockIdx.y * blockDim.y + threadIdx.y;
+  if (e >= W || c >= NC) return;
+  float held[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int sc = src_chunk[(size_t)c * W + e + k];
+    held[k] = sc >= 0 ? value[((int64_t)sc * LATCH_CHUNK + src_off[(size_t)c * W + e + k]) * W + e + k]
+                      : (state ? state[e + k] : 0.0f);
+  }
+  const int64_t n0 = (int64_t)c * LATCH_CHUNK, n1 = min(n0 + (int64_t)LATCH_CHUNK, T);
+  constexpr int G = 8;
+  for (int64_t n = n0; n < n1; n += G) {
+    float4 v[G], cc[G];
+#pragma unroll
+    for (int j = 0; j < G; ++j) {
+      const int64_t m = min(n + j, n1 - 1);
+      v[j] = __ldcs(reinterpret_cast<const float4 *>(value + m * W + e));
+      if (cond_mode == 1) {
+        const float t = cond[m];
+        cc[j] = make_float4(t, t, t, t);
+      } else {
+        cc[j] = __ldcs(reinterpret_cast<const float4 *>(cond + m * W + e));
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < G; ++j)
+      if (n + j < n1) {
+        if (cc[j].x > 0.0f) held[0] = v[j].x;
+        if (cc[j].y > 0.0f) held[1] = v[j].y;
+        if (cc[j].z > 0.0f) held[2] = v[j].z;
+        if (cc[j].w > 0.0f) held[3] = v[j].w;
+        __stcs(reinterpret_cast<float4 *>(y + (n + j) * W + e), make_float4(held[0], held[1], held[2], held[3]));
+      }
   }
 }
 
@@ -186,60 +334,83 @@ __device__ __forceinline__ float gain_reduction(const CompCoef &c, float det_db)
 constexpr int COMP_TILE = 256;            // samples per warp iteration: 8 per lane
 constexpr int COMP_WARPS = 4;
 
-// one warp per voice.  Per tile: the lanes evaluate the gain computer of their eight samples (logarithm, knee),
-// every lane then walks the 256 smoothed values in frame order from shared memory (the one serial dependence:
-// compare, two multiply-adds, select) and keeps those of its own samples, and the lanes apply the gain.
+// pass 1, sample-parallel: gain reduction in dB wanted at every sample (logarithm, knee) -> buf
+__global__ void __launch_bounds__(256)
+comp_gain_kernel(const float *__restrict__ det, int64_t n, CompCoef c, float *__restrict__ buf) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) buf[i] = gain_reduction(c, amp2db(__ldcs(det + i)));
+}
+
+// pass 2, one warp per voice, in place: the attack / release smoother, the one serial dependence of the op.
+// Per tile of 256 samples the lanes stage (g, g (1 - att), g (1 - rel)) in shared memory, every lane then walks the
+// tile in frame order (per sample: two multiply-adds and a compare side by side, then a select) and keeps the
+// smoothed values of its own eight samples for a coalesced store.
 __global__ void __launch_bounds__(COMP_WARPS * 32)
-compressor_kernel(const float *__restrict__ x, const float *__restrict__ side, int B, int64_t T, CompCoef c,
-                  float *__restrict__ state, float *__restrict__ y) {
-  __shared__ float4 gs[COMP_WARPS][COMP_TILE];   // (g, g (1 - att), g (1 - rel), unused)
+comp_smooth_kernel(float *__restrict__ buf, int B, int64_t T, float att, float rel, float *__restrict__ state) {
+  __shared__ float4 gs[COMP_WARPS][COMP_TILE];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int b = blockIdx.x * COMP_WARPS + warp;
   if (b >= B) return;
-  const float *xb = x + (size_t)b * T, *db = side ? side + (size_t)b * T : xb;
-  float *yb = y + (size_t)b * T;
+  float *gb = buf + (size_t)b * T;
   float s = state ? state[b] : 0.0f;
-  const float one_m_att = 1.0f - c.att, one_m_rel = 1.0f - c.rel;
+  const float one_m_att = 1.0f - att, one_m_rel = 1.0f - rel;
+  float nxt[COMP_TILE / 32];
+#pragma unroll
+  for (int j = 0; j < COMP_TILE / 32; ++j) nxt[j] = j * 32 + lane < T ? gb[j * 32 + lane] : 0.0f;
   for (int64_t t0 = 0; t0 < T; t0 += COMP_TILE) {
     const int len = (int)min((int64_t)COMP_TILE, T - t0);
-    float xv[COMP_TILE / 32];
 #pragma unroll
     for (int j = 0; j < COMP_TILE / 32; ++j) {
-      const int i = j * 32 + lane;
-      xv[j] = i < len ? xb[t0 + i] : 0.0f;
-      const float dv = i < len ? db[t0 + i] : 0.0f;
-      const float g = gain_reduction(c, amp2db(dv));
-      gs[warp][i] = make_float4(g, g * one_m_att, g * one_m_rel, 0.0f);
+      const float g = nxt[j];
+      gs[warp][j * 32 + lane] = make_float4(g, g * one_m_att, g * one_m_rel, 0.0f);
     }
+    // the next tile's loads are in flight while this one is walked
+    const int64_t t1 = t0 + COMP_TILE;
+#pragma unroll
+    for (int j = 0; j < COMP_TILE / 32; ++j) nxt[j] = t1 + j * 32 + lane < T ? gb[t1 + j * 32 + lane] : 0.0f;
     __syncwarp();
     float keep[COMP_TILE / 32];
 #pragma unroll
     for (int j = 0; j < COMP_TILE / 32; ++j) {
+      keep[j] = 0.0f;
       if (j * 32 < len) {                      // uniform over the warp
         const int lim = min(32, len - j * 32);
-#pragma unroll 8
-        for (int i = 0; i < lim; ++i) {
-          const float4 g = gs[warp][j * 32 + i];
-          const float a_s = fmaf(c.att, s, g.y), r_s = fmaf(c.rel, s, g.z);
-          s = g.x > s ? a_s : r_s;
-          if (i == lane) keep[j] = s;
+        if (lim == 32) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float4 g = gs[warp][j * 32 + i];
+            const float a_s = fmaf(att, s, g.y), r_s = fmaf(rel, s, g.z);
+            s = g.x > s ? a_s : r_s;
+            if (i == lane) keep[j] = s;
+          }
+        } else {
+          for (int i = 0; i < lim; ++i) {
+            const float4 g = gs[warp][j * 32 + i];
+            const float a_s = fmaf(att, s, g.y), r_s = fmaf(rel, s, g.z);
+            s = g.x > s ? a_s : r_s;
+            if (i == lane) keep[j] = s;
+          }
         }
       }
     }
     __syncwarp();
 #pragma unroll
-    for (int j = 0; j < COMP_TILE / 32; ++j) {
-      const int i = j * 32 + lane;
-      if (i < len) {
-        const float v = xv[j];
-        const float att_db = amp2db(v) - keep[j];
-        const float amp = powf(10.0f, att_db / 20.0f);
-        const float sg = v > 0.0f ? 1.0f : (v < 0.0f ? -1.0f : 0.0f);
-        yb[t0 + i] = sg * amp;
-      }
-    }
+    for (int j = 0; j < COMP_TILE / 32; ++j)
+      if (j * 32 + lane < len) gb[t0 + j * 32 + lane] = keep[j];
   }
   if (state && lane == 0) state[b] = s;
+}
+
+// pass 3, sample-parallel, in place over the smoothed reduction: y = sign(x) 10^((dB(x) - s) / 20)
+__global__ void __launch_bounds__(256)
+comp_apply_kernel(const float *__restrict__ x, int64_t n, float *__restrict__ y) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const float v = __ldcs(x + i);
+  const float att_db = amp2db(v) - y[i];
+  const float amp = powf(10.0f, att_db / 20.0f);
+  const float sg = v > 0.0f ? 1.0f : (v < 0.0f ? -1.0f : 0.0f);
+  y[i] = sg * amp;
 }
 
 // ---- phase vocoder ----------------------------------------------------------------------------------------------
@@ -339,8 +510,8 @@ DGC_EXPORT int32_t dgc_delay_line(dgc_ctx *ctx, const float *x_dev, const float 
   DGC_REQUIRE(ctx, (ring_dev == nullptr) == (head_dev == nullptr), "ring and head must be given together");
   DGC_REQUIRE(ctx, x_dev != y_dev, "in-place operation is not supported");
   DGC_REQUIRE(ctx, T * lanes / 256 < 0x7fffffffLL, "T * lanes too large");
-  frac_delay_kernel<false><<<dgc_div_up(T * lanes, 256), 256, 0, ctx->stream>>>(
-      x_dev, delay_dev, delay_mode, 0, T, lanes, max_delay, (float)(max_delay - 1), ring_dev, head_dev, y_dev);
+  launch_frac_delay<false>(ctx->stream, x_dev, delay_dev, delay_mode, 0, T, lanes, max_delay, (float)(max_delay - 1),
+                           ring_dev, head_dev, y_dev);
   DGC_LAUNCHED(ctx, "delay_line");
   if (ring_dev) {
     ring_update_kernel<false><<<dgc_div_up((int64_t)lanes * max_delay, 256), 256, 0, ctx->stream>>>(
@@ -363,8 +534,8 @@ DGC_EXPORT int32_t dgc_spectrum_delay(dgc_ctx *ctx, const float *spec_dev, const
   DGC_REQUIRE(ctx, H * N / 256 < 0x7fffffffLL, "H * N too large");
   const int R = hops + 1;
   // fixed delay: the spectrum of exactly `hops` boundaries ago; modulated: per-hop delay in [0, hops]
-  frac_delay_kernel<true><<<dgc_div_up(H * N, 256), 256, 0, ctx->stream>>>(
-      spec_dev, delay_dev, delay_dev ? 1 : -1, hops, H, N, R, (float)hops, ring_dev, row_dev, out_dev);
+  launch_frac_delay<true>(ctx->stream, spec_dev, delay_dev, delay_dev ? 1 : -1, hops, H, N, R, (float)hops, ring_dev,
+                          row_dev, out_dev);
   DGC_LAUNCHED(ctx, "spectrum_delay");
   if (ring_dev) {
     ring_update_kernel<true><<<dgc_div_up((int64_t)N * R, 256), 256, 0, ctx->stream>>>(spec_dev, H, N, R, ring_dev,
@@ -378,7 +549,8 @@ DGC_EXPORT int32_t dgc_spectrum_delay(dgc_ctx *ctx, const float *spec_dev, const
 
 DGC_EXPORT uint64_t dgc_latch_scratch_floats(int64_t T, int32_t lanes) {
   if (T <= 0 || lanes <= 0) return 0;
-  return 2ull * (uint64_t)((T + LATCH_CHUNK - 1) / LATCH_CHUNK) * (uint64_t)lanes;
+  const uint64_t NC = (uint64_t)((T + LATCH_CHUNK - 1) / LATCH_CHUNK), NS = (NC + LATCH_SEG - 1) / LATCH_SEG;
+  return (2 * NC + 2 * NS) * (uint64_t)lanes;
 }
 
 DGC_EXPORT int32_t dgc_latch(dgc_ctx *ctx, const float *value_dev, const float *cond_dev, int32_t cond_mode, int64_t T,
@@ -396,10 +568,25 @@ DGC_EXPORT int32_t dgc_latch(dgc_ctx *ctx, const float *value_dev, const float *
   dim3 grid(dgc_div_up(lanes, 128), NC);
   latch_last_kernel<<<grid, 128, 0, ctx->stream>>>(cond_dev, cond_mode, T, lanes, NC, last);
   DGC_LAUNCHED(ctx, "latch_last");
-  latch_carry_kernel<<<dgc_div_up(lanes, 4), 128, 0, ctx->stream>>>(last, src_chunk, lanes, NC);
+  const int NS = dgc_div_up(NC, LATCH_SEG);
+  int *seg_chunk = src_chunk + (size_t)NC * lanes, *seg_off = seg_chunk + (size_t)NS * lanes;
+  dim3 sgrid(dgc_div_up(lanes, 128), NS);
+  latch_seg_kernel<<<sgrid, 128, 0, ctx->stream>>>(last, lanes, NC, NS, seg_chunk, seg_off);
+  DGC_LAUNCHED(ctx, "latch_segments");
+  latch_seg_carry_kernel<<<dgc_div_up(lanes, 128), 128, 0, ctx->stream>>>(seg_chunk, seg_off, lanes, NS);
+  DGC_LAUNCHED(ctx, "latch_segment_carry");
+  latch_carry_kernel<<<sgrid, 128, 0, ctx->stream>>>(last, src_chunk, seg_chunk, seg_off, lanes, NC);
   DGC_LAUNCHED(ctx, "latch_carry");
-  latch_out_kernel<<<grid, 128, 0, ctx->stream>>>(value_dev, cond_dev, cond_mode, T, lanes, NC, last, src_chunk,
-                                                  state_dev, y_dev);
+  const bool quad = (lanes & 3) == 0 &&
+                    ((((uintptr_t)value_dev) | ((uintptr_t)y_dev) | (cond_mode == 2 ? (uintptr_t)cond_dev : 0)) & 15) == 0;
+  if (quad) {
+    const int bx = lanes / 4 >= 64 ? 64 : lanes / 4, by = 256 / bx >= 1 ? (256 / bx > 8 ? 8 : 256 / bx) : 1;
+    latch_out4_kernel<<<dim3(dgc_div_up(lanes / 4, bx), dgc_div_up(NC, by)), dim3(bx, by), 0, ctx->stream>>>(
+        value_dev, cond_dev, cond_mode, T, lanes, NC, last, src_chunk, state_dev, y_dev);
+  } else {
+    latch_out_kernel<<<grid, 128, 0, ctx->stream>>>(value_dev, cond_dev, cond_mode, T, lanes, NC, last, src_chunk,
+                                                    state_dev, y_dev);
+  }
   DGC_LAUNCHED(ctx, "latch_out");
   if (state_dev) {
     latch_state_kernel<<<dgc_div_up(lanes, 128), 128, 0, ctx->stream>>>(y_dev, T, lanes, state_dev);
@@ -427,8 +614,16 @@ DGC_EXPORT int32_t dgc_compressor(dgc_ctx *ctx, const dgc_compressor_params *p, 
   c.knee_end = p->threshold + half;
   c.hard_ratio = 1.0f - 1.0f / p->ratio;
   c.thr_minus_start = p->threshold - c.knee_start;
-  compressor_kernel<<<dgc_div_up(p->B, COMP_WARPS), COMP_WARPS * 32, 0, ctx->stream>>>(x_dev, sidechain_dev, p->B, p->T, c,
-                                                                                    state_dev, y_dev);
+  DGC_REQUIRE(ctx, x_dev != y_dev && sidechain_dev != y_dev, "in-place operation is not supported");
+  const int64_t n = (int64_t)p->B * p->T;
+  DGC_REQUIRE(ctx, n / 256 < 0x7fffffffLL, "B * T too large");
+  // y doubles as the work buffer: wanted reduction -> smoothed reduction (in place) -> output (in place)
+  comp_gain_kernel<<<dgc_div_up(n, 256), 256, 0, ctx->stream>>>(sidechain_dev ? sidechain_dev : x_dev, n, c, y_dev);
+  DGC_LAUNCHED(ctx, "compressor_gain");
+  comp_smooth_kernel<<<dgc_div_up(p->B, COMP_WARPS), COMP_WARPS * 32, 0, ctx->stream>>>(y_dev, p->B, p->T, c.att, c.rel,
+                                                                                     state_dev);
+  DGC_LAUNCHED(ctx, "compressor_smooth");
+  comp_apply_kernel<<<dgc_div_up(n, 256), 256, 0, ctx->stream>>>(x_dev, n, y_dev);
   DGC_LAUNCHED(ctx, "compressor");
   return DGC_OK;
 }
