@@ -502,11 +502,11 @@ def run_filters(args, local_rank):
         torch.cuda.synchronize()
         return a.elapsed_time(b) / args.steps
 
-    def emit(metric, workload, ms, bytes_, extra=None):
+    def emit(metric, workload, ms, bytes_, extra=None, l2="inputs + outputs larger than L2"):
         gbs = bytes_ / ms / 1e6
         line = {"metric": metric, "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
                 "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True, "dtype": "f32",
-                "data": "synthetic", "config": {"workload": workload, "l2": "inputs + outputs larger than L2"},
+                "data": "synthetic", "config": {"workload": workload, "l2": l2},
                 "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak,
                              "peak_kind": peak_kind, "algorithmic_bytes": bytes_}}
         if extra:
@@ -514,6 +514,21 @@ def run_filters(args, local_rank):
         print(json.dumps(line))
 
     scale = args.voices if args.voices > 0 else 0
+    # the reference's own small case (BASELINE.json configs[0]): 64 partials -> one-pole -> buffer(1024, hop 256) -> FFT
+    # magnitudes, 65536 frames.  Three launches' worth of work: launch latency, not a roofline, bounds it.
+    c1 = wl.osc_filter_fft_inputs()
+    fq, am = dev(c1["freq"]), dev(c1["amp"])
+
+    def c1_chain():
+        osc = ctx.osc_bank_const(fq, am, c1["T"], c1["sr"], dgen_b200.PHASE_DETERMINISTIC)
+        return ctx.stft_mag(ctx.onepole_fwd(osc.view(1, -1), c1["pole"]), c1["N"], c1["hop"])
+
+    ms = timed(c1_chain)
+    emit("oscillator bank -> one-pole -> FFT", "64 partials, 65536 frames at 44.1 kHz, FFT 1024 hop 256 (BASELINE.json configs[0])",
+         ms, 4.0 * (2 * 64 + c1["T"] + 256 * 513),
+         {"samples_per_s": c1["T"] / (ms * 1e-3), "partial_samples_per_s": 64 * c1["T"] / (ms * 1e-3),
+          "roofline_note": "launch bound at this size: three small launches and their allocations"},
+         l2="working set (0.8 MB) is L2 resident: a latency figure, not a bandwidth one")
     # biquad bank: 256 lanes x 32 voices x 262144 frames (8.6 GB of lane signals)
     d = wl.biquad_bank_inputs(20260002)
     B, L, T = (scale or d["B"]), d["L"], d["T"]
