@@ -46,6 +46,12 @@ struct dgc_ctx {
   cudaEvent_t copy_ev[3] = {nullptr, nullptr, nullptr};
   float *stage_dev = nullptr;
   uint64_t stage_floats = 0;
+  // two host-buffer steps in flight (plans.cu): per-slot input staging, upload events, end-of-step event
+  float *pipe_in[2] = {nullptr, nullptr};
+  uint64_t pipe_in_floats[2] = {0, 0};
+  cudaEvent_t pipe_ev[2][3] = {{nullptr, nullptr, nullptr}, {nullptr, nullptr, nullptr}};
+  cudaEvent_t pipe_done[2] = {nullptr, nullptr};
+  bool pipe_used[2] = {false, false}, pipe_pending[2] = {false, false};
   // NCCL communicator of the gradient exchange (comm.cu); nullptr = a world of one
   void *comm = nullptr;
   int comm_world = 1;

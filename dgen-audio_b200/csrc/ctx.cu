@@ -187,6 +187,12 @@ DGC_EXPORT int32_t dgc_ctx_destroy(dgc_ctx *c) {
   if (c->scratch) cudaFree(c->scratch);
   if (c->comm) dgc_comm_destroy(c);
   if (c->stage_dev) cudaFree(c->stage_dev);
+  for (int i = 0; i < 2; ++i) {
+    if (c->pipe_in[i]) cudaFree(c->pipe_in[i]);
+    if (c->pipe_done[i]) cudaEventDestroy(c->pipe_done[i]);
+    for (auto &e : c->pipe_ev[i])
+      if (e) cudaEventDestroy(e);
+  }
   for (auto &e : c->copy_ev)
     if (e) cudaEventDestroy(e);
   if (c->copy_stream) cudaStreamDestroy(c->copy_stream);

@@ -153,11 +153,13 @@ DGC_EXPORT int32_t dgc_hn_forward_loss(dgc_ctx *ctx, const dgc_hn_step *s, const
                               noise_dev, target_dev, work_dev, loss_dev, audio_dev, nullptr, nullptr);
 }
 
-DGC_EXPORT int32_t dgc_hn_forward_loss_host(dgc_ctx *ctx, const dgc_hn_step *s, const float *f0_host,
-                                            const float *uv_host, const float *amps_host, const float *gain_host,
-                                            const float *noise_gain_host, const float *taps_or_bands_host,
-                                            const float *w_host, const float *noise_host, const float *target_host,
-                                            double *loss_host, float *audio_host) {
+// slot < 0: the blocking call (one staging area, returns after the loss has arrived).
+// slot 0 / 1: one of two steps in flight -- inputs go to the slot's own staging area, so the upload of the next
+// step crosses PCIe while this step computes; nothing is waited for here (dgc_hn_forward_loss_host_wait does).
+static int32_t hn_host_enqueue(dgc_ctx *ctx, const dgc_hn_step *s, const float *f0_host, const float *uv_host,
+                               const float *amps_host, const float *gain_host, const float *noise_gain_host,
+                               const float *taps_or_bands_host, const float *w_host, const float *noise_host,
+                               const float *target_host, double *loss_host, float *audio_host, int slot) {
   if (!ctx) return DGC_ERR_INVALID;
   DGC_REQUIRE(ctx, s && f0_host && uv_host && amps_host && gain_host && target_host && loss_host, "null pointer");
   const int B = s->harm.B, T = s->harm.T, K = s->harm.K, F = s->harm.F;
@@ -176,16 +178,44 @@ DGC_EXPORT int32_t dgc_hn_forward_loss_host(dgc_ctx *ctx, const dgc_hn_step *s, 
   // host -> device inputs, in one contiguous pinned block
   const uint64_t in_floats = 3 * nFB + nFB * K + (noise ? nFB + n_tab + n_w + nBT : 0) + nBT;
   const uint64_t dev_extra = nBT /*audio*/ + dgc_hn_forward_loss_work_floats(s) + 64 * 16;
-  int32_t rc = ensure_stage(ctx, in_floats + dev_extra + 64 * 16);
+  const bool piped = slot >= 0;
+  if (!piped)
+    DGC_REQUIRE(ctx, !ctx->pipe_pending[0] && !ctx->pipe_pending[1],
+                "steps submitted with dgc_hn_forward_loss_host_submit are still in flight: wait for them first");
+  int32_t rc = ensure_stage(ctx, (piped ? 0 : in_floats) + dev_extra + 64 * 16);
   if (rc != DGC_OK) return rc;
 
   if (!ctx->copy_stream) {
     DGC_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->copy_stream, cudaStreamNonBlocking));
     for (auto &e : ctx->copy_ev) DGC_CUDA(ctx, cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
   }
-  // Every earlier call ended with a stream synchronisation, so no kernel still reads the staging area;
-  // work the caller queued on the context stream before this call does not touch it either.
-  Carver dc(ctx->stage_dev);
+  cudaEvent_t *ev = ctx->copy_ev;
+  if (piped) {
+    const uint64_t need = in_floats + 64 * 16;
+    if (ctx->pipe_in_floats[slot] < need) {
+      if (ctx->pipe_in[slot]) {
+        cudaStreamSynchronize(ctx->stream);
+        cudaStreamSynchronize(ctx->copy_stream);
+        cudaFree(ctx->pipe_in[slot]);
+        ctx->pipe_in[slot] = nullptr;
+        ctx->pipe_in_floats[slot] = 0;
+      }
+      DGC_CUDA(ctx, cudaMalloc(&ctx->pipe_in[slot], need * sizeof(float)));
+      ctx->pipe_in_floats[slot] = need;
+    }
+    if (!ctx->pipe_done[slot]) {
+      DGC_CUDA(ctx, cudaEventCreateWithFlags(&ctx->pipe_done[slot], cudaEventDisableTiming));
+      for (auto &e : ctx->pipe_ev[slot]) DGC_CUDA(ctx, cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    }
+    ev = ctx->pipe_ev[slot];
+    // the slot's previous step may still read its staging area: the new upload waits for that step's end
+    if (ctx->pipe_pending[slot])
+      return dgc_fail(ctx, DGC_ERR_INVALID, "slot %d still holds a step: call dgc_hn_forward_loss_host_wait first", slot);
+    if (ctx->pipe_used[slot]) DGC_CUDA(ctx, cudaStreamWaitEvent(ctx->copy_stream, ctx->pipe_done[slot], 0));
+  }
+  // Blocking form: every earlier call ended with a stream synchronisation, so no kernel still reads the staging
+  // area; work the caller queued on the context stream before this call does not touch it either.
+  Carver dc(piped ? ctx->pipe_in[slot] : ctx->stage_dev);
   cudaError_t cp_err = cudaSuccess;
   static const bool inline_upload = [] {
     const char *e = getenv("DGC_UPLOAD");
@@ -199,7 +229,7 @@ DGC_EXPORT int32_t dgc_hn_forward_loss_host(dgc_ctx *ctx, const dgc_hn_step *s, 
     return d;
   };
   auto mark = [&](int i) {
-    cudaError_t e = cudaEventRecord(ctx->copy_ev[i], up);
+    cudaError_t e = cudaEventRecord(ev[i], up);
     if (e != cudaSuccess && cp_err == cudaSuccess) cp_err = e;
   };
   // group 0: harmonic controls; group 1: noise branch; group 2: target
@@ -228,16 +258,53 @@ DGC_EXPORT int32_t dgc_hn_forward_loss_host(dgc_ctx *ctx, const dgc_hn_step *s, 
   };
   // device work area of the two-branch step, and (only when the caller wants the audio back) the summed signal
   dgc_hn_step st = *s;
-  float *d_work = dc.take(dgc_hn_forward_loss_work_floats(&st));
-  float *d_audio = audio_host ? dc.take(nBT) : nullptr;
+  // (two steps in flight share ONE work area: their kernels run one after the other on the context stream)
+  Carver wc(ctx->stage_dev);
+  Carver &work_carver = piped ? wc : dc;
+  float *d_work = work_carver.take(dgc_hn_forward_loss_work_floats(&st));
+  float *d_audio = audio_host ? work_carver.take(nBT) : nullptr;
   // the harmonic branch only needs group 0; the noise branch and the loss wait for their own uploads inside
-  if (cudaStreamWaitEvent(ctx->stream, ctx->copy_ev[0], 0) != cudaSuccess) return bail(dgc_fail(ctx, DGC_ERR_CUDA, "event wait"));
-  rc = hn_forward_loss_impl(ctx, &st, d_f0, d_uv, d_amps, d_gain, d_ng, d_tab, d_w, d_noise, d_target, d_work,
-                            ctx->loss_accum, d_audio, inline_upload ? nullptr : ctx->copy_ev[1],
-                            inline_upload ? nullptr : ctx->copy_ev[2]);
+  if (cudaStreamWaitEvent(ctx->stream, ev[0], 0) != cudaSuccess) return bail(dgc_fail(ctx, DGC_ERR_CUDA, "event wait"));
+  double *loss_dev = ctx->loss_accum + (piped ? 1 + slot : 0);
+  rc = hn_forward_loss_impl(ctx, &st, d_f0, d_uv, d_amps, d_gain, d_ng, d_tab, d_w, d_noise, d_target, d_work, loss_dev,
+                            d_audio, inline_upload ? nullptr : ev[1], inline_upload ? nullptr : ev[2]);
   if (rc != DGC_OK) return bail(rc);
-  DGC_CUDA(ctx, cudaMemcpyAsync(loss_host, ctx->loss_accum, sizeof(double), cudaMemcpyDeviceToHost, ctx->stream));
+  DGC_CUDA(ctx, cudaMemcpyAsync(loss_host, loss_dev, sizeof(double), cudaMemcpyDeviceToHost, ctx->stream));
   if (audio_host)
     DGC_CUDA(ctx, cudaMemcpyAsync(audio_host, d_audio, nBT * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
-  return dgc_sync(ctx, 0);
+  if (!piped) return dgc_sync(ctx, 0);
+  DGC_CUDA(ctx, cudaEventRecord(ctx->pipe_done[slot], ctx->stream));
+  ctx->pipe_used[slot] = true;
+  ctx->pipe_pending[slot] = true;
+  return DGC_OK;
+}
+
+DGC_EXPORT int32_t dgc_hn_forward_loss_host(dgc_ctx *ctx, const dgc_hn_step *s, const float *f0_host,
+                                            const float *uv_host, const float *amps_host, const float *gain_host,
+                                            const float *noise_gain_host, const float *taps_or_bands_host,
+                                            const float *w_host, const float *noise_host, const float *target_host,
+                                            double *loss_host, float *audio_host) {
+  return hn_host_enqueue(ctx, s, f0_host, uv_host, amps_host, gain_host, noise_gain_host, taps_or_bands_host, w_host,
+                         noise_host, target_host, loss_host, audio_host, -1);
+}
+
+DGC_EXPORT int32_t dgc_hn_forward_loss_host_submit(dgc_ctx *ctx, const dgc_hn_step *s, const float *f0_host,
+                                                   const float *uv_host, const float *amps_host,
+                                                   const float *gain_host, const float *noise_gain_host,
+                                                   const float *taps_or_bands_host, const float *w_host,
+                                                   const float *noise_host, const float *target_host, int32_t slot,
+                                                   double *loss_host, float *audio_host) {
+  if (!ctx) return DGC_ERR_INVALID;
+  DGC_REQUIRE(ctx, slot == 0 || slot == 1, "slot must be 0 or 1");
+  return hn_host_enqueue(ctx, s, f0_host, uv_host, amps_host, gain_host, noise_gain_host, taps_or_bands_host, w_host,
+                         noise_host, target_host, loss_host, audio_host, slot);
+}
+
+DGC_EXPORT int32_t dgc_hn_forward_loss_host_wait(dgc_ctx *ctx, int32_t slot) {
+  if (!ctx) return DGC_ERR_INVALID;
+  DGC_REQUIRE(ctx, slot == 0 || slot == 1, "slot must be 0 or 1");
+  DGC_REQUIRE(ctx, ctx->pipe_pending[slot], "no step was submitted on this slot");
+  ctx->pipe_pending[slot] = false;
+  DGC_CUDA(ctx, cudaEventSynchronize(ctx->pipe_done[slot]));
+  return DGC_OK;
 }

@@ -178,6 +178,8 @@ SIGNATURES = {
     "dgc_hn_forward_loss_work_floats": (_u64, [C.POINTER(HnStep)]),
     "dgc_hn_forward_loss": (_i32, [_vp, C.POINTER(HnStep)] + [_vp] * 9 + [_vp, _vp, _vp]),
     "dgc_hn_forward_loss_host": (_i32, [_vp, C.POINTER(HnStep)] + [_vp] * 9 + [C.POINTER(C.c_double), _vp]),
+    "dgc_hn_forward_loss_host_submit": (_i32, [_vp, C.POINTER(HnStep)] + [_vp] * 9 + [_i32, _vp, _vp]),
+    "dgc_hn_forward_loss_host_wait": (_i32, [_vp, _i32]),
 }
 
 _lib = None
@@ -725,6 +727,25 @@ class Context:
                                                      hp(noise_gain), hp(taps_or_bands), hp(w), hp(noise),
                                                      hp(target), C.byref(loss), hp(audio_out)))
         return loss.value
+
+
+    def hn_forward_loss_host_submit(self, step, f0, uv, amps, gain, noise_gain, taps_or_bands, w, noise, target, slot,
+                                    audio_out=None):
+        """Enqueue one host-buffer step on slot 0 or 1 and return at once; hn_forward_loss_host_wait(slot) returns its
+        loss.  The arrays must be pinned and stay untouched until the wait."""
+        def hp(a):
+            if a is None:
+                return None
+            return a.data_ptr() if hasattr(a, "data_ptr") else a.ctypes.data
+        if getattr(self, "_pipe_loss", None) is None:
+            self._pipe_loss = self.torch.zeros(2, dtype=self.torch.float64).pin_memory()
+        self.check(self.lib.dgc_hn_forward_loss_host_submit(
+            self.h, C.byref(step), hp(f0), hp(uv), hp(amps), hp(gain), hp(noise_gain), hp(taps_or_bands), hp(w),
+            hp(noise), hp(target), slot, self._pipe_loss.data_ptr() + 8 * slot, hp(audio_out)))
+
+    def hn_forward_loss_host_wait(self, slot):
+        self.check(self.lib.dgc_hn_forward_loss_host_wait(self.h, slot))
+        return float(self._pipe_loss[slot])
 
 
 _cudart_lib = None

@@ -528,6 +528,19 @@ int32_t dgc_hn_forward_loss_host(dgc_ctx *ctx, const dgc_hn_step *s, const float
                                  const float *taps_or_bands_host, const float *w_host, const float *noise_host,
                                  const float *target_host, double *loss_host, float *audio_host);
 
+/* The same step with TWO steps in flight: submit enqueues the uploads (into the slot's own staging area), the step and
+ * the read-back of the loss and returns at once; wait blocks until that slot's step has finished and *loss_host (and
+ * audio_host) are valid.  While slot 0 computes, the inputs of slot 1 cross PCIe: steady-state throughput is the
+ * larger of upload time and compute time instead of their sum.  Host buffers of a slot must stay untouched from
+ * submit to wait (pinned memory, or the copies are not asynchronous).  slot is 0 or 1; a slot is reusable after its
+ * wait.  Typical loop: submit(i % 2) then wait((i - 1) % 2). */
+int32_t dgc_hn_forward_loss_host_submit(dgc_ctx *ctx, const dgc_hn_step *s, const float *f0_host, const float *uv_host,
+                                        const float *amps_host, const float *gain_host,
+                                        const float *noise_gain_host, const float *taps_or_bands_host,
+                                        const float *w_host, const float *noise_host, const float *target_host,
+                                        int32_t slot, double *loss_host, float *audio_host);
+int32_t dgc_hn_forward_loss_host_wait(dgc_ctx *ctx, int32_t slot);
+
 #ifdef __cplusplus
 }
 #endif

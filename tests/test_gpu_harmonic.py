@@ -145,3 +145,42 @@ def test_device_resident_composite_equals_the_staged_calls(ctx):
         assert float(loss.cpu()[0]) == want
         if want_audio:
             assert torch.equal(out, audio)
+
+
+def test_two_host_buffer_steps_in_flight_equal_the_blocking_call(ctx):
+    """dgc_hn_forward_loss_host_submit / _wait: different batches alternate over the two slots; every loss (and the
+    audio read back) equals the blocking host-buffer call on the same batch; a slot cannot be resubmitted before its
+    wait, and the blocking call refuses to run while steps are in flight."""
+    import torch
+    B, T, K, F, NB, NT = 3, 9000, 40, 70, 9, 33
+    st = dgen_b200.HnStep()
+    st.harm = dgen_b200.HarmonicParams(B, T, K, F, 16000.0, 1.0, dgen_b200.PHASE_SCAN, 0)
+    st.fir = dgen_b200.FirParams(B, T, F, NT, 0.12, 1)
+    st.mss = dgen_b200.mss_params(B, T, (512, 128, 64))
+    st.nbands = NB
+    pin = lambda a: torch.from_numpy(np.ascontiguousarray(a)).pin_memory()
+    order = ("f0", "uv", "amps", "gain", "noise_gain", "bands", "W", "noise")
+    batches, want, want_audio = [], [], []
+    for i in range(5):
+        d = wl.harmonic_noise_inputs(70 + i, B=B, T=T, K=K, F=F, nbands=NB, taps=NT)
+        P = [pin(d[k]) for k in order] + [pin(np.random.default_rng(i).standard_normal((B, T)).astype(f32) * f32(0.1))]
+        batches.append(P)
+        a = pin(np.zeros((B, T), f32))
+        want.append(ctx.hn_forward_loss_host(st, *P, audio_out=a))
+        want_audio.append(a.numpy().copy())
+    got = [None] * 5
+    audio = [pin(np.zeros((B, T), f32)) for _ in range(2)]
+    ctx.hn_forward_loss_host_submit(st, *batches[0], 0, audio_out=audio[0])
+    with pytest.raises(dgen_b200.DgenCudaError):
+        ctx.hn_forward_loss_host_submit(st, *batches[1], 0)            # slot 0 is still in flight
+    with pytest.raises(dgen_b200.DgenCudaError):
+        ctx.hn_forward_loss_host(st, *batches[1])                      # blocking call while a step is in flight
+    for i in range(1, 5):
+        ctx.hn_forward_loss_host_submit(st, *batches[i], i % 2, audio_out=audio[i % 2])
+        got[i - 1] = ctx.hn_forward_loss_host_wait((i - 1) % 2)
+        assert np.array_equal(audio[(i - 1) % 2].numpy(), want_audio[i - 1])
+    got[4] = ctx.hn_forward_loss_host_wait(0)
+    assert got == want
+    with pytest.raises(dgen_b200.DgenCudaError):
+        ctx.hn_forward_loss_host_wait(1)                               # nothing submitted on slot 1 any more
+    assert ctx.hn_forward_loss_host(st, *batches[2]) == want[2]        # the blocking call works again
