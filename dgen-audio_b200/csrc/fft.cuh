@@ -82,11 +82,21 @@ __device__ __forceinline__ void stage(const float2 *__restrict__ in, float2 *__r
     for (int t = 0; t < R; ++t) v[t] = in[pad(j + t * (N / R))];
     if (Ns > 1) {
       const int step = N / (Ns * R);
+      if (R == 8) {
+        // w^1, w^2, w^4 from the table, the other four powers as products of those (one rounding more than a
+        // table value): three loads per butterfly instead of seven on the load/store pipe the stage is bound by
+        float2 w1 = __ldg(&tw[k * step]), w2 = __ldg(&tw[k * 2 * step]), w4 = __ldg(&tw[k * 4 * step]);
+        if (INV) { w1.y = -w1.y; w2.y = -w2.y; w4.y = -w4.y; }
+        const float2 w3 = cmul(w1, w2), w5 = cmul(w1, w4), w6 = cmul(w2, w4), w7 = cmul(w3, w4);
+        v[1] = cmul(v[1], w1); v[2] = cmul(v[2], w2); v[3] = cmul(v[3], w3); v[4] = cmul(v[4], w4);
+        v[5] = cmul(v[5], w5); v[6] = cmul(v[6], w6); v[7] = cmul(v[7], w7);
+      } else {
 #pragma unroll
-      for (int t = 1; t < R; ++t) {
-        float2 w = __ldg(&tw[k * t * step]);
-        if (INV) w.y = -w.y;
-        v[t] = cmul(v[t], w);
+        for (int t = 1; t < R; ++t) {
+          float2 w = __ldg(&tw[k * t * step]);
+          if (INV) w.y = -w.y;
+          v[t] = cmul(v[t], w);
+        }
       }
     }
     dftR<R, INV>(v);
@@ -97,8 +107,16 @@ __device__ __forceinline__ void stage(const float2 *__restrict__ in, float2 *__r
 }
 
 // Full transform of N points held in shared buffer `a` (scratch buffer `b`); N/8 threads take part
-// and every one of them must call this (it synchronises the whole block between stages).  Returns
-// the buffer that holds the result in natural order.
+// and every thread of the block must call this.  Between stages it synchronises the threads that share the
+// transform: the whole block when a transform spans several warps, only the warp when its N/8 <= 32 threads sit
+// inside one (transforms of other warps touch other buffers).  Callers that let OTHER threads read the result
+// synchronise the block themselves.  Returns the buffer that holds the result in natural order.
+template <int N>
+__device__ __forceinline__ void fft_sync() {
+  if (N / 8 <= 32) __syncwarp();
+  else __syncthreads();
+}
+
 template <int N, bool INV>
 __device__ __forceinline__ float2 *fft_block(float2 *a, float2 *b, int tid, const float2 *__restrict__ tw) {
   static_assert(N >= 16 && N <= 4096 && (N & (N - 1)) == 0, "N must be a power of two in 16..4096");
@@ -112,16 +130,16 @@ __device__ __forceinline__ float2 *fft_block(float2 *a, float2 *b, int tid, cons
     stage<N, 8, INV>(src, dst, Ns, tid, tw);
     Ns *= 8;
     t = src; src = dst; dst = t;
-    __syncthreads();
+    fft_sync<N>();
   }
   if (REM == 2) {
     stage<N, 4, INV>(src, dst, Ns, tid, tw);
     t = src; src = dst; dst = t;
-    __syncthreads();
+    fft_sync<N>();
   } else if (REM == 1) {
     stage<N, 2, INV>(src, dst, Ns, tid, tw);
     t = src; src = dst; dst = t;
-    __syncthreads();
+    fft_sync<N>();
   }
   return src;
 }
