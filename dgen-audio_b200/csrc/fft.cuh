@@ -144,4 +144,41 @@ __device__ __forceinline__ float2 *fft_block(float2 *a, float2 *b, int tid, cons
   return src;
 }
 
+// The same transform when thread `tid` already HOLDS its eight inputs of the first stage in registers
+// (v[t] = element tid + t * N/8, which is exactly what a thread that fills the buffer with stride N/8 produces):
+// the first radix-8 stage runs straight from the registers, which saves writing the inputs to shared memory,
+// the barrier after that, and reading them back.  `a` receives the first stage's output; nobody may still be
+// reading `a` or `b` when this is called.
+template <int N, bool INV>
+__device__ __forceinline__ float2 *fft_block_regs(float2 (&v)[8], float2 *a, float2 *b, int tid,
+                                                  const float2 *__restrict__ tw) {
+  static_assert(N >= 16 && N <= 4096 && (N & (N - 1)) == 0, "N must be a power of two in 16..4096");
+  constexpr int LOG = N == 16 ? 4 : N == 32 ? 5 : N == 64 ? 6 : N == 128 ? 7 : N == 256 ? 8 : N == 512 ? 9
+                      : N == 1024 ? 10 : N == 2048 ? 11 : 12;
+  constexpr int N8 = LOG / 3, REM = LOG % 3;
+  dft8<INV>(v);
+#pragma unroll
+  for (int t = 0; t < 8; ++t) a[pad(tid * 8 + t)] = v[t];
+  fft_sync<N>();
+  int Ns = 8;
+  float2 *src = a, *dst = b, *t;
+#pragma unroll
+  for (int s = 1; s < N8; ++s) {
+    stage<N, 8, INV>(src, dst, Ns, tid, tw);
+    Ns *= 8;
+    t = src; src = dst; dst = t;
+    fft_sync<N>();
+  }
+  if (REM == 2) {
+    stage<N, 4, INV>(src, dst, Ns, tid, tw);
+    t = src; src = dst; dst = t;
+    fft_sync<N>();
+  } else if (REM == 1) {
+    stage<N, 2, INV>(src, dst, Ns, tid, tw);
+    t = src; src = dst; dst = t;
+    fft_sync<N>();
+  }
+  return src;
+}
+
 }  // namespace dgfft

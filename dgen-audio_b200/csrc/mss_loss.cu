@@ -65,6 +65,9 @@ __device__ __forceinline__ void mss_fwd_body(float2 *sm, float *red, int bx, int
   const float *x1 = pred + (size_t)b * T, *x2 = target + (size_t)b * T;
   const float *x1b = SUM2 ? pred_b + (size_t)b * T : nullptr;   // prediction given as a sum of two signals
   float2 *a = bufa + f * PN, *bb = bufb + f * PN;
+  // the windowed samples a thread loads (stride G) are exactly its inputs of the first radix-8 stage: they stay
+  // in registers
+  float2 vin[8];
 #pragma unroll
   for (int q = 0; q < 8; ++q) {
     int i = lt + q * G, t = t_base + i;
@@ -74,10 +77,9 @@ __device__ __forceinline__ void mss_fwd_body(float2 *sm, float *red, int bx, int
       const float xp = SUM2 ? __fadd_rn(x1[t], x1b[t]) : x1[t];
       v = make_float2(xp * w, x2[t] * w);
     }
-    a[pad(i)] = v;
+    vin[q] = v;
   }
-  __syncthreads();
-  float2 *z = fft_block<N, false>(a, bb, lt, tw);
+  float2 *z = fft_block_regs<N, false>(vin, a, bb, lt, tw);
   float lin = 0.0f, lg = 0.0f;
 #pragma unroll
   for (int q = 0; q < 4; ++q) {
@@ -235,6 +237,7 @@ mss_bwd_kernel(const float *__restrict__ pred, const float *__restrict__ target,
       const int h = hr0 + 2 * f + w;
       const bool valid = h < H && (h - hA) < nwin;
       const int t_base = h * hop - (N - 1);
+      float2 vin[8];
 #pragma unroll
       for (int q = 0; q < 8; ++q) {
         int i = lt + q * G, t = t_base + i;
@@ -243,10 +246,9 @@ mss_bwd_kernel(const float *__restrict__ pred, const float *__restrict__ target,
           float wv = __ldg(&window[i]);
           v = make_float2(x1[t] * wv, x2[t] * wv);
         }
-        a[pad(i)] = v;
+        vin[q] = v;
       }
-      __syncthreads();
-      float2 *z = fft_block<N, false>(a, bb, lt, tw);
+      float2 *z = fft_block_regs<N, false>(vin, a, bb, lt, tw);
       if (valid) {
 #pragma unroll
         for (int q = 0; q < 4; ++q) {

@@ -36,6 +36,7 @@ stft_kernel(const float *__restrict__ x, int T, int hop, int H, const float *__r
   const int h0 = 2 * pair, h1 = h0 + 1;
   const float *xv = x + (size_t)v * T;
   float2 *a = bufa + f * PN, *bb = bufb + f * PN;
+  float2 vin[8];   // a thread's loads (stride G) are its inputs of the first radix-8 stage: kept in registers
 #pragma unroll
   for (int q = 0; q < 8; ++q) {
     int i = lt + q * G;
@@ -54,10 +55,9 @@ stft_kernel(const float *__restrict__ x, int T, int hop, int H, const float *__r
       if (h0 < H && t0 < T) val.x = xv[t0] * w;
       if (h1 < H && t1 < T) val.y = xv[t1] * w;
     }
-    a[pad(i)] = val;
+    vin[q] = val;
   }
-  __syncthreads();
-  float2 *z = fft_block<N, false>(a, bb, lt, tw);
+  float2 *z = fft_block_regs<N, false>(vin, a, bb, lt, tw);
   // bins 0..N/2 of both sequences
   for (int k = lt; k < NB; k += G) {
     float2 zk = z[pad(k)], zn = z[pad((N - k) & (N - 1))];
@@ -142,6 +142,7 @@ istft_kernel(const float2 *__restrict__ Y, int H, const float *__restrict__ wind
   const int h0 = 2 * pair, h1 = h0 + 1;
   float2 *a = bufa + f * PN, *bb = bufb + f * PN;
   // z = Y0 + i*Y1 with Hermitian extension: Y[N-k] = conj(Y[k])
+  float2 vin[8];
 #pragma unroll
   for (int q = 0; q < 8; ++q) {
     int k = lt + q * G;
@@ -150,10 +151,9 @@ istft_kernel(const float2 *__restrict__ Y, int H, const float *__restrict__ wind
     if (h0 < H) y0 = Y[((size_t)v * H + h0) * NB + ks];
     if (h1 < H) y1 = Y[((size_t)v * H + h1) * NB + ks];
     if (k > N / 2) { y0.y = -y0.y; y1.y = -y1.y; }
-    a[pad(k)] = make_float2(y0.x - y1.y, y0.y + y1.x);
+    vin[q] = make_float2(y0.x - y1.y, y0.y + y1.x);
   }
-  __syncthreads();
-  float2 *z = fft_block<N, true>(a, bb, lt, tw);
+  float2 *z = fft_block_regs<N, true>(vin, a, bb, lt, tw);
   const float invn = 1.0f / (float)N;
 #pragma unroll
   for (int q = 0; q < 8; ++q) {
