@@ -357,3 +357,59 @@ DGC_EXPORT int32_t dgc_sanitize(dgc_ctx *ctx, const float *in_dev, uint64_t n, f
   DGC_LAUNCHED(ctx, "sanitize");
   return DGC_OK;
 }
+
+// ---- sum over frames of per-frame tensors ----------------------------------------------------------------------
+// The reference accumulates per-frame parameter gradients into the parameter's gradient cell frame by frame
+// (tensorAccumulate / memoryAccumulate, Sources/DGen/Emit+State.swift:50-115) and reads the cells on the host
+// (Sources/DGenLazy/Backward.swift:132-165).  Here the frames are summed in two fixed-order steps (segments of
+// frames per element in double, then the segment sums), so the result does not depend on scheduling.
+namespace {
+constexpr int RF_SEG = 256;   // frames per segment
+
+__global__ void reduce_frames_seg_kernel(const float *__restrict__ x, int64_t T, int64_t E, int NS,
+                                         double *__restrict__ part /* [NS][E] */) {
+  const int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int sgm = blockIdx.y;
+  if (e >= E) return;
+  const int64_t n0 = (int64_t)sgm * RF_SEG, n1 = n0 + RF_SEG < T ? n0 + RF_SEG : T;
+  double acc = 0.0;
+  int64_t n = n0;
+  for (; n + 8 <= n1; n += 8) {   // eight independent loads in flight
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = __ldcs(x + (n + j) * E + e);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc += (double)v[j];
+  }
+  for (; n < n1; ++n) acc += (double)x[n * E + e];
+  part[(int64_t)sgm * E + e] = acc;
+}
+
+__global__ void reduce_frames_sum_kernel(const double *__restrict__ part, int64_t E, int NS, float scale, int accumulate,
+                                         float *__restrict__ out) {
+  const int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= E) return;
+  double acc = 0.0;
+  for (int s = 0; s < NS; ++s) acc += part[(int64_t)s * E + e];
+  const float r = (float)(acc * (double)scale);
+  out[e] = accumulate ? out[e] + r : r;
+}
+}  // namespace
+
+DGC_EXPORT int32_t dgc_reduce_frames(dgc_ctx *ctx, const float *x_dev, int64_t T, int64_t E, float scale,
+                                     int32_t accumulate, float *out_dev) {
+  if (!ctx) return DGC_ERR_INVALID;
+  DGC_REQUIRE(ctx, x_dev && out_dev, "null pointer");
+  DGC_REQUIRE(ctx, T > 0 && E > 0, "size out of range");
+  const int64_t NS64 = (T + RF_SEG - 1) / RF_SEG;
+  DGC_REQUIRE(ctx, NS64 <= 65535 && (E + 127) / 128 < 0x7fffffffLL, "size out of range");
+  const int NS = (int)NS64;
+  float *scr = dgc_ctx_scratch(ctx, 2ull * (uint64_t)NS * (uint64_t)E + 4);
+  if (!scr) return DGC_ERR_OOM;
+  double *part = reinterpret_cast<double *>(scr);
+  reduce_frames_seg_kernel<<<dim3((unsigned)((E + 127) / 128), NS), 128, 0, ctx->stream>>>(x_dev, T, E, NS, part);
+  DGC_LAUNCHED(ctx, "reduce_frames_segments");
+  reduce_frames_sum_kernel<<<(unsigned)((E + 127) / 128), 128, 0, ctx->stream>>>(part, E, NS, scale, accumulate, out_dev);
+  DGC_LAUNCHED(ctx, "reduce_frames_sum");
+  return DGC_OK;
+}

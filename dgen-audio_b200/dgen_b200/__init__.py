@@ -140,6 +140,7 @@ SIGNATURES = {
     "dgc_linear_bwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp]),
     "dgc_adam_step": (_i32, [_vp, _vp, _vp, _vp, _vp, _u64, _i32, _f, _f, _f, _f]),
     "dgc_sanitize": (_i32, [_vp, _vp, _u64, _vp]),
+    "dgc_reduce_frames": (_i32, [_vp, _vp, _i64, _i64, _f, _i32, _vp]),
     "dgc_onepole_bwd": (_i32, [_vp, _vp, _vp, _i32, _i32, _f, _vp, _vp]),
     "dgc_biquad_bwd": (_i32, [_vp, C.POINTER(BiquadParams)] + [_vp] * 9),
     "dgc_adam_step_counted": (_i32, [_vp, _vp, _vp, _vp, _vp, _u64, _vp, _vp, _f, _f, _f, _f]),
@@ -570,6 +571,14 @@ class Context:
         """Context manager: library calls (and torch work on the same stream) inside are recorded, not run;
         `.graph` afterwards holds the StepGraph to replay.  The context must be on a non-default stream."""
         return _Recording(self)
+
+    def reduce_frames(self, x, scale=1.0, out=None, accumulate=False):
+        """x [T][...] -> sum over the first axis (Sources/DGen/Emit+State.swift:50-115), fixed summation order."""
+        T = x.shape[0]
+        E = x.numel() // T
+        out = self._empty(*x.shape[1:]) if out is None else out
+        self.check(self.lib.dgc_reduce_frames(self.h, _ptr(x), T, E, scale, 1 if accumulate else 0, _ptr(out)))
+        return out
 
     def sanitize(self, x, out=None):
         """Non-finite -> 0 (toolchain/include/dgen_runtime.h:72-84); in place when out is None."""

@@ -344,6 +344,13 @@ int32_t dgc_adam_step_counted(dgc_ctx *ctx, float *theta_dev, const float *grad_
                               uint64_t n, int32_t *t_dev, float *corr_dev, float lr, float beta1, float beta2,
                               float eps);
 
+/* Sum over frames of a per-frame tensor: out[e] (+)= scale * sum_n x[n][e], x_dev [T][E].  The accumulation of
+ * per-frame parameter gradients into the parameter's gradient cell (tensorAccumulate / memoryAccumulate,
+ * Sources/DGen/Emit+State.swift:50-115; read back by Sources/DGenLazy/Backward.swift:132-165), in a fixed order
+ * (double-precision segment sums): the result does not depend on scheduling.  accumulate != 0 adds to out. */
+int32_t dgc_reduce_frames(dgc_ctx *ctx, const float *x_dev, int64_t T, int64_t E, float scale, int32_t accumulate,
+                          float *out_dev);
+
 /* Output sanitiser: out[i] = in[i] when its IEEE-754 exponent field is not all ones, else +0.0f (NaN and
  * +-Inf become 0; denormals, -0.0 and every finite value pass through bit for bit).  in_dev == out_dev is
  * allowed.  Replaces dgen_sanitize_f32 / dgen_sanitize_f32x4 applied at every `output` store

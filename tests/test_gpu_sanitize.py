@@ -1,6 +1,7 @@
 """GPU parity of the output sanitiser (non-finite -> 0 at the `output` store) against the oracle: bit-exact."""
 import numpy as np
 import pytest
+import torch
 
 import dgen_b200
 from oracle import oracle as orc
@@ -67,3 +68,22 @@ def test_sanitize_is_idempotent_and_clears_render_poison(ctx):
     assert bool(torch.isfinite(once).all())
     keep = torch.isfinite(d)
     assert torch.equal(once[keep].view(torch.int32), d[keep].view(torch.int32))
+
+
+@pytest.mark.parametrize("T,shape", [(1, (1,)), (1000, (1,)), (64000, (3, 5)), (513, (700,)), (70000, (2,))])
+def test_reduce_frames_sums_per_frame_tensors_in_a_fixed_order(T, shape):
+    """dgc_reduce_frames: the frame-by-frame accumulation of per-frame parameter gradients
+    (Sources/DGen/Emit+State.swift:50-115) against a float64 sum; repeated calls give identical bits."""
+    ctx = dgen_b200.Context(0)
+    rng = np.random.default_rng(T)
+    x = (rng.standard_normal((T,) + shape) * 10).astype(np.float32)
+    X = torch.from_numpy(x).cuda()
+    a = ctx.reduce_frames(X, scale=0.5)
+    b = ctx.reduce_frames(X, scale=0.5)
+    want = 0.5 * x.astype(np.float64).sum(axis=0)
+    assert tuple(a.shape) == shape and torch.equal(a, b)
+    assert np.abs(a.cpu().numpy() - want).max() <= 1e-6 * max(1.0, np.abs(want).max())
+    acc = torch.ones(shape, device="cuda")
+    ctx.reduce_frames(X, out=acc, accumulate=True)
+    assert np.abs(acc.cpu().numpy() - (1.0 + 2.0 * want)).max() <= 1e-5 * max(1.0, np.abs(want).max())
+    ctx.close()
