@@ -62,7 +62,8 @@ static int32_t emit_block(const dgc_uop *ops, int32_t n_ops, const char *kernel_
   } else {
     for (int k = 0; k < n_ops; ++k) {
       const int op = ops[k].op;
-      if (op == DGC_OP_HISTORY_READ || op == DGC_OP_HISTORY_WRITE || op == DGC_OP_PHASOR || op == DGC_OP_LATCH) {
+      if (op == DGC_OP_HISTORY_READ || op == DGC_OP_HISTORY_WRITE || op == DGC_OP_PHASOR || op == DGC_OP_LATCH ||
+          op == DGC_OP_ACCUM || op == DGC_OP_NOISE) {
         if (ops[k].a < 0) return DGC_ERR_INVALID;
         cell_var(ops[k].a);
       }
@@ -181,6 +182,27 @@ static int32_t emit_block(const dgc_uop *ops, int32_t n_ops, const char *kernel_
         e.line(N + " = " + N + " - floorf(" + N + ");");
         e.line("if (" + N + " >= 1.0f) " + N + " -= 1.0f;");
         e.line(S + " = " + Cc + " > 0.0f ? 0.0f : " + N + ";");
+        break;
+      }
+      case DGC_OP_ACCUM: {        // Sources/DGen/Definitions.swift:215-246: cell a, increment t_b, reset t_c, range [0, imm)
+        if (!seq) return DGC_ERR_UNSUPPORTED;
+        if (!ok(u.b) || !ok(u.c)) return DGC_ERR_INVALID;
+        const std::string S = cell_var(u.a), N = "n" + std::to_string(k), M = fl(u.imm);
+        e.line(R + S + ";");                                       // the output is the state BEFORE the update
+        e.line("float " + N + " = " + Cc + " > 0.0f ? 0.0f : " + S + " + " + B + ";");
+        e.line(N + " = " + N + " - floorf(" + N + " / " + M + ") * " + M + ";");
+        e.line("if (" + N + " >= " + M + ") " + N + " -= " + M + ";");
+        e.line(S + " = " + Cc + " > 0.0f ? 0.0f : " + N + ";");
+        break;
+      }
+      case DGC_OP_NOISE: {        // Sources/DGen/Renderer/CRenderer.swift:660-695: xorshift32, state bits in the cell
+        if (!seq) return DGC_ERR_UNSUPPORTED;
+        const std::string S = cell_var(u.a), X = "x" + std::to_string(k);
+        e.line("unsigned " + X + " = __float_as_uint(" + S + ");");
+        e.line("if (" + X + " == 0u) " + X + " = 1u;");
+        e.line(X + " ^= " + X + " << 13; " + X + " ^= " + X + " >> 17; " + X + " ^= " + X + " << 5;");
+        e.line(S + " = __uint_as_float(" + X + ");");
+        e.line(R + "(float)" + X + " / 4294967296.0f;");
         break;
       }
       case DGC_OP_LATCH:          // Sources/DGen/Definitions.swift:104-113: cell a, value t_b, cond t_c

@@ -58,7 +58,7 @@ OP = dict(CONST=0, LOAD=1, LOAD_SCALAR=2, FRAME_INDEX=3,
           ABS=40, SIGN=41, FLOOR=42, CEIL=43, ROUND=44, SIN=45, COS=46, TAN=47, ATAN=48, TANH=49, EXP=50, LOG=51,
           LOG10=52, SQRT=53, GSWITCH=60, STORE=70, OUTPUT=71,
           LOAD_LANE=80, LOAD_FRAME_LANE=81, STORE_FRAME_LANE=82, HISTORY_READ=83, HISTORY_WRITE=84, PHASOR=85,
-          LATCH=86)
+          LATCH=86, ACCUM=87, NOISE=88)
 
 
 def _uops(ops):

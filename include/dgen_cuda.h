@@ -471,7 +471,9 @@ enum {
   DGC_OP_HISTORY_READ = 83,     /* content of state cell a (per lane: memory[a + e]) */
   DGC_OP_HISTORY_WRITE = 84,    /* state cell a = t_b (pass-through) */
   DGC_OP_PHASOR = 85,           /* state cell a; frequency t_b, reset t_c, imm = sample rate; value = phase before the update */
-  DGC_OP_LATCH = 86             /* state cell a = t_b where t_c > 0; value = the cell */
+  DGC_OP_LATCH = 86,            /* state cell a = t_b where t_c > 0; value = the cell */
+  DGC_OP_ACCUM = 87,            /* state cell a; increment t_b, reset t_c, wraps in [0, imm); value = state before the update */
+  DGC_OP_NOISE = 88             /* state cell a = xorshift32 state (raw bits); value = new state / 2^32 */
 };
 typedef struct dgc_uop {
   int32_t op;

@@ -69,3 +69,12 @@ def test_state_ops_need_the_sequential_form():
         dgen_b200.block_source([("HISTORY_READ", 5)])
     with pytest.raises(dgen_b200.DgenCudaError):
         dgen_b200.block_source([("LOAD_LANE", 5)])
+
+
+def test_accum_and_noise_render_the_reference_state_updates():
+    ops = [("CONST", 0, 0, 0, 0.25), ("CONST", 0, 0, 0, 0.0), ("ACCUM", 100, 0, 1, 3.0), ("NOISE", 200)]
+    lines = [l.strip() for l in dgen_b200.block_source(ops, "k", sequential=True).splitlines()]
+    assert "float t2 = s100;" in lines and "n2 = n2 - floorf(n2 / 3.0f) * 3.0f;" in lines
+    assert "if (n2 >= 3.0f) n2 -= 3.0f;" in lines
+    assert "x3 ^= x3 << 13; x3 ^= x3 >> 17; x3 ^= x3 << 5;" in lines and "if (x3 == 0u) x3 = 1u;" in lines
+    assert "float t3 = (float)x3 / 4294967296.0f;" in lines and "memory[200 + e] = s200;" in lines

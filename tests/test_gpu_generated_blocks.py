@@ -278,3 +278,37 @@ def test_sequential_block_biquad_from_ops_against_the_biquad_restatement(ctx):
     want = orc.biquad_bank(x[None, :], cutoff, q)[0].T    # [frames][lanes]
     assert np.abs(got - want).max() <= 1e-4 * max(1.0, np.abs(want).max())
     m.close()
+
+
+def test_sequential_block_accum_and_noise_state_ops(ctx):
+    """accum (Sources/DGen/Definitions.swift:215-246) against the restatement, and the xorshift noise generator
+    (Sources/DGen/Renderer/CRenderer.swift:660-695) bit for bit, a different seed per lane; state cells carry over
+    a second launch."""
+    from oracle import oracle as orc
+    frames, lanes = 1500, 9
+    seeds = np.asarray([0, 1, 2, 12345, 0xdeadbeef, 7, 99, 0x7f800001, 0xffc00000], np.uint32)  # incl. NaN / Inf bit patterns
+    INCR, ACC, RNG, OUT_A, OUT_N = 0, lanes, 2 * lanes, 3 * lanes, 3 * lanes + 2 * frames * lanes
+    incr = np.linspace(0.01, 0.9, lanes).astype(f32)
+    ops = [("LOAD_LANE", INCR), ("CONST", 0, 0, 0, 0.0), ("ACCUM", ACC, 0, 1, 3.0), ("NOISE", RNG),
+           ("STORE_FRAME_LANE", OUT_A, 2), ("STORE_FRAME_LANE", OUT_N, 3)]
+    mem = np.zeros(OUT_N + 2 * frames * lanes, f32)
+    mem[INCR:INCR + lanes] = incr
+    mem[RNG:RNG + lanes] = seeds.view(f32)
+    d = torch.from_numpy(mem).cuda()
+    m = ctx.compile_block(ops, "state_ops", sequential=True)
+    m.launch("state_ops", 1, 32, [d, C.c_int(frames), C.c_int(lanes)])
+    ops2 = ops[:4] + [("STORE_FRAME_LANE", OUT_A + frames * lanes, 2), ("STORE_FRAME_LANE", OUT_N + frames * lanes, 3)]
+    m2 = ctx.compile_block(ops2, "state_ops_b", sequential=True)
+    m2.launch("state_ops_b", 1, 32, [d, C.c_int(frames), C.c_int(lanes)])
+    ctx.sync()
+    got = d.cpu().numpy()
+    acc = got[OUT_A:OUT_A + 2 * frames * lanes].reshape(2 * frames, lanes)
+    noi = got[OUT_N:OUT_N + 2 * frames * lanes].reshape(2 * frames, lanes)
+    for l in range(lanes):
+        want = orc.accum(float(incr[l]), 0.0, 3.0, 2 * frames)
+        assert np.abs(acc[:, l] - want).max() <= 2e-5, l          # the wrap may be contracted to a fused multiply-add
+        wn, st = orc.noise_xorshift(int(seeds[l]), 2 * frames)
+        assert np.array_equal(noi[:, l], wn), l
+        assert got[RNG + l:RNG + l + 1].view(np.uint32)[0] == st
+    m.close()
+    m2.close()
