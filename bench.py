@@ -496,8 +496,37 @@ def run_train(args, rank, world, local_rank):
         torch.cuda.synchronize()
         e2e_ms += a.elapsed_time(b)
     barrier()
+    # the same with the NEXT step's inputs crossing PCIe (copy stream, device staging) while this step runs; at the
+    # start of a step the staged inputs move into the step's static buffers device to device.  Every step still
+    # takes its inputs from pinned host memory and returns its loss to the host inside the timed region.
+    cur, cs = torch.cuda.current_stream(), torch.cuda.Stream()
+    S = {k: torch.empty_like(D[k]) for k in order}
+
+    def prefetch():
+        with torch.cuda.stream(cs):
+            for k in order:
+                S[k].copy_(P[k], non_blocking=True)
+
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    cs.wait_stream(cur)
+    prefetch()
+    for s in range(args.steps):
+        cur.wait_stream(cs)
+        for k in order:
+            D[k].copy_(S[k], non_blocking=True)
+        cs.wait_stream(cur)
+        if s + 1 < args.steps:
+            prefetch()
+        loss = step_fn()
+        loss_host = float(loss.cpu()[0])
+    b.record()
+    torch.cuda.synchronize()
+    piped_ms = a.elapsed_time(b)
+    barrier()
     clocks = sampler.stop() if rank == 0 else None
-    total_ms, e2e_ms = sharding.max_over_ranks([total_ms, e2e_ms], device="cuda")
+    total_ms, e2e_ms, piped_ms = sharding.max_over_ranks([total_ms, e2e_ms, piped_ms], device="cuda")
     glob_loss = sharding.global_mean_loss(loss_host, B, device="cuda")
     if rank == 0:
         ms = total_ms / args.steps
@@ -512,7 +541,9 @@ def run_train(args, rank, world, local_rank):
                            % (world, model.n_params,
                               "dgc_allreduce_sum" if model.use_ctx_comm else "torch.distributed"), "l2": "working set (>1 GB per step) exceeds L2"},
                 "samples_per_s": B * world * T / (ms * 1e-3), "clocks": clocks,
-                "e2e": {"value": e2e_ms / args.steps, "unit": "ms", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 8},
+                "e2e": {"value": piped_ms / args.steps, "unit": "ms", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 8,
+                        "mode": "the next step's inputs upload on a copy stream while this step runs",
+                        "blocking": {"value": e2e_ms / args.steps, "unit": "ms"}},
                 "gpu_launches": int(launches), "loss": glob_loss}
         print(json.dumps(line))
     ctx.close()
