@@ -35,7 +35,8 @@ int32_t ensure_stage(dgc_ctx *ctx, uint64_t nfloats) {
   return DGC_OK;
 }
 
-__global__ void add2_kernel(const float *__restrict__ a, const float *__restrict__ b, size_t n, float *__restrict__ out) {
+// out may be the same buffer as a (element i is read before it is written): no restrict on those two
+__global__ void add2_kernel(const float *a, const float *__restrict__ b, size_t n, float *out) {
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) out[i] = __fadd_rn(a[i], b[i]);
 }
