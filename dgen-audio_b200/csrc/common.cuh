@@ -55,6 +55,8 @@ struct dgc_ctx {
   // NCCL communicator of the gradient exchange (comm.cu); nullptr = a world of one
   void *comm = nullptr;
   int comm_world = 1;
+  // spectral-loss backward: windows owned per block, chosen per (N, hop, H, B) so that the grid fills whole waves
+  std::map<std::pair<std::pair<int, int>, std::pair<int, int>>, int> mss_bwd_owned;
   // step recording (graph.cu)
   bool capturing = false;
   cudaStream_t capture_stream = nullptr;   // the stream the recording started on (calls inside may rebind the context)

@@ -311,7 +311,8 @@ __device__ __forceinline__ float sanitize_bits(float v) {
 }
 // Pure streaming kernel (4 B in + 4 B out per element): 128-bit accesses over the aligned body, grid-stride,
 // scalar head / tail when the two pointers share a misalignment, all-scalar when they do not.
-__global__ void __launch_bounds__(256) sanitize_kernel(const float *__restrict__ in, float *__restrict__ out,
+// (in and out may be the same buffer: no restrict, every element is read before it is written by the same thread)
+__global__ void __launch_bounds__(256) sanitize_kernel(const float *in, float *out,
                                                        uint64_t n, uint64_t head, int vec_ok) {
   const uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x, nth = (uint64_t)gridDim.x * blockDim.x;
   if (!vec_ok) {

@@ -325,12 +325,50 @@ int32_t launch_bwd(dgc_ctx *ctx, const dgc_mss_params *p, const float *pred, con
   const float2 *tw = dgc_ctx_twiddles(ctx, N);
   if (!win || !tw) return DGC_ERR_OOM;
   const int E = (N - 1) / hop;
-  int S = Gm::WB - E;
-  if (S < 1) return dgc_fail(ctx, DGC_ERR_UNSUPPORTED, "hop %d too small for window %d", hop, N);
-  size_t smem = (size_t)3 * Gm::NF * padded(N) * sizeof(float2) + (size_t)S * hop * sizeof(float);
-  if (smem > 200 * 1024) return dgc_fail(ctx, DGC_ERR_UNSUPPORTED, "backward tile does not fit shared memory");
-  cudaError_t e = cudaFuncSetAttribute(mss_bwd_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  const int S0 = Gm::WB - E;
+  if (S0 < 1) return dgc_fail(ctx, DGC_ERR_UNSUPPORTED, "hop %d too small for window %d", hop, N);
+  auto smem_of = [&](int S_) {
+    return (size_t)3 * Gm::NF * padded(N) * sizeof(float2) + (size_t)S_ * hop * sizeof(float);
+  };
+  if (smem_of(S0) > 200 * 1024) return dgc_fail(ctx, DGC_ERR_UNSUPPORTED, "backward tile does not fit shared memory");
+  cudaError_t e = cudaFuncSetAttribute(mss_bwd_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
   if (e != cudaSuccess) return dgc_fail(ctx, DGC_ERR_CUDA, "mss_bwd smem opt-in: %s", cudaGetErrorString(e));
+  // Windows owned per block.  A block visits S + E windows (E = the windows before its first owned one that still
+  // cover its frames), so a larger S wastes less on that overlap, but what decides the time of a launch this small
+  // is whether the grid fills WHOLE waves of resident blocks: 320 blocks on 296 slots run as long as 592.  Among
+  // the S that keep the shared-memory tile within bounds, take the one with the least (waves x rounds per block);
+  // the summation order per output frame (covering windows ascending) does not depend on S, nor do the bits of
+  // the result.
+  int S = S0;
+  {
+    const auto key = std::make_pair(std::make_pair(N, hop), std::make_pair(H, p->B));
+    auto it = ctx->mss_bwd_owned.find(key);
+    if (it != ctx->mss_bwd_owned.end()) {
+      S = it->second;
+    } else {
+      long long best = -1;
+      int per_sm0 = 0;
+      for (int cand = S0; cand <= S0 + 24 && cand <= H + E; ++cand) {
+        const size_t sm = smem_of(cand);
+        if (sm > 200 * 1024) break;
+        int per_sm = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, mss_bwd_kernel<N>, LOSS_THREADS, sm) != cudaSuccess ||
+            per_sm < 1)
+          break;
+        if (cand == S0) per_sm0 = per_sm;
+        if (per_sm < per_sm0) break;   // a larger tile must not cost resident blocks
+        const long long blocks = (long long)dgc_div_up(H, cand) * p->B, slots = (long long)per_sm * ctx->sm_count;
+        const long long waves = (blocks + slots - 1) / slots;
+        const long long cost = waves * dgc_div_up(cand + E, Gm::WR);
+        if (best < 0 || cost < best) {
+          best = cost;
+          S = cand;
+        }
+      }
+      ctx->mss_bwd_owned[key] = S;
+    }
+  }
+  const size_t smem = smem_of(S);
   // block j owns the frames whose first covering window is in [j*S, (j+1)*S); frames up to T-1 have
   // first covering window <= H-1
   mss_bwd_kernel<N><<<dim3(dgc_div_up(H, S), p->B), LOSS_THREADS, smem, ctx->stream>>>(
