@@ -119,7 +119,7 @@ struct FwdDesc {
 constexpr int FWD_SMEM_BYTES = 2 * (LOSS_THREADS / (2048 / 8)) * padded(2048) * (int)sizeof(float2);
 
 template <bool SUM2>
-__global__ void __launch_bounds__(LOSS_THREADS)
+__global__ void __launch_bounds__(LOSS_THREADS, 6)
 mss_fwd_kernel(const float *__restrict__ pred, const float *__restrict__ pred_b, const float *__restrict__ target,
                int B, int T, const FwdDesc d) {
   extern __shared__ float2 fwd_sm[];
@@ -208,8 +208,10 @@ struct BwdGeom {
 
 __device__ __forceinline__ float sgn(float v) { return v > 0.f ? 1.f : (v < 0.f ? -1.f : 0.f); }
 
+// at least three resident blocks per SM for the large windows (caps the registers at 80; the kernel is latency
+// bound at the two blocks it would otherwise get), four for the small ones (which need fewer registers anyway)
 template <int N>
-__global__ void __launch_bounds__(LOSS_THREADS)
+__global__ void __launch_bounds__(LOSS_THREADS, (N >= 256 ? 3 : 4))
 mss_bwd_kernel(const float *__restrict__ pred, const float *__restrict__ target, int B, int T, int hop, int H,
                int S /* windows whose first-covered frames this block owns */, const float *__restrict__ window,
                const float2 *__restrict__ tw, float c_lin, float c_log, int accumulate, float *__restrict__ grad) {
@@ -333,6 +335,9 @@ int32_t launch_bwd(dgc_ctx *ctx, const dgc_mss_params *p, const float *pred, con
   if (smem_of(S0) > 200 * 1024) return dgc_fail(ctx, DGC_ERR_UNSUPPORTED, "backward tile does not fit shared memory");
   cudaError_t e = cudaFuncSetAttribute(mss_bwd_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
   if (e != cudaSuccess) return dgc_fail(ctx, DGC_ERR_CUDA, "mss_bwd smem opt-in: %s", cudaGetErrorString(e));
+  // the kernel lives on shared memory, not on L1: ask for the largest shared-memory carve-out so that as many
+  // blocks as the tile size allows are resident
+  cudaFuncSetAttribute(mss_bwd_kernel<N>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
   // Windows owned per block.  A block visits S + E windows (E = the windows before its first owned one that still
   // cover its frames), so a larger S wastes less on that overlap, but what decides the time of a launch this small
   // is whether the grid fills WHOLE waves of resident blocks: 320 blocks on 296 slots run as long as 592.  Among
@@ -465,6 +470,14 @@ int32_t dgc_mss_loss_fwd_sum(dgc_ctx *ctx, const dgc_mss_params *p, const float 
   }
   fd.first_block[no] = blocks;
   if (no > 0) {
+    // six resident blocks per SM (launch bounds cap the registers at 40) need 6 x 34 KB of shared memory: ask for
+    // the largest carve-out
+    static const bool carved = [] {
+      cudaFuncSetAttribute(mss_fwd_kernel<true>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+      cudaFuncSetAttribute(mss_fwd_kernel<false>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+      return true;
+    }();
+    (void)carved;
     if (pred_b_dev)
       mss_fwd_kernel<true><<<dim3(blocks, p->B), LOSS_THREADS, FWD_SMEM_BYTES, ctx->stream>>>(pred_dev, pred_b_dev,
                                                                                               target_dev, p->B, p->T, fd);
