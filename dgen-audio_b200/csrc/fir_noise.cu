@@ -16,7 +16,7 @@ namespace {
 // accumulates dot products against rows r0, r0+1 for every frame, and against r0+2 only when its
 // frames straddle a control-row boundary.
 template <int SPT, int NTH>
-__global__ void __launch_bounds__(NTH)
+__global__ void __launch_bounds__(NTH, 4)
 fir_noise_kernel(dgc_fir_params prm, const float2 *__restrict__ rowtab, const float *__restrict__ noise,
                  const float *__restrict__ taps_tab, const float *__restrict__ ngain, float *__restrict__ audio,
                  int max_rows, int32_t *status) {
