@@ -87,3 +87,41 @@ def test_reduce_frames_sums_per_frame_tensors_in_a_fixed_order(T, shape):
     ctx.reduce_frames(X, out=acc, accumulate=True)
     assert np.abs(acc.cpu().numpy() - (1.0 + 2.0 * want)).max() <= 1e-5 * max(1.0, np.abs(want).max())
     ctx.close()
+
+
+def test_step_recording_of_plain_library_calls_and_its_error_reports():
+    """dgc_graph_*: any sequence of entry points recorded on a non-default stream replays with refilled inputs; the
+    misuse cases come back as errors, not as a broken context."""
+    ctx = dgen_b200.Context(0)
+    x = torch.randn(4000, 6, device="cuda")
+    x[5, 2] = float("nan")
+    clean, total = torch.empty_like(x), torch.empty(6, device="cuda")
+    with pytest.raises(dgen_b200.DgenCudaError):           # the context is bound to the default stream here
+        with ctx.record():
+            pass
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with ctx.on_stream(s), torch.cuda.stream(s):
+        ctx.sanitize(x, clean)                             # first use outside the recording (scratch allocation)
+        ctx.reduce_frames(clean, out=total)
+        with ctx.record() as rec:
+            ctx.sanitize(x, clean)
+            ctx.reduce_frames(clean, out=total)
+            with pytest.raises(dgen_b200.DgenCudaError):   # no nested recording
+                ctx.check(ctx.lib.dgc_graph_begin(ctx.h))
+        g = rec.graph
+        assert g.nodes >= 3
+        for k in range(3):
+            x.normal_()
+            x[k, 0] = float("inf")
+            g.launch()
+            s.synchronize()
+            ref = torch.where(torch.isfinite(x), x, torch.zeros_like(x))
+            assert torch.equal(clean, ref)
+            assert torch.allclose(total, ref.double().sum(0).float(), rtol=1e-5, atol=1e-4)
+        with pytest.raises(dgen_b200.DgenCudaError):       # end without begin
+            out = dgen_b200._vp()
+            ctx.check(ctx.lib.dgc_graph_end(ctx.h, dgen_b200.C.byref(out)))
+        g.close()
+    assert ctx.sanitize(x.clone()) is not None             # the context still works
+    ctx.close()
