@@ -101,3 +101,15 @@ def test_partitioned_convolution_full_size_properties(ctx):
     want = orc.partitioned_convolve(d["x"][3, :57600], d["ir"], N, hop)
     got = ctx.partconv(x[3:4, :57600].contiguous(), ir, N, hop).cpu().numpy()[0]
     assert np.abs(got - want).max() < 1e-4 * max(1.0, np.abs(want).max())
+
+
+def test_onepole_long_signals(ctx):
+    """64 voices x 1 Mi frames (256 MB, twice L2; 512 chunks per voice carried in sequence) against the serial
+    recurrence of the oracle on a few voices, and a ragged length that leaves a partial last chunk."""
+    rng = np.random.default_rng(12)
+    for B, T, a in [(64, 1 << 20, 0.9), (48, (1 << 20) - 777, 0.999)]:
+        x = rng.standard_normal((B, T)).astype(f32)
+        y = ctx.onepole_fwd(dev(x), a).cpu().numpy()
+        for b in (0, B // 2, B - 1):
+            want = orc.onepole(x[b], a)
+            assert np.abs(y[b] - want).max() <= 1e-4 * max(1.0, np.abs(want).max()), (B, T, b)
