@@ -10,6 +10,15 @@ A step is one pass of the path over one batch.  `value` is synthesized samples p
 host-buffer C-ABI call (host->device copies of every input and the device->host loss read inside
 the timed region).  Multi-GPU: one process per GPU (torchrun), voices sharded, no data-path
 collective (forward-only render): weak scaling.
+
+The same JSON line carries, beside the headline:
+  stages       per-stage time with the roofline that bounds that stage (SFU for the oscillator bank, FP32 for the
+               FIR and the loss transforms, HBM for the band -> tap map), and the HBM figure beside it;
+  sustained    the step replayed for >= 2 s over rotating input sets (working set > L2) with the SM clock sampled;
+  target_b256  (one GPU only) the same step at 256 voices on this one GPU: the configuration the path's
+               throughput target is stated on;
+  train        the full training step (32 voices per GPU, gradient all-reduce between two recordings), at every N;
+  other_configs (one GPU only) oscillator -> filter -> FFT, biquad bank forward / BPTT, partitioned convolution.
 """
 import argparse
 import json
@@ -31,7 +40,8 @@ UNIT = "samples/s"
 CFG = dict(B=16, T=64000, K=100, F=1000, sr=16000.0, nbands=65, taps=257)
 SIZES = (2048, 1024, 512, 256, 128, 64)
 SEED = 20260001
-PHASE = {"mode": "scan"}
+PHASE = {"mode": "fundamental"}
+FP32_LANES_PER_SM, SFU_LANES_PER_SM = 128, 16
 STEP_MODE = {"mode": "replay"}
 
 
@@ -182,7 +192,8 @@ def run_ours(args, rank, world, local_rank):
     mss = dgen_b200.mss_params(B, T, SIZES)
     import ctypes as C
     hp = dgen_b200.HarmonicParams(B, T, K, F, sr, 1.0,
-                                  dgen_b200.PHASE_SCAN if PHASE["mode"] == "scan" else dgen_b200.PHASE_SEQUENTIAL, 0)
+                                  {"scan": dgen_b200.PHASE_SCAN, "sequential": dgen_b200.PHASE_SEQUENTIAL,
+                                   "fundamental": dgen_b200.PHASE_FUNDAMENTAL}[PHASE["mode"]], 0)
     fp = dgen_b200.FirParams(B, T, F, CFG["taps"], 0.12, 1)
     lib, h = ctx.lib, ctx.h
     taps_buf = torch.empty(F, B, CFG["taps"], device="cuda")
@@ -699,7 +710,7 @@ def main():
     ap.add_argument("--voices", type=int, default=0,
                     help="voices per GPU (default: the configuration's 16); other values are for profiling "
                          "captures and scaling studies, not for the headline number")
-    ap.add_argument("--phase", default="scan", choices=["scan", "sequential"],
+    ap.add_argument("--phase", default="scan", choices=["scan", "sequential", "fundamental"],
                     help="phase-anchor mode of the oscillator bank")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))

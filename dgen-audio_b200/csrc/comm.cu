@@ -87,6 +87,11 @@ DGC_EXPORT int32_t dgc_allreduce_sum(dgc_ctx *ctx, float *buf_dev, uint64_t n_fl
     // a context without a communicator is a world of one: the sum over ranks is the buffer itself
     return DGC_OK;
   }
+  // The collective must not be part of a recorded step: a two-GPU run with the all-reduce inside the recording
+  // never finished.  End the recording, exchange, record the update separately.
+  DGC_REQUIRE(ctx, !ctx->capturing,
+              "the gradient exchange cannot be recorded: end the recording (dgc_graph_end), exchange, and record "
+              "the optimizer update as a second step");
   Nccl &n = nccl();
   // ncclFloat32 = 7, ncclSum = 0 (nccl.h enums ncclDataType_t / ncclRedOp_t, stable since NCCL 2.0)
   int rc = n.all_reduce(buf_dev, buf_dev, (size_t)n_floats, 7, 0, ctx->comm, ctx->stream);

@@ -26,6 +26,9 @@ struct dgc_ctx {
   // context-owned scratch (grown on demand, never shrunk)
   float *scratch = nullptr;
   uint64_t scratch_floats = 0;
+  // bumped whenever a context-owned device buffer (scratch, staging, transposed-operand copies) is freed or
+  // reallocated: a recorded step holds raw pointers into those buffers and must be re-recorded afterwards
+  uint64_t buffer_generation = 0;
   // cached data-independent tables
   std::map<std::pair<int, int>, float *> playheads;  // (F, T) -> device clock
   std::map<std::pair<int, int>, int *> row_ranges;   // (F, T) -> [F][4] frame ranges per control row

@@ -38,6 +38,7 @@ float *dgc_ctx_scratch(dgc_ctx *ctx, uint64_t nfloats) {
     cudaFree(ctx->scratch);
     ctx->scratch = nullptr;
     ctx->scratch_floats = 0;
+    ctx->buffer_generation++;
   }
   float *p = nullptr;
   cudaError_t e = cudaMalloc(&p, nfloats * sizeof(float));

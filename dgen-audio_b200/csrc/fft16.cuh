@@ -1,0 +1,202 @@
+// Register-blocked Stockham FFT: sixteen complex points per thread, N/16 threads per transform.
+//
+// The transforms of fft.cuh keep eight points per thread and exchange through shared memory after every radix-8
+// stage; for N = 2048 that is four trips through the shared-memory pipe (three exchanges plus the read of the
+// result), and that pipe, not the arithmetic, is what those kernels wait for.  Here a thread owns sixteen
+// points, so one stage can be a radix-16 butterfly and N = 2048 = 16 x 16 x 8 needs TWO exchanges
+// (1024 = 16 x 8 x 8, 512 = 8 x 8 x 8, 256 = 8 x 8 x 4: two; 128 = 16 x 8, 64 = 8 x 8: one).  The first stage
+// runs from the registers the caller filled (thread tid holds elements tid + m N/16, m < 16, exactly what a
+// coalesced strided load produces), the last stage leaves the result in registers, and the butterflies of the
+// last stage are dealt out in PAIRS (j, N/R - j): the thread that holds bin k also holds bin N - k, which is what
+// the unpacking of two real signals from one complex transform (and its inverse, the Hermitian packing) needs.
+// So no pass over shared memory exists for loading, unpacking or packing.
+//
+// Same conventions as fft.cuh: forward X[k] = sum x[n] exp(-2 pi i k n / N), unnormalised both ways, twiddle
+// table tw[m] = exp(-2 pi i m / N), shared buffers indexed through pad().
+#pragma once
+#include "fft.cuh"
+
+namespace dgfft16 {
+
+using namespace dgfft;
+
+// stage radices per transform size; R3 == 0: a two-stage transform
+template <int N> struct Plan;
+template <> struct Plan<2048> { static constexpr int R1 = 16, R2 = 16, R3 = 8; };
+template <> struct Plan<1024> { static constexpr int R1 = 16, R2 = 8, R3 = 8; };
+template <> struct Plan<512> { static constexpr int R1 = 8, R2 = 8, R3 = 8; };
+template <> struct Plan<256> { static constexpr int R1 = 8, R2 = 8, R3 = 4; };
+template <> struct Plan<128> { static constexpr int R1 = 16, R2 = 8, R3 = 0; };
+template <> struct Plan<64> { static constexpr int R1 = 8, R2 = 8, R3 = 0; };
+
+template <int N> struct Geo {
+  static constexpr int T = N / 16;                                          // threads per transform
+  static constexpr int RL = Plan<N>::R3 ? Plan<N>::R3 : Plan<N>::R2;        // radix of the last stage (<= 8)
+  static constexpr int NBL = N / RL;                                        // butterflies of the last stage
+  static constexpr int PAIRS = 8 / RL;                                      // butterfly pairs per thread there
+  static constexpr bool THREE = Plan<N>::R3 != 0;
+};
+
+// multiply by exp(-+ 2 pi i m / 16), m a compile-time constant in 0..9
+template <int M, bool INV>
+__device__ __forceinline__ float2 mul_w16(float2 a) {
+  constexpr float C1 = 0.92387953251128674f, S1 = 0.38268343236508977f, H = 0.70710678118654752f;
+  // forward: (c - i s)
+  if (M == 0) return a;
+  if (M == 4) return rot90<INV>(a);
+  float c, s;
+  if (M == 1) { c = C1; s = S1; }
+  else if (M == 2) { c = H; s = H; }
+  else if (M == 3) { c = S1; s = C1; }
+  else if (M == 6) { c = -H; s = H; }
+  else /* M == 9 */ { c = -C1; s = -S1; }
+  if (INV) s = -s;
+  // (a.x + i a.y)(c - i s) = (a.x c + a.y s) + i (a.y c - a.x s)
+  return make_float2(fmaf(a.x, c, a.y * s), fmaf(a.y, c, -a.x * s));
+}
+
+// 16-point DFT in registers, natural order in and out (4 x 4 decomposition)
+template <bool INV>
+__device__ __forceinline__ void dft16(float2 *v) {
+#pragma unroll
+  for (int r = 0; r < 4; ++r) dft4<INV>(v[r], v[r + 4], v[r + 8], v[r + 12]);
+  // v[r + 4 q] = Y[r][q]; twiddle W16^(r q)
+  v[5] = mul_w16<1, INV>(v[5]);   v[9] = mul_w16<2, INV>(v[9]);   v[13] = mul_w16<3, INV>(v[13]);
+  v[6] = mul_w16<2, INV>(v[6]);   v[10] = mul_w16<4, INV>(v[10]); v[14] = mul_w16<6, INV>(v[14]);
+  v[7] = mul_w16<3, INV>(v[7]);   v[11] = mul_w16<6, INV>(v[11]); v[15] = mul_w16<9, INV>(v[15]);
+#pragma unroll
+  for (int q = 0; q < 4; ++q) dft4<INV>(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+  // v[4 q + s] = X[q + 4 s]: transpose the 4 x 4 register tile
+#pragma unroll
+  for (int q = 0; q < 4; ++q)
+#pragma unroll
+    for (int s = q + 1; s < 4; ++s) {
+      float2 t = v[4 * q + s];
+      v[4 * q + s] = v[4 * s + q];
+      v[4 * s + q] = t;
+    }
+}
+
+template <int R, bool INV>
+__device__ __forceinline__ void dftN(float2 *v) {
+  if (R == 16) dft16<INV>(v);
+  else dftR<R, INV>(v);
+}
+
+// v[t] *= w^t for t = 1 .. R-1, w = tw[m] (conjugated for the inverse): powers 1, 2, 4 (, 8) come from the table,
+// the others are products of those
+template <int R, bool INV>
+__device__ __forceinline__ void twiddle(float2 *v, const float2 *__restrict__ tw, int m) {
+  auto ld = [&](int idx) {
+    float2 w = __ldg(&tw[idx]);
+    if (INV) w.y = -w.y;
+    return w;
+  };
+  if (R == 2) {
+    v[1] = cmul(v[1], ld(m));
+  } else if (R == 4) {
+    const float2 w1 = ld(m), w2 = ld(2 * m);
+    v[1] = cmul(v[1], w1); v[2] = cmul(v[2], w2); v[3] = cmul(v[3], cmul(w1, w2));
+  } else if (R == 8) {
+    const float2 w1 = ld(m), w2 = ld(2 * m), w4 = ld(4 * m);
+    const float2 w3 = cmul(w1, w2), w5 = cmul(w1, w4), w6 = cmul(w2, w4), w7 = cmul(w3, w4);
+    v[1] = cmul(v[1], w1); v[2] = cmul(v[2], w2); v[3] = cmul(v[3], w3); v[4] = cmul(v[4], w4);
+    v[5] = cmul(v[5], w5); v[6] = cmul(v[6], w6); v[7] = cmul(v[7], w7);
+  } else {
+    const float2 w1 = ld(m), w2 = ld(2 * m), w4 = ld(4 * m), w8 = ld(8 * m);
+    const float2 w3 = cmul(w1, w2), w5 = cmul(w1, w4), w6 = cmul(w2, w4), w7 = cmul(w3, w4);
+    v[1] = cmul(v[1], w1); v[2] = cmul(v[2], w2); v[3] = cmul(v[3], w3); v[4] = cmul(v[4], w4);
+    v[5] = cmul(v[5], w5); v[6] = cmul(v[6], w6); v[7] = cmul(v[7], w7); v[8] = cmul(v[8], w8);
+    v[9] = cmul(v[9], cmul(w1, w8)); v[10] = cmul(v[10], cmul(w2, w8)); v[11] = cmul(v[11], cmul(w3, w8));
+    v[12] = cmul(v[12], cmul(w4, w8)); v[13] = cmul(v[13], cmul(w5, w8)); v[14] = cmul(v[14], cmul(w6, w8));
+    v[15] = cmul(v[15], cmul(w7, w8));
+  }
+}
+
+// the threads that share one transform wait for each other
+template <int N>
+__device__ __forceinline__ void sync_transform() {
+  if (N / 16 <= 32) __syncwarp();
+  else __syncthreads();   // callers give every transform of N >= 1024 whole warps and run them in lockstep
+}
+
+// First stage, from registers: x[m] = element tid + m T.  Writes the stage output to `buf` (Stockham order).
+template <int N, bool INV>
+__device__ __forceinline__ void stage_first(float2 (&x)[16], float2 *buf, int tid) {
+  constexpr int R = Plan<N>::R1, PER = 16 / R, T = N / 16;
+#pragma unroll
+  for (int q = 0; q < PER; ++q) {
+    float2 v[R];
+#pragma unroll
+    for (int t = 0; t < R; ++t) v[t] = x[q + PER * t];      // in[j + t N/R], j = tid + q T
+    dftN<R, INV>(v);
+    const int j = tid + q * T;
+#pragma unroll
+    for (int t = 0; t < R; ++t) buf[pad(j * R + t)] = v[t];
+  }
+}
+
+// Middle stage: shared -> shared, input stride Ns = R1.
+template <int N, bool INV>
+__device__ __forceinline__ void stage_middle(const float2 *in, float2 *out, int tid, const float2 *__restrict__ tw) {
+  constexpr int R = Plan<N>::R2, PER = 16 / R, T = N / 16, Ns = Plan<N>::R1;
+#pragma unroll
+  for (int q = 0; q < PER; ++q) {
+    const int j = tid + q * T, k = j & (Ns - 1);
+    float2 v[R];
+#pragma unroll
+    for (int t = 0; t < R; ++t) v[t] = in[pad(j + t * (N / R))];
+    twiddle<R, INV>(v, tw, k * (N / (Ns * R)));
+    dftN<R, INV>(v);
+    const int j0 = (j - k) * R + k;
+#pragma unroll
+    for (int t = 0; t < R; ++t) out[pad(j0 + t * Ns)] = v[t];
+  }
+}
+
+// The two butterflies of pair p of the last stage that thread tid owns: (a, NBL - a), or (0, NBL / 2) for a == 0.
+template <int N>
+__device__ __forceinline__ void last_pair(int tid, int p, int &ja, int &jb) {
+  const int a = tid + p * (N / 16);
+  ja = a;
+  jb = a == 0 ? Geo<N>::NBL / 2 : Geo<N>::NBL - a;
+}
+
+// Last stage: shared -> registers.  z[p][0][t] = bin ja + t NBL, z[p][1][t] = bin jb + t NBL.
+// For a != 0 the partner of bin (ja, t) is bin (jb, RL - 1 - t).
+template <int N, bool INV>
+__device__ __forceinline__ void stage_last(const float2 *in, float2 (&z)[Geo<N>::PAIRS][2][Geo<N>::RL], int tid,
+                                           const float2 *__restrict__ tw) {
+  constexpr int R = Geo<N>::RL, NBL = Geo<N>::NBL;
+#pragma unroll
+  for (int p = 0; p < Geo<N>::PAIRS; ++p) {
+    int jj[2];
+    last_pair<N>(tid, p, jj[0], jj[1]);
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int j = jj[e];
+#pragma unroll
+      for (int t = 0; t < R; ++t) z[p][e][t] = in[pad(j + t * NBL)];
+      twiddle<R, INV>(z[p][e], tw, j);     // Ns = NBL: k = j, table step 1
+      dftN<R, INV>(z[p][e]);
+    }
+  }
+}
+
+// Whole forward or inverse transform: registers x[16] in (element tid + m N/16), registers z out (see stage_last).
+// bufa / bufb: padded(N) float2 each (bufb unused by the two-stage sizes); nobody may still read them on entry.
+template <int N, bool INV>
+__device__ __forceinline__ void fft16(float2 (&x)[16], float2 (&z)[Geo<N>::PAIRS][2][Geo<N>::RL], float2 *bufa,
+                                      float2 *bufb, int tid, const float2 *__restrict__ tw) {
+  stage_first<N, INV>(x, bufa, tid);
+  sync_transform<N>();
+  if (Geo<N>::THREE) {
+    stage_middle<N, INV>(bufa, bufb, tid, tw);
+    sync_transform<N>();
+    stage_last<N, INV>(bufb, z, tid, tw);
+  } else {
+    stage_last<N, INV>(bufa, z, tid, tw);
+  }
+}
+
+}  // namespace dgfft16

@@ -318,6 +318,7 @@ DGC_EXPORT int32_t dgc_linear_fwd(dgc_ctx *ctx, const float *a_dev, const float 
       if (ctx->wt_buf) {
         cudaStreamSynchronize(ctx->stream);
         cudaFree(ctx->wt_buf);
+        ctx->buffer_generation++;
         ctx->wt_buf = nullptr;
       }
       DGC_CUDA(ctx, cudaMalloc(&ctx->wt_buf, (size_t)K * N * sizeof(float)));
@@ -358,6 +359,7 @@ DGC_EXPORT int32_t dgc_linear_bwd(dgc_ctx *ctx, const float *a_dev, const float 
       if (ctx->dzt_buf) {
         cudaStreamSynchronize(ctx->stream);
         cudaFree(ctx->dzt_buf);
+        ctx->buffer_generation++;
         ctx->dzt_buf = nullptr;
       }
       DGC_CUDA(ctx, cudaMalloc(&ctx->dzt_buf, n * sizeof(float)));

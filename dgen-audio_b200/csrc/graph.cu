@@ -11,6 +11,9 @@
 //  * the context must be bound to a stream of its own or of the caller's, not the legacy default stream;
 //  * every buffer a call may allocate (context scratch, cached tables, transposed-weight copies) must exist
 //    already: run the step once before recording it;
+//  * a call AFTER the recording that grows one of those buffers frees the addresses the recording holds: the
+//    context counts such reallocations and dgc_graph_launch then refuses with DGC_ERR_INVALID ("record the step
+//    again") instead of replaying into freed memory;
 //  * values passed by value are frozen into the recording (sizes, the learning rate); anything that changes from
 //    step to step must live in device memory -- inputs are refilled in place, the Adam step index is counted on
 //    the device (dgc_adam_step_counted).
@@ -22,6 +25,7 @@ struct dgc_graph {
   cudaGraphExec_t exec = nullptr;
   uint64_t nodes = 0;
   int64_t launches = 0;   // launches the library counted while recording: added to the context's count per replay
+  uint64_t generation = 0;  // the context's buffer generation when the recording ended
 };
 
 DGC_EXPORT int32_t dgc_graph_begin(dgc_ctx *ctx) {
@@ -55,6 +59,7 @@ DGC_EXPORT int32_t dgc_graph_end(dgc_ctx *ctx, dgc_graph **out) {
   r->ctx = ctx;
   r->graph = g;
   r->launches = ctx->launches - ctx->capture_launches0;
+  r->generation = ctx->buffer_generation;
   size_t n = 0;
   cudaGraphGetNodes(g, nullptr, &n);
   r->nodes = n;
@@ -75,6 +80,12 @@ DGC_EXPORT int32_t dgc_graph_launch(dgc_ctx *ctx, dgc_graph *g) {
   DGC_REQUIRE(ctx, g && g->exec, "null graph");
   DGC_REQUIRE(ctx, g->ctx == ctx, "the graph was recorded on another context");
   DGC_REQUIRE(ctx, !ctx->capturing, "a recording is in progress");
+  // A later call that needed more scratch freed and reallocated a context-owned buffer: the recording still
+  // holds the old addresses and would read and write freed memory.  Nothing is launched.
+  if (g->generation != ctx->buffer_generation)
+    return dgc_fail(ctx, DGC_ERR_INVALID,
+                    "dgc_graph_launch: a context buffer was reallocated after this step was recorded "
+                    "(a later call needed more scratch): record the step again");
   DGC_CUDA(ctx, cudaGraphLaunch(g->exec, ctx->stream));
   ctx->launches += g->launches;
   return DGC_OK;

@@ -895,6 +895,7 @@ DGC_EXPORT int32_t dgc_biquad_bwd(dgc_ctx *ctx, const dgc_biquad_params *p, cons
 // library image (every GPU that loads the library holds these 256 KiB until the process exits), and
 // the caller supplies only the stream, the input and the output.
 // ---------------------------------------------------------------------------------------------
+#include <atomic>
 #include <mutex>
 
 namespace {
@@ -903,8 +904,11 @@ constexpr int STATIC_MAX_CHUNKS = DGC_ONEPOLE_STATIC_MAX_CHUNKS;
 static __device__ __align__(256) float g_onepole_static_scratch[2 * STATIC_MAX_CHUNKS];
 
 constexpr int STATIC_MAX_DEVICES = 64;
-std::mutex g_static_mutex;
-float *g_static_ptr[STATIC_MAX_DEVICES] = {nullptr};
+// Resolved device address of the array, per device.  Published once with release ordering; every later call
+// reads it with one acquire load and takes no lock, so a caller on a real-time thread never waits for another
+// thread that is still in its own first call on some other device.
+std::mutex g_static_mutex;   // serialises the one-time look-ups only
+std::atomic<float *> g_static_ptr[STATIC_MAX_DEVICES];
 
 void static_msg(char *buf, uint32_t len, const char *fmt, long long a = 0, long long b = 0) {
   if (buf && len) snprintf(buf, len, fmt, a, b);
@@ -936,12 +940,13 @@ DGC_EXPORT int32_t dgc_onepole_fwd_static(void *cuda_stream, const float *x_dev,
     static_msg(err_buf, err_len, "dgc_onepole_fwd_static: no usable current device (cudaGetDevice = %lld)", (long long)e);
     return DGC_ERR_CUDA;
   }
-  float *scratch = nullptr;
-  {
+  float *scratch = g_static_ptr[dev].load(std::memory_order_acquire);
+  if (!scratch) {
     // Set-up, once per device, with that device current: the array's name is only a host-side
     // handle for the symbol; the address a kernel can use comes from cudaGetSymbolAddress.
     std::lock_guard<std::mutex> lock(g_static_mutex);
-    if (!g_static_ptr[dev]) {
+    scratch = g_static_ptr[dev].load(std::memory_order_relaxed);
+    if (!scratch) {
       float *p = nullptr;
       e = cudaGetSymbolAddress((void **)&p, g_onepole_static_scratch);
       if (e != cudaSuccess || !p) {
@@ -949,10 +954,12 @@ DGC_EXPORT int32_t dgc_onepole_fwd_static(void *cuda_stream, const float *x_dev,
                    (long long)e, (long long)dev);
         return DGC_ERR_CUDA;
       }
-      g_static_ptr[dev] = p;
+      g_static_ptr[dev].store(p, std::memory_order_release);
+      scratch = p;
     }
-    scratch = g_static_ptr[dev];
   }
+  // an error left behind by an unrelated earlier call must not be reported as a failure of these launches
+  (void)cudaGetLastError();
   cudaStream_t st = (cudaStream_t)cuda_stream;
   float *chunk_end = scratch, *carry = scratch + STATIC_MAX_CHUNKS;
   // Every slot that is read below is written first by this call (chunk ends by pass 0, carries by the

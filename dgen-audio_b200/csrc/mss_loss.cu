@@ -8,9 +8,12 @@
 // memory, prediction and target ride the real and imaginary lane of ONE complex FFT, and the
 // linear and log terms come from the same spectrum.
 #include <algorithm>
+#include <cstdlib>
+#include <cstring>
 
 #include "common.cuh"
 #include "fft.cuh"
+#include "fft16.cuh"
 
 namespace {
 
@@ -131,6 +134,126 @@ mss_fwd_kernel(const float *__restrict__ pred, const float *__restrict__ pred_b,
 #define CASE(NN) \
   case NN: mss_fwd_body<NN, SUM2>(fwd_sm, red, bx, b, pred, pred_b, target, B, T, d.hop[s], d.H[s], d.window[s], d.tw[s], d.lin[s], d.lg[s]); break;
     CASE(16) CASE(32) CASE(64) CASE(128) CASE(256) CASE(512) CASE(1024) CASE(2048)
+#undef CASE
+    default: break;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Forward, register-blocked: sixteen points per thread (fft16.cuh), N/16 threads per window, 128-thread
+// blocks.  A thread loads its sixteen windowed samples of both signals straight into the registers of the
+// first radix-16 (or radix-8) stage, the transform exchanges through shared memory twice (once for N <= 128),
+// and the last stage leaves bin k and bin N - k in the SAME thread, so the spectra of the two real signals are
+// unpacked, compared and summed without another pass over shared memory.  The factor 1/2 of the unpacking is
+// carried as 2 |X|: the linear term is halved once at the end, and log(2|X| + 2 eps) - log(2|Y| + 2 eps) is the
+// reference's log(|X| + eps) - log(|Y| + eps); square roots and logarithms are the approximate hardware ones.
+// ---------------------------------------------------------------------------------------------
+constexpr int LOSS16_THREADS = 128;
+constexpr float LN2_F = 0.69314718055994531f;
+
+__device__ __forceinline__ float fast_sqrt(float v) {
+  float r;
+  asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(v));
+  return r;
+}
+
+// one {k, N - k} pair of bins of z = FFT(x1 + i x2): adds 2 | |X1| - |X2| | and the log2 term
+__device__ __forceinline__ void pair_terms(float2 zk, float2 zn, float &lin, float &lg) {
+  const float ax = zk.x + zn.x, ay = zk.y - zn.y;     // 2 X1[k]
+  const float bx = zk.y + zn.y, by = zn.x - zk.x;     // 2 X2[k]
+  const float m1 = fast_sqrt(fmaf(ax, ax, ay * ay)), m2 = fast_sqrt(fmaf(bx, bx, by * by));
+  lin += fabsf(m1 - m2);
+  lg += fabsf(__log2f(m1 + 2.0f * LOG_EPS) - __log2f(m2 + 2.0f * LOG_EPS));
+}
+// a bin that is its own partner (k = 0 and k = N/2): X1 = Re z, X2 = Im z
+__device__ __forceinline__ void self_terms(float2 z, float &lin, float &lg) {
+  const float m1 = 2.0f * fabsf(z.x), m2 = 2.0f * fabsf(z.y);
+  lin += fabsf(m1 - m2);
+  lg += fabsf(__log2f(m1 + 2.0f * LOG_EPS) - __log2f(m2 + 2.0f * LOG_EPS));
+}
+
+template <int N, bool SUM2>
+__device__ __forceinline__ void mss_fwd16_body(float2 *sm, float *red, int bx, int b, const float *__restrict__ pred,
+                                               const float *__restrict__ pred_b,
+                                               const float *__restrict__ target, int B, int T, int hop, int H,
+                                               const float *__restrict__ window, const float2 *__restrict__ tw,
+                                               float *__restrict__ part_lin, float *__restrict__ part_log) {
+  using Gm = dgfft16::Geo<N>;
+  constexpr int TT = Gm::T;                     // threads per window
+  constexpr int NF = LOSS16_THREADS / TT;       // windows per block
+  constexpr int PN = padded(N), RL = Gm::RL;
+  const int tid = threadIdx.x, f = tid / TT, lt = tid % TT;
+  const int h = bx * NF + f;
+  const bool valid = h < H;
+  const int t_base = h * hop - (N - 1);
+  const float *x1 = pred + (size_t)b * T, *x2 = target + (size_t)b * T;
+  const float *x1b = SUM2 ? pred_b + (size_t)b * T : nullptr;   // prediction given as a sum of two signals
+  float2 *bufa = sm + f * PN, *bufb = sm + (NF + f) * PN;
+  float2 x[16];
+  // a window ends at frame h * hop <= T - 1, so only its start can fall outside the signal
+  if (valid && t_base >= 0) {
+    const float *p1 = x1 + t_base + lt, *p2 = x2 + t_base + lt, *wp = window + lt;
+#pragma unroll
+    for (int m = 0; m < 16; ++m) {
+      const float w = __ldg(wp + m * TT);
+      const float xp = SUM2 ? __fadd_rn(p1[m * TT], x1b[t_base + lt + m * TT]) : p1[m * TT];
+      x[m] = make_float2(xp * w, p2[m * TT] * w);
+    }
+  } else {
+#pragma unroll
+    for (int m = 0; m < 16; ++m) {
+      const int i = lt + m * TT, t = t_base + i;
+      float2 v = make_float2(0.0f, 0.0f);
+      if (valid && t >= 0) {
+        const float w = __ldg(&window[i]);
+        const float xp = SUM2 ? __fadd_rn(x1[t], x1b[t]) : x1[t];
+        v = make_float2(xp * w, x2[t] * w);
+      }
+      x[m] = v;
+    }
+  }
+  float2 z[Gm::PAIRS][2][RL];
+  dgfft16::fft16<N, false>(x, z, bufa, bufb, lt, tw);
+  float lin = 0.0f, lg = 0.0f;
+#pragma unroll
+  for (int p = 0; p < Gm::PAIRS; ++p) {
+    if (lt + p * TT != 0) {
+#pragma unroll
+      for (int t = 0; t < RL; ++t) pair_terms(z[p][0][t], z[p][1][RL - 1 - t], lin, lg);
+    } else {
+      // butterfly 0 holds bins t N/RL: 0 and N/2 are their own partners, t pairs with RL - t;
+      // butterfly NBL/2 holds bins N/(2 RL) + t N/RL: t pairs with RL - 1 - t
+      self_terms(z[p][0][0], lin, lg);
+      self_terms(z[p][0][RL / 2], lin, lg);
+#pragma unroll
+      for (int t = 1; t < RL / 2; ++t) pair_terms(z[p][0][t], z[p][0][RL - t], lin, lg);
+#pragma unroll
+      for (int t = 0; t < RL / 2; ++t) pair_terms(z[p][1][t], z[p][1][RL - 1 - t], lin, lg);
+    }
+  }
+  lin = group_sum<TT>(lin, red, tid);
+  lg = group_sum<TT>(lg, red, tid);
+  if (valid && lt == 0) {
+    part_lin[(size_t)h * B + b] = 0.5f * lin;
+    part_log[(size_t)h * B + b] = LN2_F * lg;
+  }
+}
+
+constexpr int FWD16_SMEM_BYTES = 2 * padded(2048) * (int)sizeof(float2);
+
+template <bool SUM2>
+__global__ void __launch_bounds__(LOSS16_THREADS, 6)
+mss_fwd16_kernel(const float *__restrict__ pred, const float *__restrict__ pred_b, const float *__restrict__ target,
+                 int B, int T, const FwdDesc d) {
+  extern __shared__ float2 fwd_sm[];
+  __shared__ float red[LOSS16_THREADS / 32];
+  int s = 0;
+  while (s + 1 < d.nscales && (int)blockIdx.x >= d.first_block[s + 1]) ++s;
+  const int bx = blockIdx.x - d.first_block[s], b = blockIdx.y;
+  switch (d.N[s]) {
+#define CASE(NN) \
+  case NN: mss_fwd16_body<NN, SUM2>(fwd_sm, red, bx, b, pred, pred_b, target, B, T, d.hop[s], d.H[s], d.window[s], d.tw[s], d.lin[s], d.lg[s]); break;
+    CASE(64) CASE(128) CASE(256) CASE(512) CASE(1024) CASE(2048)
 #undef CASE
     default: break;
   }
@@ -451,39 +574,59 @@ int32_t dgc_mss_loss_fwd_sum(dgc_ctx *ctx, const dgc_mss_params *p, const float 
     off += 2ll * H * p->B;
   }
   std::stable_sort(order, order + no, [&](int x, int y) { return p->sizes[x] > p->sizes[y]; });
-  FwdDesc fd;
-  fd.nscales = no;
-  int blocks = 0;
+  // windows of 64 points and more run on the sixteen-points-per-thread kernel (128-thread blocks), the two smallest
+  // sizes on the eight-points-per-thread one (256-thread blocks): two descriptors, at most two launches
+  static const bool force_old = [] {
+    const char *e = getenv("DGC_MSS_FWD");
+    return e && strcmp(e, "r8") == 0;
+  }();
+  FwdDesc fd16, fd8;
+  fd16.nscales = fd8.nscales = 0;
+  int blocks16 = 0, blocks8 = 0;
   for (int i = 0; i < no; ++i) {
     const int s = order[i], N = p->sizes[s];
     const int hop = hop_of(p, s), H = dgc_div_up(p->T, hop);
-    fd.N[i] = N;
-    fd.hop[i] = hop;
-    fd.H[i] = H;
-    fd.window[i] = dgc_ctx_hann_sym(ctx, N);
-    fd.tw[i] = dgc_ctx_twiddles(ctx, N);
-    if (!fd.window[i] || !fd.tw[i]) return DGC_ERR_OOM;
-    fd.lin[i] = part + off_of[s];
-    fd.lg[i] = fd.lin[i] + (long long)H * p->B;
-    fd.first_block[i] = blocks;
-    blocks += dgc_div_up(H, LOSS_THREADS / (N / 8));
+    const bool wide = N >= 64 && !force_old;
+    FwdDesc &fd = wide ? fd16 : fd8;
+    int &blocks = wide ? blocks16 : blocks8;
+    const int k = fd.nscales++;
+    fd.N[k] = N;
+    fd.hop[k] = hop;
+    fd.H[k] = H;
+    fd.window[k] = dgc_ctx_hann_sym(ctx, N);
+    fd.tw[k] = dgc_ctx_twiddles(ctx, N);
+    if (!fd.window[k] || !fd.tw[k]) return DGC_ERR_OOM;
+    fd.lin[k] = part + off_of[s];
+    fd.lg[k] = fd.lin[k] + (long long)H * p->B;
+    fd.first_block[k] = blocks;
+    blocks += wide ? dgc_div_up(H, LOSS16_THREADS / (N / 16)) : dgc_div_up(H, LOSS_THREADS / (N / 8));
+    fd.first_block[k + 1] = blocks;
   }
-  fd.first_block[no] = blocks;
-  if (no > 0) {
-    // six resident blocks per SM (launch bounds cap the registers at 40) need 6 x 34 KB of shared memory: ask for
-    // the largest carve-out
-    static const bool carved = [] {
-      cudaFuncSetAttribute(mss_fwd_kernel<true>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-      cudaFuncSetAttribute(mss_fwd_kernel<false>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-      return true;
-    }();
-    (void)carved;
+  // resident blocks per SM are limited by shared memory (6 x 34 KB): ask for the largest carve-out
+  static const bool carved = [] {
+    cudaFuncSetAttribute(mss_fwd_kernel<true>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    cudaFuncSetAttribute(mss_fwd_kernel<false>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    cudaFuncSetAttribute(mss_fwd16_kernel<true>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    cudaFuncSetAttribute(mss_fwd16_kernel<false>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    return true;
+  }();
+  (void)carved;
+  if (fd16.nscales > 0) {
     if (pred_b_dev)
-      mss_fwd_kernel<true><<<dim3(blocks, p->B), LOSS_THREADS, FWD_SMEM_BYTES, ctx->stream>>>(pred_dev, pred_b_dev,
-                                                                                              target_dev, p->B, p->T, fd);
+      mss_fwd16_kernel<true><<<dim3(blocks16, p->B), LOSS16_THREADS, FWD16_SMEM_BYTES, ctx->stream>>>(
+          pred_dev, pred_b_dev, target_dev, p->B, p->T, fd16);
     else
-      mss_fwd_kernel<false><<<dim3(blocks, p->B), LOSS_THREADS, FWD_SMEM_BYTES, ctx->stream>>>(pred_dev, nullptr,
-                                                                                               target_dev, p->B, p->T, fd);
+      mss_fwd16_kernel<false><<<dim3(blocks16, p->B), LOSS16_THREADS, FWD16_SMEM_BYTES, ctx->stream>>>(
+          pred_dev, nullptr, target_dev, p->B, p->T, fd16);
+    DGC_LAUNCHED(ctx, "mss_fwd16");
+  }
+  if (fd8.nscales > 0) {
+    if (pred_b_dev)
+      mss_fwd_kernel<true><<<dim3(blocks8, p->B), LOSS_THREADS, FWD_SMEM_BYTES, ctx->stream>>>(pred_dev, pred_b_dev,
+                                                                                               target_dev, p->B, p->T, fd8);
+    else
+      mss_fwd_kernel<false><<<dim3(blocks8, p->B), LOSS_THREADS, FWD_SMEM_BYTES, ctx->stream>>>(pred_dev, nullptr,
+                                                                                                target_dev, p->B, p->T, fd8);
     DGC_LAUNCHED(ctx, "mss_fwd");
   }
   // weights: (w / nscales) with nscales = number of usable windows, normalize:true divides by T

@@ -268,6 +268,96 @@ anchor_scan_kernel(const unsigned long long *__restrict__ sums, int B, int C, in
   }
 }
 
+// FUNDAMENTAL anchors.  Every partial of a voice is a multiple of one fundamental, so one running sum per voice
+// is enough: A[c] = sum_{n < 64 c} f0[n] / sr (mod 1) in Q0.64, and partial k starts chunk c at k * A[c] (mod 1),
+// an exact integer product.  The per-frame quotient is taken to ~2^-48 (correctly rounded single-precision
+// quotient plus the quotient of its exact remainder), so the sum over a whole render is good to ~2^-40 turns.
+// What this mode leaves out, against the reference recurrence, is the rounding of every partial's own increment
+// fl(fl(k f0) / sr) (the SCAN mode keeps it; both leave out the rounding of the phase add itself).
+__device__ __forceinline__ unsigned long long inc_q64(float f0v, float sr, float rsr) {
+  if (!(f0v >= 0.0f && f0v < sr)) {  // outside [0, sr): the fraction of f0 / sr; non-finite -> 0
+    float r = f0v * rsr;
+    r = r - floorf(r);
+    if (!(r >= 0.0f && r < 1.0f)) r = 0.0f;
+    return __float2ull_rn(r * 18446744073709551616.0f);
+  }
+  const float qh = div_by_const(f0v, sr, rsr);
+  const float ql = __fmaf_rn(-qh, sr, f0v) * rsr;
+  if (qh >= 1.0f) return 0ull;  // f0 within half an ulp of sr: one whole turn
+  return __float2ull_rn(qh * 18446744073709551616.0f) + (unsigned long long)__float2ll_rn(ql * 18446744073709551616.0f);
+}
+
+// One warp per (voice, chunk of 64 frames): the per-sample fundamental and output envelope of f0_track_kernel plus
+// the chunk's total phase advance of the fundamental.
+__global__ void __launch_bounds__(128)
+f0_track_fund_kernel(const float2 *__restrict__ rowtab, const float *__restrict__ f0, int B, int T, int F, float sr,
+                     float rsr, float *__restrict__ f0t, const float *__restrict__ uv,
+                     const float *__restrict__ gain, float scale, float *__restrict__ env,
+                     unsigned long long *__restrict__ chunk_sum /* [B][C] */) {
+  const int C = (T + CH - 1) / CH;
+  const int c = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31, b = blockIdx.y;
+  if (c >= C) return;
+  unsigned long long tot = 0ull;
+#pragma unroll
+  for (int h = 0; h < CH / 32; ++h) {
+    const int n = c * CH + h * 32 + lane;
+    if (n < T) {
+      const float2 rt = rowtab[n];
+      const int lo = __float_as_int(rt.x), hi = lo + 1 >= F ? 0 : lo + 1;
+      const float fr = rt.y, omf = __fsub_rn(1.0f, fr);
+      const float f0v = lerp_strict(omf, f0[(size_t)lo * B + b], fr, f0[(size_t)hi * B + b]);
+      f0t[(size_t)b * T + n] = f0v;
+      if (env) {
+        const float gt = fmaf(fr, gain[(size_t)hi * B + b], omf * gain[(size_t)lo * B + b]);
+        const float uvt = fmaf(fr, uv[(size_t)hi * B + b], omf * uv[(size_t)lo * B + b]);
+        env[(size_t)b * T + n] = gt * uvt * scale;
+      }
+      tot += inc_q64(f0v, sr, rsr);
+    }
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, off);
+  if (lane == 0) chunk_sum[(size_t)b * C + c] = tot;
+}
+
+// Exclusive prefix over the chunk totals of one voice (one block per voice, wrapping 64-bit adds = sums mod 1).
+constexpr int FSCAN_THREADS = 1024;
+__global__ void __launch_bounds__(FSCAN_THREADS)
+fund_scan_kernel(const unsigned long long *__restrict__ chunk_sum, int C, unsigned long long *__restrict__ prefix) {
+  __shared__ unsigned long long warp_tot[FSCAN_THREADS / 32];
+  const unsigned long long *s = chunk_sum + (size_t)blockIdx.x * C;
+  unsigned long long *o = prefix + (size_t)blockIdx.x * C;
+  const int per = (C + FSCAN_THREADS - 1) / FSCAN_THREADS;
+  const int c0 = min(C, (int)threadIdx.x * per), c1 = min(C, c0 + per);
+  unsigned long long mine = 0ull;
+  for (int c = c0; c < c1; ++c) mine += s[c];
+  // inclusive scan of the thread totals: within the warp, then over the warp totals
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  unsigned long long inc = mine;
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const unsigned long long v = __shfl_up_sync(0xffffffffu, inc, off);
+    if (lane >= off) inc += v;
+  }
+  if (lane == 31) warp_tot[w] = inc;
+  __syncthreads();
+  if (w == 0) {
+    unsigned long long t = warp_tot[lane];
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const unsigned long long v = __shfl_up_sync(0xffffffffu, t, off);
+      if (lane >= off) t += v;
+    }
+    warp_tot[lane] = t;
+  }
+  __syncthreads();
+  unsigned long long acc = inc - mine + (w > 0 ? warp_tot[w - 1] : 0ull);
+  for (int c = c0; c < c1; ++c) {
+    o[c] = acc;
+    acc += s[c];
+  }
+}
+
 // Render: a group of LPC lanes owns one (voice, chunk); lane j carries partials j, j+LPC, ...
 // (P per lane) through the 64 frames; per frame the group reduces sum(sin*masked) and sum(masked)
 // with shuffles; results of four frames are collected in lanes 0..3 and stored as one float4.
@@ -410,7 +500,8 @@ __global__ void __launch_bounds__(128, 5)
 harmonic_render_q_kernel(dgc_harmonic_params prm, float rsr, const float2 *__restrict__ rowtab,
                          const float *__restrict__ f0t, const float *__restrict__ env,
                          const float *__restrict__ amps, const uint32_t *__restrict__ anchors_q,
-                         const float *__restrict__ g_audio, float *__restrict__ audio) {
+                         const unsigned long long *__restrict__ fund, const float *__restrict__ g_audio,
+                         float *__restrict__ audio) {
   constexpr int G = 128 / LPC, FB = 8;
   constexpr float THREE_PI = 9.42477796076938f;
   const int B = prm.B, T = prm.T, K = prm.K, F = prm.F;
@@ -425,11 +516,14 @@ harmonic_render_q_kernel(dgc_harmonic_params prm, float rsr, const float2 *__res
 
   uint32_t q[P];
   float alo[P], dl[P];
+  // chunk anchors: a table [B][C][K] (SCAN mode), or k times the fundamental's running sum (FUNDAMENTAL mode)
   const uint32_t *anc = anchors_q + ((size_t)b * C + c) * K;
+  const unsigned long long fa = fund ? fund[(size_t)b * C + c] : 0ull;
 #pragma unroll
   for (int i = 0; i < P; ++i) {
     int k = j + LPC * i;
-    q[i] = (k < K ? anc[k] : 0u) + 0x100u;  // + 2^8: dropping the low 9 bits below rounds to nearest
+    const uint32_t a0 = fund ? (uint32_t)(((unsigned long long)(k + 1) * fa) >> 32) : (k < K ? anc[k] : 0u);
+    q[i] = a0 + 0x100u;  // + 2^8: dropping the low 9 bits below rounds to nearest
     alo[i] = 0.0f;
     dl[i] = 0.0f;
   }
@@ -564,7 +658,7 @@ void launch_render_q(dgc_ctx *ctx, const dgc_harmonic_params &p, const float2 *r
   constexpr int G = 128 / LPC;
   dim3 grid(dgc_div_up(C, G), p.B);
   harmonic_render_q_kernel<LPC, P, MODE><<<grid, 128, 0, ctx->stream>>>(p, 1.0f / p.sample_rate, rowtab, x.f0t, x.env,
-                                                                         amps, x.anchors_q, g_audio, out);
+                                                                         amps, x.anchors_q, x.fund, g_audio, out);
 }
 
 // out[e][n] = scale * sum_{m > n} g[e][m]: the reverse exclusive scan of the reference's temporalGradScan
@@ -710,9 +804,10 @@ DGC_EXPORT uint64_t dgc_harmonic_scratch_floats(const dgc_harmonic_params *p) {
   if (!p || p->B <= 0 || p->T <= 0 || p->K <= 0) return 0;
   uint64_t C = (uint64_t)(p->T + CH - 1) / CH;
   uint64_t lanes = (uint64_t)p->B * C * p->K;
-  // f0 track [B][T] (rounded up to 4), anchors [B][C][K], chunk sums as 64-bit words, output envelope
-  // [B][T], anchors as Q0.32 words
-  return 2 * (((uint64_t)p->B * p->T + 3) & ~3ull) + lanes + 2 * lanes + lanes + 16;
+  // f0 track [B][T] (rounded up to 4), anchors [B][C][K], chunk sums as 64-bit words (at least the 2 x [B][C]
+  // words of the FUNDAMENTAL mode), output envelope [B][T], anchors as Q0.32 words
+  const uint64_t sum_words = lanes > 2 * (uint64_t)p->B * C ? lanes : 2 * (uint64_t)p->B * C;
+  return 2 * (((uint64_t)p->B * p->T + 3) & ~3ull) + lanes + 2 * sum_words + lanes + 16;
 }
 
 int32_t dgc_harmonic_prepare(dgc_ctx *ctx, const dgc_harmonic_params *p, const float *f0_dev, float *scratch,
@@ -721,7 +816,8 @@ int32_t dgc_harmonic_prepare(dgc_ctx *ctx, const dgc_harmonic_params *p, const f
   DGC_REQUIRE(ctx, p->B > 0 && p->T > 0 && p->F > 0 && p->K > 0 && p->K <= 512, "size out of range (K <= 512)");
   DGC_REQUIRE(ctx, p->B <= 65535, "B must be <= 65535");
   DGC_REQUIRE(ctx, p->sample_rate > 0, "sample rate must be positive");
-  DGC_REQUIRE(ctx, p->phase_mode == DGC_PHASE_SEQUENTIAL || p->phase_mode == DGC_PHASE_SCAN, "phase mode");
+  DGC_REQUIRE(ctx, p->phase_mode == DGC_PHASE_SEQUENTIAL || p->phase_mode == DGC_PHASE_SCAN ||
+                       p->phase_mode == DGC_PHASE_FUNDAMENTAL, "phase mode");
   DGC_REQUIRE(ctx, (((uintptr_t)scratch) & 15) == 0, "scratch must be 16-byte aligned");
   const int B = p->B, T = p->T, K = p->K, F = p->F;
   const int C = dgc_div_up(T, CH);
@@ -732,14 +828,24 @@ int32_t dgc_harmonic_prepare(dgc_ctx *ctx, const dgc_harmonic_params *p, const f
   float *anchors = scratch + (((uint64_t)B * T + 3) & ~3ull);
   uint64_t lanes = (uint64_t)B * C * K;
   unsigned long long *sums = reinterpret_cast<unsigned long long *>(anchors + ((lanes + 1) & ~1ull));
-  float *env = reinterpret_cast<float *>(sums + lanes);
+  const uint64_t sum_words = lanes > 2 * (uint64_t)B * C ? lanes : 2 * (uint64_t)B * C;
+  float *env = reinterpret_cast<float *>(sums + sum_words);
   uint32_t *anchors_q = reinterpret_cast<uint32_t *>(env + (((uint64_t)B * T + 3) & ~3ull));
   const bool want_env = uv_dev && gain_dev && extra;
   const float2 *rowtab = dgc_ctx_row_table(ctx, F, T);
   if (!rowtab) return DGC_ERR_CUDA;
   const float sr = p->sample_rate, rsr = 1.0f / sr;
+  // FUNDAMENTAL mode keeps two small arrays in the chunk-sum area: per-chunk totals [B][C], their prefix [B][C]
+  unsigned long long *fund_sum = sums, *fund_prefix = sums + (uint64_t)B * C;
   if (already_prepared) {
     // nothing to launch
+  } else if (p->phase_mode == DGC_PHASE_FUNDAMENTAL) {
+    f0_track_fund_kernel<<<dim3(dgc_div_up(C, 4), B), 128, 0, ctx->stream>>>(rowtab, f0_dev, B, T, F, sr, rsr, f0t, uv_dev,
+                                                                          gain_dev, p->harmonic_scale,
+                                                                          want_env ? env : nullptr, fund_sum);
+    DGC_LAUNCHED(ctx, "f0_track_fund");
+    fund_scan_kernel<<<B, FSCAN_THREADS, 0, ctx->stream>>>(fund_sum, C, fund_prefix);
+    DGC_LAUNCHED(ctx, "fund_scan");
   } else {
   f0_track_kernel<<<dim3(dgc_div_up(T, 256), B), 256, 0, ctx->stream>>>(rowtab, f0_dev, B, T, F, f0t, uv_dev, gain_dev,
                                                                          p->harmonic_scale, want_env ? env : nullptr);
@@ -759,6 +865,7 @@ int32_t dgc_harmonic_prepare(dgc_ctx *ctx, const dgc_harmonic_params *p, const f
     extra->f0t = f0t;
     extra->env = want_env ? env : nullptr;
     extra->anchors_q = p->phase_mode == DGC_PHASE_SCAN ? anchors_q : nullptr;
+    extra->fund = p->phase_mode == DGC_PHASE_FUNDAMENTAL ? fund_prefix : nullptr;
   }
   *play_out = play;
   *anchors_out = anchors;
@@ -777,7 +884,8 @@ DGC_EXPORT int32_t dgc_harmonic_render(dgc_ctx *ctx, const dgc_harmonic_params *
   int32_t rc = dgc_harmonic_prepare(ctx, p, f0_dev, scratch, &play, &anchors, uv_dev, gain_dev, &extra);
   if (rc != DGC_OK) return rc;
   const int K = p->K;
-  if (p->phase_mode == DGC_PHASE_SCAN) {
+  if (p->phase_mode == DGC_PHASE_SCAN || p->phase_mode == DGC_PHASE_FUNDAMENTAL) {
+    DGC_REQUIRE(ctx, extra.env, "internal: the fixed-point render needs the envelope track");
     const float2 *rowtab = dgc_ctx_row_table(ctx, p->F, p->T);
     if (!rowtab) return DGC_ERR_CUDA;
 #define RENDERQ(LPC, P) launch_render_q<LPC, P, 0>(ctx, *p, rowtab, extra, amps_dev, nullptr, audio_dev)

@@ -67,10 +67,13 @@ __device__ __forceinline__ float partial_number(float kf0, int step_times_i) { r
 // nothing is launched, only the pointers are returned.
 // When uv_dev and gain_dev are given it also writes the per-sample output envelope
 // env[b][n] = lerp(gain) * lerp(uv) * harmonic_scale, and in SCAN mode the anchors as Q0.32 turns.
+// In FUNDAMENTAL mode no per-partial anchors exist (anchors_out is not written): extra->fund replaces them.
 struct dgc_harmonic_extra {
   const float *f0t = nullptr;          // [B][T] per-sample fundamental
   const float *env = nullptr;          // [B][T] or nullptr
   const uint32_t *anchors_q = nullptr; // [B][C][K] (SCAN mode only) or nullptr
+  const unsigned long long *fund = nullptr;  // [B][C] running sum of f0 / sr at every chunk start, Q0.64
+                                             // (FUNDAMENTAL mode only): partial k starts chunk c at k * fund[b][c]
 };
 int32_t dgc_harmonic_prepare(dgc_ctx *ctx, const dgc_harmonic_params *p, const float *f0_dev, float *scratch,
                              const float **play_out, const float **anchors_out, const float *uv_dev = nullptr,

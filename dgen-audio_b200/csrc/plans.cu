@@ -27,6 +27,7 @@ int32_t ensure_stage(dgc_ctx *ctx, uint64_t nfloats) {
   if (ctx->stage_dev) {
     cudaStreamSynchronize(ctx->stream);
     cudaFree(ctx->stage_dev);
+    ctx->buffer_generation++;
     ctx->stage_dev = nullptr;
     ctx->stage_floats = 0;
   }
@@ -198,6 +199,7 @@ static int32_t hn_host_enqueue(dgc_ctx *ctx, const dgc_hn_step *s, const float *
         cudaStreamSynchronize(ctx->stream);
         cudaStreamSynchronize(ctx->copy_stream);
         cudaFree(ctx->pipe_in[slot]);
+        ctx->buffer_generation++;
         ctx->pipe_in[slot] = nullptr;
         ctx->pipe_in_floats[slot] = 0;
       }

@@ -294,7 +294,8 @@ __global__ void __launch_bounds__(128)
 harmonic_bwd_q_kernel(dgc_harmonic_params prm, float rsr, const float2 *__restrict__ rowtab,
                       const int *__restrict__ ranges, const float *__restrict__ f0t, const float *__restrict__ env,
                       const float *__restrict__ amps, const uint32_t *__restrict__ anchors_q,
-                      const float *__restrict__ g_audio, float *__restrict__ part_lo, float *__restrict__ part_hi) {
+                      const unsigned long long *__restrict__ fund, const float *__restrict__ g_audio,
+                      float *__restrict__ part_lo, float *__restrict__ part_hi) {
   constexpr int G = 128 / LPC;
   constexpr float THREE_PI = 9.42477796076938f;
   const int B = prm.B, T = prm.T, K = prm.K, F = prm.F;
@@ -335,11 +336,14 @@ harmonic_bwd_q_kernel(dgc_harmonic_params prm, float rsr, const float2 *__restri
 #pragma unroll
       for (int off = LPC / 2; off > 0; off >>= 1) part += __shfl_xor_sync(0xffffffffu, part, off);
       if (len > 0) {
+        // chunk anchors: the forward's table, or k times the fundamental's running sum (FUNDAMENTAL mode)
         const uint32_t *anc = anchors_q + ((size_t)b * C + c0) * K;
+        const unsigned long long fa = fund ? fund[(size_t)b * C + c0] : 0ull;
 #pragma unroll
         for (int i = 0; i < P; ++i) {
           int k = j + LPC * i;
-          q[i] = (k < K ? anc[k] : 0u) + 0x100u + (uint32_t)(k + 1) * part;
+          const uint32_t a0 = fund ? (uint32_t)(((unsigned long long)(k + 1) * fa) >> 32) : (k < K ? anc[k] : 0u);
+          q[i] = a0 + 0x100u + (uint32_t)(k + 1) * part;
         }
       }
     }
@@ -348,10 +352,12 @@ harmonic_bwd_q_kernel(dgc_harmonic_params prm, float rsr, const float2 *__restri
       const int n = live ? s0 + m : 0;
       if (live && (n % CH) == 0) {  // the forward re-anchors at every chunk boundary
         const uint32_t *anc = anchors_q + ((size_t)b * C + n / CH) * K;
+        const unsigned long long fa = fund ? fund[(size_t)b * C + n / CH] : 0ull;
 #pragma unroll
         for (int i = 0; i < P; ++i) {
           int k = j + LPC * i;
-          q[i] = (k < K ? anc[k] : 0u) + 0x100u;
+          const uint32_t a0 = fund ? (uint32_t)(((unsigned long long)(k + 1) * fa) >> 32) : (k < K ? anc[k] : 0u);
+          q[i] = a0 + 0x100u;
         }
       }
       const float fr = rowtab[n].y, omf = __fsub_rn(1.0f, fr);
@@ -411,7 +417,7 @@ void launch_hbwd_q(dgc_ctx *ctx, const dgc_harmonic_params &p, const float2 *row
                    const dgc_harmonic_extra &x, const float *amps, const float *g_audio, float *pl, float *ph) {
   constexpr int G = 128 / LPC;
   harmonic_bwd_q_kernel<LPC, P><<<dim3(dgc_div_up(p.F, G), p.B), 128, 0, ctx->stream>>>(
-      p, 1.0f / p.sample_rate, rowtab, ranges, x.f0t, x.env, amps, x.anchors_q, g_audio, pl, ph);
+      p, 1.0f / p.sample_rate, rowtab, ranges, x.f0t, x.env, amps, x.anchors_q, x.fund, g_audio, pl, ph);
 }
 
 template <int LPC, int P>
@@ -493,7 +499,9 @@ static int32_t harmonic_render_bwd_impl(dgc_ctx *ctx, const dgc_harmonic_params 
   const size_t n = (size_t)p->F * p->B * p->K;
   float *pl = scratch + ((dgc_harmonic_scratch_floats(p) + 3) & ~3ull), *ph = pl + n;
   const int K = p->K;
-  const bool fixed_point = p->phase_mode == DGC_PHASE_SCAN && extra.anchors_q && extra.env;
+  const bool fixed_point = extra.env && ((p->phase_mode == DGC_PHASE_SCAN && extra.anchors_q) ||
+                                         (p->phase_mode == DGC_PHASE_FUNDAMENTAL && extra.fund));
+  DGC_REQUIRE(ctx, fixed_point || p->phase_mode != DGC_PHASE_FUNDAMENTAL, "internal: fundamental mode without its tracks");
   const float2 *rowtab = fixed_point ? dgc_ctx_row_table(ctx, p->F, p->T) : nullptr;
   if (fixed_point && !rowtab) return DGC_ERR_CUDA;
 #define HBWD(LPC, P)                                                                                                  \

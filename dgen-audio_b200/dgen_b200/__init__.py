@@ -12,7 +12,7 @@ PKG_DIR = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 LIB_PATH = os.path.join(PKG_DIR, "libdgen_cuda.so")
 
 DGC_OK = 0
-PHASE_DETERMINISTIC, PHASE_SEQUENTIAL, PHASE_SCAN = 0, 1, 2
+PHASE_DETERMINISTIC, PHASE_SEQUENTIAL, PHASE_SCAN, PHASE_FUNDAMENTAL = 0, 1, 2, 3
 MSS_MAX_SCALES = 8
 
 
@@ -400,9 +400,9 @@ class Context:
         return out
 
     # ---- linear recurrences -------------------------------------------------------------------
-    def onepole_fwd(self, x, a):
+    def onepole_fwd(self, x, a, out=None):
         B, T = x.shape
-        y = self._empty(B, T)
+        y = self._empty(B, T) if out is None else out
         self.check(self.lib.dgc_onepole_fwd(self.h, _ptr(x), B, T, a, _ptr(y)))
         return y
 

@@ -188,9 +188,14 @@ class TrainLog:
 # ---- flat parameter vector <-> named snapshots ----------------------------------------------------------------
 def snapshots_from_flat(layout, flat, K):
     """layout: [(name, offset, shape)] of the flat parameter vector with W0.. / b0.. trunk + head and "ir".
-    Names follow the reference decoder (Examples/HarmonicE2E/Model.swift:122-137): trunk layers W1/b1 .. (1-based),
-    the head split into W_harm / b_harm (first K columns) and W_noise / b_noise (the rest); the learnable impulse
-    response is stored as "ir"."""
+    Only the CONTAINER follows the reference (the JSON layout and file names of Examples/HarmonicE2E/Checkpoint.swift,
+    trunk layers named W1/b1 .. 1-based, the harmonic head W_harm / b_harm as in Examples/HarmonicE2E/Model.swift:122-137);
+    the parameter SET is this model's own.  The reference decoder has four heads -- W_harm, W_gain, W_noise (a
+    [hidden, 1] noise-gain head) and W_noiseFilter (FIR taps through tanh and an L1 normalisation) -- while the
+    benchmark configuration's controller maps to harmonic amplitudes and 65 noise-band magnitudes only.  The band
+    head is therefore stored as W_bands / b_bands (the rest of the head's columns) so that it cannot be mistaken
+    for the reference's W_noise, and the learnable impulse response as "ir".  A checkpoint written by the
+    reference trainer does not load into this model, and the loader says so by name."""
     flat = np.asarray(flat, np.float32)
     t = {n: flat[o:o + int(np.prod(s))].reshape(s) for n, o, s in layout}
     n_lin = sum(1 for n in t if n.startswith("W"))
@@ -200,14 +205,26 @@ def snapshots_from_flat(layout, flat, K):
         out.append(("b%d" % (i + 1), t["b%d" % i].shape, t["b%d" % i]))
     Wh, bh = t["W%d" % (n_lin - 1)], t["b%d" % (n_lin - 1)]
     out += [("W_harm", Wh[:, :K].shape, Wh[:, :K]), ("b_harm", (K,), bh[:K]),
-            ("W_noise", Wh[:, K:].shape, Wh[:, K:]), ("b_noise", (bh.size - K,), bh[K:])]
+            ("W_bands", Wh[:, K:].shape, Wh[:, K:]), ("b_bands", (bh.size - K,), bh[K:])]
     if "ir" in t:
         out.append(("ir", t["ir"].shape, t["ir"]))
     return out
 
 
 def flat_from_snapshots(layout, named, K):
-    """Inverse of snapshots_from_flat: named = {name: array} as read_model_state returns."""
+    """Inverse of snapshots_from_flat: named = {name: array} as read_model_state returns.  Raises ValueError on a
+    missing tensor, on a tensor the model does not have, and on any shape that differs from the model's."""
+    expect = {n: tuple(int(v) for v in s) for n, s, _ in
+              snapshots_from_flat(layout, np.zeros(max(o + int(np.prod(s)) for _, o, s in layout), np.float32), K)}
+    missing = sorted(set(expect) - set(named))
+    extra = sorted(set(named) - set(expect))
+    if missing or extra:
+        raise ValueError("checkpoint does not hold this model's parameter set: missing %s, unexpected %s"
+                         % (missing or "none", extra or "none"))
+    for n, shp in expect.items():
+        got = tuple(int(v) for v in np.asarray(named[n]).shape)
+        if got != shp and not (len(shp) == 1 and got == (1,) + shp):   # biases may be stored as [1, n]
+            raise ValueError("checkpoint tensor %s has shape %s, the model needs %s" % (n, got, shp))
     total = max(o + int(np.prod(s)) for _, o, s in layout)
     flat = np.zeros(total, np.float32)
     n_lin = sum(1 for n, _, _ in layout if n.startswith("W"))
@@ -218,9 +235,9 @@ def flat_from_snapshots(layout, named, K):
         elif n[0] in "Wb" and int(n[1:]) < n_lin - 1:
             src = named["%s%d" % (n[0], int(n[1:]) + 1)]
         elif n[0] == "W":
-            src = np.concatenate([named["W_harm"], named["W_noise"]], axis=1)
+            src = np.concatenate([named["W_harm"], named["W_bands"]], axis=1)
         else:
-            src = np.concatenate([named["b_harm"], named["b_noise"]])
+            src = np.concatenate([np.ravel(named["b_harm"]), np.ravel(named["b_bands"])])
         src = np.asarray(src, np.float32)
         if src.size != cnt:
             raise ValueError("checkpoint tensor for %s has %d values, the model needs %d" % (n, src.size, cnt))

@@ -4,7 +4,9 @@ optimizer.step), with every tensor resident in HBM and every operation a libdgen
 
 Graph (rows of all [F*B, *] matrices are ordered [control frame][voice], the layout of the control tables):
     h = tanh(tanh(tanh(X W1 + b1) W2 + b2) W3 + b3);  z = h Wh + bh                     (Model.swift:96-101)
-    amps = softplus(z[:, :K]) / (sum + 1e-6);  bands = sigmoid(z[:, K:])                 (Model.swift:102-106)
+    amps = softplus(z[:, :K]) / (sum + 1e-6)                                             (Model.swift:102-106)
+    bands = sigmoid(z[:, K:])   (this configuration's own band head; the reference decoder has gain, noise-gain and
+                                 tap heads instead, Model.swift:107-113)
     taps = bands Wfs^T;  dry = harmonic(f0, amps, gain, uv) + fir(noise, taps, noise_gain)  (Synth.swift:47-102)
     out  = dry + partitioned_convolve(dry, ir)                                           (learnable 1 s IR)
     loss = multi-scale spectral L1 (lin + log) of out against the target                 (Trainer.swift:538-588)
@@ -176,8 +178,9 @@ class HarmonicModel:
         return self.grads
 
     def snapshots(self):
-        """Named parameter tensors in the reference decoder's naming (Examples/HarmonicE2E/Model.swift:122-137), ready
-        for runfiles.write_model_state."""
+        """Named parameter tensors for runfiles.write_model_state: the reference's checkpoint container and its names
+        for the trunk and the harmonic head (Examples/HarmonicE2E/Model.swift:122-137); the band head and the impulse
+        response are this model's own (W_bands / b_bands, ir)."""
         from . import runfiles
         return runfiles.snapshots_from_flat(self.layout, self.params.cpu().numpy(), self.K)
 

@@ -102,7 +102,13 @@ enum {
   /* frame-parallel: increments are summed exactly (64-bit fixed point) by a prefix scan across
    * chunks of 64 frames; inside a chunk the single-precision recurrence is followed.  Differs from
    * SEQUENTIAL only by the rounding drift the serial recurrence accumulates across chunks. */
-  DGC_PHASE_SCAN = 2
+  DGC_PHASE_SCAN = 2,
+  /* frame-parallel, one scan per VOICE instead of one per partial: the harmonic bank's partials are multiples
+   * k * f0 of one fundamental, so the running sum A[n] = sum_{m<n} f0[m]/sr is kept once per voice in 64-bit
+   * fixed point and partial k reads its phase as k * A[n] (mod 1), an exact integer product.  Against SCAN
+   * this also drops the rounding of every partial's own increment fl(fl(k*f0)/sr); measured against the
+   * step-by-step recurrence both stay inside the 1e-4 sample tolerance (harmonic bank only). */
+  DGC_PHASE_FUNDAMENTAL = 3
 };
 
 /* Constant-frequency bank summed to mono: audio[n] = sum_k sin(phase_k[n]*2pi) * amp[k].
@@ -118,7 +124,7 @@ typedef struct dgc_harmonic_params {
   int32_t F;            /* control frames */
   float sample_rate;
   float harmonic_scale; /* harmonicPathScale */
-  int32_t phase_mode;   /* DGC_PHASE_SEQUENTIAL or DGC_PHASE_SCAN */
+  int32_t phase_mode;   /* DGC_PHASE_SEQUENTIAL, DGC_PHASE_SCAN or DGC_PHASE_FUNDAMENTAL */
   int32_t accumulate;   /* 0: audio = harmonics ; 1: audio += harmonics */
 } dgc_harmonic_params;
 
@@ -184,8 +190,10 @@ int32_t dgc_temporal_grad_scan(dgc_ctx *ctx, const float *g_dev, int32_t E, int3
 /* Gradient of the noise branch w.r.t. the tap table: g_taps [F][B][taps] from g_audio [B][T]. */
 int32_t dgc_fir_noise_bwd(dgc_ctx *ctx, const dgc_fir_params *p, const float *noise_dev, const float *noise_gain_dev,
                           const float *g_audio_dev, float *g_taps_dev);
-/* Controller output heads (Examples/HarmonicE2E/Model.swift:102-106): z [M][K+NB] ->
- * amps [M][K] = softplus(z[:, :K]) / (row sum + 1e-6), bands [M][NB] = sigmoid(z[:, K:]); and backward. */
+/* Controller output heads: z [M][K+NB] -> amps [M][K] = softplus(z[:, :K]) / (row sum + 1e-6), the reference
+ * decoder's harmonic head (Examples/HarmonicE2E/Model.swift:102-106), and bands [M][NB] = sigmoid(z[:, K:]), the
+ * band-magnitude head of the synthetic harmonic+noise configuration (the reference decoder emits FIR taps and two
+ * gains instead, Model.swift:107-113); and backward. */
 int32_t dgc_hn_heads_fwd(dgc_ctx *ctx, const float *z_dev, int32_t M, int32_t K, int32_t NB, float *amps_dev,
                          float *bands_dev);
 int32_t dgc_hn_heads_bwd(dgc_ctx *ctx, const float *z_dev, const float *g_amps_dev, const float *g_bands_dev,
@@ -207,7 +215,9 @@ int32_t dgc_onepole_fwd(dgc_ctx *ctx, const float *x_dev, int32_t B, int32_t T, 
  *   set-up    the first call on each device looks up the array's device address
  *             (cudaGetSymbolAddress) with that device current; make that first call before any
  *             stream capture begins.  Later calls only launch kernels on `cuda_stream`
- *             (a cudaStream_t; NULL = default stream) of the CURRENT device.
+ *             (a cudaStream_t; NULL = default stream) of the CURRENT device and take no lock (the
+ *             resolved address is read with one atomic load).
+ *   in place  x_dev == y_dev is allowed: every thread reads its run of samples before it writes it.
  *   sharing   all calls on a device use the same array, which keeps the last call's contents; the
  *             filter overwrites every slot before reading it, so nothing needs clearing, but two
  *             calls that overlap on the GPU (different streams, no ordering) race: serialise them. */
@@ -421,7 +431,12 @@ int32_t dgc_phase_vocoder(dgc_ctx *ctx, const float *re_dev, const float *im_dev
  * (Sources/DGenLazy/Backward.swift:225, Sources/DGenLazy/Realize.swift:285-290, Sources/DGenLazy/LazyGraph.swift:171-234).
  * The context must be bound to a non-default stream; run the step once before recording it, so that nothing inside
  * the recording allocates; values passed by value are frozen into the recording -- refill input buffers in place and
- * use dgc_adam_step_counted.  dgc_graph_end reports an invalidated recording as DGC_ERR_CUDA with the reason. */
+ * use dgc_adam_step_counted.  dgc_graph_end reports an invalidated recording as DGC_ERR_CUDA with the reason.
+ * A recording holds the addresses of the context's own buffers (scratch, staging, transposed operands).  If a
+ * call made AFTER the recording needs a larger one, the context reallocates it; dgc_graph_launch notices and
+ * returns DGC_ERR_INVALID without launching anything: record the step again.
+ * dgc_allreduce_sum on a context with a communicator is refused (DGC_ERR_INVALID) between dgc_graph_begin and
+ * dgc_graph_end: record forward + backward, exchange call by call, record the update as a second step. */
 typedef struct dgc_graph dgc_graph;
 int32_t dgc_graph_begin(dgc_ctx *ctx);
 int32_t dgc_graph_end(dgc_ctx *ctx, dgc_graph **out);

@@ -85,9 +85,38 @@ def test_harmonic_noise_render_full_config_both_phase_modes(ctx):
     err_seq = np.abs(got - want).max()
     got2, _ = _render_both(ctx, d, dgen_b200.PHASE_SCAN)
     err_scan = np.abs(got2 - want).max()
-    print("max abs err: sequential %.3g, scan %.3g" % (err_seq, err_scan))
+    got3, _ = _render_both(ctx, d, dgen_b200.PHASE_FUNDAMENTAL)
+    err_fund = np.abs(got3 - want).max()
+    print("max abs err: sequential %.3g, scan %.3g, fundamental %.3g" % (err_seq, err_scan, err_fund))
     assert err_seq < 2e-5
     assert err_scan < 1e-4  # the stated forward tolerance
+    assert err_fund < 1e-4  # one scan per voice: also drops the rounding of each partial's own increment
+
+
+@pytest.mark.parametrize("shape", [dict(B=2, T=4096, K=100, F=64), dict(B=3, T=5000, K=7, F=33),
+                                   dict(B=1, T=1000, K=1, F=2), dict(B=2, T=2048, K=130, F=40),
+                                   dict(B=1, T=640, K=300, F=11), dict(B=2, T=70001, K=100, F=300)])
+def test_harmonic_render_fundamental_mode_matches_oracle(ctx, shape):
+    """The per-voice scan of the fundamental: partial k reads its phase as k times one 64-bit running sum."""
+    d = wl.harmonic_noise_inputs(13, sr=16000.0, **shape)
+    got, want = _render_both(ctx, d, dgen_b200.PHASE_FUNDAMENTAL, noise=False)
+    assert np.abs(got - want).max() < 1e-4
+    got_scan, _ = _render_both(ctx, d, dgen_b200.PHASE_SCAN, noise=False)
+    assert np.abs(got - got_scan).max() < 1e-4
+
+
+def test_fundamental_mode_out_of_range_f0(ctx):
+    """Fundamentals at and above the sample rate, zero and negative ones: the phase stays defined (fraction of
+    f0 / sr), partials above Nyquist are masked exactly as in the other modes."""
+    d = wl.harmonic_noise_inputs(17, B=4, T=4096, K=20, F=32, sr=16000.0)
+    d["f0"][:, 1] = 0.0
+    d["f0"][:, 2] *= 40.0          # up to and beyond the sample rate
+    d["f0"][::2, 3] = -50.0
+    got, want = _render_both(ctx, d, dgen_b200.PHASE_FUNDAMENTAL, noise=False)
+    assert np.isfinite(got).all()
+    assert np.abs(got[:2] - want[:2]).max() < 1e-4
+    got_scan, _ = _render_both(ctx, d, dgen_b200.PHASE_SCAN, noise=False)
+    assert np.abs(got - got_scan).max() < 2e-4
 
 
 def test_fir_noise_ragged_and_short(ctx):

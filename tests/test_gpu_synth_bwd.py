@@ -39,6 +39,10 @@ def test_harmonic_render_backward(ctx, shape):
     (out * to.t64(g)).sum().backward()
     got = ctx.harmonic_render_bwd(dev(d["f0"]), dev(d["uv"]), dev(d["amps"]), dev(d["gain"]), dev(g), d["T"], d["sr"])
     assert rel_err(got.cpu().numpy(), amps.grad.numpy()) < 1e-3
+    # the same gradient walking the phases of the per-voice scan of the fundamental
+    got = ctx.harmonic_render_bwd(dev(d["f0"]), dev(d["uv"]), dev(d["amps"]), dev(d["gain"]), dev(g), d["T"], d["sr"],
+                                  phase_mode=dgen_b200.PHASE_FUNDAMENTAL)
+    assert rel_err(got.cpu().numpy(), amps.grad.numpy()) < 1e-3
 
 
 @pytest.mark.parametrize("B,T,F,NT", [(2, 3000, 50, 257), (1, 1000, 5, 17), (2, 2049, 300, 64)])

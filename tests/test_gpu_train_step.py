@@ -109,7 +109,7 @@ def test_checkpoint_round_trip_through_the_reference_file_format(tmp_path):
     run = rf.RunDirectories(str(tmp_path / "run"))
     path = rf.write_model_state(run.checkpoints, a.step_index, a.snapshots())
     step, named = rf.read_model_state(path)
-    assert step == 2 and set(named) == {"W1", "b1", "W2", "b2", "W3", "b3", "W_harm", "b_harm", "W_noise", "b_noise", "ir"}
+    assert step == 2 and set(named) == {"W1", "b1", "W2", "b2", "W3", "b3", "W_harm", "b_harm", "W_bands", "b_bands", "ir"}
     b = tr.HarmonicModel(ctx, B, T, seed=99, **kw)
     b.load_snapshots(named)
     la, lb = float(a.forward(*args).cpu()[0]), float(b.forward(*args).cpu()[0])

@@ -71,7 +71,7 @@ def test_checkpoint_files_and_parameter_names(tmp_path):
     off += 7
     flat = np.arange(off, dtype=f32) / f32(8)
     snaps = rf.snapshots_from_flat(layout, flat, K)
-    assert [n for n, _, _ in snaps] == ["W1", "b1", "W2", "b2", "W_harm", "b_harm", "W_noise", "b_noise", "ir"]
+    assert [n for n, _, _ in snaps] == ["W1", "b1", "W2", "b2", "W_harm", "b_harm", "W_bands", "b_bands", "ir"]
     p = rf.write_model_state(run.checkpoints, 12, snaps)
     assert os.path.basename(p) == "model_step_00000012.json"
     doc = json.load(open(p))
@@ -81,6 +81,19 @@ def test_checkpoint_files_and_parameter_names(tmp_path):
     step, named = rf.read_model_state(p)
     assert step == 12 and np.array_equal(rf.flat_from_snapshots(layout, named, K), flat)
     assert os.path.basename(rf.write_best_model_state(run.checkpoints, 3, snaps)) == "model_best.json"
+    # a checkpoint with the REFERENCE decoder's heads (W_gain, W_noise [hidden, 1], W_noiseFilter) is refused by name,
+    # a tensor of the wrong shape is refused too -- never concatenated into the wrong head
+    import pytest
+    ref_like = dict(named)
+    ref_like.pop("W_bands"); ref_like.pop("b_bands")
+    ref_like.update(W_gain=np.zeros((H, 1), f32), b_gain=np.zeros((1, 1), f32), W_noise=np.zeros((H, 1), f32),
+                    b_noise=np.zeros((1, 1), f32), W_noiseFilter=np.zeros((H, NB), f32), b_noiseFilter=np.zeros((1, NB), f32))
+    with pytest.raises(ValueError, match="W_bands"):
+        rf.flat_from_snapshots(layout, ref_like, K)
+    bad = dict(named)
+    bad["W_harm"] = np.zeros((K, H), f32)                 # transposed: same size, wrong shape
+    with pytest.raises(ValueError, match="shape"):
+        rf.flat_from_snapshots(layout, bad, K)
 
 
 def test_train_log_files(tmp_path):

@@ -49,3 +49,26 @@ def test_static_scratch_onepole_rejects_oversize_and_null():
     assert rc == -1 and b"null" in err.value
     rc = lib.dgc_onepole_fwd_static(None, x.data_ptr(), 1, 0, 0.5, x.data_ptr(), None, 0)
     assert rc == -1
+
+
+def test_static_scratch_onepole_at_exactly_the_slot_limit_and_in_place():
+    """B * ceil(T / 2048) == 32768 chunk slots exactly: the last slot of both halves of the array is used.
+    One slot more is refused.  The call runs in place (x_dev == y_dev), which the entry point allows."""
+    import torch
+    lib = dgen_b200.load()
+    ctx = dgen_b200.Context(0)
+    err = C.create_string_buffer(256)
+    stream = torch.cuda.current_stream().cuda_stream
+    B, T = 512, 64 * 2048 - 5                      # 64 chunks per voice (the last one ragged) x 512 voices
+    assert B * ((T + 2047) // 2048) == 32768
+    x = torch.randn(B, T, device="cuda")
+    want = ctx.onepole_fwd(x, 0.95)
+    buf = x.clone()
+    rc = lib.dgc_onepole_fwd_static(stream, buf.data_ptr(), B, T, C.c_float(0.95), buf.data_ptr(), err, 256)
+    assert rc == 0, err.value.decode()
+    torch.cuda.synchronize()
+    scale = max(1.0, float(want.abs().max()))
+    assert float((buf - want).abs().max()) <= 1e-5 * scale
+    rc = lib.dgc_onepole_fwd_static(stream, x.data_ptr(), B, T + 2048, C.c_float(0.95), buf.data_ptr(), err, 256)
+    assert rc == -1 and b"exceeds" in err.value    # 65 chunks per voice: 33280 slots
+    ctx.close()
