@@ -50,7 +50,8 @@ def config_json(n_gpus):
             "voices_per_gpu": CFG["B"], "frames": CFG["T"], "harmonics": CFG["K"], "control_frames": CFG["F"],
             "sample_rate": CFG["sr"], "noise_bands": CFG["nbands"], "fir_taps": CFG["taps"],
             "fft_sizes": list(SIZES), "overlap": 0.75, "global_voices": CFG["B"] * n_gpus,
-            "phase_mode": PHASE["mode"], "sharding": "voices across GPUs, no collective",
+            "phase_mode": PHASE["mode"], "sharding": "voices across GPUs, no collective in the forward + loss step "
+                                                     "(the train block has the gradient all-reduce)",
             "step_mode": STEP_MODE["mode"],
             "l2": "L2 flushed (512 MiB write) between timed steps"}
 
@@ -171,75 +172,247 @@ def run_reference(args, rank, world):
 # --------------------------------------------------------------------------------------------------
 # GPU arm
 # --------------------------------------------------------------------------------------------------
+def measured_peaks():
+    try:
+        return json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        return {}
+
+
+def stage_rooflines(B, T, stage_ms, sm_mhz, sm_count, hbm_peak):
+    """Per stage: the bound that applies to it and the fraction reached, the HBM figure beside it.
+    Algorithmic work per launch (fp32 = 4 bytes; B voices, T frames, K partials, F control rows):
+      harmonic_render  one sine per (voice, frame, partial) on the special-function lanes; bytes 4 (B F (K+2) + B T)
+      fir_noise        2 x taps multiply-adds per sample for the two control rows a sample is interpolated between
+                       (4 taps flops per sample); bytes 4 (B T + B F nbands + B T): noise in, band magnitudes in, out
+      mss_loss_fwd     one complex transform of N points per window carries both signals: 5 N log2 N flops per
+                       window, H = ceil(T / hop) windows per voice and scale; bytes 2 x 4 B T per scale
+      bands_to_taps    bytes 4 B F (nbands + taps): a memory-bound map (26 flops per byte moved)"""
+    K, F, taps, nbands = CFG["K"], CFG["F"], CFG["taps"], CFG["nbands"]
+    clk = sm_mhz * 1e6
+    fp32_peak = sm_count * FP32_LANES_PER_SM * 2 * clk / 1e12          # TFLOP/s, one FMA per lane and clock
+    sfu_peak = sm_count * SFU_LANES_PER_SM * clk / 1e9                 # G results / s
+    alg_bytes = {"harmonic_render": 4 * (B * F * (K + 2) + B * T),
+                 "fir_noise": 4 * (B * T + B * F * nbands + B * T),
+                 "bands_to_taps": 4 * (B * F * nbands + B * F * taps),
+                 "mss_loss_fwd": 2 * 4 * B * T * len(SIZES)}
+    fft_flops = 0.0
+    for n in SIZES:
+        if n > T:
+            continue
+        hop = max(1, n // 4)
+        fft_flops += 5.0 * n * np.log2(n) * ((T + hop - 1) // hop) * B
+    work = {"harmonic_render": ("sfu", B * T * K / 1e9, sfu_peak, "G sin/s"),
+            "fir_noise": ("fp32", 4.0 * taps * B * T / 1e12, fp32_peak, "TFLOP/s"),
+            "mss_loss_fwd": ("fp32", fft_flops / 1e12, fp32_peak, "TFLOP/s"),
+            "bands_to_taps": ("hbm", alg_bytes["bands_to_taps"] / 1e9, hbm_peak, "GB/s")}
+    out, bound_time_ms = {}, 0.0
+    for name, ms in stage_ms.items():
+        kind, amount, peak, unit = work[name]
+        ach = amount / (ms * 1e-3)
+        gbs = alg_bytes[name] / (ms * 1e-3) / 1e9
+        out[name] = {"ms": ms, "bound": kind, "achieved": ach, "peak": peak, "unit": unit, "frac": ach / peak,
+                     "hbm": {"algorithmic_bytes": alg_bytes[name], "achieved_gbs": gbs, "frac": gbs / hbm_peak}}
+        bound_time_ms += amount / peak * 1e3
+    return out, alg_bytes, bound_time_ms
+
+
+def ncu_traffic(stage, B):
+    """DRAM bytes (read + write) of the stage's kernels per launch, from the committed ncu summary
+    profiles/fwd_loss_dram_traffic.md, which states per kernel the bytes per voice and the hash of the kernel
+    sources it was captured from.  None when the summary is absent or was captured from other sources."""
+    import hashlib
+    import re
+    path = os.path.join(ROOT, "profiles", "fwd_loss_dram_traffic.md")
+    try:
+        text = open(path).read()
+    except Exception:
+        return None, "no ncu traffic summary committed"
+    h = hashlib.sha256()
+    csrc = os.path.join(ROOT, "dgen-audio_b200", "csrc")
+    for f in sorted(os.listdir(csrc)):
+        h.update(open(os.path.join(csrc, f), "rb").read())
+    m = re.search(r"sources_sha16:\s*([0-9a-f]{16})", text)
+    if not m or m.group(1) != h.hexdigest()[:16]:
+        return None, "the committed ncu summary was captured from other kernel sources"
+    m = re.search(r"^traffic_bytes_per_voice\s+%s\s+([0-9.eE+]+)" % re.escape(stage), text, re.M)
+    if not m:
+        return None, "stage not in the ncu summary"
+    return float(m.group(1)) * B, "profiles/fwd_loss_dram_traffic.md"
+
+
+class FwdLoss:
+    """The harmonic+noise forward + multi-scale loss step on one GPU for B voices: device buffers, the staged
+    single-stream sequence (per-stage times, cross-check) and the composite call (the timed step)."""
+
+    def __init__(self, ctx, B, seed, nsets=1):
+        import ctypes as C
+        import torch
+        import dgen_b200
+        from dgen_b200 import workloads as wl
+        self.ctx, self.B, self.torch, self.C, self.dg = ctx, B, torch, C, dgen_b200
+        cfg = dict(CFG, B=B)
+        T, K, F, sr = cfg["T"], cfg["K"], cfg["F"], cfg["sr"]
+        self.cfg = cfg
+        dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+        self.host = wl.harmonic_noise_inputs(seed, **cfg)
+        tg = wl.harmonic_noise_inputs(seed + 1, **cfg)
+        self.sets = [{k: dev(v) for k, v in self.host.items() if isinstance(v, np.ndarray)}]
+        for _ in range(1, nsets):
+            self.sets.append({k: v.clone() for k, v in self.sets[0].items()})
+        self.D = self.sets[0]
+        G = {k: dev(v) for k, v in tg.items() if isinstance(v, np.ndarray)}
+        self.audio = torch.empty(B, T, device="cuda")
+        self.loss = torch.zeros(1, dtype=torch.float64, device="cuda")
+        self.mss = dgen_b200.mss_params(B, T, SIZES)
+        mode = {"scan": dgen_b200.PHASE_SCAN, "sequential": dgen_b200.PHASE_SEQUENTIAL,
+                "fundamental": dgen_b200.PHASE_FUNDAMENTAL}[PHASE["mode"]]
+        self.hp = dgen_b200.HarmonicParams(B, T, K, F, sr, 1.0, mode, 0)
+        self.fp = dgen_b200.FirParams(B, T, F, cfg["taps"], 0.12, 1)
+        self.taps_buf = torch.empty(F, B, cfg["taps"], device="cuda")
+        self.st = dgen_b200.HnStep()
+        self.st.harm, self.st.fir, self.st.mss, self.st.nbands = self.hp, self.fp, self.mss, cfg["nbands"]
+        nwork = int(ctx.lib.dgc_hn_forward_loss_work_floats(C.byref(self.st)))
+        self.works = [torch.empty(nwork, device="cuda") for _ in range(nsets)]
+        # target audio: rendered once from seed+1 (setup, untimed)
+        self.target = torch.empty(B, T, device="cuda")
+        self.stage_taps(G); self.stage_harm(G, self.target); self.stage_fir(G, self.target)
+        self.targets = [self.target] + [self.target.clone() for _ in range(1, nsets)]
+        torch.cuda.synchronize()
+
+    def stage_taps(self, X):
+        c, cfg = self.ctx, self.cfg
+        c.check(c.lib.dgc_bands_to_taps(c.h, X["bands"].data_ptr(), X["W"].data_ptr(), cfg["F"] * self.B,
+                                        cfg["nbands"], cfg["taps"], self.taps_buf.data_ptr()))
+
+    def stage_harm(self, X, out):
+        c = self.ctx
+        c.check(c.lib.dgc_harmonic_render(c.h, self.C.byref(self.hp), X["f0"].data_ptr(), X["uv"].data_ptr(),
+                                          X["amps"].data_ptr(), X["gain"].data_ptr(), None, out.data_ptr()))
+
+    def stage_fir(self, X, out):
+        c = self.ctx
+        c.check(c.lib.dgc_fir_noise(c.h, self.C.byref(self.fp), X["noise"].data_ptr(), self.taps_buf.data_ptr(),
+                                    X["noise_gain"].data_ptr(), out.data_ptr()))
+
+    def stage_loss(self, pred, target):
+        c = self.ctx
+        c.check(c.lib.dgc_mss_loss_fwd(c.h, self.C.byref(self.mss), pred.data_ptr(), target.data_ptr(), None,
+                                       self.loss.data_ptr()))
+
+    def step_staged(self):
+        D = self.D
+        self.stage_taps(D); self.stage_harm(D, self.audio); self.stage_fir(D, self.audio)
+        self.stage_loss(self.audio, self.target)
+
+    def step(self, i=0):
+        """ONE call of the device-resident composite (harmonic and noise branch on two streams, joined at the loss)."""
+        c, D = self.ctx, self.sets[i]
+        c.check(c.lib.dgc_hn_forward_loss(c.h, self.C.byref(self.st), D["f0"].data_ptr(), D["uv"].data_ptr(),
+                                          D["amps"].data_ptr(), D["gain"].data_ptr(), D["noise_gain"].data_ptr(),
+                                          D["bands"].data_ptr(), D["W"].data_ptr(), D["noise"].data_ptr(),
+                                          self.targets[i].data_ptr(), self.works[i].data_ptr(), self.loss.data_ptr(),
+                                          None))
+
+    def check_composite(self):
+        self.step_staged()
+        a = float(self.loss.cpu()[0])
+        self.step()
+        b = float(self.loss.cpu()[0])
+        if not abs(b - a) <= 1e-9 * abs(a):
+            raise SystemExit("composite step and staged step disagree: %r vs %r" % (b, a))
+        return b
+
+    def record(self, stream, i=0):
+        """Record the composite step on `stream` (its two streams and their join included); returns the graph."""
+        torch = self.torch
+        stream.wait_stream(torch.cuda.current_stream())
+        with self.ctx.on_stream(stream), torch.cuda.stream(stream):
+            with self.ctx.record() as rec:
+                self.step(i)
+            for _ in range(2):
+                rec.graph.launch()
+        torch.cuda.synchronize()
+        return rec.graph
+
+    def stage_times(self, flush, reps):
+        torch, D = self.torch, self.D
+        stages = {"bands_to_taps": lambda: self.stage_taps(D), "harmonic_render": lambda: self.stage_harm(D, self.audio),
+                  "fir_noise": lambda: self.stage_fir(D, self.audio),
+                  "mss_loss_fwd": lambda: self.stage_loss(self.audio, self.target)}
+        out = {}
+        for name, fn in stages.items():
+            fn()
+            acc = 0.0
+            for r in range(reps):
+                flush.fill_(float(r))
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(); fn(); b.record()
+                torch.cuda.synchronize()
+                acc += a.elapsed_time(b)
+            out[name] = acc / reps
+        return out
+
+
+def timed_replay(ctx, fl, graphs, run_stream, flush, steps, barrier):
+    """`steps` launches of the recorded step(s), each bracketed by CUDA events on the launching stream, L2 flushed
+    before every step.  Returns the summed device time in ms."""
+    torch = fl.torch
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    barrier()
+    with ctx.on_stream(run_stream), torch.cuda.stream(run_stream):
+        for s in range(steps):
+            flush.fill_(float(s))
+            evs[s][0].record()
+            graphs[s % len(graphs)].launch()
+            evs[s][1].record()
+    barrier()
+    return sum(a.elapsed_time(b) for a, b in evs)
+
+
+def sustained_run(ctx, fl, graphs, run_stream, local_rank, seconds=2.5):
+    """The recorded step replayed back to back for at least `seconds`, rotating over input sets whose total exceeds
+    L2, with the SM clock sampled every 100 ms: a clock or throttle problem shows here, not in a 6 ms region."""
+    torch = fl.torch
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    time.sleep(0.25)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    n, t0 = 0, time.perf_counter()
+    with ctx.on_stream(run_stream), torch.cuda.stream(run_stream):
+        a.record()
+        while True:
+            for _ in range(256):
+                graphs[n % len(graphs)].launch()
+                n += 1
+            run_stream.synchronize()
+            if time.perf_counter() - t0 >= seconds:
+                break
+        b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b)
+    clocks = sampler.stop()
+    return {"seconds": ms * 1e-3, "steps": n, "ms_per_step": ms / n, "value": fl.B * fl.cfg["T"] * n / (ms * 1e-3),
+            "unit": UNIT, "clocks": clocks, "input_sets": len(graphs),
+            "l2": "%d input sets in rotation (%.0f MB per set): the working set exceeds L2, no flush kernels between steps"
+                  % (len(graphs), sum(v.numel() for v in fl.D.values()) * 4 / 1e6)}
+
+
 def run_ours(args, rank, world, local_rank):
     import torch
     import torch.distributed as dist
     import dgen_b200
-    from dgen_b200 import workloads as wl
+    from dgen_b200 import sharding
 
     torch.cuda.set_device(local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     ctx = dgen_b200.Context(local_rank)
-    B, T, K, F, sr = CFG["B"], CFG["T"], CFG["K"], CFG["F"], CFG["sr"]
-    d = wl.harmonic_noise_inputs(SEED + 100 * rank, **CFG)
-    tg = wl.harmonic_noise_inputs(SEED + 100 * rank + 1, **CFG)
-    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
-    D = {k: dev(v) for k, v in d.items() if isinstance(v, np.ndarray)}
-    G = {k: dev(v) for k, v in tg.items() if isinstance(v, np.ndarray)}
-    audio = torch.empty(B, T, device="cuda")
-    loss = torch.zeros(1, dtype=torch.float64, device="cuda")
-    mss = dgen_b200.mss_params(B, T, SIZES)
-    import ctypes as C
-    hp = dgen_b200.HarmonicParams(B, T, K, F, sr, 1.0,
-                                  {"scan": dgen_b200.PHASE_SCAN, "sequential": dgen_b200.PHASE_SEQUENTIAL,
-                                   "fundamental": dgen_b200.PHASE_FUNDAMENTAL}[PHASE["mode"]], 0)
-    fp = dgen_b200.FirParams(B, T, F, CFG["taps"], 0.12, 1)
-    lib, h = ctx.lib, ctx.h
-    taps_buf = torch.empty(F, B, CFG["taps"], device="cuda")
-
-    def stage_taps(X):
-        ctx.check(lib.dgc_bands_to_taps(h, X["bands"].data_ptr(), X["W"].data_ptr(), F * B, CFG["nbands"], CFG["taps"],
-                                        taps_buf.data_ptr()))
-
-    def stage_harm(X, out):
-        ctx.check(lib.dgc_harmonic_render(h, C.byref(hp), X["f0"].data_ptr(), X["uv"].data_ptr(),
-                                          X["amps"].data_ptr(), X["gain"].data_ptr(), None, out.data_ptr()))
-
-    def stage_fir(X, out):
-        ctx.check(lib.dgc_fir_noise(h, C.byref(fp), X["noise"].data_ptr(), taps_buf.data_ptr(),
-                                    X["noise_gain"].data_ptr(), out.data_ptr()))
-
-    def stage_loss(pred, target):
-        ctx.check(lib.dgc_mss_loss_fwd(h, C.byref(mss), pred.data_ptr(), target.data_ptr(), None, loss.data_ptr()))
-
-    # target audio: rendered once from seed+1 (setup, untimed)
-    target = torch.empty(B, T, device="cuda")
-    stage_taps(G); stage_harm(G, target); stage_fir(G, target)
-    torch.cuda.synchronize()
-
-    def step_staged():
-        stage_taps(D); stage_harm(D, audio); stage_fir(D, audio); stage_loss(audio, target)
-
-    # the timed step: ONE call of the device-resident composite (harmonic and noise branch on two streams,
-    # joined at the loss); the staged sequence above is kept for the per-stage times and as a cross-check
-    st_dev = dgen_b200.HnStep()
-    st_dev.harm, st_dev.fir, st_dev.mss, st_dev.nbands = hp, fp, mss, CFG["nbands"]
-    work = torch.empty(int(lib.dgc_hn_forward_loss_work_floats(C.byref(st_dev))), device="cuda")
-
-    def step():
-        ctx.check(lib.dgc_hn_forward_loss(h, C.byref(st_dev), D["f0"].data_ptr(), D["uv"].data_ptr(),
-                                          D["amps"].data_ptr(), D["gain"].data_ptr(), D["noise_gain"].data_ptr(),
-                                          D["bands"].data_ptr(), D["W"].data_ptr(), D["noise"].data_ptr(),
-                                          target.data_ptr(), work.data_ptr(), loss.data_ptr(), None))
-
-    step_staged()
-    loss_staged = float(loss.cpu()[0])
-    step()
-    loss_fused = float(loss.cpu()[0])
-    if not abs(loss_fused - loss_staged) <= 1e-9 * abs(loss_staged):
-        raise SystemExit("composite step and staged step disagree: %r vs %r" % (loss_fused, loss_staged))
-
+    sm_count = torch.cuda.get_device_properties(local_rank).multi_processor_count
+    B, T, K, F = CFG["B"], CFG["T"], CFG["K"], CFG["F"]
+    NSETS = 4
+    fl = FwdLoss(ctx, B, SEED + 100 * rank, nsets=NSETS)
+    loss_fused = fl.check_composite()
     flush = torch.empty(512 * 1024 * 1024 // 4, device="cuda")
 
     def barrier():
@@ -248,69 +421,44 @@ def run_ours(args, rank, world, local_rank):
         torch.cuda.synchronize()
 
     for _ in range(args.warmup):
-        step()
+        fl.step()
     barrier()
     # --step-mode replay (the default): the composite step is recorded once (its two streams and their join
     # included) and the timed step is one launch of that recording; eager: the call itself is timed.  Same kernels,
-    # same inputs, same loss; the recording only removes the host's launch gaps between the nine kernels.
+    # same inputs, same loss; the recording only removes the host's launch gaps between the kernels.
     replay = args.step_mode != "eager"
-    graph, run_stream = None, torch.cuda.current_stream()
+    run_stream = torch.cuda.Stream() if replay else torch.cuda.current_stream()
+    graphs = []
     if replay:
-        run_stream = torch.cuda.Stream()
-        run_stream.wait_stream(torch.cuda.current_stream())
-        with ctx.on_stream(run_stream), torch.cuda.stream(run_stream):
-            with ctx.record() as rec:
-                step()
-            graph = rec.graph
-            for _ in range(3):
-                graph.launch()
-        torch.cuda.synchronize()
-        loss_replayed = float(loss.cpu()[0])
+        graphs = [fl.record(run_stream, i) for i in range(NSETS)]
+        loss_replayed = float(fl.loss.cpu()[0])
         if loss_replayed != loss_fused:
             raise SystemExit("replayed step and direct call disagree: %r vs %r" % (loss_replayed, loss_fused))
     launches0 = ctx.launch_count()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
-    barrier()
-    with ctx.on_stream(run_stream), torch.cuda.stream(run_stream):
+    if replay:
+        total_ms = timed_replay(ctx, fl, graphs[:1], run_stream, flush, args.steps, barrier)
+    else:
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+        barrier()
         for s in range(args.steps):
             flush.fill_(float(s))
             evs[s][0].record()
-            if replay:
-                graph.launch()
-            else:
-                step()
+            fl.step()
             evs[s][1].record()
-    barrier()
+        barrier()
+        total_ms = sum(a.elapsed_time(b) for a, b in evs)
     launches = ctx.launch_count() - launches0
-    total_ms = sum(a.elapsed_time(b) for a, b in evs)
-    loss_val = float(loss.cpu()[0])
-    if graph is not None:
-        graph.close()
-
-    # per-stage times (device events, same L2-flush discipline) for the roofline of the dominant kernel
-    stages = {"bands_to_taps": lambda: stage_taps(D), "harmonic_render": lambda: stage_harm(D, audio),
-              "fir_noise": lambda: stage_fir(D, audio), "mss_loss_fwd": lambda: stage_loss(audio, target)}
-    stage_ms = {}
-    reps = max(3, min(args.steps, 10))
-    for name, fn in stages.items():
-        acc = 0.0
-        for r in range(reps):
-            flush.fill_(float(r))
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record(); fn(); b.record()
-            torch.cuda.synchronize()
-            acc += a.elapsed_time(b)
-        stage_ms[name] = acc / reps
+    loss_val = float(fl.loss.cpu()[0])
+    stage_ms = fl.stage_times(flush, max(3, min(args.steps, 10)))
 
     # end to end through the host-buffer entry point: pinned host inputs, H2D + D2H inside the timed region
     pin = lambda a: torch.from_numpy(np.ascontiguousarray(a)).pin_memory()
-    P = {k: pin(v) for k, v in d.items() if isinstance(v, np.ndarray)}
-    target_host = pin(target.cpu().numpy())
-    st = dgen_b200.HnStep()
-    st.harm, st.fir, st.mss, st.nbands = hp, dgen_b200.FirParams(B, T, F, CFG["taps"], 0.12, 1), mss, CFG["nbands"]
+    P = {k: pin(v) for k, v in fl.host.items() if isinstance(v, np.ndarray)}
+    target_host = pin(fl.target.cpu().numpy())
+    st = fl.st
 
     def e2e_step():
         return ctx.hn_forward_loss_host(st, P["f0"], P["uv"], P["amps"], P["gain"], P["noise_gain"], P["bands"],
@@ -354,41 +502,48 @@ def run_ours(args, rank, world, local_rank):
     clocks = sampler.stop() if rank == 0 else None
     h2d = 4 * sum(int(P[k].numel()) for k in ("f0", "uv", "amps", "gain", "noise_gain", "bands", "W", "noise")) \
         + 4 * int(target_host.numel())
-
-    from dgen_b200 import sharding
     total_ms, e2e_ms, piped_ms = sharding.max_over_ranks([total_ms, e2e_ms, piped_ms], device="cuda")
+
+    # sustained run (every rank runs it; rank 0 reports its own)
+    sustained = sustained_run(ctx, fl, graphs, run_stream, local_rank) if replay else None
+    barrier()
+    for g in graphs:
+        g.close()
+    del P, target_host
+
+    # the throughput target's own configuration: 256 voices on ONE GPU (device resident, replayed, per stage)
+    target_b256 = None
+    if world == 1 and B != 256 and not args.no_target:
+        target_b256 = run_target(ctx, args, flush, sm_count, local_rank)
+
+    # the training step, at every N: 32 voices per GPU, gradient all-reduce between the two recordings
+    train = None
+    if not args.no_train:
+        del fl
+        torch.cuda.empty_cache()
+        train = train_measure(ctx, args, rank, world, local_rank, steps=max(5, min(args.steps, 20)))
+
+    other = None
+    if world == 1 and not args.no_other:
+        torch.cuda.empty_cache()
+        other = filters_measure(ctx, args, quick=True)
+
     if rank == 0:
         samples_per_step = B * T * world
         value = samples_per_step * args.steps / (total_ms * 1e-3)
         e2e_value = samples_per_step * args.steps / (e2e_ms * 1e-3)
-        peaks = {}
-        try:
-            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
-        except Exception:
-            pass
-        peak = float(peaks.get("hbm_gbs", 6650.0))
-        # algorithmic bytes per launch of each stage (fp32 = 4 bytes)
-        alg = {"harmonic_render": 4 * (B * F * (K + 2) + B * T),
-               "fir_noise": 4 * (B * T + B * F * CFG["taps"] + 2 * B * T),
-               "bands_to_taps": 4 * (B * F * CFG["nbands"] + B * F * CFG["taps"]),
-               "mss_loss_fwd": 2 * 4 * B * T * len(SIZES)}
-        # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per voice of each stage's kernels, from the
-        # ncu --set full capture of this workload at 16 voices summarised in
-        # profiles/fwd_loss_c2_kernels_full_set.md; traffic grows in proportion to the voices per launch.
-        ncu_traffic_per_voice = {"harmonic_render": (21.55e6 + 4.12e6) / 16, "fir_noise": 25.02e6 / 16,
-                                 "mss_loss_fwd": 8.34e6 / 16, "bands_to_taps": 4.26e6 / 16}
+        peaks = measured_peaks()
+        hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
+        sm_mhz = float((clocks or {}).get("sm_mhz") or (sustained or {}).get("clocks", {}).get("sm_mhz") or 1965.0)
+        stages, alg, bound_ms = stage_rooflines(B, T, stage_ms, sm_mhz, sm_count, hbm_peak)
         dom = max(stage_ms, key=stage_ms.get)
-        achieved = alg[dom] / (stage_ms[dom] * 1e-3) / 1e9
-        traffic = ncu_traffic_per_voice.get(dom)
-        traffic = traffic * B if traffic is not None else None
+        traffic, traffic_src = ncu_traffic(dom, B)
+        rl = dict(stages[dom])
+        rl.pop("ms")
+        step_ms = total_ms / args.steps
         step_bytes = sum(alg.values())
-        sm_mhz = float((clocks or {}).get("sm_mhz") or 1965.0)
-        sfu_peak = 148 * 16 * sm_mhz / 1e3                                    # G sin/s
-        sfu_ach = B * T * K / (stage_ms["harmonic_render"] * 1e-3) / 1e9
-        sfu = {"unit": "G sin/s", "achieved": sfu_ach, "peak": sfu_peak, "frac": sfu_ach / sfu_peak,
-               "what": "render stage (4 kernels), one sine per voice x frame x harmonic"}
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-                "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
+                "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": True,
                 "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
                 "config": config_json(world), "clocks": clocks,
                 # throughput through the host-buffer API with two steps in flight (dgc_hn_forward_loss_host_submit /
@@ -401,17 +556,28 @@ def run_ours(args, rank, world, local_rank):
                                      "l2": "flushed between steps"},
                         "loss": piped_loss},
                 "gpu_launches": int(launches),
-                "roofline": {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "GB/s",
-                             "frac": achieved / peak, "traffic": traffic,
-                             "peak_source": "measured" if peaks else "fallback",
-                             "note": "the stage is FP32/SFU-issue bound, not HBM bound; see roofline.sfu",
-                             # the bound that does apply to the oscillator bank: one sine per (voice, frame,
-                             # harmonic) on the 16 SFU lanes of each SM at the sampled SM clock
-                             "sfu": sfu},
-                "stage_ms": stage_ms,
+                # the stage with the largest measured share, against the bound that applies to it
+                "roofline": dict(rl, kernel=dom, traffic=traffic, traffic_source=traffic_src,
+                                 peak_source=("measured" if peaks else "fallback") if rl["bound"] == "hbm" else
+                                 "%d SMs x lanes x sampled SM clock %.0f MHz" % (sm_count, sm_mhz)),
+                "stage_ms": stage_ms, "stages": stages,
                 "whole_step": {"algorithmic_bytes": step_bytes,
-                               "achieved_gbs": step_bytes / (total_ms / args.steps * 1e-3) / 1e9},
+                               "hbm": {"achieved_gbs": step_bytes / (step_ms * 1e-3) / 1e9,
+                                       "frac": step_bytes / (step_ms * 1e-3) / 1e9 / hbm_peak,
+                                       "peak": hbm_peak, "peak_source": "measured" if peaks else "fallback"},
+                               "bound_ms": bound_ms, "frac_of_bound": bound_ms / step_ms,
+                               "what": "bound_ms = sum over the stages of (stage work / the peak that bounds it): "
+                                       "special-function lanes for the oscillator bank, FP32 lanes for the FIR "
+                                       "and the loss transforms, measured copy bandwidth for the band -> tap map"},
                 "loss": loss_val, "e2e_loss": e2e_loss}
+        if sustained:
+            line["sustained"] = sustained
+        if target_b256:
+            line["target_b256"] = target_b256
+        if train:
+            line["train"] = train
+        if other:
+            line["other_configs"] = other
         if not args.no_cpu and world == 1:
             v, secs = cpu_arm(4, 1)
             line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": 1, "kind": "port",
@@ -424,30 +590,79 @@ def run_ours(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
+def run_target(ctx, args, flush, sm_count, local_rank):
+    """256 voices on this one GPU: replayed device-resident step, per-stage times and rooflines."""
+    import torch
+    Bt = 256
+    fl = FwdLoss(ctx, Bt, SEED + 7, nsets=1)
+    fl.check_composite()
+    for _ in range(3):
+        fl.step()
+    stream = torch.cuda.Stream()
+    graph = fl.record(stream)
+    steps = max(5, min(args.steps, 20))
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    ms = timed_replay(ctx, fl, [graph], stream, flush, steps, torch.cuda.synchronize) / steps
+    # a second, longer region for the clock record: >= 1.5 s of back-to-back replays (inputs of 0.5 GB exceed L2)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    n, t0 = 0, time.perf_counter()
+    with ctx.on_stream(stream), torch.cuda.stream(stream):
+        a.record()
+        while time.perf_counter() - t0 < 1.5:
+            for _ in range(32):
+                graph.launch()
+                n += 1
+            stream.synchronize()
+        b.record()
+    torch.cuda.synchronize()
+    sus_ms = a.elapsed_time(b) / n
+    clocks = sampler.stop()
+    stage_ms = fl.stage_times(flush, 5)
+    graph.close()
+    peaks = measured_peaks()
+    hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
+    sm_mhz = float(clocks.get("sm_mhz") or 1965.0)
+    stages, alg, bound_ms = stage_rooflines(Bt, fl.cfg["T"], stage_ms, sm_mhz, sm_count, hbm_peak)
+    step_bytes = sum(alg.values())
+    out = {"voices": Bt, "n_gpus": 1, "ms_per_step": ms, "value": Bt * fl.cfg["T"] / (ms * 1e-3), "unit": UNIT,
+           "steps": steps, "l2": "L2 flushed between timed steps; inputs (0.5 GB) exceed L2 anyway",
+           "sustained": {"ms_per_step": sus_ms, "value": Bt * fl.cfg["T"] / (sus_ms * 1e-3), "steps": n,
+                         "seconds": sus_ms * n * 1e-3}, "clocks": clocks,
+           "stages": stages,
+           "whole_step": {"algorithmic_bytes": step_bytes,
+                          "hbm": {"achieved_gbs": step_bytes / (ms * 1e-3) / 1e9,
+                                  "frac": step_bytes / (ms * 1e-3) / 1e9 / hbm_peak, "peak": hbm_peak},
+                          "bound_ms": bound_ms, "frac_of_bound": bound_ms / ms}}
+    del fl
+    torch.cuda.empty_cache()
+    return out
+
 
 # --------------------------------------------------------------------------------------------------
 # training-step workload (BASELINE.json configs[4]): 32 voices per GPU, controller MLP 2-512-512-512-165,
 # harmonic+noise synthesis, 1 s learnable IR reverb, multi-scale spectral loss, backward, gradient
 # all-reduce (NCCL) and one Adam step
 # --------------------------------------------------------------------------------------------------
-def run_train(args, rank, world, local_rank):
+def train_measure(ctx, args, rank, world, local_rank, steps, voices=32, want_e2e=True):
+    """Times the training step on an initialised context (and, for world > 1, process group).  Returns the
+    measurement as a dict on rank 0 (None elsewhere)."""
     import torch
     import torch.distributed as dist
     import dgen_b200
     from dgen_b200 import sharding, trainer as tr, workloads as wl
 
-    torch.cuda.set_device(local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    ctx = dgen_b200.Context(local_rank)
-    B = args.voices if args.voices > 0 else 32
+    B = voices
     T, K, F, sr, NB, NT = CFG["T"], CFG["K"], CFG["F"], CFG["sr"], CFG["nbands"], CFG["taps"]
     d = wl.harmonic_noise_inputs(SEED + 100 * rank, B=B, T=T, K=K, F=F, sr=sr, nbands=NB, taps=NT)
     tg = wl.harmonic_noise_inputs(SEED + 100 * rank + 1, B=B, T=T, K=K, F=F, sr=sr, nbands=NB, taps=NT)
     dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
     pin = lambda a: torch.from_numpy(np.ascontiguousarray(a)).pin_memory()
+    mode = {"scan": dgen_b200.PHASE_SCAN, "sequential": dgen_b200.PHASE_SEQUENTIAL,
+            "fundamental": dgen_b200.PHASE_FUNDAMENTAL}[PHASE["mode"]]
     model = tr.HarmonicModel(ctx, B, T, K=K, F=F, sr=sr, nbands=NB, taps=NT, hidden=512, ir_len=16000, conv_n=2048,
-                             conv_hop=1024, sizes=SIZES, seed=7, global_voices=B * world, counted_adam=True)
+                             conv_hop=1024, sizes=SIZES, seed=7, global_voices=B * world, counted_adam=True,
+                             phase_mode=mode)
     # gradient exchange: the context's own NCCL communicator (dgc_allreduce_sum through the C ABI) unless
     # --allreduce torch asks for the torch.distributed call
     model.use_ctx_comm = args.allreduce == "dgc" and sharding.init_ctx_comm(ctx)
@@ -461,18 +676,19 @@ def run_train(args, rank, world, local_rank):
     P = {k: pin(host[k]) for k in order}
     D = {k: dev(host[k]) for k in order}
     dargs = [D[k] for k in order]
+    del G
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(args.warmup):
+    for _ in range(max(3, args.warmup)):
         model.step(*dargs)
     # step mode: "replay" records the step once (both streams, Adam; with several ranks the gradient exchange stays
     # between two recordings) and launches the recording per step; "eager" enqueues it call by call.
-    mode = args.step_mode if args.step_mode != "auto" else "replay"
-    if mode == "replay":
+    mode_s = args.step_mode if args.step_mode != "auto" else "replay"
+    if mode_s == "replay":
         model.capture(*dargs)
         step_fn = model.replay
         for _ in range(2):
@@ -484,78 +700,117 @@ def run_train(args, rank, world, local_rank):
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    model.exchange_events = [] if (mode_s == "replay" and world > 1) else None
     barrier()
-    for s in range(args.steps):
+    for s in range(steps):
         evs[s][0].record()
         loss = step_fn()
         evs[s][1].record()
     barrier()
     launches = ctx.launch_count() - l0
     total_ms = sum(a.elapsed_time(b) for a, b in evs)
-    # end to end: the step's inputs come from pinned host memory, the loss goes back to the host
-    e2e_ms = 0.0
-    for s in range(args.steps):
+    exch_ms = 0.0
+    if model.exchange_events:
+        exch_ms = sum(a.elapsed_time(b) for a, b in model.exchange_events) / len(model.exchange_events)
+    model.exchange_events = None
+    e2e_ms = piped_ms = 0.0
+    loss_host = float(loss.cpu()[0])
+    if want_e2e:
+        # end to end: the step's inputs come from pinned host memory, the loss goes back to the host
+        for s in range(steps):
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for k in order:
+                D[k].copy_(P[k], non_blocking=True)
+            loss = step_fn()
+            loss_host = float(loss.cpu()[0])
+            b.record()
+            torch.cuda.synchronize()
+            e2e_ms += a.elapsed_time(b)
+        barrier()
+        # the same with the NEXT step's inputs crossing PCIe (copy stream, device staging) while this step runs; at
+        # the start of a step the staged inputs move into the step's static buffers device to device.  Every step
+        # still takes its inputs from pinned host memory and returns its loss to the host inside the timed region.
+        cur, cs = torch.cuda.current_stream(), torch.cuda.Stream()
+        S = {k: torch.empty_like(D[k]) for k in order}
+
+        def prefetch():
+            with torch.cuda.stream(cs):
+                for k in order:
+                    S[k].copy_(P[k], non_blocking=True)
+
         torch.cuda.synchronize()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
-        for k in order:
-            D[k].copy_(P[k], non_blocking=True)
-        loss = step_fn()
-        loss_host = float(loss.cpu()[0])
+        cs.wait_stream(cur)
+        prefetch()
+        for s in range(steps):
+            cur.wait_stream(cs)
+            for k in order:
+                D[k].copy_(S[k], non_blocking=True)
+            cs.wait_stream(cur)
+            if s + 1 < steps:
+                prefetch()
+            loss = step_fn()
+            loss_host = float(loss.cpu()[0])
         b.record()
         torch.cuda.synchronize()
-        e2e_ms += a.elapsed_time(b)
-    barrier()
-    # the same with the NEXT step's inputs crossing PCIe (copy stream, device staging) while this step runs; at the
-    # start of a step the staged inputs move into the step's static buffers device to device.  Every step still
-    # takes its inputs from pinned host memory and returns its loss to the host inside the timed region.
-    cur, cs = torch.cuda.current_stream(), torch.cuda.Stream()
-    S = {k: torch.empty_like(D[k]) for k in order}
-
-    def prefetch():
-        with torch.cuda.stream(cs):
-            for k in order:
-                S[k].copy_(P[k], non_blocking=True)
-
-    torch.cuda.synchronize()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
-    cs.wait_stream(cur)
-    prefetch()
-    for s in range(args.steps):
-        cur.wait_stream(cs)
-        for k in order:
-            D[k].copy_(S[k], non_blocking=True)
-        cs.wait_stream(cur)
-        if s + 1 < args.steps:
-            prefetch()
-        loss = step_fn()
-        loss_host = float(loss.cpu()[0])
-    b.record()
-    torch.cuda.synchronize()
-    piped_ms = a.elapsed_time(b)
-    barrier()
+        piped_ms = a.elapsed_time(b)
+        barrier()
     clocks = sampler.stop() if rank == 0 else None
-    total_ms, e2e_ms, piped_ms = sharding.max_over_ranks([total_ms, e2e_ms, piped_ms], device="cuda")
+    total_ms, e2e_ms, piped_ms, exch_ms = sharding.max_over_ranks([total_ms, e2e_ms, piped_ms, exch_ms], device="cuda")
     glob_loss = sharding.global_mean_loss(loss_host, B, device="cuda")
+    n_params = model.n_params
+    used_ctx_comm = bool(model.use_ctx_comm)
+    for g in model.graph or []:
+        g.close()
+    if used_ctx_comm:
+        ctx.lib.dgc_comm_destroy(ctx.h)
+    del model, D, P
+    torch.cuda.empty_cache()
+    if rank != 0:
+        return None
+    ms = total_ms / steps
+    h2d = 4 * sum(int(np.asarray(host[k]).size) for k in order)
+    out = {"metric": "ms/train step", "ms_per_step": ms, "unit": "ms", "n_gpus": world, "steps": steps,
+           "voices_per_gpu": B, "global_voices": B * world, "samples_per_s": B * world * T / (ms * 1e-3),
+           "scaling": "weak", "step_mode": mode_s,
+           "allreduce": {"floats": n_params, "bytes": 4 * n_params, "ms": exch_ms, "share_of_step": exch_ms / ms,
+                         "via": "dgc_allreduce_sum" if used_ctx_comm else
+                                ("torch.distributed" if world > 1 else "none (one rank)"),
+                         "what": "CUDA events around the NCCL all-reduce between the two recordings, max over ranks"},
+           "config": {"workload": "full training step (BASELINE.json configs[4])", "frames": T, "harmonics": K,
+                      "control_frames": F, "controller": "MLP 2-512-512-512-165 fp32", "ir_taps": 16000,
+                      "fft_sizes": list(SIZES), "optimizer": "Adam lr 1e-3", "phase_mode": PHASE["mode"],
+                      "l2": "working set (>1 GB per step) exceeds L2"},
+           "clocks": clocks, "gpu_launches": int(launches), "loss": glob_loss}
+    if want_e2e:
+        out["e2e"] = {"value": piped_ms / steps, "unit": "ms", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 8,
+                      "mode": "the next step's inputs upload on a copy stream while this step runs",
+                      "blocking": {"value": e2e_ms / steps, "unit": "ms"}}
+    return out
+
+
+def run_train(args, rank, world, local_rank):
+    import torch
+    import torch.distributed as dist
+    import dgen_b200
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    ctx = dgen_b200.Context(local_rank)
+    t = train_measure(ctx, args, rank, world, local_rank, args.steps, voices=args.voices if args.voices > 0 else 32)
     if rank == 0:
-        ms = total_ms / args.steps
-        h2d = 4 * sum(int(P[k].numel()) for k in order)
-        line = {"metric": "ms/train step", "value": ms, "unit": "ms", "n_gpus": world, "steps": args.steps,
-                "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": False, "scaling": "weak",
-                "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-                "config": {"workload": "full training step (BASELINE.json configs[4])", "voices_per_gpu": B,
-                           "global_voices": B * world, "frames": T, "harmonics": K, "control_frames": F,
-                           "controller": "MLP 2-512-512-512-165 fp32", "ir_taps": 16000, "fft_sizes": list(SIZES),
-                           "optimizer": "Adam lr 1e-3", "step_mode": mode, "parallelism": "dp%d, NCCL all-reduce of %d gradients (%s)"
-                           % (world, model.n_params,
-                              "dgc_allreduce_sum" if model.use_ctx_comm else "torch.distributed"), "l2": "working set (>1 GB per step) exceeds L2"},
-                "samples_per_s": B * world * T / (ms * 1e-3), "clocks": clocks,
-                "e2e": {"value": piped_ms / args.steps, "unit": "ms", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 8,
-                        "mode": "the next step's inputs upload on a copy stream while this step runs",
-                        "blocking": {"value": e2e_ms / args.steps, "unit": "ms"}},
-                "gpu_launches": int(launches), "loss": glob_loss}
+        line = {"metric": "ms/train step", "value": t["ms_per_step"], "unit": "ms", "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": t["ms_per_step"], "higher_is_better": False, "scaling": "weak",
+                "vs_baseline": None, "dtype": "f32", "data": "synthetic"}
+        line.update({k: v for k, v in t.items() if k not in line})
+        line["config"] = dict(t["config"], voices_per_gpu=t["voices_per_gpu"], global_voices=t["global_voices"],
+                              step_mode=t["step_mode"],
+                              parallelism="dp%d, NCCL all-reduce of %d gradients (%s)"
+                              % (world, t["allreduce"]["floats"], t["allreduce"]["via"]))
         print(json.dumps(line))
     ctx.close()
     if world > 1:
@@ -576,13 +831,25 @@ def measured_hbm_peak():
 
 
 def run_filters(args, local_rank):
+    import torch
+    import dgen_b200
+    torch.cuda.set_device(local_rank)
+    ctx = dgen_b200.Context(local_rank)
+    for line in filters_measure(ctx, args, quick=False):
+        print(json.dumps(line))
+    ctx.close()
+
+
+def filters_measure(ctx, args, quick):
+    """One dict per kernel family (the JSON lines of --workload filters).  quick: the configurations BASELINE.json
+    names only (oscillator -> filter -> FFT, biquad bank forward / BPTT, partitioned convolution), fewer steps."""
     import ctypes as C
     import torch
     import dgen_b200
     from dgen_b200 import workloads as wl
 
-    torch.cuda.set_device(local_rank)
-    ctx = dgen_b200.Context(local_rank)
+    lines = []
+    steps = max(3, min(args.steps, 10)) if quick else args.steps
     peak, peak_kind = measured_hbm_peak()
     dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
 
@@ -592,22 +859,22 @@ def run_filters(args, local_rank):
         torch.cuda.synchronize()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
-        for _ in range(args.steps):
+        for _ in range(steps):
             fn()
         b.record()
         torch.cuda.synchronize()
-        return a.elapsed_time(b) / args.steps
+        return a.elapsed_time(b) / steps
 
     def emit(metric, workload, ms, bytes_, extra=None, l2="inputs + outputs larger than L2"):
         gbs = bytes_ / ms / 1e6
-        line = {"metric": metric, "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+        line = {"metric": metric, "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": steps,
                 "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True, "dtype": "f32",
                 "data": "synthetic", "config": {"workload": workload, "l2": l2},
                 "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak,
                              "peak_kind": peak_kind, "algorithmic_bytes": bytes_}}
         if extra:
             line.update(extra)
-        print(json.dumps(line))
+        lines.append(line)
 
     scale = args.voices if args.voices > 0 else 0
     # the reference's own small case (BASELINE.json configs[0]): 64 partials -> one-pole -> buffer(1024, hop 256) -> FFT
@@ -643,7 +910,36 @@ def run_filters(args, local_rank):
                                                             gc.data_ptr(), gq.data_ptr(), loss.data_ptr())))
     emit("biquad bank BPTT", "biquad bank %d lanes x %d voices x %d frames, MSE loss, gradients of cutoff and Q" % (L, B, T),
          ms, 4.0 * T * (2 * B * L + B), {"lane_samples_per_s": B * L * T / (ms * 1e-3)})
-    del y, target
+    del y, target, x
+    torch.cuda.empty_cache()
+    if not quick:
+        filters_streams(ctx, args, scale, timed, emit)
+    # partitioned convolution: 16 voices x 480000 frames, 96000-tap IR
+    dd = wl.partconv_inputs(20260003)
+    V = min(scale, dd["V"]) if scale else dd["V"]
+    px, ir = dev(dd["x"][:V]), dev(dd["ir"])
+    po = torch.empty_like(px)
+    ms = timed(lambda: ctx.partconv(px, ir, dd["N"], dd["hop"], out=po))
+    K, H, N = (dd["ir"].size + dd["hop"] - 1) // dd["hop"], (px.shape[1] + dd["hop"] - 1) // dd["hop"], dd["N"]
+    emit("partitioned convolution", "partitioned convolution %d voices x %d frames, %d-tap IR (BASELINE.json configs[3])"
+         % (V, px.shape[1], dd["ir"].size), ms, 4.0 * 2 * px.numel() + 8.0 * K * N,
+         {"mac_gflops": 8.0 * K * N * H * V / (ms * 1e6),
+          "roofline_fp32": {"bound": "fp32", "achieved": 8.0 * K * N * H * V / (ms * 1e9), "unit": "TFLOP/s",
+                            "peak": 148 * FP32_LANES_PER_SM * 2 * 1.965e-3,
+                            "frac": 8.0 * K * N * H * V / (ms * 1e9) / (148 * FP32_LANES_PER_SM * 2 * 1.965e-3),
+                            "what": "complex multiply-accumulates of the partitions alone against 148 SMs x 128 "
+                                    "lanes x 2 flops at the maximum SM clock"},
+          "roofline_note": "compute bound: the partitioned multiply-accumulate does 8 K N flops per hop and voice"})
+    del px, ir, po
+    torch.cuda.empty_cache()
+    return lines
+
+
+def filters_streams(ctx, args, scale, timed, emit):
+    """The streaming kernels and the ring / hold ops on long signals (not BASELINE.json configurations)."""
+    import ctypes as C
+    import torch
+    import dgen_b200
     # one-pole and the output sanitiser on long streams
     n = 1 << 28 if not scale else 1 << 26
     xx = torch.randn(64, n // 64, device="cuda")
@@ -678,18 +974,6 @@ def run_filters(args, local_rank):
          {"samples_per_s": cb * ct / (ms * 1e-3),
           "roofline_note": "latency bound: the attack / release smoother is a data-dependent recurrence, one warp per voice"})
     del cx, cy
-    # partitioned convolution: 16 voices x 480000 frames, 96000-tap IR
-    dd = wl.partconv_inputs(20260003)
-    V = min(scale, dd["V"]) if scale else dd["V"]
-    px, ir = dev(dd["x"][:V]), dev(dd["ir"])
-    po = torch.empty_like(px)
-    ms = timed(lambda: ctx.partconv(px, ir, dd["N"], dd["hop"], out=po))
-    K, H, N = (dd["ir"].size + dd["hop"] - 1) // dd["hop"], (px.shape[1] + dd["hop"] - 1) // dd["hop"], dd["N"]
-    emit("partitioned convolution", "partitioned convolution %d voices x %d frames, %d-tap IR (BASELINE.json configs[3])"
-         % (V, px.shape[1], dd["ir"].size), ms, 4.0 * 2 * px.numel() + 8.0 * K * N,
-         {"mac_gflops": 8.0 * K * N * H * V / (ms * 1e6),
-          "roofline_note": "compute bound: the partitioned multiply-accumulate does 8 K N flops per hop and voice"})
-    ctx.close()
 
 
 def main():
@@ -710,8 +994,12 @@ def main():
     ap.add_argument("--voices", type=int, default=0,
                     help="voices per GPU (default: the configuration's 16); other values are for profiling "
                          "captures and scaling studies, not for the headline number")
-    ap.add_argument("--phase", default="scan", choices=["scan", "sequential", "fundamental"],
-                    help="phase-anchor mode of the oscillator bank")
+    ap.add_argument("--phase", default="fundamental", choices=["scan", "sequential", "fundamental"],
+                    help="phase-anchor mode of the oscillator bank (all three are inside the 1e-4 sample tolerance "
+                         "against the step-by-step recurrence; tests/test_gpu_harmonic.py)")
+    ap.add_argument("--no-target", action="store_true", help="skip the 256-voice single-GPU block")
+    ap.add_argument("--no-train", action="store_true", help="skip the training-step block")
+    ap.add_argument("--no-other", action="store_true", help="skip the other configurations (single GPU)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

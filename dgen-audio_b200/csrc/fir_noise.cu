@@ -207,6 +207,204 @@ fir_noise_kernel(dgc_fir_params prm, const float2 *__restrict__ rowtab, const fl
   }
 }
 
+// The same filter with the shared-memory traffic and the third dot product taken out of the main loop.
+//   * control rows are staged with a padded stride NTP (a multiple of 4 with NTP % 8 == 4, zero beyond `taps`):
+//     a thread reads four taps of a row with ONE 128-bit load (rows of the four 8-lane groups of a warp fall into
+//     distinct bank quads), so eight taps x two rows x eight frames = 128 multiply-adds cost 4 tap loads and 8 signal
+//     loads; no remainder loop (the padding taps are zero, the signal tile is zero-extended to match);
+//   * a thread whose eight frames straddle a control-row boundary needs a third row for the frames behind the
+//     boundary.  Computed inside the main loop that third dot product makes EVERY warp run the loop body a third
+//     time for its few straddling lanes (+50 % instructions).  Here the straddling threads put themselves on a
+//     list, and after the main loop every group of 8 lanes takes one list entry: the lanes split the taps, slide
+//     the signal window through registers, and reduce with shuffles (+9 % instructions).
+// Block = NTH threads x 8 frames.  Results are bit-identical from run to run (fixed summation orders; the list
+// order only decides which lane group computes an entry, not how).
+template <int NTH>
+__global__ void __launch_bounds__(NTH, 768 / NTH)
+fir_noise8_kernel(dgc_fir_params prm, const float2 *__restrict__ rowtab, const float *__restrict__ noise,
+                  const float *__restrict__ taps_tab, const float *__restrict__ ngain, float *__restrict__ audio,
+                  int max_rows, int NTP, int32_t *status) {
+  extern __shared__ __align__(16) float sh[];
+  constexpr int SPT = 8, TILE = NTH * SPT, GROUPS = NTH / 8;
+  const int B = prm.B, T = prm.T, F = prm.F, NT = prm.taps;
+  const int b = blockIdx.y, t0 = blockIdx.x * TILE;
+  const int t_last = min(T - 1, t0 + TILE - 1);
+  __shared__ int wrap_sh, n_list;
+  __shared__ int list[NTH];            // straddling threads
+  __shared__ float d2buf[NTH][SPT];    // their third dot products, by list position
+  if (threadIdx.x == 0) {
+    wrap_sh = 0x7fffffff;
+    n_list = 0;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int u = 0; u < SPT; ++u) {
+    int n = t0 + threadIdx.x * SPT + u;
+    if (n > t0 && n <= t_last && __float_as_int(rowtab[n].x) < __float_as_int(rowtab[n - 1].x)) atomicMin(&wrap_sh, n);
+  }
+  __syncthreads();
+  const int wrap = wrap_sh;
+  const int rmin = __float_as_int(rowtab[t0].x);
+  int rmax = __float_as_int(rowtab[t_last].x);
+  if (t_last >= wrap) rmax += F;
+  const int R = rmax - rmin + 3;  // rows rmin .. rmax+2 (hi of the last frame, and the straddle row)
+  if (R > max_rows) {
+    if (threadIdx.x == 0) atomicExch(status, 101);  // control rate too high for the staged tile
+    return;
+  }
+  float *rows = sh;                          // [R][NTP]
+  float *xs = sh + (size_t)max_rows * NTP;   // [SPT][Q]: position m <-> frame t0 - (NT-1) + m, de-interleaved by m % 8
+  const int XN = TILE + NTP - 1 + SPT;       // zero-extended: the padding taps read beyond the tile
+  const int Q = (XN + SPT - 1) / SPT + 1;
+  for (int i = threadIdx.x; i < R * NTP; i += NTH) {
+    const int rr = i / NTP, col = i - rr * NTP;
+    int r = rmin + rr;
+    if (r >= F) r -= F;  // the ceil row wraps to row 0
+    if (r >= F) r = F - 1;
+    rows[i] = col < NT ? taps_tab[((size_t)r * B + b) * NT + col] : 0.0f;
+  }
+  const float *xn = noise + (size_t)b * T;
+  for (int m = threadIdx.x; m < Q * SPT; m += NTH) {
+    int t = t0 - (NT - 1) + m;
+    float v = (t >= 0 && t < T && m < TILE + NT - 1) ? xn[t] : 0.0f;
+    xs[(m % SPT) * Q + m / SPT] = v;
+  }
+  __syncthreads();
+
+  const int nl = threadIdx.x * SPT;  // first local frame of this thread
+  const bool have = t0 + nl < T;
+  int lo[SPT];
+  float fr[SPT];
+#pragma unroll
+  for (int u = 0; u < SPT; ++u) {
+    int n = min(t0 + nl + u, T - 1);
+    const float2 rt = rowtab[n];
+    lo[u] = __float_as_int(rt.x);
+    fr[u] = rt.y;
+    if (n >= wrap) lo[u] += F;
+  }
+  const int r0 = lo[0] - rmin;
+  const int spread = lo[SPT - 1] - lo[0];
+  const bool straddle = have && spread == 1;
+  float d0[SPT], d1[SPT], d2[SPT];
+#pragma unroll
+  for (int u = 0; u < SPT; ++u) d0[u] = d1[u] = d2[u] = 0.0f;
+  int my_entry = -1;
+  if (straddle) {
+    my_entry = atomicAdd(&n_list, 1);
+    list[my_entry] = threadIdx.x;
+  }
+  if (have) {
+    // frame (nl+u), tap i reads xs position nl + u + i; W[t] = position nl + i0 + t = xb[(t % 8) * Q + (i0 + t) / 8]
+    const float4 *pa = reinterpret_cast<const float4 *>(rows + (size_t)r0 * NTP);
+    const float4 *pb = reinterpret_cast<const float4 *>(rows + (size_t)(r0 + 1) * NTP);
+    const float *xb = xs + threadIdx.x;
+    float W[16];
+#pragma unroll
+    for (int t = 0; t < 8; ++t) W[t] = xb[t * Q];
+    const int NG = NTP / 8;            // NTP = 8 NG + 4
+    auto four = [&](const float4 ta, const float4 tb, int j0) {
+      const float a[4] = {ta.x, ta.y, ta.z, ta.w}, c[4] = {tb.x, tb.y, tb.z, tb.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          d0[u] = fmaf(W[u + j0 + j], a[j], d0[u]);
+          d1[u] = fmaf(W[u + j0 + j], c[j], d1[u]);
+        }
+    };
+    for (int g8 = 0; g8 < NG; ++g8) {
+#pragma unroll
+      for (int t = 0; t < 8; ++t) W[8 + t] = xb[t * Q + g8 + 1];
+      four(pa[2 * g8], pb[2 * g8], 0);
+      four(pa[2 * g8 + 1], pb[2 * g8 + 1], 4);
+#pragma unroll
+      for (int t = 0; t < 8; ++t) W[t] = W[8 + t];
+    }
+#pragma unroll
+    for (int t = 0; t < 4; ++t) W[8 + t] = xb[t * Q + NG + 1];
+    four(pa[2 * NG], pb[2 * NG], 0);
+  }
+  __syncthreads();
+  // third rows of the straddling threads: one list entry per group of 8 lanes, lanes split the taps
+  {
+    const int grp = threadIdx.x >> 3, l8 = threadIdx.x & 7;
+    const unsigned gmask = 0xffu << (8 * (grp & 3));   // the 8 lanes of this group (trip counts differ between groups)
+    const int per = (NTP + 7) / 8;
+    const int nent = n_list;
+    for (int e = grp; e < nent; e += GROUPS) {
+      const int th = list[e];
+      const int nls = th * SPT;
+      // the entry thread's r0: floor row of its first frame
+      const int n_first = min(t0 + nls, T - 1);
+      int lo0 = __float_as_int(rowtab[n_first].x);
+      if (n_first >= wrap) lo0 += F;
+      const float *rc = rows + (size_t)(lo0 - rmin + 2) * NTP;
+      const int i0 = l8 * per, i1 = min(NTP, i0 + per);
+      float acc[SPT], Wd[SPT];
+#pragma unroll
+      for (int u = 0; u < SPT; ++u) acc[u] = 0.0f;
+#pragma unroll
+      for (int u = 0; u < SPT - 1; ++u) {
+        const int m = nls + u + i0;
+        Wd[u + 1] = xs[(m % SPT) * Q + m / SPT];
+      }
+      for (int i = i0; i < i1; ++i) {
+#pragma unroll
+        for (int u = 0; u < SPT - 1; ++u) Wd[u] = Wd[u + 1];
+        const int m = nls + SPT - 1 + i;
+        Wd[SPT - 1] = xs[(m % SPT) * Q + m / SPT];
+        const float tc = rc[i];
+#pragma unroll
+        for (int u = 0; u < SPT; ++u) acc[u] = fmaf(Wd[u], tc, acc[u]);
+      }
+#pragma unroll
+      for (int u = 0; u < SPT; ++u) {
+        float v = acc[u];
+        v += __shfl_xor_sync(gmask, v, 1);
+        v += __shfl_xor_sync(gmask, v, 2);
+        v += __shfl_xor_sync(gmask, v, 4);
+        if (l8 == 0) d2buf[e][u] = v;
+      }
+    }
+  }
+  __syncthreads();
+  if (!have) return;
+  if (my_entry >= 0) {
+#pragma unroll
+    for (int u = 0; u < SPT; ++u) d2[u] = d2buf[my_entry][u];
+  }
+  if (spread > 1 || spread < 0) {
+    // the frames of this thread sit across the clock wrap: evaluate each frame against its own rows
+#pragma unroll
+    for (int u = 0; u < SPT; ++u) {
+      const float *pa = rows + (size_t)(lo[u] - rmin) * NTP, *pb = pa + NTP;
+      float sa = 0.0f, sb = 0.0f;
+      for (int i = 0; i < NT; ++i) {
+        int m = nl + u + i;
+        float xv = xs[(m % SPT) * Q + m / SPT];
+        sa = fmaf(xv, pa[i], sa);
+        sb = fmaf(xv, pb[i], sb);
+      }
+      d0[u] = sa;
+      d1[u] = sb;
+    }
+  }
+  float *dst = audio + (size_t)b * T;
+#pragma unroll
+  for (int u = 0; u < SPT; ++u) {
+    int n = t0 + nl + u;
+    if (n >= T) break;
+    bool second = straddle && lo[u] != lo[0];
+    float a = second ? d1[u] : d0[u], c = second ? d2[u] : d1[u];
+    float omf = 1.0f - fr[u];
+    int l = lo[u] >= F ? lo[u] - F : lo[u], h = l + 1 >= F ? 0 : l + 1;
+    float ng = fmaf(fr[u], ngain[(size_t)h * B + b], omf * ngain[(size_t)l * B + b]);
+    float y = fmaf(fr[u], c, omf * a) * ng * prm.scale;
+    dst[n] = prm.accumulate ? dst[n] + y : y;
+  }
+}
+
 // taps[r][i] = sum_j W[i][j] * bands[r][j]; W is staged once per block and reused for BT_PASSES
 // groups of 16 rows; thread = taps i, i+256, ...
 constexpr int BT_PASSES = 8;
@@ -281,7 +479,29 @@ DGC_EXPORT int32_t dgc_fir_noise(dgc_ctx *ctx, const dgc_fir_params *p, const fl
     return dgc_check_launch(ctx, "fir_noise");
   };
   rc = DGC_ERR_UNSUPPORTED;
-  if (step * 8 < 0.98) {
+  static const int fir_variant = [] {
+    const char *e = getenv("DGC_FIR");
+    return e ? atoi(e) : 128;           // threads per block of the list-based kernel; 0 = the in-loop variant
+  }();
+  if (step * 8 < 0.98 && fir_variant > 0) {
+    int NTP = (NT + 3) & ~3;
+    if (NTP % 8 == 0) NTP += 4;
+    auto launch8 = [&](auto kern, int nth) -> int32_t {
+      const int tile = nth * 8;
+      const int max_rows = (int)(step * tile) + 5;
+      const int XN = tile + NTP - 1 + 8, Q = (XN + 7) / 8 + 1;
+      const size_t smem = ((size_t)max_rows * NTP + (size_t)8 * Q) * sizeof(float);
+      if (smem > 160 * 1024) return DGC_ERR_UNSUPPORTED;
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return dgc_fail(ctx, DGC_ERR_CUDA, "fir smem opt-in: %s", cudaGetErrorString(e));
+      kern<<<dim3(dgc_div_up(p->T, tile), p->B), nth, smem, ctx->stream>>>(*p, play, noise_dev, taps_dev, noise_gain_dev,
+                                                                            audio_dev, max_rows, NTP, ctx->status_dev);
+      ctx->launches++;
+      return dgc_check_launch(ctx, "fir_noise8");
+    };
+    rc = fir_variant == 256 ? launch8(fir_noise8_kernel<256>, 256) : launch8(fir_noise8_kernel<128>, 128);
+  }
+  if (rc == DGC_ERR_UNSUPPORTED && step * 8 < 0.98) {
     // 256-thread tiles amortise the staged control rows best (measured against 128 and 64 at the headline
     // configuration: 82.5 / 86.5 / 83 us); DGC_FIR_THREADS forces a tile size for experiments
     static const int forced = [] {

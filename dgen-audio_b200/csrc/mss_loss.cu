@@ -165,12 +165,7 @@ __device__ __forceinline__ void pair_terms(float2 zk, float2 zn, float &lin, flo
   lin += fabsf(m1 - m2);
   lg += fabsf(__log2f(m1 + 2.0f * LOG_EPS) - __log2f(m2 + 2.0f * LOG_EPS));
 }
-// a bin that is its own partner (k = 0 and k = N/2): X1 = Re z, X2 = Im z
-__device__ __forceinline__ void self_terms(float2 z, float &lin, float &lg) {
-  const float m1 = 2.0f * fabsf(z.x), m2 = 2.0f * fabsf(z.y);
-  lin += fabsf(m1 - m2);
-  lg += fabsf(__log2f(m1 + 2.0f * LOG_EPS) - __log2f(m2 + 2.0f * LOG_EPS));
-}
+// (a bin that is its own partner, k = 0 or k = N/2, is the pair (z, z): 2 X1 = 2 Re z, 2 X2 = 2 Im z)
 
 template <int N, bool SUM2>
 __device__ __forceinline__ void mss_fwd16_body(float2 *sm, float *red, int bx, int b, const float *__restrict__ pred,
@@ -215,20 +210,28 @@ __device__ __forceinline__ void mss_fwd16_body(float2 *sm, float *red, int bx, i
   float2 z[Gm::PAIRS][2][RL];
   dgfft16::fft16<N, false>(x, z, bufa, bufb, lt, tw);
   float lin = 0.0f, lg = 0.0f;
+  // Bin pairs {k, N - k}.  A pair of butterflies (a, N/RL - a) gives RL of them: bin t of the first with bin
+  // RL - 1 - t of the second.  The one thread that holds butterflies 0 and N/(2 RL) instead pairs bins INSIDE each
+  // (0 and N/2 with themselves, t with RL - t; t with RL - 1 - t): RL + 1 terms.  Both cases run the same
+  // instructions on operands picked by a select, so the warp does not execute the terms twice.
+  const bool sp = lt == 0;      // only pair 0 of local thread 0 is the special one
 #pragma unroll
   for (int p = 0; p < Gm::PAIRS; ++p) {
-    if (lt + p * TT != 0) {
+    if (p > 0) {
 #pragma unroll
       for (int t = 0; t < RL; ++t) pair_terms(z[p][0][t], z[p][1][RL - 1 - t], lin, lg);
     } else {
-      // butterfly 0 holds bins t N/RL: 0 and N/2 are their own partners, t pairs with RL - t;
-      // butterfly NBL/2 holds bins N/(2 RL) + t N/RL: t pairs with RL - 1 - t
-      self_terms(z[p][0][0], lin, lg);
-      self_terms(z[p][0][RL / 2], lin, lg);
 #pragma unroll
-      for (int t = 1; t < RL / 2; ++t) pair_terms(z[p][0][t], z[p][0][RL - t], lin, lg);
-#pragma unroll
-      for (int t = 0; t < RL / 2; ++t) pair_terms(z[p][1][t], z[p][1][RL - 1 - t], lin, lg);
+      for (int t = 0; t < RL; ++t) {
+        const float2 ks = t <= RL / 2 ? z[0][0][t] : z[0][1][t - RL / 2 - 1];
+        const float2 ns = t == 0 ? z[0][0][0] : t < RL / 2 ? z[0][0][RL - t] : t == RL / 2 ? z[0][0][RL / 2]
+                                                                                            : z[0][1][RL - 1 - (t - RL / 2 - 1)];
+        const float2 kg = z[0][0][t], ng = z[0][1][RL - 1 - t];
+        const float2 zk = make_float2(sp ? ks.x : kg.x, sp ? ks.y : kg.y);
+        const float2 zn = make_float2(sp ? ns.x : ng.x, sp ? ns.y : ng.y);
+        pair_terms(zk, zn, lin, lg);
+      }
+      if (sp) pair_terms(z[0][1][RL / 2 - 1], z[0][1][RL / 2], lin, lg);
     }
   }
   lin = group_sum<TT>(lin, red, tid);
@@ -247,9 +250,14 @@ mss_fwd16_kernel(const float *__restrict__ pred, const float *__restrict__ pred_
                  int B, int T, const FwdDesc d) {
   extern __shared__ float2 fwd_sm[];
   __shared__ float red[LOSS16_THREADS / 32];
+  // one-dimensional grid, scale-major: first_block[s] counts the blocks of ALL voices of the scales before s, so
+  // the blocks resident on an SM at any time run the same window size (the same instructions) except at the
+  // boundary between two scales
   int s = 0;
   while (s + 1 < d.nscales && (int)blockIdx.x >= d.first_block[s + 1]) ++s;
-  const int bx = blockIdx.x - d.first_block[s], b = blockIdx.y;
+  const int r = blockIdx.x - d.first_block[s];
+  const int per_voice = (d.first_block[s + 1] - d.first_block[s]) / B;
+  const int b = r / per_voice, bx = r - b * per_voice;
   switch (d.N[s]) {
 #define CASE(NN) \
   case NN: mss_fwd16_body<NN, SUM2>(fwd_sm, red, bx, b, pred, pred_b, target, B, T, d.hop[s], d.H[s], d.window[s], d.tw[s], d.lin[s], d.lg[s]); break;
@@ -599,7 +607,7 @@ int32_t dgc_mss_loss_fwd_sum(dgc_ctx *ctx, const dgc_mss_params *p, const float 
     fd.lin[k] = part + off_of[s];
     fd.lg[k] = fd.lin[k] + (long long)H * p->B;
     fd.first_block[k] = blocks;
-    blocks += wide ? dgc_div_up(H, LOSS16_THREADS / (N / 16)) : dgc_div_up(H, LOSS_THREADS / (N / 8));
+    blocks += wide ? dgc_div_up(H, LOSS16_THREADS / (N / 16)) * p->B : dgc_div_up(H, LOSS_THREADS / (N / 8));
     fd.first_block[k + 1] = blocks;
   }
   // resident blocks per SM are limited by shared memory (6 x 34 KB): ask for the largest carve-out
@@ -613,10 +621,10 @@ int32_t dgc_mss_loss_fwd_sum(dgc_ctx *ctx, const dgc_mss_params *p, const float 
   (void)carved;
   if (fd16.nscales > 0) {
     if (pred_b_dev)
-      mss_fwd16_kernel<true><<<dim3(blocks16, p->B), LOSS16_THREADS, FWD16_SMEM_BYTES, ctx->stream>>>(
+      mss_fwd16_kernel<true><<<blocks16, LOSS16_THREADS, FWD16_SMEM_BYTES, ctx->stream>>>(
           pred_dev, pred_b_dev, target_dev, p->B, p->T, fd16);
     else
-      mss_fwd16_kernel<false><<<dim3(blocks16, p->B), LOSS16_THREADS, FWD16_SMEM_BYTES, ctx->stream>>>(
+      mss_fwd16_kernel<false><<<blocks16, LOSS16_THREADS, FWD16_SMEM_BYTES, ctx->stream>>>(
           pred_dev, nullptr, target_dev, p->B, p->T, fd16);
     DGC_LAUNCHED(ctx, "mss_fwd16");
   }

@@ -63,6 +63,7 @@ class HarmonicModel:
         self.t_dev = torch.zeros(1, dtype=torch.int32, device=dev)
         self.corr = torch.zeros(2, dtype=torch.float32, device=dev)
         self.graph, self.graph_stream = None, None   # list of recordings (see capture)
+        self.exchange_events = None   # a list: replay() appends a CUDA event pair around every gradient exchange
         f = lambda *s: torch.empty(*s, dtype=torch.float32, device=dev)
         M, H = self.M, hidden
         self.act = [f(M, H), f(M, H), f(M, H), f(M, K + nbands)]
@@ -266,7 +267,14 @@ class HarmonicModel:
         with self.ctx.on_stream(s), torch.cuda.stream(s):
             self.graph[0].launch()
             if len(self.graph) > 1:
-                self._exchange()
+                if self.exchange_events is not None:
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    self._exchange()
+                    e1.record()
+                    self.exchange_events.append((e0, e1))
+                else:
+                    self._exchange()
                 self.graph[1].launch()
         cur.wait_stream(s)
         self.step_index += 1
