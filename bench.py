@@ -674,7 +674,10 @@ def train_measure(ctx, args, rank, world, local_rank, steps, voices=32, want_e2e
                 noise_gain=d["noise_gain"], noise=d["noise"], W=d["W"], target=target.cpu().numpy())
     order = ("X", "f0", "uv", "gain", "noise_gain", "noise", "W", "target")
     P = {k: pin(host[k]) for k in order}
-    D = {k: dev(host[k]) for k in order}
+    # the step's inputs live in the model's arena: fill them in place (no per-step device-to-device copies)
+    D = dict(zip(order, model.input_views()))
+    for k in order:
+        D[k].copy_(torch.from_numpy(np.ascontiguousarray(host[k])).reshape(D[k].shape))
     dargs = [D[k] for k in order]
     del G
 
@@ -764,8 +767,7 @@ def train_measure(ctx, args, rank, world, local_rank, steps, voices=32, want_e2e
     glob_loss = sharding.global_mean_loss(loss_host, B, device="cuda")
     n_params = model.n_params
     used_ctx_comm = bool(model.use_ctx_comm)
-    for g in model.graph or []:
-        g.close()
+    model.close()
     if used_ctx_comm:
         ctx.lib.dgc_comm_destroy(ctx.h)
     del model, D, P

@@ -66,6 +66,14 @@ struct dgc_ctx {
   int64_t capture_launches0 = 0;
 };
 
+// the caller-owned flat float arena (device memory) of dgc_arena_create
+struct dgc_arena {
+  dgc_ctx *ctx;
+  float *ptr;
+  uint64_t n;
+  bool owned = true;   // false: the memory belongs to the caller (dgc_arena_wrap)
+};
+
 int32_t dgc_fail(dgc_ctx *ctx, int32_t code, const char *fmt, ...);
 int32_t dgc_check_launch(dgc_ctx *ctx, const char *what);
 // returns device pointer to at least n floats of context scratch (nullptr + error set on failure)

@@ -8,12 +8,6 @@
 
 #include "common.cuh"
 
-struct dgc_arena {
-  dgc_ctx *ctx;
-  float *ptr;
-  uint64_t n;
-};
-
 int32_t dgc_fail(dgc_ctx *ctx, int32_t code, const char *fmt, ...) {
   if (ctx) {
     va_list ap;
@@ -268,15 +262,24 @@ DGC_EXPORT int32_t dgc_arena_create(dgc_ctx *ctx, uint64_t nfloats, dgc_arena **
   if (nfloats < 1024) nfloats = 1024;
   float *p = nullptr;
   DGC_CUDA(ctx, cudaMalloc(&p, nfloats * sizeof(float)));
-  dgc_arena *a = new dgc_arena{ctx, p, nfloats};
+  dgc_arena *a = new dgc_arena{ctx, p, nfloats, true};
   *out = a;
   return dgc_arena_zero(a);
+}
+
+DGC_EXPORT int32_t dgc_arena_wrap(dgc_ctx *ctx, float *dev, uint64_t nfloats, dgc_arena **out) {
+  if (!ctx || !out) return DGC_ERR_INVALID;
+  *out = nullptr;
+  DGC_REQUIRE(ctx, dev && nfloats > 0, "null memory or zero size");
+  DGC_REQUIRE(ctx, (((uintptr_t)dev) & 255) == 0, "the memory must be 256-byte aligned");
+  *out = new dgc_arena{ctx, dev, nfloats, false};
+  return DGC_OK;
 }
 
 DGC_EXPORT int32_t dgc_arena_destroy(dgc_arena *a) {
   if (!a) return DGC_ERR_INVALID;
   cudaStreamSynchronize(a->ctx->stream);
-  cudaFree(a->ptr);
+  if (a->owned) cudaFree(a->ptr);
   delete a;
   return DGC_OK;
 }

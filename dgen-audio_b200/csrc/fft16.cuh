@@ -199,4 +199,82 @@ __device__ __forceinline__ void fft16(float2 (&x)[16], float2 (&z)[Geo<N>::PAIRS
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// The transposed network.  The DFT matrix is symmetric, so running the three stages in REVERSE order, each one
+// transposed (butterfly first, then the twiddles; reads where the forward stage wrote, writes where it read),
+// computes the same transform -- but takes its input in the bin layout the forward leaves in registers
+// (y[p][e][t] = bin j_e + t NBL of last_pair) and returns element tid + m N/16 in x[m].  A spectrum that was
+// built in the registers of a forward transform's result therefore goes back to the time domain, in the
+// layout a coalesced store (or the overlap-add) wants, without any reordering pass.
+// ---------------------------------------------------------------------------------------------------------
+// v[t] *= w^t, after the butterfly (same table access as twiddle())
+template <int N, bool INV>
+__device__ __forceinline__ void stage_last_T(float2 (&y)[Geo<N>::PAIRS][2][Geo<N>::RL], float2 *out, int tid,
+                                             const float2 *__restrict__ tw) {
+  constexpr int R = Geo<N>::RL, NBL = Geo<N>::NBL;
+#pragma unroll
+  for (int p = 0; p < Geo<N>::PAIRS; ++p) {
+    int jj[2];
+    last_pair<N>(tid, p, jj[0], jj[1]);
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int j = jj[e];
+      dftN<R, INV>(y[p][e]);
+      twiddle<R, INV>(y[p][e], tw, j);
+#pragma unroll
+      for (int t = 0; t < R; ++t) out[pad(j + t * NBL)] = y[p][e][t];
+    }
+  }
+}
+
+template <int N, bool INV>
+__device__ __forceinline__ void stage_middle_T(const float2 *in, float2 *out, int tid, const float2 *__restrict__ tw) {
+  constexpr int R = Plan<N>::R2, PER = 16 / R, T = N / 16, Ns = Plan<N>::R1;
+#pragma unroll
+  for (int q = 0; q < PER; ++q) {
+    const int j = tid + q * T, k = j & (Ns - 1);
+    const int j0 = (j - k) * R + k;
+    float2 v[R];
+#pragma unroll
+    for (int t = 0; t < R; ++t) v[t] = in[pad(j0 + t * Ns)];
+    dftN<R, INV>(v);
+    twiddle<R, INV>(v, tw, k * (N / (Ns * R)));
+#pragma unroll
+    for (int t = 0; t < R; ++t) out[pad(j + t * (N / R))] = v[t];
+  }
+}
+
+template <int N, bool INV>
+__device__ __forceinline__ void stage_first_T(const float2 *buf, float2 (&x)[16], int tid) {
+  constexpr int R = Plan<N>::R1, PER = 16 / R, T = N / 16;
+#pragma unroll
+  for (int q = 0; q < PER; ++q) {
+    const int j = tid + q * T;
+    float2 v[R];
+#pragma unroll
+    for (int t = 0; t < R; ++t) v[t] = buf[pad(j * R + t)];
+    dftN<R, INV>(v);
+#pragma unroll
+    for (int t = 0; t < R; ++t) x[q + PER * t] = v[t];
+  }
+}
+
+// Transform of a spectrum held in the forward's register layout: y in (destroyed), x[m] = element tid + m N/16 out.
+// The first write goes to the buffer the forward's last stage read, so a caller that has just finished a forward
+// transform with the same buffers only has to make sure (sync_transform) that every thread is done reading it.
+template <int N, bool INV>
+__device__ __forceinline__ void fft16_T(float2 (&y)[Geo<N>::PAIRS][2][Geo<N>::RL], float2 (&x)[16], float2 *bufa,
+                                        float2 *bufb, int tid, const float2 *__restrict__ tw) {
+  if (Geo<N>::THREE) {
+    stage_last_T<N, INV>(y, bufb, tid, tw);
+    sync_transform<N>();
+    stage_middle_T<N, INV>(bufb, bufa, tid, tw);
+    sync_transform<N>();
+  } else {
+    stage_last_T<N, INV>(y, bufa, tid, tw);
+    sync_transform<N>();
+  }
+  stage_first_T<N, INV>(bufa, x, tid);
+}
+
 }  // namespace dgfft16

@@ -137,13 +137,14 @@ onepole_kernel(const float *__restrict__ x, int T, int NC, float a, const float 
 }
 
 // carry[c] = state entering chunk c; serial over chunks (few), one thread per voice
+// y0_dev (optional): per-voice state entering the first chunk (the history cell before the call), else y0
 __global__ void onepole_carry_kernel(const float *__restrict__ chunk_end, int B, int NC, float a, float y0,
-                                     float *__restrict__ carry) {
+                                     float *__restrict__ carry, const float *__restrict__ y0_dev = nullptr) {
   int b = blockIdx.x * blockDim.x + threadIdx.x;
   if (b >= B) return;
   float ac = 1.0f;
   for (int i = 0; i < OP_CHUNK; ++i) ac *= a;
-  float s = y0;
+  float s = y0_dev ? y0_dev[b] : y0;
   for (int c = 0; c < NC; ++c) {
     carry[(size_t)b * NC + c] = s;
     s = fmaf(ac, s, chunk_end[(size_t)b * NC + c]);
@@ -177,7 +178,7 @@ __device__ __forceinline__ Dual dselect(float mode1, const Dual *opt, int n) {
   return dconst(0.f);
 }
 
-// Graph.biquad coefficient DAG (Sources/DGen/HigherOps.swift:444-555), modes 0..5, node by node.
+// Graph.biquad coefficient DAG (Sources/DGen/HigherOps.swift:444-555), all eight modes, node by node.
 // coef layout per lane: b0 b1 b2 a1 a2, then d/dcutoff of the five, then d/dq of the five.
 __global__ void biquad_coef_kernel(const float *__restrict__ cutoff, const float *__restrict__ q, int L, float gain,
                                    float mode, float *__restrict__ coef) {
@@ -204,14 +205,35 @@ __global__ void biquad_coef_kernel(const float *__restrict__ cutoff, const float
   Dual mult26 = dmul(recip24, dconst(gain));
   Dual mult31 = dmul(mult9, dconst(2.f));
   Dual not_sub35 = dsub(dconst(1.f), div18);
-  Dual o23[6] = {div11, div13, mult19, mult21, dconst(1.f), add22};
-  Dual o32[6] = {add10, sub12, dconst(0.f), dconst(0.f), mult31, mult31};
-  Dual o36[6] = {div11, div13, div18, mult20, dconst(1.f), not_sub35};
-  Dual b2 = dmul(dselect(add4, o23, 6), mult26);
-  Dual b1 = dmul(dselect(add4, o32, 6), mult26);
-  Dual b0 = dmul(dselect(add4, o36, 6), mult26);
-  Dual a2 = dmul(not_sub35, recip24);
-  Dual a1 = dmul(mult31, recip24);
+  // shelf coefficients, modes 6 (high shelf) and 7 (low shelf): HigherOps.swift:468-528; A depends on the gain only
+  const float Af = sqrtf(fabsf(gain));
+  Dual A = dconst(Af);
+  Dual cosW0Pos = dmul(mult9, dconst(-1.f));
+  Dual alphaShelf = ddiv(sin14, dmul(dconst(2.0f), abs17));
+  Dual Ap1 = dconst(Af + 1.0f), Am1 = dconst(Af - 1.0f);
+  Dual Ap1_cos = dmul(Ap1, cosW0Pos), Am1_cos = dmul(Am1, cosW0Pos);
+  Dual tsa = dmul(dconst(2.0f * sqrtf(Af)), alphaShelf);
+  Dual hs_b0 = dmul(A, dadd(dadd(Ap1, Am1_cos), tsa));
+  Dual hs_b1 = dmul(dconst(-2.0f), dmul(A, dadd(Am1, Ap1_cos)));
+  Dual hs_b2 = dmul(A, dsub(dadd(Ap1, Am1_cos), tsa));
+  Dual hs_a0 = dadd(dsub(Ap1, Am1_cos), tsa);
+  Dual ls_b0 = dmul(A, dadd(dsub(Ap1, Am1_cos), tsa));
+  Dual ls_b1 = dmul(dconst(2.0f), dmul(A, dsub(Am1, Ap1_cos)));
+  Dual ls_b2 = dmul(A, dsub(dsub(Ap1, Am1_cos), tsa));
+  Dual ls_a0 = dadd(dadd(Ap1, Am1_cos), tsa);
+  Dual hs_a1n = ddiv(dmul(dconst(2.0f), dsub(Am1, Ap1_cos)), hs_a0), hs_a2n = ddiv(dsub(dsub(Ap1, Am1_cos), tsa), hs_a0);
+  Dual ls_a1n = ddiv(dmul(dconst(-2.0f), dadd(Am1, Ap1_cos)), ls_a0), ls_a2n = ddiv(dsub(dadd(Ap1, Am1_cos), tsa), ls_a0);
+  Dual o23[8] = {div11, div13, mult19, mult21, dconst(1.f), add22, ddiv(hs_b2, hs_a0), ddiv(ls_b2, ls_a0)};
+  Dual o32[8] = {add10, sub12, dconst(0.f), dconst(0.f), mult31, mult31, ddiv(hs_b1, hs_a0), ddiv(ls_b1, ls_a0)};
+  Dual o36[8] = {div11, div13, div18, mult20, dconst(1.f), not_sub35, ddiv(hs_b0, hs_a0), ddiv(ls_b0, ls_a0)};
+  // modes 0-5 scale by gain / a0; the shelves carry the gain in A (isShelfMode = mode >= 6, :533-548)
+  const bool shelf = mode >= 6.0f;
+  Dual s23 = dselect(add4, o23, 8), s32 = dselect(add4, o32, 8), s36 = dselect(add4, o36, 8);
+  Dual b2 = shelf ? s23 : dmul(s23, mult26);
+  Dual b1 = shelf ? s32 : dmul(s32, mult26);
+  Dual b0 = shelf ? s36 : dmul(s36, mult26);
+  Dual a2 = shelf ? (mode >= 7.0f ? ls_a2n : hs_a2n) : dmul(not_sub35, recip24);
+  Dual a1 = shelf ? (mode >= 7.0f ? ls_a1n : hs_a1n) : dmul(mult31, recip24);
   float *c = coef + (size_t)l * 15;
   c[0] = b0.v; c[1] = b1.v; c[2] = b2.v; c[3] = a1.v; c[4] = a2.v;
   c[5] = b0.dc; c[6] = b1.dc; c[7] = b2.dc; c[8] = a1.dc; c[9] = a2.dc;
@@ -260,7 +282,8 @@ __global__ void biquad_trans_kernel(const float *__restrict__ coef, int L, int l
 template <int PHASE>
 __global__ void __launch_bounds__(BQ_THREADS)
 biquad_fwd_kernel(const float *__restrict__ x, const float *__restrict__ coef, int B, int T, int L, int NC,
-                  float *__restrict__ state /* [B][NC][L][2] */, float *__restrict__ y) {
+                  float *__restrict__ state /* [B][NC][L][2] */, float *__restrict__ y,
+                  const float *__restrict__ st0 = nullptr /* [B][4][L]: history cells before the call */) {
   const int l = blockIdx.x * BQ_THREADS + threadIdx.x, c = blockIdx.y, b = blockIdx.z;
   __shared__ float xs[BQ_CHUNK + 2];
   const float *xb = x + (size_t)b * T;
@@ -279,6 +302,10 @@ biquad_fwd_kernel(const float *__restrict__ x, const float *__restrict__ coef, i
     y2 = st[1];
   }
   float x2 = xs[0], x1 = xs[1];
+  if (st0 && c == 0) {   // x[-1], x[-2] come from the history cells
+    x1 = st0[((size_t)b * 4 + 2) * L + l];
+    x2 = st0[((size_t)b * 4 + 3) * L + l];
+  }
   float *yo = y + ((size_t)b * T + n0) * L + l;
 #pragma unroll 4
   for (int n = 0; n < len; ++n) {
@@ -335,15 +362,16 @@ __global__ void biquad_endstate_table_kernel(const float *__restrict__ coef, int
 
 // adds the x-history terms to the matrix-product states
 __global__ void biquad_state_hist_kernel(const float *__restrict__ x, const float *__restrict__ hist, int B, int T, int L,
-                                         int NC, float *__restrict__ state) {
+                                         int NC, float *__restrict__ state, const float *__restrict__ st0 = nullptr) {
   const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (size_t)B * NC * L) return;
   const int l = (int)(idx % L);
   const size_t bc = idx / L;
   const int c = (int)(bc % NC), b = (int)(bc / NC);
-  if (c == 0) return;   // no history before the first chunk
+  if (c == 0 && !st0) return;   // no history before the first chunk
   const float *xb = x + (size_t)b * T + (size_t)c * BQ_CHUNK;
-  const float x1 = xb[-1], x2 = xb[-2];
+  const float x1 = c == 0 ? st0[((size_t)b * 4 + 2) * L + l] : xb[-1];
+  const float x2 = c == 0 ? st0[((size_t)b * 4 + 3) * L + l] : xb[-2];
   float2 *st = reinterpret_cast<float2 *>(state) + idx;
   float2 v = *st;
   v.x += hist[l * 4 + 0] * x1 + hist[l * 4 + 2] * x2;
@@ -358,7 +386,8 @@ constexpr int BQ4_CHUNKS = 4;
 template <int PHASE>
 __global__ void __launch_bounds__(256)
 biquad_fwd4_kernel(const float *__restrict__ x, const float *__restrict__ coef, int B, int T, int L, int NC,
-                   float *__restrict__ state /* [B][NC][L][2] */, float *__restrict__ y) {
+                   float *__restrict__ state /* [B][NC][L][2] */, float *__restrict__ y,
+                   const float *__restrict__ st0 = nullptr /* [B][4][L]: history cells before the call */) {
   __shared__ float xs[BQ4_CHUNKS][BQ_CHUNK + 2];
   const int lq = blockIdx.x * blockDim.x + threadIdx.x, cy = threadIdx.y;
   const int c = blockIdx.y * BQ4_CHUNKS + cy, b = blockIdx.z;
@@ -382,6 +411,10 @@ biquad_fwd4_kernel(const float *__restrict__ x, const float *__restrict__ coef, 
     y1[2] = s1.x; y2[2] = s1.y; y1[3] = s1.z; y2[3] = s1.w;
   }
   float x2 = xs[cy][0], x1 = xs[cy][1];
+  if (st0 && c == 0) {   // x[-1], x[-2] come from the history cells (one input feeds all lanes: the first lane's)
+    x1 = st0[((size_t)b * 4 + 2) * L + 4 * lq];
+    x2 = st0[((size_t)b * 4 + 3) * L + 4 * lq];
+  }
   float *yo = y + ((size_t)b * T + n0) * L + 4 * lq;
 #pragma unroll 2
   for (int n = 0; n < len; ++n) {
@@ -405,13 +438,14 @@ biquad_fwd4_kernel(const float *__restrict__ x, const float *__restrict__ coef, 
 
 // state[c] <- state entering chunk c (exclusive scan of the affine maps), thread per (voice, lane)
 __global__ void biquad_carry_kernel(const double *__restrict__ trans, int B, int L, int NC,
-                                    float *__restrict__ state) {
+                                    float *__restrict__ state, const float *__restrict__ st0 = nullptr) {
   int idx = blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= B * L) return;
   int b = idx / L, l = idx - b * L;
   const double m11 = trans[(size_t)l * 4], m12 = trans[(size_t)l * 4 + 1], m21 = trans[(size_t)l * 4 + 2],
                m22 = trans[(size_t)l * 4 + 3];
-  double s1 = 0.0, s2 = 0.0;
+  // y[-1], y[-2]: the history cells before the call, else rest
+  double s1 = st0 ? (double)st0[((size_t)b * 4 + 0) * L + l] : 0.0, s2 = st0 ? (double)st0[((size_t)b * 4 + 1) * L + l] : 0.0;
   for (int c = 0; c < NC; ++c) {
     float *st = state + (((size_t)b * NC + c) * L + l) * 2;
     double e1 = st[0], e2 = st[1];
@@ -683,10 +717,36 @@ DGC_EXPORT int32_t dgc_onepole_fwd(dgc_ctx *ctx, const float *x_dev, int32_t B, 
   return DGC_OK;
 }
 
+__global__ void onepole_final_state_kernel(const float *__restrict__ y, int B, int T, float *__restrict__ state) {
+  int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b < B) state[b] = y[(size_t)b * T + T - 1];
+}
+
+DGC_EXPORT int32_t dgc_onepole_fwd_state(dgc_ctx *ctx, const float *x_dev, int32_t B, int32_t T, float a,
+                                         float *state_dev, float *y_dev) {
+  if (!ctx) return DGC_ERR_INVALID;
+  if (!state_dev) return dgc_onepole_fwd(ctx, x_dev, B, T, a, y_dev);
+  DGC_REQUIRE(ctx, x_dev && y_dev, "null pointer");
+  DGC_REQUIRE(ctx, B > 0 && T > 0, "size out of range");
+  const int NC = dgc_div_up(T, OP_CHUNK);
+  float *scr = dgc_ctx_scratch(ctx, 2ull * B * NC + 8);
+  if (!scr) return DGC_ERR_OOM;
+  float *chunk_end = scr, *carry = scr + (size_t)B * NC;
+  onepole_kernel<0><<<dim3(NC, B), OP_THREADS, 0, ctx->stream>>>(x_dev, T, NC, a, nullptr, chunk_end, nullptr);
+  DGC_LAUNCHED(ctx, "onepole_pass0");
+  onepole_carry_kernel<<<dgc_div_up(B, 64), 64, 0, ctx->stream>>>(chunk_end, B, NC, a, 0.0f, carry, state_dev);
+  DGC_LAUNCHED(ctx, "onepole_carry");
+  onepole_kernel<1><<<dim3(NC, B), OP_THREADS, 0, ctx->stream>>>(x_dev, T, NC, a, carry, nullptr, y_dev);
+  DGC_LAUNCHED(ctx, "onepole_pass1");
+  onepole_final_state_kernel<<<dgc_div_up(B, 128), 128, 0, ctx->stream>>>(y_dev, B, T, state_dev);
+  DGC_LAUNCHED(ctx, "onepole_final_state");
+  return DGC_OK;
+}
+
 static int32_t biquad_validate(dgc_ctx *ctx, const dgc_biquad_params *p) {
   DGC_REQUIRE(ctx, p->B > 0 && p->T > 0 && p->L > 0, "size out of range");
   DGC_REQUIRE(ctx, p->B <= 65535, "B must be <= 65535");
-  DGC_REQUIRE(ctx, p->mode >= 0.0f && p->mode <= 5.0f, "mode must be in 0..5");
+  DGC_REQUIRE(ctx, p->mode >= 0.0f && p->mode <= 7.0f, "mode must be in 0..7");
   return DGC_OK;
 }
 
@@ -704,8 +764,38 @@ DGC_EXPORT uint64_t dgc_biquad_scratch_floats(const dgc_biquad_params *p, int32_
   return base + 2 * (uint64_t)p->B * NC * p->L + blocks * (uint64_t)p->B * p->T + 16;
 }
 
+// history cells after the call: y[T-1], y[T-2], x[T-1], x[T-2] per (voice, lane); frames before the call come
+// from the cells as they were
+__global__ void biquad_final_state_kernel(const float *__restrict__ x, const float *__restrict__ y, int B, int T, int L,
+                                          float *__restrict__ st) {
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= B * L) return;
+  const int b = idx / L, l = idx - b * L;
+  float *s = st + (size_t)b * 4 * L + l;
+  const float *yb = y + (size_t)b * T * L + l, *xb = x + (size_t)b * T;
+  const float oy1 = s[0], ox1 = s[2 * L];
+  s[0] = yb[(size_t)(T - 1) * L];
+  s[L] = T >= 2 ? yb[(size_t)(T - 2) * L] : oy1;
+  s[2 * L] = xb[T - 1];
+  s[3 * L] = T >= 2 ? xb[T - 2] : ox1;
+}
+
+static int32_t biquad_fwd_impl(dgc_ctx *ctx, const dgc_biquad_params *p, const float *x_dev, const float *cutoff_dev,
+                               const float *q_dev, float *scratch_dev, float *st0, float *y_dev);
+
 DGC_EXPORT int32_t dgc_biquad_fwd(dgc_ctx *ctx, const dgc_biquad_params *p, const float *x_dev,
                                   const float *cutoff_dev, const float *q_dev, float *scratch_dev, float *y_dev) {
+  return biquad_fwd_impl(ctx, p, x_dev, cutoff_dev, q_dev, scratch_dev, nullptr, y_dev);
+}
+
+DGC_EXPORT int32_t dgc_biquad_fwd_state(dgc_ctx *ctx, const dgc_biquad_params *p, const float *x_dev,
+                                        const float *cutoff_dev, const float *q_dev, float *scratch_dev,
+                                        float *state_dev, float *y_dev) {
+  return biquad_fwd_impl(ctx, p, x_dev, cutoff_dev, q_dev, scratch_dev, state_dev, y_dev);
+}
+
+static int32_t biquad_fwd_impl(dgc_ctx *ctx, const dgc_biquad_params *p, const float *x_dev, const float *cutoff_dev,
+                               const float *q_dev, float *scratch_dev, float *st0, float *y_dev) {
   if (!ctx) return DGC_ERR_INVALID;
   DGC_REQUIRE(ctx, p && x_dev && cutoff_dev && q_dev && y_dev, "null pointer");
   int32_t rc = biquad_validate(ctx, p);
@@ -736,15 +826,19 @@ DGC_EXPORT int32_t dgc_biquad_fwd(dgc_ctx *ctx, const dgc_biquad_params *p, cons
     DGC_LAUNCHED(ctx, "biquad_endstate_table");
     rc = dgc_gemm_nt(ctx, x_dev, G, B * NC, 2 * L, BQ_CHUNK, state);
     if (rc != DGC_OK) return rc;
-    biquad_state_hist_kernel<<<dgc_div_up((int64_t)B * NC * L, 256), 256, 0, ctx->stream>>>(x_dev, hist, B, T, L, NC, state);
-  } else if (quad) biquad_fwd4_kernel<0><<<grid4, block4, 0, ctx->stream>>>(x_dev, coef, B, T, L, NC, state, nullptr);
-  else biquad_fwd_kernel<0><<<grid, BQ_THREADS, 0, ctx->stream>>>(x_dev, coef, B, T, L, NC, state, nullptr);
+    biquad_state_hist_kernel<<<dgc_div_up((int64_t)B * NC * L, 256), 256, 0, ctx->stream>>>(x_dev, hist, B, T, L, NC, state, st0);
+  } else if (quad) biquad_fwd4_kernel<0><<<grid4, block4, 0, ctx->stream>>>(x_dev, coef, B, T, L, NC, state, nullptr, st0);
+  else biquad_fwd_kernel<0><<<grid, BQ_THREADS, 0, ctx->stream>>>(x_dev, coef, B, T, L, NC, state, nullptr, st0);
   DGC_LAUNCHED(ctx, "biquad_fwd_state");
-  biquad_carry_kernel<<<dgc_div_up(B * L, 128), 128, 0, ctx->stream>>>(trans, B, L, NC, state);
+  biquad_carry_kernel<<<dgc_div_up(B * L, 128), 128, 0, ctx->stream>>>(trans, B, L, NC, state, st0);
   DGC_LAUNCHED(ctx, "biquad_carry");
-  if (quad) biquad_fwd4_kernel<1><<<grid4, block4, 0, ctx->stream>>>(x_dev, coef, B, T, L, NC, state, y_dev);
-  else biquad_fwd_kernel<1><<<grid, BQ_THREADS, 0, ctx->stream>>>(x_dev, coef, B, T, L, NC, state, y_dev);
+  if (quad) biquad_fwd4_kernel<1><<<grid4, block4, 0, ctx->stream>>>(x_dev, coef, B, T, L, NC, state, y_dev, st0);
+  else biquad_fwd_kernel<1><<<grid, BQ_THREADS, 0, ctx->stream>>>(x_dev, coef, B, T, L, NC, state, y_dev, st0);
   DGC_LAUNCHED(ctx, "biquad_fwd_out");
+  if (st0) {
+    biquad_final_state_kernel<<<dgc_div_up(B * L, 128), 128, 0, ctx->stream>>>(x_dev, y_dev, B, T, L, st0);
+    DGC_LAUNCHED(ctx, "biquad_final_state");
+  }
   return DGC_OK;
 }
 

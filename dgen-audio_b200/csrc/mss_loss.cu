@@ -450,6 +450,227 @@ mss_bwd_kernel(const float *__restrict__ pred, const float *__restrict__ target,
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Backward, register-blocked (fft16.cuh): same block organisation as mss_bwd_kernel (a block owns the output frames
+// whose first covering window lies in its range, recomputes every window that covers them, sums the covering
+// windows per output frame in ascending order), but every transform keeps sixteen points per thread:
+//   forward of window A  -> spectral gradient of A written into the REAL lane of a register spectrum Y, bins k and
+//                           N - k side by side in the thread that holds both (Hermitian extension for free);
+//   forward of window B  -> the same into the IMAGINARY lane of Y;
+//   transposed network   -> Y goes back to the time domain straight from those registers and arrives as element
+//                           tid + m N/16 per thread: window, store, done.
+// Two shared-memory exchanges per transform instead of four round trips, no pass that builds or symmetrises the
+// gradient spectrum in shared memory, two transform buffers instead of three.
+// ---------------------------------------------------------------------------------------------
+template <int N>
+struct Bwd16Geom {
+  static constexpr int TT = N / 16;
+  static constexpr int NF = LOSS16_THREADS / TT;                   // window pairs per round
+  static constexpr int WR = 2 * NF;                                // windows per round
+  static constexpr int ROUNDS = WR >= 16 ? 1 : 16 / WR;            // at least 16 windows per block
+  static constexpr int WB = WR * ROUNDS;                           // windows per block
+};
+
+// Gradient of the two loss terms with respect to the spectrum of the prediction, one {k, N - k} pair of bins of
+// z = FFT(x1 + i x2).  hk = half the gradient at bin k; lane 0 adds (hk, conj hk) to (Yk, Yn), lane 1 adds i times that.
+__device__ __forceinline__ void grad_pair(float2 zk, float2 zn, float c_lin, float c_log2, int lane, float2 &Yk,
+                                          float2 &Yn) {
+  const float ax = zk.x + zn.x, ay = zk.y - zn.y;     // 2 X1[k]
+  const float bx = zk.y + zn.y, by = zn.x - zk.x;     // 2 X2[k]
+  const float m1 = fast_sqrt(fmaf(ax, ax, ay * ay)), m2 = fast_sqrt(fmaf(bx, bx, by * by));   // 2 |X1|, 2 |X2|
+  const float ld = __log2f(m1 + 2.0f * LOG_EPS) - __log2f(m2 + 2.0f * LOG_EPS);
+  // d/d|X1| of |(|X1| - |X2|)| and of |log(|X1| + eps) - log(|X2| + eps)|, with |X1| = m1 / 2
+  const float gm = c_lin * sgn(m1 - m2) + c_log2 * sgn(ld) / (m1 + 2.0f * LOG_EPS);
+  const float sc = 0.5f * gm / fmaxf(m1, 2e-8f);      // hk = (gm / 2) * X1 / max(|X1|, 1e-8) = sc * (2 X1)
+  const float hx = sc * ax, hy = sc * ay;
+  if (lane == 0) {
+    Yk.x += hx; Yk.y += hy;
+    Yn.x += hx; Yn.y -= hy;
+  } else {  // times i: (x, y) -> (-y, x)
+    Yk.x -= hy; Yk.y += hx;
+    Yn.x += hy; Yn.y += hx;
+  }
+}
+// a bin that is its own partner (0 and N/2): X1 = Re z real, only the real part of the gradient counts
+__device__ __forceinline__ void grad_self(float2 z, float c_lin, float c_log2, int lane, float2 &Y) {
+  const float m1 = 2.0f * fabsf(z.x), m2 = 2.0f * fabsf(z.y);
+  const float ld = __log2f(m1 + 2.0f * LOG_EPS) - __log2f(m2 + 2.0f * LOG_EPS);
+  const float gm = c_lin * sgn(m1 - m2) + c_log2 * sgn(ld) / (m1 + 2.0f * LOG_EPS);
+  const float gre = gm / fmaxf(0.5f * m1, 1e-8f) * z.x;
+  if (lane == 0) Y.x += gre; else Y.y += gre;
+}
+
+template <int N>
+__global__ void __launch_bounds__(LOSS16_THREADS, 4)
+mss_bwd16_kernel(const float *__restrict__ pred, const float *__restrict__ target, int B, int T, int hop, int H,
+                 int S /* windows whose first-covered frames this block owns */, const float *__restrict__ window,
+                 const float2 *__restrict__ tw, float c_lin, float c_log, int accumulate, float *__restrict__ grad) {
+  using Gm = Bwd16Geom<N>;
+  using Ge = dgfft16::Geo<N>;
+  constexpr int TT = Gm::TT, NF = Gm::NF, WR = Gm::WR, RL = Ge::RL;
+  extern __shared__ float2 sm2[];
+  constexpr int PN = padded(N);
+  float2 *bufa_all = sm2, *bufb_all = sm2 + NF * PN;
+  float *tile = reinterpret_cast<float *>(sm2 + 2 * NF * PN);
+  const int tid = threadIdx.x, f = tid / TT, lt = tid % TT;
+  const int b = blockIdx.y;
+  const int hA = blockIdx.x * S;
+  const int p0 = (hA - 1) * hop + 1;          // first owned frame (may be negative for the first block)
+  const int owned = S * hop;
+  const float *x1 = pred + (size_t)b * T, *x2 = target + (size_t)b * T;
+  float2 *bufa = bufa_all + f * PN, *bufb = bufb_all + f * PN;
+  // d/dm of log(m + eps) in terms of the doubled magnitude m' = 2 m: 2 / (m' + 2 eps)
+  const float c_log2 = 2.0f * c_log;
+  for (int o = tid; o < owned; o += LOSS16_THREADS) tile[o] = 0.0f;
+  const int E = (N - 1) / hop;
+  const int nwin = min(S + E, H - hA);        // windows this block must visit
+  for (int r0 = 0; r0 < nwin; r0 += WR) {
+    const int hr0 = hA + r0;
+    float2 Y[Ge::PAIRS][2][RL];
+#pragma unroll
+    for (int p = 0; p < Ge::PAIRS; ++p)
+#pragma unroll
+      for (int e = 0; e < 2; ++e)
+#pragma unroll
+        for (int t = 0; t < RL; ++t) Y[p][e][t] = make_float2(0.f, 0.f);
+#pragma unroll 1
+    for (int w = 0; w < 2; ++w) {
+      const int h = hr0 + 2 * f + w;
+      const bool valid = h < H && (h - hA) < nwin;
+      const int t_base = h * hop - (N - 1);
+      float2 x[16];
+      if (valid && t_base >= 0) {
+        const float *p1 = x1 + t_base + lt, *p2 = x2 + t_base + lt, *wp = window + lt;
+#pragma unroll
+        for (int m = 0; m < 16; ++m) {
+          const float wv = __ldg(wp + m * TT);
+          x[m] = make_float2(p1[m * TT] * wv, p2[m * TT] * wv);
+        }
+      } else {
+#pragma unroll
+        for (int m = 0; m < 16; ++m) {
+          const int i = lt + m * TT, t = t_base + i;
+          float2 v = make_float2(0.f, 0.f);
+          if (valid && t >= 0) {
+            const float wv = __ldg(&window[i]);
+            v = make_float2(x1[t] * wv, x2[t] * wv);
+          }
+          x[m] = v;
+        }
+      }
+      float2 z[Ge::PAIRS][2][RL];
+      dgfft16::sync_transform<N>();   // the previous transform's last reads of the buffers are done
+      dgfft16::fft16<N, false>(x, z, bufa, bufb, lt, tw);
+      if (valid) {
+#pragma unroll
+        for (int p = 0; p < Ge::PAIRS; ++p) {
+          if (p > 0 || lt != 0) {
+#pragma unroll
+            for (int t = 0; t < RL; ++t) grad_pair(z[p][0][t], z[p][1][RL - 1 - t], c_lin, c_log2, w, Y[p][0][t], Y[p][1][RL - 1 - t]);
+          } else {
+            // butterflies 0 and N/(2 RL): bins pair up inside each of them
+            grad_self(z[0][0][0], c_lin, c_log2, w, Y[0][0][0]);
+            grad_self(z[0][0][RL / 2], c_lin, c_log2, w, Y[0][0][RL / 2]);
+#pragma unroll
+            for (int t = 1; t < RL / 2; ++t) grad_pair(z[0][0][t], z[0][0][RL - t], c_lin, c_log2, w, Y[0][0][t], Y[0][0][RL - t]);
+#pragma unroll
+            for (int t = 0; t < RL / 2; ++t) grad_pair(z[0][1][t], z[0][1][RL - 1 - t], c_lin, c_log2, w, Y[0][1][t], Y[0][1][RL - 1 - t]);
+          }
+        }
+      }
+    }
+    // back to the time domain: un-normalised, + sign (Sources/DGen/Emit+SpectralLoss.swift:577-649)
+    float2 g[16];
+    dgfft16::sync_transform<N>();
+    dgfft16::fft16_T<N, true>(Y, g, bufa, bufb, lt, tw);
+    // bufb is free: the transposed network's last read of it is behind a barrier every thread has passed
+    {
+      const float *wp = window + lt;
+#pragma unroll
+      for (int m = 0; m < 16; ++m) {
+        const float wv = __ldg(wp + m * TT);
+        bufb[pad(lt + m * TT)] = make_float2(g[m].x * wv, g[m].y * wv);
+      }
+    }
+    __syncthreads();
+    const float2 *res = bufb_all;
+    for (int o = tid; o < owned; o += LOSS16_THREADS) {
+      int p = p0 + o;
+      if (p < 0 || p >= T) continue;
+      int hlo = max(hr0, (p + hop - 1) / hop);
+      int hhi = min(min(hr0 + WR - 1, (p + N - 1) / hop), min(H - 1, hA + nwin - 1));
+      float acc = tile[o];
+      for (int h = hlo; h <= hhi; ++h) {
+        int slot = h - hr0;
+        float2 v = res[(slot >> 1) * PN + pad(p - (h * hop - (N - 1)))];
+        acc += (slot & 1) ? v.y : v.x;
+      }
+      tile[o] = acc;
+    }
+    __syncthreads();
+  }
+  float *gout = grad + (size_t)b * T;
+  for (int o = tid; o < owned; o += LOSS16_THREADS) {
+    int p = p0 + o;
+    if (p >= 0 && p < T) gout[p] = accumulate ? gout[p] + tile[o] : tile[o];
+  }
+}
+
+template <int N>
+int32_t launch_bwd16(dgc_ctx *ctx, const dgc_mss_params *p, const float *pred, const float *target, int hop, int H,
+                     float c_lin, float c_log, int accumulate, float *grad) {
+  using Gm = Bwd16Geom<N>;
+  const float *win = dgc_ctx_hann_sym(ctx, N);
+  const float2 *tw = dgc_ctx_twiddles(ctx, N);
+  if (!win || !tw) return DGC_ERR_OOM;
+  const int E = (N - 1) / hop;
+  const int S0 = Gm::WB - E;
+  if (S0 < 1) return dgc_fail(ctx, DGC_ERR_UNSUPPORTED, "hop %d too small for window %d", hop, N);
+  auto smem_of = [&](int S_) {
+    return (size_t)2 * Gm::NF * padded(N) * sizeof(float2) + (size_t)S_ * hop * sizeof(float);
+  };
+  if (smem_of(S0) > 200 * 1024) return dgc_fail(ctx, DGC_ERR_UNSUPPORTED, "backward tile does not fit shared memory");
+  cudaError_t e = cudaFuncSetAttribute(mss_bwd16_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+  if (e != cudaSuccess) return dgc_fail(ctx, DGC_ERR_CUDA, "mss_bwd smem opt-in: %s", cudaGetErrorString(e));
+  cudaFuncSetAttribute(mss_bwd16_kernel<N>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+  // windows owned per block: the choice that minimises (waves of resident blocks x rounds per block), see launch_bwd;
+  // the summation order per output frame does not depend on it
+  int S = S0;
+  {
+    const auto key = std::make_pair(std::make_pair(N, -hop), std::make_pair(H, p->B));   // (-hop: this kernel's own entries)
+    auto it = ctx->mss_bwd_owned.find(key);
+    if (it != ctx->mss_bwd_owned.end()) {
+      S = it->second;
+    } else {
+      long long best = -1;
+      int per_sm0 = 0;
+      for (int cand = S0; cand <= S0 + 24 && cand <= H + E; ++cand) {
+        const size_t sm = smem_of(cand);
+        if (sm > 200 * 1024) break;
+        int per_sm = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, mss_bwd16_kernel<N>, LOSS16_THREADS, sm) != cudaSuccess ||
+            per_sm < 1)
+          break;
+        if (cand == S0) per_sm0 = per_sm;
+        if (per_sm < per_sm0) break;   // a larger tile must not cost resident blocks
+        const long long blocks = (long long)dgc_div_up(H, cand) * p->B, slots = (long long)per_sm * ctx->sm_count;
+        const long long waves = (blocks + slots - 1) / slots;
+        const long long cost = waves * dgc_div_up(cand + E, Gm::WR);
+        if (best < 0 || cost < best) {
+          best = cost;
+          S = cand;
+        }
+      }
+      ctx->mss_bwd_owned[key] = S;
+    }
+  }
+  const size_t smem = smem_of(S);
+  mss_bwd16_kernel<N><<<dim3(dgc_div_up(H, S), p->B), LOSS16_THREADS, smem, ctx->stream>>>(
+      pred, target, p->B, p->T, hop, H, S, win, tw, c_lin, c_log, accumulate, grad);
+  ctx->launches++;
+  return dgc_check_launch(ctx, "mss_bwd16");
+}
+
 template <int N>
 int32_t launch_bwd(dgc_ctx *ctx, const dgc_mss_params *p, const float *pred, const float *target, int hop, int H,
                    float c_lin, float c_log, int accumulate, float *grad) {
@@ -668,9 +889,18 @@ DGC_EXPORT int32_t dgc_mss_loss_bwd(dgc_ctx *ctx, const dgc_mss_params *p, const
     const int N = p->sizes[s];
     if (N > p->T) continue;
     const int hop = hop_of(p, s), H = dgc_div_up(p->T, hop);
-    switch (N) {
-#define CASE(NN) case NN: rc = launch_bwd<NN>(ctx, p, pred_dev, target_dev, hop, H, c_lin, c_log, accumulate, grad_pred_dev); break;
+    static const bool bwd_old = [] {
+      const char *e = getenv("DGC_MSS_BWD");
+      return e && strcmp(e, "r8") == 0;
+    }();
+    // windows of 64 points and more run on the sixteen-points-per-thread kernel
+    const bool wide = N >= 64 && !bwd_old;
+    switch (wide ? N : -N) {
+#define CASE(NN) case -NN: rc = launch_bwd<NN>(ctx, p, pred_dev, target_dev, hop, H, c_lin, c_log, accumulate, grad_pred_dev); break;
       CASE(16) CASE(32) CASE(64) CASE(128) CASE(256) CASE(512) CASE(1024) CASE(2048)
+#undef CASE
+#define CASE(NN) case NN: rc = launch_bwd16<NN>(ctx, p, pred_dev, target_dev, hop, H, c_lin, c_log, accumulate, grad_pred_dev); break;
+      CASE(64) CASE(128) CASE(256) CASE(512) CASE(1024) CASE(2048)
 #undef CASE
       default: return dgc_fail(ctx, DGC_ERR_UNSUPPORTED, "window size %d", N);
     }

@@ -661,32 +661,54 @@ void launch_render_q(dgc_ctx *ctx, const dgc_harmonic_params &p, const float2 *r
                                                                          amps, x.anchors_q, x.fund, g_audio, out);
 }
 
-// out[e][n] = scale * sum_{m > n} g[e][m]: the reverse exclusive scan of the reference's temporalGradScan
-// (Sources/DGen/Emit+TemporalGradient.swift:60-88, no resets).  One block per element row; every thread
-// owns a contiguous run of frames, run totals are scanned in double through shared memory.
+// The reverse scan of the reference's temporalGradScan (Sources/DGen/Emit+TemporalGradient.swift:54-88), per row e
+// of T frames, walking n = T-1 .. 0 with carry = 0:
+//     active = reset[n] > 0 ? 0 : carry ;  out[n] = scale * active ;  carry = g[n] + active
+// i.e. out[n] = scale * sum of g[m] over n < m <= (the first frame after n with a reset, or T-1), and 0 on a reset
+// frame itself: the gradient of the pre-update output still enters frame n even when reset[n] cuts the later
+// recurrence.  reset is one signal [T] shared by all rows (the reference keeps one reset cell per frame); NULL =
+// no resets, the plain exclusive suffix sum.
+// One block per row; every thread owns a contiguous run of frames.  A run acts on the carry as c -> a c + b with
+// a in {0, 1} (0 when the run holds a reset); those maps are composed over the later runs by a Hillis-Steele scan
+// in double, then every thread walks its run from its incoming carry.
 constexpr int TSCAN_THREADS = 1024;
 __global__ void __launch_bounds__(TSCAN_THREADS)
-temporal_suffix_scan_kernel(const float *__restrict__ g, int T, float scale, float *__restrict__ out) {
+temporal_suffix_scan_kernel(const float *__restrict__ g, const float *__restrict__ reset, int T, float scale,
+                            float *__restrict__ out) {
   __shared__ double tot[TSCAN_THREADS];
+  __shared__ unsigned char pass[TSCAN_THREADS];   // a of the composed map
   const float *row = g + (size_t)blockIdx.x * T;
   float *orow = out + (size_t)blockIdx.x * T;
   const int per = (T + TSCAN_THREADS - 1) / TSCAN_THREADS;
   const int n0 = min(T, (int)threadIdx.x * per), n1 = min(T, n0 + per);
   double s = 0.0;
-  for (int n = n0; n < n1; ++n) s += (double)row[n];
+  unsigned char a = 1;
+  for (int n = n1 - 1; n >= n0; --n) {
+    const bool r = reset && reset[n] > 0.0f;
+    s = (double)row[n] + (r ? 0.0 : s);
+    if (r) a = 0;
+  }
   tot[threadIdx.x] = s;
+  pass[threadIdx.x] = a;
   __syncthreads();
-  // inclusive suffix scan over the run totals (Hillis-Steele, 10 steps)
+  // inclusive composition over this run and all later ones (10 steps): F_i o (F_{i+1} o ...)
   for (int off = 1; off < TSCAN_THREADS; off <<= 1) {
-    double add = threadIdx.x + off < TSCAN_THREADS ? tot[threadIdx.x + off] : 0.0;
+    const bool has = threadIdx.x + off < TSCAN_THREADS;
+    const double b_late = has ? tot[threadIdx.x + off] : 0.0;
+    const unsigned char a_late = has ? pass[threadIdx.x + off] : 1;
     __syncthreads();
-    tot[threadIdx.x] += add;
+    if (has) {
+      if (pass[threadIdx.x]) tot[threadIdx.x] += b_late;
+      pass[threadIdx.x] = pass[threadIdx.x] & a_late;
+    }
     __syncthreads();
   }
-  double carry = threadIdx.x + 1 < TSCAN_THREADS ? tot[threadIdx.x + 1] : 0.0;  // everything after this run
+  double carry = threadIdx.x + 1 < TSCAN_THREADS ? tot[threadIdx.x + 1] : 0.0;  // everything after this run, from 0
   for (int n = n1 - 1; n >= n0; --n) {
-    orow[n] = (float)(carry * (double)scale);
-    carry += (double)row[n];
+    const bool r = reset && reset[n] > 0.0f;
+    const double active = r ? 0.0 : carry;
+    orow[n] = (float)(active * (double)scale);
+    carry = (double)row[n] + active;
   }
 }
 
@@ -900,13 +922,13 @@ DGC_EXPORT int32_t dgc_harmonic_render(dgc_ctx *ctx, const dgc_harmonic_params *
   return DGC_OK;
 }
 
-DGC_EXPORT int32_t dgc_temporal_grad_scan(dgc_ctx *ctx, const float *g_dev, int32_t E, int32_t T, float scale,
-                                          float *out_dev) {
+DGC_EXPORT int32_t dgc_temporal_grad_scan(dgc_ctx *ctx, const float *g_dev, const float *reset_dev, int32_t E, int32_t T,
+                                          float scale, float *out_dev) {
   if (!ctx) return DGC_ERR_INVALID;
   DGC_REQUIRE(ctx, g_dev && out_dev, "null pointer");
   DGC_REQUIRE(ctx, E > 0 && T > 0, "E and T must be positive");
   DGC_REQUIRE(ctx, g_dev != out_dev, "the scan is not in place");
-  temporal_suffix_scan_kernel<<<E, TSCAN_THREADS, 0, ctx->stream>>>(g_dev, T, scale, out_dev);
+  temporal_suffix_scan_kernel<<<E, TSCAN_THREADS, 0, ctx->stream>>>(g_dev, reset_dev, T, scale, out_dev);
   DGC_LAUNCHED(ctx, "temporal_grad_scan");
   return DGC_OK;
 }
@@ -942,7 +964,7 @@ DGC_EXPORT int32_t dgc_harmonic_f0_bwd(dgc_ctx *ctx, const dgc_harmonic_params *
   DGC_PICK_GROUP(K, PHGRAD);
 #undef PHGRAD
   DGC_LAUNCHED(ctx, "harmonic_phase_grad");
-  temporal_suffix_scan_kernel<<<q.B, TSCAN_THREADS, 0, ctx->stream>>>(gphi, q.T, 1.0f / q.sample_rate, gsum);
+  temporal_suffix_scan_kernel<<<q.B, TSCAN_THREADS, 0, ctx->stream>>>(gphi, nullptr, q.T, 1.0f / q.sample_rate, gsum);
   DGC_LAUNCHED(ctx, "temporal_grad_scan");
   f0_rows_grad_kernel<<<dgc_div_up((int64_t)q.F * q.B, 128), 128, 0, ctx->stream>>>(rowtab, ranges, gsum, q.F, q.B, q.T,
                                                                                 g_f0_dev);

@@ -93,6 +93,51 @@ class HnStep(C.Structure):
 
 _vp, _i32, _i64, _u64, _u32, _f = C.c_void_p, C.c_int32, C.c_int64, C.c_uint64, C.c_uint32, C.c_float
 
+PLAN_NONE = 0xffffffffffffffff
+(PLAN_FORK, PLAN_JOIN, PLAN_OSC_BANK_CONST, PLAN_HARMONIC_RENDER, PLAN_BANDS_TO_TAPS, PLAN_FIR_NOISE, PLAN_ADD, PLAN_COPY,
+ PLAN_ONEPOLE, PLAN_BIQUAD_FWD, PLAN_BIQUAD_MSE_BWD, PLAN_STFT_MAG, PLAN_PARTCONV, PLAN_PARTCONV_BWD, PLAN_MSS_LOSS_FWD,
+ PLAN_MSS_LOSS_BWD, PLAN_LINEAR_FWD, PLAN_LINEAR_BWD, PLAN_HEADS_FWD, PLAN_HEADS_BWD, PLAN_HARMONIC_BWD, PLAN_FIR_BWD,
+ PLAN_ALLREDUCE, PLAN_ADAM, PLAN_SANITIZE, PLAN_BLOCK) = range(26)
+
+
+class PlanStep(C.Structure):
+    _fields_ = [("op", C.c_int32), ("stream", C.c_int32), ("a", C.c_uint64 * 10), ("i", C.c_int32 * 16),
+                ("f", C.c_float * 4)]
+
+
+def plan_step(op, a=(), i=(), f=(), stream=0):
+    """One dgc_plan_step: arena offsets a (None = absent), integers i, floats f."""
+    s = PlanStep()
+    s.op, s.stream = op, stream
+    for k in range(10):
+        s.a[k] = PLAN_NONE
+    for k, v in enumerate(a):
+        s.a[k] = PLAN_NONE if v is None else int(v)
+    for k, v in enumerate(i):
+        s.i[k] = int(v)
+    for k, v in enumerate(f):
+        s.f[k] = float(v)
+    return s
+
+
+class Plan(C.Structure):
+    _fields_ = [("steps", C.POINTER(PlanStep)), ("n_steps", C.c_int32), ("modules", C.POINTER(C.c_void_p)),
+                ("kernels", C.POINTER(C.c_char_p)), ("n_kernels", C.c_int32)]
+
+
+class HnTrainConfig(C.Structure):
+    _fields_ = [("B", C.c_int32), ("T", C.c_int32), ("K", C.c_int32), ("F", C.c_int32), ("sample_rate", C.c_float),
+                ("nbands", C.c_int32), ("taps", C.c_int32), ("in_features", C.c_int32), ("hidden", C.c_int32),
+                ("n_trunk", C.c_int32), ("ir_len", C.c_int32), ("conv_n", C.c_int32), ("conv_hop", C.c_int32),
+                ("mss", MssParams), ("phase_mode", C.c_int32), ("global_voices", C.c_int32), ("lr", C.c_float),
+                ("beta1", C.c_float), ("beta2", C.c_float), ("eps", C.c_float)]
+
+
+class HnTrainLayout(C.Structure):
+    _fields_ = [(n, C.c_uint64) for n in ("total_floats", "n_params", "params", "grads", "adam_m", "adam_v", "adam_t",
+                                          "adam_corr", "x", "f0", "uv", "gain", "noise_gain", "noise", "w_fs", "target",
+                                          "loss", "audio")] + [("n_steps", C.c_int32), ("n_forward_backward", C.c_int32)]
+
 # name -> (restype, argtypes); one line per declaration of include/dgen_cuda.h
 SIGNATURES = {
     "dgc_abi_version": (_i32, []),
@@ -105,6 +150,9 @@ SIGNATURES = {
     "dgc_profile_end": (_i32, [_vp, C.POINTER(_f)]),
     "dgc_launch_count": (_i64, [_vp]),
     "dgc_arena_create": (_i32, [_vp, _u64, C.POINTER(_vp)]),
+    "dgc_arena_wrap": (_i32, [_vp, _vp, _u64, C.POINTER(_vp)]),
+    "dgc_plan_run": (_i32, [_vp, _vp, C.POINTER(Plan), _i32, _i32]),
+    "dgc_hn_train_plan": (_i32, [C.POINTER(HnTrainConfig), C.POINTER(HnTrainLayout), C.POINTER(PlanStep), _i32]),
     "dgc_arena_destroy": (_i32, [_vp]),
     "dgc_arena_ptr": (_vp, [_vp]),
     "dgc_arena_size": (_u64, [_vp]),
@@ -119,6 +167,8 @@ SIGNATURES = {
     "dgc_fir_noise": (_i32, [_vp, C.POINTER(FirParams), _vp, _vp, _vp, _vp]),
     "dgc_bands_to_taps": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _vp]),
     "dgc_onepole_fwd": (_i32, [_vp, _vp, _i32, _i32, _f, _vp]),
+    "dgc_onepole_fwd_state": (_i32, [_vp, _vp, _i32, _i32, _f, _vp, _vp]),
+    "dgc_biquad_fwd_state": (_i32, [_vp, C.POINTER(BiquadParams), _vp, _vp, _vp, _vp, _vp, _vp]),
     "dgc_onepole_fwd_static": (_i32, [_vp, _vp, _i32, _i32, _f, _vp, C.c_char_p, _u32]),
     "dgc_biquad_scratch_floats": (_u64, [C.POINTER(BiquadParams), _i32]),
     "dgc_biquad_fwd": (_i32, [_vp, C.POINTER(BiquadParams), _vp, _vp, _vp, _vp, _vp]),
@@ -175,7 +225,7 @@ SIGNATURES = {
     "dgc_harmonic_render_bwd_prepared": (_i32, [_vp, C.POINTER(HarmonicParams), _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "dgc_harmonic_f0_bwd_scratch_floats": (_u64, [C.POINTER(HarmonicParams)]),
     "dgc_harmonic_f0_bwd": (_i32, [_vp, C.POINTER(HarmonicParams), _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
-    "dgc_temporal_grad_scan": (_i32, [_vp, _vp, _i32, _i32, _f, _vp]),
+    "dgc_temporal_grad_scan": (_i32, [_vp, _vp, _vp, _i32, _i32, _f, _vp]),
     "dgc_hn_forward_loss_work_floats": (_u64, [C.POINTER(HnStep)]),
     "dgc_hn_forward_loss": (_i32, [_vp, C.POINTER(HnStep)] + [_vp] * 9 + [_vp, _vp, _vp]),
     "dgc_hn_forward_loss_host": (_i32, [_vp, C.POINTER(HnStep)] + [_vp] * 9 + [C.POINTER(C.c_double), _vp]),
@@ -400,18 +450,27 @@ class Context:
         return out
 
     # ---- linear recurrences -------------------------------------------------------------------
-    def onepole_fwd(self, x, a, out=None):
+    def onepole_fwd(self, x, a, out=None, state=None):
+        """state [B] (optional): y[-1] per voice on entry, y[T-1] on return (updated in place)."""
         B, T = x.shape
         y = self._empty(B, T) if out is None else out
-        self.check(self.lib.dgc_onepole_fwd(self.h, _ptr(x), B, T, a, _ptr(y)))
+        if state is None:
+            self.check(self.lib.dgc_onepole_fwd(self.h, _ptr(x), B, T, a, _ptr(y)))
+        else:
+            self.check(self.lib.dgc_onepole_fwd_state(self.h, _ptr(x), B, T, a, _ptr(state), _ptr(y)))
         return y
 
-    def biquad_fwd(self, x, cutoff, q, gain=1.0, mode=0.0):
+    def biquad_fwd(self, x, cutoff, q, gain=1.0, mode=0.0, state=None):
+        """state [B][4][L] (optional): the four history cells y1, y2, x1, x2, continued from and updated in place."""
         B, T = x.shape
         L = cutoff.numel()
         p = BiquadParams(B, T, L, gain, mode)
         y = self._empty(B, T, L)
-        self.check(self.lib.dgc_biquad_fwd(self.h, C.byref(p), _ptr(x), _ptr(cutoff), _ptr(q), None, _ptr(y)))
+        if state is None:
+            self.check(self.lib.dgc_biquad_fwd(self.h, C.byref(p), _ptr(x), _ptr(cutoff), _ptr(q), None, _ptr(y)))
+        else:
+            self.check(self.lib.dgc_biquad_fwd_state(self.h, C.byref(p), _ptr(x), _ptr(cutoff), _ptr(q), None,
+                                                     _ptr(state), _ptr(y)))
         return y
 
     def biquad_mse_bwd(self, x, cutoff, q, y, target, loss_scale=1.0, gain=1.0, mode=0.0):
@@ -500,11 +559,13 @@ class Context:
                                                 _ptr(g_audio), None, _ptr(g)))
         return g
 
-    def temporal_grad_scan(self, g, scale=1.0):
-        """out[e][n] = scale * sum_{m>n} g[e][m]."""
+    def temporal_grad_scan(self, g, scale=1.0, reset=None):
+        """out[e][n] = scale * sum of g[e][m] over n < m <= (first frame after n with reset > 0, or the last
+        frame); 0 on a reset frame.  reset [T] or None."""
         E, T = g.shape
         out = self._empty(E, T)
-        self.check(self.lib.dgc_temporal_grad_scan(self.h, _ptr(g), E, T, scale, _ptr(out)))
+        self.check(self.lib.dgc_temporal_grad_scan(self.h, _ptr(g), _ptr(reset) if reset is not None else None, E, T,
+                                                   scale, _ptr(out)))
         return out
 
     def fir_noise_bwd(self, noise, noise_gain, g_audio, F, taps, scale=0.12):

@@ -18,13 +18,21 @@ import ctypes as C
 
 import numpy as np
 
-from . import Context, FirParams, HarmonicParams, PHASE_SCAN, mss_params, sharding
+from . import (Context, HnTrainConfig, HnTrainLayout, PLAN_ADAM, PLAN_ALLREDUCE, PLAN_MSS_LOSS_BWD, PHASE_SCAN, Plan,
+               PlanStep, mss_params, sharding)
 
 
 class HarmonicModel:
+    """The training step as ONE block plan in the library (dgc_hn_train_plan / dgc_plan_run): this class owns the
+    arena (one device buffer that holds parameters, Adam state, inputs, activations and outputs at the offsets the
+    library chose), exposes views into it, and decides when the plan's three parts run -- forward + backward, the
+    gradient exchange, the update.  No kernel is launched from Python."""
+
+    INPUTS = ("x", "f0", "uv", "gain", "noise_gain", "noise", "w_fs", "target")
+
     def __init__(self, ctx: Context, B, T, K=100, F=1000, sr=16000.0, nbands=65, taps=257, hidden=512, in_features=2,
                  ir_len=16000, conv_n=2048, conv_hop=1024, sizes=(2048, 1024, 512, 256, 128, 64), seed=0,
-                 phase_mode=PHASE_SCAN, global_voices=None, counted_adam=False):
+                 phase_mode=PHASE_SCAN, global_voices=None, counted_adam=False, n_trunk=3, lr=1e-3):
         import torch
         self.torch, self.ctx = torch, ctx
         self.B, self.T, self.K, self.F, self.sr = B, T, K, F, sr
@@ -33,7 +41,24 @@ class HarmonicModel:
         self.phase_mode = phase_mode
         self.global_voices = global_voices or B
         self.M = F * B
-        dims = [(in_features, hidden), (hidden, hidden), (hidden, hidden), (hidden, K + nbands)]
+        cfg = HnTrainConfig(B, T, K, F, sr, nbands, taps, in_features, hidden, n_trunk, ir_len, conv_n, conv_hop,
+                            mss_params(B, T, self.sizes), phase_mode, self.global_voices, lr, 0.9, 0.999, 1e-8)
+        lay = HnTrainLayout()
+        ctx.check(ctx.lib.dgc_hn_train_plan(C.byref(cfg), C.byref(lay), None, 0))
+        self.steps = (PlanStep * lay.n_steps)()
+        ctx.check(ctx.lib.dgc_hn_train_plan(C.byref(cfg), C.byref(lay), self.steps, lay.n_steps))
+        self.lay, self.cfg = lay, cfg
+        self.plan = Plan(self.steps, lay.n_steps, None, None, 0)
+        ops = [self.steps[i].op for i in range(lay.n_steps)]
+        self.i_backward = ops.index(PLAN_MSS_LOSS_BWD)            # [0, i_backward) is the forward
+        self.i_exchange, self.i_update = ops.index(PLAN_ALLREDUCE), ops.index(PLAN_ADAM)
+        assert self.i_exchange == lay.n_forward_backward and self.i_update == self.i_exchange + 1
+        dev = "cuda:%d" % ctx.device
+        self.arena_t = torch.zeros(int(lay.total_floats), dtype=torch.float32, device=dev)
+        h = C.c_void_p()
+        ctx.check(ctx.lib.dgc_arena_wrap(ctx.h, self.arena_t.data_ptr(), int(lay.total_floats), C.byref(h)))
+        self.arena = h
+        dims = [(in_features, hidden)] + [(hidden, hidden)] * (n_trunk - 1) + [(hidden, K + nbands)]
         self.layout, off = [], 0
         for i, (a, b) in enumerate(dims):
             self.layout.append(("W%d" % i, off, (a, b)))
@@ -42,7 +67,18 @@ class HarmonicModel:
             off += b
         self.layout.append(("ir", off, (ir_len,)))
         off += ir_len
+        assert off == lay.n_params
         self.n_params = off
+        view = lambda o, n: self.arena_t[int(o):int(o) + int(n)]
+        self.params, self.grads = view(lay.params, off), view(lay.grads, off)
+        self.m, self.v = view(lay.adam_m, off), view(lay.adam_v, off)
+        self.t_dev = view(lay.adam_t, 1).view(torch.int32)
+        self.corr = view(lay.adam_corr, 2)
+        self.loss = view(lay.loss, 2).view(torch.float64)
+        self.out = view(lay.audio, B * T).view(B, T)
+        shapes = dict(x=(self.M, in_features), f0=(F, B), uv=(F, B), gain=(F, B), noise_gain=(F, B), noise=(B, T),
+                      w_fs=(taps, nbands), target=(B, T))
+        self.inputs = {k: view(getattr(lay, k), int(np.prod(shapes[k]))).view(*shapes[k]) for k in self.INPUTS}
         rng = np.random.default_rng(seed)
         flat = np.zeros(off, np.float32)
         for name, o, shape in self.layout:
@@ -52,39 +88,24 @@ class HarmonicModel:
             elif name == "ir":
                 t = np.arange(ir_len) / sr
                 flat[o:o + n] = (0.05 * rng.standard_normal(n) * np.exp(-6.91 * t / 0.4)).astype(np.float32)
-        dev = "cuda:%d" % ctx.device
-        self.params = torch.from_numpy(flat).to(dev)
-        self.grads = torch.zeros_like(self.params)
-        self.m = torch.zeros_like(self.params)
-        self.v = torch.zeros_like(self.params)
+        self.params.copy_(torch.from_numpy(flat).to(dev))
         self.step_index = 0
         # step index in device memory: a recorded step advances it on every replay
         self.counted_adam = counted_adam
-        self.t_dev = torch.zeros(1, dtype=torch.int32, device=dev)
-        self.corr = torch.zeros(2, dtype=torch.float32, device=dev)
         self.graph, self.graph_stream = None, None   # list of recordings (see capture)
+        self.static_args = None
         self.exchange_events = None   # a list: replay() appends a CUDA event pair around every gradient exchange
-        f = lambda *s: torch.empty(*s, dtype=torch.float32, device=dev)
-        M, H = self.M, hidden
-        self.act = [f(M, H), f(M, H), f(M, H), f(M, K + nbands)]
-        self.act_t = [f(H, M), f(H, M), f(H, M)]         # transposed copies of the trunk activations
-        hp0 = HarmonicParams(B, T, K, F, sr, 1.0, phase_mode, 0)
-        self.h_scratch = f(int(ctx.lib.dgc_harmonic_bwd_scratch_floats(C.byref(hp0))) + 64)
-        self.h_prepared = None
-        self.side = torch.cuda.Stream(device=dev)        # second stream for the noise branch
-        self.noise_out = f(B, T)
         # the per-(F, T) clock tables are built on first use by a kernel on the then-current stream: build them
         # now, so that the two concurrent branches of the first step both find them complete
         ctx.check(ctx.lib.dgc_ctx_prepare_tables(ctx.h, F, T))
-        self.dact = [f(M, H), f(M, H), f(M, H)]          # gradient w.r.t. a layer's input
-        self.dz = [f(M, H), f(M, H), f(M, H), f(M, K + nbands)]
-        self.head_dz = f(M, K + nbands)
-        self.amps, self.bands = f(F, B, K), f(F, B, nbands)
-        self.taps_tab, self.g_taps = f(F, B, taps), f(F, B, taps)
-        self.g_amps, self.g_bands = f(F, B, K), f(F, B, nbands)
-        self.dry, self.out, self.g_out = f(B, T), f(B, T), f(B, T)
-        self.loss = torch.zeros(1, dtype=torch.float64, device=dev)
-        self.mss = mss_params(B, T, self.sizes)
+
+    def close(self):
+        for g in self.graph or []:
+            g.close()
+        self.graph = None
+        if self.arena:
+            self.ctx.lib.dgc_arena_destroy(self.arena)
+            self.arena = None
 
     def view(self, name, buf=None):
         buf = self.params if buf is None else buf
@@ -93,89 +114,28 @@ class HarmonicModel:
                 return buf[o:o + int(np.prod(shape))].view(*shape)
         raise KeyError(name)
 
+    def input_views(self):
+        """The step's input buffers inside the arena, in the order step() takes them: fill them in place."""
+        return [self.inputs[k] for k in self.INPUTS]
+
     # ------------------------------------------------------------------------------------------
+    def _load(self, args):
+        """Inputs given as other tensors are copied into their arena slots (device to device)."""
+        for k, a in zip(self.INPUTS, args):
+            v = self.inputs[k]
+            if a.data_ptr() != v.data_ptr():
+                v.copy_(a.reshape(v.shape))
+
+    def _run(self, first, count):
+        self.ctx.check(self.ctx.lib.dgc_plan_run(self.ctx.h, self.arena, C.byref(self.plan), first, count))
+
     def forward(self, X, f0, uv, gain, noise_gain, noise, w_fs, target):
-        c = self.ctx
-        lib, h = c.lib, c.h
-        a = X
-        for i in range(4):
-            W, b = self.view("W%d" % i), self.view("b%d" % i)
-            # trunk activations are also kept transposed: the next layer's weight gradient reads them along m
-            c.check(lib.dgc_linear_fwd(h, a.data_ptr(), W.data_ptr(), b.data_ptr(), self.M, W.shape[0], W.shape[1],
-                                       1 if i < 3 else 0, self.act[i].data_ptr(),
-                                       self.act_t[i].data_ptr() if i < 3 else None))
-            a = self.act[i]
-        c.check(lib.dgc_hn_heads_fwd(h, self.act[3].data_ptr(), self.M, self.K, self.nbands, self.amps.data_ptr(),
-                                     self.bands.data_ptr()))
-        # the noise branch (band -> tap map, FIR) shares nothing with the harmonic branch until the two are
-        # summed: it runs on a side stream beside it
-        cur = self.torch.cuda.current_stream()
-        self.side.wait_stream(cur)
-        with c.on_stream(self.side):
-            c.check(lib.dgc_bands_to_taps(h, self.bands.data_ptr(), w_fs.data_ptr(), self.M, self.nbands, self.taps,
-                                          self.taps_tab.data_ptr()))
-            fp = FirParams(self.B, self.T, self.F, self.taps, 0.12, 0)
-            c.check(lib.dgc_fir_noise(h, C.byref(fp), noise.data_ptr(), self.taps_tab.data_ptr(),
-                                      noise_gain.data_ptr(), self.noise_out.data_ptr()))
-        hp = HarmonicParams(self.B, self.T, self.K, self.F, self.sr, 1.0, self.phase_mode, 0)
-        # the render's per-sample tracks and phase anchors stay in this scratch for the backward pass
-        c.check(lib.dgc_harmonic_render(h, C.byref(hp), f0.data_ptr(), uv.data_ptr(), self.amps.data_ptr(),
-                                        gain.data_ptr(), self.h_scratch.data_ptr(), self.dry.data_ptr()))
-        self.h_prepared = (f0.data_ptr(), uv.data_ptr(), gain.data_ptr())
-        cur.wait_stream(self.side)
-        self.torch.add(self.dry, self.noise_out, out=self.dry)
-        self.out.copy_(self.dry)
-        ir = self.view("ir")
-        c.check(lib.dgc_partconv(h, self.dry.data_ptr(), self.B, self.T, ir.data_ptr(), self.ir_len, self.conv_n,
-                                 self.conv_hop, 1.0, None, 1, self.out.data_ptr()))
-        c.check(lib.dgc_mss_loss_fwd(h, C.byref(self.mss), self.out.data_ptr(), target.data_ptr(), None,
-                                     self.loss.data_ptr()))
+        self._load((X, f0, uv, gain, noise_gain, noise, w_fs, target))
+        self._run(0, self.i_backward)
         return self.loss
 
     def backward(self, X, f0, uv, gain, noise_gain, noise, w_fs, target):
-        c = self.ctx
-        lib, h = c.lib, c.h
-        upstream = float(self.B) / float(self.global_voices)   # local share of the global-batch mean
-        c.check(lib.dgc_mss_loss_bwd(h, C.byref(self.mss), self.out.data_ptr(), target.data_ptr(), upstream,
-                                     self.g_out.data_ptr()))
-        ir, g_ir = self.view("ir"), self.view("ir", self.grads)
-        # g_dry = g_out + A(ir)^T g_out, accumulated in place; g_ir
-        c.check(lib.dgc_partconv_bwd(h, self.dry.data_ptr(), self.B, self.T, ir.data_ptr(), self.ir_len, self.conv_n,
-                                     self.conv_hop, 1.0, self.g_out.data_ptr(), None, 1, self.g_out.data_ptr(),
-                                     g_ir.data_ptr()))
-        hp = HarmonicParams(self.B, self.T, self.K, self.F, self.sr, 1.0, self.phase_mode, 0)
-        bwd = lib.dgc_harmonic_render_bwd_prepared \
-            if getattr(self, "h_prepared", None) == (f0.data_ptr(), uv.data_ptr(), gain.data_ptr()) \
-            else lib.dgc_harmonic_render_bwd
-        # the two synthesis branches again side by side: noise-branch gradients on the side stream (the context
-        # scratch they use is not touched by the harmonic backward, which works in the model's own scratch)
-        cur = self.torch.cuda.current_stream()
-        self.side.wait_stream(cur)
-        with c.on_stream(self.side):
-            fp = FirParams(self.B, self.T, self.F, self.taps, 0.12, 0)
-            c.check(lib.dgc_fir_noise_bwd(h, C.byref(fp), noise.data_ptr(), noise_gain.data_ptr(),
-                                          self.g_out.data_ptr(), self.g_taps.data_ptr()))
-            # g_bands = g_taps Wfs   ([M, taps] x [taps, nbands])
-            c.check(lib.dgc_linear_fwd(h, self.g_taps.data_ptr(), w_fs.data_ptr(), None, self.M, self.taps,
-                                       self.nbands, 0, self.g_bands.data_ptr(), None))
-        c.check(bwd(h, C.byref(hp), f0.data_ptr(), uv.data_ptr(), self.amps.data_ptr(), gain.data_ptr(),
-                    self.g_out.data_ptr(), self.h_scratch.data_ptr(), self.g_amps.data_ptr()))
-        self.h_prepared = None
-        cur.wait_stream(self.side)
-        c.check(lib.dgc_hn_heads_bwd(h, self.act[3].data_ptr(), self.g_amps.data_ptr(), self.g_bands.data_ptr(),
-                                     self.M, self.K, self.nbands, self.dz[3].data_ptr()))
-        # head layer: dz[3] is the gradient w.r.t. z (no activation); trunk layers: dact[i] is the gradient
-        # w.r.t. act[i] and the kernel applies tanh' to it
-        for i in (3, 2, 1, 0):
-            W = self.view("W%d" % i)
-            inp = X if i == 0 else self.act[i - 1]
-            gW, gb = self.view("W%d" % i, self.grads), self.view("b%d" % i, self.grads)
-            dc = self.dz[3] if i == 3 else self.dact[i]
-            dz_out = self.head_dz if i == 3 else self.dz[i]
-            da = self.dact[i - 1].data_ptr() if i > 0 else None
-            c.check(lib.dgc_linear_bwd(h, inp.data_ptr(), W.data_ptr(), self.act[i].data_ptr(), dc.data_ptr(), self.M,
-                                       W.shape[0], W.shape[1], 1 if i < 3 else 0, dz_out.data_ptr(), da,
-                                       gW.data_ptr(), gb.data_ptr(), self.act_t[i - 1].data_ptr() if i > 0 else None))
+        self._run(self.i_backward, self.i_exchange - self.i_backward)
         return self.grads
 
     def snapshots(self):
@@ -197,7 +157,7 @@ class HarmonicModel:
 
     def _exchange(self):
         if getattr(self, "use_ctx_comm", False):
-            self.ctx.allreduce_sum_(self.grads)   # NCCL communicator owned by the context (C ABI)
+            self._run(self.i_exchange, 1)         # NCCL communicator owned by the context (the plan's ALLREDUCE step)
         else:
             sharding.allreduce_sum_(self.grads)   # torch.distributed process group
 
@@ -209,7 +169,8 @@ class HarmonicModel:
 
     def _update(self, lr):
         if self.counted_adam:
-            self.ctx.adam_step_counted(self.params, self.grads, self.m, self.v, self.t_dev, self.corr, lr=lr)
+            self.steps[self.i_update].f[0] = lr
+            self._run(self.i_update, 1)
         else:
             self.ctx.adam_step(self.params, self.grads, self.m, self.v, self.step_index, lr=lr)
 
@@ -223,15 +184,15 @@ class HarmonicModel:
         return self.loss
 
     def capture(self, X, f0, uv, gain, noise_gain, noise, w_fs, target, lr=1e-3):
-        """Record one whole training step (both streams, Adam) on the given tensors, which become the step's static
-        input buffers: refill them in place and call replay().  Where the reference rebuilds and recompiles its
-        graph every step (Sources/DGenLazy/Backward.swift:225), this keeps one recording per model.  Needs
-        counted_adam=True and one eager step() before it (so that nothing allocates inside).
+        """Record one whole training step (both streams, Adam).  The step's inputs live in the arena
+        (input_views()); tensors given here that are not those views are remembered and copied into them at the
+        start of every replay().  Where the reference rebuilds and recompiles its graph every step
+        (Sources/DGenLazy/Backward.swift:225), this keeps one recording per model.  Needs counted_adam=True and one
+        eager step() before it (so that nothing allocates inside).
 
         With one rank the step is ONE recording.  With several the gradient exchange stays outside: forward +
         backward is one recording, the all-reduce is enqueued call by call between, the update is a second one
-        (a collective inside a recording makes every rank's replay depend on the others' through the library's
-        own host threads; the call-by-call exchange is the path the multi-GPU runs have verified)."""
+        (the library refuses a collective inside a recording)."""
         torch = self.torch
         if not self.counted_adam:
             raise ValueError("capture() needs a model built with counted_adam=True")
@@ -242,17 +203,19 @@ class HarmonicModel:
         s = self.graph_stream
         s.wait_stream(torch.cuda.current_stream())
         args = (X, f0, uv, gain, noise_gain, noise, w_fs, target)
+        self.static_args = args
+        self._load(args)
+        self.steps[self.i_update].f[0] = lr
         split = self._exchanges()
         with self.ctx.on_stream(s), torch.cuda.stream(s):
             with self.ctx.record() as rec:
-                self.forward(*args)
-                self.backward(*args)
+                self._run(0, self.i_exchange)
                 if not split:
-                    self._update(lr)
+                    self._run(self.i_update, 1)
             graphs = [rec.graph]
             if split:
                 with self.ctx.record() as rec2:
-                    self._update(lr)
+                    self._run(self.i_update, 1)
                 graphs.append(rec2.graph)
         for g in self.graph or []:
             g.close()
@@ -265,6 +228,8 @@ class HarmonicModel:
         cur, s = torch.cuda.current_stream(), self.graph_stream
         s.wait_stream(cur)            # the caller refilled the inputs on its own stream
         with self.ctx.on_stream(s), torch.cuda.stream(s):
+            if self.static_args is not None:
+                self._load(self.static_args)
             self.graph[0].launch()
             if len(self.graph) > 1:
                 if self.exchange_events is not None:

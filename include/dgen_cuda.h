@@ -68,6 +68,9 @@ int64_t dgc_launch_count(dgc_ctx *ctx);
  * (toolchain/include/dgen_runtime.h:282-288) and LazyRuntime.memoryPointer()
  * (Sources/DGenLazy/Realize.swift:12-19): device memory plus explicit upload / download. */
 int32_t dgc_arena_create(dgc_ctx *ctx, uint64_t nfloats, dgc_arena **out);
+/* An arena over device memory the CALLER owns (256-byte aligned; it stays the caller's: dgc_arena_destroy only drops
+ * the handle): for hosts that allocate device memory themselves and want plans to address it. */
+int32_t dgc_arena_wrap(dgc_ctx *ctx, float *dev, uint64_t nfloats, dgc_arena **out);
 int32_t dgc_arena_destroy(dgc_arena *a);
 float *dgc_arena_ptr(dgc_arena *a);
 uint64_t dgc_arena_size(dgc_arena *a);
@@ -183,10 +186,15 @@ uint64_t dgc_harmonic_f0_bwd_scratch_floats(const dgc_harmonic_params *p);
 int32_t dgc_harmonic_f0_bwd(dgc_ctx *ctx, const dgc_harmonic_params *p, const float *f0_dev, const float *uv_dev,
                             const float *amps_dev, const float *gain_dev, const float *g_audio_dev,
                             float *scratch_dev, float *g_f0_dev);
-/* The scan alone: out[e][n] = scale * sum_{m>n} g[e][m] for E rows of T frames (not in place).
- * replaces: temporalGradScan + temporalGradRead (Emit+TemporalGradient.swift:60-110) for a graph without
- * resets; scale = 1/sampleRate for a phasor, 1 for an accum. */
-int32_t dgc_temporal_grad_scan(dgc_ctx *ctx, const float *g_dev, int32_t E, int32_t T, float scale, float *out_dev);
+/* The scan alone, for E rows of T frames (not in place), walking n = T-1 .. 0 from carry = 0:
+ *     active = reset[n] > 0 ? 0 : carry ;  out[e][n] = scale * active ;  carry = g[e][n] + active
+ * Without resets that is out[e][n] = scale * sum_{m>n} g[e][m]; a reset at frame r cuts the sum for the frames
+ * before r AFTER g[r] (the gradient of the pre-update output still enters frame r) and makes out[r] = 0.
+ * reset_dev [T] is one signal shared by all rows (> 0 = reset), or NULL for none.
+ * replaces: temporalGradScan + temporalGradRead (Emit+TemporalGradient.swift:54-110);
+ * scale = 1/sampleRate for a phasor, 1 for an accum. */
+int32_t dgc_temporal_grad_scan(dgc_ctx *ctx, const float *g_dev, const float *reset_dev, int32_t E, int32_t T,
+                               float scale, float *out_dev);
 /* Gradient of the noise branch w.r.t. the tap table: g_taps [F][B][taps] from g_audio [B][T]. */
 int32_t dgc_fir_noise_bwd(dgc_ctx *ctx, const dgc_fir_params *p, const float *noise_dev, const float *noise_gain_dev,
                           const float *g_audio_dev, float *g_taps_dev);
@@ -203,6 +211,13 @@ int32_t dgc_hn_heads_bwd(dgc_ctx *ctx, const float *z_dev, const float *g_amps_d
  * y[n] = x[n] + a*y[n-1] per voice, chunked parallel scan over time.
  * replaces: historyRead/historyWrite feedback (Sources/DGen/Emit+State.swift:150-224). x,y [B][T]. */
 int32_t dgc_onepole_fwd(dgc_ctx *ctx, const float *x_dev, int32_t B, int32_t T, float a, float *y_dev);
+
+/* The same filter continuing from, and leaving behind, the history cell: state_dev [B] holds y[-1] of every voice on
+ * entry and y[T-1] on return, so consecutive calls over consecutive blocks of a stream give the output of one call
+ * over the whole stream (the reference keeps its cells between realize() calls, preserveState,
+ * Sources/DGenLazy/Realize.swift:551-553).  state_dev NULL = start from rest and keep nothing (dgc_onepole_fwd). */
+int32_t dgc_onepole_fwd_state(dgc_ctx *ctx, const float *x_dev, int32_t B, int32_t T, float a, float *state_dev,
+                              float *y_dev);
 
 /* The same filter for callers that must not allocate.  No counterpart in the reference: it exists
  * because a real-time audio thread (a plug-in render callback, a driver I/O thread) cannot call
@@ -234,7 +249,9 @@ int32_t dgc_onepole_bwd(dgc_ctx *ctx, const float *y_dev, const float *gy_dev, i
 typedef struct dgc_biquad_params {
   int32_t B, T, L;   /* voices, frames, lanes */
   float gain;
-  float mode;        /* 0 low-pass .. 5, as Graph.biquad's selector */
+  float mode;        /* Graph.biquad's selector: 0 low-pass, 1 high-pass, 2 / 3 band-pass (constant skirt / peak
+                        gain), 4 all-pass, 5 notch, 6 high shelf, 7 low shelf (the shelves take their amount from
+                        `gain`: A = sqrt(|gain|)) */
 } dgc_biquad_params;
 
 /* Device scratch (floats) the biquad entry points need: backward 0 = dgc_biquad_fwd, 1 = dgc_biquad_mse_bwd and
@@ -244,6 +261,14 @@ uint64_t dgc_biquad_scratch_floats(const dgc_biquad_params *p, int32_t backward)
  * per-lane cutoff/q; y [B][T][L].  scratch_dev NULL = context-owned buffer. */
 int32_t dgc_biquad_fwd(dgc_ctx *ctx, const dgc_biquad_params *p, const float *x_dev, const float *cutoff_dev,
                        const float *q_dev, float *scratch_dev, float *y_dev);
+/* The bank continuing from, and leaving behind, Graph.biquad's four history cells (HigherOps.swift:408-437):
+ * state_dev [B][4][L] = y[n-1], y[n-2], x[n-1], x[n-2] per voice and lane (the x rows hold the shared input's
+ * history: equal across lanes, the kernels read the first lane of a group).  Consecutive calls over consecutive
+ * blocks continue the recurrence exactly (preserveState, Sources/DGenLazy/Realize.swift:551-553); calling it block
+ * by block with NEW cutoff / q per block is the control-rate form of the reference's per-frame coefficient
+ * evaluation (coefficients constant inside a block, state carried across).  state_dev NULL = dgc_biquad_fwd. */
+int32_t dgc_biquad_fwd_state(dgc_ctx *ctx, const dgc_biquad_params *p, const float *x_dev, const float *cutoff_dev,
+                             const float *q_dev, float *scratch_dev, float *state_dev, float *y_dev);
 /* Reverse-time pass (BPTT, Sources/DGen/Gradients.swift:765-778,
  * Sources/DGen/Blocks/Emission/BPTTEmission.swift:471-518) for loss = loss_scale * sum (y - target)^2:
  * gradients w.r.t. the per-lane cutoff and q, summed over voices and frames; loss_dev gets the loss.
@@ -510,6 +535,107 @@ int32_t dgc_block_emit_sequential(const dgc_uop *ops, int32_t n_ops, const char 
                                   uint64_t out_cap, uint64_t *needed);
 int32_t dgc_block_compile_sequential(dgc_ctx *ctx, const dgc_uop *ops, int32_t n_ops, const char *kernel_name,
                                      dgc_module **out);
+
+/* ---- block plans ---------------------------------------------------------------------------------------
+ * What the host's block matcher hands over for one realize() / backward(): the scheduler's blocks in order
+ * (Sources/DGen/Blocks/BlockFormation.swift:5-85 partitionIntoBlocks, :1733 determineTensorBlocks), each either a
+ * recognised primitive of this library or a generated block (dgc_block_compile), with every buffer given as an
+ * OFFSET into one arena, the way the reference's kernels address one flat `memory` through cell offsets
+ * (Sources/DGen/Renderer/Renderer.swift:134-143 CompiledKernel, Sources/DGen/Runtime.swift:732-744).
+ * dgc_plan_run enqueues the steps on the context stream in order; steps marked stream 1 go to the context's side
+ * stream between a DGC_PLAN_FORK (side starts where main stands) and a DGC_PLAN_JOIN (main waits for side), which
+ * is how independent blocks -- the harmonic and the noise branch of the synthesiser -- overlap.  A plan can be
+ * recorded (dgc_graph_begin / _end around dgc_plan_run) and replayed, except for DGC_PLAN_ALLREDUCE steps.
+ *
+ * Step arguments: a[] = arena offsets in floats (DGC_PLAN_NONE = absent), i[] = integers, f[] = floats; an
+ * offset that receives a double (a loss) must be even and takes two floats.  Per op (names as the entry points):
+ *   FORK, JOIN            -
+ *   OSC_BANK_CONST        a: freq amp audio                  i: K T phase_mode             f: sample_rate
+ *   HARMONIC_RENDER       a: f0 uv amps gain scratch audio   i: B T K F phase_mode accumulate   f: sample_rate scale
+ *   BANDS_TO_TAPS         a: bands w taps                    i: rows nbands taps
+ *   FIR_NOISE             a: noise taps noise_gain audio     i: B T F taps accumulate      f: scale
+ *   ADD                   a: x y out n                       (out = x + y over n floats; out may be x)
+ *   COPY                  a: src dst n
+ *   ONEPOLE               a: x y state                       i: B T                        f: a
+ *   BIQUAD_FWD            a: x cutoff q scratch state y      i: B T L                      f: gain mode
+ *   BIQUAD_MSE_BWD        a: x cutoff q y target scratch grad_cutoff grad_q loss   i: B T L   f: gain mode loss_scale
+ *   STFT_MAG              a: x window mags                   i: V T N hop
+ *   PARTCONV              a: x ir scratch out                i: V T ir_len N hop accumulate    f: gain
+ *   PARTCONV_BWD          a: x ir g_out scratch g_x g_ir     i: V T ir_len N hop accumulate_gx f: gain
+ *   MSS_LOSS_FWD          a: pred target partial loss        i: B T nscales hop_div size0..    f: w_lin w_log
+ *   MSS_LOSS_BWD          a: pred target grad                i: B T nscales hop_div size0..    f: w_lin w_log upstream
+ *   LINEAR_FWD            a: A W bias C Ct                   i: M K N act
+ *   LINEAR_BWD            a: A W C dC dZ dA dW dbias At      i: M K N act
+ *   HEADS_FWD             a: z amps bands                    i: M K NB
+ *   HEADS_BWD             a: z g_amps g_bands gz             i: M K NB
+ *   HARMONIC_BWD          a: f0 uv amps gain g_audio scratch g_amps   i: B T K F phase_mode prepared   f: sample_rate scale
+ *   FIR_BWD               a: noise noise_gain g_audio g_taps i: B T F taps                 f: scale
+ *   ALLREDUCE             a: buf n
+ *   ADAM                  a: theta grad m v t_cell corr n    f: lr beta1 beta2 eps   (dgc_adam_step_counted: t_cell is one
+ *                                                            int32 in the arena, corr two floats)
+ *   SANITIZE              a: in out n
+ *   BLOCK                 i: kernel_index form count_or_frames lanes   (form 0: name(memory, count), one thread per
+ *                                                            index; form 1: name(memory, frames, lanes), one thread per lane)
+ */
+#define DGC_PLAN_NONE 0xffffffffffffffffull
+enum {
+  DGC_PLAN_FORK = 0, DGC_PLAN_JOIN, DGC_PLAN_OSC_BANK_CONST, DGC_PLAN_HARMONIC_RENDER, DGC_PLAN_BANDS_TO_TAPS,
+  DGC_PLAN_FIR_NOISE, DGC_PLAN_ADD, DGC_PLAN_COPY, DGC_PLAN_ONEPOLE, DGC_PLAN_BIQUAD_FWD, DGC_PLAN_BIQUAD_MSE_BWD,
+  DGC_PLAN_STFT_MAG, DGC_PLAN_PARTCONV, DGC_PLAN_PARTCONV_BWD, DGC_PLAN_MSS_LOSS_FWD, DGC_PLAN_MSS_LOSS_BWD,
+  DGC_PLAN_LINEAR_FWD, DGC_PLAN_LINEAR_BWD, DGC_PLAN_HEADS_FWD, DGC_PLAN_HEADS_BWD, DGC_PLAN_HARMONIC_BWD,
+  DGC_PLAN_FIR_BWD, DGC_PLAN_ALLREDUCE, DGC_PLAN_ADAM, DGC_PLAN_SANITIZE, DGC_PLAN_BLOCK, DGC_PLAN_OP_COUNT
+};
+typedef struct dgc_plan_step {
+  int32_t op;        /* DGC_PLAN_* */
+  int32_t stream;    /* 0 = the context stream, 1 = the side stream */
+  uint64_t a[10];
+  int32_t i[16];
+  float f[4];
+} dgc_plan_step;
+typedef struct dgc_plan {
+  const dgc_plan_step *steps;
+  int32_t n_steps;
+  dgc_module *const *modules;   /* BLOCK steps: i[0] indexes modules and kernels (may be NULL when there are none) */
+  const char *const *kernels;
+  int32_t n_kernels;
+} dgc_plan;
+/* Runs steps [first, first + count) of the plan on the arena (count < 0: to the end).  On an error the step index is
+ * part of dgc_last_error and nothing after it is enqueued; a side stream that was forked is joined first. */
+int32_t dgc_plan_run(dgc_ctx *ctx, dgc_arena *arena, const dgc_plan *plan, int32_t first, int32_t count);
+
+/* The training step of the harmonic+noise model as a plan (Examples/HarmonicE2E/Trainer.swift:247-487: forward ->
+ * multi-scale spectral loss -> backward -> optimizer step; Sources/DGenLazy/Backward.swift:174-230,
+ * Sources/DGenLazy/Optimizers.swift:164-243), with every tensor at a fixed arena offset:
+ *   controller h = tanh(.. tanh(X W0 + b0) ..) (n_trunk layers of `hidden`), z = h Wh + bh, heads (dgc_hn_heads_fwd),
+ *   taps = bands Wfs^T, dry = harmonic + FIR noise, out = dry + partitioned_convolve(dry, ir), 6-scale loss,
+ *   the backward of all of it into ONE flat gradient vector, all-reduce, Adam.
+ * Parameters are one flat vector: W0 [in][hidden], b0, W1, b1, .., Wh [hidden][K + nbands], bh, ir [ir_len].
+ * dgc_hn_train_plan fills `layout` (where the host puts inputs and finds outputs) and writes the steps:
+ * [0, n_forward_backward) is forward + backward, then one ALLREDUCE step, then one ADAM step.  A host with several
+ * ranks records the first range and the ADAM step separately and runs the ALLREDUCE step between the replays. */
+typedef struct dgc_hn_train_config {
+  int32_t B, T, K, F;        /* local voices, frames, harmonics, control frames */
+  float sample_rate;
+  int32_t nbands, taps;
+  int32_t in_features, hidden, n_trunk;   /* controller: in -> hidden x n_trunk (tanh) -> K + nbands */
+  int32_t ir_len, conv_n, conv_hop;       /* learnable impulse response, partition size and hop */
+  dgc_mss_params mss;
+  int32_t phase_mode;
+  int32_t global_voices;     /* voices over all ranks (the loss gradient is scaled by B / global_voices) */
+  float lr, beta1, beta2, eps;
+} dgc_hn_train_config;
+typedef struct dgc_hn_train_layout {
+  uint64_t total_floats;     /* arena size */
+  uint64_t n_params;
+  uint64_t params, grads, adam_m, adam_v, adam_t, adam_corr;
+  uint64_t x, f0, uv, gain, noise_gain, noise, w_fs, target;    /* inputs: X [F*B][in], controls [F][B], noise and target [B][T], Wfs [taps][nbands] */
+  uint64_t loss;             /* one double (two floats, even offset) */
+  uint64_t audio;            /* out [B][T]: dry + reverb */
+  int32_t n_steps, n_forward_backward;
+} dgc_hn_train_layout;
+/* steps may be NULL to size it (layout->n_steps).  Returns DGC_ERR_INVALID when cap is too small. */
+int32_t dgc_hn_train_plan(const dgc_hn_train_config *cfg, dgc_hn_train_layout *layout, dgc_plan_step *steps,
+                          int32_t cap);
 
 /* ---- gradient exchange between GPUs ------------------------------------------------------------------
  * One process per GPU, one communicator per context (NCCL, found at run time; DGC_NCCL_PATH overrides).

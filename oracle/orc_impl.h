@@ -200,14 +200,34 @@ void FN(orc_biquad_coef)(R cutoff, R q, R gain, R mode, FN(OrcBiquadCoef) *c) {
   R mult26 = recip24 * gain;
   R mult31 = mult9 * (R)2;
   R not_sub35 = (R)1 - div18;
-  R o23[6] = {div11, div13, mult19, mult21, (R)1, add22};
-  R o32[6] = {add10, sub12, 0, 0, mult31, mult31};
-  R o36[6] = {div11, div13, div18, mult20, (R)1, not_sub35};
-  c->b2 = FN(orc_selector)(add4, o23, 6) * mult26;
-  c->b1 = FN(orc_selector)(add4, o32, 6) * mult26;
-  c->b0 = FN(orc_selector)(add4, o36, 6) * mult26;
-  c->a2 = not_sub35 * recip24;
-  c->a1 = mult31 * recip24;
+  /* shelf coefficients, modes 6 (high shelf) and 7 (low shelf): HigherOps.swift:468-528 */
+  R A = SQRT(FABS(gain));
+  R cosW0Pos = mult9 * (R)-1;
+  R alphaShelf = sin14 / ((R)2.0 * abs17);
+  R Ap1 = A + (R)1, Am1 = A - (R)1;
+  R Ap1_cos = Ap1 * cosW0Pos, Am1_cos = Am1 * cosW0Pos;
+  R twoSqrtA_alpha = ((R)2.0 * SQRT(A)) * alphaShelf;
+  R hs_b0 = A * ((Ap1 + Am1_cos) + twoSqrtA_alpha);
+  R hs_b1 = (R)-2.0 * (A * (Am1 + Ap1_cos));
+  R hs_b2 = A * ((Ap1 + Am1_cos) - twoSqrtA_alpha);
+  R hs_a0 = (Ap1 - Am1_cos) + twoSqrtA_alpha;
+  R ls_b0 = A * ((Ap1 - Am1_cos) + twoSqrtA_alpha);
+  R ls_b1 = (R)2.0 * (A * (Am1 - Ap1_cos));
+  R ls_b2 = A * ((Ap1 - Am1_cos) - twoSqrtA_alpha);
+  R ls_a0 = (Ap1 + Am1_cos) + twoSqrtA_alpha;
+  R hs_a1n = ((R)2.0 * (Am1 - Ap1_cos)) / hs_a0, hs_a2n = ((Ap1 - Am1_cos) - twoSqrtA_alpha) / hs_a0;
+  R ls_a1n = ((R)-2.0 * (Am1 + Ap1_cos)) / ls_a0, ls_a2n = ((Ap1 + Am1_cos) - twoSqrtA_alpha) / ls_a0;
+  R o23[8] = {div11, div13, mult19, mult21, (R)1, add22, hs_b2 / hs_a0, ls_b2 / ls_a0};
+  R o32[8] = {add10, sub12, 0, 0, mult31, mult31, hs_b1 / hs_a0, ls_b1 / ls_a0};
+  R o36[8] = {div11, div13, div18, mult20, (R)1, not_sub35, hs_b0 / hs_a0, ls_b0 / ls_a0};
+  /* modes 0-5 scale by gain / a0; the shelves carry the gain in A (isShelfMode = mode >= 6, :533-548) */
+  int shelf = mode >= (R)6;
+  R s23 = FN(orc_selector)(add4, o23, 8), s32 = FN(orc_selector)(add4, o32, 8), s36 = FN(orc_selector)(add4, o36, 8);
+  c->b2 = shelf ? s23 : s23 * mult26;
+  c->b1 = shelf ? s32 : s32 * mult26;
+  c->b0 = shelf ? s36 : s36 * mult26;
+  c->a2 = shelf ? (mode >= (R)7 ? ls_a2n : hs_a2n) : not_sub35 * recip24;
+  c->a1 = shelf ? (mode >= (R)7 ? ls_a1n : hs_a1n) : mult31 * recip24;
 }
 
 /* y = ((b2*x2 + b1*x1) + b0*x0) - (a2*y2 + a1*y1)   (HigherOps.swift:532-567) */

@@ -58,6 +58,106 @@ def test_biquad_forward_matches_oracle(ctx, B, T, L, mode):
     assert np.abs(got - want).max() < 1e-4 * max(1.0, np.abs(want).max())
 
 
+@pytest.mark.parametrize("mode,gain", [(0.0, 0.7), (1.0, 1.0), (2.0, 1.3), (3.0, 1.0), (4.0, 1.0), (5.0, 0.5),
+                                       (6.0, 2.0), (6.0, 0.4), (7.0, 2.0), (7.0, 0.25), (5.5, 1.5), (6.5, 1.5)])
+def test_biquad_all_eight_modes_forward_and_gradients(ctx, mode, gain):
+    """Graph.biquad documents eight filter types (Sources/DGen/HigherOps.swift:388-398): the shelves (6 high, 7 low)
+    take their boost / cut from `gain` through A = sqrt(|gain|) and carry their own normalisation; a fractional
+    mode follows the graph's selector and `>= 6` / `>= 7` switches literally.  Forward against the oracle's
+    restatement of the coefficient graph, BPTT gradients against its fp64 evaluation."""
+    B, T, L = 2, 3000, 12
+    d = wl.biquad_bank_inputs(41, B=B, L=L, T=T)
+    x, q = d["x"], d["q"]
+    cut = np.exp(np.random.default_rng(7).uniform(np.log(400.0), np.log(8000.0), L)).astype(f32)
+    want = orc.biquad_bank(x, cut, q, gain=gain, mode=mode)                                  # [B][L][T]
+    y = ctx.biquad_fwd(dev(x), dev(cut), dev(q), gain=gain, mode=mode)
+    got = y.cpu().numpy().transpose(0, 2, 1)
+    assert np.abs(got - want).max() < 1e-4 * max(1.0, np.abs(want).max())
+    target = orc.biquad_bank(x, cut * f32(1.05), q * f32(0.9), gain=gain, mode=mode)
+    scale = 1.0 / (B * T)
+    loss64, gc64, gq64 = orc.biquad_bank_mse_grad(x, cut, q, target, scale=scale, gain=gain, mode=mode)
+    gc, gq, loss = ctx.biquad_mse_bwd(dev(x), dev(cut), dev(q), y, dev(target.transpose(0, 2, 1)), loss_scale=scale,
+                                      gain=gain, mode=mode)
+    assert abs(float(loss.cpu()[0]) - loss64) < 1e-3 * abs(loss64)
+    assert np.abs(gc.cpu().numpy() - gc64).max() < 2e-3 * np.abs(gc64).max()
+    assert np.abs(gq.cpu().numpy() - gq64).max() < 2e-3 * np.abs(gq64).max()
+
+
+def test_biquad_mode_out_of_range_is_refused(ctx):
+    d = wl.biquad_bank_inputs(3, B=1, L=2, T=64)
+    with pytest.raises(dgen_b200.DgenCudaError):
+        ctx.biquad_fwd(dev(d["x"]), dev(d["cutoff"]), dev(d["q"]), mode=8.0)
+
+
+@pytest.mark.parametrize("B,L,cuts", [(2, 8, (700, 1300, 512)), (1, 130, (1024, 1024)), (2, 16, (1, 2, 3, 2048, 5)),
+                                      (64, 1024, (1024, 512))])
+def test_biquad_state_cells_continue_across_calls(ctx, B, L, cuts):
+    """Consecutive calls over consecutive blocks with the history cells carried (preserveState,
+    Sources/DGenLazy/Realize.swift:551-553) equal one call over the whole signal -- also across the tensor-core
+    first pass (the last case), ragged blocks and blocks of one or two frames."""
+    import torch
+    T = int(sum(cuts))
+    d = wl.biquad_bank_inputs(23, B=B, L=L, T=T)
+    x, cut, q = dev(d["x"]), dev(d["cutoff"]), dev(d["q"])
+    whole = ctx.biquad_fwd(x, cut, q)
+    state = torch.zeros(B, 4, L, device="cuda")
+    n0, parts = 0, []
+    for n in cuts:
+        parts.append(ctx.biquad_fwd(x[:, n0:n0 + n].contiguous(), cut, q, state=state))
+        n0 += n
+    got = torch.cat(parts, dim=1)
+    scale = max(1.0, float(whole.abs().max()))
+    assert float((got - whole).abs().max()) <= 2e-5 * scale
+    ctx.sync()
+    st = state.cpu().numpy()
+    w = whole.cpu().numpy()
+    assert np.abs(st[:, 0] - w[:, T - 1]).max() <= 2e-5 * scale and np.abs(st[:, 1] - w[:, T - 2]).max() <= 2e-5 * scale
+    assert np.array_equal(st[:, 2], np.repeat(d["x"][:, T - 1:T], L, axis=1))
+    assert np.array_equal(st[:, 3], np.repeat(d["x"][:, T - 2:T - 1], L, axis=1))
+
+
+def test_biquad_control_rate_coefficients_by_blocks(ctx):
+    """Coefficients that change at control rate: one call per control block with that block's cutoff and Q, the
+    history cells carried across -- against the reference recurrence with the coefficient graph evaluated per
+    frame (Sources/DGen/HigherOps.swift:401-570) on piecewise-constant cutoff / Q."""
+    import torch
+    B, L, blocks, n = 1, 6, 5, 600
+    T = blocks * n
+    rng = np.random.default_rng(9)
+    x = rng.standard_normal((B, T)).astype(f32)
+    cuts = np.exp(rng.uniform(np.log(300.0), np.log(6000.0), (blocks, L))).astype(f32)
+    qs = np.exp(rng.uniform(np.log(0.5), np.log(6.0), (blocks, L))).astype(f32)
+    want = np.zeros((T, L), f32)
+    for l in range(L):
+        x1 = x2 = y1 = y2 = f32(0)
+        for t in range(T):
+            b0, b1, b2, a1, a2 = [f32(v) for v in orc.biquad_coef(cuts[t // n, l], qs[t // n, l], 1.0, 0.0)]
+            x0 = x[0, t]
+            v = f32(f32(f32(x2 * b2) + f32(x1 * b1)) + f32(x0 * b0)) - f32(f32(y2 * a2) + f32(y1 * a1))
+            want[t, l] = v
+            x2, x1, y2, y1 = x1, x0, y1, f32(v)
+    state = torch.zeros(B, 4, L, device="cuda")
+    parts = [ctx.biquad_fwd(dev(x[:, k * n:(k + 1) * n]), dev(cuts[k]), dev(qs[k]), state=state) for k in range(blocks)]
+    got = torch.cat(parts, dim=1).cpu().numpy()[0]
+    assert np.abs(got - want).max() <= 1e-4 * max(1.0, np.abs(want).max())
+
+
+def test_onepole_state_cell_continues_across_calls(ctx):
+    import torch
+    B, cuts = 3, (5000, 1, 2047, 2049, 300)
+    T = int(sum(cuts))
+    x = torch.randn(B, T, device="cuda")
+    whole = ctx.onepole_fwd(x, 0.97)
+    state = torch.zeros(B, device="cuda")
+    n0, parts = 0, []
+    for n in cuts:
+        parts.append(ctx.onepole_fwd(x[:, n0:n0 + n].contiguous(), 0.97, state=state))
+        n0 += n
+    got = torch.cat(parts, dim=1)
+    assert float((got - whole).abs().max()) <= 1e-5 * max(1.0, float(whole.abs().max()))
+    assert torch.equal(state, got[:, -1])
+
+
 def test_biquad_lanes_are_independent(ctx):
     """Lane independence is exact (Tests/DGenLazyTests/TensorBiquadGradientTests.swift)."""
     d = wl.biquad_bank_inputs(3, B=2, L=8, T=2000)

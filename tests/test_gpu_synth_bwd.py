@@ -97,6 +97,37 @@ def test_backward_kernels_are_deterministic(ctx):
     assert np.array_equal(a, b)
 
 
+def temporal_grad_scan_reference(g, reset, scale):
+    """The reference's reverse loop, literally (Sources/DGen/Emit+TemporalGradient.swift:60-88), in float64."""
+    E, T = g.shape
+    out = np.zeros((E, T), np.float64)
+    for e in range(E):
+        carry = 0.0
+        for n in range(T - 1, -1, -1):
+            active = 0.0 if (reset is not None and reset[n] > 0) else carry
+            out[e, n] = active
+            carry = float(g[e, n]) + active
+    return out * scale
+
+
+@pytest.mark.parametrize("E,T,density", [(1, 1, 1.0), (3, 7, 0.3), (2, 1025, 0.01), (4, 3000, 0.2), (2, 40000, 0.0005),
+                                         (1, 5000, 1.0), (2, 2048, 0.0)])
+def test_temporal_grad_scan_with_resets_follows_the_reference_loop(ctx, E, T, density):
+    """A reset at frame r cuts the sum for earlier frames after g[r] and zeroes out[r]; runs of resets, resets on the
+    first and last frame, a reset on every frame, none at all."""
+    rng = np.random.default_rng(T)
+    g = rng.standard_normal((E, T)).astype(f32)
+    reset = (rng.uniform(size=T) < density).astype(f32)
+    if T > 4:
+        reset[0] = 1.0
+        reset[T - 1] = 1.0 if density > 0 else 0.0
+        reset[T // 2] = -1.0            # not a reset: the test is > 0
+    want = temporal_grad_scan_reference(g, reset, 1.0 / 44100.0)
+    got = ctx.temporal_grad_scan(dev(g), 1.0 / 44100.0, reset=dev(reset)).cpu().numpy()
+    assert np.abs(got - want).max() <= 1e-6 * max(np.abs(want).max(), 1e-12)
+    assert np.all(got[:, reset > 0] == 0.0)
+
+
 def test_temporal_grad_scan_is_the_exclusive_reverse_sum(ctx):
     """temporalGradScan without resets (Sources/DGen/Emit+TemporalGradient.swift:60-88): out[n] = sum_{m>n} g[m]."""
     rng = np.random.default_rng(3)
