@@ -60,6 +60,9 @@ struct dgc_ctx {
   int comm_world = 1;
   // spectral-loss backward: windows owned per block, chosen per (N, hop, H, B) so that the grid fills whole waves
   std::map<std::pair<std::pair<int, int>, std::pair<int, int>>, int> mss_bwd_owned;
+  // matrix products issued per kernel family since the context was created (dgc_gemm_path_counts):
+  // 0 SIMT register tiles, 1 tcgen05 generic-orientation kernel, 2 tcgen05 asynchronous pipeline, 3 the same with 128 x 256 tiles
+  int64_t gemm_paths[4] = {0, 0, 0, 0};
   // step recording (graph.cu)
   bool capturing = false;
   cudaStream_t capture_stream = nullptr;   // the stream the recording started on (calls inside may rebind the context)

@@ -156,6 +156,7 @@ int32_t launch_sgemm(dgc_ctx *ctx, const float *A, const float *B, const float *
     if (!dst) return DGC_ERR_OOM;
   }
   dim3 grid(dgc_div_up(N, bn), dgc_div_up(M, bm), splits);
+  ctx->gemm_paths[(kk && (splits == 1 || kps % 32 == 0)) ? (wide ? 3 : 2) : (tc ? 1 : 0)]++;
   if (kk && (splits == 1 || kps % 32 == 0)) {
     // both operands contiguous along k: the cp.async pipeline
 #define DGC_KK_LAUNCH(BKV, SWV)                                                                                      \
@@ -446,6 +447,12 @@ DGC_EXPORT int32_t dgc_adam_step_counted(dgc_ctx *ctx, float *theta_dev, const f
   adam_counted_kernel<<<dgc_div_up((int64_t)n, 256), 256, 0, ctx->stream>>>(theta_dev, grad_dev, m_dev, v_dev, n, lr,
                                                                             beta1, beta2, eps, corr_dev);
   DGC_LAUNCHED(ctx, "adam");
+  return DGC_OK;
+}
+
+DGC_EXPORT int32_t dgc_gemm_path_counts(dgc_ctx *ctx, int64_t *out4) {
+  if (!ctx || !out4) return DGC_ERR_INVALID;
+  for (int i = 0; i < 4; ++i) out4[i] = ctx->gemm_paths[i];
   return DGC_OK;
 }
 

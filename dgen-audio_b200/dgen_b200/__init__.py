@@ -188,6 +188,7 @@ SIGNATURES = {
     "dgc_partconv_bwd": (_i32, [_vp, _vp, _i32, _i32, _vp, _i32, _i32, _i32, _f, _vp, _vp, _i32, _vp, _vp]),
     "dgc_linear_fwd": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp]),
     "dgc_linear_bwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp]),
+    "dgc_gemm_path_counts": (_i32, [_vp, C.POINTER(C.c_int64)]),
     "dgc_adam_step": (_i32, [_vp, _vp, _vp, _vp, _vp, _u64, _i32, _f, _f, _f, _f]),
     "dgc_sanitize": (_i32, [_vp, _vp, _u64, _vp]),
     "dgc_reduce_frames": (_i32, [_vp, _vp, _i64, _i64, _f, _i32, _vp]),
@@ -390,6 +391,12 @@ class Context:
 
     def launch_count(self):
         return self.lib.dgc_launch_count(self.h)
+
+    def gemm_path_counts(self):
+        """(simt, tcgen05 generic, tcgen05 pipeline, tcgen05 pipeline with wide tiles) products issued so far."""
+        out = (C.c_int64 * 4)()
+        self.check(self.lib.dgc_gemm_path_counts(self.h, out))
+        return tuple(out)
 
     def _empty(self, *shape, dtype=None):
         return self.torch.empty(*shape, dtype=dtype or self.torch.float32, device="cuda:%d" % self.device)

@@ -367,6 +367,12 @@ int32_t dgc_linear_bwd(dgc_ctx *ctx, const float *a_dev, const float *w_dev, con
                        int32_t M, int32_t K, int32_t N, int32_t act, float *dz_dev, float *da_dev, float *dw_dev,
                        float *dbias_dev, const float *at_dev);
 
+/* How many matrix products this context has sent to each kernel family since it was created: out4[0] SIMT register
+ * tiles (small products), [1] tcgen05 kernel for any operand orientation, [2] tcgen05 asynchronous pipeline (both
+ * operands contiguous along the reduction), [3] the same with 128 x 256 output tiles.  For tests and profiling: a shape
+ * that silently left the tensor cores shows here.  No reference counterpart. */
+int32_t dgc_gemm_path_counts(dgc_ctx *ctx, int64_t *out4);
+
 /* Adam step on device (Sources/DGenLazy/Optimizers.swift:164-243: bias-corrected, eps outside the
  * square root, the reference's operation order); t is the 1-based step index. */
 int32_t dgc_adam_step(dgc_ctx *ctx, float *theta_dev, const float *grad_dev, float *m_dev, float *v_dev, uint64_t n,

@@ -32,6 +32,14 @@ HANN16 = np.array([0.0, 0.038060218, 0.14644659, 0.3086583, 0.49999997, 0.691341
                    1.0, 0.9619398, 0.85355353, 0.69134176, 0.5, 0.30865842, 0.14644668, 0.038060308], np.float32)
 
 
+# toolchain/harness/toolchain_harness.c:106-112 (kWavetable), copied to memory[0..31] as it stands; the generated
+# code reads the two waves as memory[16 * wave + sample]
+WAVETABLE = np.array([0.0, 0.0, 0.38268343, 0.125, 0.70710677, 0.25, 0.9238795, 0.375, 1.0, 0.5, 0.9238795, 0.625,
+                      0.70710677, 0.75, 0.38268343, 0.875, 0.0, -1.0, -0.38268343, -0.875, -0.70710677, -0.75,
+                      -0.9238795, -0.625, -1.0, -0.5, -0.9238795, -0.375, -0.70710677, -0.25, -0.38268343, -0.125],
+                     np.float32)
+
+
 def memory_for(kind):
     if kind == "scalar-synth":
         m = np.zeros(1024, np.float32)
@@ -39,6 +47,10 @@ def memory_for(kind):
     elif kind == "feedback-delay-effect":
         m = np.zeros(88005, np.float32)
         m[:3] = [37.0, 0.35, 0.4]
+    elif kind == "wavetable-instrument":
+        m = np.zeros(1024, np.float32)
+        m[:32] = WAVETABLE
+        m[32:35] = [110.0, 0.35, 0.2]
     elif kind == "spectral-effect":
         m = np.zeros(3700, np.float32)
         m[0], m[8], m[16], m[24] = 1.0, 0.35, 0.15, 0.05
@@ -60,6 +72,9 @@ def main():
     out["feedback_delay"] = orc.ref_run("feedback-delay-effect", m, x, BLOCKS, FRAMES, SR)
     m = memory_for("spectral-effect")
     out["spectral_effect"] = orc.ref_run("spectral-effect", m, x, BLOCKS, FRAMES, SR)
+    m = memory_for("wavetable-instrument")
+    out["wavetable_instrument"] = orc.ref_run("wavetable-instrument", m, None, BLOCKS, FRAMES, SR)
+    out["wavetable_memory"] = memory_for("wavetable-instrument")[:36].copy()
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "ref_artefacts.npz")
     np.savez_compressed(path, **out)
     print("wrote", path, {k: v.shape for k, v in out.items()})

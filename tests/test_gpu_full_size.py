@@ -58,6 +58,36 @@ def test_biquad_bank_full_size_forward_and_bptt(ctx):
     assert np.abs(got - want).max() < 1e-4 * max(1.0, np.abs(want).max())
     got_full = y[0, :6000][:, lanes].cpu().numpy()
     assert np.abs(got_full - want).max() < 1e-4 * max(1.0, np.abs(want).max())
+    # the WHOLE length against the serial recurrence of the oracle, last chunk included, for lanes that span the
+    # parameter range -- the lowest cutoff, the highest Q (poles closest to the unit circle: the double-precision
+    # carry over 512 chunks is what keeps these right), the highest cutoff, the lowest Q, and two in between
+    cn, qn = d["cutoff"], d["q"]
+    span = sorted({int(np.argmin(cn)), int(np.argmax(qn)), int(np.argmax(cn)), int(np.argmin(qn)),
+                   int(np.argmin(cn / qn)), 77, 200})
+    want_full = orc.biquad_bank(d["x"][0:1], cn[span], qn[span])[0].T                      # [T][lanes]
+    got_full = y[0][:, span].cpu().numpy()
+    scale = np.maximum(1.0, np.abs(want_full).max(axis=0))
+    err = np.abs(got_full - want_full).max(axis=0) / scale
+    print("full-length biquad vs oracle, lanes %s (cutoff %s, Q %s): max rel err %s"
+          % (span, np.round(cn[span], 1), np.round(qn[span], 2), err))
+    assert (err < 1e-4).all(), err
+    assert (np.abs(got_full[-600:] - want_full[-600:]).max(axis=0) / scale < 1e-4).all()      # the last chunk
+    # BPTT over the whole length for those lanes (one voice) against the fp64 evaluation of the recurrence
+    tspan = orc.biquad_bank(d["x"][0:1], cn[span] * f32(1.05), qn[span])                    # [1][lanes][T]
+    l64, gc64, gq64 = orc.biquad_bank_mse_grad(d["x"][0:1], cn[span], qn[span], tspan, scale=1.0 / T)
+    ys = ctx.biquad_fwd(x[0:1].contiguous(), dev(cn[span]), dev(qn[span]))
+    g1, g2, l1 = ctx.biquad_mse_bwd(x[0:1].contiguous(), dev(cn[span]), dev(qn[span]), ys,
+                                    dev(tspan.transpose(0, 2, 1)), loss_scale=1.0 / T)
+    ctx.sync()
+    g1, g2 = g1.cpu().numpy(), g2.cpu().numpy()
+    # 1e-3 where the single-precision coefficient formula allows it (cutoff >= 400 Hz, see test_gpu_linrec.py)
+    hi = cn[span] >= 400.0
+    rel_c, rel_q = np.abs(g1 - gc64) / np.abs(gc64).max(), np.abs(g2 - gq64) / np.abs(gq64).max()
+    print("full-length BPTT vs fp64: rel err cutoff %s, q %s" % (rel_c, rel_q))
+    assert abs(float(l1.cpu()[0]) - l64) < 1e-3 * abs(l64)
+    assert (rel_c[hi] < 1e-3).all() and (rel_q[hi] < 1e-3).all()
+    assert (rel_c < 5e-2).all() and (rel_q < 5e-2).all()
+    del ys
     # BPTT at full size: gradients of the lanes above equal those of the small bank run alone (per-lane sums over
     # voices and frames do not mix lanes), up to the split of the voice sum
     target = ctx.biquad_fwd(x, cut * 1.05, q)

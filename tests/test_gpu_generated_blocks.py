@@ -312,3 +312,60 @@ def test_sequential_block_accum_and_noise_state_ops(ctx):
         assert got[RNG + l:RNG + l + 1].view(np.uint32)[0] == st
     m.close()
     m2.close()
+
+
+# ---- the reference's own fixture graphs as op lists, against the outputs of the reference's emitted C ----------
+def test_reference_fixture_graphs_as_op_lists_match_the_reference_artefacts(ctx):
+    """toolchain/fixtures/scalar-synth.lisp and feedback-delay-effect.lisp are "leftover" graphs (a stateful phasor
+    with waveshaping; a delay with one-sample history feedback) that no primitive covers: written as op lists,
+    emitted and compiled here, they reproduce the outputs of the reference's own generated C for the same graphs and
+    harness inputs (tests/golden/ref_artefacts.npz, made by tests/golden/make_golden.py from
+    toolchain/generated/hermetic/*.c).  This pins the emitter to the reference's emitted code, not to an
+    interpreter of its own."""
+    gold = np.load(os.path.join(HERE, "golden", "ref_artefacts.npz"))
+    n, sr = gold["scalar_synth"].size, 48000.0
+    # --- scalar-synth: memory[0..2] = freq, drive, gain; cell 3 = phasor state; out at OUT
+    OUT = 64
+    ops = [("LOAD_SCALAR", 0), ("CONST", 0, 0, 0, 0.0), ("PHASOR", 3, 0, 1, sr),          # 0 1 2: phase
+           ("CONST", 0, 0, 0, 6.283185), ("MUL", 2, 3), ("SIN", 4),                        # 3 4 5: fundamental
+           ("CONST", 0, 0, 0, 12.56637), ("MUL", 2, 6), ("COS", 7),                        # 6 7 8: harmonic
+           ("CONST", 0, 0, 0, 0.125), ("MUL", 8, 9), ("ADD", 5, 10),                       # 9 10 11
+           ("LOAD_SCALAR", 1), ("MUL", 12, 11), ("TANH", 13),                              # 12 13 14: shaped
+           ("LOAD_SCALAR", 2), ("MUL", 15, 14), ("STORE_FRAME_LANE", OUT, 16)]             # 15 16 17
+    mem = torch.zeros(OUT + n, device="cuda")
+    mem[:3] = torch.tensor([220.0, 1.75, 0.2])
+    m = ctx.compile_block(ops, name="scalar_synth", sequential=True)
+    # the harness calls the artefact block by block with the state kept in memory: two calls here, the second
+    # continuing from the phasor cell the first one left
+    half = n // 2
+    m.launch("scalar_synth", 1, 32, [mem, C.c_int(half), C.c_int(1)])
+    ctx.sync()
+    state_mid = float(mem[3].cpu())
+    ops2 = [tuple(o) if o[0] != "STORE_FRAME_LANE" else ("STORE_FRAME_LANE", OUT + half, 16) for o in ops]
+    m2 = ctx.compile_block(ops2, name="scalar_synth_b", sequential=True)
+    m2.launch("scalar_synth_b", 1, 32, [mem, C.c_int(n - half), C.c_int(1)])
+    ctx.sync()
+    mem2 = mem
+    got = mem[OUT:OUT + n].cpu().numpy()
+    assert 0.0 <= state_mid < 1.0
+    assert np.abs(got - gold["scalar_synth"]).max() < 2e-6      # the artefact uses a 4-lane polynomial sine
+    assert float(mem2[3].cpu()) == float(gold["scalar_synth_final_phase"][0])   # the phasor state, bit for bit
+    m.close()
+    m2.close()
+    # --- feedback-delay-effect: delayed = delay(dry + fb * history, 37); history <- delayed; out = mix(dry, delayed, wet)
+    x = gold["input"]
+    D, X, W, HIST, OUTF = 37, 128, 128 + n + 64, 8, 128 + 2 * n + 128
+    ops = [("LOAD", X), ("HISTORY_READ", HIST), ("LOAD_SCALAR", 1), ("MUL", 2, 1), ("ADD", 0, 3),   # 0..4: w = dry + fb * h
+           ("STORE_FRAME_LANE", W, 4),                                                              # 5: the delay's storage
+           ("LOAD", W - D), ("HISTORY_WRITE", HIST, 6),                                             # 6 7: delayed = w[n - 37]
+           ("LOAD_SCALAR", 2), ("CONST", 0, 0, 0, 1.0), ("SUB", 9, 8), ("MUL", 0, 10), ("MUL", 7, 8),  # 8..12
+           ("ADD", 11, 12), ("OUTPUT", OUTF, 13)]
+    mem = torch.zeros(OUTF + n, device="cuda")
+    mem[:3] = torch.tensor([37.0, 0.35, 0.4])
+    mem[X:X + n] = torch.from_numpy(x).cuda()
+    m = ctx.compile_block(ops, name="feedback_delay", sequential=True)
+    m.launch("feedback_delay", 1, 32, [mem, C.c_int(n), C.c_int(1)])
+    ctx.sync()
+    got = mem[OUTF:OUTF + n].cpu().numpy()
+    assert np.abs(got - gold["feedback_delay"]).max() < 1e-6
+    m.close()

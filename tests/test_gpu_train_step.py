@@ -73,6 +73,53 @@ def test_train_step_gradients_and_adam_update():
     ctx.close()
 
 
+def test_train_step_gradients_through_the_tensor_core_matmuls():
+    """The same comparison at the controller width of the training configuration (hidden 512, 4096 rows): every large
+    product of the step -- forward layers, input gradients, split-K weight gradients, the transposed-activation
+    epilogue -- runs on the tcgen05 kernels, which the context's path counters confirm, and the gradients that
+    flowed through them still agree with the fp64 autograd evaluation of the graph."""
+    B, T, K, F, NB, NT, H = 4, 4096, 24, 1024, 9, 33, 512
+    d = wl.harmonic_noise_inputs(71, B=B, T=T, K=K, F=F, nbands=NB, taps=NT)
+    tg = wl.harmonic_noise_inputs(72, B=B, T=T, K=K, F=F, nbands=NB, taps=NT)
+    target = orc.harmonic_noise_render(tg["f0"], tg["uv"], tg["amps"], tg["gain"], tg["noise_gain"],
+                                       wl.taps_from_bands(tg), tg["noise"], T, d["sr"])
+    X = tr.features_from_controls(d["f0"], d["gain"])
+    ctx = dgen_b200.Context(0)
+    model = tr.HarmonicModel(ctx, B, T, K=K, F=F, nbands=NB, taps=NT, hidden=H, ir_len=600, conv_n=256, conv_hop=128,
+                             sizes=(512, 128, 64), seed=5)
+    args = [dev(X), dev(d["f0"]), dev(d["uv"]), dev(d["gain"]), dev(d["noise_gain"]), dev(d["noise"]), dev(d["W"]),
+            dev(target)]
+    p0 = model.params.cpu().numpy().copy()
+    P = {n: to.t64(p0[o:o + int(np.prod(s))].reshape(s)).requires_grad_(True) for n, o, s in model.layout}
+    rows = to.rows_of(F, T)
+    z = to.mlp(to.t64(X), [P["W%d" % i] for i in range(4)], [P["b%d" % i] for i in range(4)])
+    amps, bands = to.heads(z, K)
+    taps = (bands @ to.t64(d["W"]).T).reshape(F, B, NT)
+    dry = to.harmonic_render(to.t64(d["f0"]), to.t64(d["uv"]), amps.reshape(F, B, K), to.t64(d["gain"]), T, d["sr"], rows) \
+        + to.fir_noise(to.t64(d["noise"]), taps, to.t64(d["noise_gain"]), rows)
+    out = dry + to.partconv(dry, P["ir"], 256, 128)
+    loss64 = to.mss_loss(out, to.t64(target), sizes=(512, 128, 64))
+    loss64.backward()
+    before = ctx.gemm_path_counts()
+    loss = model.forward(*args)
+    grads = model.backward(*args).cpu().numpy()
+    ctx.sync()
+    used = [a - b for a, b in zip(ctx.gemm_path_counts(), before)]
+    print("matrix products by kernel family (simt, tc generic, tc pipeline, tc pipeline wide):", used)
+    # three 512-wide trunk layers forward, their input gradients and their weight gradients: at least nine products
+    # on the asynchronous tensor-core pipeline; nothing that large may have fallen back to the SIMT kernel
+    assert used[2] + used[3] >= 9 and used[1] + used[2] + used[3] >= 12
+    assert abs(float(loss.cpu()[0]) - float(loss64.detach())) < 1e-4 * float(loss64.detach())
+    for n, o, s in model.layout:
+        g = grads[o:o + int(np.prod(s))].reshape(s)
+        want = P[n].grad.numpy()
+        err = np.abs(g - want).max() / np.abs(want).max()
+        print("%-3s rel grad err max %.2e" % (n, err))
+        assert err < (1e-2 if n == "ir" else 1e-3), (n, err)
+    model.close()
+    ctx.close()
+
+
 def test_loss_decreases_over_a_few_steps():
     """OptimizerTests-style convergence check (Tests/DGenLazyTests/OptimizerTests.swift:147-390)."""
     B, T, K, F, NB, NT = 2, 4096, 16, 32, 9, 33

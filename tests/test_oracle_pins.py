@@ -71,6 +71,29 @@ def test_history_feedback_matches_reference_artefact():
     assert np.abs(out - GOLD["feedback_delay"]).max() < 1e-6
 
 
+def test_row_lerp_matches_reference_artefact():
+    """wavetable-instrument: `peek` reads a [16 x 2] table at a fractional sample index with the arithmetic
+    sampleRow shares -- wrap into [0, rows), floor row, next row wrapping to 0 at the end, (1 - frac) * lo + frac * hi
+    (toolchain/generated/hermetic/wavetable-instrument.c: t28..t69; Sources/DGen/Emit+RowSelection.swift:166-199).
+    The oracle's orc_sample_row on the artefact's own table and phase reproduces the artefact's audio."""
+    gold, mem = GOLD["wavetable_instrument"], GOLD["wavetable_memory"]
+    n = gold.size
+    freq, wave, gain = f32(mem[32]), f32(mem[33]), f32(mem[34])
+    ph = orc.phasor_stateful(np.full((n, 1), freq, f32), 48000.0)[:, 0]
+    idx = ((ph - np.floor(ph)) * f32(16.0)).astype(f32)
+    table = np.stack([mem[0:16], mem[16:32]], axis=1).astype(f32)            # [sample][wave] = memory[16 * wave + sample]
+    rows = orc.sample_row(table, idx)                                        # [n][2]: both waves at the sample index
+    w = f32(min(max(wave, f32(0)), f32(1)))
+    wl = f32(np.floor(w))
+    wf = f32(w - wl)
+    hi = int(min(wl + 1, 1))
+    out = gain * ((rows[:, int(wl)] * (f32(1) - wf)).astype(f32) + (rows[:, hi] * wf).astype(f32)).astype(f32)
+    assert np.abs(out.astype(f32) - gold).max() < 1e-7
+    # the wrap of the upper row: the last sample interpolates towards sample 0
+    k = int(np.argmax(idx >= 15.0))
+    assert idx[k] >= 15.0 and abs(rows[k, 0] - ((f32(1) - (idx[k] - 15)) * table[15, 0] + (idx[k] - 15) * table[0, 0])) < 1e-6
+
+
 def test_partitioned_convolve_matches_reference_artefact():
     """spectral-effect: bufferView ring + hop counter + Hann + FFT + partitioned MAC + IFFT +
     overlapAdd, N=16 hop=8 gain=0.5, 32-tap IR (toolchain/fixtures/spectral-effect.lisp)."""
