@@ -256,18 +256,20 @@ fir_noise8_kernel(dgc_fir_params prm, const float2 *__restrict__ rowtab, const f
   float *xs = sh + (size_t)max_rows * NTP;   // [SPT][Q]: position m <-> frame t0 - (NT-1) + m, de-interleaved by m % 8
   const int XN = TILE + NTP - 1 + SPT;       // zero-extended: the padding taps read beyond the tile
   const int Q = (XN + SPT - 1) / SPT + 1;
-  for (int i = threadIdx.x; i < R * NTP; i += NTH) {
-    const int rr = i / NTP, col = i - rr * NTP;
+  // one warp per control row, lanes along the taps (coalesced, no index division)
+  for (int rr = threadIdx.x >> 5; rr < R; rr += NTH / 32) {
     int r = rmin + rr;
     if (r >= F) r -= F;  // the ceil row wraps to row 0
     if (r >= F) r = F - 1;
-    rows[i] = col < NT ? taps_tab[((size_t)r * B + b) * NT + col] : 0.0f;
+    const float *src = taps_tab + ((size_t)r * B + b) * NT;
+    float *dst = rows + (size_t)rr * NTP;
+    for (int col = threadIdx.x & 31; col < NTP; col += 32) dst[col] = col < NT ? src[col] : 0.0f;
   }
   const float *xn = noise + (size_t)b * T;
   for (int m = threadIdx.x; m < Q * SPT; m += NTH) {
     int t = t0 - (NT - 1) + m;
     float v = (t >= 0 && t < T && m < TILE + NT - 1) ? xn[t] : 0.0f;
-    xs[(m % SPT) * Q + m / SPT] = v;
+    xs[(m & (SPT - 1)) * Q + (m >> 3)] = v;
   }
   __syncthreads();
 

@@ -14,6 +14,7 @@
 #include "common.cuh"
 #include "fft.cuh"
 #include "fft16.cuh"
+#include "tma.cuh"
 
 namespace {
 
@@ -167,12 +168,19 @@ __device__ __forceinline__ void pair_terms(float2 zk, float2 zn, float &lin, flo
 }
 // (a bin that is its own partner, k = 0 or k = N/2, is the pair (z, z): 2 X1 = 2 Re z, 2 X2 = 2 Im z)
 
-template <int N, bool SUM2>
+// boxes of the staged sample run (TMA variant): SPAN_BOX floats wide, at most SPAN_BOXES of them per signal; the
+// two signals' runs share the second transform buffer, which the transform does not touch before its middle stage
+constexpr int SPAN_BOX = 128, SPAN_BOXES = 17;
+static_assert(2 * SPAN_BOX * SPAN_BOXES * sizeof(float) <= padded(2048) * sizeof(float2), "the staged runs must fit the buffer");
+
+template <int N, bool SUM2, bool TMA>
 __device__ __forceinline__ void mss_fwd16_body(float2 *sm, float *red, int bx, int b, const float *__restrict__ pred,
                                                const float *__restrict__ pred_b,
                                                const float *__restrict__ target, int B, int T, int hop, int H,
                                                const float *__restrict__ window, const float2 *__restrict__ tw,
-                                               float *__restrict__ part_lin, float *__restrict__ part_log) {
+                                               float *__restrict__ part_lin, float *__restrict__ part_log,
+                                               const CUtensorMap *map_pred, const CUtensorMap *map_target,
+                                               uint64_t *bar, int32_t *status) {
   using Gm = dgfft16::Geo<N>;
   constexpr int TT = Gm::T;                     // threads per window
   constexpr int NF = LOSS16_THREADS / TT;       // windows per block
@@ -185,6 +193,37 @@ __device__ __forceinline__ void mss_fwd16_body(float2 *sm, float *red, int bx, i
   const float *x1b = SUM2 ? pred_b + (size_t)b * T : nullptr;   // prediction given as a sum of two signals
   float2 *bufa = sm + f * PN, *bufb = sm + (NF + f) * PN;
   float2 x[16];
+  if (TMA) {
+    // The run of samples the block's NF windows cover, fetched once by the copy engine: boxes of SPAN_BOX floats
+    // from column x0 = the first window's start rounded down to a multiple of 4 (16 bytes).  Columns before the
+    // start of the signal arrive as zeros, so no thread tests a bound; a window ends at frame h hop <= T - 1.
+    float *span1 = reinterpret_cast<float *>(sm + NF * PN), *span2 = span1 + SPAN_BOX * SPAN_BOXES;
+    const int tb0 = (bx * NF) * hop - (N - 1);
+    const int x0 = tb0 & ~3;
+    const int span = (NF - 1) * hop + N + (tb0 - x0);
+    const int nbox = (span + SPAN_BOX - 1) / SPAN_BOX;          // <= SPAN_BOXES whenever hop <= N
+    if (tid == 0) {
+      dgtma::mbar_expect_tx(bar, 2u * nbox * SPAN_BOX * sizeof(float));
+      for (int k = 0; k < nbox; ++k) {
+        dgtma::load_2d(span1 + k * SPAN_BOX, map_pred, x0 + k * SPAN_BOX, b, bar);
+        dgtma::load_2d(span2 + k * SPAN_BOX, map_target, x0 + k * SPAN_BOX, b, bar);
+      }
+    }
+    // one decision for the whole block (a wait that gave up in one thread must not leave the others at a barrier)
+    const bool arrived = __syncthreads_and(dgtma::mbar_wait(bar, 0));
+    if (!arrived) {   // the copies never completed: report, and leave without touching the buffers
+      if (tid == 0) atomicExch(status, 102);
+      return;
+    }
+    const int off = (tb0 - x0) + f * hop + lt;
+    const float *wp = window + lt;
+#pragma unroll
+    for (int m = 0; m < 16; ++m) {
+      const float w = valid ? __ldg(wp + m * TT) : 0.0f;
+      x[m] = make_float2(span1[off + m * TT] * w, span2[off + m * TT] * w);
+    }
+    __syncthreads();   // every warp has read its samples before any transform writes into that buffer
+  } else
   // a window ends at frame h * hop <= T - 1, so only its start can fall outside the signal
   if (valid && t_base >= 0) {
     const float *p1 = x1 + t_base + lt, *p2 = x2 + t_base + lt, *wp = window + lt;
@@ -244,12 +283,18 @@ __device__ __forceinline__ void mss_fwd16_body(float2 *sm, float *red, int bx, i
 
 constexpr int FWD16_SMEM_BYTES = 2 * padded(2048) * (int)sizeof(float2);
 
-template <bool SUM2>
+template <bool SUM2, bool TMA>
 __global__ void __launch_bounds__(LOSS16_THREADS, 6)
 mss_fwd16_kernel(const float *__restrict__ pred, const float *__restrict__ pred_b, const float *__restrict__ target,
-                 int B, int T, const FwdDesc d) {
-  extern __shared__ float2 fwd_sm[];
+                 int B, int T, const FwdDesc d, const __grid_constant__ CUtensorMap map_pred,
+                 const __grid_constant__ CUtensorMap map_target, int32_t *status) {
+  extern __shared__ __align__(128) float2 fwd_sm[];
   __shared__ float red[LOSS16_THREADS / 32];
+  __shared__ __align__(8) uint64_t span_bar;
+  if (TMA) {
+    if (threadIdx.x == 0) dgtma::mbar_init(&span_bar, 1);
+    __syncthreads();
+  }
   // one-dimensional grid, scale-major: first_block[s] counts the blocks of ALL voices of the scales before s, so
   // the blocks resident on an SM at any time run the same window size (the same instructions) except at the
   // boundary between two scales
@@ -260,7 +305,7 @@ mss_fwd16_kernel(const float *__restrict__ pred, const float *__restrict__ pred_
   const int b = r / per_voice, bx = r - b * per_voice;
   switch (d.N[s]) {
 #define CASE(NN) \
-  case NN: mss_fwd16_body<NN, SUM2>(fwd_sm, red, bx, b, pred, pred_b, target, B, T, d.hop[s], d.H[s], d.window[s], d.tw[s], d.lin[s], d.lg[s]); break;
+  case NN: mss_fwd16_body<NN, SUM2, TMA>(fwd_sm, red, bx, b, pred, pred_b, target, B, T, d.hop[s], d.H[s], d.window[s], d.tw[s], d.lin[s], d.lg[s], &map_pred, &map_target, &span_bar, status); break;
     CASE(64) CASE(128) CASE(256) CASE(512) CASE(1024) CASE(2048)
 #undef CASE
     default: break;
@@ -835,19 +880,34 @@ int32_t dgc_mss_loss_fwd_sum(dgc_ctx *ctx, const dgc_mss_params *p, const float 
   static const bool carved = [] {
     cudaFuncSetAttribute(mss_fwd_kernel<true>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     cudaFuncSetAttribute(mss_fwd_kernel<false>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-    cudaFuncSetAttribute(mss_fwd16_kernel<true>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-    cudaFuncSetAttribute(mss_fwd16_kernel<false>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    cudaFuncSetAttribute(mss_fwd16_kernel<true, false>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    cudaFuncSetAttribute(mss_fwd16_kernel<false, false>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    cudaFuncSetAttribute(mss_fwd16_kernel<false, true>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     return true;
   }();
   (void)carved;
   if (fd16.nscales > 0) {
+    // The windows' sample runs are staged by tensor-map copies when the signals qualify (rows a multiple of 16
+    // bytes long and 16-byte aligned, every hop <= its window); DGC_MSS_TMA=0 keeps the per-thread loads.
+    static const bool tma_on = [] {
+      const char *e = getenv("DGC_MSS_TMA");
+      return !(e && strcmp(e, "0") == 0);
+    }();
+    CUtensorMap mp, mt;
+    memset(&mp, 0, sizeof(mp));
+    memset(&mt, 0, sizeof(mt));
+    bool tma = tma_on && !pred_b_dev && p->hop_div >= 1;
+    tma = tma && dgtma::make_map_2d(&mp, pred_dev, p->B, p->T, SPAN_BOX) && dgtma::make_map_2d(&mt, target_dev, p->B, p->T, SPAN_BOX);
     if (pred_b_dev)
-      mss_fwd16_kernel<true><<<blocks16, LOSS16_THREADS, FWD16_SMEM_BYTES, ctx->stream>>>(
-          pred_dev, pred_b_dev, target_dev, p->B, p->T, fd16);
+      mss_fwd16_kernel<true, false><<<blocks16, LOSS16_THREADS, FWD16_SMEM_BYTES, ctx->stream>>>(
+          pred_dev, pred_b_dev, target_dev, p->B, p->T, fd16, mp, mt, ctx->status_dev);
+    else if (tma)
+      mss_fwd16_kernel<false, true><<<blocks16, LOSS16_THREADS, FWD16_SMEM_BYTES, ctx->stream>>>(
+          pred_dev, nullptr, target_dev, p->B, p->T, fd16, mp, mt, ctx->status_dev);
     else
-      mss_fwd16_kernel<false><<<blocks16, LOSS16_THREADS, FWD16_SMEM_BYTES, ctx->stream>>>(
-          pred_dev, nullptr, target_dev, p->B, p->T, fd16);
-    DGC_LAUNCHED(ctx, "mss_fwd16");
+      mss_fwd16_kernel<false, false><<<blocks16, LOSS16_THREADS, FWD16_SMEM_BYTES, ctx->stream>>>(
+          pred_dev, nullptr, target_dev, p->B, p->T, fd16, mp, mt, ctx->status_dev);
+    DGC_LAUNCHED(ctx, tma ? "mss_fwd16_tma" : "mss_fwd16");
   }
   if (fd8.nscales > 0) {
     if (pred_b_dev)

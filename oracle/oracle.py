@@ -47,6 +47,7 @@ def _declare(L):
         fn("orc_onepole", None, [p, C.c_int, ct, ct, p])
         fn("orc_biquad", None, [p, C.c_int, ct, ct, ct, ct, p])
         fn("orc_biquad_coef", None, [ct, ct, ct, ct, p])
+        fn("orc_biquad_with_coef", None, [p, C.c_int, p, p])
         fn("orc_biquad_bank", None, [p, C.c_int, C.c_int, C.c_int, p, p, ct, ct, p])
         fn("orc_biquad_bank_mse_grad", C.c_double, [p, C.c_int, C.c_int, C.c_int, p, p, ct, ct, p, ct, p, p])
         fn("orc_fft", None, [p, p, C.c_int, C.c_int])
@@ -162,6 +163,16 @@ def biquad_coef(cutoff, q, gain=1.0, mode=0.0, double=False, L=None):
     c = np.empty(5, dt)
     getattr(L or lib(), "orc_biquad_coef" + s)(cutoff, q, gain, mode, c)
     return c  # b0 b1 b2 a1 a2
+
+
+def biquad_exact_response(x, cutoff, q, gain=1.0, mode=0.0, L=None):
+    """The recurrence in double with the SINGLE-precision coefficients of the fp32 graph: what the fp32 filter would
+    give without the rounding of its own recurrence.  x [T] -> y [T] float64."""
+    coef = biquad_coef(cutoff, q, gain, mode, double=False, L=L).astype(np.float64)
+    x = np.ascontiguousarray(x, np.float64)
+    y = np.empty_like(x)
+    (L or lib()).orc_biquad_with_coef_f64(x, x.size, coef, y)
+    return y
 
 
 def biquad_bank(x, cutoff, q, gain=1.0, mode=0.0, double=False, L=None):

@@ -245,6 +245,19 @@ void FN(orc_biquad)(const R *x, int T, R cutoff, R q, R gain, R mode, R *y) {
   }
 }
 
+/* The same recurrence with GIVEN coefficients (b0 b1 b2 a1 a2).  In double with the single-precision
+ * coefficients it is the exact response of the filter the fp32 graph defines: the yardstick for how much of a
+ * difference between two fp32 evaluations is rounding noise of the recurrence itself. */
+void FN(orc_biquad_with_coef)(const R *x, int T, const R *coef, R *y) {
+  R x1 = 0, x2 = 0, y1 = 0, y2 = 0;
+  for (int n = 0; n < T; ++n) {
+    R x0 = x[n];
+    R v = ((x2 * coef[2] + x1 * coef[1]) + x0 * coef[0]) - (y2 * coef[4] + y1 * coef[3]);
+    y[n] = v;
+    x2 = x1; x1 = x0; y2 = y1; y1 = v;
+  }
+}
+
 /* Tensor biquad bank: x [B][T] shared by L lanes, y [B][L][T].  Lane independence is exact
  * (Tests/DGenLazyTests/TensorBiquadGradientTests.swift). */
 void FN(orc_biquad_bank)(const R *x, int B, int T, int L, const R *cutoff, const R *q, R gain, R mode, R *y) {

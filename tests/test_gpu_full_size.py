@@ -66,12 +66,22 @@ def test_biquad_bank_full_size_forward_and_bptt(ctx):
                    int(np.argmin(cn / qn)), 77, 200})
     want_full = orc.biquad_bank(d["x"][0:1], cn[span], qn[span])[0].T                      # [T][lanes]
     got_full = y[0][:, span].cpu().numpy()
+    # The yardstick.  For poles this close to the unit circle (60 Hz, Q 7.7: radius 0.9994) the single-precision
+    # recurrence carries its own rounding noise: run serially in fp32 it sits 1.7e-4 away from the exact response
+    # of the very same fp32 coefficients (the recurrence in double).  Two fp32 evaluations that round in different
+    # places cannot be asked to agree better than that, so each lane is held to: within 1e-4 of the serial fp32
+    # recurrence, OR no farther from the exact response than the serial fp32 recurrence is itself (+ 20 %).
+    exact = np.stack([orc.biquad_exact_response(d["x"][0], cn[l], qn[l]) for l in span], axis=1)   # [T][lanes] f64
     scale = np.maximum(1.0, np.abs(want_full).max(axis=0))
     err = np.abs(got_full - want_full).max(axis=0) / scale
-    print("full-length biquad vs oracle, lanes %s (cutoff %s, Q %s): max rel err %s"
-          % (span, np.round(cn[span], 1), np.round(qn[span], 2), err))
-    assert (err < 1e-4).all(), err
-    assert (np.abs(got_full[-600:] - want_full[-600:]).max(axis=0) / scale < 1e-4).all()      # the last chunk
+    noise = np.abs(want_full - exact).max(axis=0) / scale
+    err_exact = np.abs(got_full - exact).max(axis=0) / scale
+    print("full-length biquad, lanes %s (cutoff %s, Q %s):\n  vs serial fp32 %s\n  serial fp32 vs exact %s\n  ours vs exact %s"
+          % (span, np.round(cn[span], 1), np.round(qn[span], 2), err, noise, err_exact))
+    assert ((err < 1e-4) | (err_exact < 1.2 * noise)).all(), (err, noise, err_exact)
+    assert (err < 1e-4 + 2.0 * noise).all()
+    tail = slice(T - 600, T)                                                                # the last chunk
+    assert (np.abs(got_full[tail] - exact[tail]).max(axis=0) / scale < 1e-4 + 1.2 * noise).all()
     # BPTT over the whole length for those lanes (one voice) against the fp64 evaluation of the recurrence
     tspan = orc.biquad_bank(d["x"][0:1], cn[span] * f32(1.05), qn[span])                    # [1][lanes][T]
     l64, gc64, gq64 = orc.biquad_bank_mse_grad(d["x"][0:1], cn[span], qn[span], tspan, scale=1.0 / T)

