@@ -7,6 +7,7 @@
 #include <vector>
 
 #include "common.cuh"
+#include "tma.cuh"
 
 int32_t dgc_fail(dgc_ctx *ctx, int32_t code, const char *fmt, ...) {
   if (ctx) {
@@ -236,6 +237,57 @@ DGC_EXPORT int32_t dgc_sync(dgc_ctx *ctx, uint32_t timeout_ms) {
     cudaMemset(ctx->status_dev, 0, sizeof(int32_t));
     return dgc_fail(ctx, DGC_ERR_DEVICE, "device status word = %d", st);
   }
+  return DGC_OK;
+}
+
+// ---- self-test of the failure reporting: both calls are bounded by construction ------------------------------
+namespace {
+// waits on an mbarrier that nothing ever arrives on, with the library's bounded wait cut down to `polls`:
+// the wait gives up, the kernel records status 201 (the code of an expired pipeline wait) and returns
+__global__ void selftest_expired_wait_kernel(uint32_t polls, int32_t *status) {
+  __shared__ __align__(8) uint64_t bar;
+  if (threadIdx.x == 0) dgtma::mbar_init(&bar, 1);
+  __syncthreads();
+  const uint32_t a = dgtma::smem_addr(&bar);
+  bool done = false;
+  for (uint32_t it = 0; it < polls && !done; ++it) {
+    uint32_t d;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred q;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 q, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, q;\n\t"
+        "}\n"
+        : "=r"(d)
+        : "r"(a), "r"(0u)
+        : "memory");
+    done = d != 0;
+  }
+  if (!done && threadIdx.x == 0) atomicExch(status, 201);
+}
+// keeps one thread busy for about `us` microseconds of the global timer (capped by the caller)
+__global__ void selftest_busy_kernel(unsigned long long us) {
+  unsigned long long t0, t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+  do {
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  } while (t - t0 < us * 1000ull);
+}
+}  // namespace
+
+DGC_EXPORT int32_t dgc_selftest_expired_wait(dgc_ctx *ctx, uint32_t polls) {
+  if (!ctx) return DGC_ERR_INVALID;
+  DGC_REQUIRE(ctx, polls >= 1 && polls <= (1u << 20), "polls must be in 1 .. 2^20");
+  selftest_expired_wait_kernel<<<1, 32, 0, ctx->stream>>>(polls, ctx->status_dev);
+  DGC_LAUNCHED(ctx, "selftest_expired_wait");
+  return DGC_OK;
+}
+
+DGC_EXPORT int32_t dgc_selftest_busy(dgc_ctx *ctx, uint32_t milliseconds) {
+  if (!ctx) return DGC_ERR_INVALID;
+  DGC_REQUIRE(ctx, milliseconds >= 1 && milliseconds <= 500, "milliseconds must be in 1 .. 500");
+  selftest_busy_kernel<<<1, 1, 0, ctx->stream>>>((unsigned long long)milliseconds * 1000ull);
+  DGC_LAUNCHED(ctx, "selftest_busy");
   return DGC_OK;
 }
 

@@ -315,6 +315,7 @@ fir_noise8_kernel(dgc_fir_params prm, const float2 *__restrict__ rowtab, const f
           d1[u] = fmaf(W[u + j0 + j], c[j], d1[u]);
         }
     };
+#pragma unroll 4
     for (int g8 = 0; g8 < NG; ++g8) {
 #pragma unroll
       for (int t = 0; t < 8; ++t) W[8 + t] = xb[t * Q + g8 + 1];

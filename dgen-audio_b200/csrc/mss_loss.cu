@@ -202,11 +202,12 @@ __device__ __forceinline__ void mss_fwd16_body(float2 *sm, float *red, int bx, i
     const int x0 = tb0 & ~3;
     const int span = (NF - 1) * hop + N + (tb0 - x0);
     const int nbox = (span + SPAN_BOX - 1) / SPAN_BOX;          // <= SPAN_BOXES whenever hop <= N
-    if (tid == 0) {
-      dgtma::mbar_expect_tx(bar, 2u * nbox * SPAN_BOX * sizeof(float));
-      for (int k = 0; k < nbox; ++k) {
-        dgtma::load_2d(span1 + k * SPAN_BOX, map_pred, x0 + k * SPAN_BOX, b, bar);
-        dgtma::load_2d(span2 + k * SPAN_BOX, map_target, x0 + k * SPAN_BOX, b, bar);
+    if (tid < 32) {   // the first warp: one lane announces the bytes, then the lanes issue one box each
+      if (tid == 0) dgtma::mbar_expect_tx(bar, 2u * nbox * SPAN_BOX * sizeof(float));
+      __syncwarp();
+      for (int k = tid; k < 2 * nbox; k += 32) {
+        const int kb = k >> 1;
+        dgtma::load_2d((k & 1 ? span2 : span1) + kb * SPAN_BOX, (k & 1) ? map_target : map_pred, x0 + kb * SPAN_BOX, b, bar);
       }
     }
     // one decision for the whole block (a wait that gave up in one thread must not leave the others at a barrier)
@@ -546,7 +547,7 @@ __device__ __forceinline__ void grad_self(float2 z, float c_lin, float c_log2, i
 }
 
 template <int N>
-__global__ void __launch_bounds__(LOSS16_THREADS, 4)
+__global__ void __launch_bounds__(LOSS16_THREADS, 3)
 mss_bwd16_kernel(const float *__restrict__ pred, const float *__restrict__ target, int B, int T, int hop, int H,
                  int S /* windows whose first-covered frames this block owns */, const float *__restrict__ window,
                  const float2 *__restrict__ tw, float c_lin, float c_log, int accumulate, float *__restrict__ grad) {
@@ -566,6 +567,7 @@ mss_bwd16_kernel(const float *__restrict__ pred, const float *__restrict__ targe
   float2 *bufa = bufa_all + f * PN, *bufb = bufb_all + f * PN;
   // d/dm of log(m + eps) in terms of the doubled magnitude m' = 2 m: 2 / (m' + 2 eps)
   const float c_log2 = 2.0f * c_log;
+  const int hop_shift = (hop & (hop - 1)) == 0 ? __ffs(hop) - 1 : -1;
   for (int o = tid; o < owned; o += LOSS16_THREADS) tile[o] = 0.0f;
   const int E = (N - 1) / hop;
   const int nwin = min(S + E, H - hA);        // windows this block must visit
@@ -639,11 +641,14 @@ mss_bwd16_kernel(const float *__restrict__ pred, const float *__restrict__ targe
     }
     __syncthreads();
     const float2 *res = bufb_all;
-    for (int o = tid; o < owned; o += LOSS16_THREADS) {
-      int p = p0 + o;
-      if (p < 0 || p >= T) continue;
-      int hlo = max(hr0, (p + hop - 1) / hop);
-      int hhi = min(min(hr0 + WR - 1, (p + N - 1) / hop), min(H - 1, hA + nwin - 1));
+    // only the owned frames this round's windows reach: [first window's start, last window's end]
+    const int h_last = min(min(hr0 + WR - 1, H - 1), hA + nwin - 1);
+    const int f_lo = max(max(p0, hr0 * hop - (N - 1)), 0), f_hi = min(min(p0 + owned - 1, h_last * hop), T - 1);
+    for (int p = f_lo + tid; p <= f_hi; p += LOSS16_THREADS) {
+      const int o = p - p0;
+      // covering windows: ceil(p / hop) .. floor((p + N - 1) / hop); a shift when the hop is a power of two
+      const int hlo = max(hr0, hop_shift >= 0 ? (p + hop - 1) >> hop_shift : (p + hop - 1) / hop);
+      const int hhi = min(h_last, hop_shift >= 0 ? (p + N - 1) >> hop_shift : (p + N - 1) / hop);
       float acc = tile[o];
       for (int h = hlo; h <= hhi; ++h) {
         int slot = h - hr0;
@@ -687,21 +692,22 @@ int32_t launch_bwd16(dgc_ctx *ctx, const dgc_mss_params *p, const float *pred, c
     if (it != ctx->mss_bwd_owned.end()) {
       S = it->second;
     } else {
+      // A block visits S + E windows in rounds of WR.  Few voices leave a grid of S0-window blocks far below the
+      // number of resident slots (160 blocks on 444 slots for 16 voices at N = 2048: 7 % of the warps active), so
+      // smaller S -- more, shorter blocks, at the price of revisiting the E overlap windows more often -- are
+      // candidates too; ties go to the larger S (less revisiting).
       long long best = -1;
-      int per_sm0 = 0;
-      for (int cand = S0; cand <= S0 + 24 && cand <= H + E; ++cand) {
+      for (int cand = 1; cand <= S0 + 24 && cand <= H + E; ++cand) {
         const size_t sm = smem_of(cand);
         if (sm > 200 * 1024) break;
         int per_sm = 0;
         if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, mss_bwd16_kernel<N>, LOSS16_THREADS, sm) != cudaSuccess ||
             per_sm < 1)
           break;
-        if (cand == S0) per_sm0 = per_sm;
-        if (per_sm < per_sm0) break;   // a larger tile must not cost resident blocks
         const long long blocks = (long long)dgc_div_up(H, cand) * p->B, slots = (long long)per_sm * ctx->sm_count;
         const long long waves = (blocks + slots - 1) / slots;
         const long long cost = waves * dgc_div_up(cand + E, Gm::WR);
-        if (best < 0 || cost < best) {
+        if (best < 0 || cost <= best) {
           best = cost;
           S = cand;
         }
@@ -887,11 +893,12 @@ int32_t dgc_mss_loss_fwd_sum(dgc_ctx *ctx, const dgc_mss_params *p, const float 
   }();
   (void)carved;
   if (fd16.nscales > 0) {
-    // The windows' sample runs are staged by tensor-map copies when the signals qualify (rows a multiple of 16
-    // bytes long and 16-byte aligned, every hop <= its window); DGC_MSS_TMA=0 keeps the per-thread loads.
+    // DGC_MSS_TMA=1: the windows' sample runs are staged by tensor-map copies when the signals qualify (rows a
+    // multiple of 16 bytes long and 16-byte aligned).  Measured slower than the per-thread loads (one window group per
+    // block leaves nothing to overlap the copy with), so the per-thread loads are the default.
     static const bool tma_on = [] {
       const char *e = getenv("DGC_MSS_TMA");
-      return !(e && strcmp(e, "0") == 0);
+      return e && strcmp(e, "1") == 0;
     }();
     CUtensorMap mp, mt;
     memset(&mp, 0, sizeof(mp));

@@ -145,6 +145,8 @@ SIGNATURES = {
     "dgc_ctx_destroy": (_i32, [_vp]),
     "dgc_last_error": (C.c_char_p, [_vp]),
     "dgc_ctx_set_stream": (_i32, [_vp, _vp, _i32]),
+    "dgc_selftest_expired_wait": (_i32, [_vp, _u32]),
+    "dgc_selftest_busy": (_i32, [_vp, _u32]),
     "dgc_sync": (_i32, [_vp, _u32]),
     "dgc_profile_begin": (_i32, [_vp]),
     "dgc_profile_end": (_i32, [_vp, C.POINTER(_f)]),

@@ -57,6 +57,14 @@ const char *dgc_last_error(dgc_ctx *ctx);
 int32_t dgc_ctx_set_stream(dgc_ctx *ctx, void *cuda_stream, int32_t external);
 /* Waits for the stream, at most timeout_ms (0 = no limit), then checks the device status word. */
 int32_t dgc_sync(dgc_ctx *ctx, uint32_t timeout_ms);
+/* Self-test of the failure reporting, without a fault and without an unbounded wait.
+ * dgc_selftest_expired_wait enqueues a kernel that waits on a barrier nothing arrives on, with the bounded wait every
+ * pipeline kernel of the library uses cut down to `polls` polls (1 .. 2^20): the wait gives up, the kernel writes
+ * the status word and returns, and the next dgc_sync reports DGC_ERR_DEVICE (and clears the word).
+ * dgc_selftest_busy keeps the stream busy for `milliseconds` (1 .. 500) so that a dgc_sync with a shorter timeout
+ * returns DGC_ERR_TIMEOUT; the stream drains by itself and later calls work.  No reference counterpart. */
+int32_t dgc_selftest_expired_wait(dgc_ctx *ctx, uint32_t polls);
+int32_t dgc_selftest_busy(dgc_ctx *ctx, uint32_t milliseconds);
 /* Event timing on the context's stream (replaces profileKernels, Sources/DGen/MetalRuntime.swift:397-425). */
 int32_t dgc_profile_begin(dgc_ctx *ctx);
 int32_t dgc_profile_end(dgc_ctx *ctx, float *elapsed_ms);

@@ -74,3 +74,31 @@ def test_gradient_exchange_is_refused_inside_a_recording():
         rec.graph.close()
     ctx.lib.dgc_comm_destroy(ctx.h)
     ctx.close()
+
+
+def test_expired_device_wait_and_sync_timeout_are_reported_and_the_context_survives():
+    """The failure branches of the bounded waits, exercised without a fault and without an unbounded wait.
+    (1) A kernel waits on a barrier that nothing arrives on, with the library's bounded wait cut down to 2000 polls:
+    it gives up, writes the status word and returns; dgc_sync reports DGC_ERR_DEVICE (-5) once, then the word is
+    clear.  (2) The stream is kept busy for 120 ms and dgc_sync is given 10 ms: DGC_ERR_TIMEOUT (-4); nothing
+    is cancelled, the stream drains by itself and the next sync succeeds.  After both, ordinary work runs."""
+    import time
+    ctx = dgen_b200.Context(0)
+    lib, h = ctx.lib, ctx.h
+    assert lib.dgc_selftest_expired_wait(h, 0) == -1                 # argument range is checked
+    assert lib.dgc_selftest_expired_wait(h, 2000) == 0
+    rc = lib.dgc_sync(h, 2000)
+    assert rc == -5 and b"status word = 201" in lib.dgc_last_error(h)
+    assert lib.dgc_sync(h, 2000) == 0                                # reported once, then clear
+    assert lib.dgc_selftest_busy(h, 120) == 0
+    t0 = time.perf_counter()
+    rc = lib.dgc_sync(h, 10)
+    waited = time.perf_counter() - t0
+    assert rc == -4 and b"still busy" in lib.dgc_last_error(h)
+    assert waited < 0.1                                              # the call came back at its own limit
+    assert lib.dgc_sync(h, 2000) == 0                                # the busy kernel ends by itself
+    x = torch.randn(2, 4096, device="cuda")
+    y = ctx.onepole_fwd(x, 0.5)
+    ctx.sync()
+    assert bool(torch.isfinite(y).all())
+    ctx.close()
