@@ -453,6 +453,15 @@ bands_to_taps_kernel(const float *__restrict__ bands, const float *__restrict__ 
   }
 }
 
+// out[r][c] = c < K ? in[r][c] : 0, rows of Kp floats (Kp a multiple of 4: 16-byte aligned rows)
+__global__ void pad_rows_kernel(const float *__restrict__ in, int64_t rows, int K, int Kp, float *__restrict__ out) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= rows * Kp) return;
+  const int64_t r = i / Kp;
+  const int c = (int)(i - r * Kp);
+  out[i] = c < K ? in[r * K + c] : 0.0f;
+}
+
 }  // namespace
 
 DGC_EXPORT int32_t dgc_fir_noise(dgc_ctx *ctx, const dgc_fir_params *p, const float *noise_dev,
@@ -529,7 +538,31 @@ DGC_EXPORT int32_t dgc_bands_to_taps(dgc_ctx *ctx, const float *bands_dev, const
   DGC_REQUIRE(ctx, bands_dev && w_dev && taps_dev, "null pointer");
   DGC_REQUIRE(ctx, rows > 0 && nbands > 0 && taps > 0, "size out of range");
   // large row counts go to the tensor-core matmul (taps = bands * W^T); the shared-memory kernel keeps small ones
-  if ((double)rows * nbands * taps >= (double)(1 << 24)) return dgc_gemm_nt(ctx, bands_dev, w_dev, rows, taps, nbands, taps_dev);
+  if ((double)rows * nbands * taps >= (double)(1 << 24)) {
+    if ((nbands & 3) == 0) return dgc_gemm_nt(ctx, bands_dev, w_dev, rows, taps, nbands, taps_dev);
+    // 65 bands: rows of 260 bytes are not 16-byte aligned, which keeps the product off the asynchronous
+    // tensor-core pipeline (its 16-byte copies) and on the slower any-orientation kernel.  Copy both operands
+    // to a row length that is a multiple of 4 floats (zero beyond nbands) first: one small pass over the bands.
+    const int Kp = (nbands + 3) & ~3;
+    const uint64_t need = ((uint64_t)rows + taps) * Kp + 8;
+    if (ctx->pad_floats < need) {
+      if (ctx->pad_buf) {
+        cudaStreamSynchronize(ctx->stream);
+        cudaFree(ctx->pad_buf);
+        ctx->buffer_generation++;
+        ctx->pad_buf = nullptr;
+        ctx->pad_floats = 0;
+      }
+      DGC_CUDA(ctx, cudaMalloc(&ctx->pad_buf, need * sizeof(float)));
+      ctx->pad_floats = need;
+    }
+    float *bp = ctx->pad_buf, *wp = bp + (((uint64_t)rows * Kp + 3) & ~3ull);
+    pad_rows_kernel<<<dgc_div_up((int64_t)rows * Kp, 256), 256, 0, ctx->stream>>>(bands_dev, rows, nbands, Kp, bp);
+    DGC_LAUNCHED(ctx, "pad_bands");
+    pad_rows_kernel<<<dgc_div_up((int64_t)taps * Kp, 256), 256, 0, ctx->stream>>>(w_dev, taps, nbands, Kp, wp);
+    DGC_LAUNCHED(ctx, "pad_w");
+    return dgc_gemm_nt(ctx, bp, wp, rows, taps, Kp, taps_dev);
+  }
   size_t smem = ((((size_t)taps * (nbands | 1) + 3) & ~(size_t)3) + (size_t)nbands * 16) * sizeof(float);
   DGC_REQUIRE(ctx, smem <= 200 * 1024, "taps*nbands too large for shared memory");
   DGC_CUDA(ctx, cudaFuncSetAttribute(bands_to_taps_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));

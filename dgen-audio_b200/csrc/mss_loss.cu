@@ -704,7 +704,7 @@ int32_t launch_bwd16(dgc_ctx *ctx, const dgc_mss_params *p, const float *pred, c
         if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, mss_bwd16_kernel<N>, LOSS16_THREADS, sm) != cudaSuccess ||
             per_sm < 1)
           break;
-        const long long blocks = (long long)dgc_div_up(H, cand) * p->B, slots = (long long)per_sm * ctx->sm_count;
+        const long long blocks = (long long)dgc_div_up(H + 1, cand) * p->B, slots = (long long)per_sm * ctx->sm_count;
         const long long waves = (blocks + slots - 1) / slots;
         const long long cost = waves * dgc_div_up(cand + E, Gm::WR);
         if (best < 0 || cost <= best) {
@@ -716,7 +716,10 @@ int32_t launch_bwd16(dgc_ctx *ctx, const dgc_mss_params *p, const float *pred, c
     }
   }
   const size_t smem = smem_of(S);
-  mss_bwd16_kernel<N><<<dim3(dgc_div_up(H, S), p->B), LOSS16_THREADS, smem, ctx->stream>>>(
+  // block j owns the frames whose first covering window is in [j S, (j+1) S).  The frames behind the last window
+  // ((H-1) hop, T-1] are covered by no window at all -- their "first covering window" would be number H -- and must
+  // still be written (zero, or left as accumulated): the grid spans window indices 0 .. H.
+  mss_bwd16_kernel<N><<<dim3(dgc_div_up(H + 1, S), p->B), LOSS16_THREADS, smem, ctx->stream>>>(
       pred, target, p->B, p->T, hop, H, S, win, tw, c_lin, c_log, accumulate, grad);
   ctx->launches++;
   return dgc_check_launch(ctx, "mss_bwd16");
@@ -765,7 +768,7 @@ int32_t launch_bwd(dgc_ctx *ctx, const dgc_mss_params *p, const float *pred, con
           break;
         if (cand == S0) per_sm0 = per_sm;
         if (per_sm < per_sm0) break;   // a larger tile must not cost resident blocks
-        const long long blocks = (long long)dgc_div_up(H, cand) * p->B, slots = (long long)per_sm * ctx->sm_count;
+        const long long blocks = (long long)dgc_div_up(H + 1, cand) * p->B, slots = (long long)per_sm * ctx->sm_count;
         const long long waves = (blocks + slots - 1) / slots;
         const long long cost = waves * dgc_div_up(cand + E, Gm::WR);
         if (best < 0 || cost < best) {
@@ -779,7 +782,7 @@ int32_t launch_bwd(dgc_ctx *ctx, const dgc_mss_params *p, const float *pred, con
   const size_t smem = smem_of(S);
   // block j owns the frames whose first covering window is in [j*S, (j+1)*S); frames up to T-1 have
   // first covering window <= H-1
-  mss_bwd_kernel<N><<<dim3(dgc_div_up(H, S), p->B), LOSS_THREADS, smem, ctx->stream>>>(
+  mss_bwd_kernel<N><<<dim3(dgc_div_up(H + 1, S), p->B), LOSS_THREADS, smem, ctx->stream>>>(
       pred, target, p->B, p->T, hop, H, S, win, tw, c_lin, c_log, accumulate, grad);
   ctx->launches++;
   return dgc_check_launch(ctx, "mss_bwd");

@@ -287,13 +287,29 @@ __device__ __forceinline__ unsigned long long inc_q64(float f0v, float sr, float
   return __float2ull_rn(qh * 18446744073709551616.0f) + (unsigned long long)__float2ll_rn(ql * 18446744073709551616.0f);
 }
 
+// How many partials k = 1, 2, .. pass the Nyquist mask fl(k f0) < nyq of the reference (Examples/HarmonicE2E/
+// Synth.swift:161-170): the products are monotone in k for f0 >= 0, so the passing partials are a prefix 1 .. kcut
+// and one count per frame replaces a multiply and a compare per partial and frame.  Decided on the reference's own
+// single-precision product, so a partial exactly at Nyquist flips exactly where the reference flips it.
+__device__ __forceinline__ int nyquist_count(float f0v, float nyq, int K) {
+  if (!(f0v == f0v)) return 0;            // NaN: every comparison is false
+  if (!(f0v > 0.0f)) return K;            // zero or negative: every product is <= 0 < nyq
+  const float r = nyq / f0v;
+  if (!(r < (float)(K + 2))) return K;
+  int k = (int)r + 1;
+  if (k > K) k = K;
+  while (k > 0 && !(__fmul_rn((float)k, f0v) < nyq)) --k;
+  return k;
+}
+
 // One warp per (voice, chunk of 64 frames): the per-sample fundamental and output envelope of f0_track_kernel plus
-// the chunk's total phase advance of the fundamental.
+// the chunk's total phase advance of the fundamental, and per frame the pair (phase increment of the fundamental in
+// Q0.32, number of partials below Nyquist) the render kernel reads instead of deriving both in every lane.
 __global__ void __launch_bounds__(128)
-f0_track_fund_kernel(const float2 *__restrict__ rowtab, const float *__restrict__ f0, int B, int T, int F, float sr,
+f0_track_fund_kernel(const float2 *__restrict__ rowtab, const float *__restrict__ f0, int B, int T, int F, int K, float sr,
                      float rsr, float *__restrict__ f0t, const float *__restrict__ uv,
                      const float *__restrict__ gain, float scale, float *__restrict__ env,
-                     unsigned long long *__restrict__ chunk_sum /* [B][C] */) {
+                     unsigned long long *__restrict__ chunk_sum /* [B][C] */, int2 *__restrict__ trk /* [B][T] */) {
   const int C = (T + CH - 1) / CH;
   const int c = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31, b = blockIdx.y;
   if (c >= C) return;
@@ -312,7 +328,9 @@ f0_track_fund_kernel(const float2 *__restrict__ rowtab, const float *__restrict_
         const float uvt = fmaf(fr, uv[(size_t)hi * B + b], omf * uv[(size_t)lo * B + b]);
         env[(size_t)b * T + n] = gt * uvt * scale;
       }
-      tot += inc_q64(f0v, sr, rsr);
+      const unsigned long long d64 = inc_q64(f0v, sr, rsr);
+      tot += d64;
+      if (trk) trk[(size_t)b * T + n] = make_int2((int)(uint32_t)((d64 + 0x80000000ull) >> 32), nyquist_count(f0v, sr * 0.5f, K));
     }
   }
 #pragma unroll
@@ -495,14 +513,15 @@ __device__ __forceinline__ uint32_t inc_q32(float f0v, float sr, float rsr) {
 // MODE 0 renders audio.  MODE 1 writes, per frame, the phase gradient folded over the partials,
 // sum_k k * dL/dphi_k[m] with dL/dphi_k = g_audio * env * a_k / (sum a + eps) * 2 pi cos(2 pi phi_k): the
 // input of the temporal scan that gives dL/df0 (the same walk over the phases, cosine instead of sine).
-template <int LPC, int P, int MODE>
+template <int LPC, int P, int MODE, bool TRK>
 __global__ void __launch_bounds__(128, 5)
 harmonic_render_q_kernel(dgc_harmonic_params prm, float rsr, const float2 *__restrict__ rowtab,
                          const float *__restrict__ f0t, const float *__restrict__ env,
                          const float *__restrict__ amps, const uint32_t *__restrict__ anchors_q,
-                         const unsigned long long *__restrict__ fund, const float *__restrict__ g_audio,
-                         float *__restrict__ audio) {
+                         const unsigned long long *__restrict__ fund, const int2 *__restrict__ trk,
+                         const float *__restrict__ g_audio, float *__restrict__ audio) {
   constexpr int G = 128 / LPC, FB = 8;
+  constexpr int LOG_LPC = LPC == 8 ? 3 : LPC == 16 ? 4 : 5;
   constexpr float THREE_PI = 9.42477796076938f;
   const int B = prm.B, T = prm.T, K = prm.K, F = prm.F;
   const int C = (T + CH - 1) / CH;
@@ -551,25 +570,47 @@ harmonic_render_q_kernel(dgc_harmonic_params prm, float rsr, const float2 *__res
           dl[i] = k < K ? rh[k] - alo[i] : 0.0f;
         }
       }
-      const float f0v = f0p[n];
-      const uint32_t dq = inc_q32(f0v, sr, rsr);
-      uint32_t incv = (uint32_t)(j + 1) * dq;
-      const uint32_t step = (uint32_t)LPC * dq;
       float s1 = 0.0f, s2 = 0.0f;
+      if (TRK) {
+        // the fundamental's increment and the number of partials below Nyquist come per frame from the track
+        // kernel: per partial and frame only the amplitude lerp, the phase-to-angle map, the sine and two adds
+        const int2 tk = trk[(size_t)b * T + n];
+        const uint32_t dq = (uint32_t)tk.x;
+        uint32_t incv = (uint32_t)(j + 1) * dq;
+        const uint32_t step = (uint32_t)LPC * dq;
+        const int ilim = max(tk.y - j + LPC - 1, 0) >> LOG_LPC;   // partial j + LPC i + 1 <= count  <=>  i < ilim
 #pragma unroll
-      for (int i = 0; i < P; ++i) {
-        const float kf = partial_number(kf0, LPC * i);
-        const float freq = __fmul_rn(kf, f0v);
-        const float a = fmaf(fr, dl[i], alo[i]);
-        const float ph1 = __uint_as_float(__funnelshift_r(q[i], 0x7Fu, 9));  // 1 + phase
-        const float xr = fmaf(ph1, TWO_PI_F, -THREE_PI);
-        if (freq < nyq) {  // Nyquist mask on the reference's single-precision product
-          s2 += a;
-          if (MODE == 0) s1 = fmaf(__sinf(xr), a, s1);
-          else s1 = fmaf(__cosf(xr), kf * a, s1);
+        for (int i = 0; i < P; ++i) {
+          const float a = fmaf(fr, dl[i], alo[i]);
+          const float ph1 = __uint_as_float(__funnelshift_r(q[i], 0x7Fu, 9));  // 1 + phase
+          const float xr = fmaf(ph1, TWO_PI_F, -THREE_PI);
+          if (i < ilim) {
+            s2 += a;
+            s1 = fmaf(__sinf(xr), a, s1);
+          }
+          q[i] += incv;
+          incv += step;
         }
-        q[i] += incv;
-        incv += step;
+      } else {
+        const float f0v = f0p[n];
+        const uint32_t dq = inc_q32(f0v, sr, rsr);
+        uint32_t incv = (uint32_t)(j + 1) * dq;
+        const uint32_t step = (uint32_t)LPC * dq;
+#pragma unroll
+        for (int i = 0; i < P; ++i) {
+          const float kf = partial_number(kf0, LPC * i);
+          const float freq = __fmul_rn(kf, f0v);
+          const float a = fmaf(fr, dl[i], alo[i]);
+          const float ph1 = __uint_as_float(__funnelshift_r(q[i], 0x7Fu, 9));  // 1 + phase
+          const float xr = fmaf(ph1, TWO_PI_F, -THREE_PI);
+          if (freq < nyq) {  // Nyquist mask on the reference's single-precision product
+            s2 += a;
+            if (MODE == 0) s1 = fmaf(__sinf(xr), a, s1);
+            else s1 = fmaf(__cosf(xr), kf * a, s1);
+          }
+          q[i] += incv;
+          incv += step;
+        }
       }
       S1[u] = s1;
       S2[u] = s2;
@@ -657,8 +698,13 @@ void launch_render_q(dgc_ctx *ctx, const dgc_harmonic_params &p, const float2 *r
   int C = (p.T + CH - 1) / CH;
   constexpr int G = 128 / LPC;
   dim3 grid(dgc_div_up(C, G), p.B);
-  harmonic_render_q_kernel<LPC, P, MODE><<<grid, 128, 0, ctx->stream>>>(p, 1.0f / p.sample_rate, rowtab, x.f0t, x.env,
-                                                                         amps, x.anchors_q, x.fund, g_audio, out);
+  if (MODE == 0 && x.trk)
+    harmonic_render_q_kernel<LPC, P, 0, true><<<grid, 128, 0, ctx->stream>>>(p, 1.0f / p.sample_rate, rowtab, x.f0t, x.env,
+                                                                              amps, x.anchors_q, x.fund, x.trk, g_audio, out);
+  else
+    harmonic_render_q_kernel<LPC, P, MODE, false><<<grid, 128, 0, ctx->stream>>>(p, 1.0f / p.sample_rate, rowtab, x.f0t,
+                                                                                  x.env, amps, x.anchors_q, x.fund, x.trk,
+                                                                                  g_audio, out);
 }
 
 // The reverse scan of the reference's temporalGradScan (Sources/DGen/Emit+TemporalGradient.swift:54-88), per row e
@@ -829,7 +875,9 @@ DGC_EXPORT uint64_t dgc_harmonic_scratch_floats(const dgc_harmonic_params *p) {
   // f0 track [B][T] (rounded up to 4), anchors [B][C][K], chunk sums as 64-bit words (at least the 2 x [B][C]
   // words of the FUNDAMENTAL mode), output envelope [B][T], anchors as Q0.32 words
   const uint64_t sum_words = lanes > 2 * (uint64_t)p->B * C ? lanes : 2 * (uint64_t)p->B * C;
-  return 2 * (((uint64_t)p->B * p->T + 3) & ~3ull) + lanes + 2 * sum_words + lanes + 16;
+  // (+ the per-frame (increment, Nyquist count) pairs of the FUNDAMENTAL mode, [B][T] int2)
+  return 2 * (((uint64_t)p->B * p->T + 3) & ~3ull) + lanes + 2 * sum_words + lanes + 16 +
+         2 * (((uint64_t)p->B * p->T + 3) & ~3ull);
 }
 
 int32_t dgc_harmonic_prepare(dgc_ctx *ctx, const dgc_harmonic_params *p, const float *f0_dev, float *scratch,
@@ -853,6 +901,7 @@ int32_t dgc_harmonic_prepare(dgc_ctx *ctx, const dgc_harmonic_params *p, const f
   const uint64_t sum_words = lanes > 2 * (uint64_t)B * C ? lanes : 2 * (uint64_t)B * C;
   float *env = reinterpret_cast<float *>(sums + sum_words);
   uint32_t *anchors_q = reinterpret_cast<uint32_t *>(env + (((uint64_t)B * T + 3) & ~3ull));
+  int2 *trk = reinterpret_cast<int2 *>(anchors_q + ((lanes + 3) & ~3ull));   // 8-byte aligned: every part before it is a multiple of 4 floats from a 16-byte aligned base
   const bool want_env = uv_dev && gain_dev && extra;
   const float2 *rowtab = dgc_ctx_row_table(ctx, F, T);
   if (!rowtab) return DGC_ERR_CUDA;
@@ -862,9 +911,9 @@ int32_t dgc_harmonic_prepare(dgc_ctx *ctx, const dgc_harmonic_params *p, const f
   if (already_prepared) {
     // nothing to launch
   } else if (p->phase_mode == DGC_PHASE_FUNDAMENTAL) {
-    f0_track_fund_kernel<<<dim3(dgc_div_up(C, 4), B), 128, 0, ctx->stream>>>(rowtab, f0_dev, B, T, F, sr, rsr, f0t, uv_dev,
+    f0_track_fund_kernel<<<dim3(dgc_div_up(C, 4), B), 128, 0, ctx->stream>>>(rowtab, f0_dev, B, T, F, K, sr, rsr, f0t, uv_dev,
                                                                           gain_dev, p->harmonic_scale,
-                                                                          want_env ? env : nullptr, fund_sum);
+                                                                          want_env ? env : nullptr, fund_sum, trk);
     DGC_LAUNCHED(ctx, "f0_track_fund");
     fund_scan_kernel<<<B, FSCAN_THREADS, 0, ctx->stream>>>(fund_sum, C, fund_prefix);
     DGC_LAUNCHED(ctx, "fund_scan");
@@ -888,6 +937,7 @@ int32_t dgc_harmonic_prepare(dgc_ctx *ctx, const dgc_harmonic_params *p, const f
     extra->env = want_env ? env : nullptr;
     extra->anchors_q = p->phase_mode == DGC_PHASE_SCAN ? anchors_q : nullptr;
     extra->fund = p->phase_mode == DGC_PHASE_FUNDAMENTAL ? fund_prefix : nullptr;
+    extra->trk = p->phase_mode == DGC_PHASE_FUNDAMENTAL ? trk : nullptr;
   }
   *play_out = play;
   *anchors_out = anchors;

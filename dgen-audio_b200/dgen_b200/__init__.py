@@ -541,10 +541,10 @@ class Context:
         return (loss, part) if want_partial else loss
 
     def mss_loss_bwd(self, pred, target, sizes=(2048, 1024, 512, 256, 128, 64), hop_div=4, w_lin=1.0, w_log=1.0,
-                     upstream=1.0):
+                     upstream=1.0, out=None):
         B, T = pred.shape
         p = mss_params(B, T, sizes, hop_div, w_lin, w_log)
-        grad = self._empty(B, T)
+        grad = self._empty(B, T) if out is None else out
         self.check(self.lib.dgc_mss_loss_bwd(self.h, C.byref(p), _ptr(pred), _ptr(target), upstream, _ptr(grad)))
         return grad
 

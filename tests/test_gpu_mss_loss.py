@@ -111,3 +111,25 @@ def test_backward_is_bit_deterministic(ctx):
     a = ctx.mss_loss_bwd(x, y).cpu().numpy()
     b = ctx.mss_loss_bwd(x, y).cpu().numpy()
     assert a.tobytes() == b.tobytes()
+
+
+def test_backward_writes_every_frame_whatever_the_length(ctx):
+    """The frames behind the last hop window are covered by no window; they must still be written (zero).  Lengths
+    around multiples of the hop and of the blocks' window counts, into a gradient buffer pre-filled with NaN."""
+    import torch
+    rng = np.random.default_rng(3)
+    for sizes, lengths in (((64,), range(1000, 1034)), ((2048, 256), (8192, 8193, 8703, 8704, 8705, 9215, 9216, 9217))):
+        for T in lengths:
+            x = rng.standard_normal((2, T)).astype(f32)
+            y = rng.standard_normal((2, T)).astype(f32)
+            g = torch.full((2, T), float("nan"), device="cuda")
+            ctx.mss_loss_bwd(dev(x), dev(y), sizes=sizes, out=g)
+            got = g.cpu().numpy()
+            assert np.isfinite(got).all(), (sizes, T, int(np.argmax(~np.isfinite(got[0]))))
+            want = orc.mss_loss_grad(x, y, sizes)
+            err = np.abs(got - want)
+            assert np.quantile(err, 0.99) < 1e-3 * np.abs(want).max() and err.max() < 2e-2 * np.abs(want).max(), (sizes, T)
+            hop = min(sizes) // 4
+            tail = ((T - 1) // hop) * hop + 1           # first frame behind the last window of the smallest scale
+            if len(sizes) == 1 and tail < T:
+                assert np.all(got[:, tail:] == 0.0)
