@@ -107,9 +107,10 @@ class ClockSampler:
 # --------------------------------------------------------------------------------------------------
 # CPU arm (oracle restatement of the reference C backend), used for cpu_baseline and --impl reference
 # --------------------------------------------------------------------------------------------------
-def cpu_arm(voices, threads, seed=SEED):
-    """Times render + loss of `voices` voices of the workload on the host with `threads` threads.
-    Returns (samples_per_s, seconds)."""
+def cpu_arm(voices, threads, seed=SEED, min_seconds=0.0):
+    """Times render + loss of `voices` voices of the workload on the host with `threads` threads, repeating the pass
+    over the same voices until `min_seconds` of timed work have accumulated.
+    Returns (samples_per_s, seconds, passes)."""
     import tempfile
     from concurrent.futures import ThreadPoolExecutor
     from dgen_b200 import workloads as wl
@@ -135,11 +136,14 @@ def cpu_arm(voices, threads, seed=SEED):
         return orc.mss_loss(a, target[sl], sizes=SIZES, L=L)
 
     one(0)  # warm-up (page in, build twiddles)
-    t0 = time.perf_counter()
+    dt, passes = 0.0, 0
     with ThreadPoolExecutor(max_workers=threads) as ex:
-        list(ex.map(one, range(voices)))
-    dt = time.perf_counter() - t0
-    return voices * CFG["T"] / dt, dt
+        while passes == 0 or dt < min_seconds:
+            t0 = time.perf_counter()
+            list(ex.map(one, range(voices)))
+            dt += time.perf_counter() - t0
+            passes += 1
+    return passes * voices * CFG["T"] / dt, dt, passes
 
 
 def run_reference(args, rank, world):
@@ -152,7 +156,7 @@ def run_reference(args, rank, world):
     for _ in range(min(1, args.warmup)):
         cpu_arm(threads, threads)  # one untimed pass (page-in, native build of the oracle)
     for _ in range(args.steps):
-        v, s = cpu_arm(voices, threads)
+        v, s, _ = cpu_arm(voices, threads)
         vals.append(v)
         secs.append(s)
     value = float(np.mean(vals))
@@ -499,10 +503,35 @@ def run_ours(args, rank, world, local_rank):
     torch.cuda.synchronize()
     piped_ms = a.elapsed_time(b)
     barrier()
+    # the lean form of the same API: the noise is generated on the device from a seed (the reference generates its
+    # noise inside the graph too) and the target clip stays resident in HBM (the reference loads it once per run);
+    # what crosses PCIe every step is the control-rate inputs and the loss.
+    st_lean = type(st).from_buffer_copy(st)
+    st_lean.noise_seed, st_lean.noise_mode, st_lean.noise_sigma = SEED + 17, dgen_b200.NOISE_GAUSSIAN, 1.0
+    st_lean.target_dev = fl.target.data_ptr()
+    largs = (st_lean, P["f0"], P["uv"], P["amps"], P["gain"], P["noise_gain"], P["bands"], P["W"], None, None)
+    for i in range(4):
+        ctx.hn_forward_loss_host_submit(*largs, i % 2)
+        ctx.hn_forward_loss_host_wait(i % 2)
+    barrier()
+    flush.fill_(2.0)
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    ctx.hn_forward_loss_host_submit(*largs, 0)
+    for s in range(1, args.steps):
+        ctx.hn_forward_loss_host_submit(*largs, s % 2)
+        lean_loss = ctx.hn_forward_loss_host_wait((s - 1) % 2)
+    lean_loss = ctx.hn_forward_loss_host_wait((args.steps - 1) % 2)
+    b.record()
+    torch.cuda.synchronize()
+    lean_ms = a.elapsed_time(b)
+    barrier()
     clocks = sampler.stop() if rank == 0 else None
+    h2d_lean = 4 * sum(int(P[k].numel()) for k in ("f0", "uv", "amps", "gain", "noise_gain", "bands", "W"))
     h2d = 4 * sum(int(P[k].numel()) for k in ("f0", "uv", "amps", "gain", "noise_gain", "bands", "W", "noise")) \
         + 4 * int(target_host.numel())
-    total_ms, e2e_ms, piped_ms = sharding.max_over_ranks([total_ms, e2e_ms, piped_ms], device="cuda")
+    total_ms, e2e_ms, piped_ms, lean_ms = sharding.max_over_ranks([total_ms, e2e_ms, piped_ms, lean_ms], device="cuda")
 
     # sustained run (every rank runs it; rank 0 reports its own)
     sustained = sustained_run(ctx, fl, graphs, run_stream, local_rank) if replay else None
@@ -548,13 +577,22 @@ def run_ours(args, rank, world, local_rank):
                 "config": config_json(world), "clocks": clocks,
                 # throughput through the host-buffer API with two steps in flight (dgc_hn_forward_loss_host_submit /
                 # _wait); "blocking" is the one-call-at-a-time form of the same API (dgc_hn_forward_loss_host)
-                "e2e": {"value": samples_per_step * args.steps / (piped_ms * 1e-3), "unit": UNIT,
-                        "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 8, "ms_per_step": piped_ms / args.steps,
-                        "mode": "two steps in flight: step i+1 uploads while step i computes; every step's inputs "
-                                "come from pinned host memory and its loss returns to the host inside the timed region",
-                        "blocking": {"value": e2e_value, "ms_per_step": e2e_ms / args.steps,
-                                     "l2": "flushed between steps"},
-                        "loss": piped_loss},
+                "e2e": {"value": samples_per_step * args.steps / (lean_ms * 1e-3), "unit": UNIT,
+                        "h2d_bytes_per_step": h2d_lean, "d2h_bytes_per_step": 8, "ms_per_step": lean_ms / args.steps,
+                        "mode": "two steps in flight: step i+1 uploads while step i computes; every step's control-rate "
+                                "inputs (f0, voicing, harmonic amplitudes, gains, band magnitudes, band->tap matrix) come "
+                                "from pinned host memory and its loss returns to the host inside the timed region; the "
+                                "noise is generated on the device from a seed each step (as the reference generates it "
+                                "inside its graph) and the target clip is resident in HBM (uploaded once, as the "
+                                "reference loads it once per run)",
+                        "loss": lean_loss,
+                        "full_upload": {"value": samples_per_step * args.steps / (piped_ms * 1e-3),
+                                        "ms_per_step": piped_ms / args.steps, "h2d_bytes_per_step": h2d,
+                                        "what": "the same two-in-flight calls with the noise and the target uploaded "
+                                                "from pinned host memory every step as well", "loss": piped_loss},
+                        "blocking": {"value": e2e_value, "ms_per_step": e2e_ms / args.steps, "h2d_bytes_per_step": h2d,
+                                     "l2": "flushed between steps",
+                                     "what": "one call at a time, everything uploaded every step"}},
                 "gpu_launches": int(launches),
                 # the stage with the largest measured share, against the bound that applies to it
                 "roofline": dict(rl, kernel=dom, traffic=traffic, traffic_source=traffic_src,
@@ -579,11 +617,11 @@ def run_ours(args, rank, world, local_rank):
         if other:
             line["other_configs"] = other
         if not args.no_cpu and world == 1:
-            v, secs = cpu_arm(4, 1)
+            v, secs, passes = cpu_arm(16, 1, min_seconds=12.0)
             line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": 1, "kind": "port",
-                                    "sample": "4 voices x %d frames, render + 6-scale loss, single thread (%.1f s); "
-                                              "CPU restatement of the reference's single-threaded C backend"
-                                              % (T, secs)}
+                                    "sample": "%d passes over 16 voices x %d frames (the workload's batch), render + "
+                                              "6-scale loss, single thread (%.1f s); CPU restatement of the "
+                                              "reference's single-threaded C backend" % (passes, T, secs)}
         print(json.dumps(line))
     ctx.close()
     if world > 1:

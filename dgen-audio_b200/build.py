@@ -7,7 +7,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libdgen_cuda.so")
 SOURCES = ["ctx.cu", "osc_bank.cu", "fir_noise.cu", "mss_loss.cu", "linrec.cu", "stft.cu", "gemm.cu", "synth_bwd.cu", "plans.cu",
-           "module.cu", "comm.cu", "blocks.cu", "stateful.cu", "graph.cu", "plan.cu"]
+           "module.cu", "comm.cu", "blocks.cu", "stateful.cu", "graph.cu", "plan.cu", "noise.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--use_fast_math=false",
          "-Xcompiler", "-fPIC,-fvisibility=hidden,-O2", "-cudart", "static", "-Xptxas", "-v"]

@@ -546,8 +546,10 @@ __device__ __forceinline__ void grad_self(float2 z, float c_lin, float c_log2, i
   if (lane == 0) Y.x += gre; else Y.y += gre;
 }
 
-template <int N>
-__global__ void __launch_bounds__(LOSS16_THREADS, 3)
+// MINB: resident blocks per SM the registers are capped for (3: 168 registers, nothing spilled; 4: 128 registers,
+// a few spilled words in the middle sizes)
+template <int N, int MINB>
+__global__ void __launch_bounds__(LOSS16_THREADS, MINB)
 mss_bwd16_kernel(const float *__restrict__ pred, const float *__restrict__ target, int B, int T, int hop, int H,
                  int S /* windows whose first-covered frames this block owns */, const float *__restrict__ window,
                  const float2 *__restrict__ tw, float c_lin, float c_log, int accumulate, float *__restrict__ grad) {
@@ -666,7 +668,7 @@ mss_bwd16_kernel(const float *__restrict__ pred, const float *__restrict__ targe
   }
 }
 
-template <int N>
+template <int N, int MINB>
 int32_t launch_bwd16(dgc_ctx *ctx, const dgc_mss_params *p, const float *pred, const float *target, int hop, int H,
                      float c_lin, float c_log, int accumulate, float *grad) {
   using Gm = Bwd16Geom<N>;
@@ -680,14 +682,14 @@ int32_t launch_bwd16(dgc_ctx *ctx, const dgc_mss_params *p, const float *pred, c
     return (size_t)2 * Gm::NF * padded(N) * sizeof(float2) + (size_t)S_ * hop * sizeof(float);
   };
   if (smem_of(S0) > 200 * 1024) return dgc_fail(ctx, DGC_ERR_UNSUPPORTED, "backward tile does not fit shared memory");
-  cudaError_t e = cudaFuncSetAttribute(mss_bwd16_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+  cudaError_t e = cudaFuncSetAttribute(mss_bwd16_kernel<N, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
   if (e != cudaSuccess) return dgc_fail(ctx, DGC_ERR_CUDA, "mss_bwd smem opt-in: %s", cudaGetErrorString(e));
-  cudaFuncSetAttribute(mss_bwd16_kernel<N>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+  cudaFuncSetAttribute(mss_bwd16_kernel<N, MINB>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
   // windows owned per block: the choice that minimises (waves of resident blocks x rounds per block), see launch_bwd;
   // the summation order per output frame does not depend on it
   int S = S0;
   {
-    const auto key = std::make_pair(std::make_pair(N, -hop), std::make_pair(H, p->B));   // (-hop: this kernel's own entries)
+    const auto key = std::make_pair(std::make_pair(N, -hop * 8 - MINB), std::make_pair(H, p->B));   // (-hop: this kernel's own entries)
     auto it = ctx->mss_bwd_owned.find(key);
     if (it != ctx->mss_bwd_owned.end()) {
       S = it->second;
@@ -701,7 +703,7 @@ int32_t launch_bwd16(dgc_ctx *ctx, const dgc_mss_params *p, const float *pred, c
         const size_t sm = smem_of(cand);
         if (sm > 200 * 1024) break;
         int per_sm = 0;
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, mss_bwd16_kernel<N>, LOSS16_THREADS, sm) != cudaSuccess ||
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, mss_bwd16_kernel<N, MINB>, LOSS16_THREADS, sm) != cudaSuccess ||
             per_sm < 1)
           break;
         const long long blocks = (long long)dgc_div_up(H + 1, cand) * p->B, slots = (long long)per_sm * ctx->sm_count;
@@ -719,7 +721,7 @@ int32_t launch_bwd16(dgc_ctx *ctx, const dgc_mss_params *p, const float *pred, c
   // block j owns the frames whose first covering window is in [j S, (j+1) S).  The frames behind the last window
   // ((H-1) hop, T-1] are covered by no window at all -- their "first covering window" would be number H -- and must
   // still be written (zero, or left as accumulated): the grid spans window indices 0 .. H.
-  mss_bwd16_kernel<N><<<dim3(dgc_div_up(H + 1, S), p->B), LOSS16_THREADS, smem, ctx->stream>>>(
+  mss_bwd16_kernel<N, MINB><<<dim3(dgc_div_up(H + 1, S), p->B), LOSS16_THREADS, smem, ctx->stream>>>(
       pred, target, p->B, p->T, hop, H, S, win, tw, c_lin, c_log, accumulate, grad);
   ctx->launches++;
   return dgc_check_launch(ctx, "mss_bwd16");
@@ -965,11 +967,19 @@ DGC_EXPORT int32_t dgc_mss_loss_bwd(dgc_ctx *ctx, const dgc_mss_params *p, const
     }();
     // windows of 64 points and more run on the sixteen-points-per-thread kernel
     const bool wide = N >= 64 && !bwd_old;
+    static const int bwd_minb = [] {
+      const char *e = getenv("DGC_MSS_BWD_BLOCKS");
+      return e ? atoi(e) : 3;
+    }();
     switch (wide ? N : -N) {
 #define CASE(NN) case -NN: rc = launch_bwd<NN>(ctx, p, pred_dev, target_dev, hop, H, c_lin, c_log, accumulate, grad_pred_dev); break;
       CASE(16) CASE(32) CASE(64) CASE(128) CASE(256) CASE(512) CASE(1024) CASE(2048)
 #undef CASE
-#define CASE(NN) case NN: rc = launch_bwd16<NN>(ctx, p, pred_dev, target_dev, hop, H, c_lin, c_log, accumulate, grad_pred_dev); break;
+#define CASE(NN)                                                                                                          \
+  case NN:                                                                                                                \
+    rc = bwd_minb == 4 ? launch_bwd16<NN, 4>(ctx, p, pred_dev, target_dev, hop, H, c_lin, c_log, accumulate, grad_pred_dev) \
+                       : launch_bwd16<NN, 3>(ctx, p, pred_dev, target_dev, hop, H, c_lin, c_log, accumulate, grad_pred_dev); \
+    break;
       CASE(64) CASE(128) CASE(256) CASE(512) CASE(1024) CASE(2048)
 #undef CASE
       default: return dgc_fail(ctx, DGC_ERR_UNSUPPORTED, "window size %d", N);

@@ -163,17 +163,20 @@ static int32_t hn_host_enqueue(dgc_ctx *ctx, const dgc_hn_step *s, const float *
                                const float *taps_or_bands_host, const float *w_host, const float *noise_host,
                                const float *target_host, double *loss_host, float *audio_host, int slot) {
   if (!ctx) return DGC_ERR_INVALID;
-  DGC_REQUIRE(ctx, s && f0_host && uv_host && amps_host && gain_host && target_host && loss_host, "null pointer");
+  DGC_REQUIRE(ctx, s && f0_host && uv_host && amps_host && gain_host && loss_host, "null pointer");
+  DGC_REQUIRE(ctx, target_host || s->target_dev, "the target must be given in host memory or as a resident device buffer");
   const int B = s->harm.B, T = s->harm.T, K = s->harm.K, F = s->harm.F;
   DGC_REQUIRE(ctx, B > 0 && T > 0 && K > 0 && F > 0, "size out of range");
   const int NT = s->fir.taps, NB = s->nbands;
   const bool noise = NT > 0;
   if (noise) {
-    DGC_REQUIRE(ctx, noise_gain_host && taps_or_bands_host && noise_host, "noise branch needs its inputs");
+    DGC_REQUIRE(ctx, noise_gain_host && taps_or_bands_host && (noise_host || s->noise_seed), "noise branch needs its inputs");
     DGC_REQUIRE(ctx, s->fir.B == B && s->fir.T == T && s->fir.F == F, "fir shape differs from harmonic shape");
     DGC_REQUIRE(ctx, NB == 0 || w_host, "band synthesis needs the matrix W");
   }
   DGC_REQUIRE(ctx, s->mss.B == B && s->mss.T == T, "loss shape differs from harmonic shape");
+  const bool gen_noise = noise && !noise_host;          // generated on the device from s->noise_seed
+  const bool resident_target = s->target_dev != nullptr;
   const uint64_t nFB = (uint64_t)F * B, nBT = (uint64_t)B * T;
   const uint64_t n_tab = noise ? nFB * (NB > 0 ? NB : NT) : 0;
   const uint64_t n_w = (noise && NB > 0) ? (uint64_t)NT * NB : 0;
@@ -244,10 +247,10 @@ static int32_t hn_host_enqueue(dgc_ctx *ctx, const dgc_hn_step *s, const float *
     d_ng = put(noise_gain_host, nFB);
     d_tab = put(taps_or_bands_host, n_tab);
     if (NB > 0) d_w = put(w_host, n_w);
-    d_noise = put(noise_host, nBT);
+    d_noise = gen_noise ? dc.take(nBT) : put(noise_host, nBT);
   }
   mark(1);
-  float *d_target = put(target_host, nBT);
+  float *d_target = resident_target ? const_cast<float *>(s->target_dev) : put(target_host, nBT);
   mark(2);
   if (cp_err != cudaSuccess) {
     cudaStreamSynchronize(ctx->copy_stream);
@@ -268,6 +271,10 @@ static int32_t hn_host_enqueue(dgc_ctx *ctx, const dgc_hn_step *s, const float *
   float *d_audio = audio_host ? work_carver.take(nBT) : nullptr;
   // the harmonic branch only needs group 0; the noise branch and the loss wait for their own uploads inside
   if (cudaStreamWaitEvent(ctx->stream, ev[0], 0) != cudaSuccess) return bail(dgc_fail(ctx, DGC_ERR_CUDA, "event wait"));
+  if (gen_noise) {   // on the context stream, before the step forks its noise branch off it
+    rc = dgc_noise_fill(ctx, s->noise_seed, s->noise_mode, B, T, s->noise_sigma, d_noise);
+    if (rc != DGC_OK) return bail(rc);
+  }
   double *loss_dev = ctx->loss_accum + (piped ? 1 + slot : 0);
   rc = hn_forward_loss_impl(ctx, &st, d_f0, d_uv, d_amps, d_gain, d_ng, d_tab, d_w, d_noise, d_target, d_work, loss_dev,
                             d_audio, inline_upload ? nullptr : ev[1], inline_upload ? nullptr : ev[2]);

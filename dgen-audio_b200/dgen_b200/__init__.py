@@ -88,7 +88,12 @@ def block_source(ops, name="dgen_block", sequential=False):
 
 
 class HnStep(C.Structure):
-    _fields_ = [("harm", HarmonicParams), ("fir", FirParams), ("mss", MssParams), ("nbands", C.c_int32)]
+    _fields_ = [("harm", HarmonicParams), ("fir", FirParams), ("mss", MssParams), ("nbands", C.c_int32),
+                ("noise_seed", C.c_uint32), ("noise_mode", C.c_int32), ("noise_sigma", C.c_float),
+                ("target_dev", C.c_void_p)]
+
+
+NOISE_STREAM, NOISE_GAUSSIAN = 0, 1
 
 
 _vp, _i32, _i64, _u64, _u32, _f = C.c_void_p, C.c_int32, C.c_int64, C.c_uint64, C.c_uint32, C.c_float
@@ -167,6 +172,7 @@ SIGNATURES = {
     "dgc_harmonic_scratch_floats": (_u64, [C.POINTER(HarmonicParams)]),
     "dgc_harmonic_render": (_i32, [_vp, C.POINTER(HarmonicParams), _vp, _vp, _vp, _vp, _vp, _vp]),
     "dgc_fir_noise": (_i32, [_vp, C.POINTER(FirParams), _vp, _vp, _vp, _vp]),
+    "dgc_noise_fill": (_i32, [_vp, _u32, _i32, _i32, _i32, _f, _vp]),
     "dgc_bands_to_taps": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _vp]),
     "dgc_onepole_fwd": (_i32, [_vp, _vp, _i32, _i32, _f, _vp]),
     "dgc_onepole_fwd_state": (_i32, [_vp, _vp, _i32, _i32, _f, _vp, _vp]),
@@ -450,6 +456,13 @@ class Context:
             out = self._empty(B, T)
         self.check(self.lib.dgc_fir_noise(self.h, C.byref(p), _ptr(noise), _ptr(taps), _ptr(noise_gain), _ptr(out)))
         return out
+
+    def noise_fill(self, seed, B, T, mode=NOISE_STREAM, sigma=1.0, out=None):
+        """Signal.noise() generated on the device: the reference stream (NOISE_STREAM, the same for every voice) or
+        per-voice white N(0, sigma) (NOISE_GAUSSIAN)."""
+        y = self._empty(B, T) if out is None else out
+        self.check(self.lib.dgc_noise_fill(self.h, seed & 0xFFFFFFFF, mode, B, T, sigma, _ptr(y)))
+        return y
 
     def bands_to_taps(self, bands, w):
         F, B, NB = bands.shape

@@ -162,6 +162,18 @@ typedef struct dgc_fir_params {
 int32_t dgc_fir_noise(dgc_ctx *ctx, const dgc_fir_params *p, const float *noise_dev, const float *taps_dev,
                       const float *noise_gain_dev, float *audio_dev);
 
+/* Signal.noise() on the device, frame-parallel (jump-ahead of the generator's linear map, then stepping).
+ * replaces: the `noise` op -- xorshift32 (13, 17, 5), state bit-stored in a cell, a zero state reseeded to 1,
+ * value = state / 2^32 in (0, 1) (Sources/DGen/Renderer/CRenderer.swift:660-695).
+ *   DGC_NOISE_STREAM    out[b][n] = value n of the ONE reference stream started from `seed`, bit for bit, the same for
+ *                       every voice (Signal.noise().buffer(size:).expand([B, size]), Examples/HarmonicE2E/Synth.swift:97-98);
+ *                       sigma is ignored;
+ *   DGC_NOISE_GAUSSIAN  white N(0, sigma) per voice, for the synthetic harmonic+noise workload (no reference
+ *                       counterpart): voice b runs its own xorshift32 stream from a state hashed from (seed, b);
+ *                       frame n maps values 2n and 2n+1 of it through Box-Muller, sigma sqrt(-2 ln u1) cos(2 pi u2). */
+enum { DGC_NOISE_STREAM = 0, DGC_NOISE_GAUSSIAN = 1 };
+int32_t dgc_noise_fill(dgc_ctx *ctx, uint32_t seed, int32_t mode, int32_t B, int32_t T, float sigma, float *out_dev);
+
 /* taps[r][i] = sum_j W[i][j] * bands[r][j]  (rows r = F*B, W is [taps][nbands]): the linear map
  * from band magnitudes to zero-phase FIR taps used by the synthetic harmonic+noise workload. */
 int32_t dgc_bands_to_taps(dgc_ctx *ctx, const float *bands_dev, const float *w_dev, int32_t rows, int32_t nbands,
@@ -670,6 +682,14 @@ typedef struct dgc_hn_step {
   dgc_fir_params fir;      /* fir.taps == 0 disables the noise branch */
   dgc_mss_params mss;
   int32_t nbands;          /* > 0: taps are synthesised from bands_host [F][B][nbands] with w_host [taps][nbands] */
+  /* Host-buffer entry points only (the device-resident call ignores them):
+   * noise_seed != 0 and noise_host == NULL: the noise is generated on the device (dgc_noise_fill with noise_mode and
+   * noise_sigma) instead of being uploaded -- the reference generates its noise inside the graph too;
+   * target_dev != NULL: the target already lives in device memory ([B][T]) and target_host is not uploaded. */
+  uint32_t noise_seed;
+  int32_t noise_mode;
+  float noise_sigma;
+  const float *target_dev;
 } dgc_hn_step;
 
 /* Harmonic+noise synthesis forward + multi-scale spectral loss with every buffer in device memory: what a host
