@@ -36,7 +36,7 @@ struct dgc_ctx {
   std::map<int, float *> hann_sym;                   // N -> symmetric Hann (spectral loss)
   std::map<int, float *> hann_per;                   // N -> periodic Hann (hann())
   std::map<int, float2 *> twiddles;                  // N -> exp(-2 pi i m / N), m < N
-  double *loss_accum = nullptr;                      // 256 doubles: [0..64) results, [64..) per-block sums
+  double *loss_accum = nullptr;                      // 512 doubles: [0..64) results, [64..320) per-block sums
   float *wt_buf = nullptr;  // transposed copy of the current layer's weights (matmul forward)
   uint64_t wt_floats = 0;
   float *dzt_buf = nullptr;  // transposed copy of the current layer's output gradient (matmul backward)

@@ -158,7 +158,7 @@ DGC_EXPORT int32_t dgc_ctx_create(int32_t device, dgc_ctx **out) {
             cudaEventCreate(&c->ev_begin) == cudaSuccess && cudaEventCreate(&c->ev_end) == cudaSuccess &&
             cudaEventCreateWithFlags(&c->ev_sync, cudaEventDisableTiming) == cudaSuccess &&
             cudaMalloc(&c->status_dev, 2 * sizeof(int32_t)) == cudaSuccess &&
-            cudaMalloc(&c->loss_accum, 256 * sizeof(double)) == cudaSuccess &&
+            cudaMalloc(&c->loss_accum, 512 * sizeof(double)) == cudaSuccess &&
             cudaMemset(c->status_dev, 0, 2 * sizeof(int32_t)) == cudaSuccess;
   c->ticket_dev = reinterpret_cast<unsigned int *>(c->status_dev + 1);
   if (!ok) {

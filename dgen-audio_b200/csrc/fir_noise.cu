@@ -219,13 +219,13 @@ fir_noise_kernel(dgc_fir_params prm, const float2 *__restrict__ rowtab, const fl
 //     the signal window through registers, and reduce with shuffles (+9 % instructions).
 // Block = NTH threads x 8 frames.  Results are bit-identical from run to run (fixed summation orders; the list
 // order only decides which lane group computes an entry, not how).
-template <int NTH>
-__global__ void __launch_bounds__(NTH, 768 / NTH)
+template <int NTH, int SPT>
+__global__ void __launch_bounds__(NTH, (SPT == 8 ? 768 : 512) / NTH)
 fir_noise8_kernel(dgc_fir_params prm, const float2 *__restrict__ rowtab, const float *__restrict__ noise,
                   const float *__restrict__ taps_tab, const float *__restrict__ ngain, float *__restrict__ audio,
                   int max_rows, int NTP, int32_t *status) {
   extern __shared__ __align__(16) float sh[];
-  constexpr int SPT = 8, TILE = NTH * SPT, GROUPS = NTH / 8;
+  constexpr int TILE = NTH * SPT, GROUPS = NTH / 8;
   const int B = prm.B, T = prm.T, F = prm.F, NT = prm.taps;
   const int b = blockIdx.y, t0 = blockIdx.x * TILE;
   const int t_last = min(T - 1, t0 + TILE - 1);
@@ -253,7 +253,7 @@ fir_noise8_kernel(dgc_fir_params prm, const float2 *__restrict__ rowtab, const f
     return;
   }
   float *rows = sh;                          // [R][NTP]
-  float *xs = sh + (size_t)max_rows * NTP;   // [SPT][Q]: position m <-> frame t0 - (NT-1) + m, de-interleaved by m % 8
+  float *xs = sh + (size_t)max_rows * NTP;   // [SPT][Q]: position m <-> frame t0 - (NT-1) + m, de-interleaved by m % SPT
   const int XN = TILE + NTP - 1 + SPT;       // zero-extended: the padding taps read beyond the tile
   const int Q = (XN + SPT - 1) / SPT + 1;
   // one warp per control row, lanes along the taps (coalesced, no index division)
@@ -269,7 +269,7 @@ fir_noise8_kernel(dgc_fir_params prm, const float2 *__restrict__ rowtab, const f
   for (int m = threadIdx.x; m < Q * SPT; m += NTH) {
     int t = t0 - (NT - 1) + m;
     float v = (t >= 0 && t < T && m < TILE + NT - 1) ? xn[t] : 0.0f;
-    xs[(m & (SPT - 1)) * Q + (m >> 3)] = v;
+    xs[(m & (SPT - 1)) * Q + m / SPT] = v;
   }
   __syncthreads();
 
@@ -297,36 +297,38 @@ fir_noise8_kernel(dgc_fir_params prm, const float2 *__restrict__ rowtab, const f
     list[my_entry] = threadIdx.x;
   }
   if (have) {
-    // frame (nl+u), tap i reads xs position nl + u + i; W[t] = position nl + i0 + t = xb[(t % 8) * Q + (i0 + t) / 8]
+    // frame (nl+u), tap i reads xs position nl + u + i; W[w] = position nl + SPT g + w = xb[(w % SPT) * Q + g + w / SPT]
     const float4 *pa = reinterpret_cast<const float4 *>(rows + (size_t)r0 * NTP);
     const float4 *pb = reinterpret_cast<const float4 *>(rows + (size_t)(r0 + 1) * NTP);
     const float *xb = xs + threadIdx.x;
-    float W[16];
+    float W[2 * SPT];
 #pragma unroll
-    for (int t = 0; t < 8; ++t) W[t] = xb[t * Q];
-    const int NG = NTP / 8;            // NTP = 8 NG + 4
+    for (int t = 0; t < SPT; ++t) W[t] = xb[t * Q];
+    const int NG = NTP / SPT, rem = NTP - NG * SPT;     // rem: 4 (SPT 8), 4 or 12 (SPT 16)
     auto four = [&](const float4 ta, const float4 tb, int j0) {
       const float a[4] = {ta.x, ta.y, ta.z, ta.w}, c[4] = {tb.x, tb.y, tb.z, tb.w};
 #pragma unroll
       for (int j = 0; j < 4; ++j)
 #pragma unroll
-        for (int u = 0; u < 8; ++u) {
+        for (int u = 0; u < SPT; ++u) {
           d0[u] = fmaf(W[u + j0 + j], a[j], d0[u]);
           d1[u] = fmaf(W[u + j0 + j], c[j], d1[u]);
         }
     };
-#pragma unroll 4
-    for (int g8 = 0; g8 < NG; ++g8) {
+#pragma unroll(SPT == 8 ? 4 : 2)
+    for (int g = 0; g < NG; ++g) {
 #pragma unroll
-      for (int t = 0; t < 8; ++t) W[8 + t] = xb[t * Q + g8 + 1];
-      four(pa[2 * g8], pb[2 * g8], 0);
-      four(pa[2 * g8 + 1], pb[2 * g8 + 1], 4);
+      for (int t = 0; t < SPT; ++t) W[SPT + t] = xb[t * Q + g + 1];
 #pragma unroll
-      for (int t = 0; t < 8; ++t) W[t] = W[8 + t];
+      for (int jb = 0; jb < SPT / 4; ++jb) four(pa[g * (SPT / 4) + jb], pb[g * (SPT / 4) + jb], 4 * jb);
+#pragma unroll
+      for (int t = 0; t < SPT; ++t) W[t] = W[SPT + t];
     }
 #pragma unroll
-    for (int t = 0; t < 4; ++t) W[8 + t] = xb[t * Q + NG + 1];
-    four(pa[2 * NG], pb[2 * NG], 0);
+    for (int t = 0; t < SPT - 4; ++t) W[SPT + t] = t < rem ? xb[t * Q + NG + 1] : 0.0f;
+#pragma unroll
+    for (int jb = 0; jb < SPT / 4 - 1; ++jb)
+      if (4 * jb < rem) four(pa[NG * (SPT / 4) + jb], pb[NG * (SPT / 4) + jb], 4 * jb);
   }
   __syncthreads();
   // third rows of the straddling threads: one list entry per group of 8 lanes, lanes split the taps
@@ -495,14 +497,23 @@ DGC_EXPORT int32_t dgc_fir_noise(dgc_ctx *ctx, const dgc_fir_params *p, const fl
     const char *e = getenv("DGC_FIR");
     return e ? atoi(e) : 128;           // threads per block of the list-based kernel; 0 = the in-loop variant
   }();
+  // frames per thread of the list-based kernel.  16 (DGC_FIR_SPT=16) halves the shared-memory traffic per
+  // multiply-add (16 new signal values and 16 taps of two rows feed 512 multiply-adds instead of 128 for 8 and 8),
+  // but its 128 registers per thread cost more in resident warps than the traffic saves: measured 0.78 ms against
+  // 0.59 ms for 8 frames per thread at 256 voices, 0.097 against 0.076 ms at 16
+  static const int fir_spt = [] {
+    const char *e = getenv("DGC_FIR_SPT");
+    return e && atoi(e) == 16 ? 16 : 8;
+  }();
+  const int spt = (fir_spt == 16 && step * 16 < 0.98 && NT >= 16) ? 16 : 8;
   if (step * 8 < 0.98 && fir_variant > 0) {
     int NTP = (NT + 3) & ~3;
     if (NTP % 8 == 0) NTP += 4;
     auto launch8 = [&](auto kern, int nth) -> int32_t {
-      const int tile = nth * 8;
+      const int tile = nth * spt;
       const int max_rows = (int)(step * tile) + 5;
-      const int XN = tile + NTP - 1 + 8, Q = (XN + 7) / 8 + 1;
-      const size_t smem = ((size_t)max_rows * NTP + (size_t)8 * Q) * sizeof(float);
+      const int XN = tile + NTP - 1 + spt, Q = (XN + spt - 1) / spt + 1;
+      const size_t smem = ((size_t)max_rows * NTP + (size_t)spt * Q) * sizeof(float);
       if (smem > 160 * 1024) return DGC_ERR_UNSUPPORTED;
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return dgc_fail(ctx, DGC_ERR_CUDA, "fir smem opt-in: %s", cudaGetErrorString(e));
@@ -511,7 +522,8 @@ DGC_EXPORT int32_t dgc_fir_noise(dgc_ctx *ctx, const dgc_fir_params *p, const fl
       ctx->launches++;
       return dgc_check_launch(ctx, "fir_noise8");
     };
-    rc = fir_variant == 256 ? launch8(fir_noise8_kernel<256>, 256) : launch8(fir_noise8_kernel<128>, 128);
+    if (spt == 16) rc = fir_variant == 64 ? launch8(fir_noise8_kernel<64, 16>, 64) : launch8(fir_noise8_kernel<128, 16>, 128);
+    else rc = fir_variant == 256 ? launch8(fir_noise8_kernel<256, 8>, 256) : launch8(fir_noise8_kernel<128, 8>, 128);
   }
   if (rc == DGC_ERR_UNSUPPORTED && step * 8 < 0.98) {
     // 256-thread tiles amortise the staged control rows best (measured against 128 and 64 at the headline

@@ -320,10 +320,10 @@ struct ReduceDesc {
   long long cnt[DGC_MSS_MAX_SCALES];  // H_s * B
 };
 
-constexpr int RED_BLOCKS = 64, RED_THREADS = 256;
+constexpr int RED_BLOCKS = 256, RED_THREADS = 256;
 
 // Stage 1: every block sums a strided share of all partials (weighted) in double, in a fixed
-// order; the last block to finish (ticket counter) adds the RED_BLOCKS block sums in index order.
+// order; the last block to finish (ticket counter) adds the RED_BLOCKS block sums by the same fixed tree.
 // The result therefore does not depend on scheduling.
 __global__ void __launch_bounds__(RED_THREADS)
 mss_reduce_kernel(const float *__restrict__ part, ReduceDesc d, double scale_lin, double scale_log,
@@ -353,12 +353,19 @@ mss_reduce_kernel(const float *__restrict__ part, ReduceDesc d, double scale_lin
     last = atomicAdd(ticket, 1u) == RED_BLOCKS - 1;
   }
   __syncthreads();
-  if (last && threadIdx.x == 0) {
+  if (last) {   // the same fixed tree over the block sums, whichever block comes last
+    static_assert(RED_BLOCKS == RED_THREADS, "one block sum per thread of the last block");
     __threadfence();
-    double t = 0.0;
-    for (int i = 0; i < RED_BLOCKS; ++i) t += reinterpret_cast<volatile double *>(block_sums)[i];
-    out[0] = t;
-    *ticket = 0u;
+    sh[threadIdx.x] = reinterpret_cast<volatile double *>(block_sums)[threadIdx.x];
+    __syncthreads();
+    for (int off = RED_THREADS / 2; off > 0; off >>= 1) {
+      if (threadIdx.x < off) sh[threadIdx.x] += sh[threadIdx.x + off];
+      __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+      out[0] = sh[0];
+      *ticket = 0u;
+    }
   }
 }
 

@@ -68,20 +68,32 @@ __global__ void noise_stream_kernel(uint32_t seed, int B, int T, float *__restri
     for (int n = n0; n < n1; ++n) out[(size_t)b * T + n] = v[n - n0];
 }
 
-__global__ void noise_gaussian_kernel(uint32_t seed, int B, int T, float sigma, float *__restrict__ out) {
+// One block = 64 threads = 64 runs = 4096 consecutive frames of one voice.  A thread's run is 256 contiguous bytes,
+// so storing from the registers would make every store instruction touch 32 different 256-byte stretches; the runs
+// go through a shared-memory tile instead (rows padded to 65 floats) and leave as full 128-byte row segments.
+__global__ void __launch_bounds__(64) noise_gaussian_kernel(uint32_t seed, int B, int T, float sigma,
+                                                             float *__restrict__ out) {
+  __shared__ float tile[64][RUN + 1];
   const unsigned run = blockIdx.x * blockDim.x + threadIdx.x;
   const int b = blockIdx.y, n0 = (int)run * RUN;
-  if (n0 >= T) return;
-  uint32_t s = jump_to_run<true>(voice_state(seed, (uint32_t)b), run);
-  const int n1 = min(T, n0 + RUN);
+  if (n0 < T) {
+    uint32_t s = jump_to_run<true>(voice_state(seed, (uint32_t)b), run);
+#pragma unroll 4
+    for (int u = 0; u < RUN; ++u) {
+      s = xs_step(s);
+      const float u1 = (float)s / 4294967296.0f;
+      s = xs_step(s);
+      const float u2 = (float)s / 4294967296.0f;
+      // u1 in (0, 1]: (float)s can round up to 2^32; log(1) = 0 is fine, log(0) cannot happen (s != 0)
+      tile[threadIdx.x][u] = sigma * sqrtf(-2.0f * __logf(u1)) * __cosf(6.283185307179586f * u2);
+    }
+  }
+  __syncthreads();
+  const int base = (int)(blockIdx.x * blockDim.x) * RUN;
   float *o = out + (size_t)b * T;
-  for (int n = n0; n < n1; ++n) {
-    s = xs_step(s);
-    const float u1 = (float)s / 4294967296.0f;
-    s = xs_step(s);
-    const float u2 = (float)s / 4294967296.0f;
-    // u1 in (0, 1]: (float)s can round up to 2^32; log(1) = 0 is fine, log(0) cannot happen (s != 0)
-    o[n] = sigma * sqrtf(-2.0f * __logf(u1)) * __cosf(6.283185307179586f * u2);
+  for (int i = threadIdx.x; i < 64 * RUN; i += 64) {
+    const int n = base + i;
+    if (n < T) o[n] = tile[i / RUN][i % RUN];
   }
 }
 

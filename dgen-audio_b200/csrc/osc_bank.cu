@@ -303,8 +303,9 @@ __device__ __forceinline__ int nyquist_count(float f0v, float nyq, int K) {
 }
 
 // One warp per (voice, chunk of 64 frames): the per-sample fundamental and output envelope of f0_track_kernel plus
-// the chunk's total phase advance of the fundamental, and per frame the pair (phase increment of the fundamental in
-// Q0.32, number of partials below Nyquist) the render kernel reads instead of deriving both in every lane.
+// the chunk's total phase advance of the fundamental (Q0.64), and per frame the pair (phase advance of the
+// fundamental from the chunk's first frame to this one: the wrapping sum of the frames' increments rounded to
+// Q0.32; number of partials below Nyquist) that the render and its backward read instead of deriving them.
 __global__ void __launch_bounds__(128)
 f0_track_fund_kernel(const float2 *__restrict__ rowtab, const float *__restrict__ f0, int B, int T, int F, int K, float sr,
                      float rsr, float *__restrict__ f0t, const float *__restrict__ uv,
@@ -314,9 +315,12 @@ f0_track_fund_kernel(const float2 *__restrict__ rowtab, const float *__restrict_
   const int c = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31, b = blockIdx.y;
   if (c >= C) return;
   unsigned long long tot = 0ull;
+  uint32_t carry = 0u;   // sum of the rounded increments of the chunk's frames before this half
 #pragma unroll
   for (int h = 0; h < CH / 32; ++h) {
     const int n = c * CH + h * 32 + lane;
+    uint32_t dq = 0u;
+    int cnt = 0;
     if (n < T) {
       const float2 rt = rowtab[n];
       const int lo = __float_as_int(rt.x), hi = lo + 1 >= F ? 0 : lo + 1;
@@ -330,7 +334,18 @@ f0_track_fund_kernel(const float2 *__restrict__ rowtab, const float *__restrict_
       }
       const unsigned long long d64 = inc_q64(f0v, sr, rsr);
       tot += d64;
-      if (trk) trk[(size_t)b * T + n] = make_int2((int)(uint32_t)((d64 + 0x80000000ull) >> 32), nyquist_count(f0v, sr * 0.5f, K));
+      dq = (uint32_t)((d64 + 0x80000000ull) >> 32);
+      cnt = nyquist_count(f0v, sr * 0.5f, K);
+    }
+    if (trk) {   // warp-uniform
+      uint32_t inc = dq;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const uint32_t v = __shfl_up_sync(0xffffffffu, inc, off);
+        if (lane >= off) inc += v;
+      }
+      if (n < T) trk[(size_t)b * T + n] = make_int2((int)(carry + inc - dq), cnt);
+      carry += __shfl_sync(0xffffffffu, inc, 31);
     }
   }
 #pragma unroll
@@ -499,6 +514,51 @@ __device__ __forceinline__ uint32_t inc_q32(float f0v, float sr, float rsr) {
   return __float2uint_rn(qh * 4294967296.0f) + (uint32_t)__float2int_rn(ql * 4294967296.0f);
 }
 
+// Sums of one 8-frame block held per lane (S1: sum of a sin, S2: sum of a, over the lane's partials) -> the lanes of
+// the group are reduced so that lane (j & 7) ends with the totals of frame (j & 7), which it normalises, scales by
+// the envelope and stores.  Lanes that differ in bits >= 3 of j hold disjoint partials of the same frames (plain
+// butterfly); the low three bits go through a transposing butterfly (7 shuffles per quantity instead of 24).
+template <int LPC, int MODE>
+__device__ __forceinline__ void render_block_reduce_store(float (&S1)[8], float (&S2)[8], int j, int nb, int T, bool active,
+                                                          const float *__restrict__ envp, const float *__restrict__ gp,
+                                                          float *__restrict__ dst, int accumulate) {
+  constexpr int FB = 8;
+#pragma unroll
+  for (int off = LPC / 2; off >= 8; off >>= 1) {
+#pragma unroll
+    for (int u = 0; u < FB; ++u) {
+      S1[u] += __shfl_xor_sync(0xffffffffu, S1[u], off);
+      S2[u] += __shfl_xor_sync(0xffffffffu, S2[u], off);
+    }
+  }
+  const bool h2 = (j & 4) != 0, h1 = (j & 2) != 0, h0 = (j & 1) != 0;
+  float A1[4], A2[4];
+#pragma unroll
+  for (int v = 0; v < 4; ++v) {
+    const float k1 = h2 ? S1[v + 4] : S1[v], x1 = h2 ? S1[v] : S1[v + 4];
+    const float k2 = h2 ? S2[v + 4] : S2[v], x2 = h2 ? S2[v] : S2[v + 4];
+    A1[v] = k1 + __shfl_xor_sync(0xffffffffu, x1, 4);
+    A2[v] = k2 + __shfl_xor_sync(0xffffffffu, x2, 4);
+  }
+  float B1[2], B2[2];
+#pragma unroll
+  for (int v = 0; v < 2; ++v) {
+    const float k1 = h1 ? A1[v + 2] : A1[v], x1 = h1 ? A1[v] : A1[v + 2];
+    const float k2 = h1 ? A2[v + 2] : A2[v], x2 = h1 ? A2[v] : A2[v + 2];
+    B1[v] = k1 + __shfl_xor_sync(0xffffffffu, x1, 2);
+    B2[v] = k2 + __shfl_xor_sync(0xffffffffu, x2, 2);
+  }
+  const float r1 = (h0 ? B1[1] : B1[0]) + __shfl_xor_sync(0xffffffffu, h0 ? B1[0] : B1[1], 1);
+  const float r2 = (h0 ? B2[1] : B2[0]) + __shfl_xor_sync(0xffffffffu, h0 ? B2[0] : B2[1], 1);
+  const int n = nb + (j & 7);
+  if (active && j < 8 && n < T) {
+    // the kernels take sin / cos of (2 pi p - pi): sin(2 pi p) = -sin(xr), cos(2 pi p) = -cos(xr)
+    float val = -r1 / (r2 + 1e-8f) * envp[n];
+    if (MODE == 1) val *= TWO_PI_F * gp[n];
+    dst[n] = (MODE == 0 && accumulate) ? dst[n] + val : val;
+  }
+}
+
 // SCAN-mode render with fixed-point phases.  The chunk anchors (exact sums of the reference's rounded
 // single-precision increments, Q0.32) carry the long-term phase, so inside a 64-frame chunk the phase of
 // partial k only has to advance by k * (f0 / sr): one integer add per partial and frame in Q0.32, wrapping
@@ -513,15 +573,14 @@ __device__ __forceinline__ uint32_t inc_q32(float f0v, float sr, float rsr) {
 // MODE 0 renders audio.  MODE 1 writes, per frame, the phase gradient folded over the partials,
 // sum_k k * dL/dphi_k[m] with dL/dphi_k = g_audio * env * a_k / (sum a + eps) * 2 pi cos(2 pi phi_k): the
 // input of the temporal scan that gives dL/df0 (the same walk over the phases, cosine instead of sine).
-template <int LPC, int P, int MODE, bool TRK>
+template <int LPC, int P, int MODE>
 __global__ void __launch_bounds__(128, 5)
 harmonic_render_q_kernel(dgc_harmonic_params prm, float rsr, const float2 *__restrict__ rowtab,
                          const float *__restrict__ f0t, const float *__restrict__ env,
                          const float *__restrict__ amps, const uint32_t *__restrict__ anchors_q,
-                         const unsigned long long *__restrict__ fund, const int2 *__restrict__ trk,
+                         const unsigned long long *__restrict__ fund,
                          const float *__restrict__ g_audio, float *__restrict__ audio) {
   constexpr int G = 128 / LPC, FB = 8;
-  constexpr int LOG_LPC = LPC == 8 ? 3 : LPC == 16 ? 4 : 5;
   constexpr float THREE_PI = 9.42477796076938f;
   const int B = prm.B, T = prm.T, K = prm.K, F = prm.F;
   const int C = (T + CH - 1) / CH;
@@ -571,27 +630,7 @@ harmonic_render_q_kernel(dgc_harmonic_params prm, float rsr, const float2 *__res
         }
       }
       float s1 = 0.0f, s2 = 0.0f;
-      if (TRK) {
-        // the fundamental's increment and the number of partials below Nyquist come per frame from the track
-        // kernel: per partial and frame only the amplitude lerp, the phase-to-angle map, the sine and two adds
-        const int2 tk = trk[(size_t)b * T + n];
-        const uint32_t dq = (uint32_t)tk.x;
-        uint32_t incv = (uint32_t)(j + 1) * dq;
-        const uint32_t step = (uint32_t)LPC * dq;
-        const int ilim = max(tk.y - j + LPC - 1, 0) >> LOG_LPC;   // partial j + LPC i + 1 <= count  <=>  i < ilim
-#pragma unroll
-        for (int i = 0; i < P; ++i) {
-          const float a = fmaf(fr, dl[i], alo[i]);
-          const float ph1 = __uint_as_float(__funnelshift_r(q[i], 0x7Fu, 9));  // 1 + phase
-          const float xr = fmaf(ph1, TWO_PI_F, -THREE_PI);
-          if (i < ilim) {
-            s2 += a;
-            s1 = fmaf(__sinf(xr), a, s1);
-          }
-          q[i] += incv;
-          incv += step;
-        }
-      } else {
+      {
         const float f0v = f0p[n];
         const uint32_t dq = inc_q32(f0v, sr, rsr);
         uint32_t incv = (uint32_t)(j + 1) * dq;
@@ -615,43 +654,83 @@ harmonic_render_q_kernel(dgc_harmonic_params prm, float rsr, const float2 *__res
       S1[u] = s1;
       S2[u] = s2;
     }
-    // lanes that differ in bits >= 3 of j hold disjoint partials of the same frames: plain butterfly
-#pragma unroll
-    for (int off = LPC / 2; off >= 8; off >>= 1) {
-#pragma unroll
-      for (int u = 0; u < FB; ++u) {
-        S1[u] += __shfl_xor_sync(0xffffffffu, S1[u], off);
-        S2[u] += __shfl_xor_sync(0xffffffffu, S2[u], off);
-      }
+    render_block_reduce_store<LPC, MODE>(S1, S2, j, n0 + blk * FB, T, active, envp,
+                                         MODE == 1 ? g_audio + (size_t)b * T : nullptr, dst, prm.accumulate);
+  }
+}
+
+// FUNDAMENTAL-mode render from the forward's tracks: ONE THREAD PER FRAME.
+// The track kernel leaves, per voice and frame, the fundamental's phase advance inside its chunk (Q0.32) and the
+// number of partials below Nyquist; with the chunk anchor A (Q0.64) the fundamental's phase at the frame is
+// P = A + (advance << 32), and partial k has phase k P (mod 1): an exact integer product, built as a running 64-bit
+// sum over k.  So a frame needs no state from other frames and no per-partial state at all, and a thread walks the
+// partials of its own frame from 1 to the last audible one:
+//   * nothing is reduced across lanes (the previous mapping spent a third of its instructions on the per-frame
+//     butterfly and the per-lane bookkeeping around 13 partials);
+//   * partials at or above Nyquist cost nothing, and since neighbouring frames have the same count (f0 moves
+//     slowly) a warp's 32 loops end together;
+//   * the amplitude rows are read straight from global memory: the 32 frames of a warp sit on the same control
+//     row (or on two, across a row boundary), so every load is one broadcast line that stays in L1;
+//   * ~40 registers per thread: the latencies of the dependent chain phase -> angle -> sine -> accumulate are
+//     covered by resident warps.
+// Per audible partial and frame: the 64-bit add, the shift, two multiply-adds, the sine, the two accumulates and
+// a quarter of two 16-byte loads (VEC: K a multiple of 4 and 16-byte aligned rows; scalar loads otherwise).
+template <bool VEC>
+__global__ void __launch_bounds__(128)
+harmonic_render_frame_kernel(dgc_harmonic_params prm, const float2 *__restrict__ rowtab, const float *__restrict__ env,
+                             const float *__restrict__ amps, const unsigned long long *__restrict__ fund,
+                             const int2 *__restrict__ trk, float *__restrict__ audio) {
+  constexpr float THREE_PI = 9.42477796076938f;
+  const int B = prm.B, T = prm.T, K = prm.K, F = prm.F;
+  const int C = (T + CH - 1) / CH;
+  const int n = blockIdx.x * 128 + threadIdx.x, b = blockIdx.y;
+  if (n >= T) return;
+  const float2 rt = rowtab[n];
+  const int lo = __float_as_int(rt.x), hi = lo + 1 >= F ? 0 : lo + 1;
+  const float fr = rt.y;
+  const int2 tk = trk[(size_t)b * T + n];
+  const unsigned long long step = fund[(size_t)b * C + n / CH] + ((unsigned long long)(uint32_t)tk.x << 32);
+  const int count = min(tk.y, K);
+  const float *rl = amps + ((size_t)lo * B + b) * K, *rh = amps + ((size_t)hi * B + b) * K;
+  // k * P for k = 1, plus 2^8 in the high word for good: dropping the low 9 bits below then rounds to nearest
+  unsigned long long acc = step + (0x100ull << 32);
+  float s1 = 0.0f, s2 = 0.0f;
+  auto partial = [&](float al, float ah) {
+    const uint32_t q = (uint32_t)(acc >> 32);
+    acc += step;
+    const float a = fmaf(fr, ah - al, al);
+    const float ph1 = __uint_as_float(__funnelshift_r(q, 0x7Fu, 9));  // 1 + phase
+    const float xr = fmaf(ph1, TWO_PI_F, -THREE_PI);                  // 2 pi phase - pi
+    s2 += a;
+    s1 = fmaf(__sinf(xr), a, s1);
+  };
+  int k = 0;
+  if (VEC) {
+    const float4 *rl4 = reinterpret_cast<const float4 *>(rl), *rh4 = reinterpret_cast<const float4 *>(rh);
+#pragma unroll 2
+    for (; k + 4 <= count; k += 4) {
+      const float4 l = __ldg(rl4 + (k >> 2)), h = __ldg(rh4 + (k >> 2));
+      partial(l.x, h.x);
+      partial(l.y, h.y);
+      partial(l.z, h.z);
+      partial(l.w, h.w);
     }
-    // transposing butterfly over the low three bits: lane (j & 7) ends with the totals of frame (j & 7)
-    const bool h2 = (j & 4) != 0, h1 = (j & 2) != 0, h0 = (j & 1) != 0;
-    float A1[4], A2[4];
-#pragma unroll
-    for (int v = 0; v < 4; ++v) {
-      const float k1 = h2 ? S1[v + 4] : S1[v], x1 = h2 ? S1[v] : S1[v + 4];
-      const float k2 = h2 ? S2[v + 4] : S2[v], x2 = h2 ? S2[v] : S2[v + 4];
-      A1[v] = k1 + __shfl_xor_sync(0xffffffffu, x1, 4);
-      A2[v] = k2 + __shfl_xor_sync(0xffffffffu, x2, 4);
-    }
-    float B1[2], B2[2];
-#pragma unroll
-    for (int v = 0; v < 2; ++v) {
-      const float k1 = h1 ? A1[v + 2] : A1[v], x1 = h1 ? A1[v] : A1[v + 2];
-      const float k2 = h1 ? A2[v + 2] : A2[v], x2 = h1 ? A2[v] : A2[v + 2];
-      B1[v] = k1 + __shfl_xor_sync(0xffffffffu, x1, 2);
-      B2[v] = k2 + __shfl_xor_sync(0xffffffffu, x2, 2);
-    }
-    const float r1 = (h0 ? B1[1] : B1[0]) + __shfl_xor_sync(0xffffffffu, h0 ? B1[0] : B1[1], 1);
-    const float r2 = (h0 ? B2[1] : B2[0]) + __shfl_xor_sync(0xffffffffu, h0 ? B2[0] : B2[1], 1);
-    const int n = n0 + blk * FB + (j & 7);
-    if (active && j < 8 && n < T) {
-      // sin(2 pi p) = -sin(xr), cos(2 pi p) = -cos(xr)
-      float val = -r1 / (r2 + 1e-8f) * envp[n];
-      if (MODE == 1) val *= TWO_PI_F * g_audio[(size_t)b * T + n];
-      dst[n] = (MODE == 0 && prm.accumulate) ? dst[n] + val : val;
+  } else {
+#pragma unroll 4
+    for (; k + 4 <= count; k += 4) {
+      const float l0 = __ldg(rl + k), l1 = __ldg(rl + k + 1), l2 = __ldg(rl + k + 2), l3 = __ldg(rl + k + 3);
+      const float h0 = __ldg(rh + k), h1 = __ldg(rh + k + 1), h2 = __ldg(rh + k + 2), h3 = __ldg(rh + k + 3);
+      partial(l0, h0);
+      partial(l1, h1);
+      partial(l2, h2);
+      partial(l3, h3);
     }
   }
+  for (; k < count; ++k) partial(__ldg(rl + k), __ldg(rh + k));
+  // sin(2 pi p) = -sin(2 pi p - pi)
+  const float val = -s1 / (s2 + 1e-8f) * env[(size_t)b * T + n];
+  float *dst = audio + (size_t)b * T + n;
+  *dst = prm.accumulate ? *dst + val : val;
 }
 
 template <int LPC, int P>
@@ -698,13 +777,14 @@ void launch_render_q(dgc_ctx *ctx, const dgc_harmonic_params &p, const float2 *r
   int C = (p.T + CH - 1) / CH;
   constexpr int G = 128 / LPC;
   dim3 grid(dgc_div_up(C, G), p.B);
-  if (MODE == 0 && x.trk)
-    harmonic_render_q_kernel<LPC, P, 0, true><<<grid, 128, 0, ctx->stream>>>(p, 1.0f / p.sample_rate, rowtab, x.f0t, x.env,
-                                                                              amps, x.anchors_q, x.fund, x.trk, g_audio, out);
-  else
-    harmonic_render_q_kernel<LPC, P, MODE, false><<<grid, 128, 0, ctx->stream>>>(p, 1.0f / p.sample_rate, rowtab, x.f0t,
-                                                                                  x.env, amps, x.anchors_q, x.fund, x.trk,
-                                                                                  g_audio, out);
+  if (MODE == 0 && x.fund && x.trk) {
+    const dim3 fgrid(dgc_div_up(p.T, 128), p.B);
+    const bool vec = (p.K & 3) == 0 && (((uintptr_t)amps) & 15) == 0;
+    if (vec) harmonic_render_frame_kernel<true><<<fgrid, 128, 0, ctx->stream>>>(p, rowtab, x.env, amps, x.fund, x.trk, out);
+    else harmonic_render_frame_kernel<false><<<fgrid, 128, 0, ctx->stream>>>(p, rowtab, x.env, amps, x.fund, x.trk, out);
+  } else
+    harmonic_render_q_kernel<LPC, P, MODE><<<grid, 128, 0, ctx->stream>>>(p, 1.0f / p.sample_rate, rowtab, x.f0t, x.env,
+                                                                           amps, x.anchors_q, x.fund, g_audio, out);
 }
 
 // The reverse scan of the reference's temporalGradScan (Sources/DGen/Emit+TemporalGradient.swift:54-88), per row e

@@ -97,6 +97,15 @@ static int32_t hn_forward_loss_impl(dgc_ctx *ctx, const dgc_hn_step *s, const fl
   int32_t rc = DGC_OK;
   cudaStream_t main_stream = ctx->stream;
   bool forked = false;
+  // From a few million samples per step on, every big kernel fills the GPU by itself and running the FIR beside the
+  // render buys nothing: then only the band -> tap map runs on the side stream, and the FIR follows the render on
+  // the caller's stream ADDING into the render's output, which drops the pass that sums the two branches (the sum
+  // is the same single-precision add either way: the results are bit-identical).  DGC_HN_FIR=side|serial forces one.
+  static const int fir_mode = [] {
+    const char *e = getenv("DGC_HN_FIR");
+    return !e ? 0 : strcmp(e, "side") == 0 ? 1 : strcmp(e, "serial") == 0 ? 2 : 0;
+  }();
+  const bool serial_fir = noise && (fir_mode == 2 || (fir_mode == 0 && nBT >= (4ull << 20)));
   if (noise) {
     // fork: the noise branch starts where the caller's stream stands now
     DGC_CUDA(ctx, cudaEventRecord(ctx->fork_ev, main_stream));
@@ -105,7 +114,7 @@ static int32_t hn_forward_loss_impl(dgc_ctx *ctx, const dgc_hn_step *s, const fl
     forked = true;
     ctx->stream = ctx->aux_stream;
     if (NB > 0) rc = dgc_bands_to_taps(ctx, taps_or_bands_dev, w_dev, (int32_t)nFB, NB, NT, d_taps);
-    if (rc == DGC_OK) {
+    if (rc == DGC_OK && !serial_fir) {
       dgc_fir_params fp = s->fir;
       fp.accumulate = 0;
       rc = dgc_fir_noise(ctx, &fp, noise_dev, d_taps, noise_gain_dev, d_noise);
@@ -123,9 +132,15 @@ static int32_t hn_forward_loss_impl(dgc_ctx *ctx, const dgc_hn_step *s, const fl
   // join, whatever happened above: nothing of this call is left running beside the caller's stream
   if (forked) cudaStreamWaitEvent(main_stream, ctx->join_ev, 0);
   if (rc != DGC_OK) return rc;
+  if (serial_fir) {
+    dgc_fir_params fp = s->fir;
+    fp.accumulate = 1;
+    rc = dgc_fir_noise(ctx, &fp, noise_dev, d_taps, noise_gain_dev, d_harm);
+    if (rc != DGC_OK) return rc;
+  }
   if (ev_target) DGC_CUDA(ctx, cudaStreamWaitEvent(main_stream, ev_target, 0));
   if (audio_dev) {
-    if (noise) {
+    if (noise && !serial_fir) {
       add2_kernel<<<dgc_div_up((int64_t)nBT, 256), 256, 0, ctx->stream>>>(d_harm, d_noise, nBT, audio_dev);
       DGC_LAUNCHED(ctx, "add_branches");
     } else {
@@ -139,6 +154,7 @@ static int32_t hn_forward_loss_impl(dgc_ctx *ctx, const dgc_hn_step *s, const fl
     const char *e = getenv("DGC_HN_SUM");
     return !(e && strcmp(e, "fused") == 0);
   }();
+  if (serial_fir) return dgc_mss_loss_fwd_sum(ctx, &s->mss, d_harm, nullptr, target_dev, nullptr, loss_dev);
   if (add_first && noise) {
     add2_kernel<<<dgc_div_up((int64_t)nBT, 256), 256, 0, ctx->stream>>>(d_harm, d_noise, nBT, d_harm);
     DGC_LAUNCHED(ctx, "add_branches");

@@ -289,14 +289,20 @@ __device__ __forceinline__ uint32_t inc_q32_bwd(float f0v, float sr, float rsr) 
   return __float2uint_rn(qh * 4294967296.0f) + (uint32_t)__float2int_rn(ql * 4294967296.0f);
 }
 
-template <int LPC, int P>
+//
+// TRK (FUNDAMENTAL mode, tracks of the forward at hand): the fundamental's phase advance inside the chunk and the
+// number of partials below Nyquist are read per frame from the forward's track; the phase of partial k is
+// anchor_k + k * phi with phi that advance, so no per-partial state advances and both loops over this lane's partials end at the
+// last audible one (the partials at or above Nyquist contribute an exact zero and are not visited).
+template <int LPC, int P, bool TRK>
 __global__ void __launch_bounds__(128)
 harmonic_bwd_q_kernel(dgc_harmonic_params prm, float rsr, const float2 *__restrict__ rowtab,
                       const int *__restrict__ ranges, const float *__restrict__ f0t, const float *__restrict__ env,
                       const float *__restrict__ amps, const uint32_t *__restrict__ anchors_q,
-                      const unsigned long long *__restrict__ fund, const float *__restrict__ g_audio,
-                      float *__restrict__ part_lo, float *__restrict__ part_hi) {
+                      const unsigned long long *__restrict__ fund, const int2 *__restrict__ trk,
+                      const float *__restrict__ g_audio, float *__restrict__ part_lo, float *__restrict__ part_hi) {
   constexpr int G = 128 / LPC;
+  constexpr int LOG_LPC = LPC == 8 ? 3 : LPC == 16 ? 4 : 5;
   constexpr float THREE_PI = 9.42477796076938f;
   const int B = prm.B, T = prm.T, K = prm.K, F = prm.F;
   const int C = (T + CH - 1) / CH;
@@ -319,6 +325,8 @@ harmonic_bwd_q_kernel(dgc_harmonic_params prm, float rsr, const float2 *__restri
     q[i] = 0u;
   }
   const float *g = g_audio + (size_t)b * T, *f0p = f0t + (size_t)b * T, *envp = env + (size_t)b * T;
+  const int2 *tkp = trk + (size_t)b * T;
+  uint32_t phi = 0u;   // TRK: the fundamental's increments summed from the chunk start to the current frame
   for (int run = 0; run < 2; ++run) {
     const int s0 = ranges[r * 4 + 2 * run], s1 = ranges[r * 4 + 2 * run + 1];
     const int len = active ? s1 - s0 : 0;
@@ -332,7 +340,7 @@ harmonic_bwd_q_kernel(dgc_harmonic_params prm, float rsr, const float2 *__restri
       const int c0 = len > 0 ? s0 / CH : 0;
       uint32_t part = 0u;
       if (len > 0)
-        for (int n = c0 * CH + j; n < s0; n += LPC) part += inc_q32_bwd(f0p[n], sr, rsr);
+        for (int n = c0 * CH + j; !TRK && n < s0; n += LPC) part += inc_q32_bwd(f0p[n], sr, rsr);
 #pragma unroll
       for (int off = LPC / 2; off > 0; off >>= 1) part += __shfl_xor_sync(0xffffffffu, part, off);
       if (len > 0) {
@@ -343,8 +351,9 @@ harmonic_bwd_q_kernel(dgc_harmonic_params prm, float rsr, const float2 *__restri
         for (int i = 0; i < P; ++i) {
           int k = j + LPC * i;
           const uint32_t a0 = fund ? (uint32_t)(((unsigned long long)(k + 1) * fa) >> 32) : (k < K ? anc[k] : 0u);
-          q[i] = a0 + 0x100u + (uint32_t)(k + 1) * part;
+          q[i] = a0 + 0x100u + (TRK ? 0u : (uint32_t)(k + 1) * part);
         }
+        phi = part;
       }
     }
     for (int m = 0; m < maxlen; ++m) {
@@ -359,8 +368,48 @@ harmonic_bwd_q_kernel(dgc_harmonic_params prm, float rsr, const float2 *__restri
           const uint32_t a0 = fund ? (uint32_t)(((unsigned long long)(k + 1) * fa) >> 32) : (k < K ? anc[k] : 0u);
           q[i] = a0 + 0x100u;
         }
+        phi = 0u;
       }
       const float fr = rowtab[n].y, omf = __fsub_rn(1.0f, fr);
+      if (TRK) {
+        const int2 tk = tkp[n];
+        phi = (uint32_t)tk.x;   // the fundamental's phase advance from the chunk's first frame, from the forward's track
+        const int ilim = live ? max(tk.y - j + LPC - 1, 0) >> LOG_LPC : 0;   // partial j + LPC i + 1 <= count  <=>  i < ilim
+        float sn[P];
+        float s1v = 0.0f, s2v = 0.0f;
+        uint32_t w = (uint32_t)(j + 1) * phi;          // k * phi as a running sum over this lane's partials
+        const uint32_t r = phi << LOG_LPC;
+#pragma unroll
+        for (int i = 0; i < P; ++i) {
+          if (i >= ilim) break;
+          const uint32_t qq = q[i] + w;
+          w += r;
+          const float a = fmaf(fr, dl[i], alo[i]);
+          const float ph1 = __uint_as_float(__funnelshift_r(qq, 0x7Fu, 9));
+          sn[i] = -__sinf(fmaf(ph1, TWO_PI_F, -THREE_PI));   // sin(2 pi p)
+          s2v += a;
+          s1v = fmaf(sn[i], a, s1v);
+        }
+#pragma unroll
+        for (int off = LPC / 2; off > 0; off >>= 1) {
+          s1v += __shfl_xor_sync(0xffffffffu, s1v, off);
+          s2v += __shfl_xor_sync(0xffffffffu, s2v, off);
+        }
+        if (live) {
+          const float inv = 1.0f / (s2v + 1e-8f);
+          const float ratio = s1v * inv;
+          const float c = g[n] * envp[n] * inv;
+          const float cl = c * omf, chh = c * fr;
+#pragma unroll
+          for (int i = 0; i < P; ++i) {
+            if (i >= ilim) break;
+            const float d = sn[i] - ratio;
+            pl[i] = fmaf(cl, d, pl[i]);
+            phh[i] = fmaf(chh, d, phh[i]);
+          }
+        }
+        continue;
+      }
       const float f0v = f0p[n];
       const uint32_t dq = inc_q32_bwd(f0v, sr, rsr);
       uint32_t incv = (uint32_t)(j + 1) * dq;
@@ -416,8 +465,12 @@ template <int LPC, int P>
 void launch_hbwd_q(dgc_ctx *ctx, const dgc_harmonic_params &p, const float2 *rowtab, const int *ranges,
                    const dgc_harmonic_extra &x, const float *amps, const float *g_audio, float *pl, float *ph) {
   constexpr int G = 128 / LPC;
-  harmonic_bwd_q_kernel<LPC, P><<<dim3(dgc_div_up(p.F, G), p.B), 128, 0, ctx->stream>>>(
-      p, 1.0f / p.sample_rate, rowtab, ranges, x.f0t, x.env, amps, x.anchors_q, x.fund, g_audio, pl, ph);
+  if (x.fund && x.trk)
+    harmonic_bwd_q_kernel<LPC, P, true><<<dim3(dgc_div_up(p.F, G), p.B), 128, 0, ctx->stream>>>(
+        p, 1.0f / p.sample_rate, rowtab, ranges, x.f0t, x.env, amps, x.anchors_q, x.fund, x.trk, g_audio, pl, ph);
+  else
+    harmonic_bwd_q_kernel<LPC, P, false><<<dim3(dgc_div_up(p.F, G), p.B), 128, 0, ctx->stream>>>(
+        p, 1.0f / p.sample_rate, rowtab, ranges, x.f0t, x.env, amps, x.anchors_q, x.fund, x.trk, g_audio, pl, ph);
 }
 
 template <int LPC, int P>

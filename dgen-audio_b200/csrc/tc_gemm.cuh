@@ -198,6 +198,7 @@ __device__ __forceinline__ void epilogue(uint32_t tmem_d, const float *__restric
   const bool aligned = ((N & 3) == 0) && ((((uintptr_t)C) & 15) == 0);
 #pragma unroll 1
   for (int c0 = col_base; c0 < col_base + BN / 2; c0 += 32) {
+    if (n0 + c0 >= N) break;   // the rest of this tile lies beyond the last column (warp-uniform)
     uint32_t r[32];
     const uint32_t taddr = tmem_d + ((uint32_t)lane_base << 16) + (uint32_t)c0;
     asm volatile(
@@ -220,23 +221,26 @@ __device__ __forceinline__ void epilogue(uint32_t tmem_d, const float *__restric
       stage[lane * 33 + j] = x;   // bank (lane + j) % 32: conflict-free
     }
     __syncwarp();
-    // 4 rows per instruction: lane -> (row it * 4 + lane / 8, columns 4 * (lane % 8) ..)
-    const int rsub = lane >> 3, c4 = (lane & 7) * 4;
     const bool vec_ok = aligned && gn0 + 31 < N;
+    if (vec_ok) {
+      // 4 rows per instruction: lane -> (row it * 4 + lane / 8, columns 4 * (lane % 8) ..)
+      const int rsub = lane >> 3, c4 = (lane & 7) * 4;
 #pragma unroll
-    for (int it = 0; it < 8; ++it) {
-      const int rr = it * 4 + rsub, grow = m0 + lane_base + rr;
-      const float *sp = stage + rr * 33 + c4;
-      const float v0 = sp[0], v1 = sp[1], v2 = sp[2], v3 = sp[3];
-      if (grow < M) {
-        float *crow = C + (size_t)grow * N + gn0 + c4;
-        if (vec_ok) *reinterpret_cast<float4 *>(crow) = make_float4(v0, v1, v2, v3);
-        else {
-          if (gn0 + c4 < N) crow[0] = v0;
-          if (gn0 + c4 + 1 < N) crow[1] = v1;
-          if (gn0 + c4 + 2 < N) crow[2] = v2;
-          if (gn0 + c4 + 3 < N) crow[3] = v3;
-        }
+      for (int it = 0; it < 8; ++it) {
+        const int rr = it * 4 + rsub, grow = m0 + lane_base + rr;
+        const float *sp = stage + rr * 33 + c4;
+        const float v0 = sp[0], v1 = sp[1], v2 = sp[2], v3 = sp[3];
+        if (grow < M) *reinterpret_cast<float4 *>(C + (size_t)grow * N + gn0 + c4) = make_float4(v0, v1, v2, v3);
+      }
+    } else {
+      // rows that are not 16-byte aligned (N not a multiple of 4) or the ragged last columns: one row per
+      // instruction, lanes = consecutive columns, so every store still covers one contiguous run of a row
+      const bool col_ok = gn0 + lane < N;
+#pragma unroll 8
+      for (int rr = 0; rr < 32; ++rr) {
+        const int grow = m0 + lane_base + rr;
+        const float v = stage[rr * 33 + lane];
+        if (col_ok && grow < M) C[(size_t)grow * N + gn0 + lane] = v;
       }
     }
     __syncwarp();
