@@ -41,8 +41,6 @@ struct dgc_ctx {
   uint64_t wt_floats = 0;
   float *dzt_buf = nullptr;  // transposed copy of the current layer's output gradient (matmul backward)
   uint64_t dzt_floats = 0;
-  float *pad_buf = nullptr;  // operands copied to a row length that is a multiple of 4 floats (band -> tap map)
-  uint64_t pad_floats = 0;
   // staging for the host-buffer composite entry points; uploads run on their own stream so that the
   // first kernels start while later inputs are still crossing PCIe
   cudaStream_t aux_stream = nullptr;   // second stream of the composite steps (noise branch beside the harmonic one)

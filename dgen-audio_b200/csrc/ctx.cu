@@ -197,7 +197,6 @@ DGC_EXPORT int32_t dgc_ctx_destroy(dgc_ctx *c) {
   if (c->aux_stream) cudaStreamDestroy(c->aux_stream);
   if (c->wt_buf) cudaFree(c->wt_buf);
   if (c->dzt_buf) cudaFree(c->dzt_buf);
-  if (c->pad_buf) cudaFree(c->pad_buf);
   if (c->status_dev) cudaFree(c->status_dev);
   if (c->loss_accum) cudaFree(c->loss_accum);
   if (c->ev_begin) cudaEventDestroy(c->ev_begin);

@@ -229,21 +229,15 @@ fir_noise8_kernel(dgc_fir_params prm, const float2 *__restrict__ rowtab, const f
   const int B = prm.B, T = prm.T, F = prm.F, NT = prm.taps;
   const int b = blockIdx.y, t0 = blockIdx.x * TILE;
   const int t_last = min(T - 1, t0 + TILE - 1);
-  __shared__ int wrap_sh, n_list;
+  __shared__ int n_list;
   __shared__ int list[NTH];            // straddling threads
   __shared__ float d2buf[NTH][SPT];    // their third dot products, by list position
-  if (threadIdx.x == 0) {
-    wrap_sh = 0x7fffffff;
-    n_list = 0;
-  }
-  __syncthreads();
-#pragma unroll
-  for (int u = 0; u < SPT; ++u) {
-    int n = t0 + threadIdx.x * SPT + u;
-    if (n > t0 && n <= t_last && __float_as_int(rowtab[n].x) < __float_as_int(rowtab[n - 1].x)) atomicMin(&wrap_sh, n);
-  }
-  __syncthreads();
-  const int wrap = wrap_sh;
+  if (threadIdx.x == 0) n_list = 0;
+  // The frame at which the control clock wrapped (entry T of the row table; above every frame when it never does:
+  // the playhead sweeps the control rows once, so there is at most one).  It concerns this tile only when it lies
+  // strictly inside: the rows behind it are then numbered F, F + 1, .. so that the tile's rows stay ascending.
+  const int wrap_all = __float_as_int(rowtab[T].x);
+  const int wrap = (wrap_all > t0 && wrap_all <= t_last) ? wrap_all : 0x7fffffff;
   const int rmin = __float_as_int(rowtab[t0].x);
   int rmax = __float_as_int(rowtab[t_last].x);
   if (t_last >= wrap) rmax += F;
@@ -256,21 +250,33 @@ fir_noise8_kernel(dgc_fir_params prm, const float2 *__restrict__ rowtab, const f
   float *xs = sh + (size_t)max_rows * NTP;   // [SPT][Q]: position m <-> frame t0 - (NT-1) + m, de-interleaved by m % SPT
   const int XN = TILE + NTP - 1 + SPT;       // zero-extended: the padding taps read beyond the tile
   const int Q = (XN + SPT - 1) / SPT + 1;
-  // one warp per control row, lanes along the taps (coalesced, no index division)
+  // Staging by asynchronous 4-byte copies (the rows of the tap table are not 16-byte aligned): every copy of the
+  // tile is in flight before the first one is waited for, and nothing passes through registers.  One warp per
+  // control row, lanes along the taps (coalesced, no index division); padding taps and frames outside the signal
+  // are zero-filled by the copy itself (source size 0).
   for (int rr = threadIdx.x >> 5; rr < R; rr += NTH / 32) {
     int r = rmin + rr;
     if (r >= F) r -= F;  // the ceil row wraps to row 0
     if (r >= F) r = F - 1;
     const float *src = taps_tab + ((size_t)r * B + b) * NT;
-    float *dst = rows + (size_t)rr * NTP;
-    for (int col = threadIdx.x & 31; col < NTP; col += 32) dst[col] = col < NT ? src[col] : 0.0f;
+    const uint32_t dst = (uint32_t)__cvta_generic_to_shared(rows + (size_t)rr * NTP);
+    for (int col = threadIdx.x & 31; col < NTP; col += 32) {
+      const bool in = col < NT;
+      asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst + 4u * col), "l"(in ? src + col : src),
+                   "r"(in ? 4 : 0)
+                   : "memory");
+    }
   }
   const float *xn = noise + (size_t)b * T;
   for (int m = threadIdx.x; m < Q * SPT; m += NTH) {
-    int t = t0 - (NT - 1) + m;
-    float v = (t >= 0 && t < T && m < TILE + NT - 1) ? xn[t] : 0.0f;
-    xs[(m & (SPT - 1)) * Q + m / SPT] = v;
+    const int t = t0 - (NT - 1) + m;
+    const bool in = t >= 0 && t < T && m < TILE + NT - 1;
+    const uint32_t dst = (uint32_t)__cvta_generic_to_shared(xs + (m & (SPT - 1)) * Q + m / SPT);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(in ? xn + t : xn), "r"(in ? 4 : 0)
+                 : "memory");
   }
+  asm volatile("cp.async.commit_group;" ::: "memory");
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
   __syncthreads();
 
   const int nl = threadIdx.x * SPT;  // first local frame of this thread
@@ -455,15 +461,6 @@ bands_to_taps_kernel(const float *__restrict__ bands, const float *__restrict__ 
   }
 }
 
-// out[r][c] = c < K ? in[r][c] : 0, rows of Kp floats (Kp a multiple of 4: 16-byte aligned rows)
-__global__ void pad_rows_kernel(const float *__restrict__ in, int64_t rows, int K, int Kp, float *__restrict__ out) {
-  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= rows * Kp) return;
-  const int64_t r = i / Kp;
-  const int c = (int)(i - r * Kp);
-  out[i] = c < K ? in[r * K + c] : 0.0f;
-}
-
 }  // namespace
 
 DGC_EXPORT int32_t dgc_fir_noise(dgc_ctx *ctx, const dgc_fir_params *p, const float *noise_dev,
@@ -551,29 +548,9 @@ DGC_EXPORT int32_t dgc_bands_to_taps(dgc_ctx *ctx, const float *bands_dev, const
   DGC_REQUIRE(ctx, rows > 0 && nbands > 0 && taps > 0, "size out of range");
   // large row counts go to the tensor-core matmul (taps = bands * W^T); the shared-memory kernel keeps small ones
   if ((double)rows * nbands * taps >= (double)(1 << 24)) {
-    if ((nbands & 3) == 0) return dgc_gemm_nt(ctx, bands_dev, w_dev, rows, taps, nbands, taps_dev);
-    // 65 bands: rows of 260 bytes are not 16-byte aligned, which keeps the product off the asynchronous
-    // tensor-core pipeline (its 16-byte copies) and on the slower any-orientation kernel.  Copy both operands
-    // to a row length that is a multiple of 4 floats (zero beyond nbands) first: one small pass over the bands.
-    const int Kp = (nbands + 3) & ~3;
-    const uint64_t need = ((uint64_t)rows + taps) * Kp + 8;
-    if (ctx->pad_floats < need) {
-      if (ctx->pad_buf) {
-        cudaStreamSynchronize(ctx->stream);
-        cudaFree(ctx->pad_buf);
-        ctx->buffer_generation++;
-        ctx->pad_buf = nullptr;
-        ctx->pad_floats = 0;
-      }
-      DGC_CUDA(ctx, cudaMalloc(&ctx->pad_buf, need * sizeof(float)));
-      ctx->pad_floats = need;
-    }
-    float *bp = ctx->pad_buf, *wp = bp + (((uint64_t)rows * Kp + 3) & ~3ull);
-    pad_rows_kernel<<<dgc_div_up((int64_t)rows * Kp, 256), 256, 0, ctx->stream>>>(bands_dev, rows, nbands, Kp, bp);
-    DGC_LAUNCHED(ctx, "pad_bands");
-    pad_rows_kernel<<<dgc_div_up((int64_t)taps * Kp, 256), 256, 0, ctx->stream>>>(w_dev, taps, nbands, Kp, wp);
-    DGC_LAUNCHED(ctx, "pad_w");
-    return dgc_gemm_nt(ctx, bp, wp, rows, taps, Kp, taps_dev);
+    // (65 bands: rows of 260 bytes are not 16-byte aligned; the matmul then fetches its operands with 4-byte
+    // asynchronous copies instead of 16-byte ones, which is cheaper than a padding pass over the bands)
+    return dgc_gemm_nt(ctx, bands_dev, w_dev, rows, taps, nbands, taps_dev);
   }
   size_t smem = ((((size_t)taps * (nbands | 1) + 3) & ~(size_t)3) + (size_t)nbands * 16) * sizeof(float);
   DGC_REQUIRE(ctx, smem <= 200 * 1024, "taps*nbands too large for shared memory");

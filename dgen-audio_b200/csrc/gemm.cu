@@ -130,13 +130,16 @@ int32_t launch_sgemm(dgc_ctx *ctx, const float *A, const float *B, const float *
     return e ? atoi(e) : 16;
   }();
   // the asynchronous pipeline needs both operands contiguous along k, K a multiple of 4 and aligned rows
-  const bool kk = tc && !TA && TB && kk_bk && (K & 3) == 0 && ((((uintptr_t)A) | ((uintptr_t)B)) & 15) == 0;
+  const bool kk16 = tc && !TA && TB && kk_bk && (K & 3) == 0 && ((((uintptr_t)A) | ((uintptr_t)B)) & 15) == 0;
+  // rows that are not 16-byte aligned (K % 4 != 0, e.g. 65 band magnitudes): the same pipeline with 4-byte copies
+  const bool kk4 = tc && !TA && TB && kk_bk && !kk16 && EPI == 0;
+  const bool kk = kk16 || kk4;
   // 128 x 256 tiles, one CTA per SM: 25 % less shared-memory traffic per flop, but prologue and epilogue are no
   // longer hidden by a second resident CTA, so they only pay where a CTA runs a long reduction -- the split-K
   // weight gradients (measured: training step 3.84 -> 3.78 ms; the forward layers get 4 % slower with them).
   // DGC_GEMM_KK=256 forces them wherever N >= 256.
   const bool long_reduction = EPI == 0 && K >= 2048 && dgc_div_up(N, dgtc::TBN) * dgc_div_up(M, dgtc::TBM) < ctx->sm_count;
-  const bool wide = kk && N >= 256 && (kk_bk == 256 || (kk_bk == 16 && long_reduction));
+  const bool wide = kk16 && N >= 256 && (kk_bk == 256 || (kk_bk == 16 && long_reduction));
   const int bm = tc ? dgtc::TBM : BM, bn = wide ? 256 : (tc ? dgtc::TBN : BN);
   const int tiles = dgc_div_up(N, bn) * dgc_div_up(M, bm);
   int splits = 1;
@@ -168,7 +171,13 @@ int32_t launch_sgemm(dgc_ctx *ctx, const float *A, const float *B, const float *
     kern<<<grid, dgtc::KK_THREADS, SM, ctx->stream>>>(A, B, bias, M, N, K, kps, dst, splits == 1 ? Ct : nullptr,    \
                                                    ctx->status_dev);                                                \
   } while (0)
-    if (wide) {
+    if (kk4) {
+      auto kern = dgtc::tc_gemm_kk_kernel<0, 16, true, dgtc::TBN, true>;
+      constexpr int SM = dgtc::KK<16, true, dgtc::TBN>::SMEM;
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM);
+      if (e != cudaSuccess) return dgc_fail(ctx, DGC_ERR_CUDA, "tc_gemm smem opt-in: %s", cudaGetErrorString(e));
+      kern<<<grid, dgtc::KK_THREADS, SM, ctx->stream>>>(A, B, nullptr, M, N, K, kps, dst, nullptr, ctx->status_dev);
+    } else if (wide) {
       auto kern = dgtc::tc_gemm_kk_kernel<EPI, 16, true, 256>;
       constexpr int SM = dgtc::KK<16, true, 256>::SMEM;
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM);

@@ -105,7 +105,10 @@ __global__ void osc_const_render_kernel(const float *__restrict__ freq, const fl
 // ---------------------------------------------------------------------------------------------
 // batched harmonic bank
 // ---------------------------------------------------------------------------------------------
-// per-frame sampleRow position of the cached control clock: (floor row as int bits, fraction)
+// per-frame sampleRow position of the cached control clock: (floor row as int bits, fraction).
+// Entry T (one past the frames) holds, as int bits in .x, the first frame whose floor row is below its
+// predecessor's (the control clock wrapped), or a value above every frame index when the rows only ascend:
+// preset by the host, lowered here with an atomic minimum.
 __global__ void row_table_kernel(const float *__restrict__ play, int T, int F, float2 *__restrict__ tab) {
   int n = blockIdx.x * blockDim.x + threadIdx.x;
   if (n >= T) return;
@@ -113,6 +116,12 @@ __global__ void row_table_kernel(const float *__restrict__ play, int T, int F, f
   float fr;
   row_pos(play[n], F, lo, hi, fr);
   tab[n] = make_float2(__int_as_float(lo), fr);
+  if (n > 0) {
+    int plo, phi;
+    float pfr;
+    row_pos(play[n - 1], F, plo, phi, pfr);
+    if (lo < plo) atomicMin(reinterpret_cast<int *>(&tab[T].x), n);
+  }
 }
 
 // f0t[b][n] = sampleRow(f0)[n][b], strict single-precision lerp; optionally the output envelope
@@ -706,6 +715,8 @@ harmonic_render_frame_kernel(dgc_harmonic_params prm, const float2 *__restrict__
   };
   int k = 0;
   if (VEC) {
+    // (keeping the next four partials' amplitudes in flight by hand, or staging the block's rows in shared memory,
+    // both measured slower than this plain loop: 0.64 and 0.74 ms against 0.57 ms for the stage at 256 voices)
     const float4 *rl4 = reinterpret_cast<const float4 *>(rl), *rh4 = reinterpret_cast<const float4 *>(rh);
 #pragma unroll 2
     for (; k + 4 <= count; k += 4) {
@@ -868,8 +879,14 @@ const float2 *dgc_ctx_row_table(dgc_ctx *ctx, int F, int T) {
   const float *play = nullptr;
   if (dgc_playhead(ctx, F, T, &play) != DGC_OK) return nullptr;
   float2 *d = nullptr;
-  if (cudaMalloc(&d, (size_t)T * sizeof(float2)) != cudaSuccess) {
+  if (cudaMalloc(&d, ((size_t)T + 1) * sizeof(float2)) != cudaSuccess) {
     dgc_fail(ctx, DGC_ERR_OOM, "row table allocation failed");
+    return nullptr;
+  }
+  // entry T: "no wrap" = 0x7f7f7f7f, above every frame index
+  if (cudaMemsetAsync(d + T, 0x7f, sizeof(float2), ctx->stream) != cudaSuccess) {
+    cudaFree(d);
+    dgc_fail(ctx, DGC_ERR_CUDA, "row table preset failed");
     return nullptr;
   }
   row_table_kernel<<<dgc_div_up(T, 256), 256, 0, ctx->stream>>>(play, T, F, d);

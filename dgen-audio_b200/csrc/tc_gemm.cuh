@@ -387,6 +387,10 @@ struct KK {
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, int src_bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
 }
+// one float; src_bytes 0 = zero fill.  For operands whose rows are not 16-byte aligned (K not a multiple of 4).
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void *src, int src_bytes) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
 
 // K-major, 128-byte swizzle: LBO unused (1), SBO = 1024 bytes between 8-row groups, layout type 2 at [61,64)
 // (64-byte swizzle: SBO = 512 bytes, layout type 4)
@@ -415,7 +419,8 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
-template <int EPI, int BK, bool SW, int BN = TBN>
+// A4: the operands' rows are only 4-byte aligned (K % 4 != 0): every 16-byte unit is fetched as four 4-byte copies.
+template <int EPI, int BK, bool SW, int BN = TBN, bool A4 = false>
 __global__ void __launch_bounds__(KK_THREADS, (BK == 16 && BN == TBN) ? 2 : 1)
 tc_gemm_kk_kernel(const float *__restrict__ A, const float *__restrict__ B, const float *__restrict__ bias, int M, int N,
                   int K, int k_per_split, float *__restrict__ C, float *__restrict__ Ct, int32_t *status) {
@@ -487,6 +492,13 @@ tc_gemm_kk_kernel(const float *__restrict__ A, const float *__restrict__ B, cons
         for (int i = 0; i < UPT; ++i) {
           int bytes = (k_end - k_begin - k0 - kc4[i]) * 4;
           bytes = rowok[i] ? (bytes > 16 ? 16 : (bytes < 0 ? 0 : bytes)) : 0;
+          if (A4) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const bool in = 4 * e < bytes;
+              cp_async4(st + soff[i] + 4 * e, in ? src0[i] + k0 + e : A, in ? 4 : 0);
+            }
+          } else
           cp_async16(st + soff[i], bytes > 0 ? src0[i] + k0 : A, bytes);   // 0 bytes: zero fill, any valid address
         }
       }
