@@ -183,10 +183,20 @@ def measured_peaks():
         return {}
 
 
-def stage_rooflines(B, T, stage_ms, sm_mhz, sm_count, hbm_peak):
+def audible_fraction(f0):
+    """Share of the (control row, voice, partial) triples whose partial lies below Nyquist: fl(k f0) < sr / 2, the
+    reference's mask.  The render evaluates a sine only for those; the rest contribute an exact zero."""
+    K, nyq = CFG["K"], np.float32(CFG["sr"] * 0.5)
+    k = np.arange(1, K + 1, dtype=np.float32)
+    return float((np.asarray(f0, np.float32)[..., None] * k < nyq).mean())
+
+
+def stage_rooflines(B, T, stage_ms, sm_mhz, sm_count, hbm_peak, audible=1.0):
     """Per stage: the bound that applies to it and the fraction reached, the HBM figure beside it.
     Algorithmic work per launch (fp32 = 4 bytes; B voices, T frames, K partials, F control rows):
-      harmonic_render  one sine per (voice, frame, partial) on the special-function lanes; bytes 4 (B F (K+2) + B T)
+      harmonic_render  one sine per (voice, frame, partial BELOW NYQUIST) on the special-function lanes (`audible` =
+                       that share of the B T K partial-frames; the reference evaluates all K and multiplies the
+                       others by a zero mask); bytes 4 (B F (K+2) + B T)
       fir_noise        2 x taps multiply-adds per sample for the two control rows a sample is interpolated between
                        (4 taps flops per sample); bytes 4 (B T + B F nbands + B T): noise in, band magnitudes in, out
       mss_loss_fwd     one complex transform of N points per window carries both signals: 5 N log2 N flops per
@@ -206,7 +216,7 @@ def stage_rooflines(B, T, stage_ms, sm_mhz, sm_count, hbm_peak):
             continue
         hop = max(1, n // 4)
         fft_flops += 5.0 * n * np.log2(n) * ((T + hop - 1) // hop) * B
-    work = {"harmonic_render": ("sfu", B * T * K / 1e9, sfu_peak, "G sin/s"),
+    work = {"harmonic_render": ("sfu", B * T * K * audible / 1e9, sfu_peak, "G sin/s"),
             "fir_noise": ("fp32", 4.0 * taps * B * T / 1e12, fp32_peak, "TFLOP/s"),
             "mss_loss_fwd": ("fp32", fft_flops / 1e12, fp32_peak, "TFLOP/s"),
             "bands_to_taps": ("hbm", alg_bytes["bands_to_taps"] / 1e9, hbm_peak, "GB/s")}
@@ -218,6 +228,8 @@ def stage_rooflines(B, T, stage_ms, sm_mhz, sm_count, hbm_peak):
         out[name] = {"ms": ms, "bound": kind, "achieved": ach, "peak": peak, "unit": unit, "frac": ach / peak,
                      "hbm": {"algorithmic_bytes": alg_bytes[name], "achieved_gbs": gbs, "frac": gbs / hbm_peak}}
         bound_time_ms += amount / peak * 1e3
+    out["harmonic_render"]["audible_share_of_partials"] = audible
+    out["harmonic_render"]["masked_form_sines_per_s"] = B * T * K / (stage_ms["harmonic_render"] * 1e-3) / 1e9
     return out, alg_bytes, bound_time_ms
 
 
@@ -457,6 +469,7 @@ def run_ours(args, rank, world, local_rank):
     launches = ctx.launch_count() - launches0
     loss_val = float(fl.loss.cpu()[0])
     stage_ms = fl.stage_times(flush, max(3, min(args.steps, 10)))
+    audible = audible_fraction(fl.host["f0"])
 
     # end to end through the host-buffer entry point: pinned host inputs, H2D + D2H inside the timed region
     pin = lambda a: torch.from_numpy(np.ascontiguousarray(a)).pin_memory()
@@ -564,7 +577,7 @@ def run_ours(args, rank, world, local_rank):
         peaks = measured_peaks()
         hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
         sm_mhz = float((clocks or {}).get("sm_mhz") or (sustained or {}).get("clocks", {}).get("sm_mhz") or 1965.0)
-        stages, alg, bound_ms = stage_rooflines(B, T, stage_ms, sm_mhz, sm_count, hbm_peak)
+        stages, alg, bound_ms = stage_rooflines(B, T, stage_ms, sm_mhz, sm_count, hbm_peak, audible)
         dom = max(stage_ms, key=stage_ms.get)
         traffic, traffic_src = ncu_traffic(dom, B)
         rl = dict(stages[dom])
@@ -661,7 +674,8 @@ def run_target(ctx, args, flush, sm_count, local_rank):
     peaks = measured_peaks()
     hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
     sm_mhz = float(clocks.get("sm_mhz") or 1965.0)
-    stages, alg, bound_ms = stage_rooflines(Bt, fl.cfg["T"], stage_ms, sm_mhz, sm_count, hbm_peak)
+    stages, alg, bound_ms = stage_rooflines(Bt, fl.cfg["T"], stage_ms, sm_mhz, sm_count, hbm_peak,
+                                            audible_fraction(fl.host["f0"]))
     step_bytes = sum(alg.values())
     out = {"voices": Bt, "n_gpus": 1, "ms_per_step": ms, "value": Bt * fl.cfg["T"] / (ms * 1e-3), "unit": UNIT,
            "steps": steps, "l2": "L2 flushed between timed steps; inputs (0.5 GB) exceed L2 anyway",

@@ -554,7 +554,8 @@ __device__ __forceinline__ void grad_self(float2 z, float c_lin, float c_log2, i
 }
 
 // MINB: resident blocks per SM the registers are capped for (3: 168 registers, nothing spilled; 4: 128 registers,
-// a few spilled words in the middle sizes)
+// a few spilled words in the middle sizes; 5: 102 registers).  4 is the default: measured 0.315 / 0.498 / 3.53 ms
+// at 16 / 32 / 256 voices against 0.336 / 0.550 / 3.91 ms for 3.
 template <int N, int MINB>
 __global__ void __launch_bounds__(LOSS16_THREADS, MINB)
 mss_bwd16_kernel(const float *__restrict__ pred, const float *__restrict__ target, int B, int T, int hop, int H,
@@ -976,7 +977,7 @@ DGC_EXPORT int32_t dgc_mss_loss_bwd(dgc_ctx *ctx, const dgc_mss_params *p, const
     const bool wide = N >= 64 && !bwd_old;
     static const int bwd_minb = [] {
       const char *e = getenv("DGC_MSS_BWD_BLOCKS");
-      return e ? atoi(e) : 3;
+      return e ? atoi(e) : 4;
     }();
     switch (wide ? N : -N) {
 #define CASE(NN) case -NN: rc = launch_bwd<NN>(ctx, p, pred_dev, target_dev, hop, H, c_lin, c_log, accumulate, grad_pred_dev); break;
@@ -984,7 +985,8 @@ DGC_EXPORT int32_t dgc_mss_loss_bwd(dgc_ctx *ctx, const dgc_mss_params *p, const
 #undef CASE
 #define CASE(NN)                                                                                                          \
   case NN:                                                                                                                \
-    rc = bwd_minb == 4 ? launch_bwd16<NN, 4>(ctx, p, pred_dev, target_dev, hop, H, c_lin, c_log, accumulate, grad_pred_dev) \
+    rc = bwd_minb >= 5 ? launch_bwd16<NN, 5>(ctx, p, pred_dev, target_dev, hop, H, c_lin, c_log, accumulate, grad_pred_dev) \
+       : bwd_minb == 4 ? launch_bwd16<NN, 4>(ctx, p, pred_dev, target_dev, hop, H, c_lin, c_log, accumulate, grad_pred_dev) \
                        : launch_bwd16<NN, 3>(ctx, p, pred_dev, target_dev, hop, H, c_lin, c_log, accumulate, grad_pred_dev); \
     break;
       CASE(64) CASE(128) CASE(256) CASE(512) CASE(1024) CASE(2048)
