@@ -219,8 +219,9 @@ fir_noise_kernel(dgc_fir_params prm, const float2 *__restrict__ rowtab, const fl
 //     the signal window through registers, and reduce with shuffles (+9 % instructions).
 // Block = NTH threads x 8 frames.  Results are bit-identical from run to run (fixed summation orders; the list
 // order only decides which lane group computes an entry, not how).
-template <int NTH, int SPT>
-__global__ void __launch_bounds__(NTH, (SPT == 8 ? 768 : 512) / NTH)
+// RB: resident blocks per SM the registers are capped for (0: 768 threads for 8 frames per thread, 512 for 16).
+template <int NTH, int SPT, int RB = 0>
+__global__ void __launch_bounds__(NTH, RB ? RB : (SPT == 8 ? 768 : 512) / NTH)
 fir_noise8_kernel(dgc_fir_params prm, const float2 *__restrict__ rowtab, const float *__restrict__ noise,
                   const float *__restrict__ taps_tab, const float *__restrict__ ngain, float *__restrict__ audio,
                   int max_rows, int NTP, int32_t *status) {
@@ -229,9 +230,7 @@ fir_noise8_kernel(dgc_fir_params prm, const float2 *__restrict__ rowtab, const f
   const int B = prm.B, T = prm.T, F = prm.F, NT = prm.taps;
   const int b = blockIdx.y, t0 = blockIdx.x * TILE;
   const int t_last = min(T - 1, t0 + TILE - 1);
-  __shared__ int n_list;
-  __shared__ int list[NTH];            // straddling threads
-  __shared__ float d2buf[NTH][SPT];    // their third dot products, by list position
+  __shared__ int n_list;               // straddling threads: their list and third dot products live behind the tile
   if (threadIdx.x == 0) n_list = 0;
   // The frame at which the control clock wrapped (entry T of the row table; above every frame when it never does:
   // the playhead sweeps the control rows once, so there is at most one).  It concerns this tile only when it lies
@@ -250,6 +249,9 @@ fir_noise8_kernel(dgc_fir_params prm, const float2 *__restrict__ rowtab, const f
   float *xs = sh + (size_t)max_rows * NTP;   // [SPT][Q]: position m <-> frame t0 - (NT-1) + m, de-interleaved by m % SPT
   const int XN = TILE + NTP - 1 + SPT;       // zero-extended: the padding taps read beyond the tile
   const int Q = (XN + SPT - 1) / SPT + 1;
+  // every control-row boundary inside the tile makes one thread straddle: at most max_rows entries
+  float *d2buf = xs + (size_t)SPT * Q;                               // [max_rows][SPT], by list position
+  int *list = reinterpret_cast<int *>(d2buf + (size_t)max_rows * SPT);   // [max_rows]
   // Staging by asynchronous 4-byte copies (the rows of the tap table are not 16-byte aligned): every copy of the
   // tile is in flight before the first one is waited for, and nothing passes through registers.  One warp per
   // control row, lanes along the taps (coalesced, no index division); padding taps and frames outside the signal
@@ -298,9 +300,14 @@ fir_noise8_kernel(dgc_fir_params prm, const float2 *__restrict__ rowtab, const f
 #pragma unroll
   for (int u = 0; u < SPT; ++u) d0[u] = d1[u] = d2[u] = 0.0f;
   int my_entry = -1;
+  bool overflow = false;   // more straddling threads than the list holds (cannot happen while rows ascend): slow path
   if (straddle) {
     my_entry = atomicAdd(&n_list, 1);
-    list[my_entry] = threadIdx.x;
+    if (my_entry < max_rows) list[my_entry] = threadIdx.x;
+    else {
+      overflow = true;
+      my_entry = -1;
+    }
   }
   if (have) {
     // frame (nl+u), tap i reads xs position nl + u + i; W[w] = position nl + SPT g + w = xb[(w % SPT) * Q + g + w / SPT]
@@ -342,7 +349,7 @@ fir_noise8_kernel(dgc_fir_params prm, const float2 *__restrict__ rowtab, const f
     const int grp = threadIdx.x >> 3, l8 = threadIdx.x & 7;
     const unsigned gmask = 0xffu << (8 * (grp & 3));   // the 8 lanes of this group (trip counts differ between groups)
     const int per = (NTP + 7) / 8;
-    const int nent = n_list;
+    const int nent = min(n_list, max_rows);
     for (int e = grp; e < nent; e += GROUPS) {
       const int th = list[e];
       const int nls = th * SPT;
@@ -375,7 +382,7 @@ fir_noise8_kernel(dgc_fir_params prm, const float2 *__restrict__ rowtab, const f
         v += __shfl_xor_sync(gmask, v, 1);
         v += __shfl_xor_sync(gmask, v, 2);
         v += __shfl_xor_sync(gmask, v, 4);
-        if (l8 == 0) d2buf[e][u] = v;
+        if (l8 == 0) d2buf[e * SPT + u] = v;
       }
     }
   }
@@ -383,9 +390,9 @@ fir_noise8_kernel(dgc_fir_params prm, const float2 *__restrict__ rowtab, const f
   if (!have) return;
   if (my_entry >= 0) {
 #pragma unroll
-    for (int u = 0; u < SPT; ++u) d2[u] = d2buf[my_entry][u];
+    for (int u = 0; u < SPT; ++u) d2[u] = d2buf[my_entry * SPT + u];
   }
-  if (spread > 1 || spread < 0) {
+  if (spread > 1 || spread < 0 || overflow) {
     // the frames of this thread sit across the clock wrap: evaluate each frame against its own rows
 #pragma unroll
     for (int u = 0; u < SPT; ++u) {
@@ -406,13 +413,92 @@ fir_noise8_kernel(dgc_fir_params prm, const float2 *__restrict__ rowtab, const f
   for (int u = 0; u < SPT; ++u) {
     int n = t0 + nl + u;
     if (n >= T) break;
-    bool second = straddle && lo[u] != lo[0];
+    bool second = straddle && !overflow && lo[u] != lo[0];
     float a = second ? d1[u] : d0[u], c = second ? d2[u] : d1[u];
     float omf = 1.0f - fr[u];
     int l = lo[u] >= F ? lo[u] - F : lo[u], h = l + 1 >= F ? 0 : l + 1;
     float ng = fmaf(fr[u], ngain[(size_t)h * B + b], omf * ngain[(size_t)l * B + b]);
     float y = fmaf(fr[u], c, omf * a) * ng * prm.scale;
     dst[n] = prm.accumulate ? dst[n] + y : y;
+  }
+}
+
+// The band -> tap map as a plain single-precision tile kernel: C[M][N] = A[M][K] * W[N][K]^T with a SHORT reduction
+// (K = 65 bands) and a wide output (N = 257 taps), shaped for the case: both 128-row operand tiles sit WHOLE in
+// shared memory, k-major (As[k][m], Ws[k][n], rows of 132 floats), staged once by 4-byte asynchronous copies with
+// the lanes along m / n (conflict-free stores; the 260-byte global rows are re-read from L1 over the k values), one
+// barrier, then K rank-1 updates of an 8 x 8 register tile per thread with 16-byte shared loads: a warp covers
+// 64 x 32 outputs as 8 x 4 lanes, each lane two 4-wide halves 32 / 16 apart, so every load is one conflict-free
+// wavefront (4 per 64 multiply-adds).  Exact single-precision accumulation in k order.
+// A remainder tile of at most TMAP_NARROW columns (N = 257 = 2 x 128 + 1) is not worth a tile: its blocks compute
+// one dot product per (row, column) pair straight from global memory.
+constexpr int TMAP_LD = 132, TMAP_KMAX = 80, TMAP_NARROW = 16;
+
+__global__ void __launch_bounds__(256, 2)
+tap_map_tile_kernel(const float *__restrict__ A, const float *__restrict__ W, int M, int N, int K, float *__restrict__ C) {
+  extern __shared__ __align__(16) float tmap_sh[];
+  const int tid = threadIdx.x, m0 = blockIdx.y * 128, n0 = blockIdx.x * 128;
+  const int nw = min(128, N - n0);
+  if (nw <= TMAP_NARROW) {
+    for (int idx = tid; idx < 128 * nw; idx += 256) {
+      const int m = idx / nw, n = idx - m * nw;
+      if (m0 + m >= M) break;
+      const float *a = A + (size_t)(m0 + m) * K, *w = W + (size_t)(n0 + n) * K;
+      float acc = 0.0f;
+      for (int k = 0; k < K; ++k) acc = fmaf(a[k], w[k], acc);
+      C[(size_t)(m0 + m) * N + n0 + n] = acc;
+    }
+    return;
+  }
+  float *As = tmap_sh, *Ws = tmap_sh + K * TMAP_LD;
+  {
+    const uint32_t as = (uint32_t)__cvta_generic_to_shared(As), ws = (uint32_t)__cvta_generic_to_shared(Ws);
+    for (int idx = tid; idx < 128 * K; idx += 256) {
+      const int r = idx & 127, k = idx >> 7;
+      const bool ina = m0 + r < M, inw = n0 + r < N;
+      asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(as + 4u * (k * TMAP_LD + r)),
+                   "l"(ina ? A + (size_t)(m0 + r) * K + k : A), "r"(ina ? 4 : 0)
+                   : "memory");
+      asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(ws + 4u * (k * TMAP_LD + r)),
+                   "l"(inw ? W + (size_t)(n0 + r) * K + k : W), "r"(inw ? 4 : 0)
+                   : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+  }
+  __syncthreads();
+  const int warp = tid >> 5, lane = tid & 31;
+  const int wm = (warp >> 2) * 64, wn = (warp & 3) * 32;      // 2 x 4 warps of 64 x 32 outputs
+  const int ly = lane >> 2, lx = lane & 3;                     // 8 x 4 lanes
+  const int ma = wm + ly * 4, na = wn + lx * 4;                // halves at ma, ma + 32 and na, na + 16
+  float acc[8][8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[i][j] = 0.0f;
+#pragma unroll 4
+  for (int k = 0; k < K; ++k) {
+    const float4 a0 = *reinterpret_cast<const float4 *>(As + k * TMAP_LD + ma);
+    const float4 a1 = *reinterpret_cast<const float4 *>(As + k * TMAP_LD + ma + 32);
+    const float4 b0 = *reinterpret_cast<const float4 *>(Ws + k * TMAP_LD + na);
+    const float4 b1 = *reinterpret_cast<const float4 *>(Ws + k * TMAP_LD + na + 16);
+    const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+    const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int gm = m0 + ma + (i & 3) + (i >> 2) * 32;
+    if (gm >= M) continue;
+    float *row = C + (size_t)gm * N + n0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int n = na + (j & 3) + (j >> 2) * 16;
+      if (n < nw) row[n] = acc[i][j];
+    }
   }
 }
 
@@ -510,7 +596,7 @@ DGC_EXPORT int32_t dgc_fir_noise(dgc_ctx *ctx, const dgc_fir_params *p, const fl
       const int tile = nth * spt;
       const int max_rows = (int)(step * tile) + 5;
       const int XN = tile + NTP - 1 + spt, Q = (XN + spt - 1) / spt + 1;
-      const size_t smem = ((size_t)max_rows * NTP + (size_t)spt * Q) * sizeof(float);
+      const size_t smem = ((size_t)max_rows * NTP + (size_t)spt * Q + (size_t)max_rows * (spt + 1)) * sizeof(float);
       if (smem > 160 * 1024) return DGC_ERR_UNSUPPORTED;
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return dgc_fail(ctx, DGC_ERR_CUDA, "fir smem opt-in: %s", cudaGetErrorString(e));
@@ -520,7 +606,20 @@ DGC_EXPORT int32_t dgc_fir_noise(dgc_ctx *ctx, const dgc_fir_params *p, const fl
       return dgc_check_launch(ctx, "fir_noise8");
     };
     if (spt == 16) rc = fir_variant == 64 ? launch8(fir_noise8_kernel<64, 16>, 64) : launch8(fir_noise8_kernel<128, 16>, 128);
-    else rc = fir_variant == 256 ? launch8(fir_noise8_kernel<256, 8>, 256) : launch8(fir_noise8_kernel<128, 8>, 128);
+    else if (fir_variant == 256) rc = launch8(fir_noise8_kernel<256, 8>, 256);
+    else {
+      // A grid that fits 7 resident blocks per SM but not 6 (16 voices x 64000 frames: 1008 blocks on 148 SMs) runs
+      // as ONE wave on the 72-register build instead of a full wave and a nearly empty second one (the per-SM busy
+      // time of that launch was 58k to 120k cycles: half the SMs idle for half the kernel).  Larger grids keep the
+      // 80-register build, which is 3 % faster per block.
+      const int64_t nblocks = (int64_t)dgc_div_up(p->T, 128 * 8) * p->B;
+      if (nblocks > 6 * (int64_t)ctx->sm_count && nblocks <= 7 * (int64_t)ctx->sm_count) {
+        cudaFuncSetAttribute(fir_noise8_kernel<128, 8, 7>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                             cudaSharedmemCarveoutMaxShared);
+        rc = launch8(fir_noise8_kernel<128, 8, 7>, 128);
+      } else
+        rc = launch8(fir_noise8_kernel<128, 8>, 128);
+    }
   }
   if (rc == DGC_ERR_UNSUPPORTED && step * 8 < 0.98) {
     // 256-thread tiles amortise the staged control rows best (measured against 128 and 64 at the headline
@@ -546,7 +645,25 @@ DGC_EXPORT int32_t dgc_bands_to_taps(dgc_ctx *ctx, const float *bands_dev, const
   if (!ctx) return DGC_ERR_INVALID;
   DGC_REQUIRE(ctx, bands_dev && w_dev && taps_dev, "null pointer");
   DGC_REQUIRE(ctx, rows > 0 && nbands > 0 && taps > 0, "size out of range");
-  // large row counts go to the tensor-core matmul (taps = bands * W^T); the shared-memory kernel keeps small ones
+  // Large row counts run as a matmul.  Up to a few hundred tiles (the 16- and 32-voice steps) on the plain tile
+  // kernel: alone it is no faster than the tensor-core matmul (0.037 vs 0.035 ms at 16 voices), but the map runs
+  // BESIDE the harmonic branch on the other stream, and a kernel of plain 256-thread blocks shares the SMs with the
+  // render better than CTAs that hold 97 KB of shared memory and tensor memory each: the whole 16-voice step takes
+  // 0.198 ms with it against 0.209 ms.  Beyond that size every kernel fills the GPU by itself and the tensor-core
+  // matmul is faster (0.29 vs 0.38 ms at 256 voices).  DGC_TAP_MAP=tc|tile forces one.
+  static const int tmap_mode = [] {
+    const char *e = getenv("DGC_TAP_MAP");
+    return !e ? 0 : strcmp(e, "tc") == 0 ? 1 : strcmp(e, "tile") == 0 ? 2 : 0;
+  }();
+  const bool tmap_tile = tmap_mode == 2 || (tmap_mode == 0 && (int64_t)dgc_div_up(rows, 128) * dgc_div_up(taps, 128) <= 1024);
+  if ((double)rows * nbands * taps >= (double)(1 << 24) && nbands <= TMAP_KMAX && tmap_tile) {
+    const size_t smem = (size_t)2 * nbands * TMAP_LD * sizeof(float);
+    DGC_CUDA(ctx, cudaFuncSetAttribute(tap_map_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    tap_map_tile_kernel<<<dim3(dgc_div_up(taps, 128), dgc_div_up(rows, 128)), 256, smem, ctx->stream>>>(
+        bands_dev, w_dev, rows, taps, nbands, taps_dev);
+    DGC_LAUNCHED(ctx, "tap_map_tile");
+    return DGC_OK;
+  }
   if ((double)rows * nbands * taps >= (double)(1 << 24)) {
     // (65 bands: rows of 260 bytes are not 16-byte aligned; the matmul then fetches its operands with 4-byte
     // asynchronous copies instead of 16-byte ones, which is cheaper than a padding pass over the bands)

@@ -688,7 +688,7 @@ template <bool VEC>
 __global__ void __launch_bounds__(128)
 harmonic_render_frame_kernel(dgc_harmonic_params prm, const float2 *__restrict__ rowtab, const float *__restrict__ env,
                              const float *__restrict__ amps, const unsigned long long *__restrict__ fund,
-                             const int2 *__restrict__ trk, float *__restrict__ audio) {
+                             const int2 *__restrict__ trk, float2 *__restrict__ sums, float *__restrict__ audio) {
   constexpr float THREE_PI = 9.42477796076938f;
   const int B = prm.B, T = prm.T, K = prm.K, F = prm.F;
   const int C = (T + CH - 1) / CH;
@@ -739,7 +739,10 @@ harmonic_render_frame_kernel(dgc_harmonic_params prm, const float2 *__restrict__
   }
   for (; k < count; ++k) partial(__ldg(rl + k), __ldg(rh + k));
   // sin(2 pi p) = -sin(2 pi p - pi)
-  const float val = -s1 / (s2 + 1e-8f) * env[(size_t)b * T + n];
+  const float inv = 1.0f / (s2 + 1e-8f);
+  const float ratio = -s1 * inv;
+  if (sums) sums[(size_t)b * T + n] = make_float2(ratio, inv);   // for the backward: it then reduces nothing per frame
+  const float val = ratio * env[(size_t)b * T + n];
   float *dst = audio + (size_t)b * T + n;
   *dst = prm.accumulate ? *dst + val : val;
 }
@@ -784,15 +787,16 @@ void launch_render(dgc_ctx *ctx, const dgc_harmonic_params &p, const float *play
 
 template <int LPC, int P, int MODE>
 void launch_render_q(dgc_ctx *ctx, const dgc_harmonic_params &p, const float2 *rowtab, const dgc_harmonic_extra &x,
-                     const float *amps, const float *g_audio, float *out) {
+                     const float *amps, const float *g_audio, float *out, bool keep_sums = false) {
   int C = (p.T + CH - 1) / CH;
   constexpr int G = 128 / LPC;
   dim3 grid(dgc_div_up(C, G), p.B);
   if (MODE == 0 && x.fund && x.trk) {
     const dim3 fgrid(dgc_div_up(p.T, 128), p.B);
     const bool vec = (p.K & 3) == 0 && (((uintptr_t)amps) & 15) == 0;
-    if (vec) harmonic_render_frame_kernel<true><<<fgrid, 128, 0, ctx->stream>>>(p, rowtab, x.env, amps, x.fund, x.trk, out);
-    else harmonic_render_frame_kernel<false><<<fgrid, 128, 0, ctx->stream>>>(p, rowtab, x.env, amps, x.fund, x.trk, out);
+    float2 *keep = keep_sums ? x.sums : nullptr;
+    if (vec) harmonic_render_frame_kernel<true><<<fgrid, 128, 0, ctx->stream>>>(p, rowtab, x.env, amps, x.fund, x.trk, keep, out);
+    else harmonic_render_frame_kernel<false><<<fgrid, 128, 0, ctx->stream>>>(p, rowtab, x.env, amps, x.fund, x.trk, keep, out);
   } else
     harmonic_render_q_kernel<LPC, P, MODE><<<grid, 128, 0, ctx->stream>>>(p, 1.0f / p.sample_rate, rowtab, x.f0t, x.env,
                                                                            amps, x.anchors_q, x.fund, g_audio, out);
@@ -972,9 +976,10 @@ DGC_EXPORT uint64_t dgc_harmonic_scratch_floats(const dgc_harmonic_params *p) {
   // f0 track [B][T] (rounded up to 4), anchors [B][C][K], chunk sums as 64-bit words (at least the 2 x [B][C]
   // words of the FUNDAMENTAL mode), output envelope [B][T], anchors as Q0.32 words
   const uint64_t sum_words = lanes > 2 * (uint64_t)p->B * C ? lanes : 2 * (uint64_t)p->B * C;
-  // (+ the per-frame (increment, Nyquist count) pairs of the FUNDAMENTAL mode, [B][T] int2)
+  // (+ the per-frame (phase advance, Nyquist count) pairs of the FUNDAMENTAL mode, [B][T] int2, and the per-frame
+  // (normalised sum, reciprocal amplitude sum) pairs the forward leaves for its backward, [B][T] float2)
   return 2 * (((uint64_t)p->B * p->T + 3) & ~3ull) + lanes + 2 * sum_words + lanes + 16 +
-         2 * (((uint64_t)p->B * p->T + 3) & ~3ull);
+         4 * (((uint64_t)p->B * p->T + 3) & ~3ull);
 }
 
 int32_t dgc_harmonic_prepare(dgc_ctx *ctx, const dgc_harmonic_params *p, const float *f0_dev, float *scratch,
@@ -1035,6 +1040,8 @@ int32_t dgc_harmonic_prepare(dgc_ctx *ctx, const dgc_harmonic_params *p, const f
     extra->anchors_q = p->phase_mode == DGC_PHASE_SCAN ? anchors_q : nullptr;
     extra->fund = p->phase_mode == DGC_PHASE_FUNDAMENTAL ? fund_prefix : nullptr;
     extra->trk = p->phase_mode == DGC_PHASE_FUNDAMENTAL ? trk : nullptr;
+    extra->sums = p->phase_mode == DGC_PHASE_FUNDAMENTAL
+                      ? reinterpret_cast<float2 *>(trk + (((uint64_t)B * T + 3) & ~3ull)) : nullptr;
   }
   *play_out = play;
   *anchors_out = anchors;
@@ -1057,7 +1064,8 @@ DGC_EXPORT int32_t dgc_harmonic_render(dgc_ctx *ctx, const dgc_harmonic_params *
     DGC_REQUIRE(ctx, extra.env, "internal: the fixed-point render needs the envelope track");
     const float2 *rowtab = dgc_ctx_row_table(ctx, p->F, p->T);
     if (!rowtab) return DGC_ERR_CUDA;
-#define RENDERQ(LPC, P) launch_render_q<LPC, P, 0>(ctx, *p, rowtab, extra, amps_dev, nullptr, audio_dev)
+    // a caller that hands in the scratch keeps it for the backward: leave the per-frame sums there
+#define RENDERQ(LPC, P) launch_render_q<LPC, P, 0>(ctx, *p, rowtab, extra, amps_dev, nullptr, audio_dev, scratch_dev != nullptr)
     DGC_PICK_GROUP(K, RENDERQ);
 #undef RENDERQ
   } else {

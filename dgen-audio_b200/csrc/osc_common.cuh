@@ -74,8 +74,14 @@ struct dgc_harmonic_extra {
   const uint32_t *anchors_q = nullptr; // [B][C][K] (SCAN mode only) or nullptr
   const unsigned long long *fund = nullptr;  // [B][C] running sum of f0 / sr at every chunk start, Q0.64
                                              // (FUNDAMENTAL mode only): partial k starts chunk c at k * fund[b][c]
-  const int2 *trk = nullptr;                 // [B][T] (FUNDAMENTAL mode only): x = the fundamental's phase increment in
-                                             // Q0.32, y = number of partials below Nyquist at that frame
+  const int2 *trk = nullptr;                 // [B][T] (FUNDAMENTAL mode only): x = the fundamental's phase advance from
+                                             // the start of the frame's chunk in Q0.32, y = number of partials below
+                                             // Nyquist at that frame
+  float2 *sums = nullptr;                    // [B][T] (FUNDAMENTAL mode only): room for what the render divides per
+                                             // frame, x = sum_k a_k sin(2 pi phi_k) / (sum_k a_k + eps), y = 1 / (sum_k
+                                             // a_k + eps).  Written by a forward call that was given the scratch by
+                                             // its caller (who keeps it for the backward); read by the backward that
+                                             // is told the scratch is the forward's.
 };
 int32_t dgc_harmonic_prepare(dgc_ctx *ctx, const dgc_harmonic_params *p, const float *f0_dev, float *scratch,
                              const float **play_out, const float **anchors_out, const float *uv_dev = nullptr,

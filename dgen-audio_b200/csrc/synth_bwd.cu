@@ -294,13 +294,17 @@ __device__ __forceinline__ uint32_t inc_q32_bwd(float f0v, float sr, float rsr) 
 // number of partials below Nyquist are read per frame from the forward's track; the phase of partial k is
 // anchor_k + k * phi with phi that advance, so no per-partial state advances and both loops over this lane's partials end at the
 // last audible one (the partials at or above Nyquist contribute an exact zero and are not visited).
-template <int LPC, int P, bool TRK>
+// SUMS (with TRK): the forward left, per frame, the normalised sum and the reciprocal of the amplitude sum; the
+// group then reduces nothing over its lanes -- per audible partial and frame the phase, the sine and the two
+// gradient accumulates remain.
+template <int LPC, int P, bool TRK, bool SUMS>
 __global__ void __launch_bounds__(128)
 harmonic_bwd_q_kernel(dgc_harmonic_params prm, float rsr, const float2 *__restrict__ rowtab,
                       const int *__restrict__ ranges, const float *__restrict__ f0t, const float *__restrict__ env,
                       const float *__restrict__ amps, const uint32_t *__restrict__ anchors_q,
                       const unsigned long long *__restrict__ fund, const int2 *__restrict__ trk,
-                      const float *__restrict__ g_audio, float *__restrict__ part_lo, float *__restrict__ part_hi) {
+                      const float2 *__restrict__ sums, const float *__restrict__ g_audio, float *__restrict__ part_lo,
+                      float *__restrict__ part_hi) {
   constexpr int G = 128 / LPC;
   constexpr int LOG_LPC = LPC == 8 ? 3 : LPC == 16 ? 4 : 5;
   constexpr float THREE_PI = 9.42477796076938f;
@@ -375,10 +379,27 @@ harmonic_bwd_q_kernel(dgc_harmonic_params prm, float rsr, const float2 *__restri
         const int2 tk = tkp[n];
         phi = (uint32_t)tk.x;   // the fundamental's phase advance from the chunk's first frame, from the forward's track
         const int ilim = live ? max(tk.y - j + LPC - 1, 0) >> LOG_LPC : 0;   // partial j + LPC i + 1 <= count  <=>  i < ilim
-        float sn[P];
-        float s1v = 0.0f, s2v = 0.0f;
         uint32_t w = (uint32_t)(j + 1) * phi;          // k * phi as a running sum over this lane's partials
         const uint32_t r = phi << LOG_LPC;
+        if (SUMS) {
+          if (live) {
+            const float2 sm = sums[(size_t)b * T + n];   // (sum a sin / (sum a + eps), 1 / (sum a + eps)) of the forward
+            const float c = g[n] * envp[n] * sm.y;
+            const float cl = c * omf, chh = c * fr;
+#pragma unroll
+            for (int i = 0; i < P; ++i) {
+              if (i >= ilim) break;
+              const float ph1 = __uint_as_float(__funnelshift_r(q[i] + w, 0x7Fu, 9));
+              w += r;
+              const float d = -__sinf(fmaf(ph1, TWO_PI_F, -THREE_PI)) - sm.x;   // sin(2 pi p) - normalised sum
+              pl[i] = fmaf(cl, d, pl[i]);
+              phh[i] = fmaf(chh, d, phh[i]);
+            }
+          }
+          continue;
+        }
+        float sn[P];
+        float s1v = 0.0f, s2v = 0.0f;
 #pragma unroll
         for (int i = 0; i < P; ++i) {
           if (i >= ilim) break;
@@ -463,14 +484,19 @@ harmonic_bwd_q_kernel(dgc_harmonic_params prm, float rsr, const float2 *__restri
 
 template <int LPC, int P>
 void launch_hbwd_q(dgc_ctx *ctx, const dgc_harmonic_params &p, const float2 *rowtab, const int *ranges,
-                   const dgc_harmonic_extra &x, const float *amps, const float *g_audio, float *pl, float *ph) {
+                   const dgc_harmonic_extra &x, const float *amps, const float *g_audio, float *pl, float *ph,
+                   bool have_sums) {
   constexpr int G = 128 / LPC;
-  if (x.fund && x.trk)
-    harmonic_bwd_q_kernel<LPC, P, true><<<dim3(dgc_div_up(p.F, G), p.B), 128, 0, ctx->stream>>>(
-        p, 1.0f / p.sample_rate, rowtab, ranges, x.f0t, x.env, amps, x.anchors_q, x.fund, x.trk, g_audio, pl, ph);
+  const dim3 grid(dgc_div_up(p.F, G), p.B);
+  if (x.fund && x.trk && have_sums && x.sums)
+    harmonic_bwd_q_kernel<LPC, P, true, true><<<grid, 128, 0, ctx->stream>>>(
+        p, 1.0f / p.sample_rate, rowtab, ranges, x.f0t, x.env, amps, x.anchors_q, x.fund, x.trk, x.sums, g_audio, pl, ph);
+  else if (x.fund && x.trk)
+    harmonic_bwd_q_kernel<LPC, P, true, false><<<grid, 128, 0, ctx->stream>>>(
+        p, 1.0f / p.sample_rate, rowtab, ranges, x.f0t, x.env, amps, x.anchors_q, x.fund, x.trk, nullptr, g_audio, pl, ph);
   else
-    harmonic_bwd_q_kernel<LPC, P, false><<<dim3(dgc_div_up(p.F, G), p.B), 128, 0, ctx->stream>>>(
-        p, 1.0f / p.sample_rate, rowtab, ranges, x.f0t, x.env, amps, x.anchors_q, x.fund, x.trk, g_audio, pl, ph);
+    harmonic_bwd_q_kernel<LPC, P, false, false><<<grid, 128, 0, ctx->stream>>>(
+        p, 1.0f / p.sample_rate, rowtab, ranges, x.f0t, x.env, amps, x.anchors_q, x.fund, x.trk, nullptr, g_audio, pl, ph);
 }
 
 template <int LPC, int P>
@@ -559,7 +585,7 @@ static int32_t harmonic_render_bwd_impl(dgc_ctx *ctx, const dgc_harmonic_params 
   if (fixed_point && !rowtab) return DGC_ERR_CUDA;
 #define HBWD(LPC, P)                                                                                                  \
   do {                                                                                                                \
-    if (fixed_point) launch_hbwd_q<LPC, P>(ctx, *p, rowtab, ranges, extra, amps_dev, g_audio_dev, pl, ph);            \
+    if (fixed_point) launch_hbwd_q<LPC, P>(ctx, *p, rowtab, ranges, extra, amps_dev, g_audio_dev, pl, ph, prepared);  \
     else launch_hbwd<LPC, P>(ctx, *p, play, ranges, f0_dev, uv_dev, amps_dev, gain_dev, anchors, g_audio_dev, pl, ph); \
   } while (0)
   if (K <= 8) HBWD(8, 1);

@@ -190,7 +190,9 @@ int32_t dgc_harmonic_render_bwd(dgc_ctx *ctx, const dgc_harmonic_params *p, cons
                                 float *scratch_dev, float *g_amps_dev);
 /* The same, for a caller that has just rendered the forward with dgc_harmonic_render on the same p, f0, uv and
  * gain and passed it scratch_dev (sized with dgc_harmonic_bwd_scratch_floats): the per-sample tracks and
- * phase anchors the forward left in that scratch are used as they are instead of being computed again.
+ * phase anchors the forward left in that scratch are used as they are instead of being computed again; in
+ * DGC_PHASE_FUNDAMENTAL mode so are the two per-frame sums the forward divided by (a forward call that is given a
+ * scratch leaves them there), and amps_dev is then not read.  The amplitudes must be the forward's.
  * The caller guarantees that the scratch was not written in between.  No reference counterpart (the
  * reference recomputes the forward inside its backward kernels). */
 int32_t dgc_harmonic_render_bwd_prepared(dgc_ctx *ctx, const dgc_harmonic_params *p, const float *f0_dev,

@@ -69,6 +69,27 @@ def _render_both(ctx, d, mode, noise=True):
     return audio.cpu().numpy(), want
 
 
+@pytest.mark.parametrize("F,B,NB,NT", [(500, 40, 65, 257), (333, 61, 65, 257), (211, 33, 33, 129), (130, 9, 80, 400),
+                                       (700, 3, 65, 130)])
+def test_band_to_tap_map_at_scale_against_a_double_precision_product(ctx, F, B, NB, NT):
+    """From 2^24 multiply-adds on the map runs on the short-reduction tile kernel: row counts that are no multiple
+    of the 128-row tile, tap counts with a one-column remainder tile (257 = 2 x 128 + 1), a two-column one (130) and
+    a wide ragged one (400), band counts up to the shared-memory limit of the kernel (80).  Single-precision
+    accumulation in band order: within a few ulps of the double-precision product."""
+    assert F * B * NB * NT >= 1 << 24
+    rng = np.random.default_rng(F)
+    bands = rng.uniform(0, 1, (F, B, NB)).astype(f32)
+    W = rng.standard_normal((NT, NB)).astype(f32)
+    want = bands.reshape(F * B, NB).astype(np.float64) @ W.astype(np.float64).T
+    got = ctx.bands_to_taps(dev(bands), dev(W)).cpu().numpy().reshape(F * B, NT)
+    scale = np.abs(want).max()
+    assert np.abs(got - want).max() < 2e-6 * scale
+    # the matrix of the synthetic workload as well (windowed frequency sampling)
+    d = wl.harmonic_noise_inputs(5, B=B, T=1024, K=4, F=F, nbands=NB, taps=NT)
+    got = ctx.bands_to_taps(dev(d["bands"]), dev(d["W"])).cpu().numpy()
+    assert np.abs(got - wl.taps_from_bands(d)).max() < 1e-5
+
+
 @pytest.mark.parametrize("shape", [dict(B=2, T=4096, K=100, F=64), dict(B=3, T=5000, K=7, F=33),
                                    dict(B=1, T=1000, K=1, F=2), dict(B=2, T=2048, K=130, F=40),
                                    dict(B=1, T=640, K=300, F=11)])

@@ -43,6 +43,25 @@ def test_harmonic_render_backward(ctx, shape):
     got = ctx.harmonic_render_bwd(dev(d["f0"]), dev(d["uv"]), dev(d["amps"]), dev(d["gain"]), dev(g), d["T"], d["sr"],
                                   phase_mode=dgen_b200.PHASE_FUNDAMENTAL)
     assert rel_err(got.cpu().numpy(), amps.grad.numpy()) < 1e-3
+    # and the form a training step uses: the forward is handed the scratch, leaves its per-frame sums there, and the
+    # backward that is told so reads them instead of reducing over its lanes -- the same gradient
+    import ctypes as C
+    B, T, K, F = d["B"], d["T"], d["K"], d["F"]
+    hp = dgen_b200.HarmonicParams(B, T, K, F, d["sr"], 1.0, dgen_b200.PHASE_FUNDAMENTAL, 0)
+    scratch = torch.empty(int(ctx.lib.dgc_harmonic_bwd_scratch_floats(C.byref(hp))), device="cuda")
+    D = {k: dev(d[k]) for k in ("f0", "uv", "amps", "gain")}
+    audio = ctx.harmonic_render(D["f0"], D["uv"], D["amps"], D["gain"], T, d["sr"],
+                                phase_mode=dgen_b200.PHASE_FUNDAMENTAL, scratch=scratch)
+    plain = ctx.harmonic_render(D["f0"], D["uv"], D["amps"], D["gain"], T, d["sr"], phase_mode=dgen_b200.PHASE_FUNDAMENTAL)
+    assert torch.equal(audio, plain)                      # keeping the sums does not change the audio
+    gp = torch.empty(F, B, K, device="cuda")
+    gd = dev(g)
+    ctx.check(ctx.lib.dgc_harmonic_render_bwd_prepared(ctx.h, C.byref(hp), D["f0"].data_ptr(), D["uv"].data_ptr(),
+                                                       D["amps"].data_ptr(), D["gain"].data_ptr(), gd.data_ptr(),
+                                                       scratch.data_ptr(), gp.data_ptr()))
+    ctx.sync()
+    assert rel_err(gp.cpu().numpy(), amps.grad.numpy()) < 1e-3
+    assert rel_err(gp.cpu().numpy(), got.cpu().numpy()) < 2e-5
 
 
 @pytest.mark.parametrize("B,T,F,NT", [(2, 3000, 50, 257), (1, 1000, 5, 17), (2, 2049, 300, 64)])
