@@ -231,7 +231,17 @@ fir_noise8_kernel(dgc_fir_params prm, const float2 *__restrict__ rowtab, const f
   const int b = blockIdx.y, t0 = blockIdx.x * TILE;
   const int t_last = min(T - 1, t0 + TILE - 1);
   __shared__ int n_list;               // straddling threads: their list and third dot products live behind the tile
-  if (threadIdx.x == 0) n_list = 0;
+  // Threads whose frames sit across the clock wrap (the row numbers jump there: each frame has its own pair of
+  // rows).  At most one per tile while the playhead sweeps the rows once; the whole block evaluates them together
+  // after the main loop -- left to the thread itself, those 8 x 2 x taps dependent multiply-adds keep one block
+  // (and the SM that hosts it) busy for as long again as the rest of the tile.
+  constexpr int IRR_MAX = 4, PARTS = NTH / SPT;
+  __shared__ int n_irr, irr_list[IRR_MAX];
+  __shared__ float irr_buf[IRR_MAX][SPT][2];
+  if (threadIdx.x == 0) {
+    n_list = 0;
+    n_irr = 0;
+  }
   // The frame at which the control clock wrapped (entry T of the row table; above every frame when it never does:
   // the playhead sweeps the control rows once, so there is at most one).  It concerns this tile only when it lies
   // strictly inside: the rows behind it are then numbered F, F + 1, .. so that the tile's rows stay ascending.
@@ -308,6 +318,11 @@ fir_noise8_kernel(dgc_fir_params prm, const float2 *__restrict__ rowtab, const f
       overflow = true;
       my_entry = -1;
     }
+  }
+  int my_irr = -1;
+  if (have && (spread > 1 || spread < 0 || overflow)) {
+    my_irr = atomicAdd(&n_irr, 1);
+    if (my_irr < IRR_MAX) irr_list[my_irr] = threadIdx.x;
   }
   if (have) {
     // frame (nl+u), tap i reads xs position nl + u + i; W[w] = position nl + SPT g + w = xb[(w % SPT) * Q + g + w / SPT]
@@ -386,14 +401,48 @@ fir_noise8_kernel(dgc_fir_params prm, const float2 *__restrict__ rowtab, const f
       }
     }
   }
+  // irregular threads: thread (u, part) of the block takes frame u of the entry and every PARTS-th tap
+  {
+    const int nirr = min(n_irr, IRR_MAX);
+    const int u = threadIdx.x / PARTS, part = threadIdx.x % PARTS;
+    for (int e = 0; e < nirr; ++e) {
+      const int nls = irr_list[e] * SPT;
+      const int n = min(t0 + nls + u, T - 1);
+      int lo_u = __float_as_int(rowtab[n].x);
+      if (n >= wrap) lo_u += F;
+      const float *pa = rows + (size_t)(lo_u - rmin) * NTP, *pb = pa + NTP;
+      float sa = 0.0f, sb = 0.0f;
+      for (int i = part; i < NT; i += PARTS) {
+        const int m = nls + u + i;
+        const float xv = xs[(m % SPT) * Q + m / SPT];
+        sa = fmaf(xv, pa[i], sa);
+        sb = fmaf(xv, pb[i], sb);
+      }
+#pragma unroll
+      for (int off = PARTS / 2; off > 0; off >>= 1) {
+        sa += __shfl_xor_sync(0xffffffffu, sa, off);
+        sb += __shfl_xor_sync(0xffffffffu, sb, off);
+      }
+      if (part == 0) {
+        irr_buf[e][u][0] = sa;
+        irr_buf[e][u][1] = sb;
+      }
+    }
+  }
   __syncthreads();
   if (!have) return;
   if (my_entry >= 0) {
 #pragma unroll
     for (int u = 0; u < SPT; ++u) d2[u] = d2buf[my_entry * SPT + u];
   }
-  if (spread > 1 || spread < 0 || overflow) {
-    // the frames of this thread sit across the clock wrap: evaluate each frame against its own rows
+  if (my_irr >= 0 && my_irr < IRR_MAX) {
+#pragma unroll
+    for (int u = 0; u < SPT; ++u) {
+      d0[u] = irr_buf[my_irr][u][0];
+      d1[u] = irr_buf[my_irr][u][1];
+    }
+  } else if (my_irr >= 0) {
+    // more irregular threads than the block-wide pass takes: evaluate each frame against its own rows here
 #pragma unroll
     for (int u = 0; u < SPT; ++u) {
       const float *pa = rows + (size_t)(lo[u] - rmin) * NTP, *pb = pa + NTP;
@@ -413,7 +462,7 @@ fir_noise8_kernel(dgc_fir_params prm, const float2 *__restrict__ rowtab, const f
   for (int u = 0; u < SPT; ++u) {
     int n = t0 + nl + u;
     if (n >= T) break;
-    bool second = straddle && !overflow && lo[u] != lo[0];
+    bool second = straddle && my_irr < 0 && lo[u] != lo[0];
     float a = second ? d1[u] : d0[u], c = second ? d2[u] : d1[u];
     float omf = 1.0f - fr[u];
     int l = lo[u] >= F ? lo[u] - F : lo[u], h = l + 1 >= F ? 0 : l + 1;
