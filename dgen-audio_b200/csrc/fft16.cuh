@@ -154,6 +154,32 @@ __device__ __forceinline__ void stage_middle(const float2 *in, float2 *out, int 
   }
 }
 
+// The middle stage IN PLACE: every thread first reads all sixteen of its inputs, the threads of the transform wait
+// for each other, then the butterflies run from the registers and their outputs go back into the same buffer.  One
+// more wait per transform, half the shared memory: the transforms of a block then leave room for more resident
+// blocks.
+template <int N, bool INV>
+__device__ __forceinline__ void stage_middle_inplace(float2 *buf, int tid, const float2 *__restrict__ tw) {
+  constexpr int R = Plan<N>::R2, PER = 16 / R, T = N / 16, Ns = Plan<N>::R1;
+  float2 v[PER][R];
+#pragma unroll
+  for (int q = 0; q < PER; ++q) {
+    const int j = tid + q * T;
+#pragma unroll
+    for (int t = 0; t < R; ++t) v[q][t] = buf[pad(j + t * (N / R))];
+  }
+  sync_transform<N>();
+#pragma unroll
+  for (int q = 0; q < PER; ++q) {
+    const int j = tid + q * T, k = j & (Ns - 1);
+    twiddle<R, INV>(v[q], tw, k * (N / (Ns * R)));
+    dftN<R, INV>(v[q]);
+    const int j0 = (j - k) * R + k;
+#pragma unroll
+    for (int t = 0; t < R; ++t) buf[pad(j0 + t * Ns)] = v[q][t];
+  }
+}
+
 // The two butterflies of pair p of the last stage that thread tid owns: (a, NBL - a), or (0, NBL / 2) for a == 0.
 template <int N>
 __device__ __forceinline__ void last_pair(int tid, int p, int &ja, int &jb) {
@@ -185,13 +211,15 @@ __device__ __forceinline__ void stage_last(const float2 *in, float2 (&z)[Geo<N>:
 
 // Whole forward or inverse transform: registers x[16] in (element tid + m N/16), registers z out (see stage_last).
 // bufa / bufb: padded(N) float2 each (bufb unused by the two-stage sizes); nobody may still read them on entry.
+// bufb == bufa selects the in-place middle stage (one buffer per transform).
 template <int N, bool INV>
 __device__ __forceinline__ void fft16(float2 (&x)[16], float2 (&z)[Geo<N>::PAIRS][2][Geo<N>::RL], float2 *bufa,
                                       float2 *bufb, int tid, const float2 *__restrict__ tw) {
   stage_first<N, INV>(x, bufa, tid);
   sync_transform<N>();
   if (Geo<N>::THREE) {
-    stage_middle<N, INV>(bufa, bufb, tid, tw);
+    if (bufb == bufa) stage_middle_inplace<N, INV>(bufa, tid, tw);
+    else stage_middle<N, INV>(bufa, bufb, tid, tw);
     sync_transform<N>();
     stage_last<N, INV>(bufb, z, tid, tw);
   } else {

@@ -191,7 +191,9 @@ __device__ __forceinline__ void mss_fwd16_body(float2 *sm, float *red, int bx, i
   const int t_base = h * hop - (N - 1);
   const float *x1 = pred + (size_t)b * T, *x2 = target + (size_t)b * T;
   const float *x1b = SUM2 ? pred_b + (size_t)b * T : nullptr;   // prediction given as a sum of two signals
-  float2 *bufa = sm + f * PN, *bufb = sm + (NF + f) * PN;
+  // one buffer per transform (in-place middle stage): 17 KB per block instead of 33, room for 8 resident blocks;
+  // the variant that stages the sample runs with the copy engine keeps the second buffer for them
+  float2 *bufa = sm + f * PN, *bufb = TMA ? sm + (NF + f) * PN : bufa;
   float2 x[16];
   if (TMA) {
     // The run of samples the block's NF windows cover, fetched once by the copy engine: boxes of SPAN_BOX floats
@@ -282,10 +284,10 @@ __device__ __forceinline__ void mss_fwd16_body(float2 *sm, float *red, int bx, i
   }
 }
 
-constexpr int FWD16_SMEM_BYTES = 2 * padded(2048) * (int)sizeof(float2);
+constexpr int FWD16_SMEM_BYTES = padded(2048) * (int)sizeof(float2);   // x 2 for the copy-engine variant
 
 template <bool SUM2, bool TMA>
-__global__ void __launch_bounds__(LOSS16_THREADS, 6)
+__global__ void __launch_bounds__(LOSS16_THREADS, TMA ? 6 : 8)
 mss_fwd16_kernel(const float *__restrict__ pred, const float *__restrict__ pred_b, const float *__restrict__ target,
                  int B, int T, const FwdDesc d, const __grid_constant__ CUtensorMap map_pred,
                  const __grid_constant__ CUtensorMap map_target, int32_t *status) {
@@ -922,7 +924,7 @@ int32_t dgc_mss_loss_fwd_sum(dgc_ctx *ctx, const dgc_mss_params *p, const float 
       mss_fwd16_kernel<true, false><<<blocks16, LOSS16_THREADS, FWD16_SMEM_BYTES, ctx->stream>>>(
           pred_dev, pred_b_dev, target_dev, p->B, p->T, fd16, mp, mt, ctx->status_dev);
     else if (tma)
-      mss_fwd16_kernel<false, true><<<blocks16, LOSS16_THREADS, FWD16_SMEM_BYTES, ctx->stream>>>(
+      mss_fwd16_kernel<false, true><<<blocks16, LOSS16_THREADS, 2 * FWD16_SMEM_BYTES, ctx->stream>>>(
           pred_dev, nullptr, target_dev, p->B, p->T, fd16, mp, mt, ctx->status_dev);
     else
       mss_fwd16_kernel<false, false><<<blocks16, LOSS16_THREADS, FWD16_SMEM_BYTES, ctx->stream>>>(
