@@ -5,6 +5,7 @@ tests cover), linearity, time-shift invariance by a whole number of hops, and a 
   biquad bank:       256 lanes x 32 voices x 262144 frames (8.6 GB of lane signals), forward and BPTT
   partitioned conv:  16 voices x 480000 frames, 96000-tap impulse response (94 partitions of 1024, N = 2048)
   oscillator bank -> one-pole -> FFT: 64 partials, 65536 frames (against the oracle directly, see test_gpu_linrec)
+  forward + loss:    256 voices x 64000 frames x 100 partials on one GPU, the throughput target's own configuration
 """
 import numpy as np
 import pytest
@@ -153,3 +154,53 @@ def test_onepole_long_signals(ctx):
         for b in (0, B // 2, B - 1):
             want = orc.onepole(x[b], a)
             assert np.abs(y[b] - want).max() <= 1e-4 * max(1.0, np.abs(want).max()), (B, T, b)
+
+
+def test_forward_loss_256_voices_against_16_voice_runs_and_the_oracle(ctx):
+    """The throughput target's configuration, 256 voices x 64000 frames through ONE composite call, checked by
+    properties and slices.  At this size the step takes other code paths than at 16 voices (the band -> tap map on
+    the tensor-core matmul instead of the tile kernel, the FIR after the render on one stream adding into its output
+    instead of beside it with a summing pass, the 80-register FIR build), so:
+      * voice independence: the audio of voices 32..47 and 240..255 inside the 256-voice step equals a 16-voice
+        step over those voices alone to single-precision accumulation differences (the 3xTF32 map);
+      * the loss is a mean over voices: the 256-voice loss equals the mean of the sixteen 16-voice losses;
+      * two voices of the 256-voice audio against the CPU oracle (the same bound as the 2-voice test);
+      * the same call twice gives bit-identical audio and loss."""
+    B, T, K, F, NB, NT, sr = 256, 64000, 100, 1000, 65, 257, 16000.0
+    d = wl.harmonic_noise_inputs(4242, B=B, T=T, K=K, F=F, sr=sr, nbands=NB, taps=NT)
+    rng = np.random.default_rng(9)
+    target = (rng.standard_normal((B, T)) * 0.1).astype(f32)
+
+    def step_for(b):
+        st = dgen_b200.HnStep()
+        st.harm = dgen_b200.HarmonicParams(b, T, K, F, sr, 1.0, dgen_b200.PHASE_FUNDAMENTAL, 0)
+        st.fir = dgen_b200.FirParams(b, T, F, NT, 0.12, 1)
+        st.mss = dgen_b200.mss_params(b, T)
+        st.nbands = NB
+        return st
+
+    def run(sl):
+        n = sl.stop - sl.start
+        args = [dev(d[k][:, sl]) for k in ("f0", "uv", "amps", "gain", "noise_gain", "bands")]
+        out = torch.empty(n, T, device="cuda")
+        loss, _ = ctx.hn_forward_loss(step_for(n), *args, dev(d["W"]), dev(d["noise"][sl]), dev(target[sl]), audio=out)
+        ctx.sync()
+        return out, float(loss.cpu()[0])
+
+    full, loss_full = run(slice(0, B))
+    again, loss_again = run(slice(0, B))
+    assert torch.equal(full, again) and loss_full == loss_again
+    losses = []
+    for c in range(B // 16):
+        sl = slice(16 * c, 16 * c + 16)
+        part, l = run(sl)
+        losses.append(l)
+        if c in (2, 15):
+            err = float((part - full[sl]).abs().max())
+            assert err < 5e-6, (c, err)
+    assert abs(np.mean(losses) - loss_full) < 1e-6 * abs(loss_full)
+    taps = wl.taps_from_bands({k: (v[:, 100:102] if k == "bands" else v) for k, v in d.items()})
+    want = orc.harmonic_noise_render(d["f0"][:, 100:102], d["uv"][:, 100:102], d["amps"][:, 100:102],
+                                     d["gain"][:, 100:102], d["noise_gain"][:, 100:102], taps, d["noise"][100:102], T, sr)
+    got = full[100:102].cpu().numpy()
+    assert np.abs(got - want).max() < 1e-4
