@@ -474,52 +474,58 @@ fir_noise8_kernel(dgc_fir_params prm, const float2 *__restrict__ rowtab, const f
 
 // The band -> tap map as a plain single-precision tile kernel: C[M][N] = A[M][K] * W[N][K]^T with a SHORT reduction
 // (K = 65 bands) and a wide output (N = 257 taps), shaped for the case: both 128-row operand tiles sit WHOLE in
-// shared memory, k-major (As[k][m], Ws[k][n], rows of 132 floats), staged once by 4-byte asynchronous copies with
-// the lanes along m / n (conflict-free stores; the 260-byte global rows are re-read from L1 over the k values), one
-// barrier, then K rank-1 updates of an 8 x 8 register tile per thread with 16-byte shared loads: a warp covers
-// 64 x 32 outputs as 8 x 4 lanes, each lane two 4-wide halves 32 / 16 apart, so every load is one conflict-free
-// wavefront (4 per 64 multiply-adds).  Exact single-precision accumulation in k order.
-// A remainder tile of at most TMAP_NARROW columns (N = 257 = 2 x 128 + 1) is not worth a tile: its blocks compute
-// one dot product per (row, column) pair straight from global memory.
-constexpr int TMAP_LD = 132, TMAP_KMAX = 80, TMAP_NARROW = 16;
+// shared memory, row-major as they lie in global memory with rows of K | 1 floats, staged once by 4-byte
+// asynchronous copies (a warp per row, lanes along k: coalesced), one barrier, then K rank-1 updates of an 8 x 8
+// register tile per thread: a warp covers 64 x 32 outputs as 8 x 4 lanes, so the 16 scalar loads per k are
+// broadcasts or conflict-free.  Exact single-precision accumulation in k order.
+// A remainder of at most TMAP_NARROW columns (N = 257 = 2 x 128 + 1) is computed by the last tile's block as dot
+// products: blocks of their own for it made the 16-voice grid 1.27 waves and the kernel twice as long.
+constexpr int TMAP_KMAX = 80, TMAP_NARROW = 16;
 
 __global__ void __launch_bounds__(256, 2)
 tap_map_tile_kernel(const float *__restrict__ A, const float *__restrict__ W, int M, int N, int K, float *__restrict__ C) {
   extern __shared__ __align__(16) float tmap_sh[];
   const int tid = threadIdx.x, m0 = blockIdx.y * 128, n0 = blockIdx.x * 128;
+  // columns of this tile; a remainder of at most TMAP_NARROW columns behind the last full tile (N = 257 = 2 x 128 + 1)
+  // is not worth blocks of its own: the last tile's block computes it as dot products after its main loop
   const int nw = min(128, N - n0);
-  if (nw <= TMAP_NARROW) {
-    for (int idx = tid; idx < 128 * nw; idx += 256) {
-      const int m = idx / nw, n = idx - m * nw;
-      if (m0 + m >= M) break;
-      const float *a = A + (size_t)(m0 + m) * K, *w = W + (size_t)(n0 + n) * K;
-      float acc = 0.0f;
-      for (int k = 0; k < K; ++k) acc = fmaf(a[k], w[k], acc);
-      C[(size_t)(m0 + m) * N + n0 + n] = acc;
-    }
-    return;
-  }
-  float *As = tmap_sh, *Ws = tmap_sh + K * TMAP_LD;
+  const int extra = (blockIdx.x == gridDim.x - 1) ? N - n0 - nw : 0;
+  // Both tiles row-major as they lie in memory, rows of KS = K | 1 floats (odd: a walk down a column touches every
+  // bank once).  Staged by 4-byte asynchronous copies, one warp per row with the lanes along k: coalesced global
+  // reads, consecutive shared-memory writes.
+  const int KS = K | 1;
+  float *As = tmap_sh, *Ws = tmap_sh + 128 * KS;
+  const int warp = tid >> 5, lane = tid & 31;
   {
     const uint32_t as = (uint32_t)__cvta_generic_to_shared(As), ws = (uint32_t)__cvta_generic_to_shared(Ws);
-    for (int idx = tid; idx < 128 * K; idx += 256) {
-      const int r = idx & 127, k = idx >> 7;
+    for (int r = warp; r < 128; r += 8) {
       const bool ina = m0 + r < M, inw = n0 + r < N;
-      asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(as + 4u * (k * TMAP_LD + r)),
-                   "l"(ina ? A + (size_t)(m0 + r) * K + k : A), "r"(ina ? 4 : 0)
-                   : "memory");
-      asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(ws + 4u * (k * TMAP_LD + r)),
-                   "l"(inw ? W + (size_t)(n0 + r) * K + k : W), "r"(inw ? 4 : 0)
-                   : "memory");
+      const float *ga = A + (size_t)(ina ? m0 + r : 0) * K, *gw = W + (size_t)(inw ? n0 + r : 0) * K;
+      for (int k = lane; k < K; k += 32) {
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(as + 4u * (r * KS + k)), "l"(ga + k),
+                     "r"(ina ? 4 : 0)
+                     : "memory");
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(ws + 4u * (r * KS + k)), "l"(gw + k),
+                     "r"(inw ? 4 : 0)
+                     : "memory");
+      }
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
     asm volatile("cp.async.wait_group 0;" ::: "memory");
   }
   __syncthreads();
-  const int warp = tid >> 5, lane = tid & 31;
   const int wm = (warp >> 2) * 64, wn = (warp & 3) * 32;      // 2 x 4 warps of 64 x 32 outputs
   const int ly = lane >> 2, lx = lane & 3;                     // 8 x 4 lanes
   const int ma = wm + ly * 4, na = wn + lx * 4;                // halves at ma, ma + 32 and na, na + 16
+  // row r of this thread's 8 x 8 register tile: ma + (i & 3) + 32 (i >> 2); column: na + (j & 3) + 16 (j >> 2).
+  // Per k: 8 + 8 scalar loads (lanes that share a row or a column read the same word: broadcast; the others sit
+  // in different banks) for 64 multiply-adds.
+  const float *ap[8], *bp[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    ap[i] = As + (ma + (i & 3) + (i >> 2) * 32) * KS;
+    bp[i] = Ws + (na + (i & 3) + (i >> 2) * 16) * KS;
+  }
   float acc[8][8];
 #pragma unroll
   for (int i = 0; i < 8; ++i)
@@ -527,12 +533,12 @@ tap_map_tile_kernel(const float *__restrict__ A, const float *__restrict__ W, in
     for (int j = 0; j < 8; ++j) acc[i][j] = 0.0f;
 #pragma unroll 4
   for (int k = 0; k < K; ++k) {
-    const float4 a0 = *reinterpret_cast<const float4 *>(As + k * TMAP_LD + ma);
-    const float4 a1 = *reinterpret_cast<const float4 *>(As + k * TMAP_LD + ma + 32);
-    const float4 b0 = *reinterpret_cast<const float4 *>(Ws + k * TMAP_LD + na);
-    const float4 b1 = *reinterpret_cast<const float4 *>(Ws + k * TMAP_LD + na + 16);
-    const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-    const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+    float a[8], b[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      a[i] = ap[i][k];
+      b[i] = bp[i][k];
+    }
 #pragma unroll
     for (int i = 0; i < 8; ++i)
 #pragma unroll
@@ -548,6 +554,15 @@ tap_map_tile_kernel(const float *__restrict__ A, const float *__restrict__ W, in
       const int n = na + (j & 3) + (j >> 2) * 16;
       if (n < nw) row[n] = acc[i][j];
     }
+  }
+  // the remainder columns: thread (row, column) pairs, the A row from shared memory, the W row from global memory
+  for (int idx = tid; idx < 128 * extra; idx += 256) {
+    const int m = idx % 128, c = idx / 128;
+    if (m0 + m >= M) continue;
+    const float *a = As + m * KS, *w = W + (size_t)(n0 + 128 + c) * K;
+    float sum = 0.0f;
+    for (int k = 0; k < K; ++k) sum = fmaf(a[k], __ldg(w + k), sum);
+    C[(size_t)(m0 + m) * N + n0 + 128 + c] = sum;
   }
 }
 
@@ -706,10 +721,12 @@ DGC_EXPORT int32_t dgc_bands_to_taps(dgc_ctx *ctx, const float *bands_dev, const
   }();
   const bool tmap_tile = tmap_mode == 2 || (tmap_mode == 0 && (int64_t)dgc_div_up(rows, 128) * dgc_div_up(taps, 128) <= 1024);
   if ((double)rows * nbands * taps >= (double)(1 << 24) && nbands <= TMAP_KMAX && tmap_tile) {
-    const size_t smem = (size_t)2 * nbands * TMAP_LD * sizeof(float);
+    const size_t smem = (size_t)2 * 128 * (nbands | 1) * sizeof(float);
     DGC_CUDA(ctx, cudaFuncSetAttribute(tap_map_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    tap_map_tile_kernel<<<dim3(dgc_div_up(taps, 128), dgc_div_up(rows, 128)), 256, smem, ctx->stream>>>(
-        bands_dev, w_dev, rows, taps, nbands, taps_dev);
+    const int rem = taps % 128;
+    const int ntx = (taps >= 128 && rem > 0 && rem <= TMAP_NARROW) ? taps / 128 : dgc_div_up(taps, 128);
+    tap_map_tile_kernel<<<dim3(ntx, dgc_div_up(rows, 128)), 256, smem, ctx->stream>>>(bands_dev, w_dev, rows, taps,
+                                                                                     nbands, taps_dev);
     DGC_LAUNCHED(ctx, "tap_map_tile");
     return DGC_OK;
   }
