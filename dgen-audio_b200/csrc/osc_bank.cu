@@ -701,6 +701,16 @@ harmonic_render_frame_kernel(dgc_harmonic_params prm, const float2 *__restrict__
   const unsigned long long step = fund[(size_t)b * C + n / CH] + ((unsigned long long)(uint32_t)tk.x << 32);
   const int count = min(tk.y, K);
   const float *rl = amps + ((size_t)lo * B + b) * K, *rh = amps + ((size_t)hi * B + b) * K;
+  // The two rows are used by 64 frames and then never again: every 128-byte line of them is a first touch from HBM
+  // for the warp that walks into it.  The lanes of the warp ask for the lines the audible partials span up front
+  // (lane l: line l of both rows), so the walk finds them on their way instead of stalling once per line.
+  {
+    const int l = threadIdx.x & 31, k0 = l * 32;
+    if (k0 < count) {
+      asm volatile("prefetch.global.L1 [%0];" ::"l"(rl + min(k0, K - 1)));
+      asm volatile("prefetch.global.L1 [%0];" ::"l"(rh + min(k0, K - 1)));
+    }
+  }
   // k * P for k = 1, plus 2^8 in the high word for good: dropping the low 9 bits below then rounds to nearest
   unsigned long long acc = step + (0x100ull << 32);
   float s1 = 0.0f, s2 = 0.0f;
