@@ -474,13 +474,16 @@ fir_noise8_kernel(dgc_fir_params prm, const float2 *__restrict__ rowtab, const f
 
 // The band -> tap map as a plain single-precision tile kernel: C[M][N] = A[M][K] * W[N][K]^T with a SHORT reduction
 // (K = 65 bands) and a wide output (N = 257 taps), shaped for the case: both 128-row operand tiles sit WHOLE in
-// shared memory, row-major as they lie in global memory with rows of K | 1 floats, staged once by 4-byte
-// asynchronous copies (a warp per row, lanes along k: coalesced), one barrier, then K rank-1 updates of an 8 x 8
-// register tile per thread: a warp covers 64 x 32 outputs as 8 x 4 lanes, so the 16 scalar loads per k are
-// broadcasts or conflict-free.  Exact single-precision accumulation in k order.
+// shared memory, row-major as they lie in global memory (rows of KS floats, KS % 8 == 4, zero beyond K), staged
+// once by 4-byte asynchronous copies (a warp per row, lanes along k: coalesced), one barrier, then the reduction
+// four k values at a time: a thread owns an 8 x 8 register tile of interleaved rows and columns, so that the
+// lanes of a warp read eight consecutive rows of A and four consecutive rows of W as conflict-free 16-byte
+// fragments along k (16 loads per 256 multiply-adds).  Exact single-precision accumulation in k order.
 // A remainder of at most TMAP_NARROW columns (N = 257 = 2 x 128 + 1) is computed by the last tile's block as dot
-// products: blocks of their own for it made the 16-voice grid 1.27 waves and the kernel twice as long.
+// products: blocks of their own for it made the 16-voice grid 1.27 waves.
 constexpr int TMAP_KMAX = 80, TMAP_NARROW = 16;
+// row length of the staged tiles: the smallest multiple of 4 at or above K that is 4 modulo 8
+__host__ __device__ constexpr int tmap_stride(int K) { return ((K + 3) & ~3) % 8 == 4 ? ((K + 3) & ~3) : ((K + 3) & ~3) + 4; }
 
 __global__ void __launch_bounds__(256, 2)
 tap_map_tile_kernel(const float *__restrict__ A, const float *__restrict__ W, int M, int N, int K, float *__restrict__ C) {
@@ -490,10 +493,10 @@ tap_map_tile_kernel(const float *__restrict__ A, const float *__restrict__ W, in
   // is not worth blocks of its own: the last tile's block computes it as dot products after its main loop
   const int nw = min(128, N - n0);
   const int extra = (blockIdx.x == gridDim.x - 1) ? N - n0 - nw : 0;
-  // Both tiles row-major as they lie in memory, rows of KS = K | 1 floats (odd: a walk down a column touches every
-  // bank once).  Staged by 4-byte asynchronous copies, one warp per row with the lanes along k: coalesced global
-  // reads, consecutive shared-memory writes.
-  const int KS = K | 1;
+  // Both tiles row-major as they lie in memory, rows of KS floats with KS % 8 == 4 (16-byte aligned rows whose
+  // starts fall into bank quads 4 apart), zero beyond K.  Staged by 4-byte asynchronous copies, one warp per row
+  // with the lanes along k: coalesced global reads, consecutive shared-memory writes.
+  const int KS = tmap_stride(K);
   float *As = tmap_sh, *Ws = tmap_sh + 128 * KS;
   const int warp = tid >> 5, lane = tid & 31;
   {
@@ -501,12 +504,13 @@ tap_map_tile_kernel(const float *__restrict__ A, const float *__restrict__ W, in
     for (int r = warp; r < 128; r += 8) {
       const bool ina = m0 + r < M, inw = n0 + r < N;
       const float *ga = A + (size_t)(ina ? m0 + r : 0) * K, *gw = W + (size_t)(inw ? n0 + r : 0) * K;
-      for (int k = lane; k < K; k += 32) {
-        asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(as + 4u * (r * KS + k)), "l"(ga + k),
-                     "r"(ina ? 4 : 0)
+      for (int k = lane; k < KS; k += 32) {
+        const bool ink = k < K;
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(as + 4u * (r * KS + k)),
+                     "l"(ink ? ga + k : ga), "r"(ina && ink ? 4 : 0)
                      : "memory");
-        asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(ws + 4u * (r * KS + k)), "l"(gw + k),
-                     "r"(inw ? 4 : 0)
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(ws + 4u * (r * KS + k)),
+                     "l"(ink ? gw + k : gw), "r"(inw && ink ? 4 : 0)
                      : "memory");
       }
     }
@@ -514,44 +518,43 @@ tap_map_tile_kernel(const float *__restrict__ A, const float *__restrict__ W, in
     asm volatile("cp.async.wait_group 0;" ::: "memory");
   }
   __syncthreads();
-  const int wm = (warp >> 2) * 64, wn = (warp & 3) * 32;      // 2 x 4 warps of 64 x 32 outputs
-  const int ly = lane >> 2, lx = lane & 3;                     // 8 x 4 lanes
-  const int ma = wm + ly * 4, na = wn + lx * 4;                // halves at ma, ma + 32 and na, na + 16
-  // row r of this thread's 8 x 8 register tile: ma + (i & 3) + 32 (i >> 2); column: na + (j & 3) + 16 (j >> 2).
-  // Per k: 8 + 8 scalar loads (lanes that share a row or a column read the same word: broadcast; the others sit
-  // in different banks) for 64 multiply-adds.
-  const float *ap[8], *bp[8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    ap[i] = As + (ma + (i & 3) + (i >> 2) * 32) * KS;
-    bp[i] = Ws + (na + (i & 3) + (i >> 2) * 16) * KS;
-  }
+  // 2 x 4 warps of 64 x 32 outputs, 8 x 4 lanes; a thread owns the rows wm + ly + 8 i and the columns wn + lx + 4 j
+  // (i, j < 8): for a fixed i the eight ly lanes read eight CONSECUTIVE rows, whose 16-byte fragments along k sit in
+  // eight different bank quads -- so both operands are read four k values at a time with one conflict-free
+  // 16-byte load each: 16 loads per 256 multiply-adds.
+  const int wm = (warp >> 2) * 64, wn = (warp & 3) * 32;
+  const int ly = lane >> 2, lx = lane & 3;
+  const float *ap = As + (wm + ly) * KS, *bp = Ws + (wn + lx) * KS;
   float acc[8][8];
 #pragma unroll
   for (int i = 0; i < 8; ++i)
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[i][j] = 0.0f;
-#pragma unroll 4
-  for (int k = 0; k < K; ++k) {
-    float a[8], b[8];
+#pragma unroll 1
+  for (int k = 0; k < KS; k += 4) {
+    float4 a[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      a[i] = ap[i][k];
-      b[i] = bp[i][k];
+    for (int i = 0; i < 8; ++i) a[i] = *reinterpret_cast<const float4 *>(ap + (8 * i) * KS + k);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float4 b = *reinterpret_cast<const float4 *>(bp + (4 * j) * KS + k);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        acc[i][j] = fmaf(a[i].x, b.x, acc[i][j]);
+        acc[i][j] = fmaf(a[i].y, b.y, acc[i][j]);
+        acc[i][j] = fmaf(a[i].z, b.z, acc[i][j]);
+        acc[i][j] = fmaf(a[i].w, b.w, acc[i][j]);
+      }
     }
-#pragma unroll
-    for (int i = 0; i < 8; ++i)
-#pragma unroll
-      for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
   }
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
-    const int gm = m0 + ma + (i & 3) + (i >> 2) * 32;
+    const int gm = m0 + wm + ly + 8 * i;
     if (gm >= M) continue;
     float *row = C + (size_t)gm * N + n0;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      const int n = na + (j & 3) + (j >> 2) * 16;
+      const int n = wn + lx + 4 * j;
       if (n < nw) row[n] = acc[i][j];
     }
   }
@@ -721,7 +724,7 @@ DGC_EXPORT int32_t dgc_bands_to_taps(dgc_ctx *ctx, const float *bands_dev, const
   }();
   const bool tmap_tile = tmap_mode == 2 || (tmap_mode == 0 && (int64_t)dgc_div_up(rows, 128) * dgc_div_up(taps, 128) <= 1024);
   if ((double)rows * nbands * taps >= (double)(1 << 24) && nbands <= TMAP_KMAX && tmap_tile) {
-    const size_t smem = (size_t)2 * 128 * (nbands | 1) * sizeof(float);
+    const size_t smem = (size_t)2 * 128 * tmap_stride(nbands) * sizeof(float);
     DGC_CUDA(ctx, cudaFuncSetAttribute(tap_map_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const int rem = taps % 128;
     const int ntx = (taps >= 128 && rem > 0 && rem <= TMAP_NARROW) ? taps / 128 : dgc_div_up(taps, 128);
