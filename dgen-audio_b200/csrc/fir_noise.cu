@@ -547,17 +547,6 @@ tap_map_tile_kernel(const float *__restrict__ A, const float *__restrict__ W, in
       }
     }
   }
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const int gm = m0 + wm + ly + 8 * i;
-    if (gm >= M) continue;
-    float *row = C + (size_t)gm * N + n0;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int n = wn + lx + 4 * j;
-      if (n < nw) row[n] = acc[i][j];
-    }
-  }
   // the remainder columns: thread (row, column) pairs, the A row from shared memory, the W row from global memory
   for (int idx = tid; idx < 128 * extra; idx += 256) {
     const int m = idx % 128, c = idx / 128;
@@ -566,6 +555,23 @@ tap_map_tile_kernel(const float *__restrict__ A, const float *__restrict__ W, in
     float sum = 0.0f;
     for (int k = 0; k < K; ++k) sum = fmaf(a[k], __ldg(w + k), sum);
     C[(size_t)(m0 + m) * N + n0 + 128 + c] = sum;
+  }
+  // The tile leaves through shared memory (the operand tiles are done with): a thread's 8 x 8 outputs are scattered
+  // over 8 rows and 8 columns, so storing them directly would write 16-byte pieces of 8 different rows per
+  // instruction; from the staged tile a warp writes whole rows, 128 contiguous bytes per instruction.
+  __syncthreads();
+  float *Cs = tmap_sh;                       // [128][132]: 132 % 32 == 4, the 8 x 4 lanes of a store hit 32 banks
+  constexpr int LDC = 132;
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) Cs[(wm + ly + 8 * i) * LDC + wn + lx + 4 * j] = acc[i][j];
+  __syncthreads();
+  for (int r = warp; r < 128; r += 8) {
+    const int gm = m0 + r;
+    if (gm >= M) break;
+    float *row = C + (size_t)gm * N + n0;
+    for (int c = lane; c < nw; c += 32) row[c] = Cs[r * LDC + c];
   }
 }
 
@@ -724,7 +730,8 @@ DGC_EXPORT int32_t dgc_bands_to_taps(dgc_ctx *ctx, const float *bands_dev, const
   }();
   const bool tmap_tile = tmap_mode == 2 || (tmap_mode == 0 && (int64_t)dgc_div_up(rows, 128) * dgc_div_up(taps, 128) <= 1024);
   if ((double)rows * nbands * taps >= (double)(1 << 24) && nbands <= TMAP_KMAX && tmap_tile) {
-    const size_t smem = (size_t)2 * 128 * tmap_stride(nbands) * sizeof(float);
+    size_t smem = (size_t)2 * 128 * tmap_stride(nbands) * sizeof(float);
+    if (smem < (size_t)128 * 132 * sizeof(float)) smem = (size_t)128 * 132 * sizeof(float);   // the staged output tile
     DGC_CUDA(ctx, cudaFuncSetAttribute(tap_map_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const int rem = taps % 128;
     const int ntx = (taps >= 128 && rem > 0 && rem <= TMAP_NARROW) ? taps / 128 : dgc_div_up(taps, 128);
