@@ -37,6 +37,32 @@ template <int N> struct Geo {
   static constexpr bool THREE = Plan<N>::R3 != 0;
 };
 
+// Where element i of a stage's output sits in the transform's shared-memory buffer.  l1: written by the first stage
+// (read by the middle stage, or by the last one of a two-stage transform); l2: written by the middle stage, read by
+// the last.  Classic: pad() for both, padded(N) elements per transform.
+struct LayoutClassic {
+  template <int N> __device__ static __forceinline__ int l1(int i) { return pad(i); }
+  template <int N> __device__ static __forceinline__ int l2(int i) { return pad(i); }
+  template <int N> __host__ __device__ static constexpr int size() { return padded(N); }
+};
+// Conflict-free for every exchange of the forward transform run IN PLACE (8-byte elements, half-warps of 16 lanes
+// over 16 bank pairs; found by enumerating the access patterns of a warp for every size and stage):
+//   * the last stage reads butterfly j and its partner NBL - j: an ascending and a DESCENDING run of 16 lanes.
+//     With a pad every 16 elements the descending run from a multiple of 16 straddles a pad and two of its lanes
+//     meet (1.5 x the wavefronts); the middle stage's output needs no padding at all for N >= 1024 (its scatter
+//     has stride 16), so there l2 is the identity;
+//   * for N = 512 / 256 (first radix 8) the middle stage's scatter puts lanes k and k + 8 sixty-four elements
+//     apart: a shift of 8 elements per 64 separates them (2 x before);
+//   * for N = 64 the first stage's scatter (stride 8, eight transforms per warp) wants a pad every 8 elements and
+//     76 elements per transform (2 x before).
+struct LayoutFree {
+  template <int N> __device__ static __forceinline__ int l1(int i) { return N == 64 ? i + (i >> 3) : pad(i); }
+  template <int N> __device__ static __forceinline__ int l2(int i) {
+    return N >= 1024 ? i : (N == 512 || N == 256) ? i + 8 * (i >> 6) : l1<N>(i);
+  }
+  template <int N> __host__ __device__ static constexpr int size() { return N == 64 ? 76 : N == 512 ? 568 : N == 256 ? 280 : padded(N); }
+};
+
 // multiply by exp(-+ 2 pi i m / 16), m a compile-time constant in 0..9
 template <int M, bool INV>
 __device__ __forceinline__ float2 mul_w16(float2 a) {
@@ -121,7 +147,7 @@ __device__ __forceinline__ void sync_transform() {
 }
 
 // First stage, from registers: x[m] = element tid + m T.  Writes the stage output to `buf` (Stockham order).
-template <int N, bool INV>
+template <int N, bool INV, class LAY = LayoutClassic>
 __device__ __forceinline__ void stage_first(float2 (&x)[16], float2 *buf, int tid) {
   constexpr int R = Plan<N>::R1, PER = 16 / R, T = N / 16;
 #pragma unroll
@@ -132,7 +158,7 @@ __device__ __forceinline__ void stage_first(float2 (&x)[16], float2 *buf, int ti
     dftN<R, INV>(v);
     const int j = tid + q * T;
 #pragma unroll
-    for (int t = 0; t < R; ++t) buf[pad(j * R + t)] = v[t];
+    for (int t = 0; t < R; ++t) buf[LAY::template l1<N>(j * R + t)] = v[t];
   }
 }
 
@@ -158,7 +184,7 @@ __device__ __forceinline__ void stage_middle(const float2 *in, float2 *out, int 
 // for each other, then the butterflies run from the registers and their outputs go back into the same buffer.  One
 // more wait per transform, half the shared memory: the transforms of a block then leave room for more resident
 // blocks.
-template <int N, bool INV>
+template <int N, bool INV, class LAY = LayoutClassic>
 __device__ __forceinline__ void stage_middle_inplace(float2 *buf, int tid, const float2 *__restrict__ tw) {
   constexpr int R = Plan<N>::R2, PER = 16 / R, T = N / 16, Ns = Plan<N>::R1;
   float2 v[PER][R];
@@ -166,7 +192,7 @@ __device__ __forceinline__ void stage_middle_inplace(float2 *buf, int tid, const
   for (int q = 0; q < PER; ++q) {
     const int j = tid + q * T;
 #pragma unroll
-    for (int t = 0; t < R; ++t) v[q][t] = buf[pad(j + t * (N / R))];
+    for (int t = 0; t < R; ++t) v[q][t] = buf[LAY::template l1<N>(j + t * (N / R))];
   }
   sync_transform<N>();
 #pragma unroll
@@ -176,7 +202,7 @@ __device__ __forceinline__ void stage_middle_inplace(float2 *buf, int tid, const
     dftN<R, INV>(v[q]);
     const int j0 = (j - k) * R + k;
 #pragma unroll
-    for (int t = 0; t < R; ++t) buf[pad(j0 + t * Ns)] = v[q][t];
+    for (int t = 0; t < R; ++t) buf[LAY::template l2<N>(j0 + t * Ns)] = v[q][t];
   }
 }
 
@@ -190,7 +216,7 @@ __device__ __forceinline__ void last_pair(int tid, int p, int &ja, int &jb) {
 
 // Last stage: shared -> registers.  z[p][0][t] = bin ja + t NBL, z[p][1][t] = bin jb + t NBL.
 // For a != 0 the partner of bin (ja, t) is bin (jb, RL - 1 - t).
-template <int N, bool INV>
+template <int N, bool INV, class LAY = LayoutClassic>
 __device__ __forceinline__ void stage_last(const float2 *in, float2 (&z)[Geo<N>::PAIRS][2][Geo<N>::RL], int tid,
                                            const float2 *__restrict__ tw) {
   constexpr int R = Geo<N>::RL, NBL = Geo<N>::NBL;
@@ -202,7 +228,8 @@ __device__ __forceinline__ void stage_last(const float2 *in, float2 (&z)[Geo<N>:
     for (int e = 0; e < 2; ++e) {
       const int j = jj[e];
 #pragma unroll
-      for (int t = 0; t < R; ++t) z[p][e][t] = in[pad(j + t * NBL)];
+      for (int t = 0; t < R; ++t)
+        z[p][e][t] = in[Geo<N>::THREE ? LAY::template l2<N>(j + t * NBL) : LAY::template l1<N>(j + t * NBL)];
       twiddle<R, INV>(z[p][e], tw, j);     // Ns = NBL: k = j, table step 1
       dftN<R, INV>(z[p][e]);
     }
@@ -212,18 +239,19 @@ __device__ __forceinline__ void stage_last(const float2 *in, float2 (&z)[Geo<N>:
 // Whole forward or inverse transform: registers x[16] in (element tid + m N/16), registers z out (see stage_last).
 // bufa / bufb: padded(N) float2 each (bufb unused by the two-stage sizes); nobody may still read them on entry.
 // bufb == bufa selects the in-place middle stage (one buffer per transform).
-template <int N, bool INV>
+// LAY other than LayoutClassic: in place only (bufb == bufa), LAY::size<N>() elements per transform.
+template <int N, bool INV, class LAY = LayoutClassic>
 __device__ __forceinline__ void fft16(float2 (&x)[16], float2 (&z)[Geo<N>::PAIRS][2][Geo<N>::RL], float2 *bufa,
                                       float2 *bufb, int tid, const float2 *__restrict__ tw) {
-  stage_first<N, INV>(x, bufa, tid);
+  stage_first<N, INV, LAY>(x, bufa, tid);
   sync_transform<N>();
   if (Geo<N>::THREE) {
-    if (bufb == bufa) stage_middle_inplace<N, INV>(bufa, tid, tw);
+    if (bufb == bufa) stage_middle_inplace<N, INV, LAY>(bufa, tid, tw);
     else stage_middle<N, INV>(bufa, bufb, tid, tw);
     sync_transform<N>();
-    stage_last<N, INV>(bufb, z, tid, tw);
+    stage_last<N, INV, LAY>(bufb, z, tid, tw);
   } else {
-    stage_last<N, INV>(bufa, z, tid, tw);
+    stage_last<N, INV, LAY>(bufa, z, tid, tw);
   }
 }
 

@@ -10,6 +10,7 @@
 #include <algorithm>
 #include <cstdlib>
 #include <cstring>
+#include <type_traits>
 
 #include "common.cuh"
 #include "fft.cuh"
@@ -184,7 +185,9 @@ __device__ __forceinline__ void mss_fwd16_body(float2 *sm, float *red, int bx, i
   using Gm = dgfft16::Geo<N>;
   constexpr int TT = Gm::T;                     // threads per window
   constexpr int NF = LOSS16_THREADS / TT;       // windows per block
-  constexpr int PN = padded(N), RL = Gm::RL;
+  // conflict-free layouts for the in-place transform; the copy-engine variant keeps the classic two-buffer form
+  using Lay = typename std::conditional<TMA, dgfft16::LayoutClassic, dgfft16::LayoutFree>::type;
+  constexpr int PN = Lay::template size<N>(), RL = Gm::RL;
   const int tid = threadIdx.x, f = tid / TT, lt = tid % TT;
   const int h = bx * NF + f;
   const bool valid = h < H;
@@ -250,7 +253,7 @@ __device__ __forceinline__ void mss_fwd16_body(float2 *sm, float *red, int bx, i
     }
   }
   float2 z[Gm::PAIRS][2][RL];
-  dgfft16::fft16<N, false>(x, z, bufa, bufb, lt, tw);
+  dgfft16::fft16<N, false, Lay>(x, z, bufa, bufb, lt, tw);
   float lin = 0.0f, lg = 0.0f;
   // Bin pairs {k, N - k}.  A pair of butterflies (a, N/RL - a) gives RL of them: bin t of the first with bin
   // RL - 1 - t of the second.  The one thread that holds butterflies 0 and N/(2 RL) instead pairs bins INSIDE each
@@ -284,7 +287,11 @@ __device__ __forceinline__ void mss_fwd16_body(float2 *sm, float *red, int bx, i
   }
 }
 
-constexpr int FWD16_SMEM_BYTES = padded(2048) * (int)sizeof(float2);   // x 2 for the copy-engine variant
+// 128 threads of transforms per block: the largest of NF * size<N>() over the sizes is 32 x 76 elements (N = 64);
+// the copy-engine variant uses two classic buffers of padded(2048)
+constexpr int FWD16_SMEM_BYTES = 32 * 76 * (int)sizeof(float2);
+static_assert(FWD16_SMEM_BYTES >= padded(2048) * (int)sizeof(float2) && FWD16_SMEM_BYTES >= 4 * 568 * (int)sizeof(float2) &&
+              FWD16_SMEM_BYTES >= 8 * 280 * (int)sizeof(float2), "one buffer per transform must fit");
 
 template <bool SUM2, bool TMA>
 __global__ void __launch_bounds__(LOSS16_THREADS, TMA ? 6 : 8)
@@ -924,7 +931,7 @@ int32_t dgc_mss_loss_fwd_sum(dgc_ctx *ctx, const dgc_mss_params *p, const float 
       mss_fwd16_kernel<true, false><<<blocks16, LOSS16_THREADS, FWD16_SMEM_BYTES, ctx->stream>>>(
           pred_dev, pred_b_dev, target_dev, p->B, p->T, fd16, mp, mt, ctx->status_dev);
     else if (tma)
-      mss_fwd16_kernel<false, true><<<blocks16, LOSS16_THREADS, 2 * FWD16_SMEM_BYTES, ctx->stream>>>(
+      mss_fwd16_kernel<false, true><<<blocks16, LOSS16_THREADS, 2 * padded(2048) * (int)sizeof(float2), ctx->stream>>>(
           pred_dev, nullptr, target_dev, p->B, p->T, fd16, mp, mt, ctx->status_dev);
     else
       mss_fwd16_kernel<false, false><<<blocks16, LOSS16_THREADS, FWD16_SMEM_BYTES, ctx->stream>>>(
