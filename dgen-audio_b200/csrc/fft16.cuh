@@ -163,7 +163,7 @@ __device__ __forceinline__ void stage_first(float2 (&x)[16], float2 *buf, int ti
 }
 
 // Middle stage: shared -> shared, input stride Ns = R1.
-template <int N, bool INV>
+template <int N, bool INV, class LAY = LayoutClassic>
 __device__ __forceinline__ void stage_middle(const float2 *in, float2 *out, int tid, const float2 *__restrict__ tw) {
   constexpr int R = Plan<N>::R2, PER = 16 / R, T = N / 16, Ns = Plan<N>::R1;
 #pragma unroll
@@ -171,12 +171,12 @@ __device__ __forceinline__ void stage_middle(const float2 *in, float2 *out, int 
     const int j = tid + q * T, k = j & (Ns - 1);
     float2 v[R];
 #pragma unroll
-    for (int t = 0; t < R; ++t) v[t] = in[pad(j + t * (N / R))];
+    for (int t = 0; t < R; ++t) v[t] = in[LAY::template l1<N>(j + t * (N / R))];
     twiddle<R, INV>(v, tw, k * (N / (Ns * R)));
     dftN<R, INV>(v);
     const int j0 = (j - k) * R + k;
 #pragma unroll
-    for (int t = 0; t < R; ++t) out[pad(j0 + t * Ns)] = v[t];
+    for (int t = 0; t < R; ++t) out[LAY::template l2<N>(j0 + t * Ns)] = v[t];
   }
 }
 
@@ -239,7 +239,7 @@ __device__ __forceinline__ void stage_last(const float2 *in, float2 (&z)[Geo<N>:
 // Whole forward or inverse transform: registers x[16] in (element tid + m N/16), registers z out (see stage_last).
 // bufa / bufb: padded(N) float2 each (bufb unused by the two-stage sizes); nobody may still read them on entry.
 // bufb == bufa selects the in-place middle stage (one buffer per transform).
-// LAY other than LayoutClassic: in place only (bufb == bufa), LAY::size<N>() elements per transform.
+// LAY::size<N>() elements per transform buffer.
 template <int N, bool INV, class LAY = LayoutClassic>
 __device__ __forceinline__ void fft16(float2 (&x)[16], float2 (&z)[Geo<N>::PAIRS][2][Geo<N>::RL], float2 *bufa,
                                       float2 *bufb, int tid, const float2 *__restrict__ tw) {
@@ -247,7 +247,7 @@ __device__ __forceinline__ void fft16(float2 (&x)[16], float2 (&z)[Geo<N>::PAIRS
   sync_transform<N>();
   if (Geo<N>::THREE) {
     if (bufb == bufa) stage_middle_inplace<N, INV, LAY>(bufa, tid, tw);
-    else stage_middle<N, INV>(bufa, bufb, tid, tw);
+    else stage_middle<N, INV, LAY>(bufa, bufb, tid, tw);
     sync_transform<N>();
     stage_last<N, INV, LAY>(bufb, z, tid, tw);
   } else {
@@ -264,7 +264,7 @@ __device__ __forceinline__ void fft16(float2 (&x)[16], float2 (&z)[Geo<N>::PAIRS
 // layout a coalesced store (or the overlap-add) wants, without any reordering pass.
 // ---------------------------------------------------------------------------------------------------------
 // v[t] *= w^t, after the butterfly (same table access as twiddle())
-template <int N, bool INV>
+template <int N, bool INV, class LAY = LayoutClassic>
 __device__ __forceinline__ void stage_last_T(float2 (&y)[Geo<N>::PAIRS][2][Geo<N>::RL], float2 *out, int tid,
                                              const float2 *__restrict__ tw) {
   constexpr int R = Geo<N>::RL, NBL = Geo<N>::NBL;
@@ -278,12 +278,13 @@ __device__ __forceinline__ void stage_last_T(float2 (&y)[Geo<N>::PAIRS][2][Geo<N
       dftN<R, INV>(y[p][e]);
       twiddle<R, INV>(y[p][e], tw, j);
 #pragma unroll
-      for (int t = 0; t < R; ++t) out[pad(j + t * NBL)] = y[p][e][t];
+      for (int t = 0; t < R; ++t)
+        out[Geo<N>::THREE ? LAY::template l2<N>(j + t * NBL) : LAY::template l1<N>(j + t * NBL)] = y[p][e][t];
     }
   }
 }
 
-template <int N, bool INV>
+template <int N, bool INV, class LAY = LayoutClassic>
 __device__ __forceinline__ void stage_middle_T(const float2 *in, float2 *out, int tid, const float2 *__restrict__ tw) {
   constexpr int R = Plan<N>::R2, PER = 16 / R, T = N / 16, Ns = Plan<N>::R1;
 #pragma unroll
@@ -292,15 +293,15 @@ __device__ __forceinline__ void stage_middle_T(const float2 *in, float2 *out, in
     const int j0 = (j - k) * R + k;
     float2 v[R];
 #pragma unroll
-    for (int t = 0; t < R; ++t) v[t] = in[pad(j0 + t * Ns)];
+    for (int t = 0; t < R; ++t) v[t] = in[LAY::template l2<N>(j0 + t * Ns)];
     dftN<R, INV>(v);
     twiddle<R, INV>(v, tw, k * (N / (Ns * R)));
 #pragma unroll
-    for (int t = 0; t < R; ++t) out[pad(j + t * (N / R))] = v[t];
+    for (int t = 0; t < R; ++t) out[LAY::template l1<N>(j + t * (N / R))] = v[t];
   }
 }
 
-template <int N, bool INV>
+template <int N, bool INV, class LAY = LayoutClassic>
 __device__ __forceinline__ void stage_first_T(const float2 *buf, float2 (&x)[16], int tid) {
   constexpr int R = Plan<N>::R1, PER = 16 / R, T = N / 16;
 #pragma unroll
@@ -308,7 +309,7 @@ __device__ __forceinline__ void stage_first_T(const float2 *buf, float2 (&x)[16]
     const int j = tid + q * T;
     float2 v[R];
 #pragma unroll
-    for (int t = 0; t < R; ++t) v[t] = buf[pad(j * R + t)];
+    for (int t = 0; t < R; ++t) v[t] = buf[LAY::template l1<N>(j * R + t)];
     dftN<R, INV>(v);
 #pragma unroll
     for (int t = 0; t < R; ++t) x[q + PER * t] = v[t];
@@ -318,19 +319,19 @@ __device__ __forceinline__ void stage_first_T(const float2 *buf, float2 (&x)[16]
 // Transform of a spectrum held in the forward's register layout: y in (destroyed), x[m] = element tid + m N/16 out.
 // The first write goes to the buffer the forward's last stage read, so a caller that has just finished a forward
 // transform with the same buffers only has to make sure (sync_transform) that every thread is done reading it.
-template <int N, bool INV>
+template <int N, bool INV, class LAY = LayoutClassic>
 __device__ __forceinline__ void fft16_T(float2 (&y)[Geo<N>::PAIRS][2][Geo<N>::RL], float2 (&x)[16], float2 *bufa,
                                         float2 *bufb, int tid, const float2 *__restrict__ tw) {
   if (Geo<N>::THREE) {
-    stage_last_T<N, INV>(y, bufb, tid, tw);
+    stage_last_T<N, INV, LAY>(y, bufb, tid, tw);
     sync_transform<N>();
-    stage_middle_T<N, INV>(bufb, bufa, tid, tw);
+    stage_middle_T<N, INV, LAY>(bufb, bufa, tid, tw);
     sync_transform<N>();
   } else {
-    stage_last_T<N, INV>(y, bufa, tid, tw);
+    stage_last_T<N, INV, LAY>(y, bufa, tid, tw);
     sync_transform<N>();
   }
-  stage_first_T<N, INV>(bufa, x, tid);
+  stage_first_T<N, INV, LAY>(bufa, x, tid);
 }
 
 }  // namespace dgfft16

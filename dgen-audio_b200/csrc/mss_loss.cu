@@ -574,7 +574,8 @@ mss_bwd16_kernel(const float *__restrict__ pred, const float *__restrict__ targe
   using Ge = dgfft16::Geo<N>;
   constexpr int TT = Gm::TT, NF = Gm::NF, WR = Gm::WR, RL = Ge::RL;
   extern __shared__ float2 sm2[];
-  constexpr int PN = padded(N);
+  using Lay = dgfft16::LayoutFree;   // conflict-free exchange layouts (the windowed results below keep pad())
+  constexpr int PN = Lay::template size<N>();
   float2 *bufa_all = sm2, *bufb_all = sm2 + NF * PN;
   float *tile = reinterpret_cast<float *>(sm2 + 2 * NF * PN);
   const int tid = threadIdx.x, f = tid / TT, lt = tid % TT;
@@ -626,7 +627,7 @@ mss_bwd16_kernel(const float *__restrict__ pred, const float *__restrict__ targe
       }
       float2 z[Ge::PAIRS][2][RL];
       dgfft16::sync_transform<N>();   // the previous transform's last reads of the buffers are done
-      dgfft16::fft16<N, false>(x, z, bufa, bufb, lt, tw);
+      dgfft16::fft16<N, false, Lay>(x, z, bufa, bufb, lt, tw);
       if (valid) {
 #pragma unroll
         for (int p = 0; p < Ge::PAIRS; ++p) {
@@ -648,7 +649,7 @@ mss_bwd16_kernel(const float *__restrict__ pred, const float *__restrict__ targe
     // back to the time domain: un-normalised, + sign (Sources/DGen/Emit+SpectralLoss.swift:577-649)
     float2 g[16];
     dgfft16::sync_transform<N>();
-    dgfft16::fft16_T<N, true>(Y, g, bufa, bufb, lt, tw);
+    dgfft16::fft16_T<N, true, Lay>(Y, g, bufa, bufb, lt, tw);
     // bufb is free: the transposed network's last read of it is behind a barrier every thread has passed
     {
       const float *wp = window + lt;
@@ -696,7 +697,7 @@ int32_t launch_bwd16(dgc_ctx *ctx, const dgc_mss_params *p, const float *pred, c
   const int S0 = Gm::WB - E;
   if (S0 < 1) return dgc_fail(ctx, DGC_ERR_UNSUPPORTED, "hop %d too small for window %d", hop, N);
   auto smem_of = [&](int S_) {
-    return (size_t)2 * Gm::NF * padded(N) * sizeof(float2) + (size_t)S_ * hop * sizeof(float);
+    return (size_t)2 * Gm::NF * dgfft16::LayoutFree::size<N>() * sizeof(float2) + (size_t)S_ * hop * sizeof(float);
   };
   if (smem_of(S0) > 200 * 1024) return dgc_fail(ctx, DGC_ERR_UNSUPPORTED, "backward tile does not fit shared memory");
   cudaError_t e = cudaFuncSetAttribute(mss_bwd16_kernel<N, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
