@@ -72,16 +72,22 @@ __global__ void heads_bwd_kernel(const float *__restrict__ z, const float *__res
 // ---------------------------------------------------------------------------------------------
 constexpr int FB_MAXRUN = 512;  // frames per control row the shared staging can hold
 
+// A thread owns FOUR consecutive taps and walks the frames of the run four at a time: the two weights of a frame are
+// broadcast loads shared by its eight multiply-adds, the signal window slides through registers (one 16-byte load
+// of new samples per four frames), so four frames x four taps x two rows = 32 multiply-adds cost three 16-byte
+// shared loads (one tap per thread: three 4-byte loads per two multiply-adds, and the 257th tap ran a pass of its
+// own for a single thread).  Per tap the frames are summed in the same ascending order as before.
 __global__ void __launch_bounds__(256)
 fir_bwd_kernel(dgc_fir_params prm, const float *__restrict__ play, const int *__restrict__ ranges,
                const float *__restrict__ noise, const float *__restrict__ ngain, const float *__restrict__ g_audio,
                float *__restrict__ part_lo, float *__restrict__ part_hi, int32_t *status) {
-  extern __shared__ float sh[];
+  extern __shared__ __align__(16) float sh[];
   const int B = prm.B, T = prm.T, F = prm.F, NT = prm.taps;
-  const int r = blockIdx.x, b = blockIdx.y;
-  float *wl = sh, *wh = sh + FB_MAXRUN, *xs = sh + 2 * FB_MAXRUN;  // xs: FB_MAXRUN + NT - 1
+  const int r = blockIdx.x, b = blockIdx.y, nth = blockDim.x;
+  float *wl = sh, *wh = sh + FB_MAXRUN, *xs = sh + 2 * FB_MAXRUN;  // xs: FB_MAXRUN + NT + 11 (zero-extended)
   const float *xn = noise + (size_t)b * T, *g = g_audio + (size_t)b * T;
-  float acc_lo[4] = {0, 0, 0, 0}, acc_hi[4] = {0, 0, 0, 0};  // taps i = tid + 256*q, q < 4 (NT <= 1024)
+  const int i0 = 4 * threadIdx.x;          // taps i0 .. i0 + 3
+  float acc_lo[4] = {0, 0, 0, 0}, acc_hi[4] = {0, 0, 0, 0};
   const int hi_row = r + 1 >= F ? 0 : r + 1;
   for (int run = 0; run < 2; ++run) {
     const int s0 = ranges[r * 4 + 2 * run], s1 = ranges[r * 4 + 2 * run + 1];
@@ -91,45 +97,59 @@ fir_bwd_kernel(dgc_fir_params prm, const float *__restrict__ play, const int *__
       if (threadIdx.x == 0) atomicExch(status, 102);  // control rate too low for the staged run
       return;
     }
+    const int len4 = (len + 3) & ~3;       // frames beyond the run carry zero weights
     __syncthreads();
-    for (int i = threadIdx.x; i < len; i += 256) {
-      int n = s0 + i, lo;
-      float fr;
-      {
-        int hi;
+    for (int i = threadIdx.x; i < len4; i += nth) {
+      float vl = 0.0f, vh = 0.0f;
+      if (i < len) {
+        int n = s0 + i, lo, hi;
+        float fr;
         row_pos(play[n], F, lo, hi, fr);
+        float omf = 1.0f - fr;
+        float ng = fmaf(fr, ngain[(size_t)hi_row * B + b], omf * ngain[(size_t)r * B + b]);
+        float gp = g[n] * ng * prm.scale;
+        vl = omf * gp;
+        vh = fr * gp;
       }
-      float omf = 1.0f - fr;
-      float ng = fmaf(fr, ngain[(size_t)hi_row * B + b], omf * ngain[(size_t)r * B + b]);
-      float gp = g[n] * ng * prm.scale;
-      wl[i] = omf * gp;
-      wh[i] = fr * gp;
+      wl[i] = vl;
+      wh[i] = vh;
     }
-    for (int i = threadIdx.x; i < len + NT - 1; i += 256) {
+    const int xlen = len4 + 4 * nth + 8;   // every window a thread can read
+    for (int i = threadIdx.x; i < xlen; i += nth) {
       int t = s0 - (NT - 1) + i;
-      xs[i] = (t >= 0 && t < T) ? xn[t] : 0.0f;
+      xs[i] = (i < len + NT - 1 && t >= 0 && t < T) ? xn[t] : 0.0f;
     }
     __syncthreads();
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      int i = threadIdx.x + 256 * q;
-      if (i >= NT) break;
-      float a = acc_lo[q], c = acc_hi[q];
-      for (int m = 0; m < len; ++m) {
-        float xv = xs[m + i];
-        a = fmaf(wl[m], xv, a);
-        c = fmaf(wh[m], xv, c);
+    if (i0 < NT) {
+      const float4 *wl4 = reinterpret_cast<const float4 *>(wl), *wh4 = reinterpret_cast<const float4 *>(wh);
+      const float4 *x4 = reinterpret_cast<const float4 *>(xs + i0);
+      float xw[8];
+      {
+        const float4 v = x4[0];
+        xw[0] = v.x; xw[1] = v.y; xw[2] = v.z; xw[3] = v.w;
       }
-      acc_lo[q] = a;
-      acc_hi[q] = c;
+      for (int m4 = 0; m4 < len4 / 4; ++m4) {
+        const float4 v = x4[m4 + 1], a4 = wl4[m4], c4 = wh4[m4];
+        xw[4] = v.x; xw[5] = v.y; xw[6] = v.z; xw[7] = v.w;
+        const float a[4] = {a4.x, a4.y, a4.z, a4.w}, c[4] = {c4.x, c4.y, c4.z, c4.w};
+#pragma unroll
+        for (int s = 0; s < 4; ++s)       // frame m = 4 m4 + s: tap i0 + j reads xs[m + i0 + j]
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            acc_lo[j] = fmaf(a[s], xw[s + j], acc_lo[j]);
+            acc_hi[j] = fmaf(c[s], xw[s + j], acc_hi[j]);
+          }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) xw[j] = xw[4 + j];
+      }
     }
   }
 #pragma unroll
-  for (int q = 0; q < 4; ++q) {
-    int i = threadIdx.x + 256 * q;
+  for (int j = 0; j < 4; ++j) {
+    const int i = i0 + j;
     if (i >= NT) break;
-    part_lo[((size_t)r * B + b) * NT + i] = acc_lo[q];
-    part_hi[((size_t)r * B + b) * NT + i] = acc_hi[q];
+    part_lo[((size_t)r * B + b) * NT + i] = acc_lo[j];
+    part_hi[((size_t)r * B + b) * NT + i] = acc_hi[j];
   }
 }
 
@@ -545,8 +565,10 @@ DGC_EXPORT int32_t dgc_fir_noise_bwd(dgc_ctx *ctx, const dgc_fir_params *p, cons
   const size_t n = (size_t)p->F * p->B * p->taps;
   float *part = dgc_ctx_scratch(ctx, 2 * n + 8);
   if (!part) return DGC_ERR_OOM;
-  size_t smem = (size_t)(3 * FB_MAXRUN + p->taps) * sizeof(float);
-  fir_bwd_kernel<<<dim3(p->F, p->B), 256, smem, ctx->stream>>>(*p, play, ranges, noise_dev, noise_gain_dev,
+  // four taps per thread, whole warps
+  const int nth = dgc_div_up(dgc_div_up(p->taps, 4), 32) * 32;
+  size_t smem = (size_t)(3 * FB_MAXRUN + 4 * nth + 16) * sizeof(float);
+  fir_bwd_kernel<<<dim3(p->F, p->B), nth, smem, ctx->stream>>>(*p, play, ranges, noise_dev, noise_gain_dev,
                                                                 g_audio_dev, part, part + n, ctx->status_dev);
   DGC_LAUNCHED(ctx, "fir_bwd");
   combine_rows_kernel<<<dgc_div_up((int64_t)n, 256), 256, 0, ctx->stream>>>(part, part + n, p->F,
