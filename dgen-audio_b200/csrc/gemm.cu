@@ -259,6 +259,86 @@ __global__ void act_bwd_kernel(const float *__restrict__ dC, const float *__rest
   dZ[i] = g;
 }
 
+// A layer with a handful of inputs (the controller's first layer: K = 2 features) is not a matmul but a streaming
+// map: C[m][n] = act(sum_k A[m][k] W[k][n] + bias[n]).  One thread per four consecutive outputs of a row: the K
+// inputs of the row are broadcast loads, W and the bias stay in L1, the store is 16 bytes.  Same operation order as
+// the tile kernel (k ascending from zero, then the bias, then the library tanh).
+template <int KK, int EPI>
+__global__ void __launch_bounds__(256)
+smallk_fwd_kernel(const float *__restrict__ A, const float *__restrict__ W, const float *__restrict__ bias, int M, int N,
+                  float *__restrict__ C) {
+  const int nq = N >> 2;
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (size_t)M * nq) return;
+  const int m = (int)(idx / nq), n = (int)(idx - (size_t)m * nq) * 4;
+  float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+  for (int k = 0; k < KK; ++k) {
+    const float a = __ldg(A + (size_t)m * KK + k);
+    const float4 w = __ldg(reinterpret_cast<const float4 *>(W + (size_t)k * N + n));
+    v[0] = fmaf(a, w.x, v[0]);
+    v[1] = fmaf(a, w.y, v[1]);
+    v[2] = fmaf(a, w.z, v[2]);
+    v[3] = fmaf(a, w.w, v[3]);
+  }
+  if (EPI >= 1) {
+    const float4 bq = __ldg(reinterpret_cast<const float4 *>(bias + n));
+    v[0] += bq.x; v[1] += bq.y; v[2] += bq.z; v[3] += bq.w;
+  }
+  if (EPI == 2) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] = tanhf(v[j]);
+  }
+  *reinterpret_cast<float4 *>(C + (size_t)m * N + n) = make_float4(v[0], v[1], v[2], v[3]);
+}
+
+// Its backward: db[n] = sum_m dZ[m][n] and dW[k][n] = sum_m A[m][k] dZ[m][n] from ONE pass over dZ (a matmul
+// with a 32000-long reduction and a 2 x 512 output reads dZ at a fraction of the memory rate).  Same two fixed-order
+// stages as the bias gradient: block (32 columns x 1024 rows) -> part[chunk][1 + KK][n], then the chunks in order.
+template <int KK>
+__global__ void __launch_bounds__(256)
+smallk_grad_kernel(const float *__restrict__ A, const float *__restrict__ dZ, int M, int N, float *__restrict__ part) {
+  __shared__ float sh[KK + 1][8][33];
+  const int lane = threadIdx.x & 31, col = blockIdx.x * 32 + lane, rg = threadIdx.x >> 5;
+  const int m_begin = blockIdx.y * 1024, m_end = min(M, m_begin + 1024);
+  float acc[KK + 1];
+#pragma unroll
+  for (int q = 0; q <= KK; ++q) acc[q] = 0.0f;
+  if (col < N)
+    for (int m = m_begin + rg; m < m_end; m += 8) {
+      const float d = dZ[(size_t)m * N + col];
+      acc[0] += d;
+#pragma unroll
+      for (int k = 0; k < KK; ++k) acc[1 + k] = fmaf(__ldg(A + (size_t)m * KK + k), d, acc[1 + k]);
+    }
+#pragma unroll
+  for (int q = 0; q <= KK; ++q) sh[q][rg][lane] = acc[q];
+  __syncthreads();
+  if (rg == 0 && col < N) {
+#pragma unroll
+    for (int q = 0; q <= KK; ++q) {
+      float t = 0.0f;
+#pragma unroll
+      for (int r = 0; r < 8; ++r) t += sh[q][r][lane];
+      part[((size_t)blockIdx.y * (KK + 1) + q) * N + col] = t;
+    }
+  }
+}
+
+// db (may be null) and dW from the chunk sums, chunks in index order
+__global__ void smallk_grad_reduce_kernel(const float *__restrict__ part, int chunks, int KK, int N, float *__restrict__ db,
+                                          float *__restrict__ dW) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (KK + 1) * N) return;
+  const int q = i / N, col = i - q * N;
+  float t = 0.0f;
+  for (int c = 0; c < chunks; ++c) t += part[((size_t)c * (KK + 1) + q) * N + col];
+  if (q == 0) {
+    if (db) db[col] = t;
+  } else
+    dW[(size_t)(q - 1) * N + col] = t;
+}
+
 // db[n] = sum_m dZ[m][n].  Stage 1: block (32 columns x 1024 rows) sums its rows in a fixed order into
 // part[chunk][n]; stage 2 adds the chunks in index order: bit-reproducible.
 __global__ void __launch_bounds__(256)
@@ -339,6 +419,22 @@ DGC_EXPORT int32_t dgc_linear_fwd(dgc_ctx *ctx, const float *a_dev, const float 
     if (act == 1) rc = launch_sgemm<false, true, 2>(ctx, a_dev, ctx->wt_buf, bias_dev, M, N, K, c_dev, ct_dev, &ct_done);
     else if (bias_dev) rc = launch_sgemm<false, true, 1>(ctx, a_dev, ctx->wt_buf, bias_dev, M, N, K, c_dev, ct_dev, &ct_done);
     else rc = launch_sgemm<false, true, 0>(ctx, a_dev, ctx->wt_buf, nullptr, M, N, K, c_dev, ct_dev, &ct_done);
+  } else if (K <= 4 && (N & 3) == 0 && ((((uintptr_t)w_dev) | ((uintptr_t)c_dev) | ((uintptr_t)bias_dev)) & 15) == 0) {
+    // a handful of inputs: the streaming map
+    const int64_t work = (int64_t)M * (N >> 2);
+    const dim3 grid((unsigned)dgc_div_up(work, 256));
+#define DGC_SMALLK_FWD(KKV)                                                                                           \
+  do {                                                                                                               \
+    if (act == 1) smallk_fwd_kernel<KKV, 2><<<grid, 256, 0, ctx->stream>>>(a_dev, w_dev, bias_dev, M, N, c_dev);      \
+    else if (bias_dev) smallk_fwd_kernel<KKV, 1><<<grid, 256, 0, ctx->stream>>>(a_dev, w_dev, bias_dev, M, N, c_dev); \
+    else smallk_fwd_kernel<KKV, 0><<<grid, 256, 0, ctx->stream>>>(a_dev, w_dev, nullptr, M, N, c_dev);                \
+  } while (0)
+    if (K == 1) DGC_SMALLK_FWD(1);
+    else if (K == 2) DGC_SMALLK_FWD(2);
+    else if (K == 3) DGC_SMALLK_FWD(3);
+    else DGC_SMALLK_FWD(4);
+#undef DGC_SMALLK_FWD
+    rc = DGC_OK;
   } else
   if (act == 1) rc = launch_sgemm<false, false, 2>(ctx, a_dev, w_dev, bias_dev, M, N, K, c_dev);
   else if (bias_dev) rc = launch_sgemm<false, false, 1>(ctx, a_dev, w_dev, bias_dev, M, N, K, c_dev);
@@ -381,7 +477,20 @@ DGC_EXPORT int32_t dgc_linear_bwd(dgc_ctx *ctx, const float *a_dev, const float 
     act_bwd_kernel<<<dgc_div_up((int64_t)n, 256), 256, 0, ctx->stream>>>(dc_dev, c_dev, n, act, dz_dev);
   }
   DGC_LAUNCHED(ctx, "act_bwd");
-  if (dbias_dev) {
+  const bool smallk = K <= 4;   // bias and weight gradient from one pass over dZ
+  if (smallk) {
+    const int chunks = dgc_div_up(M, 1024);
+    float *part = dgc_ctx_scratch(ctx, (uint64_t)chunks * (K + 1) * N + 4);
+    if (!part) return DGC_ERR_OOM;
+    const dim3 grid(dgc_div_up(N, 32), chunks);
+    if (K == 1) smallk_grad_kernel<1><<<grid, 256, 0, ctx->stream>>>(a_dev, dz_dev, M, N, part);
+    else if (K == 2) smallk_grad_kernel<2><<<grid, 256, 0, ctx->stream>>>(a_dev, dz_dev, M, N, part);
+    else if (K == 3) smallk_grad_kernel<3><<<grid, 256, 0, ctx->stream>>>(a_dev, dz_dev, M, N, part);
+    else smallk_grad_kernel<4><<<grid, 256, 0, ctx->stream>>>(a_dev, dz_dev, M, N, part);
+    DGC_LAUNCHED(ctx, "smallk_grad");
+    smallk_grad_reduce_kernel<<<dgc_div_up((K + 1) * N, 128), 128, 0, ctx->stream>>>(part, chunks, K, N, dbias_dev, dw_dev);
+    DGC_LAUNCHED(ctx, "smallk_grad_reduce");
+  } else if (dbias_dev) {
     const int chunks = dgc_div_up(M, 1024);
     float *part = dgc_ctx_scratch(ctx, (uint64_t)chunks * N + 4);
     if (!part) return DGC_ERR_OOM;
@@ -391,10 +500,10 @@ DGC_EXPORT int32_t dgc_linear_bwd(dgc_ctx *ctx, const float *a_dev, const float 
     DGC_LAUNCHED(ctx, "bias_grad_reduce");
   }
   // dW[K][N] = A^T[K][M] * dZ[M][N]
-  int32_t rc = dw_kmajor ? launch_sgemm<false, true, 0>(ctx, at_dev, ctx->dzt_buf, nullptr, K, N, M, dw_dev)
+  int32_t rc = smallk ? DGC_OK : dw_kmajor ? launch_sgemm<false, true, 0>(ctx, at_dev, ctx->dzt_buf, nullptr, K, N, M, dw_dev)
                          : launch_sgemm<true, false, 0>(ctx, a_dev, dz_dev, nullptr, K, N, M, dw_dev);
   if (rc != DGC_OK) return rc;
-  DGC_LAUNCHED(ctx, "linear_bwd_dw");
+  if (!smallk) DGC_LAUNCHED(ctx, "linear_bwd_dw");
   if (da_dev) {
     // dA[M][K] = dZ[M][N] * W^T[N][K]
     rc = launch_sgemm<false, true, 0>(ctx, dz_dev, w_dev, nullptr, M, K, N, da_dev);
