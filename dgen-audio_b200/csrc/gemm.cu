@@ -259,6 +259,22 @@ __global__ void act_bwd_kernel(const float *__restrict__ dC, const float *__rest
   dZ[i] = g;
 }
 
+// the same, four elements per thread (n a multiple of 4, 16-byte aligned buffers)
+__global__ void act_bwd4_kernel(const float4 *__restrict__ dC, const float4 *__restrict__ Cv, size_t n4, int act,
+                                float4 *__restrict__ dZ) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n4) return;
+  float4 g = dC[i];
+  if (act == 1) {
+    const float4 c = Cv[i];
+    g.x *= (1.0f - c.x * c.x);
+    g.y *= (1.0f - c.y * c.y);
+    g.z *= (1.0f - c.z * c.z);
+    g.w *= (1.0f - c.w * c.w);
+  }
+  dZ[i] = g;
+}
+
 // A layer with a handful of inputs (the controller's first layer: K = 2 features) is not a matmul but a streaming
 // map: C[m][n] = act(sum_k A[m][k] W[k][n] + bias[n]).  One thread per four consecutive outputs of a row: the K
 // inputs of the row are broadcast loads, W and the bias stay in L1, the store is 16 bytes.  Same operation order as
@@ -474,7 +490,13 @@ DGC_EXPORT int32_t dgc_linear_bwd(dgc_ctx *ctx, const float *a_dev, const float 
     act_bwd_t_kernel<<<dim3(dgc_div_up(N, 32), dgc_div_up(M, 32)), dim3(32, 8), 0, ctx->stream>>>(dc_dev, c_dev, M, N, act,
                                                                                                 dz_dev, ctx->dzt_buf);
   } else {
-    act_bwd_kernel<<<dgc_div_up((int64_t)n, 256), 256, 0, ctx->stream>>>(dc_dev, c_dev, n, act, dz_dev);
+    const bool vec = (n & 3) == 0 && ((((uintptr_t)dc_dev) | ((uintptr_t)dz_dev) | (act == 1 ? (uintptr_t)c_dev : 0)) & 15) == 0;
+    if (vec)
+      act_bwd4_kernel<<<dgc_div_up((int64_t)(n / 4), 256), 256, 0, ctx->stream>>>(
+          reinterpret_cast<const float4 *>(dc_dev), reinterpret_cast<const float4 *>(c_dev), n / 4, act,
+          reinterpret_cast<float4 *>(dz_dev));
+    else
+      act_bwd_kernel<<<dgc_div_up((int64_t)n, 256), 256, 0, ctx->stream>>>(dc_dev, c_dev, n, act, dz_dev);
   }
   DGC_LAUNCHED(ctx, "act_bwd");
   const bool smallk = K <= 4;   // bias and weight gradient from one pass over dZ

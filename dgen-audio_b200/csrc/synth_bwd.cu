@@ -153,6 +153,16 @@ fir_bwd_kernel(dgc_fir_params prm, const float *__restrict__ play, const int *__
   }
 }
 
+// the same four elements at a time (row_elems a multiple of 4, 16-byte aligned buffers); row_elems4 = row_elems / 4
+__global__ void combine_rows4_kernel(const float4 *__restrict__ part_lo, const float4 *__restrict__ part_hi, int F,
+                                     unsigned row_elems4, float4 *__restrict__ grad) {
+  const unsigned e = blockIdx.x * blockDim.x + threadIdx.x, r = blockIdx.y;
+  if (e >= row_elems4) return;
+  const unsigned rp = r == 0 ? (unsigned)F - 1 : r - 1;
+  const float4 a = part_lo[(size_t)r * row_elems4 + e], b = part_hi[(size_t)rp * row_elems4 + e];
+  grad[(size_t)r * row_elems4 + e] = make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w);
+}
+
 // grad[r] = part_lo[r] + part_hi[r-1]  (the ceil row of floor row F-1 is row 0)
 __global__ void combine_rows_kernel(const float *__restrict__ part_lo, const float *__restrict__ part_hi, int F,
                                     size_t row_elems, float *__restrict__ grad) {
@@ -502,6 +512,21 @@ harmonic_bwd_q_kernel(dgc_harmonic_params prm, float rsr, const float2 *__restri
   }
 }
 
+// grad[r] = part_lo[r] + part_hi[r-1] over F rows of row_elems floats
+void launch_combine_rows(dgc_ctx *ctx, const float *pl, const float *ph, int F, size_t row_elems, float *grad) {
+  const bool vec = (row_elems & 3) == 0 && F <= 65535 &&
+                   ((((uintptr_t)pl) | ((uintptr_t)ph) | ((uintptr_t)grad)) & 15) == 0;
+  if (vec) {
+    const unsigned re4 = (unsigned)(row_elems / 4);
+    combine_rows4_kernel<<<dim3(dgc_div_up((int64_t)re4, 256), F), 256, 0, ctx->stream>>>(
+        reinterpret_cast<const float4 *>(pl), reinterpret_cast<const float4 *>(ph), F, re4,
+        reinterpret_cast<float4 *>(grad));
+  } else {
+    const size_t n = (size_t)F * row_elems;
+    combine_rows_kernel<<<dgc_div_up((int64_t)n, 256), 256, 0, ctx->stream>>>(pl, ph, F, row_elems, grad);
+  }
+}
+
 template <int LPC, int P>
 void launch_hbwd_q(dgc_ctx *ctx, const dgc_harmonic_params &p, const float2 *rowtab, const int *ranges,
                    const dgc_harmonic_extra &x, const float *amps, const float *g_audio, float *pl, float *ph,
@@ -571,8 +596,7 @@ DGC_EXPORT int32_t dgc_fir_noise_bwd(dgc_ctx *ctx, const dgc_fir_params *p, cons
   fir_bwd_kernel<<<dim3(p->F, p->B), nth, smem, ctx->stream>>>(*p, play, ranges, noise_dev, noise_gain_dev,
                                                                 g_audio_dev, part, part + n, ctx->status_dev);
   DGC_LAUNCHED(ctx, "fir_bwd");
-  combine_rows_kernel<<<dgc_div_up((int64_t)n, 256), 256, 0, ctx->stream>>>(part, part + n, p->F,
-                                                                             (size_t)p->B * p->taps, g_taps_dev);
+  launch_combine_rows(ctx, part, part + n, p->F, (size_t)p->B * p->taps, g_taps_dev);
   DGC_LAUNCHED(ctx, "combine_rows");
   return DGC_OK;
 }
@@ -620,8 +644,7 @@ static int32_t harmonic_render_bwd_impl(dgc_ctx *ctx, const dgc_harmonic_params 
   else HBWD(32, 16);
 #undef HBWD
   DGC_LAUNCHED(ctx, "harmonic_bwd");
-  combine_rows_kernel<<<dgc_div_up((int64_t)n, 256), 256, 0, ctx->stream>>>(pl, ph, p->F, (size_t)p->B * K,
-                                                                             g_amps_dev);
+  launch_combine_rows(ctx, pl, ph, p->F, (size_t)p->B * K, g_amps_dev);
   DGC_LAUNCHED(ctx, "combine_rows");
   return DGC_OK;
 }
