@@ -315,18 +315,23 @@ template <int KK>
 __global__ void __launch_bounds__(256)
 smallk_grad_kernel(const float *__restrict__ A, const float *__restrict__ dZ, int M, int N, float *__restrict__ part) {
   __shared__ float sh[KK + 1][8][33];
+  __shared__ float as[1024 * KK];          // the chunk's rows of A: one coalesced read, then broadcast loads
   const int lane = threadIdx.x & 31, col = blockIdx.x * 32 + lane, rg = threadIdx.x >> 5;
   const int m_begin = blockIdx.y * 1024, m_end = min(M, m_begin + 1024);
+  for (int i = threadIdx.x; i < (m_end - m_begin) * KK; i += 256) as[i] = A[(size_t)m_begin * KK + i];
+  __syncthreads();
   float acc[KK + 1];
 #pragma unroll
   for (int q = 0; q <= KK; ++q) acc[q] = 0.0f;
-  if (col < N)
+  if (col < N) {
+#pragma unroll 4
     for (int m = m_begin + rg; m < m_end; m += 8) {
       const float d = dZ[(size_t)m * N + col];
       acc[0] += d;
 #pragma unroll
-      for (int k = 0; k < KK; ++k) acc[1 + k] = fmaf(__ldg(A + (size_t)m * KK + k), d, acc[1 + k]);
+      for (int k = 0; k < KK; ++k) acc[1 + k] = fmaf(as[(m - m_begin) * KK + k], d, acc[1 + k]);
     }
+  }
 #pragma unroll
   for (int q = 0; q <= KK; ++q) sh[q][rg][lane] = acc[q];
   __syncthreads();
