@@ -89,6 +89,8 @@ const float *dgc_ctx_hann_sym(dgc_ctx *ctx, int N);
 const float *dgc_ctx_hann_per(dgc_ctx *ctx, int N);
 // C[M][N] = A[M][K] * B[N][K]^T on the matmul path of gemm.cu
 int32_t dgc_gemm_nt(dgc_ctx *ctx, const float *a, const float *b, int M, int N, int K, float *c);
+// true when dgc_gemm_nt() runs this shape on its persistent short-reduction tensor-core kernel
+bool dgc_gemm_nt_persistent(const dgc_ctx *ctx, const float *a, int M, int N, int K);
 const float2 *dgc_ctx_twiddles(dgc_ctx *ctx, int N);
 // dgc_mss_loss_fwd with the prediction given as the sum of two signals (pred_b may be null)
 int32_t dgc_mss_loss_fwd_sum(dgc_ctx *ctx, const dgc_mss_params *p, const float *pred_dev, const float *pred_b_dev,

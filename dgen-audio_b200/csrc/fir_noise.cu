@@ -718,16 +718,18 @@ DGC_EXPORT int32_t dgc_bands_to_taps(dgc_ctx *ctx, const float *bands_dev, const
   if (!ctx) return DGC_ERR_INVALID;
   DGC_REQUIRE(ctx, bands_dev && w_dev && taps_dev, "null pointer");
   DGC_REQUIRE(ctx, rows > 0 && nbands > 0 && taps > 0, "size out of range");
-  // Large row counts run as a matmul.  Up to a few hundred tiles (the 16- and 32-voice steps) on the plain tile
-  // kernel: alone it is no faster than the tensor-core matmul (0.037 vs 0.035 ms at 16 voices), but the map runs
-  // BESIDE the harmonic branch on the other stream, and a kernel of plain 256-thread blocks shares the SMs with the
-  // render better than CTAs that hold 97 KB of shared memory and tensor memory each: the whole 16-voice step takes
-  // 0.198 ms with it against 0.209 ms.  Beyond that size every kernel fills the GPU by itself and the tensor-core
-  // matmul is faster (0.29 vs 0.38 ms at 256 voices).  DGC_TAP_MAP=tc|tile forces one.
-  static const int tmap_mode = [] {
-    const char *e = getenv("DGC_TAP_MAP");
-    return !e ? 0 : strcmp(e, "tc") == 0 ? 1 : strcmp(e, "tile") == 0 ? 2 : 0;
-  }();
+  // From 2^24 multiply-adds on the map runs as a matmul.  For 32 to 72 bands and at least 128 taps: the persistent
+  // short-reduction tensor-core kernel of the matmul entry point (3xTF32 with rounded parts; a CTA keeps its 128
+  // taps of the matrix in shared memory and streams row tiles of the bands through two accumulators): 9 us for the
+  // 16-voice map and 0.135 ms for the 256-voice one, against 28 us and 0.32 ms for the plain fp32 tile kernel and
+  // 0.30 ms for the general tensor-core pipeline; whole steps 0.164 against 0.172 ms (16 voices) and 2.15 against
+  // 2.32 ms (256).  Other shapes: the tile kernel up to 1024 output tiles, the matmul entry point beyond.
+  // DGC_TAP_MAP=tile|tc forces the tile kernel / the matmul entry point.
+  const char *tmap_env = getenv("DGC_TAP_MAP");   // read per call: a test can switch kernels inside one process
+  const int tmap_mode = !tmap_env ? 0 : strcmp(tmap_env, "tc") == 0 ? 1 : strcmp(tmap_env, "tile") == 0 ? 2 : 0;
+  const bool big = (double)rows * nbands * taps >= (double)(1 << 24);
+  if (big && tmap_mode != 2 && dgc_gemm_nt_persistent(ctx, bands_dev, rows, taps, nbands))
+    return dgc_gemm_nt(ctx, bands_dev, w_dev, rows, taps, nbands, taps_dev);
   const bool tmap_tile = tmap_mode == 2 || (tmap_mode == 0 && (int64_t)dgc_div_up(rows, 128) * dgc_div_up(taps, 128) <= 1024);
   if ((double)rows * nbands * taps >= (double)(1 << 24) && nbands <= TMAP_KMAX && tmap_tile) {
     size_t smem = (size_t)2 * 128 * tmap_stride(nbands) * sizeof(float);

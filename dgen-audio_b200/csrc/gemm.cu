@@ -119,6 +119,22 @@ bool use_tensor_cores() {
   return v == 1;
 }
 
+// true when C = A B^T of this shape runs on the persistent short-reduction tensor-core kernel: 32 <= K <= 72, at
+// least one full block of 128 columns, A 16-byte aligned (its row tiles are fetched by bulk copies), no more column
+// blocks than SMs.  DGC_GEMM_SMALLK=0 keeps such shapes on the general pipeline.
+bool smallk_shape(const dgc_ctx *ctx, const float *A, int M, int N, int K) {
+  static const bool on = [] {
+    const char *e = getenv("DGC_GEMM_SMALLK");
+    return !(e && atoi(e) == 0);
+  }();
+  if (!on || !use_tensor_cores() || (double)M * N * K < (double)(1 << 21) || K < 32 || K > dgtc::SK::KP_MAX ||
+      N < dgtc::TBN || (((uintptr_t)A) & 15) != 0)
+    return false;
+  const int rem = N % dgtc::TBN;
+  const int nblk = (rem > 0 && rem <= dgtc::SK::EXTRA_MAX) ? N / dgtc::TBN : dgc_div_up(N, dgtc::TBN);
+  return nblk <= ctx->sm_count;
+}
+
 template <bool TA, bool TB, int EPI>
 int32_t launch_sgemm(dgc_ctx *ctx, const float *A, const float *B, const float *bias, int M, int N, int K, float *C,
                      float *Ct = nullptr, bool *ct_written = nullptr) {
@@ -140,6 +156,20 @@ int32_t launch_sgemm(dgc_ctx *ctx, const float *A, const float *B, const float *
   // DGC_GEMM_KK=256 forces them wherever N >= 256.
   const bool long_reduction = EPI == 0 && K >= 2048 && dgc_div_up(N, dgtc::TBN) * dgc_div_up(M, dgtc::TBM) < ctx->sm_count;
   const bool wide = kk16 && N >= 256 && (kk_bk == 256 || (kk_bk == 16 && long_reduction));
+  // short reductions (the band -> tap map): persistent CTAs that keep their block of B in shared memory
+  if (!TA && TB && EPI == 0 && smallk_shape(ctx, A, M, N, K)) {
+    const int rem = N % dgtc::TBN;
+    const int n_extra = (rem > 0 && rem <= dgtc::SK::EXTRA_MAX) ? rem : 0;
+    const int nblk = n_extra ? N / dgtc::TBN : dgc_div_up(N, dgtc::TBN);
+    const int per = std::min(dgc_div_up(M, dgtc::TBM), ctx->sm_count / nblk);
+    auto kern = dgtc::tc_gemm_smallk_kernel;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, dgtc::SK::SMEM);
+    if (e != cudaSuccess) return dgc_fail(ctx, DGC_ERR_CUDA, "tc_gemm smem opt-in: %s", cudaGetErrorString(e));
+    ctx->gemm_paths[2]++;
+    kern<<<nblk * per, dgtc::SK::THREADS_ALL, dgtc::SK::SMEM, ctx->stream>>>(A, B, M, N, K, nblk, n_extra, per, C,
+                                                                             ctx->status_dev);
+    return DGC_OK;
+  }
   const int bm = tc ? dgtc::TBM : BM, bn = wide ? 256 : (tc ? dgtc::TBN : BN);
   const int tiles = dgc_div_up(N, bn) * dgc_div_up(M, bm);
   int splits = 1;
@@ -405,6 +435,8 @@ __global__ void adam_kernel(float *__restrict__ theta, const float *__restrict__
 
 }  // namespace
 
+bool dgc_gemm_nt_persistent(const dgc_ctx *ctx, const float *a, int M, int N, int K) { return smallk_shape(ctx, a, M, N, K); }
+
 // C[M][N] = A[M][K] * B[N][K]^T, no epilogue (used for the band -> tap map)
 int32_t dgc_gemm_nt(dgc_ctx *ctx, const float *a, const float *b, int M, int N, int K, float *c) {
   int32_t rc = launch_sgemm<false, true, 0>(ctx, a, b, nullptr, M, N, K, c);
@@ -605,5 +637,9 @@ DGC_EXPORT int32_t dgc_gemm_path_counts(dgc_ctx *ctx, int64_t *out4) {
 DGC_EXPORT int32_t dgc_debug_kk_times(unsigned long long *out8) {
   cudaDeviceSynchronize();
   return cudaMemcpyFromSymbol(out8, dgtc::dgc_kk_times, 8 * sizeof(unsigned long long)) == cudaSuccess ? 0 : -1;
+}
+DGC_EXPORT int32_t dgc_debug_sk_times(unsigned long long *out128) {
+  cudaDeviceSynchronize();
+  return cudaMemcpyFromSymbol(out128, dgtc::dgc_sk_times, 128 * sizeof(unsigned long long)) == cudaSuccess ? 0 : -1;
 }
 #endif

@@ -96,6 +96,17 @@ __device__ __forceinline__ void split_tf32(float x, float &hi, float &lo) {
   lo = x - hi;
 }
 
+// The same split with both parts ROUNDED to TF32 (round to nearest, ties away): |lo| <= 2^-11 |x| and what is
+// lost, x - hi - lo, is at most 2^-22 |x| with either sign, where truncation loses up to 2^-20 |x| always
+// towards zero (a bias that sums over a reduction instead of averaging out).
+__device__ __forceinline__ void split_tf32_rn(float x, float &hi, float &lo) {
+  // adding half a TF32 ulp to the bit pattern and clearing the 13 low bits rounds the magnitude to nearest, ties
+  // away from zero (a carry into the exponent is the correct result); two integer instructions where the
+  // conversion instruction runs at a quarter of their rate
+  hi = __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xFFFFE000u);
+  lo = __uint_as_float((__float_as_uint(x - hi) + 0x1000u) & 0xFFFFE000u);
+}
+
 // One 128 x 32 operand tile (rows r0.., k range k0..) moves in two steps so that the global loads of tile
 // t+1 can be in flight while tile t is stored and multiplied: fetch() global memory -> 4 float4 registers
 // per thread, stash() registers -> hi / lo parts in shared memory (256 threads).
@@ -577,6 +588,268 @@ tc_gemm_kk_kernel(const float *__restrict__ A, const float *__restrict__ B, cons
   __syncthreads();
   if (warp == 0) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"((uint32_t)BN) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Short reductions (K <= 72; the band -> tap map has K = 65, N = 257): A [M][K], B [N][K], both contiguous
+// along k.  With so few k-tiles a CTA per output tile spends its life in prologue, load latency and epilogue,
+// so this kernel is persistent: a CTA owns ONE 128-column block of the output, keeps that block of B (hi and
+// lo parts) in shared memory for its whole life and walks down the row tiles of A.
+//   copy     a 128-row tile of A is one contiguous, 16-byte aligned run of 128 K floats whatever K's alignment:
+//            the thread that issues the MMAs fetches it with ONE bulk copy (cp.async.bulk, completion on an
+//            mbarrier) into a linear staging buffer, as soon as the previous tile has been split out of it
+//   split    sixteen worker warps read the linear tile and write its hi and lo parts (both rounded to TF32) into
+//            the K-major no-swizzle layout of make_desc<true>(): 16-byte unit (row r, chunk kc) at
+//            kc * LBO_BYTES + r * 16; k is padded to a multiple of 8 with zeros that are written once
+//   multiply one thread issues the 3 x ceil(K / 8) MMAs of the tile into one of TWO 128-column accumulators
+//   store    while the tensor core works on tile i, the worker warps move tile i-1 from the other accumulator to
+//            global memory (32 x 16 blocks turned through shared memory into row segments)
+// N % 128 <= SK::EXTRA_MAX leftover columns (the 257th tap) are plain fp32 dot products of the CTAs of the
+// last column block, from the linear tile, instead of a third block of 127 empty columns.
+// Every wait is bounded; on expiry the kernel raises status 202, stops waiting everywhere and frees its TMEM.
+// ---------------------------------------------------------------------------------------------------------
+#ifdef DGC_KK_TIMING
+__device__ unsigned long long dgc_sk_times[128];
+#define SK_STAMP(i) do { if (tid == 0 && blockIdx.x == 0 && (i) < 128) dgc_sk_times[(i)] = gtime(); } while (0)
+#else
+#define SK_STAMP(i) do {} while (0)
+#endif
+struct SK {
+  static constexpr int KP_MAX = 72;                          // largest K (nine k-steps of 8)
+  static constexpr int WORKERS = 512, THREADS_ALL = WORKERS + 32;
+  static constexpr int OPER = (KP_MAX / 4) * LBO_BYTES;      // one operand part: 18 chunks
+  static constexpr int OFF_BHI = 0, OFF_BLO = OPER, OFF_AHI = 2 * OPER, OFF_ALO = 3 * OPER, OFF_LIN = 4 * OPER;
+  static constexpr int LIN_BYTES = TBM * KP_MAX * 4;
+  static constexpr int EPI_ROW = 20;                         // floats per staged row of 16 (16-byte stores, no conflicts)
+  static constexpr int OFF_STAGE = OFF_LIN + LIN_BYTES;
+  static constexpr int OFF_BARS = OFF_STAGE + (WORKERS / 32) * 32 * EPI_ROW * 4;
+  static constexpr int SMEM = OFF_BARS + 64;
+  static constexpr int EPT = TBM * KP_MAX / WORKERS;         // elements of a tile per worker thread
+  static constexpr int EXTRA_MAX = 8;
+};
+static_assert(SK::SMEM <= 227 * 1024, "the persistent small-K kernel must fit one CTA's shared memory");
+static_assert(SK::OFF_LIN % 128 == 0 && SK::OFF_STAGE % 16 == 0 && SK::OFF_BARS % 8 == 0, "alignment of the buffers");
+
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// linear global -> shared copy by the copy engine; both addresses 16-byte aligned, bytes a multiple of 16
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+
+__global__ void __launch_bounds__(SK::THREADS_ALL, 1)
+tc_gemm_smallk_kernel(const float *__restrict__ A, const float *__restrict__ B, int M, int N, int K, int nblk,
+                      int n_extra, int ctas_per_blk, float *__restrict__ C, int32_t *status) {
+  extern __shared__ __align__(128) char smem[];
+  char *b_hi = smem + SK::OFF_BHI, *b_lo = smem + SK::OFF_BLO, *a_hi = smem + SK::OFF_AHI, *a_lo = smem + SK::OFF_ALO;
+  float *lin = reinterpret_cast<float *>(smem + SK::OFF_LIN);
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + SK::OFF_BARS);
+  const uint32_t bar_ready = smem_u32(bars), bar_done = smem_u32(bars + 1), bar_load = smem_u32(bars + 2);
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + SK::OFF_BARS + 32);
+  volatile int *failed = reinterpret_cast<volatile int *>(tmem_slot + 1);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int cb = blockIdx.x % nblk, slot = blockIdx.x / nblk;
+  const int n0 = cb * TBN;
+  const int row_tiles = (M + TBM - 1) / TBM;
+  const int nt = (row_tiles - slot + ctas_per_blk - 1) / ctas_per_blk;   // row tiles slot, slot + ctas_per_blk, ...
+  const bool has_extra = n_extra > 0 && cb == nblk - 1;
+  const int ksteps = (K + 7) / 8;
+  const int tile_elems = TBM * K;
+
+  // zeros once: the k padding of all four operand parts and the rows past the end of B are never written again
+  for (int u = tid; u < SK::OFF_LIN / 16; u += SK::THREADS_ALL)
+    reinterpret_cast<float4 *>(smem)[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (tid == 0) {
+    mbar_init(bar_ready, SK::WORKERS / 32);   // one arrival per worker warp
+    mbar_init(bar_done, 1);
+    mbar_init(bar_load, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    *failed = 0;
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"((uint32_t)(2 * TBN))
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_d = *tmem_slot;
+  SK_STAMP(0);
+
+  if (warp < SK::WORKERS / 32) {
+    // ---- worker warps ---------------------------------------------------------------------------------------
+    // element e = tid + 512 j of a tile is (row e / K, k = e % K); its byte offset inside an operand part is the
+    // same for A and B and fixed for the life of the thread
+    unsigned short off[SK::EPT];
+    {
+      int r = tid / K, k = tid - r * K;
+      const int dr = SK::WORKERS / K, dk = SK::WORKERS - dr * K;
+#pragma unroll
+      for (int j = 0; j < SK::EPT; ++j) {
+        off[j] = (unsigned short)((k >> 2) * LBO_BYTES + r * 16 + (k & 3) * 4);   // < 65536 (rows past 127: unused)
+        r += dr; k += dk;
+        if (k >= K) { k -= K; ++r; }
+      }
+    }
+    // this CTA's block of B, split once
+    {
+      const size_t b0 = (size_t)n0 * K, bend = (size_t)N * K;
+#pragma unroll
+      for (int j = 0; j < SK::EPT; ++j) {
+        const int e = tid + SK::WORKERS * j;
+        if (e < tile_elems && b0 + e < bend) {
+          float h, l;
+          split_tf32_rn(__ldg(B + b0 + e), h, l);
+          *reinterpret_cast<float *>(b_hi + off[j]) = h;
+          *reinterpret_cast<float *>(b_lo + off[j]) = l;
+        }
+      }
+    }
+    // accumulator i & 1 -> C, after the MMAs of tile i completed.  Warp w may read tensor-memory lanes
+    // 32 (w % 4) ..; it takes columns 32 (w / 4) .. of them, sixteen at a time: after tcgen05.ld a lane holds 16
+    // columns of ONE row, the block is turned through the warp's private staging rows, and every store
+    // instruction writes two 64-byte row segments.
+    float *stage = reinterpret_cast<float *>(smem + SK::OFF_STAGE) + warp * 32 * SK::EPI_ROW;
+    auto store_tile = [&](int i) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int lane_base = (warp & 3) * 32, m0 = (slot + i * ctas_per_blk) * TBM;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int c0 = (warp >> 2) * 32 + 16 * h, gn0 = n0 + c0;
+        if (gn0 >= N) break;   // warp-uniform: the rest of this block lies beyond the last column
+        uint32_t r[16];
+        const uint32_t taddr = tmem_d + (uint32_t)((i & 1) * TBN) + ((uint32_t)lane_base << 16) + (uint32_t)c0;
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
+            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+              "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+            : "r"(taddr));
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (h == 0) SK_STAMP(8 + 8 * (i + 1));
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+          *reinterpret_cast<uint4 *>(stage + lane * SK::EPI_ROW + 4 * q) = make_uint4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
+        __syncwarp();
+        const int rsub = lane >> 4, col = lane & 15;
+        const bool col_ok = gn0 + col < N;
+        float v[16];
+#pragma unroll
+        for (int it = 0; it < 16; ++it) v[it] = stage[(2 * it + rsub) * SK::EPI_ROW + col];
+        if (h == 0) SK_STAMP(9 + 8 * (i + 1));
+#pragma unroll
+        for (int it = 0; it < 16; ++it) {
+          const int grow = m0 + lane_base + 2 * it + rsub;
+          if (col_ok && grow < M) C[(size_t)grow * N + gn0 + col] = v[it];
+        }
+        if (h == 0) SK_STAMP(10 + 8 * (i + 1));
+        __syncwarp();
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      SK_STAMP(11 + 8 * (i + 1));
+    };
+    SK_STAMP(1);
+    for (int i = 0; i < nt; ++i) {
+      // tile i has landed in the linear buffer; tile i-1 is multiplied: its accumulator is complete and the
+      // operand parts of A may be overwritten
+      if (!*failed && !mbar_wait(bar_load, (uint32_t)(i & 1))) *failed = 1;
+      SK_STAMP(4 + 8 * i);
+      if (i >= 1 && !*failed && !mbar_wait(bar_done, (uint32_t)((i - 1) & 1))) *failed = 1;
+      SK_STAMP(5 + 8 * i);
+      if (has_extra) {
+        // four threads per row, every fourth k each (all loads first, then one chain of multiply-adds), combined in
+        // a fixed order
+        const int r = tid >> 2, part = tid & 3, gm = (slot + i * ctas_per_blk) * TBM + r;
+        const float *ar = lin + r * K + part;
+        for (int x = 0; x < n_extra; ++x) {
+          const float *bx = B + (size_t)(nblk * TBN + x) * K + part;
+          float av[SK::KP_MAX / 4], bv[SK::KP_MAX / 4];
+#pragma unroll
+          for (int m = 0; m < SK::KP_MAX / 4; ++m) {
+            const bool in = 4 * m + part < K;
+            av[m] = in ? ar[4 * m] : 0.0f;
+            bv[m] = in ? __ldg(bx + 4 * m) : 0.0f;
+          }
+          float acc = 0.0f;
+#pragma unroll
+          for (int m = 0; m < SK::KP_MAX / 4; ++m) acc = fmaf(av[m], bv[m], acc);
+          acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+          acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+          if (part == 0 && gm < M) C[(size_t)gm * N + nblk * TBN + x] = acc;
+        }
+      }
+      SK_STAMP(6 + 8 * i);
+      {
+        float v[SK::EPT];
+#pragma unroll
+        for (int j = 0; j < SK::EPT; ++j) {
+          const int e = tid + SK::WORKERS * j;
+          v[j] = e < tile_elems ? lin[e] : 0.0f;
+        }
+#pragma unroll
+        for (int j = 0; j < SK::EPT; ++j) {
+          const int e = tid + SK::WORKERS * j;
+          if (e < tile_elems) {
+            float h, l;
+            split_tf32_rn(v[j], h, l);
+            *reinterpret_cast<float *>(a_hi + off[j]) = h;
+            *reinterpret_cast<float *>(a_lo + off[j]) = l;
+          }
+        }
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // this thread's writes -> tensor-core proxy
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_ready);
+      SK_STAMP(7 + 8 * i);
+      if (i >= 1 && !*failed) store_tile(i - 1);   // while the tensor core multiplies tile i
+    }
+    if (nt > 0 && !*failed && !mbar_wait(bar_done, (uint32_t)((nt - 1) & 1))) *failed = 1;
+    if (nt > 0 && !*failed) store_tile(nt - 1);
+  } else if (lane == 0) {
+    // ---- copy and MMA issue: one thread -------------------------------------------------------------------
+    constexpr uint32_t ID = IDesc<true, true, TBN>::value;
+    auto load_tile = [&](int i) {   // the CTA's i-th row tile -> linear buffer (rows past M keep stale values: never stored)
+      const size_t a0 = (size_t)(slot + i * ctas_per_blk) * TBM * K, aend = (size_t)M * K;
+      const size_t left = aend - a0;
+      const uint32_t elems = left < (size_t)tile_elems ? (uint32_t)left : (uint32_t)tile_elems;
+      const uint32_t bulk = (elems * 4u) & ~15u;
+      for (uint32_t e = bulk / 4; e < elems; ++e) lin[e] = A[a0 + e];   // at most three floats of a ragged last tile
+      mbar_expect_tx(bar_load, bulk);   // (release: the plain stores above are visible to whoever sees the phase)
+      bulk_load(smem_u32(lin), A + a0, bulk, bar_load);
+    };
+    if (nt > 0) load_tile(0);
+    for (int i = 0; i < nt; ++i) {
+      if (*failed || !mbar_wait(bar_ready, (uint32_t)(i & 1))) {
+        *failed = 1;
+        break;
+      }
+      if (i + 1 < nt) load_tile(i + 1);   // every worker has read tile i out of the linear buffer
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t d = tmem_d + (uint32_t)((i & 1) * TBN);
+      const uint32_t ah = smem_u32(a_hi), al = smem_u32(a_lo), bh = smem_u32(b_hi), bl = smem_u32(b_lo);
+      for (int ks = 0; ks < ksteps; ++ks) {
+        const uint32_t adv = ks * 2 * LBO_BYTES;   // 8 tf32 along k: two 16-byte chunks
+        const uint64_t dah = make_desc<true>(ah + adv), dal = make_desc<true>(al + adv);
+        const uint64_t dbh = make_desc<true>(bh + adv), dbl = make_desc<true>(bl + adv);
+        mma_tf32(d, dal, dbh, ID, ks ? 1u : 0u);
+        mma_tf32(d, dah, dbl, ID, 1u);
+        mma_tf32(d, dah, dbh, ID, 1u);
+      }
+      commit_to(bar_done);
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (*failed && tid == 0) atomicExch(status, 202);
+  if (warp == 0) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"((uint32_t)(2 * TBN)) : "memory");
   }
 }
 

@@ -71,11 +71,13 @@ def _render_both(ctx, d, mode, noise=True):
 
 @pytest.mark.parametrize("F,B,NB,NT", [(500, 40, 65, 257), (333, 61, 65, 257), (211, 33, 33, 129), (130, 9, 80, 400),
                                        (700, 3, 65, 130)])
-def test_band_to_tap_map_at_scale_against_a_double_precision_product(ctx, F, B, NB, NT):
-    """From 2^24 multiply-adds on the map runs on the short-reduction tile kernel: row counts that are no multiple
-    of the 128-row tile, tap counts with a one-column remainder tile (257 = 2 x 128 + 1), a two-column one (130) and
-    a wide ragged one (400), band counts up to the shared-memory limit of the kernel (80).  Single-precision
-    accumulation in band order: within a few ulps of the double-precision product."""
+def test_band_to_tap_map_at_scale_against_a_double_precision_product(ctx, F, B, NB, NT, monkeypatch):
+    """The plain single-precision tile kernel of the map (forced here; the default where the tensor-core kernel does
+    not apply, up to 1024 output tiles): row counts that are no multiple of the 128-row tile, tap counts with a
+    one-column remainder tile (257 = 2 x 128 + 1), a two-column one (130) and a wide ragged one (400), band counts
+    up to the shared-memory limit of the kernel (80).  Single-precision accumulation in band order: within a few
+    ulps of the double-precision product."""
+    monkeypatch.setenv("DGC_TAP_MAP", "tile")
     assert F * B * NB * NT >= 1 << 24
     rng = np.random.default_rng(F)
     bands = rng.uniform(0, 1, (F, B, NB)).astype(f32)
@@ -88,6 +90,32 @@ def test_band_to_tap_map_at_scale_against_a_double_precision_product(ctx, F, B, 
     d = wl.harmonic_noise_inputs(5, B=B, T=1024, K=4, F=F, nbands=NB, taps=NT)
     got = ctx.bands_to_taps(dev(d["bands"]), dev(d["W"])).cpu().numpy()
     assert np.abs(got - wl.taps_from_bands(d)).max() < 1e-5
+
+
+@pytest.mark.parametrize("rows,NB,NT", [(1010, 65, 257), (2100, 65, 257), (40001, 33, 128), (20000, 32, 136),
+                                        (9000, 72, 137), (30011, 65, 300), (64000, 65, 257), (5000, 40, 1024)])
+def test_band_to_tap_map_on_the_persistent_tensor_core_kernel(ctx, rows, NB, NT, monkeypatch):
+    """32 to 72 bands and at least 128 taps: the matmul entry point (forced here for every size; the default beyond
+    1024 output tiles) runs the map on the persistent short-reduction tensor-core kernel (3xTF32 with rounded
+    parts).  One row tile and several per CTA (the accumulators and the copy stages alternate),
+    rows that end inside a tile, up to eight leftover columns computed as plain dot products (257, 136), a ragged
+    last column block (137, 300), more column blocks than a few (1024), band counts of every alignment.  The result
+    stays within a few single-precision ulps of the double-precision product, and the same call twice gives the same
+    bits."""
+    assert rows * NB * NT >= 1 << 24, "below 2^24 multiply-adds the map does not run as a matmul"
+    rng = np.random.default_rng(rows + NB + NT)
+    bands = rng.uniform(0, 1, (rows, 1, NB)).astype(f32)
+    W = rng.standard_normal((NT, NB)).astype(f32)
+    want = bands.reshape(rows, NB).astype(np.float64) @ W.astype(np.float64).T
+    monkeypatch.setenv("DGC_TAP_MAP", "tc")
+    before = ctx.gemm_path_counts()
+    got_dev = ctx.bands_to_taps(dev(bands), dev(W))
+    got = got_dev.cpu().numpy().reshape(rows, NT)
+    after = ctx.gemm_path_counts()
+    assert sum(after) == sum(before) + 1, "the map did not go through the matmul entry point"
+    assert np.abs(got - want).max() < 2e-6 * np.abs(want).max()
+    again = ctx.bands_to_taps(dev(bands), dev(W)).cpu().numpy().reshape(rows, NT)
+    assert np.array_equal(got, again)
 
 
 @pytest.mark.parametrize("shape", [dict(B=2, T=4096, K=100, F=64), dict(B=3, T=5000, K=7, F=33),
