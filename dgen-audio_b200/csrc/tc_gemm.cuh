@@ -495,22 +495,36 @@ tc_gemm_kk_kernel(const float *__restrict__ A, const float *__restrict__ B, cons
       src0[i] = (op ? B : A) + (rowok[i] ? (size_t)gr * K : 0) + k_begin + 4 * kc;
       soff[i] = op * G::OPER + G::unit_offset(r, kc);
     }
+    // A4 (rows only 4-byte aligned): the tile is copied float by float, element e = tid + 256 i -> (row e / BK,
+    // k = e % BK), so the lanes of a warp copy consecutive floats of two rows (a unit-wise assignment would
+    // make every instruction touch eight rows).  256 % BK == 0: k is the same for all of a thread's elements, its
+    // rows are 16 apart, and each element's place in shared memory moves by a constant from one to the next.
+    static_assert(!A4 || (BK == 16 && BN == TBN), "the 4-byte copy path is written for 16-wide k tiles and 128 columns");
+    constexpr int EPT4 = (TBM + BN) * BK / THREADS;          // 16 elements per thread: 8 of A, 8 of B
+    const int k4 = tid % BK, r4 = tid / BK;                  // A4: this thread's k and first row
+    const int soff4 = G::unit_offset(r4, k4 >> 2) + (k4 & 3) * 4;
+    const int dsoff4 = G::unit_offset(r4 + THREADS / BK, k4 >> 2) - G::unit_offset(r4, k4 >> 2);
     auto issue_tile = [&](int kt) {
       if (kt < KT) {
         const int k0 = kt * BK;   // relative to k_begin
         const uint32_t st = smem_u32(raw + (kt % G::RAW) * G::RAW_STAGE);
+        if (A4) {
+          const bool kin = k_begin + k0 + k4 < k_end;
 #pragma unroll
-        for (int i = 0; i < UPT; ++i) {
-          int bytes = (k_end - k_begin - k0 - kc4[i]) * 4;
-          bytes = rowok[i] ? (bytes > 16 ? 16 : (bytes < 0 ? 0 : bytes)) : 0;
-          if (A4) {
+          for (int i = 0; i < EPT4; ++i) {
+            const int op = i >= EPT4 / 2, r = r4 + (THREADS / BK) * (i - op * (EPT4 / 2));
+            const int gr = (op ? n0 : m0) + r;
+            const bool in = kin && gr < (op ? N : M);
+            cp_async4(st + op * G::OPER + soff4 + (i - op * (EPT4 / 2)) * dsoff4,
+                      in ? (op ? B : A) + (size_t)gr * K + k_begin + k0 + k4 : A, in ? 4 : 0);
+          }
+        } else {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const bool in = 4 * e < bytes;
-              cp_async4(st + soff[i] + 4 * e, in ? src0[i] + k0 + e : A, in ? 4 : 0);
-            }
-          } else
-          cp_async16(st + soff[i], bytes > 0 ? src0[i] + k0 : A, bytes);   // 0 bytes: zero fill, any valid address
+          for (int i = 0; i < UPT; ++i) {
+            int bytes = (k_end - k_begin - k0 - kc4[i]) * 4;
+            bytes = rowok[i] ? (bytes > 16 ? 16 : (bytes < 0 ? 0 : bytes)) : 0;
+            cp_async16(st + soff[i], bytes > 0 ? src0[i] + k0 : A, bytes);   // 0 bytes: zero fill, any valid address
+          }
         }
       }
       asm volatile("cp.async.commit_group;" ::: "memory");   // one group per call keeps the counting uniform
@@ -525,12 +539,25 @@ tc_gemm_kk_kernel(const float *__restrict__ A, const float *__restrict__ B, cons
       asm volatile("cp.async.wait_group %0;" ::"n"(G::PF) : "memory");   // this thread's chunks of tile kt landed
       if (kt == 0) KK_STAMP(2);
       char *st = raw + (kt % G::RAW) * G::RAW_STAGE, *lo = lob + (kt & 1) * G::RAW_STAGE;
+      if (A4) {
+        float v[EPT4];
 #pragma unroll
-      for (int i = 0; i < UPT; ++i) {
-        const float4 v = *reinterpret_cast<const float4 *>(st + soff[i]);
-        float4 h, l;
-        split_tf32(v.x, h.x, l.x); split_tf32(v.y, h.y, l.y); split_tf32(v.z, h.z, l.z); split_tf32(v.w, h.w, l.w);
-        *reinterpret_cast<float4 *>(lo + soff[i]) = l;
+        for (int i = 0; i < EPT4; ++i)
+          v[i] = *reinterpret_cast<const float *>(st + (i >= EPT4 / 2) * G::OPER + soff4 + (i % (EPT4 / 2)) * dsoff4);
+#pragma unroll
+        for (int i = 0; i < EPT4; ++i) {
+          float h, l;
+          split_tf32(v[i], h, l);
+          *reinterpret_cast<float *>(lo + (i >= EPT4 / 2) * G::OPER + soff4 + (i % (EPT4 / 2)) * dsoff4) = l;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < UPT; ++i) {
+          const float4 v = *reinterpret_cast<const float4 *>(st + soff[i]);
+          float4 h, l;
+          split_tf32(v.x, h.x, l.x); split_tf32(v.y, h.y, l.y); split_tf32(v.z, h.z, l.z); split_tf32(v.w, h.w, l.w);
+          *reinterpret_cast<float4 *>(lo + soff[i]) = l;
+        }
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // this thread's writes -> tensor-core proxy
       __syncwarp();
