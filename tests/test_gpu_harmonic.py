@@ -93,13 +93,15 @@ def test_band_to_tap_map_at_scale_against_a_double_precision_product(ctx, F, B, 
 
 
 @pytest.mark.parametrize("rows,NB,NT", [(1010, 65, 257), (2100, 65, 257), (40001, 33, 128), (20000, 32, 136),
-                                        (9000, 72, 137), (30011, 65, 300), (64000, 65, 257), (5000, 40, 1024)])
+                                        (9000, 72, 137), (30011, 65, 300), (64000, 65, 257), (5000, 40, 1024),
+                                        (100, 72, 2400), (129, 64, 2100)])
 def test_band_to_tap_map_on_the_persistent_tensor_core_kernel(ctx, rows, NB, NT, monkeypatch):
     """32 to 72 bands and at least 128 taps: the matmul entry point (forced here for every size; the default beyond
     1024 output tiles) runs the map on the persistent short-reduction tensor-core kernel (3xTF32 with rounded
     parts).  One row tile and several per CTA (the accumulators and the copy stages alternate),
     rows that end inside a tile, up to eight leftover columns computed as plain dot products (257, 136), a ragged
-    last column block (137, 300), more column blocks than a few (1024), band counts of every alignment.  The result
+    last column block (137, 300), more column blocks than a few (1024), fewer rows than one tile and a second tile
+    of a single row (100 and 129 rows), band counts of every alignment.  The result
     stays within a few single-precision ulps of the double-precision product, and the same call twice gives the same
     bits."""
     assert rows * NB * NT >= 1 << 24, "below 2^24 multiply-adds the map does not run as a matmul"
