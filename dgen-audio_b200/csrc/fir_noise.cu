@@ -720,10 +720,10 @@ DGC_EXPORT int32_t dgc_bands_to_taps(dgc_ctx *ctx, const float *bands_dev, const
   DGC_REQUIRE(ctx, rows > 0 && nbands > 0 && taps > 0, "size out of range");
   // From 2^24 multiply-adds on the map runs as a matmul.  For 32 to 72 bands and at least 128 taps: the persistent
   // short-reduction tensor-core kernel of the matmul entry point (3xTF32 with rounded parts; a CTA keeps its 128
-  // taps of the matrix in shared memory and streams row tiles of the bands through two accumulators): 9 us for the
-  // 16-voice map and 0.135 ms for the 256-voice one, against 28 us and 0.32 ms for the plain fp32 tile kernel and
-  // 0.30 ms for the general tensor-core pipeline; whole steps 0.164 against 0.172 ms (16 voices) and 2.15 against
-  // 2.32 ms (256).  Other shapes: the tile kernel up to 1024 output tiles, the matmul entry point beyond.
+  // taps of the matrix in shared memory and streams row tiles of the bands through two accumulators): 17 us for
+  // the 16-voice map and 0.124 ms for the 256-voice one under the profiler, against 28 us and 0.32 ms for the plain
+  // fp32 tile kernel and 0.30 ms for the general tensor-core pipeline; whole steps 0.166 against 0.172 ms (16
+  // voices) and 2.15 against 2.32 ms (256).  Other shapes: the tile kernel up to 1024 output tiles, the matmul entry point beyond.
   // DGC_TAP_MAP=tile|tc forces the tile kernel / the matmul entry point.
   const char *tmap_env = getenv("DGC_TAP_MAP");   // read per call: a test can switch kernels inside one process
   const int tmap_mode = !tmap_env ? 0 : strcmp(tmap_env, "tc") == 0 ? 1 : strcmp(tmap_env, "tile") == 0 ? 2 : 0;

@@ -631,7 +631,7 @@ tc_gemm_kk_kernel(const float *__restrict__ A, const float *__restrict__ B, cons
 //            kc * LBO_BYTES + r * 16; k is padded to a multiple of 8 with zeros that are written once
 //   multiply one thread issues the 3 x ceil(K / 8) MMAs of the tile into one of TWO 128-column accumulators
 //   store    while the tensor core works on tile i, the worker warps move tile i-1 from the other accumulator to
-//            global memory (32 x 16 blocks turned through shared memory into row segments)
+//            global memory (32 x 16 blocks turned through shared memory into 64-byte row segments)
 // N % 128 <= SK::EXTRA_MAX leftover columns (the 257th tap) are plain fp32 dot products of the CTAs of the
 // last column block, from the linear tile, instead of a third block of 127 empty columns.
 // Every wait is bounded; on expiry the kernel raises status 202, stops waiting everywhere and frees its TMEM.
@@ -764,15 +764,17 @@ tc_gemm_smallk_kernel(const float *__restrict__ A, const float *__restrict__ B, 
         for (int q = 0; q < 4; ++q)
           *reinterpret_cast<uint4 *>(stage + lane * SK::EPI_ROW + 4 * q) = make_uint4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
         __syncwarp();
+        // an instruction stores rows r and r + 4: 4 x 20 floats apart, i.e. 16 banks apart, so the two 16-float
+        // segments it reads from the staging rows cover all 32 banks once
         const int rsub = lane >> 4, col = lane & 15;
         const bool col_ok = gn0 + col < N;
         float v[16];
 #pragma unroll
-        for (int it = 0; it < 16; ++it) v[it] = stage[(2 * it + rsub) * SK::EPI_ROW + col];
+        for (int it = 0; it < 16; ++it) v[it] = stage[((it & 3) + 8 * (it >> 2) + 4 * rsub) * SK::EPI_ROW + col];
         if (h == 0) SK_STAMP(9 + 8 * (i + 1));
 #pragma unroll
         for (int it = 0; it < 16; ++it) {
-          const int grow = m0 + lane_base + 2 * it + rsub;
+          const int grow = m0 + lane_base + (it & 3) + 8 * (it >> 2) + 4 * rsub;
           if (col_ok && grow < M) C[(size_t)grow * N + gn0 + col] = v[it];
         }
         if (h == 0) SK_STAMP(10 + 8 * (i + 1));
